@@ -1,0 +1,167 @@
+/*
+ * moe_b200.h -- C ABI of the B200 (sm_100a) dropless MoE block kernels.
+ *
+ * The library is a drop-in for the GPU half of nanoSpeaker's MoE block: each entry point below
+ * replaces one stage that the reference runs as Triton kernels (src/model/moe_kernel.py) or as
+ * plain PyTorch (src/model/router.py, src/model/moe.py), and is what a host binding (ctypes,
+ * pybind, a torch.library op) calls.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer owned by the caller unless marked "host".
+ *   - Activations, weights and per-pair rows are bf16, row-major, 16-byte aligned.
+ *   - Index tensors are int32 except topk_idx, which is int64 (what torch.topk returns).
+ *   - Nothing here allocates, frees or synchronises; work is queued on `stream`
+ *     (a cudaStream_t passed as void*).
+ *   - Return value: MOE_B200_OK or a negative MOE_B200_ERR_* (see moe_b200_error_string).
+ *   - `status` is a device int32 word the kernels set non-zero when they notice a problem while
+ *     running (a bounded wait that ran out = 1, an expert id out of range = 2). The host reads it
+ *     whenever it wants to pay for the synchronisation.
+ *   - "slot order": pairs (token, expert) sorted by expert, every expert's run padded to a
+ *     multiple of 128 rows; pad slots hold the sentinel n_pairs in sorted_ids and zero rows in
+ *     every slot-ordered activation buffer. l_cap = moe_b200_l_cap(n_pairs, n_experts) rows.
+ */
+#ifndef MOE_B200_H_
+#define MOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOE_B200_OK 0
+#define MOE_B200_ERR_SHAPE (-1)       /* a size is negative, zero where it may not be, or inconsistent */
+#define MOE_B200_ERR_NULL (-2)        /* a required pointer is NULL */
+#define MOE_B200_ERR_ALIGN (-3)       /* a pointer or row stride is not 16-byte aligned */
+#define MOE_B200_ERR_SCRATCH (-4)     /* scratch buffer missing or too small */
+#define MOE_B200_ERR_UNSUPPORTED (-5) /* shape / activation the kernels do not cover */
+#define MOE_B200_ERR_TMA (-6)         /* the driver refused a tensor map */
+#define MOE_B200_ERR_CUDA (-7)        /* a launch failed; see cudaGetLastError */
+
+/* Activation ids; same numbering as KERNEL_ACTIVATIONS in src/model/moe_kernel.py:75. */
+#define MOE_B200_ACT_SILU 0
+#define MOE_B200_ACT_GELU 1
+#define MOE_B200_ACT_RELU 2
+#define MOE_B200_ACT_SIGMOID 3
+#define MOE_B200_ACT_TANH 4
+
+/* ABI version of this header. */
+int32_t moe_b200_abi_version(void);
+
+/* Text for a MOE_B200_ERR_* code (host pointer, static storage). */
+const char* moe_b200_error_string(int32_t code);
+
+/* Worst-case padded pair count, a multiple of 128.
+ * Replaces _l_cap (src/model/moe_kernel.py:100-108). */
+int64_t moe_b200_l_cap(int64_t n_pairs, int32_t n_experts);
+
+/* Bytes of scratch moe_b200_dispatch needs (per-block expert histograms). */
+size_t moe_b200_dispatch_scratch_bytes(int64_t n_pairs, int32_t n_experts);
+
+/* Router top-k on fp32 logits [n_tokens, n_experts] (n_experts <= 256, top_k <= 16).
+ * Replaces the softmax / topk / renormalise half of TopKRouter.forward
+ * (src/model/router.py:79-97). Selection is by descending logit, ties to the lowest expert index,
+ * output sorted the same way. full_softmax != 0 is the training spelling (weights from the softmax
+ * over all experts, renormalised over the winners when normalize != 0 and top_k > 1; probs
+ * [n_tokens, n_experts] written when non-NULL); full_softmax == 0 is the eval spelling (softmax
+ * over the winning logits when normalize != 0, else the full-softmax probabilities).
+ * topk_w [n_tokens, top_k] fp32, topk_idx [n_tokens, top_k] int64. */
+int moe_b200_router_topk(const float* logits, int64_t n_tokens, int32_t n_experts, int32_t top_k,
+                         int32_t normalize, int32_t full_softmax, float* topk_w, int64_t* topk_idx,
+                         float* probs, void* stream);
+
+/* d(logits) [n_tokens, n_experts] fp32 from d(topk_w) [n_tokens, top_k] fp32 and, optionally,
+ * d(probs) [n_tokens, n_experts] fp32 (the balance-loss path). Replaces what autograd derives for
+ * src/model/router.py:79-97. */
+int moe_b200_router_topk_bwd(const float* logits, const int64_t* topk_idx, const float* d_topk_w,
+                             const float* d_probs, int64_t n_tokens, int32_t n_experts,
+                             int32_t top_k, int32_t normalize, int32_t full_softmax,
+                             float* d_logits, void* stream);
+
+/* Dispatch plan from topk_idx (flat [n_pairs] int64): replaces moe_dispatch and its four kernels
+ * (src/model/moe_kernel.py:113-209) and MoEBlock._plan (src/model/moe.py:208-223).
+ *   sorted_ids  [l_cap]      slot -> pair id, sentinel n_pairs in pad slots
+ *   expert_ids  [l_cap/128]  owner of each 128-row block (0 past the live range)
+ *   pad_offsets [E+1]        128-aligned run starts
+ *   counts      [E]          routing histogram
+ *   n_post_pad  [1]          live padded length
+ *   inv_ids     [n_pairs]    pair id -> slot
+ * Unlike the reference's atomic scatter the order inside a run is STABLE (ascending pair id), so
+ * sorted_ids with the sentinels removed equals a stable sort of the expert ids. */
+int moe_b200_dispatch(const int64_t* topk_idx, int64_t n_pairs, int32_t n_experts,
+                      int32_t* sorted_ids, int32_t* expert_ids, int32_t* pad_offsets,
+                      int32_t* counts, int32_t* n_post_pad, int32_t* inv_ids, void* scratch,
+                      size_t scratch_bytes, int32_t* status, void* stream);
+
+/* Token permute: xs[slot, :] = x[sorted_ids[slot] / top_k, :], zero rows in pad slots, for slots
+ * below n_post_pad. Replaces x.index_select(0, token_idx) (src/model/moe.py:397) and the gather
+ * loads inside _gemm1_kernel (src/model/moe_kernel.py:295-305). x [n_tokens, d_model],
+ * xs [l_cap, d_model]. */
+int moe_b200_permute(const void* x, int64_t n_tokens, int32_t d_model, int32_t top_k,
+                     const int32_t* sorted_ids, const int32_t* n_post_pad, int64_t l_cap, void* xs,
+                     void* stream);
+
+/* Token-major combine: out[t, :] = sum_j y[inv_ids[t*top_k + j], :] (+ extra[t, :] + extra2[t, :])
+ * accumulated in fp32. Replaces _reduce_kernel (src/model/moe_kernel.py:415-437) and
+ * out.index_add_ (src/model/moe.py:413); extra / extra2 (nullable, [n_tokens, d_model]) carry the
+ * shared experts' rows (src/model/moe.py:416-417). */
+int moe_b200_combine(const void* y, const int32_t* inv_ids, int64_t n_tokens, int32_t top_k,
+                     int32_t d_model, const void* extra, const void* extra2, void* out,
+                     void* stream);
+
+/* Schedule arguments shared by the row-grouped GEMMs below:
+ *   rows        rows of the slot-ordered A buffer (l_cap), or the token count when fixed_group >= 0
+ *   expert_ids, n_post_pad   from moe_b200_dispatch
+ *   fixed_group >= 0: every row uses weight matrix `fixed_group` (shared experts, rows in token
+ *               order, `rows` need not be a multiple of 128); < 0: per-block owners from expert_ids. */
+
+/* Up/gate GEMM with the GLU fused: for each live row, [g | u] = a[row] @ w_in[e] (w_in
+ * [n_groups, d_model, 2*d_hidden]); out[row] = act(g) * u ([rows, d_hidden], row stride ld_out)
+ * or, when write_raw != 0, out[row] = [g | u] ([rows, 2*d_hidden]).
+ * Replaces _gemm1_kernel (src/model/moe_kernel.py:269-323). d_hidden must be 128. */
+int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w_in,
+                     int32_t n_groups, int32_t d_hidden, const int32_t* expert_ids,
+                     const int32_t* n_post_pad, int32_t fixed_group, int32_t write_raw,
+                     int32_t activation, void* out, int64_t ld_out, int32_t* status, void* stream);
+
+/* Down GEMM with the router weight fused: y[row] = (hid[row] @ w_out[e]) * pair_w[sorted_ids[row]]
+ * (w_out [n_groups, k_dim, d_model]; weight 1 when pair_w is NULL).
+ * Replaces the forward use of _gemm2_kernel (src/model/moe_kernel.py:339-402, 603-613). */
+int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void* w_out,
+                       int32_t n_groups, int32_t d_model, const int32_t* expert_ids,
+                       const int32_t* n_post_pad, int32_t fixed_group, const int32_t* sorted_ids,
+                       const void* pair_w, int64_t n_pairs, void* y, int32_t* status, void* stream);
+
+/* Backward through the down GEMM and the GLU in one kernel: G = douts[row] @ w_out[e]^T, then with
+ * [g | u] = a1[row] and w = pair_w[pair]:  dtw[pair] = <G, act(g)*u>,
+ * da1[row] = [w*G*u*act'(g) | w*G*act(g)],  hidw[row] = w * act(g) * u.
+ * Replaces the dH use of _gemm2_kernel plus _glu_bwd_kernel
+ * (src/model/moe_kernel.py:676-692, 510-553). dtw may be NULL. */
+int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, const void* w_out,
+                             int32_t n_groups, int32_t d_hidden, const int32_t* expert_ids,
+                             const int32_t* n_post_pad, int32_t fixed_group,
+                             const int32_t* sorted_ids, const void* pair_w, int64_t n_pairs,
+                             const void* a1, int32_t activation, void* da1, void* hidw, void* dtw,
+                             int32_t* status, void* stream);
+
+/* dX GEMM: ydx[row] = da1[row] @ w_in[e]^T, reading w_in [n_groups, d_model, 2*d_hidden] in place
+ * (no transposed copy). Replaces the dX use of _gemm2_kernel and the w_in.transpose copy
+ * (src/model/moe_kernel.py:696-707). */
+int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,
+                     int32_t n_groups, int32_t d_model, const int32_t* expert_ids,
+                     const int32_t* n_post_pad, int32_t fixed_group, void* ydx, int32_t* status,
+                     void* stream);
+
+/* Per-expert weight gradient dw[e] = a_e^T @ b_e over the rows of run e
+ * (a [rows, m_dim], b [rows, n_dim], dw [n_groups, m_dim, n_dim]); empty runs give zeros.
+ * pad_offsets NULL with n_groups == 1 means one run over rows [0, rows).
+ * Replaces _dw_kernel (src/model/moe_kernel.py:453-507, 712-721). */
+int moe_b200_wgrad(const void* a, int32_t m_dim, const void* b, int32_t n_dim, int64_t rows,
+                   const int32_t* pad_offsets, int32_t n_groups, void* dw, int32_t* status,
+                   void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_B200_H_ */

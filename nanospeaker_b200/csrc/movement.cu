@@ -1,0 +1,149 @@
+// HBM-bound data movement of the MoE block: the token permute (gather rows into expert-sorted,
+// 128-aligned slot order) and the token-major combine (sum each token's top_k per-pair rows in
+// fp32). Both move 16 bytes per thread with fully coalesced rows; the roofline for them is the
+// HBM copy bandwidth.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/moe_b200.h"
+
+namespace moe {
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+
+// xs[slot, :] = x[sorted_ids[slot] / top_k, :] for live slots, zero rows for pad slots.
+// row_bytes is a multiple of 16. One thread moves one 16-byte chunk.
+__global__ void __launch_bounds__(256)
+    permute_rows_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ sorted_ids,
+                        const int32_t* __restrict__ n_post_pad, int32_t n_pairs, int32_t top_k,
+                        int32_t chunks_per_row, uint4* __restrict__ xs) {
+  const int32_t live = __ldg(n_post_pad);
+  const int64_t total = int64_t(live) * chunks_per_row;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    const int32_t slot = int32_t(i / chunks_per_row);
+    const int32_t c = int32_t(i - int64_t(slot) * chunks_per_row);
+    const int32_t pair = __ldg(sorted_ids + slot);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (pair < n_pairs) v = ld_stream(x + int64_t(pair / top_k) * chunks_per_row + c);
+    xs[i] = v;
+  }
+}
+
+__device__ __forceinline__ void acc_bf16x8(float* acc, uint4 r) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+    const float2 f = __bfloat1622float2(h);
+    acc[2 * i] += f.x;
+    acc[2 * i + 1] += f.y;
+  }
+}
+
+// out[t, :] = sum_j y[inv_ids[t*top_k + j], :]  (+ extra[t, :])  in fp32, stored as bf16.
+template <int TOPK>
+__global__ void __launch_bounds__(256)
+    combine_rows_kernel(const uint4* __restrict__ y, const int32_t* __restrict__ inv_ids,
+                        int64_t n_tokens, int32_t top_k_rt, int32_t chunks_per_row,
+                        const uint4* __restrict__ extra, const uint4* __restrict__ extra2,
+                        uint4* __restrict__ out) {
+  const int top_k = TOPK > 0 ? TOPK : top_k_rt;
+  const int64_t total = n_tokens * chunks_per_row;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t t = i / chunks_per_row;
+    const int32_t c = int32_t(i - t * chunks_per_row);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (TOPK > 0) {
+      uint4 rows[TOPK > 0 ? TOPK : 1];
+#pragma unroll
+      for (int j = 0; j < TOPK; ++j) {
+        const int32_t slot = __ldg(inv_ids + t * TOPK + j);
+        rows[j] = ld_stream(y + int64_t(slot) * chunks_per_row + c);
+      }
+#pragma unroll
+      for (int j = 0; j < TOPK; ++j) acc_bf16x8(acc, rows[j]);
+    } else {
+      for (int j = 0; j < top_k; ++j) {
+        const int32_t slot = __ldg(inv_ids + t * top_k + j);
+        acc_bf16x8(acc, ld_stream(y + int64_t(slot) * chunks_per_row + c));
+      }
+    }
+    if (extra != nullptr) acc_bf16x8(acc, ld_stream(extra + i));
+    if (extra2 != nullptr) acc_bf16x8(acc, ld_stream(extra2 + i));
+    uint32_t w[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+      w[q] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    out[i] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+}  // namespace moe
+
+using namespace moe;
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+extern "C" {
+
+int moe_b200_permute(const void* x, int64_t n_tokens, int32_t d_model, int32_t top_k,
+                     const int32_t* sorted_ids, const int32_t* n_post_pad, int64_t l_cap, void* xs,
+                     void* stream) {
+  if (d_model < 8 || d_model % 8 != 0 || top_k < 1 || n_tokens < 0 || l_cap < 0)
+    return MOE_B200_ERR_SHAPE;
+  if (l_cap == 0 || n_tokens == 0) return MOE_B200_OK;
+  if (!x || !sorted_ids || !n_post_pad || !xs) return MOE_B200_ERR_NULL;
+  if (!aligned16(x) || !aligned16(xs)) return MOE_B200_ERR_ALIGN;
+  const int32_t cpr = d_model / 8;
+  const int64_t total = l_cap * cpr;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;  // grid-stride; a multiple of the SM count
+  permute_rows_kernel<<<unsigned(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), sorted_ids, n_post_pad, int32_t(n_tokens * top_k), top_k, cpr,
+      static_cast<uint4*>(xs));
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+int moe_b200_combine(const void* y, const int32_t* inv_ids, int64_t n_tokens, int32_t top_k,
+                     int32_t d_model, const void* extra, const void* extra2, void* out,
+                     void* stream) {
+  if (d_model < 8 || d_model % 8 != 0 || top_k < 1 || n_tokens < 0) return MOE_B200_ERR_SHAPE;
+  if (n_tokens == 0) return MOE_B200_OK;
+  if (!y || !inv_ids || !out) return MOE_B200_ERR_NULL;
+  if (!aligned16(y) || !aligned16(out) || !aligned16(extra) || !aligned16(extra2))
+    return MOE_B200_ERR_ALIGN;
+  const int32_t cpr = d_model / 8;
+  const int64_t total = n_tokens * cpr;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint4* yy = static_cast<const uint4*>(y);
+  const uint4* ex = static_cast<const uint4*>(extra);
+  const uint4* ex2 = static_cast<const uint4*>(extra2);
+  uint4* oo = static_cast<uint4*>(out);
+#define LAUNCH(K) \
+  combine_rows_kernel<K><<<unsigned(blocks), 256, 0, st>>>(yy, inv_ids, n_tokens, top_k, cpr, ex, ex2, oo)
+  switch (top_k) {
+    case 1: LAUNCH(1); break;
+    case 2: LAUNCH(2); break;
+    case 4: LAUNCH(4); break;
+    case 6: LAUNCH(6); break;
+    case 8: LAUNCH(8); break;
+    default: LAUNCH(0); break;
+  }
+#undef LAUNCH
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+}  // extern "C"

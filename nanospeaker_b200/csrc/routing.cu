@@ -1,0 +1,466 @@
+// Routing for the dropless MoE block: top-k selection with softmax weights (and its backward),
+// then the dispatch plan -- per-expert histogram, 128-aligned run offsets, tile->expert map and a
+// STABLE counting-sort permutation (inside a run, pairs keep ascending pair id, which is the order
+// a stable sort of the flat expert ids gives).
+//
+// All kernels are integer / fp32 SIMT work bound by HBM and latency: warp shuffles and
+// __match_any_sync do the selection and ranking, global accesses are 16-byte vectors where the
+// layout allows.
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "../../include/moe_b200.h"
+#include "gemm.cuh"  // DevStatus
+
+namespace moe {
+
+constexpr int ALIGN_M = 128;
+constexpr int MAX_EXPERTS = 256;            // router + dispatch kernels keep per-expert state on chip
+constexpr int ROUTER_VPL = MAX_EXPERTS / 32;  // logits held per lane
+constexpr int MAX_TOPK = 16;
+
+// ----------------------------------------------------------------------------- router top-k
+// Order-preserving map fp32 -> uint32 (larger float -> larger key); NaN sorts above +inf and
+// -0.0 ties with +0.0, so ties between equal values fall to the lowest expert index below.
+__device__ __forceinline__ uint32_t float_key(float f) {
+  if (f != f) return 0xFFFFFFFFu;
+  if (f == 0.f) f = 0.f;
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// One warp per token. Selection key = (value desc, expert index asc): unique per expert, so a
+// 64-bit max-reduction over the warp finds each winner and the output is sorted the same way.
+// full_softmax != 0 : weights come from the softmax over all experts (renormalised over the k
+//                     winners when normalize != 0 and k > 1), and probs [T,E] is written if given.
+// full_softmax == 0 : normalize != 0 -> softmax over the k winning logits;
+//                     normalize == 0 -> the full-softmax probabilities of the winners.
+__global__ void __launch_bounds__(256)
+    router_topk_kernel(const float* __restrict__ logits, int64_t n_tokens, int n_experts, int top_k,
+                       int normalize, int full_softmax, float* __restrict__ topk_w,
+                       int64_t* __restrict__ topk_idx, float* __restrict__ probs) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (t >= n_tokens) return;
+  const float* row = logits + t * n_experts;
+
+  float v[ROUTER_VPL];
+  float mx = -CUDART_INF_F;
+#pragma unroll
+  for (int i = 0; i < ROUTER_VPL; ++i) {
+    const int e = i * 32 + lane;
+    v[i] = e < n_experts ? row[e] : -CUDART_INF_F;
+    mx = fmaxf(mx, v[i]);
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+
+  const bool need_full = full_softmax || !normalize;
+  float denom = 0.f;
+  if (need_full) {
+#pragma unroll
+    for (int i = 0; i < ROUTER_VPL; ++i)
+      if (i * 32 + lane < n_experts) denom += expf(v[i] - mx);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+    if (probs != nullptr) {
+#pragma unroll
+      for (int i = 0; i < ROUTER_VPL; ++i) {
+        const int e = i * 32 + lane;
+        if (e < n_experts) probs[t * n_experts + e] = expf(v[i] - mx) / denom;
+      }
+    }
+  }
+
+  uint32_t taken = 0;  // bit i: this lane's i-th logit already selected
+  float sel_val = 0.f; // lane j < top_k keeps the j-th winner
+  int sel_idx = 0;
+  for (int j = 0; j < top_k; ++j) {
+    unsigned long long best = 0ull;
+#pragma unroll
+    for (int i = 0; i < ROUTER_VPL; ++i) {
+      const int e = i * 32 + lane;
+      if (e < n_experts && !((taken >> i) & 1u)) {
+        const unsigned long long key =
+            (static_cast<unsigned long long>(float_key(v[i])) << 32) | (0xFFFFFFFFu - uint32_t(e));
+        // +1 keeps a real candidate above the "nothing left" value 0
+        best = key + 1ull > best ? key + 1ull : best;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+      best = other > best ? other : best;
+    }
+    const int e_win = int(0xFFFFFFFFu - uint32_t((best - 1ull) & 0xFFFFFFFFull));
+    const int owner = e_win & 31, slot = e_win >> 5;
+    float val = 0.f;
+#pragma unroll
+    for (int i = 0; i < ROUTER_VPL; ++i)
+      if (i == slot) val = v[i];
+    val = __shfl_sync(0xffffffffu, val, owner);
+    if (lane == owner) taken |= 1u << slot;
+    if (lane == j) {
+      sel_val = val;
+      sel_idx = e_win;
+    }
+  }
+
+  // weights: lanes [0, top_k) hold the winners
+  float wgt;
+  const bool active = lane < top_k;
+  if (need_full) {
+    wgt = active ? expf(sel_val - mx) / denom : 0.f;
+    if (normalize && top_k > 1 && full_softmax) {
+      float s = wgt;
+#pragma unroll
+      for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      wgt = wgt / s;
+    }
+  } else {
+    // softmax over the k winning logits; the first winner is the row maximum
+    const float top = __shfl_sync(0xffffffffu, sel_val, 0);
+    const float ex = active ? expf(sel_val - top) : 0.f;
+    float s = ex;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    wgt = ex / s;
+  }
+  if (active) {
+    topk_w[t * top_k + lane] = wgt;
+    topk_idx[t * top_k + lane] = sel_idx;
+  }
+}
+
+// Backward of router_topk w.r.t. the logits. Recomputes the softmax from the saved logits.
+//   full_softmax, normalize, k>1 : w_i = p_i / s,  s = sum_{i in S} p_i
+//        dp_i = (dw_i - sum_j dw_j w_j) / s on S;  dp += d_probs;  dl = p * (dp - <p, dp>)
+//   full_softmax, else           : dp_i = dw_i on S (+ d_probs), same softmax Jacobian
+//   !full_softmax, normalize     : dl_i = w_i (dw_i - sum_j w_j dw_j) on S, 0 elsewhere
+//   !full_softmax, !normalize    : dp_i = dw_i on S, softmax Jacobian
+__global__ void __launch_bounds__(256)
+    router_topk_bwd_kernel(const float* __restrict__ logits, const int64_t* __restrict__ topk_idx,
+                           const float* __restrict__ d_topk_w, const float* __restrict__ d_probs,
+                           int64_t n_tokens, int n_experts, int top_k, int normalize,
+                           int full_softmax, float* __restrict__ d_logits) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (t >= n_tokens) return;
+  const float* row = logits + t * n_experts;
+
+  float v[ROUTER_VPL], pr[ROUTER_VPL], dp[ROUTER_VPL];
+  float mx = -CUDART_INF_F;
+#pragma unroll
+  for (int i = 0; i < ROUTER_VPL; ++i) {
+    const int e = i * 32 + lane;
+    v[i] = e < n_experts ? row[e] : -CUDART_INF_F;
+    mx = fmaxf(mx, v[i]);
+    dp[i] = 0.f;
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+
+  const bool active = lane < top_k;
+  const int my_idx = active ? int(topk_idx[t * top_k + lane]) : -1;
+  const float my_dw = active ? d_topk_w[t * top_k + lane] : 0.f;
+  const bool need_full = full_softmax || !normalize;
+
+  if (!need_full) {
+    // local softmax over the winners
+    float my_l = 0.f;
+    {
+      // fetch my winner's logit from the owning lane's registers via shared index math
+      my_l = active ? row[my_idx] : -CUDART_INF_F;
+    }
+    float top = my_l;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+    const float ex = active ? expf(my_l - top) : 0.f;
+    float s = ex;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float w = ex / s;
+    float dot = w * my_dw;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    // zero the row, then scatter the k entries
+#pragma unroll
+    for (int i = 0; i < ROUTER_VPL; ++i) {
+      const int e = i * 32 + lane;
+      if (e < n_experts) d_logits[t * n_experts + e] = 0.f;
+    }
+    __syncwarp();
+    if (active) d_logits[t * n_experts + my_idx] = w * (my_dw - dot);
+    return;
+  }
+
+  float denom = 0.f;
+#pragma unroll
+  for (int i = 0; i < ROUTER_VPL; ++i) {
+    pr[i] = (i * 32 + lane < n_experts) ? expf(v[i] - mx) : 0.f;
+    denom += pr[i];
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+#pragma unroll
+  for (int i = 0; i < ROUTER_VPL; ++i) pr[i] /= denom;
+
+  // probability of my winner
+  float my_p = active ? expf(row[my_idx] - mx) / denom : 0.f;
+  float my_dp = my_dw;
+  if (normalize && top_k > 1 && full_softmax) {
+    float s = my_p;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float w = my_p / s;
+    float dot = my_dw * w;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    my_dp = (my_dw - dot) / s;
+  }
+  // scatter winners' dp into the per-lane expert slots
+  for (int j = 0; j < top_k; ++j) {
+    const int e = __shfl_sync(0xffffffffu, my_idx, j);
+    const float d = __shfl_sync(0xffffffffu, my_dp, j);
+    if ((e & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < ROUTER_VPL; ++i)
+        if (i == (e >> 5)) dp[i] += d;
+    }
+  }
+  if (d_probs != nullptr) {
+#pragma unroll
+    for (int i = 0; i < ROUTER_VPL; ++i) {
+      const int e = i * 32 + lane;
+      if (e < n_experts) dp[i] += d_probs[t * n_experts + e];
+    }
+  }
+  float inner = 0.f;
+#pragma unroll
+  for (int i = 0; i < ROUTER_VPL; ++i) inner += pr[i] * dp[i];
+#pragma unroll
+  for (int o = 16; o; o >>= 1) inner += __shfl_xor_sync(0xffffffffu, inner, o);
+#pragma unroll
+  for (int i = 0; i < ROUTER_VPL; ++i) {
+    const int e = i * 32 + lane;
+    if (e < n_experts) d_logits[t * n_experts + e] = pr[i] * (dp[i] - inner);
+  }
+}
+
+// ------------------------------------------------------------------------------- dispatch
+constexpr int DISPATCH_THREADS = 512;
+constexpr int DISPATCH_WARPS = DISPATCH_THREADS / 32;
+constexpr int DISPATCH_CHUNK = 4096;  // pairs per block; a warp owns a contiguous 256-pair slice
+constexpr int WARP_SLICE = DISPATCH_CHUNK / DISPATCH_WARPS;
+
+// Pass 1: per-block histogram of expert ids -> block_hist[block][E]; also paints this block's
+// share of sorted_ids with the sentinel so pad slots need no separate fill launch.
+__global__ void __launch_bounds__(DISPATCH_THREADS)
+    dispatch_hist_kernel(const int64_t* __restrict__ topk_idx, int64_t n_pairs, int n_experts,
+                         int32_t* __restrict__ block_hist, int32_t* __restrict__ sorted_ids,
+                         int64_t l_cap, int32_t* status) {
+  __shared__ int32_t hist[MAX_EXPERTS];
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int64_t base = int64_t(blockIdx.x) * DISPATCH_CHUNK;
+  for (int i = threadIdx.x; i < DISPATCH_CHUNK; i += blockDim.x) {
+    const int64_t pidx = base + i;
+    if (pidx < n_pairs) {
+      const int64_t e = topk_idx[pidx];
+      if (e >= 0 && e < n_experts)
+        atomicAdd(&hist[int(e)], 1);
+      else
+        atomicExch(status, ST_BAD_EXPERT);
+    }
+  }
+  // sentinel fill: each block paints an equal slice of [0, l_cap)
+  const int64_t per = (l_cap + gridDim.x - 1) / gridDim.x;
+  const int64_t lo = per * blockIdx.x;
+  const int64_t hi = lo + per < l_cap ? lo + per : l_cap;
+  for (int64_t s = lo + threadIdx.x; s < hi; s += blockDim.x) sorted_ids[s] = int32_t(n_pairs);
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x)
+    block_hist[int64_t(blockIdx.x) * n_experts + e] = hist[e];
+}
+
+// Pass 2 (one block): turn block histograms into exclusive prefixes over blocks, total counts,
+// 128-aligned run offsets, the live padded length and the tile -> expert map.
+__global__ void __launch_bounds__(1024)
+    dispatch_scan_kernel(int32_t* __restrict__ block_hist, int n_blocks, int n_experts,
+                         int32_t* __restrict__ counts, int32_t* __restrict__ pad_offsets,
+                         int32_t* __restrict__ n_post_pad, int32_t* __restrict__ expert_ids,
+                         int64_t n_tiles_cap) {
+  __shared__ int32_t off[MAX_EXPERTS + 1];
+  __shared__ int32_t padded[MAX_EXPERTS];
+  const int e = threadIdx.x;
+  if (e < n_experts) {
+    int32_t run = 0;
+    for (int b = 0; b < n_blocks; ++b) {
+      const int32_t c = block_hist[int64_t(b) * n_experts + e];
+      block_hist[int64_t(b) * n_experts + e] = run;
+      run += c;
+    }
+    counts[e] = run;
+    padded[e] = (run + ALIGN_M - 1) / ALIGN_M * ALIGN_M;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int32_t acc = 0;
+    for (int i = 0; i < n_experts; ++i) {
+      off[i] = acc;
+      acc += padded[i];
+    }
+    off[n_experts] = acc;
+    *n_post_pad = acc;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i <= n_experts; i += blockDim.x) pad_offsets[i] = off[i];
+  const int32_t total = off[n_experts];
+  for (int64_t tile = threadIdx.x; tile < n_tiles_cap; tile += blockDim.x) {
+    int32_t owner = 0;
+    const int64_t row = tile * ALIGN_M;
+    if (row < total) {
+      // last expert whose run starts at or before this row and is non-empty there
+      int lo = 0, hi = n_experts;  // invariant: off[lo] <= row < off[hi]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (off[mid] <= row) lo = mid; else hi = mid;
+      }
+      owner = lo;
+    }
+    expert_ids[tile] = owner;
+  }
+}
+
+// Pass 3: stable scatter. Pair i of expert e lands at
+//   pad_offsets[e] + (#pairs of e in earlier blocks) + (#pairs of e earlier in this block).
+// Inside the block each warp owns a contiguous slice; warps first count their slice, the counts are
+// prefix-summed over warps, then every warp walks its slice 32 pairs at a time and ranks equal
+// experts with __match_any_sync (lower lane = lower pair id = earlier slot).
+__global__ void __launch_bounds__(DISPATCH_THREADS)
+    dispatch_scatter_kernel(const int64_t* __restrict__ topk_idx, int64_t n_pairs, int n_experts,
+                            const int32_t* __restrict__ block_prefix,
+                            const int32_t* __restrict__ pad_offsets,
+                            int32_t* __restrict__ sorted_ids, int32_t* __restrict__ inv_ids) {
+  __shared__ int32_t cursor[DISPATCH_WARPS][MAX_EXPERTS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < DISPATCH_WARPS * MAX_EXPERTS; i += blockDim.x)
+    (&cursor[0][0])[i] = 0;
+  __syncthreads();
+
+  const int64_t wbase = int64_t(blockIdx.x) * DISPATCH_CHUNK + int64_t(warp) * WARP_SLICE;
+  int32_t my_e[WARP_SLICE / 32];
+#pragma unroll
+  for (int r = 0; r < WARP_SLICE / 32; ++r) {
+    const int64_t pidx = wbase + r * 32 + lane;
+    int32_t e = -1;
+    if (pidx < n_pairs) {
+      const int64_t ee = topk_idx[pidx];
+      e = (ee >= 0 && ee < n_experts) ? int32_t(ee) : -1;
+    }
+    my_e[r] = e;
+    if (e >= 0) atomicAdd(&cursor[warp][e], 1);
+  }
+  __syncthreads();
+  // exclusive prefix over warps, seeded with the run start and the earlier blocks' share
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    int32_t run = pad_offsets[e] + block_prefix[int64_t(blockIdx.x) * n_experts + e];
+    for (int w = 0; w < DISPATCH_WARPS; ++w) {
+      const int32_t c = cursor[w][e];
+      cursor[w][e] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < WARP_SLICE / 32; ++r) {
+    const int32_t e = my_e[r];
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    if (e >= 0) {
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      const int32_t dst = cursor[warp][e] + rank;
+      const int64_t pidx = wbase + r * 32 + lane;
+      sorted_ids[dst] = int32_t(pidx);
+      inv_ids[pidx] = dst;
+    }
+    __syncwarp();
+    if (e >= 0 && lane == 31 - __clz(peers)) cursor[warp][e] += __popc(peers);
+    __syncwarp();
+  }
+}
+
+}  // namespace moe
+
+using namespace moe;
+
+extern "C" {
+
+int64_t moe_b200_l_cap(int64_t n_pairs, int32_t n_experts) {
+  const int64_t live = n_pairs < n_experts ? n_pairs : n_experts;
+  return (n_pairs + live * (ALIGN_M - 1) + ALIGN_M - 1) / ALIGN_M * ALIGN_M;
+}
+
+size_t moe_b200_dispatch_scratch_bytes(int64_t n_pairs, int32_t n_experts) {
+  const int64_t blocks = (n_pairs + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK;
+  return size_t(blocks > 0 ? blocks : 1) * size_t(n_experts) * sizeof(int32_t);
+}
+
+int moe_b200_router_topk(const float* logits, int64_t n_tokens, int32_t n_experts, int32_t top_k,
+                         int32_t normalize, int32_t full_softmax, float* topk_w, int64_t* topk_idx,
+                         float* probs, void* stream) {
+  if (n_experts < 1 || n_experts > MAX_EXPERTS || top_k < 1 || top_k > n_experts ||
+      top_k > MAX_TOPK || n_tokens < 0)
+    return MOE_B200_ERR_SHAPE;
+  if (n_tokens == 0) return MOE_B200_OK;
+  if (!logits || !topk_w || !topk_idx) return MOE_B200_ERR_NULL;
+  const int64_t threads = n_tokens * 32;
+  const unsigned grid = unsigned((threads + 255) / 256);
+  router_topk_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      logits, n_tokens, n_experts, top_k, normalize, full_softmax, topk_w, topk_idx, probs);
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+int moe_b200_router_topk_bwd(const float* logits, const int64_t* topk_idx, const float* d_topk_w,
+                             const float* d_probs, int64_t n_tokens, int32_t n_experts,
+                             int32_t top_k, int32_t normalize, int32_t full_softmax,
+                             float* d_logits, void* stream) {
+  if (n_experts < 1 || n_experts > MAX_EXPERTS || top_k < 1 || top_k > n_experts ||
+      top_k > MAX_TOPK || n_tokens < 0)
+    return MOE_B200_ERR_SHAPE;
+  if (n_tokens == 0) return MOE_B200_OK;
+  if (!logits || !topk_idx || !d_topk_w || !d_logits) return MOE_B200_ERR_NULL;
+  const int64_t threads = n_tokens * 32;
+  const unsigned grid = unsigned((threads + 255) / 256);
+  router_topk_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      logits, topk_idx, d_topk_w, d_probs, n_tokens, n_experts, top_k, normalize, full_softmax,
+      d_logits);
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+int moe_b200_dispatch(const int64_t* topk_idx, int64_t n_pairs, int32_t n_experts,
+                      int32_t* sorted_ids, int32_t* expert_ids, int32_t* pad_offsets,
+                      int32_t* counts, int32_t* n_post_pad, int32_t* inv_ids, void* scratch,
+                      size_t scratch_bytes, int32_t* status, void* stream) {
+  if (n_experts < 1 || n_experts > MAX_EXPERTS || n_pairs < 0 || n_pairs > (int64_t(1) << 30))
+    return MOE_B200_ERR_SHAPE;
+  if (!sorted_ids && n_pairs) return MOE_B200_ERR_NULL;
+  if (!pad_offsets || !counts || !n_post_pad || !status) return MOE_B200_ERR_NULL;
+  if (scratch_bytes < moe_b200_dispatch_scratch_bytes(n_pairs, n_experts) || !scratch)
+    return MOE_B200_ERR_SCRATCH;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t l_cap = moe_b200_l_cap(n_pairs, n_experts);
+  const int blocks = int((n_pairs + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK);
+  int32_t* block_hist = static_cast<int32_t*>(scratch);
+  if (blocks > 0)
+    dispatch_hist_kernel<<<blocks, DISPATCH_THREADS, 0, st>>>(topk_idx, n_pairs, n_experts,
+                                                               block_hist, sorted_ids, l_cap, status);
+  dispatch_scan_kernel<<<1, 1024, 0, st>>>(block_hist, blocks, n_experts, counts, pad_offsets,
+                                           n_post_pad, expert_ids, l_cap / ALIGN_M);
+  if (blocks > 0)
+    dispatch_scatter_kernel<<<blocks, DISPATCH_THREADS, 0, st>>>(
+        topk_idx, n_pairs, n_experts, block_hist, pad_offsets, sorted_ids, inv_ids);
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+}  // extern "C"

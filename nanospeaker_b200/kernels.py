@@ -1,0 +1,208 @@
+"""Tensor-level wrappers around the C ABI: allocate outputs with torch, pass raw device pointers and
+the current CUDA stream, raise on any error code. One function per entry point of
+include/moe_b200.h; `moe_kernel.py` composes them into the differentiable ops.
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+ALIGN_M = 128  # rows every expert's run is padded to (src/model/moe_kernel.py:71 uses the same)
+
+# Gate activations the epilogues implement; ids as in src/model/moe_kernel.py:75.
+KERNEL_ACTIVATIONS = {"silu": 0, "swish": 0, "gelu": 1, "relu": 2, "sigmoid": 3, "tanh": 4}
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("moe_b200 kernels take CUDA tensors only; there is no CPU path")
+
+
+_status_words = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """The per-device int32 status word kernels write problems into (0 = none seen)."""
+    dev = torch.device(device)
+    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
+    w = _status_words.get(key)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status_words[key] = w
+    return w
+
+
+def check_status(device) -> None:
+    """Synchronising read of the status word; raises if a kernel flagged a problem."""
+    w = status_word(device)
+    code = int(w.item())
+    if code:
+        w.zero_()
+        what = {1: "a bounded wait inside a GEMM kernel ran out",
+                2: "an expert id outside [0, n_experts) reached the dispatch"}.get(code, "unknown")
+        raise RuntimeError(f"moe_b200 device status {code}: {what}")
+
+
+def l_cap(n_pairs: int, n_experts: int) -> int:
+    """Worst-case padded pair count (pure arithmetic, safe without a GPU)."""
+    live = min(n_experts, n_pairs)
+    return (n_pairs + live * (ALIGN_M - 1) + ALIGN_M - 1) // ALIGN_M * ALIGN_M
+
+
+def router_topk(logits: torch.Tensor, top_k: int, normalize: bool, full_softmax: bool,
+                want_probs: bool) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """fp32 logits [T, E] -> (topk_w fp32 [T, k], topk_idx int64 [T, k], probs fp32 [T, E] | None)."""
+    _need_cuda(logits)
+    logits = logits.contiguous()
+    t, e = logits.shape
+    w = torch.empty((t, top_k), dtype=torch.float32, device=logits.device)
+    idx = torch.empty((t, top_k), dtype=torch.int64, device=logits.device)
+    probs = torch.empty_like(logits) if want_probs else None
+    _lib.check(_lib.load().moe_b200_router_topk(
+        logits.data_ptr(), t, e, top_k, int(normalize), int(full_softmax), w.data_ptr(),
+        idx.data_ptr(), _lib.ptr(probs), _stream(logits)), "moe_b200_router_topk")
+    return w, idx, probs
+
+
+def router_topk_bwd(logits, topk_idx, d_topk_w, d_probs, normalize: bool,
+                    full_softmax: bool) -> torch.Tensor:
+    _need_cuda(logits, topk_idx, d_topk_w, d_probs)
+    logits = logits.contiguous()
+    t, e = logits.shape
+    k = topk_idx.shape[-1]
+    d_topk_w = d_topk_w.to(torch.float32).contiguous()
+    d_probs = None if d_probs is None else d_probs.to(torch.float32).contiguous()
+    out = torch.empty_like(logits)
+    _lib.check(_lib.load().moe_b200_router_topk_bwd(
+        logits.data_ptr(), topk_idx.contiguous().data_ptr(), d_topk_w.data_ptr(),
+        _lib.ptr(d_probs), t, e, k, int(normalize), int(full_softmax), out.data_ptr(),
+        _stream(logits)), "moe_b200_router_topk_bwd")
+    return out
+
+
+def dispatch(topk_idx: torch.Tensor, n_experts: int):
+    """int64 topk_idx [T, k] -> (sorted_ids, expert_ids, pad_offsets, counts, n_post_pad, inv_ids)."""
+    _need_cuda(topk_idx)
+    flat = topk_idx.reshape(-1).contiguous()
+    if flat.dtype != torch.int64:
+        flat = flat.to(torch.int64)
+    m = flat.numel()
+    dev, i32 = flat.device, torch.int32
+    cap = l_cap(m, n_experts)
+    lib = _lib.load()
+    sids = torch.empty(cap, dtype=i32, device=dev)
+    eids = torch.empty(cap // ALIGN_M, dtype=i32, device=dev)
+    offs = torch.empty(n_experts + 1, dtype=i32, device=dev)
+    counts = torch.empty(n_experts, dtype=i32, device=dev)
+    npp = torch.empty(1, dtype=i32, device=dev)
+    inv = torch.empty(m, dtype=i32, device=dev)
+    nbytes = lib.moe_b200_dispatch_scratch_bytes(m, n_experts)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    _lib.check(lib.moe_b200_dispatch(
+        flat.data_ptr(), m, n_experts, sids.data_ptr(), eids.data_ptr(), offs.data_ptr(),
+        counts.data_ptr(), npp.data_ptr(), inv.data_ptr(), scratch.data_ptr(), nbytes,
+        status_word(dev).data_ptr(), _stream(flat)), "moe_b200_dispatch")
+    return sids, eids, offs, counts, npp, inv
+
+
+def permute(x: torch.Tensor, top_k: int, sorted_ids: torch.Tensor,
+            n_post_pad: torch.Tensor) -> torch.Tensor:
+    """x [T, D] -> xs [l_cap, D] in slot order; rows at or past n_post_pad are left unwritten."""
+    _need_cuda(x)
+    t, d = x.shape
+    cap = sorted_ids.numel()
+    xs = torch.empty((cap, d), dtype=x.dtype, device=x.device)
+    _lib.check(_lib.load().moe_b200_permute(
+        x.data_ptr(), t, d, top_k, sorted_ids.data_ptr(), n_post_pad.data_ptr(), cap,
+        xs.data_ptr(), _stream(x)), "moe_b200_permute")
+    return xs
+
+
+def combine(y: torch.Tensor, inv_ids: torch.Tensor, n_tokens: int, top_k: int,
+            extra: Optional[torch.Tensor] = None,
+            extra2: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need_cuda(y)
+    d = y.shape[1]
+    out = torch.empty((n_tokens, d), dtype=y.dtype, device=y.device)
+    _lib.check(_lib.load().moe_b200_combine(
+        y.data_ptr(), inv_ids.data_ptr(), n_tokens, top_k, d, _lib.ptr(extra), _lib.ptr(extra2),
+        out.data_ptr(), _stream(y)), "moe_b200_combine")
+    return out
+
+
+def up_gemm(a, w_in, expert_ids, n_post_pad, fixed_group: int, write_raw: bool, act: int,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a [rows, D] x w_in [G, D, 2H] -> act(g)*u [rows, H] (or raw [g|u] [rows, 2H])."""
+    _need_cuda(a, w_in)
+    rows, d = a.shape
+    g, _, h2 = w_in.shape
+    h = h2 // 2
+    if out is None:
+        out = torch.empty((rows, h2 if write_raw else h), dtype=a.dtype, device=a.device)
+    _lib.check(_lib.load().moe_b200_up_gemm(
+        a.data_ptr(), rows, d, w_in.data_ptr(), g, h, _lib.ptr(expert_ids), _lib.ptr(n_post_pad),
+        fixed_group, int(write_raw), act, out.data_ptr(), out.stride(0),
+        status_word(a.device).data_ptr(), _stream(a)), "moe_b200_up_gemm")
+    return out
+
+
+def down_gemm(hid, w_out, expert_ids, n_post_pad, fixed_group: int, sorted_ids, pair_w,
+              n_pairs: int) -> torch.Tensor:
+    """hid [rows, K] x w_out [G, K, D] -> y [rows, D], scaled per row by pair_w[sorted_ids[row]]."""
+    _need_cuda(hid, w_out)
+    rows, k = hid.shape
+    g, _, d = w_out.shape
+    y = torch.empty((rows, d), dtype=hid.dtype, device=hid.device)
+    _lib.check(_lib.load().moe_b200_down_gemm(
+        hid.data_ptr(), rows, k, w_out.data_ptr(), g, d, _lib.ptr(expert_ids),
+        _lib.ptr(n_post_pad), fixed_group, _lib.ptr(sorted_ids), _lib.ptr(pair_w), n_pairs,
+        y.data_ptr(), status_word(hid.device).data_ptr(), _stream(hid)), "moe_b200_down_gemm")
+    return y
+
+
+def dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, fixed_group: int, sorted_ids, pair_w,
+                    n_pairs: int, a1, act: int, want_dtw: bool):
+    """-> (da1 [rows, 2H], hidw [rows, H], dtw [n_pairs] | None)."""
+    _need_cuda(douts, w_out, a1)
+    rows, d = douts.shape
+    g, h, _ = w_out.shape
+    da1 = torch.empty((rows, 2 * h), dtype=douts.dtype, device=douts.device)
+    hidw = torch.empty((rows, h), dtype=douts.dtype, device=douts.device)
+    dtw = torch.empty(n_pairs, dtype=douts.dtype, device=douts.device) if want_dtw else None
+    _lib.check(_lib.load().moe_b200_dhidden_glu_bwd(
+        douts.data_ptr(), rows, d, w_out.data_ptr(), g, h, _lib.ptr(expert_ids),
+        _lib.ptr(n_post_pad), fixed_group, _lib.ptr(sorted_ids), _lib.ptr(pair_w), n_pairs,
+        a1.data_ptr(), act, da1.data_ptr(), hidw.data_ptr(), _lib.ptr(dtw),
+        status_word(douts.device).data_ptr(), _stream(douts)), "moe_b200_dhidden_glu_bwd")
+    return da1, hidw, dtw
+
+
+def dx_gemm(da1, w_in, expert_ids, n_post_pad, fixed_group: int) -> torch.Tensor:
+    """da1 [rows, 2H] x w_in[e]^T -> ydx [rows, D]."""
+    _need_cuda(da1, w_in)
+    rows, h2 = da1.shape
+    g, d, _ = w_in.shape
+    ydx = torch.empty((rows, d), dtype=da1.dtype, device=da1.device)
+    _lib.check(_lib.load().moe_b200_dx_gemm(
+        da1.data_ptr(), rows, h2 // 2, w_in.data_ptr(), g, d, _lib.ptr(expert_ids),
+        _lib.ptr(n_post_pad), fixed_group, ydx.data_ptr(), status_word(da1.device).data_ptr(),
+        _stream(da1)), "moe_b200_dx_gemm")
+    return ydx
+
+
+def wgrad(a, b, pad_offsets, n_groups: int) -> torch.Tensor:
+    """dw[e] = a_e^T @ b_e over run e's rows: a [rows, Mdim], b [rows, Ndim] -> [G, Mdim, Ndim]."""
+    _need_cuda(a, b)
+    rows, m_dim = a.shape
+    n_dim = b.shape[1]
+    dw = torch.empty((n_groups, m_dim, n_dim), dtype=a.dtype, device=a.device)
+    _lib.check(_lib.load().moe_b200_wgrad(
+        a.data_ptr(), m_dim, b.data_ptr(), n_dim, rows, _lib.ptr(pad_offsets), n_groups,
+        dw.data_ptr(), status_word(a.device).data_ptr(), _stream(a)), "moe_b200_wgrad")
+    return dw
