@@ -1,0 +1,430 @@
+"""Benchmark of the MoE block on B200: tokens/s of one forward+backward of the block.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N=1): BASELINE config 2 -- T=16384 tokens (8 x 2048), d_model 576, 76 routed + 2 shared
+SwiGLU experts (d_expert 128), top-6 softmax routing, bf16 with fp32 accumulation, training mode,
+per-expert logit bias ~N(0, 0.27) so the expert load has CV ~ 1. One step = router, dispatch,
+permute, grouped GEMMs, combine, shared experts and the full backward (dx, dW_in, dW_out,
+dW_sh_*, d_router). With N > 1 every rank runs the same per-GPU workload on its own token shard
+(weak scaling; tokens are independent, so the block's data path needs no collective).
+
+Prints ONE JSON line (rank 0). `value` times K steps with inputs resident in HBM; `e2e` times
+the same step through MoEBlock.forward/backward with the step's input copied from pinned host
+memory and the loss read back. `--impl reference` times the CPU oracle (the reference's
+pure-PyTorch path restated, see oracle/moe_oracle.py) on the host cores instead.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+D_MODEL, N_EXPERTS, TOP_K, N_SHARED, D_FF, D_HIDDEN = 576, 76, 6, 2, 192, 128
+TOKENS = 16384
+BIAS_STD = 0.27          # logit-bias spread that gives load CV ~ 1 with router W ~ N(0, 0.02)
+N_INPUT_SETS = 8         # x / dOut pairs cycled through so successive steps do not hit L2
+METRIC = "MoE-block tokens/s (fwd+bwd)"
+
+FLOP_PER_TOKEN_FWD_BWD = 10_879_488   # 3 * (routed up 1 769 472 + down 884 736 + shared 884 736 + router 87 552)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+def init_weights(seed=0):
+    """Draw order: x sets, router W, W_in, W_out, W_sh_in, W_sh_out, then the routing bias."""
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, generator=g)
+    w = {
+        "router_W": rn(D_MODEL, N_EXPERTS) * 0.02,
+        "W_in": rn(N_EXPERTS, D_MODEL, 2 * D_HIDDEN) * D_MODEL ** -0.5,
+        "W_out": rn(N_EXPERTS, D_HIDDEN, D_MODEL) * D_HIDDEN ** -0.5,
+        "W_sh_in": rn(N_SHARED, D_MODEL, 2 * D_HIDDEN) * D_MODEL ** -0.5,
+        "W_sh_out": rn(N_SHARED, D_HIDDEN, D_MODEL) * D_HIDDEN ** -0.5,
+    }
+    bias = torch.randn(N_EXPERTS, generator=torch.Generator().manual_seed(1)) * BIAS_STD
+    return {k: v.bfloat16() for k, v in w.items()}, bias
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons of one GPU, sampled while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for t, r in self.rows if t0 <= t <= t1 and len(r) == 6] or \
+               [r for _, r in self.rows if len(r) == 6]
+        sm, reasons, mx = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except ValueError:
+                continue
+            for name, v in zip(names, r[2:]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------- CPU arm
+def cpu_steps(tokens, steps, warmup, threads):
+    """Forward+backward of the oracle block on the host cores; returns (seconds per step, tokens)."""
+    from oracle import moe_oracle as O
+    torch.set_num_threads(threads)
+    w, bias = init_weights()
+    m = O.OracleBlock(D_MODEL, N_EXPERTS, D_FF, TOP_K, N_SHARED).to(torch.bfloat16)
+    with torch.no_grad():
+        m.router_W.copy_(w["router_W"])
+        m.W_in.copy_(w["W_in"])
+        m.W_out.copy_(w["W_out"])
+        m.W_sh_in.copy_(w["W_sh_in"])
+        m.W_sh_out.copy_(w["W_sh_out"])
+    m.routing_bias = bias
+    m.train()
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(tokens, D_MODEL, generator=g).bfloat16()
+    dout = torch.randn(tokens, D_MODEL, generator=g).bfloat16()
+
+    def step():
+        for p in m.parameters():
+            p.grad = None
+        xi = x.clone().requires_grad_(True)
+        out = m(xi)
+        torch.autograd.backward([out, m.aux_loss], [dout, torch.ones(())])
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    return (time.perf_counter() - t0) / max(steps, 1)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    tokens = TOKENS
+    # bound the run: one probe step decides how large a sample each step can be
+    t_probe = cpu_steps(2048, 1, 1, threads)
+    budget = 150.0 / max(args.steps + args.warmup, 1)
+    while tokens > 2048 and t_probe * (tokens / 2048) > budget:
+        tokens //= 2
+    sec = cpu_steps(tokens, args.steps, args.warmup, threads)
+    value = tokens / sec * 1.0
+    sample = (f"{tokens} of {TOKENS} tokens per step, fwd+bwd, bf16, "
+              f"torch {torch.__version__} CPU, {threads} threads")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus, tokens),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus, tokens_per_gpu=TOKENS):
+    return {
+        "workload": "BASELINE config 2: dropless MoE block fwd+bwd, T=16384 (8x2048) per GPU, "
+                    "d_model 576, 76 routed + 2 shared SwiGLU experts, d_expert 128, top-6",
+        "tokens_per_gpu": tokens_per_gpu, "global_tokens": tokens_per_gpu * n_gpus,
+        "skew": f"cv1: per-expert logit bias N(0,{BIAS_STD}), seed 1",
+        "parallelism": f"token-sharded replicas x{n_gpus}, no data-path collective",
+        "l2": f"{N_INPUT_SETS} input/dOut sets cycled (302 MB) and ~1 GB of intermediates per "
+              "step, both beyond the 126 MB L2; no explicit flush",
+    }
+
+
+# --------------------------------------------------------------------------------- GPU arm
+def build_block(device):
+    from nanospeaker_b200 import MoEBlock
+    w, bias = init_weights()
+    m = MoEBlock(D_MODEL, N_EXPERTS, d_ff=D_FF, top_k=TOP_K, n_shared=N_SHARED,
+                 capacity_factor=None).to(torch.bfloat16)
+    with torch.no_grad():
+        m.router.W.copy_(w["router_W"])
+        m.W_in.copy_(w["W_in"])
+        m.W_out.copy_(w["W_out"])
+        m.W_sh_in.copy_(w["W_sh_in"])
+        m.W_sh_out.copy_(w["W_sh_out"])
+    m = m.to(device).train()
+    m.router.logit_bias = bias.to(device)
+    return m
+
+
+def stage_rooflines(m, x, pk):
+    """Time every kernel of the step alone (CUDA events on the current stream, operands rotated
+    through 3 buffer copies so a launch does not find its input in L2) and put each next to its
+    algorithmic work."""
+    from nanospeaker_b200 import kernels as K
+    T, D, H, E, k = x.shape[0], D_MODEL, D_HIDDEN, N_EXPERTS, TOP_K
+    M = T * k
+    with torch.no_grad():
+        w, idx, _ = m.router(x)
+        sids, eids, offs, counts, npp, inv = K.dispatch(idx, E)
+        tw = w.reshape(-1).contiguous()
+        logits = (x @ m.router.W).float() + m.router.logit_bias
+        copies = lambda t: [t.clone() for _ in range(3)]
+        xs = copies(K.permute(x, k, sids, npp))
+        xr = copies(x)
+        hid = copies(K.up_gemm(xs[0], m.W_in, eids, npp, -1, False, 0))
+        a1 = K.up_gemm(xs[0], m.W_in, eids, npp, -1, True, 0)
+        y = copies(K.down_gemm(hid[0], m.W_out, eids, npp, -1, sids, tw, M))
+        da1 = copies(K.dhidden_glu_bwd(xs[0], m.W_out, eids, npp, -1, sids, tw, M, a1, 0, True)[0])
+        hs = copies(K.up_gemm(x, m.W_sh_in, None, None, 0, False, 0))
+        a1s = K.up_gemm(x, m.W_sh_in, None, None, 0, True, 0)
+        das = copies(K.dhidden_glu_bwd(x, m.W_sh_out, None, None, 0, None, None, 0, a1s, 0,
+                                       False)[0])
+        ys = K.down_gemm(hs[0], m.W_sh_out, None, None, 0, None, None, 0)
+        dwl = torch.randn_like(w, dtype=torch.float32)
+
+        GE, TF = "hbm", "tensor"
+        stages = [
+            # name, bound, work per launch (bytes or flop), launches per step, callable(i)
+            ("router_topk", GE, T * E * 4 * 2 + T * k * 12, 1,
+             lambda i: K.router_topk(logits, k, True, True, True)),
+            ("router_topk_bwd", GE, T * E * 4 * 3 + T * k * 12, 1,
+             lambda i: K.router_topk_bwd(logits, idx, dwl, logits, True, True)),
+            ("dispatch(3 kernels)", GE, M * 8 * 2 + M * 4 * 3, 1, lambda i: K.dispatch(idx, E)),
+            ("permute", GE, 2 * M * D * 2 + M * 4, 2,
+             lambda i: K.permute(xr[i % 3], k, sids, npp)),
+            ("up_gemm+glu", TF, 2.0 * M * D * 2 * H, 1,
+             lambda i: K.up_gemm(xs[i % 3], m.W_in, eids, npp, -1, False, 0)),
+            ("up_gemm raw (bwd recompute)", TF, 2.0 * M * D * 2 * H, 1,
+             lambda i: K.up_gemm(xs[i % 3], m.W_in, eids, npp, -1, True, 0)),
+            ("down_gemm+scale", TF, 2.0 * M * H * D, 1,
+             lambda i: K.down_gemm(hid[i % 3], m.W_out, eids, npp, -1, sids, tw, M)),
+            ("combine", GE, M * D * 2 + M * 4 + 3 * T * D * 2, 2,
+             lambda i: K.combine(y[i % 3], inv, T, k, ys, ys)),
+            ("dhidden+glu_bwd", TF, 2.0 * M * D * H, 1,
+             lambda i: K.dhidden_glu_bwd(xs[i % 3], m.W_out, eids, npp, -1, sids, tw, M, a1, 0,
+                                         True)),
+            ("dx_gemm", TF, 2.0 * M * 2 * H * D, 1,
+             lambda i: K.dx_gemm(da1[i % 3], m.W_in, eids, npp, -1)),
+            ("wgrad_in", TF, 2.0 * M * D * 2 * H, 1,
+             lambda i: K.wgrad(xs[i % 3], da1[i % 3], offs, E)),
+            ("wgrad_out", TF, 2.0 * M * H * D, 1,
+             lambda i: K.wgrad(hid[i % 3], xs[i % 3], offs, E)),
+            ("shared up_gemm (per expert)", TF, 2.0 * T * D * 2 * H, 2 * N_SHARED,
+             lambda i: K.up_gemm(xr[i % 3], m.W_sh_in, None, None, 0, False, 0)),
+            ("shared down_gemm (per expert)", TF, 2.0 * T * H * D, N_SHARED,
+             lambda i: K.down_gemm(hs[i % 3], m.W_sh_out, None, None, 0, None, None, 0)),
+            ("shared dhidden (per expert)", TF, 2.0 * T * D * H, N_SHARED,
+             lambda i: K.dhidden_glu_bwd(xr[i % 3], m.W_sh_out, None, None, 0, None, None, 0, a1s,
+                                         0, False)),
+            ("shared dx_gemm (per expert)", TF, 2.0 * T * 2 * H * D, N_SHARED,
+             lambda i: K.dx_gemm(das[i % 3], m.W_sh_in, None, None, 0)),
+            ("shared wgrad_in (per expert)", TF, 2.0 * T * D * 2 * H, N_SHARED,
+             lambda i: K.wgrad(xr[i % 3], das[i % 3], None, 1)),
+            ("shared wgrad_out (per expert)", TF, 2.0 * T * H * D, N_SHARED,
+             lambda i: K.wgrad(hs[i % 3], xr[i % 3], None, 1)),
+        ]
+        out = []
+        for name, bound, work, per_step, fn in stages:
+            for i in range(3):
+                fn(i)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n = 12
+            e0.record()
+            for i in range(n):
+                fn(i)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / n * 1e3
+            if bound == GE:
+                ach, peak, unit = work / us / 1e3, pk["hbm_gbs"], "GB/s"
+            else:
+                ach, peak, unit = work / us / 1e6, pk["bf16_tflops"], "TFLOP/s"
+            out.append({"kernel": name, "bound": bound, "us": round(us, 2),
+                        "launches_per_step": per_step, "achieved": round(ach, 1), "peak": peak,
+                        "unit": unit, "frac": round(ach / peak, 4)})
+    return out
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    from nanospeaker_b200 import kernels as K
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the MoE block has no CPU implementation")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pk = peaks()
+
+    m = build_block(dev)
+    g = torch.Generator().manual_seed(100 + rank)      # every rank has its own token shard
+    host_x = [torch.randn(TOKENS, D_MODEL, generator=g).bfloat16().pin_memory()
+              for _ in range(N_INPUT_SETS)]
+    dev_x = [h.to(dev) for h in host_x]
+    dev_dout = [torch.randn(TOKENS, D_MODEL, generator=g).bfloat16().to(dev)
+                for _ in range(N_INPUT_SETS)]
+    one = torch.ones((), device=dev)
+    params = list(m.parameters())
+
+    def step(i):
+        for p in params:
+            p.grad = None
+        x = dev_x[i % N_INPUT_SETS].detach().requires_grad_(True)
+        out = m(x)
+        torch.autograd.backward([out, m.aux_loss], [dev_dout[i % N_INPUT_SETS], one])
+        if args.grad_allreduce and world > 1:
+            from nanospeaker_b200.parallel import all_reduce_gradients
+            all_reduce_gradients(params)
+
+    def e2e_step(i):
+        for p in params:
+            p.grad = None
+        x = host_x[i % N_INPUT_SETS].to(dev, non_blocking=True).requires_grad_(True)
+        out = m(x)
+        loss = out.float().square().mean() + m.aux_loss
+        loss.backward()
+        return loss.item()                              # device -> host read of the step's result
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.time()
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t)
+        return ms, t0, time.time()
+
+    warmup = max(args.warmup, 3)
+    sampler = ClockSampler(local)
+    l0 = K.LAUNCHES
+    ms, t0, t1 = timed(step, args.steps, warmup)
+    launches = (K.LAUNCHES - l0) * args.steps // (args.steps + warmup)
+    clocks = sampler.stop(t0, t1)
+    K.check_status(dev)
+    e2e_ms, _, _ = timed(e2e_step, args.steps, warmup)
+
+    value = TOKENS * world * args.steps / (ms / 1e3)
+    e2e_value = TOKENS * world * args.steps / (e2e_ms / 1e3)
+
+    line = None
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(world),
+            "e2e": {"value": e2e_value, "unit": "tokens/s",
+                    "h2d_bytes_per_step": TOKENS * D_MODEL * 2, "d2h_bytes_per_step": 4,
+                    "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches, "clocks": clocks,
+            "pct_bf16_peak": {"measured_burst": 100 * value / world * FLOP_PER_TOKEN_FWD_BWD
+                              / (pk["bf16_tflops"] * 1e12),
+                              "nominal_2250": 100 * value / world * FLOP_PER_TOKEN_FWD_BWD / 2.25e15},
+            "grad_allreduce": bool(args.grad_allreduce and world > 1),
+        }
+        if not args.no_stages:
+            stages = stage_rooflines(m, dev_x[0], pk)
+            top = max(stages, key=lambda s: s["us"] * s["launches_per_step"])
+            line["roofline"] = {"kernel": top["kernel"], "bound": top["bound"],
+                                "achieved": top["achieved"], "peak": top["peak"],
+                                "unit": top["unit"], "frac": top["frac"], "traffic": None,
+                                "peak_source": pk["source"] + " (burst: kernel timed alone)"}
+            line["stages"] = stages
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            sec = cpu_steps(TOKENS, 3, 1, threads)
+            line["cpu_baseline"] = {
+                "value": TOKENS / sec, "unit": "tokens/s", "cores": threads, "kind": "port",
+                "sample": f"full T={TOKENS} fwd+bwd, 1 warm-up + 3 timed steps, bf16, "
+                          f"torch {torch.__version__} CPU"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--grad-allreduce", action="store_true",
+                    help="also all-reduce the weight gradients across ranks inside the step")
+    ap.add_argument("--no-stages", action="store_true", help="skip the per-kernel roofline pass")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

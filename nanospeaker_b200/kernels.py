@@ -24,6 +24,15 @@ def _need_cuda(*tensors) -> None:
             raise RuntimeError("moe_b200 kernels take CUDA tensors only; there is no CPU path")
 
 
+# Number of CUDA kernels this module has launched (every entry point launches a fixed number).
+LAUNCHES = 0
+
+
+def _count(n: int) -> None:
+    global LAUNCHES
+    LAUNCHES += n
+
+
 _status_words = {}
 
 
@@ -67,6 +76,7 @@ def router_topk(logits: torch.Tensor, top_k: int, normalize: bool, full_softmax:
     _lib.check(_lib.load().moe_b200_router_topk(
         logits.data_ptr(), t, e, top_k, int(normalize), int(full_softmax), w.data_ptr(),
         idx.data_ptr(), _lib.ptr(probs), _stream(logits)), "moe_b200_router_topk")
+    _count(1 if t else 0)
     return w, idx, probs
 
 
@@ -83,6 +93,7 @@ def router_topk_bwd(logits, topk_idx, d_topk_w, d_probs, normalize: bool,
         logits.data_ptr(), topk_idx.contiguous().data_ptr(), d_topk_w.data_ptr(),
         _lib.ptr(d_probs), t, e, k, int(normalize), int(full_softmax), out.data_ptr(),
         _stream(logits)), "moe_b200_router_topk_bwd")
+    _count(1 if t else 0)
     return out
 
 
@@ -108,6 +119,7 @@ def dispatch(topk_idx: torch.Tensor, n_experts: int):
         flat.data_ptr(), m, n_experts, sids.data_ptr(), eids.data_ptr(), offs.data_ptr(),
         counts.data_ptr(), npp.data_ptr(), inv.data_ptr(), scratch.data_ptr(), nbytes,
         status_word(dev).data_ptr(), _stream(flat)), "moe_b200_dispatch")
+    _count(3 if m else 1)
     return sids, eids, offs, counts, npp, inv
 
 
@@ -121,6 +133,7 @@ def permute(x: torch.Tensor, top_k: int, sorted_ids: torch.Tensor,
     _lib.check(_lib.load().moe_b200_permute(
         x.data_ptr(), t, d, top_k, sorted_ids.data_ptr(), n_post_pad.data_ptr(), cap,
         xs.data_ptr(), _stream(x)), "moe_b200_permute")
+    _count(1 if cap and t else 0)
     return xs
 
 
@@ -133,6 +146,7 @@ def combine(y: torch.Tensor, inv_ids: torch.Tensor, n_tokens: int, top_k: int,
     _lib.check(_lib.load().moe_b200_combine(
         y.data_ptr(), inv_ids.data_ptr(), n_tokens, top_k, d, _lib.ptr(extra), _lib.ptr(extra2),
         out.data_ptr(), _stream(y)), "moe_b200_combine")
+    _count(1 if n_tokens else 0)
     return out
 
 
@@ -149,6 +163,7 @@ def up_gemm(a, w_in, expert_ids, n_post_pad, fixed_group: int, write_raw: bool, 
         a.data_ptr(), rows, d, w_in.data_ptr(), g, h, _lib.ptr(expert_ids), _lib.ptr(n_post_pad),
         fixed_group, int(write_raw), act, out.data_ptr(), out.stride(0),
         status_word(a.device).data_ptr(), _stream(a)), "moe_b200_up_gemm")
+    _count(1 if rows else 0)
     return out
 
 
@@ -163,6 +178,7 @@ def down_gemm(hid, w_out, expert_ids, n_post_pad, fixed_group: int, sorted_ids, 
         hid.data_ptr(), rows, k, w_out.data_ptr(), g, d, _lib.ptr(expert_ids),
         _lib.ptr(n_post_pad), fixed_group, _lib.ptr(sorted_ids), _lib.ptr(pair_w), n_pairs,
         y.data_ptr(), status_word(hid.device).data_ptr(), _stream(hid)), "moe_b200_down_gemm")
+    _count(1 if rows else 0)
     return y
 
 
@@ -180,6 +196,7 @@ def dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, fixed_group: int, sort
         _lib.ptr(n_post_pad), fixed_group, _lib.ptr(sorted_ids), _lib.ptr(pair_w), n_pairs,
         a1.data_ptr(), act, da1.data_ptr(), hidw.data_ptr(), _lib.ptr(dtw),
         status_word(douts.device).data_ptr(), _stream(douts)), "moe_b200_dhidden_glu_bwd")
+    _count(1 if rows else 0)
     return da1, hidw, dtw
 
 
@@ -193,6 +210,7 @@ def dx_gemm(da1, w_in, expert_ids, n_post_pad, fixed_group: int) -> torch.Tensor
         da1.data_ptr(), rows, h2 // 2, w_in.data_ptr(), g, d, _lib.ptr(expert_ids),
         _lib.ptr(n_post_pad), fixed_group, ydx.data_ptr(), status_word(da1.device).data_ptr(),
         _stream(da1)), "moe_b200_dx_gemm")
+    _count(1 if rows else 0)
     return ydx
 
 
@@ -205,4 +223,5 @@ def wgrad(a, b, pad_offsets, n_groups: int) -> torch.Tensor:
     _lib.check(_lib.load().moe_b200_wgrad(
         a.data_ptr(), m_dim, b.data_ptr(), n_dim, rows, _lib.ptr(pad_offsets), n_groups,
         dw.data_ptr(), status_word(a.device).data_ptr(), _stream(a)), "moe_b200_wgrad")
+    _count(1)
     return dw

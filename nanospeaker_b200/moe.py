@@ -1,0 +1,254 @@
+"""MoEBlock: drop-in for nanoSpeaker's sparse Mixture-of-Experts feed-forward block
+(src/model/moe.py:42-474) with the dropless path running on hand-written sm_100a kernels.
+
+Constructor keywords, parameter names and shapes, the `router` sub-module, `forward`,
+`dense_forward` and the post-forward attributes `aux_loss`, `expert_counts`, `dropped` are those of
+the reference, so its callers (Block in src/model/nanospeaker.py:153-169, moe_health in
+src/train/metrics.py:84-97) and its checkpoints work unchanged.
+
+Paths, in the order `forward` tries them:
+  1. kernel    CUDA + bf16 + a named activation + no capacity cap + no bias + shapes the tiles
+               cover: router top-k, dispatch, permute, grouped GEMMs, combine and the shared
+               experts all run as the `moe_b200` ops. No host sync. A missing or failing library
+               raises; nothing is silently rerouted.
+  2. padded    a capacity_factor is set: fixed-capacity batched GEMM in torch
+               (src/model/moe.py:225-283); not a dropless path and not accelerated here.
+  3. eager     the ragged per-expert loop in torch (src/model/moe.py:377-418) for everything the
+               kernels decline (CPU, fp32/fp64, custom activations, biases).
+"""
+import math
+
+import torch
+from torch import nn
+
+from . import moe_kernel as MK
+from .glu import glu_hidden_dim, make_glu
+from .moe_kernel import KERNEL_ACTIVATIONS, fused_moe_forward, kernel_supported
+from .router import TopKRouter
+from .utils import ACTIVATIONS, resolve_activation
+
+# Capacity the "auto" setting resolves to where the kernels do not run.
+AUTO_CAPACITY = 1.25
+
+
+class MoEBlock(nn.Module):
+    """Sparse MoE feed-forward block with GLU experts (SwiGLU by default).
+
+    Args (identical to src/model/moe.py:96-112):
+        d_model, n_experts, d_ff (FFN width each expert replaces; GLU hidden = 2*d_ff//3,
+        default 4*d_model), top_k, n_shared (always-on experts), capacity_factor (float, None
+        for dropless, or "auto" = None where the kernels run and 1.25 elsewhere), activation,
+        bias, normalize_weights, aux_loss_coef, noise_std, fused (accepted, unused: the GLU is
+        fused into the GEMM epilogue on the kernel path), kernel, std.
+    """
+
+    def __init__(self, d_model, n_experts, d_ff=None, top_k=2, n_shared=0,
+                 capacity_factor="auto", activation="silu", bias=False, normalize_weights=True,
+                 aux_loss_coef=1e-2, noise_std=0.0, fused=True, kernel=True, std=0.02):
+        super().__init__()
+        d_ff = 4 * d_model if d_ff is None else d_ff
+        self.d_model, self.n_experts, self.d_ff = d_model, n_experts, d_ff
+        self.d_hidden = glu_hidden_dim(d_ff)
+        self.top_k = top_k
+        if n_shared < 0:
+            raise ValueError(f"n_shared ({n_shared}) cannot be negative.")
+        self.n_shared = n_shared
+        if capacity_factor != "auto" and capacity_factor is not None and capacity_factor <= 0:
+            raise ValueError(
+                f"capacity_factor ({capacity_factor}) must be > 0, None, or \"auto\"."
+            )
+        self._capacity_setting = capacity_factor
+
+        self.router = TopKRouter(d_model, n_experts, top_k, normalize_weights, aux_loss_coef,
+                                 noise_std, std)
+        self.activation, act_fn = resolve_activation(activation)
+        self.glu = make_glu(act_fn, fused)
+        self.kernel = kernel
+        # a registered name bound to its registered function, and known to the epilogues
+        named = ACTIVATIONS.get(self.activation) is act_fn and self.activation in KERNEL_ACTIVATIONS
+        self._kernel_act = self.activation if named else None
+
+        h = self.d_hidden
+        self.W_in = nn.Parameter(torch.randn(n_experts, d_model, 2 * h) * std)    # [gate | up]
+        self.W_out = nn.Parameter(torch.randn(n_experts, h, d_model) * std)
+        self.b_in = nn.Parameter(torch.zeros(n_experts, 2 * h)) if bias else None
+        self.b_out = nn.Parameter(torch.zeros(n_experts, d_model)) if bias else None
+        self.W_sh_in = self.W_sh_out = self.b_sh_in = self.b_sh_out = None
+        if n_shared:
+            self.W_sh_in = nn.Parameter(torch.randn(n_shared, d_model, 2 * h) * std)
+            self.W_sh_out = nn.Parameter(torch.randn(n_shared, h, d_model) * std)
+            if bias:
+                self.b_sh_in = nn.Parameter(torch.zeros(n_shared, 2 * h))
+                self.b_sh_out = nn.Parameter(torch.zeros(n_shared, d_model))
+
+        # refreshed by every forward
+        self.aux_loss = torch.zeros(())
+        self.expert_counts = torch.zeros(n_experts)
+        self.dropped = torch.zeros((), dtype=torch.long)
+        self.register_buffer("edges", torch.arange(n_experts + 1, dtype=torch.long),
+                             persistent=False)
+
+    # ------------------------------------------------------------------------------ gating
+    def _kernel_config_ok(self) -> bool:
+        """Everything about this block, other than the tensor it is handed, that the kernels need."""
+        return (self.kernel and self._kernel_act is not None and self.b_in is None
+                and MK.shapes_supported(self.d_model, self.d_hidden, self.n_experts, self.top_k,
+                                        self.n_shared))
+
+    def _kernel_ready(self) -> bool:
+        return self._kernel_config_ok() and kernel_supported(self.W_in)
+
+    @property
+    def capacity_factor(self):
+        """Effective capacity: the explicit setting, or for "auto" None where the kernels take
+        this block's weights as they sit now and AUTO_CAPACITY elsewhere
+        (src/model/moe.py:189-206)."""
+        if self._capacity_setting != "auto":
+            return self._capacity_setting
+        return None if self._kernel_ready() else AUTO_CAPACITY
+
+    def _use_kernel(self, x: torch.Tensor) -> bool:
+        return (self._kernel_config_ok() and self.capacity_factor is None
+                and kernel_supported(x))
+
+    # ---------------------------------------------------------------------------- bookkeeping
+    def _record(self, probs, counts, x):
+        self.expert_counts = counts.detach()
+        if probs is not None:
+            self.aux_loss = self.router.balance_loss(probs, counts)
+        else:
+            self.aux_loss = torch.zeros((), device=x.device, dtype=x.dtype)
+
+    def _plan(self, topk_idx: torch.Tensor):
+        """Stable sort of the flat expert ids: (experts, order, token_idx, counts), all int64
+        (src/model/moe.py:208-223). `order` is the canonical permutation the CUDA dispatch also
+        produces."""
+        experts, order = topk_idx.reshape(-1).sort(stable=True)
+        token_idx = order.div(self.top_k, rounding_mode="floor")
+        counts = torch.searchsorted(experts, self.edges).diff()
+        return experts, order, token_idx, counts
+
+    # ------------------------------------------------------------------------ torch paths
+    def _expert(self, e, x, w, wts):
+        w_in, w_out, b_in, b_out = wts
+        h = x @ w_in[e]
+        if b_in is not None:
+            h = h + b_in[e]
+        gate, up = h.chunk(2, dim=-1)
+        y = self.glu(gate, up) @ w_out[e]
+        if b_out is not None:
+            y = y + b_out[e]
+        return y * w[:, None]
+
+    def _shared(self, x):
+        total = None
+        for s in range(self.n_shared):
+            h = x @ self.W_sh_in[s]
+            if self.b_sh_in is not None:
+                h = h + self.b_sh_in[s]
+            gate, up = h.chunk(2, dim=-1)
+            y = self.glu(gate, up) @ self.W_sh_out[s]
+            if self.b_sh_out is not None:
+                y = y + self.b_sh_out[s]
+            total = y if total is None else total + y
+        return total
+
+    def _capacity(self, n_tokens: int) -> int:
+        fair = n_tokens * self.top_k / self.n_experts
+        return max(1, min(math.ceil(self.capacity_factor * fair), n_tokens * self.top_k))
+
+    def _slots(self, experts, counts, cap: int):
+        starts = counts.cumsum(0) - counts
+        rank = torch.arange(experts.numel(), device=experts.device) - starts[experts]
+        keep = rank < cap
+        return torch.where(keep, experts * cap + rank, self.n_experts * cap), keep
+
+    def _forward_padded(self, x, experts, order, token_idx, counts, topk_w, shape):
+        n = x.shape[0]
+        cap = self._capacity(n)
+        slot, keep = self._slots(experts, counts, cap)
+        self.dropped = (~keep).sum().detach()
+        buf = x.new_zeros(self.n_experts * cap + 1, self.d_model)
+        buf.index_copy_(0, slot, x.index_select(0, token_idx))
+        buf = buf[: self.n_experts * cap].view(self.n_experts, cap, self.d_model)
+        h = buf @ self.W_in
+        if self.b_in is not None:
+            h = h + self.b_in[:, None, :]
+        gate, up = h.chunk(2, dim=-1)
+        y = self.glu(gate, up) @ self.W_out
+        if self.b_out is not None:
+            y = y + self.b_out[:, None, :]
+        y = torch.cat((y.reshape(-1, self.d_model), y.new_zeros(1, self.d_model)))
+        w = topk_w.reshape(-1).index_select(0, order)
+        out = torch.zeros_like(x)
+        out.index_add_(0, token_idx, y.index_select(0, slot) * w[:, None])
+        if self.n_shared:
+            out = out + self._shared(x)
+        return out.view(shape)
+
+    # ------------------------------------------------------------------------------ forward
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.shape[-1] != self.d_model:
+            raise ValueError(f"expected last dim {self.d_model}, got {tuple(x.shape)}.")
+        shape = x.shape
+        x = x.reshape(-1, self.d_model)
+        if x.shape[0] == 0:
+            return x.clone().view(shape)
+        topk_w, topk_idx, probs = self.router(x)
+
+        if self._use_kernel(x):
+            out, counts = fused_moe_forward(
+                x, self.W_in, self.W_out, topk_w, topk_idx, self.b_in, self.b_out,
+                self._kernel_act, w_sh_in=self.W_sh_in, w_sh_out=self.W_sh_out,
+            )
+            self._record(probs, counts, x)
+            return out.view(shape)
+
+        experts, order, token_idx, counts = self._plan(topk_idx)
+        self._record(probs, counts, x)
+        if self.capacity_factor is not None:
+            return self._forward_padded(x, experts, order, token_idx, counts, topk_w, shape)
+
+        sizes = counts.tolist()
+        xs = x.index_select(0, token_idx).split(sizes)
+        ws = topk_w.reshape(-1).index_select(0, order).split(sizes)
+        rows = token_idx.split(sizes)
+        wts = (self.W_in.unbind(0), self.W_out.unbind(0),
+               None if self.b_in is None else self.b_in.unbind(0),
+               None if self.b_out is None else self.b_out.unbind(0))
+        out = torch.zeros_like(x)
+        for e in range(self.n_experts):
+            if sizes[e]:
+                out.index_add_(0, rows[e], self._expert(e, xs[e], ws[e], wts))
+        if self.n_shared:
+            out = out + self._shared(x)
+        return out.view(shape)
+
+    def dense_forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Every expert on every token, mixed by a dense [N, E] gate matrix: the shape-static
+        cross-check of `forward` (src/model/moe.py:420-474). Same side effects as `forward`."""
+        if x.shape[-1] != self.d_model:
+            raise ValueError(f"expected last dim {self.d_model}, got {tuple(x.shape)}.")
+        shape = x.shape
+        x = x.reshape(-1, self.d_model)
+        topk_w, topk_idx, probs = self.router(x)
+        experts, order, _, counts = self._plan(topk_idx)
+        self._record(probs, counts, x)
+        if self.capacity_factor is not None and x.shape[0]:
+            _, keep = self._slots(experts, counts, self._capacity(x.shape[0]))
+            kept = torch.empty_like(keep).index_copy_(0, order, keep)
+            self.dropped = (~keep).sum().detach()
+            topk_w = topk_w * kept.view_as(topk_w)
+        gates = torch.zeros(x.shape[0], self.n_experts, dtype=x.dtype, device=x.device)
+        gates.scatter_(1, topk_idx, topk_w)
+        h = x @ self.W_in
+        if self.b_in is not None:
+            h = h + self.b_in[:, None, :]
+        gate, up = h.chunk(2, dim=-1)
+        y = self.glu(gate, up) @ self.W_out
+        if self.b_out is not None:
+            y = y + self.b_out[:, None, :]
+        out = torch.einsum("enf,ne->nf", y, gates)
+        if self.n_shared:
+            out = out + self._shared(x)
+        return out.view(shape)

@@ -1,0 +1,297 @@
+"""Differentiable torch.library ops over the sm_100a MoE kernels, and the three names the MoE module
+imports from its kernel module: KERNEL_ACTIVATIONS, fused_moe_forward, kernel_supported
+(the interface of src/model/moe_kernel.py:71-108, 785-803).
+
+Ops (namespace `moe_b200`, all functional, all with fake kernels so torch.compile traces them):
+
+  router_topk      fp32 logits -> (topk_w, topk_idx, probs)          src/model/router.py:79-97
+  moe_dispatch     topk_idx -> six int32 plan tensors                src/model/moe_kernel.py:180-218
+  moe_experts      routed (+ shared) experts on dispatched pairs     src/model/moe_kernel.py:558-623
+  moe_experts_bwd  its backward as one opaque op                     src/model/moe_kernel.py:626-749
+
+No op synchronises the host: buffers are sized by the worst case `l_cap` and the live padded length
+stays in a 1-element device tensor that the kernels read.
+"""
+from typing import List, Optional, Tuple
+
+import torch
+
+from . import kernels as K
+from .kernels import ALIGN_M, KERNEL_ACTIVATIONS, l_cap as _l_cap  # noqa: F401  (re-exported)
+
+# dtypes the tcgen05 path computes in (fp32 accumulation inside).
+KERNEL_DTYPES = (torch.bfloat16,)
+
+MAX_EXPERTS = 256  # per-expert state of the routing kernels lives on chip
+MAX_TOPK = 16
+MAX_SHARED = 2     # the combine kernel adds at most two extra token-major row sets
+
+
+def kernel_supported(t: torch.Tensor) -> bool:
+    """Device + dtype half of the gate (src/model/moe_kernel.py:81-90): CUDA and bf16."""
+    return t.is_cuda and t.dtype in KERNEL_DTYPES
+
+
+def shapes_supported(d_model: int, d_hidden: int, n_experts: int, top_k: int,
+                     n_shared: int = 0) -> bool:
+    """Shape half of the gate: what the tile shapes of the sm_100a kernels cover."""
+    return (d_hidden == 128 and d_model >= 64 and d_model % 32 == 0
+            and 1 <= n_experts <= MAX_EXPERTS and 1 <= top_k <= min(MAX_TOPK, n_experts)
+            and 0 <= n_shared <= MAX_SHARED)
+
+
+# ------------------------------------------------------------------------------ router top-k
+@torch.library.custom_op("moe_b200::router_topk", mutates_args=())
+def router_topk(logits: torch.Tensor, top_k: int, normalize: bool,
+                full_softmax: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(topk_w fp32 [T,k], topk_idx int64 [T,k], probs fp32 [T,E] or empty when not full_softmax).
+
+    Winners by descending logit, ties to the lowest expert index.
+    """
+    w, idx, probs = K.router_topk(logits.float(), top_k, normalize, full_softmax, full_softmax)
+    return w, idx, probs if probs is not None else logits.new_empty(0, dtype=torch.float32)
+
+
+@router_topk.register_fake
+def _(logits, top_k, normalize, full_softmax):
+    t, e = logits.shape
+    return (logits.new_empty((t, top_k), dtype=torch.float32),
+            logits.new_empty((t, top_k), dtype=torch.int64),
+            logits.new_empty((t, e) if full_softmax else (0,), dtype=torch.float32))
+
+
+@torch.library.custom_op("moe_b200::router_topk_bwd", mutates_args=())
+def router_topk_bwd(logits: torch.Tensor, topk_idx: torch.Tensor, d_topk_w: torch.Tensor,
+                    d_probs: Optional[torch.Tensor], normalize: bool,
+                    full_softmax: bool) -> torch.Tensor:
+    return K.router_topk_bwd(logits.float(), topk_idx, d_topk_w, d_probs, normalize,
+                             full_softmax).to(logits.dtype)
+
+
+@router_topk_bwd.register_fake
+def _(logits, topk_idx, d_topk_w, d_probs, normalize, full_softmax):
+    return torch.empty_like(logits)
+
+
+def _router_setup(ctx, inputs, output):
+    logits, top_k, normalize, full_softmax = inputs
+    ctx.save_for_backward(logits, output[1])
+    ctx.normalize, ctx.full_softmax = normalize, full_softmax
+    ctx.mark_non_differentiable(output[1])
+
+
+def _router_backward(ctx, d_w, d_idx, d_probs):
+    logits, idx = ctx.saved_tensors
+    if d_w is None:
+        d_w = torch.zeros(idx.shape, dtype=torch.float32, device=idx.device)
+    if not ctx.full_softmax or d_probs is None or d_probs.numel() == 0:
+        d_probs = None
+    return router_topk_bwd(logits, idx, d_w, d_probs, ctx.normalize, ctx.full_softmax), None, None, None
+
+
+router_topk.register_autograd(_router_backward, setup_context=_router_setup)
+
+
+# ---------------------------------------------------------------------------------- dispatch
+@torch.library.custom_op("moe_b200::moe_dispatch", mutates_args=())
+def moe_dispatch(topk_idx: torch.Tensor, n_experts: int) -> Tuple[
+    torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor
+]:
+    """(sorted_ids [l_cap], expert_ids [l_cap/128], pad_offsets [E+1], counts [E], n_post_pad [1],
+    inv_ids [M]) as int32 -- the tuple of src/model/moe_kernel.py:180-209, with one stronger
+    guarantee: inside a run, pairs are in ascending pair id (a stable sort by expert)."""
+    return K.dispatch(topk_idx, n_experts)
+
+
+@moe_dispatch.register_fake
+def _(topk_idx, n_experts):
+    m = topk_idx.numel()
+    cap = _l_cap(m, n_experts)
+    mk = lambda n: topk_idx.new_empty((n,), dtype=torch.int32)
+    return mk(cap), mk(cap // ALIGN_M), mk(n_experts + 1), mk(n_experts), mk(1), mk(m)
+
+
+# ----------------------------------------------------------------------------------- experts
+def _act_id(activation: str) -> int:
+    if activation not in KERNEL_ACTIVATIONS:
+        raise ValueError(
+            f"activation {activation!r} has no kernel; use one of "
+            f"{sorted(set(KERNEL_ACTIVATIONS))} or fall back to the eager path."
+        )
+    return KERNEL_ACTIVATIONS[activation]
+
+
+def _check_inputs(x, w_in, w_out, w_sh_in):
+    if not kernel_supported(x):
+        raise RuntimeError(
+            f"moe_b200 kernels need CUDA bf16 tensors, got {x.device} {x.dtype}; there is no "
+            "CPU or other-dtype implementation behind these ops")
+    n_shared = 0 if w_sh_in is None else w_sh_in.shape[0]
+    if not shapes_supported(x.shape[1], w_in.shape[2] // 2, w_in.shape[0], 1, n_shared):
+        raise RuntimeError(
+            f"moe_b200 kernels do not cover d_model={x.shape[1]}, d_hidden={w_in.shape[2] // 2}, "
+            f"n_experts={w_in.shape[0]}, n_shared={n_shared}")
+
+
+@torch.library.custom_op("moe_b200::moe_experts", mutates_args=())
+def moe_experts(
+    x: torch.Tensor,
+    w_in: torch.Tensor,
+    w_out: torch.Tensor,
+    topk_w: torch.Tensor,
+    w_sh_in: Optional[torch.Tensor],
+    w_sh_out: Optional[torch.Tensor],
+    sorted_ids: torch.Tensor,
+    expert_ids: torch.Tensor,
+    pad_offsets: torch.Tensor,
+    counts: torch.Tensor,
+    n_post_pad: torch.Tensor,
+    inv_ids: torch.Tensor,
+    activation: str,
+) -> torch.Tensor:
+    """out[t] = sum_j topk_w[t,j] * expert_{idx[t,j]}(x[t])  (+ sum_s shared_s(x[t])).
+
+    permute -> up/gate GEMM with fused GLU -> down GEMM with fused router weight -> token-major
+    fp32 combine; the shared experts run through the same GEMM kernels on the unpermuted tokens
+    and join in the combine. All tensors share x's dtype (the wrapper casts).
+    """
+    x, w_in, w_out = x.contiguous(), w_in.contiguous(), w_out.contiguous()
+    _check_inputs(x, w_in, w_out, w_sh_in)
+    act = _act_id(activation)
+    n, d = x.shape
+    topk = topk_w.shape[-1]
+    m = n * topk
+    if n == 0:
+        return x.new_zeros((0, d))
+    tw = topk_w.reshape(-1).contiguous()
+
+    xs = K.permute(x, topk, sorted_ids, n_post_pad)
+    hid = K.up_gemm(xs, w_in, expert_ids, n_post_pad, -1, False, act)
+    y = K.down_gemm(hid, w_out, expert_ids, n_post_pad, -1, sorted_ids, tw, m)
+    extras: List[Optional[torch.Tensor]] = [None, None]
+    if w_sh_in is not None:
+        w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
+        for s in range(w_sh_in.shape[0]):
+            hs = K.up_gemm(x, w_sh_in, None, None, s, False, act)
+            extras[s] = K.down_gemm(hs, w_sh_out, None, None, s, None, None, 0)
+    return K.combine(y, inv_ids, n, topk, extras[0], extras[1])
+
+
+@moe_experts.register_fake
+def _(x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
+      n_post_pad, inv_ids, activation):
+    return x.new_empty(x.shape)
+
+
+@torch.library.custom_op("moe_b200::moe_experts_bwd", mutates_args=())
+def moe_experts_bwd(
+    grad_out: torch.Tensor,
+    x: torch.Tensor,
+    w_in: torch.Tensor,
+    w_out: torch.Tensor,
+    topk_w: torch.Tensor,
+    w_sh_in: Optional[torch.Tensor],
+    w_sh_out: Optional[torch.Tensor],
+    sorted_ids: torch.Tensor,
+    expert_ids: torch.Tensor,
+    pad_offsets: torch.Tensor,
+    counts: torch.Tensor,
+    n_post_pad: torch.Tensor,
+    inv_ids: torch.Tensor,
+    activation: str,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(dx, dW_in, dW_out, dtopk_w, dW_sh_in, dW_sh_out); the last two are empty without shared
+    experts. Pre-activations are recomputed, as in src/model/moe_kernel.py:663-672."""
+    grad_out = grad_out.to(x.dtype).contiguous()
+    x, w_in, w_out = x.contiguous(), w_in.contiguous(), w_out.contiguous()
+    _check_inputs(x, w_in, w_out, w_sh_in)
+    act = _act_id(activation)
+    n, d = x.shape
+    e_n = w_in.shape[0]
+    topk = topk_w.shape[-1]
+    m = n * topk
+    tw = topk_w.reshape(-1).contiguous()
+
+    xs = K.permute(x, topk, sorted_ids, n_post_pad)
+    a1 = K.up_gemm(xs, w_in, expert_ids, n_post_pad, -1, True, act)
+    douts = K.permute(grad_out, topk, sorted_ids, n_post_pad)
+    da1, hidw, dtw = K.dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, -1, sorted_ids, tw, m,
+                                       a1, act, True)
+    ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, -1)
+    dw_in = K.wgrad(xs, da1, pad_offsets, e_n)
+    dw_out = K.wgrad(hidw, douts, pad_offsets, e_n)
+
+    extras: List[Optional[torch.Tensor]] = [None, None]
+    dw_sh_in = x.new_empty(0)
+    dw_sh_out = x.new_empty(0)
+    if w_sh_in is not None:
+        w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
+        s_n = w_sh_in.shape[0]
+        dw_sh_in = torch.empty_like(w_sh_in)
+        dw_sh_out = torch.empty_like(w_sh_out)
+        for s in range(s_n):
+            a1s = K.up_gemm(x, w_sh_in, None, None, s, True, act)
+            da1s, hids, _ = K.dhidden_glu_bwd(grad_out, w_sh_out, None, None, s, None, None, 0,
+                                              a1s, act, False)
+            extras[s] = K.dx_gemm(da1s, w_sh_in, None, None, s)
+            dw_sh_in[s] = K.wgrad(x, da1s, None, 1)[0]
+            dw_sh_out[s] = K.wgrad(hids, grad_out, None, 1)[0]
+    dx = K.combine(ydx, inv_ids, n, topk, extras[0], extras[1])
+    return dx, dw_in, dw_out, dtw.view_as(topk_w), dw_sh_in, dw_sh_out
+
+
+@moe_experts_bwd.register_fake
+def _(grad_out, x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets,
+      counts, n_post_pad, inv_ids, activation):
+    return (torch.empty_like(x), torch.empty_like(w_in), torch.empty_like(w_out),
+            torch.empty_like(topk_w),
+            torch.empty_like(w_sh_in) if w_sh_in is not None else x.new_empty(0),
+            torch.empty_like(w_sh_out) if w_sh_out is not None else x.new_empty(0))
+
+
+def _experts_setup(ctx, inputs, output):
+    (x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
+     n_post_pad, inv_ids, activation) = inputs
+    saved = [x, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts, n_post_pad,
+             inv_ids]
+    ctx.has_shared = w_sh_in is not None
+    if ctx.has_shared:
+        saved += [w_sh_in, w_sh_out]
+    ctx.save_for_backward(*saved)
+    ctx.activation = activation
+
+
+def _experts_backward(ctx, grad_out):
+    (x, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts, n_post_pad, inv_ids,
+     *rest) = ctx.saved_tensors
+    w_sh_in, w_sh_out = (rest[0], rest[1]) if ctx.has_shared else (None, None)
+    dx, dw_in, dw_out, dtw, dsi, dso = moe_experts_bwd(
+        grad_out, x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets,
+        counts, n_post_pad, inv_ids, ctx.activation)
+    return (dx, dw_in, dw_out, dtw, dsi if ctx.has_shared else None,
+            dso if ctx.has_shared else None, None, None, None, None, None, None, None)
+
+
+moe_experts.register_autograd(_experts_backward, setup_context=_experts_setup)
+
+
+# ------------------------------------------------------------------------------- entry point
+def fused_moe_forward(x, w_in, w_out, topk_w, topk_idx, b_in, b_out, activation,
+                      w_sh_in=None, w_sh_out=None):
+    """Dispatch + experts on the GPU; returns (out [N, d_model], counts [n_experts] int32).
+
+    Same contract as src/model/moe_kernel.py:785-803, plus optional stacked shared-expert weights
+    (`w_sh_in [S, D, 2H]`, `w_sh_out [S, H, D]`) whose outputs are then included in `out`.
+    Parameters are cast to x.dtype here (what autocast would do); gradients flow back through
+    the cast. Per-expert biases are not implemented by the kernels.
+    """
+    _act_id(activation)
+    if b_in is not None or b_out is not None:
+        raise NotImplementedError(
+            "moe_b200 kernels do not apply per-expert biases; build the block with bias=False "
+            "or kernel=False")
+    sids, eids, offs, counts, npp, inv = moe_dispatch(topk_idx, w_in.shape[0])
+    cast = lambda t: None if t is None else t.to(x.dtype)
+    out = moe_experts(x, cast(w_in), cast(w_out), topk_w.to(x.dtype), cast(w_sh_in),
+                      cast(w_sh_out), sids, eids, offs, counts, npp, inv, activation)
+    return out, counts

@@ -1,0 +1,127 @@
+"""Generate the golden vectors in this directory by running the UNMODIFIED reference.
+
+Usage (needs a checkout of Osmansiddiquer/nanospeaker):
+    python tests/golden/make_golden.py /path/to/nanospeaker
+
+Each .npz holds the inputs and everything the reference's pure-PyTorch MoE path
+(MoEBlock(..., fused=False, kernel=False, capacity_factor=None) on CPU) computes from them:
+router logits, top-k, the stable-sort plan, the block output, the balance loss and -- for the
+training cases -- all gradients of `out.float().square().mean() + aux_loss`.
+bf16 tensors are stored as their uint16 bit patterns under the key suffix `__bf16`.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def put(store, name, t):
+    t = t.detach()
+    if t.dtype == torch.bfloat16:
+        store[name + "__bf16"] = t.contiguous().view(torch.int16).numpy().view(np.uint16)
+    else:
+        store[name] = t.contiguous().numpy()
+
+
+def block_case(MoEBlock, name, *, d_model, n_experts, d_ff, top_k, n_shared, tokens, dtype, train,
+               seed, activation="silu", normalize=True):
+    torch.manual_seed(seed)
+    m = MoEBlock(d_model, n_experts, d_ff=d_ff, top_k=top_k, n_shared=n_shared,
+                 capacity_factor=None, activation=activation, normalize_weights=normalize,
+                 fused=False, kernel=False)
+    with torch.no_grad():
+        m.router.W.copy_(torch.randn_like(m.router.W) * 0.3)
+        m.W_in.copy_(torch.randn_like(m.W_in) * d_model ** -0.5)
+        m.W_out.copy_(torch.randn_like(m.W_out) * m.d_hidden ** -0.5)
+        if n_shared:
+            m.W_sh_in.copy_(torch.randn_like(m.W_sh_in) * d_model ** -0.5)
+            m.W_sh_out.copy_(torch.randn_like(m.W_sh_out) * m.d_hidden ** -0.5)
+    x = torch.randn(tokens, d_model)
+    m = m.to(dtype)
+    x = x.to(dtype).requires_grad_(train)
+    m.train(train)
+
+    s = {}
+    put(s, "x", x)
+    put(s, "router_W", m.router.W)
+    put(s, "W_in", m.W_in)
+    put(s, "W_out", m.W_out)
+    if n_shared:
+        put(s, "W_sh_in", m.W_sh_in)
+        put(s, "W_sh_out", m.W_sh_out)
+    s["meta"] = np.array([d_model, n_experts, d_ff, top_k, n_shared, tokens, int(train),
+                          int(normalize)], dtype=np.int64)
+    s["activation"] = np.array(activation)
+    s["dtype"] = np.array(str(dtype).replace("torch.", ""))
+
+    with torch.set_grad_enabled(train):
+        logits = (x.detach() @ m.router.W.detach()).float()
+        topk_w, topk_idx, probs = m.router(x.detach())
+        experts, order, token_idx, counts = m._plan(topk_idx)
+        out = m(x)
+        if not train:
+            dense = m.dense_forward(x)
+            put(s, "dense_out", dense)
+    put(s, "logits", logits)
+    put(s, "topk_w", topk_w)
+    put(s, "topk_idx", topk_idx)
+    if probs is not None:
+        put(s, "probs", probs)
+    put(s, "plan_experts", experts)
+    put(s, "plan_order", order)
+    put(s, "plan_token_idx", token_idx)
+    put(s, "plan_counts", counts)
+    put(s, "out", out)
+    put(s, "aux_loss", m.aux_loss.float())
+    if train:
+        (out.float().square().mean() + m.aux_loss).backward()
+        put(s, "grad_x", x.grad)
+        put(s, "grad_router_W", m.router.W.grad)
+        put(s, "grad_W_in", m.W_in.grad)
+        put(s, "grad_W_out", m.W_out.grad)
+        if n_shared:
+            put(s, "grad_W_sh_in", m.W_sh_in.grad)
+            put(s, "grad_W_sh_out", m.W_sh_out.grad)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **s)
+    print(name, {k: v.shape for k, v in s.items() if hasattr(v, "shape") and v.ndim})
+
+
+def routing_case(MoEBlock, name, *, tokens, n_experts, top_k, seed, bf16_logits):
+    """Routing only at nanoSpeaker's width: logits -> torch.topk -> stable-sort plan."""
+    torch.manual_seed(seed)
+    m = MoEBlock(64, n_experts, d_ff=192, top_k=top_k, capacity_factor=None, fused=False,
+                 kernel=False)
+    logits = torch.randn(tokens, n_experts) * 0.5
+    if bf16_logits:
+        logits = logits.bfloat16().float()
+    topk_idx = logits.topk(top_k, dim=-1).indices
+    experts, order, token_idx, counts = m._plan(topk_idx)
+    np.savez_compressed(
+        os.path.join(HERE, name + ".npz"), logits=logits.numpy(), topk_idx=topk_idx.numpy(),
+        plan_order=order.numpy(), plan_token_idx=token_idx.numpy(), plan_counts=counts.numpy(),
+        meta=np.array([tokens, n_experts, top_k, int(bf16_logits)], dtype=np.int64))
+    print(name, tuple(logits.shape))
+
+
+def main():
+    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    sys.path.insert(0, ref)
+    from src.model.moe import MoEBlock  # the reference, unmodified
+
+    common = dict(d_model=64, n_experts=4, d_ff=192, top_k=2, n_shared=1, tokens=80)
+    block_case(MoEBlock, "block_fp32_eval", dtype=torch.float32, train=False, seed=1, **common)
+    block_case(MoEBlock, "block_fp32_train", dtype=torch.float32, train=True, seed=2, **common)
+    block_case(MoEBlock, "block_bf16_train", dtype=torch.bfloat16, train=True, seed=3, **common)
+    block_case(MoEBlock, "block_bf16_eval_gelu", dtype=torch.bfloat16, train=False, seed=4,
+               activation="gelu", normalize=False, **common)
+    routing_case(MoEBlock, "routing_e76_k6_fp32", tokens=512, n_experts=76, top_k=6, seed=5,
+                 bf16_logits=False)
+    routing_case(MoEBlock, "routing_e76_k6_bf16", tokens=512, n_experts=76, top_k=6, seed=6,
+                 bf16_logits=True)
+
+
+if __name__ == "__main__":
+    main()

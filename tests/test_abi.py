@@ -1,0 +1,86 @@
+"""The C-ABI library: it loads, exports every symbol include/moe_b200.h declares, and validates
+arguments before touching the GPU. No compute calls, so this runs without a CUDA device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+from oracle import moe_oracle as O
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from nanospeaker_b200 import _lib, build
+    build.build()
+    return _lib.load()
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "moe_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(moe_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree(lib):
+    from nanospeaker_b200 import _lib
+    declared = _declared_symbols()
+    assert len(declared) >= 14
+    assert declared == sorted(_lib.SIGNATURES), "ctypes table and header differ"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+
+
+def test_abi_version_and_error_strings(lib):
+    from nanospeaker_b200 import _lib
+    assert lib.moe_b200_abi_version() == 1
+    assert _lib.error_string(0) == "ok"
+    for code in range(-7, 0):
+        assert _lib.error_string(code) not in ("ok", "unknown moe_b200 error code")
+    assert "unknown" in _lib.error_string(-99)
+
+
+@pytest.mark.parametrize("m,e", [(0, 8), (1, 8), (3, 8), (100, 8), (12288, 76), (98304, 76),
+                                 (786432, 76), (5, 200)])
+def test_l_cap_matches_reference_formula(lib, m, e):
+    """ceil((M + min(E, M) * 127) / 128) * 128 (src/model/moe_kernel.py:100-108)."""
+    from nanospeaker_b200 import kernels
+    want = O.l_cap(m, e)
+    assert lib.moe_b200_l_cap(m, e) == want == kernels.l_cap(m, e)
+    assert want % 128 == 0 and want >= m
+
+
+def test_scratch_bytes_is_modest(lib):
+    assert lib.moe_b200_dispatch_scratch_bytes(0, 76) > 0
+    assert lib.moe_b200_dispatch_scratch_bytes(98304, 76) == 24 * 76 * 4
+
+
+def test_arguments_are_validated_before_any_launch(lib):
+    """Bad shapes / NULL pointers come back as error codes, not faults (no GPU needed)."""
+    null = ctypes.c_void_p(0)
+    assert lib.moe_b200_router_topk(null, 4, 0, 1, 1, 0, null, null, null, null) == -1   # E < 1
+    assert lib.moe_b200_router_topk(null, 4, 300, 1, 1, 0, null, null, null, null) == -1  # E > 256
+    assert lib.moe_b200_router_topk(null, 4, 8, 9, 1, 0, null, null, null, null) == -1    # k > E
+    assert lib.moe_b200_router_topk(null, 4, 8, 2, 1, 0, null, null, null, null) == -2    # NULL
+    assert lib.moe_b200_router_topk(null, 0, 8, 2, 1, 0, null, null, null, null) == 0     # empty
+    assert lib.moe_b200_dispatch(null, 10, 8, null, null, null, null, null, null, null, 0, null,
+                                 null) == -2
+    assert lib.moe_b200_permute(null, 4, 100, 2, null, null, 128, null, null) == -1       # D % 8
+    assert lib.moe_b200_permute(null, 4, 64, 2, null, null, 128, null, null) == -2
+    assert lib.moe_b200_combine(null, null, 4, 2, 64, null, null, null, null) == -2
+    assert lib.moe_b200_up_gemm(null, 128, 64, null, 4, 64, null, null, 0, 0, 0, null, 128, null,
+                                null) == -2
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    assert lib.moe_b200_up_gemm(p, 128, 64, p, 4, 64, p, p, 0, 0, 0, p, 128, p, null) == -5  # H
+    assert lib.moe_b200_up_gemm(p, 100, 64, p, 4, 128, p, p, -1, 0, 0, p, 128, p, null) == -1
+    assert lib.moe_b200_wgrad(p, 64, p, 100, 128, p, 4, p, p, null) == -5
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from nanospeaker_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no non-CUDA implementation"):
+        _lib.load()

@@ -1,0 +1,179 @@
+"""GPU parity of the data-movement and grouped-GEMM stages, each against plain fp32 CPU math on the
+same seeded inputs. Movement is bit-exact; GEMM stages are bf16-out / fp32-accumulate and are held
+to rel-L2 <= 5e-3 (the bar for the whole block is 1e-2)."""
+import pytest
+import torch
+
+from conftest import rel_l2
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = 5e-3
+
+
+def K():
+    from nanospeaker_b200 import kernels
+    return kernels
+
+
+def _setup(T, E, k, D, H=128, skew=0.0, seed=0):
+    torch.manual_seed(seed)
+    logits = torch.randn(T, E) + skew * torch.randn(E)
+    idx = logits.topk(k, -1).indices
+    plan = O.dispatch(idx, E)
+    x = torch.randn(T, D).bfloat16()
+    w_in = (torch.randn(E, D, 2 * H) * D ** -0.5).bfloat16()
+    w_out = (torch.randn(E, H, D) * H ** -0.5).bfloat16()
+    tw = torch.rand(T, k).bfloat16()
+    return idx, plan, x, w_in, w_out, tw
+
+
+def _slot_rows(src, sids, k, nl, M):
+    """CPU permute: src[pair // k] per live slot, zeros in pad slots."""
+    s = sids[:nl].long()
+    live = s < M
+    rows = src[(s // k).clamp(max=src.shape[0] - 1)].clone()
+    rows[~live] = 0
+    return rows, live
+
+
+def _per_expert(a, w, offs, transpose=False):
+    out = torch.zeros(a.shape[0], w.shape[1] if transpose else w.shape[2])
+    for e in range(w.shape[0]):
+        lo, hi = int(offs[e]), int(offs[e + 1])
+        if hi > lo:
+            wf = w[e].float()
+            out[lo:hi] = a[lo:hi].float() @ (wf.t() if transpose else wf)
+    return out
+
+
+CASES = [(300, 8, 2, 576, 0.0), (1, 8, 1, 64, 0.0), (129, 4, 2, 96, 0.0), (2048, 76, 6, 576, 1.0)]
+
+
+@pytest.mark.parametrize("T,E,k,D,skew", CASES)
+def test_permute_and_combine_are_bit_exact(T, E, k, D, skew):
+    idx, (sids, eids, offs, counts, npp, inv), x, _, _, _ = _setup(T, E, k, D, skew=skew)
+    nl, M = int(npp), T * k
+    g = lambda t: t.cuda()
+    xs = K().permute(g(x), k, g(sids), g(npp)).cpu()
+    ref, _ = _slot_rows(x, sids, k, nl, M)
+    assert torch.equal(xs[:nl], ref)
+
+    y = torch.randn(sids.numel(), D).bfloat16()
+    e1, e2 = torch.randn(T, D).bfloat16(), torch.randn(T, D).bfloat16()
+    for extras in [(None, None), (e1, None), (e1, e2)]:
+        out = K().combine(g(y), g(inv), T, k, *[None if e is None else g(e) for e in extras]).cpu()
+        acc = torch.zeros(T, D)
+        for j in range(k):
+            acc += y[inv.view(T, k)[:, j].long()].float()
+        for e in extras:
+            if e is not None:
+                acc += e.float()
+        assert torch.equal(out, acc.bfloat16())
+
+
+@pytest.mark.parametrize("T,E,k,D,skew", CASES)
+def test_forward_gemm_stages(T, E, k, D, skew):
+    H = 128
+    idx, (sids, eids, offs, counts, npp, inv), x, w_in, w_out, tw = _setup(T, E, k, D, skew=skew)
+    nl, M = int(npp), T * k
+    g = lambda t: t.cuda()
+    xs_ref, live = _slot_rows(x, sids, k, nl, M)
+    xs = torch.zeros(sids.numel(), D, dtype=torch.bfloat16)
+    xs[:nl] = xs_ref
+    a1_ref = _per_expert(xs_ref, w_in, offs)
+    a1 = K().up_gemm(g(xs), g(w_in), g(eids), g(npp), -1, True, 0).cpu()
+    assert rel_l2(a1[:nl], a1_ref) < TOL
+    for name, act in [("silu", 0), ("gelu", 1), ("relu", 2), ("sigmoid", 3), ("tanh", 4)]:
+        hid = K().up_gemm(g(xs), g(w_in), g(eids), g(npp), -1, False, act).cpu()
+        gate, up = a1_ref.chunk(2, -1)
+        assert rel_l2(hid[:nl], O.ACTS[name](gate) * up) < TOL, name
+    gate, up = a1_ref.chunk(2, -1)
+    hid_b = torch.zeros(sids.numel(), H, dtype=torch.bfloat16)
+    hid_b[:nl] = (torch.nn.functional.silu(gate) * up).bfloat16()
+    twf = tw.reshape(-1)
+    wslot = torch.where(live, twf[sids[:nl].long().clamp(max=M - 1)].float(), torch.zeros(()))
+    y = K().down_gemm(g(hid_b), g(w_out), g(eids), g(npp), -1, g(sids), g(twf), M).cpu()
+    y_ref = _per_expert(hid_b[:nl], w_out, offs) * wslot[:, None]
+    assert rel_l2(y[:nl], y_ref) < TOL
+    assert (y[:nl][~live] == 0).all()                 # pad slots carry exact zeros
+    K().check_status("cuda")
+
+
+@pytest.mark.parametrize("T,E,k,D,skew", CASES)
+def test_backward_gemm_stages(T, E, k, D, skew):
+    H = 128
+    idx, (sids, eids, offs, counts, npp, inv), x, w_in, w_out, tw = _setup(T, E, k, D, skew=skew,
+                                                                            seed=3)
+    nl, M, cap = int(npp), T * k, sids.numel()
+    g = lambda t: t.cuda()
+    twf = tw.reshape(-1)
+    xs_ref, live = _slot_rows(x, sids, k, nl, M)
+    wslot = torch.where(live, twf[sids[:nl].long().clamp(max=M - 1)].float(), torch.zeros(()))
+    dout = torch.randn(T, D).bfloat16()
+    douts_ref, _ = _slot_rows(dout, sids, k, nl, M)
+    pad = lambda t, w: torch.cat([t, torch.zeros(cap - nl, w, dtype=t.dtype)])
+    a1_b = pad(_per_expert(xs_ref, w_in, offs).bfloat16(), 2 * H)
+
+    da1, hidw, dtw = K().dhidden_glu_bwd(g(pad(douts_ref, D)), g(w_out), g(eids), g(npp), -1,
+                                         g(sids), g(twf), M, g(a1_b), 0, True)
+    G = _per_expert(douts_ref, w_out, offs, transpose=True)
+    gate, up = a1_b[:nl].float().chunk(2, -1)
+    sg = torch.sigmoid(gate)
+    act, dact = gate * sg, sg * (1 + gate * (1 - sg))
+    dh = wslot[:, None] * G
+    assert rel_l2(da1.cpu()[:nl], torch.cat([dh * up * dact, dh * act], -1)) < TOL
+    assert rel_l2(hidw.cpu()[:nl], act * up * wslot[:, None]) < TOL
+    dtw_ref = torch.zeros(M)
+    dtw_ref[sids[:nl][live].long()] = (G * act * up).sum(-1)[live]
+    assert rel_l2(dtw.cpu(), dtw_ref) < TOL
+
+    da1_in = pad((torch.randn(nl, 2 * H) * live[:, None]).bfloat16(), 2 * H)
+    ydx = K().dx_gemm(g(da1_in), g(w_in), g(eids), g(npp), -1).cpu()
+    assert rel_l2(ydx[:nl], _per_expert(da1_in[:nl], w_in, offs, transpose=True)) < TOL
+
+    xs_b = pad(xs_ref, D)
+    dw_in = K().wgrad(g(xs_b), g(da1_in), g(offs), E).cpu()
+    dw_out = K().wgrad(g(pad((act * up).bfloat16(), H)), g(pad(douts_ref, D)), g(offs), E).cpu()
+    for e in range(E):
+        lo, hi = int(offs[e]), int(offs[e + 1])
+        if hi == lo:
+            assert (dw_in[e] == 0).all() and (dw_out[e] == 0).all()   # empty expert: exact zeros
+    ref_in = torch.stack([xs_ref[int(offs[e]):int(offs[e + 1])].float().t()
+                          @ da1_in[int(offs[e]):int(offs[e + 1])].float() for e in range(E)])
+    ref_out = torch.stack([(act * up).bfloat16()[int(offs[e]):int(offs[e + 1])].float().t()
+                           @ douts_ref[int(offs[e]):int(offs[e + 1])].float() for e in range(E)])
+    assert rel_l2(dw_in, ref_in) < TOL
+    assert rel_l2(dw_out, ref_out) < TOL
+    K().check_status("cuda")
+
+
+@pytest.mark.parametrize("T", [1, 5, 127, 128, 129, 1000])
+def test_shared_expert_schedule_on_unpermuted_tokens(T):
+    """fixed_group: rows in token order, any row count, OOB rows masked."""
+    D, H, S = 576, 128, 2
+    x = torch.randn(T, D).bfloat16()
+    wsi = (torch.randn(S, D, 2 * H) * D ** -0.5).bfloat16()
+    wso = (torch.randn(S, H, D) * H ** -0.5).bfloat16()
+    g = lambda t: t.cuda()
+    for s in range(S):
+        gate, up = (x.float() @ wsi[s].float()).chunk(2, -1)
+        hid_ref = torch.nn.functional.silu(gate) * up
+        hid = K().up_gemm(g(x), g(wsi), None, None, s, False, 0)
+        assert rel_l2(hid.cpu(), hid_ref) < TOL
+        y = K().down_gemm(hid, g(wso), None, None, s, None, None, 0).cpu()
+        assert rel_l2(y, hid.cpu().float() @ wso[s].float()) < TOL
+        dws = K().wgrad(g(x), hid, None, 1).cpu()
+        assert rel_l2(dws[0], x.float().t() @ hid.cpu().float()) < TOL
+
+
+def test_entry_points_reject_bad_arguments():
+    x = torch.randn(4, 100, device="cuda").bfloat16()          # d_model % 8 != 0
+    with pytest.raises(RuntimeError, match="shape|covered"):
+        K().permute(x, 2, torch.zeros(128, dtype=torch.int32, device="cuda"),
+                    torch.zeros(1, dtype=torch.int32, device="cuda"))
+    w = torch.randn(2, 64, 128, device="cuda").bfloat16()       # d_hidden 64: not covered
+    with pytest.raises(RuntimeError, match="not covered"):
+        K().up_gemm(torch.randn(128, 64, device="cuda").bfloat16(), w, None, None, 0, False, 0)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        K().router_topk(torch.randn(4, 8), 2, True, False, False)   # CPU tensor: no fallback

@@ -1,0 +1,188 @@
+"""The CPU oracle against the golden vectors produced by the unmodified reference
+(tests/golden/make_golden.py), and against the reference imported live when a checkout exists."""
+import os
+import sys
+
+import pytest
+import torch
+
+from conftest import load_golden, rel_l2
+from oracle import moe_oracle as O
+
+REF = os.environ.get("NANOSPEAKER_REF", "/root/reference")
+BLOCK_CASES = ["block_fp32_eval", "block_fp32_train", "block_bf16_train", "block_bf16_eval_gelu"]
+
+
+def _block_from_golden(g):
+    d_model, n_experts, d_ff, top_k, n_shared, tokens, train, normalize = g["meta"].tolist()
+    m = O.OracleBlock(d_model, n_experts, d_ff, top_k, n_shared, activation=g["activation"],
+                      normalize_weights=bool(normalize))
+    dt = g["x"].dtype
+    m = m.to(dt)
+    with torch.no_grad():
+        m.router_W.copy_(g["router_W"])
+        m.W_in.copy_(g["W_in"])
+        m.W_out.copy_(g["W_out"])
+        if n_shared:
+            m.W_sh_in.copy_(g["W_sh_in"])
+            m.W_sh_out.copy_(g["W_sh_out"])
+    m.train(bool(train))
+    return m
+
+
+@pytest.mark.parametrize("case", BLOCK_CASES)
+def test_router_and_plan_match_golden(case):
+    g = load_golden(case)
+    m = _block_from_golden(g)
+    logits, w, idx, probs = m.route(g["x"])
+    assert torch.equal(logits, g["logits"])
+    assert torch.equal(idx, g["topk_idx"])
+    assert torch.equal(w, g["topk_w"])
+    if "probs" in g:
+        assert torch.equal(probs, g["probs"])
+    experts, order, token_idx, counts = O.plan(idx, m.n_experts)
+    assert torch.equal(experts, g["plan_experts"])
+    assert torch.equal(order, g["plan_order"])
+    assert torch.equal(token_idx, g["plan_token_idx"])
+    assert torch.equal(counts, g["plan_counts"])
+    # the canonical tie rule picks the same experts wherever torch.topk had no freedom, and the
+    # same values everywhere
+    tied = O.tied_rows(logits.detach(), m.top_k)
+    canon = O.canonical_topk(logits.detach(), m.top_k)
+    assert torch.equal(canon[~tied], idx[~tied])
+    assert torch.equal(logits.detach().gather(1, canon), logits.detach().gather(1, idx))
+
+
+@pytest.mark.parametrize("case", BLOCK_CASES)
+def test_block_output_matches_golden(case):
+    g = load_golden(case)
+    m = _block_from_golden(g)
+    with torch.no_grad():
+        out = m(g["x"])
+    assert torch.equal(out, g["out"]), rel_l2(out, g["out"])
+    assert torch.allclose(m.aux_loss.float(), g["aux_loss"], atol=1e-7)
+    if "dense_out" in g:
+        w, idx = g["topk_w"], g["topk_idx"]
+        dense = O.dense_forward(g["x"], m.W_in, m.W_out, w, idx, m.activation, m.W_sh_in,
+                                m.W_sh_out)
+        assert torch.equal(dense, g["dense_out"])
+
+
+@pytest.mark.parametrize("case", ["block_fp32_train", "block_bf16_train"])
+def test_block_gradients_match_golden(case):
+    g = load_golden(case)
+    m = _block_from_golden(g)
+    x = g["x"].clone().requires_grad_(True)
+    out = m(x)
+    (out.float().square().mean() + m.aux_loss).backward()
+    pairs = [(x.grad, "grad_x"), (m.router_W.grad, "grad_router_W"), (m.W_in.grad, "grad_W_in"),
+             (m.W_out.grad, "grad_W_out"), (m.W_sh_in.grad, "grad_W_sh_in"),
+             (m.W_sh_out.grad, "grad_W_sh_out")]
+    for got, key in pairs:
+        assert torch.equal(got, g[key]), (key, rel_l2(got, g[key]))
+
+
+def test_closed_form_backward_matches_golden_fp32():
+    """experts_backward / router_backward (the formulas the CUDA kernels implement) reproduce the
+    reference's autograd gradients."""
+    g = load_golden("block_fp32_train")
+    m = _block_from_golden(g)
+    x = g["x"]
+    T, D = x.shape
+    logits, w, idx, probs = m.route(x)
+    out = g["out"]
+    d_out = 2.0 * out / out.numel()
+    dx, dw_in, dw_out, dtw, dsi, dso = O.experts_backward(
+        d_out, x, m.W_in.detach(), m.W_out.detach(), w.detach(), idx, "silu",
+        m.W_sh_in.detach(), m.W_sh_out.detach())
+    assert rel_l2(dw_in, g["grad_W_in"]) < 1e-5
+    assert rel_l2(dw_out, g["grad_W_out"]) < 1e-5
+    assert rel_l2(dsi, g["grad_W_sh_in"]) < 1e-5
+    assert rel_l2(dso, g["grad_W_sh_out"]) < 1e-5
+    counts = g["plan_counts"]
+    f = counts.float() / counts.sum()
+    d_probs = (m.aux_loss_coef * m.n_experts * f / T).expand(T, -1)
+    dl = O.router_backward(logits.detach(), idx, dtw, d_probs, True, True)
+    d_router = x.t() @ dl
+    assert rel_l2(d_router, g["grad_router_W"]) < 1e-5
+    dx_total = dx + dl @ m.router_W.detach().t()
+    assert rel_l2(dx_total, g["grad_x"]) < 1e-5
+
+
+@pytest.mark.parametrize("case", ["routing_e76_k6_fp32", "routing_e76_k6_bf16"])
+def test_routing_at_model_width_matches_golden(case):
+    g = load_golden(case)
+    tokens, n_experts, top_k, _ = g["meta"].tolist()
+    logits, ref_idx = g["logits"], g["topk_idx"]
+    canon = O.canonical_topk(logits, top_k)
+    tied = O.tied_rows(logits, top_k)
+    # bit-equal wherever torch.topk had no freedom
+    assert torch.equal(canon[~tied], ref_idx[~tied])
+    # on tied rows: the same VALUES are selected, in the same order
+    assert torch.equal(logits.gather(1, canon), logits.gather(1, ref_idx))
+    if case.endswith("bf16"):
+        assert tied.any(), "bf16-derived logits are expected to produce exact ties"
+    _, order, token_idx, counts = O.plan(ref_idx, n_experts)
+    assert torch.equal(order, g["plan_order"])
+    assert torch.equal(token_idx, g["plan_token_idx"])
+    assert torch.equal(counts, g["plan_counts"])
+
+
+def test_padded_dispatch_layout_invariants():
+    """The invariants the reference asserts on its dispatch op (tests/test_moe_kernel.py:197-216),
+    on the oracle's padded layout, plus stability."""
+    idx = torch.randint(0, 8, (50, 2))
+    sids, eids, offs, counts, npp, inv = O.dispatch(idx, 8)
+    m = idx.numel()
+    assert sids.numel() == O.l_cap(m, 8)
+    assert torch.equal(sids[inv.long()], torch.arange(m, dtype=torch.int32))
+    assert torch.equal(counts.long(), torch.bincount(idx.reshape(-1), minlength=8))
+    assert int(npp) == int(((counts + 127) // 128 * 128).sum())
+    flat = idx.reshape(-1)
+    for e in range(8):
+        run = sids[int(offs[e]): int(offs[e]) + int(counts[e])].long()
+        assert (flat[run] == e).all()
+        assert (run[1:] > run[:-1]).all()          # stable: ascending pair id inside a run
+        assert (sids[int(offs[e]) + int(counts[e]): int(offs[e + 1])] == m).all()
+    _, order, _, _ = O.plan(idx, 8)
+    assert torch.equal(sids[sids < m].long(), order)
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "src", "model")),
+                    reason="no checkout of the reference on this machine")
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("train", [False, True])
+def test_oracle_matches_live_reference_at_model_shape(dtype, train):
+    """nanoSpeaker's real block shape (E=76, k=6, D=576, d_ff=192, S=2) on fresh random inputs:
+    the oracle and the imported reference agree bit for bit, forward and backward."""
+    sys.path.insert(0, REF)
+    try:
+        from src.model.moe import MoEBlock as RefBlock
+    finally:
+        sys.path.remove(REF)
+    torch.manual_seed(11)
+    ref = RefBlock(576, 76, d_ff=192, top_k=6, n_shared=2, capacity_factor=None, fused=False,
+                   kernel=False).to(dtype)
+    ref.train(train)
+    m = O.OracleBlock(576, 76, 192, 6, 2).to(dtype)
+    m.train(train)
+    with torch.no_grad():
+        m.router_W.copy_(ref.router.W)
+        m.W_in.copy_(ref.W_in)
+        m.W_out.copy_(ref.W_out)
+        m.W_sh_in.copy_(ref.W_sh_in)
+        m.W_sh_out.copy_(ref.W_sh_out)
+    x = torch.randn(256, 576).to(dtype)
+    xa, xb = x.clone().requires_grad_(train), x.clone().requires_grad_(train)
+    with torch.set_grad_enabled(train):
+        oa, ob = ref(xa), m(xb)
+    assert torch.equal(oa, ob)
+    assert torch.equal(ref.expert_counts, m.expert_counts)
+    if train:
+        (oa.float().square().mean() + ref.aux_loss).backward()
+        (ob.float().square().mean() + m.aux_loss).backward()
+        assert torch.equal(xa.grad, xb.grad)
+        assert torch.equal(ref.W_in.grad, m.W_in.grad)
+        assert torch.equal(ref.W_out.grad, m.W_out.grad)
+        assert torch.equal(ref.router.W.grad, m.router_W.grad)
+        assert torch.equal(ref.W_sh_in.grad, m.W_sh_in.grad)
