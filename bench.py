@@ -201,10 +201,9 @@ def build_block(device):
     return m
 
 
-def stage_rooflines(m, x, pk):
-    """Time every kernel of the step alone (CUDA events on the current stream, operands rotated
-    through 3 buffer copies so a launch does not find its input in L2) and put each next to its
-    algorithmic work."""
+def build_stages(m, x):
+    """Every kernel of the step as a standalone callable with its algorithmic work per launch.
+    Operands are rotated through 3 buffer copies so a launch does not find its input in L2."""
     from nanospeaker_b200 import kernels as K
     T, D, H, E, k = x.shape[0], D_MODEL, D_HIDDEN, N_EXPERTS, TOP_K
     M = T * k
@@ -268,6 +267,15 @@ def stage_rooflines(m, x, pk):
             ("shared wgrad_out (per expert)", TF, 2.0 * T * H * D, N_SHARED,
              lambda i: K.wgrad(hs[i % 3], xr[i % 3], None, 1)),
         ]
+    return stages
+
+
+def stage_rooflines(m, x, pk):
+    """Time every kernel of the step alone (CUDA events on the current stream) and put each next
+    to its algorithmic work."""
+    GE = "hbm"
+    stages = build_stages(m, x)
+    with torch.no_grad():
         out = []
         for name, bound, work, per_step, fn in stages:
             for i in range(3):
@@ -307,6 +315,19 @@ def run_ours(args):
     pk = peaks()
 
     m = build_block(dev)
+    if args.profile_stage:
+        # for `ncu -k ...`: launch one stage's kernel a few times on the bench workload and leave
+        x = torch.randn(TOKENS, D_MODEL, generator=torch.Generator().manual_seed(100)).bfloat16()
+        hits = [s for s in build_stages(m, x.to(dev)) if args.profile_stage in s[0]]
+        if not hits:
+            raise SystemExit(f"no stage matches {args.profile_stage!r}")
+        with torch.no_grad():
+            for i in range(3):
+                hits[0][4](i)
+        torch.cuda.synchronize()
+        K.check_status(dev)
+        print(json.dumps({"profiled_stage": hits[0][0], "launches": 3}))
+        return
     g = torch.Generator().manual_seed(100 + rank)      # every rank has its own token shard
     host_x = [torch.randn(TOKENS, D_MODEL, generator=g).bfloat16().pin_memory()
               for _ in range(N_INPUT_SETS)]
@@ -419,6 +440,8 @@ def main():
                     help="also all-reduce the weight gradients across ranks inside the step")
     ap.add_argument("--no-stages", action="store_true", help="skip the per-kernel roofline pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-stage", default="",
+                    help="run only the stage whose name contains this text, 3 launches (for ncu)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
