@@ -38,6 +38,7 @@ extern "C" {
 #define MOE_B200_ERR_UNSUPPORTED (-5) /* shape / activation the kernels do not cover */
 #define MOE_B200_ERR_TMA (-6)         /* the driver refused a tensor map */
 #define MOE_B200_ERR_CUDA (-7)        /* a launch failed; see cudaGetLastError */
+#define MOE_B200_ERR_TOO_LARGE (-8)   /* problem exceeds the fixed scratch of a *_static entry point */
 
 /* Activation ids; same numbering as KERNEL_ACTIVATIONS in src/model/moe_kernel.py:75. */
 #define MOE_B200_ACT_SILU 0
@@ -93,6 +94,26 @@ int moe_b200_dispatch(const int64_t* topk_idx, int64_t n_pairs, int32_t n_expert
                       int32_t* sorted_ids, int32_t* expert_ids, int32_t* pad_offsets,
                       int32_t* counts, int32_t* n_post_pad, int32_t* inv_ids, void* scratch,
                       size_t scratch_bytes, int32_t* status, void* stream);
+
+/* moe_b200_dispatch for callers that cannot supply scratch memory. (No counterpart in the
+ * reference: its dispatch allocates through torch.) Meant for hosts that may not allocate device
+ * memory at call time -- a process whose memory plan was frozen at start-up, or a foreign-function
+ * caller that owns its input/output buffers but has no device allocator. The per-block histograms
+ * live in a 256 KB __device__ array inside the library instead of a caller buffer, so:
+ *   - n_pairs may not exceed moe_b200_dispatch_static_max_pairs(n_experts)
+ *     (= floor(65536 / n_experts) * 4096; 3 530 752 pairs at 76 experts), else
+ *     MOE_B200_ERR_TOO_LARGE;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ *     with that device current); make that first call outside any stream capture;
+ *   - all calls on a device share the one array: two calls that may overlap on the GPU (different
+ *     streams, no dependency) race and give wrong plans. Calls ordered on one stream are safe, and
+ *     nothing needs clearing between them because every entry that is read is rewritten first.
+ * It allocates nothing and frees nothing. Outputs are exactly those of moe_b200_dispatch. */
+int64_t moe_b200_dispatch_static_max_pairs(int32_t n_experts);
+int moe_b200_dispatch_static(const int64_t* topk_idx, int64_t n_pairs, int32_t n_experts,
+                             int32_t* sorted_ids, int32_t* expert_ids, int32_t* pad_offsets,
+                             int32_t* counts, int32_t* n_post_pad, int32_t* inv_ids,
+                             int32_t* status, void* stream);
 
 /* Token permute: xs[slot, :] = x[sorted_ids[slot] / top_k, :], zero rows in pad slots, for slots
  * below n_post_pad. Replaces x.index_select(0, token_idx) (src/model/moe.py:397) and the gather

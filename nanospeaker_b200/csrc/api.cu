@@ -15,6 +15,8 @@ const char* moe_b200_error_string(int32_t code) {
     case MOE_B200_ERR_UNSUPPORTED: return "shape or activation not covered by the sm_100a kernels";
     case MOE_B200_ERR_TMA: return "cuTensorMapEncodeTiled refused a tensor map";
     case MOE_B200_ERR_CUDA: return "kernel launch failed";
+    case MOE_B200_ERR_TOO_LARGE:
+      return "problem larger than the fixed built-in scratch of the no-allocation entry point";
     default: return "unknown moe_b200 error code";
   }
 }

@@ -10,6 +10,8 @@
 #include <math_constants.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/moe_b200.h"
 #include "gemm.cuh"  // DevStatus
 
@@ -452,6 +454,74 @@ int moe_b200_dispatch(const int64_t* topk_idx, int64_t n_pairs, int32_t n_expert
   const int64_t l_cap = moe_b200_l_cap(n_pairs, n_experts);
   const int blocks = int((n_pairs + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK);
   int32_t* block_hist = static_cast<int32_t*>(scratch);
+  if (blocks > 0)
+    dispatch_hist_kernel<<<blocks, DISPATCH_THREADS, 0, st>>>(topk_idx, n_pairs, n_experts,
+                                                               block_hist, sorted_ids, l_cap, status);
+  dispatch_scan_kernel<<<1, 1024, 0, st>>>(block_hist, blocks, n_experts, counts, pad_offsets,
+                                           n_post_pad, expert_ids, l_cap / ALIGN_M);
+  if (blocks > 0)
+    dispatch_scatter_kernel<<<blocks, DISPATCH_THREADS, 0, st>>>(
+        topk_idx, n_pairs, n_experts, block_hist, pad_offsets, sorted_ids, inv_ids);
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------- dispatch without caller scratch
+// Some hosts cannot hand this library a scratch buffer: a serving process that fixed its whole
+// device-memory plan at start-up and forbids any later allocation (a late cudaMalloc can
+// synchronise the device and fragment the pool), or a thin foreign-function caller that owns
+// pointers for its inputs and outputs but has no device allocator to ask for one more buffer.
+// For them the per-block histograms of the dispatch live in this fixed array instead. Every GPU
+// that loads the library carries it (256 KB) until the process exits.
+constexpr int STATIC_SCRATCH_INTS = 65536;  // blocks * n_experts must fit: 256 KB of int32
+static __device__ __align__(256) int32_t g_dispatch_scratch[STATIC_SCRATCH_INTS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+std::mutex g_scratch_mutex;
+int32_t* g_scratch_ptr[MAX_DEVICES] = {};  // device address of g_dispatch_scratch, per device
+}  // namespace
+
+// In host code `g_dispatch_scratch` is only a handle for the symbol, not a device address, so the
+// address is looked up once per device (with that device current) and cached.
+static int static_scratch_for_current_device(int32_t** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return MOE_B200_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_dispatch_scratch) != cudaSuccess || p == nullptr)
+      return MOE_B200_ERR_CUDA;
+    g_scratch_ptr[dev] = static_cast<int32_t*>(p);
+  }
+  *out = g_scratch_ptr[dev];
+  return MOE_B200_OK;
+}
+
+extern "C" {
+
+int64_t moe_b200_dispatch_static_max_pairs(int32_t n_experts) {
+  if (n_experts < 1 || n_experts > MAX_EXPERTS) return 0;
+  return int64_t(STATIC_SCRATCH_INTS / n_experts) * DISPATCH_CHUNK;
+}
+
+int moe_b200_dispatch_static(const int64_t* topk_idx, int64_t n_pairs, int32_t n_experts,
+                             int32_t* sorted_ids, int32_t* expert_ids, int32_t* pad_offsets,
+                             int32_t* counts, int32_t* n_post_pad, int32_t* inv_ids,
+                             int32_t* status, void* stream) {
+  if (n_experts < 1 || n_experts > MAX_EXPERTS || n_pairs < 0) return MOE_B200_ERR_SHAPE;
+  if (n_pairs > moe_b200_dispatch_static_max_pairs(n_experts)) return MOE_B200_ERR_TOO_LARGE;
+  if (!sorted_ids && n_pairs) return MOE_B200_ERR_NULL;
+  if (!pad_offsets || !counts || !n_post_pad || !status) return MOE_B200_ERR_NULL;
+  int32_t* block_hist = nullptr;
+  const int rc = static_scratch_for_current_device(&block_hist);
+  if (rc != MOE_B200_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t l_cap = moe_b200_l_cap(n_pairs, n_experts);
+  const int blocks = int((n_pairs + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK);
+  // Nothing in the array has to start at zero: pass 1 overwrites every (block, expert) entry that
+  // passes 2 and 3 read, so whatever the previous call left behind is never seen.
   if (blocks > 0)
     dispatch_hist_kernel<<<blocks, DISPATCH_THREADS, 0, st>>>(topk_idx, n_pairs, n_experts,
                                                                block_hist, sorted_ids, l_cap, status);
