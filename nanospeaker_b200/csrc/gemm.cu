@@ -95,15 +95,6 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs
     attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   });
   if (attr_err != cudaSuccess) return MOE_B200_ERR_CUDA;
-#ifdef MOE_DESC_OVERRIDE
-  GemmArgs dbg = args;
-  const char* e;
-  dbg.mn_lbo = (e = getenv("MOE_MN_LBO")) ? uint32_t(atoi(e)) : 8192u;
-  dbg.mn_sbo = (e = getenv("MOE_MN_SBO")) ? uint32_t(atoi(e)) : 1024u;
-  dbg.mn_kadv = (e = getenv("MOE_MN_KADV")) ? uint32_t(atoi(e)) : 2048u;
-  kern<<<grid, 192, smem, st>>>(tmA, tmB, dbg);
-  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
-#endif
   kern<<<grid, 192, smem, st>>>(tmA, tmB, args);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }

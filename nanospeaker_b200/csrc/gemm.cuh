@@ -47,23 +47,14 @@ struct GemmArgs {
   const __nv_bfloat16* pair_w; // SCALE / GLUBWD: topk_w flat [n_pairs] (null -> weight 1)
   int32_t act;
   int32_t* status;
-#ifdef MOE_DESC_OVERRIDE
-  uint32_t mn_lbo, mn_sbo, mn_kadv;  // bring-up only: MN-major descriptor fields from the host
-#endif
 };
 
 // MN-major 128B-swizzled operand as TMA lays it down in 64 x 64 boxes: 64 MN elements (128 B) per
 // k row, 8 k rows per 1024-byte swizzle atom (SBO), next 64 MN elements one 8 KB box further (LBO);
 // one UMMA K step (16) spans two atoms.
-#ifdef MOE_DESC_OVERRIDE
-#define MN_LBO p.mn_lbo
-#define MN_SBO p.mn_sbo
-#define MN_KADV p.mn_kadv
-#else
 #define MN_LBO 8192u
 #define MN_SBO 1024u
 #define MN_KADV 2048u
-#endif
 
 __device__ __forceinline__ float act_fwd(float g, int act) {
   switch (act) {

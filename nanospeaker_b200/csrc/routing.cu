@@ -86,8 +86,8 @@ __global__ void __launch_bounds__(256)
       if (e < n_experts && !((taken >> i) & 1u)) {
         const unsigned long long key =
             (static_cast<unsigned long long>(float_key(v[i])) << 32) | (0xFFFFFFFFu - uint32_t(e));
-        // +1 keeps a real candidate above the "nothing left" value 0
-        best = key + 1ull > best ? key + 1ull : best;
+        // a real candidate is never 0 (its low word is at least 0xFFFFFFFF - 255)
+        best = key > best ? key : best;
       }
     }
 #pragma unroll
@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(256)
       const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
       best = other > best ? other : best;
     }
-    const int e_win = int(0xFFFFFFFFu - uint32_t((best - 1ull) & 0xFFFFFFFFull));
+    const int e_win = int(0xFFFFFFFFu - uint32_t(best & 0xFFFFFFFFull));
     const int owner = e_win & 31, slot = e_win >> 5;
     float val = 0.f;
 #pragma unroll

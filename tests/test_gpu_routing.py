@@ -54,7 +54,8 @@ def test_router_topk_shapes_and_backward(T, E, k, normalize, full):
 
 
 def test_router_ties_go_to_the_lowest_index():
-    logits = torch.zeros(5, 76)
+    logits = torch.zeros(6, 76)
+    logits[5, 0] = float("nan")
     logits[1, 40] = 1.0
     logits[2] = float("-inf")
     logits[3, 7] = float("nan")         # torch orders NaN above everything
@@ -66,6 +67,7 @@ def test_router_ties_go_to_the_lowest_index():
     assert idx[2].tolist() == [0, 1, 2, 3, 4, 5]
     assert idx[3].tolist() == [7, 0, 1, 2, 3, 4]
     assert idx[4].tolist() == [0, 1, 2, 3, 4, 5]
+    assert idx[5].tolist() == [0, 1, 2, 3, 4, 5]
 
 
 def _check_dispatch(idx, E):
