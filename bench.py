@@ -213,17 +213,18 @@ def build_stages(m, x):
         tw = w.reshape(-1).contiguous()
         logits = (x @ m.router.W).float() + m.router.logit_bias
         copies = lambda t: [t.clone() for _ in range(3)]
+        S = N_SHARED
         xs = copies(K.permute(x, k, sids, npp))
         xr = copies(x)
-        hid = copies(K.up_gemm(xs[0], m.W_in, eids, npp, -1, False, 0))
-        a1 = K.up_gemm(xs[0], m.W_in, eids, npp, -1, True, 0)
-        y = copies(K.down_gemm(hid[0], m.W_out, eids, npp, -1, sids, tw, M))
-        da1 = copies(K.dhidden_glu_bwd(xs[0], m.W_out, eids, npp, -1, sids, tw, M, a1, 0, True)[0])
-        hs = copies(K.up_gemm(x, m.W_sh_in, None, None, 0, False, 0))
-        a1s = K.up_gemm(x, m.W_sh_in, None, None, 0, True, 0)
-        das = copies(K.dhidden_glu_bwd(x, m.W_sh_out, None, None, 0, None, None, 0, a1s, 0,
+        hid0, a1 = K.up_gemm(xs[0], m.W_in, eids, npp, 0, 0, True)
+        hid = copies(hid0)
+        y = copies(K.down_gemm(hid[0], m.W_out, eids, npp, 0, sids, tw, M))
+        da1 = copies(K.dhidden_glu_bwd(xs[0], m.W_out, eids, npp, 0, sids, tw, M, a1, 0, True)[0])
+        hs0, a1s = K.up_gemm(x, m.W_sh_in, None, None, S, 0, True)
+        hs = copies(hs0)
+        das = copies(K.dhidden_glu_bwd(x, m.W_sh_out, None, None, S, None, None, 0, a1s, 0,
                                        False)[0])
-        ys = K.down_gemm(hs[0], m.W_sh_out, None, None, 0, None, None, 0)
+        ys = K.down_gemm(hs[0], m.W_sh_out, None, None, S, None, None, 0)
         dwl = torch.randn_like(w, dtype=torch.float32)
 
         GE, TF = "hbm", "tensor"
@@ -236,36 +237,34 @@ def build_stages(m, x):
             ("dispatch(3 kernels)", GE, M * 8 * 2 + M * 4 * 3, 1, lambda i: K.dispatch(idx, E)),
             ("permute", GE, 2 * M * D * 2 + M * 4, 2,
              lambda i: K.permute(xr[i % 3], k, sids, npp)),
-            ("up_gemm+glu", TF, 2.0 * M * D * 2 * H, 1,
-             lambda i: K.up_gemm(xs[i % 3], m.W_in, eids, npp, -1, False, 0)),
-            ("up_gemm raw (bwd recompute)", TF, 2.0 * M * D * 2 * H, 1,
-             lambda i: K.up_gemm(xs[i % 3], m.W_in, eids, npp, -1, True, 0)),
+            ("up_gemm+glu (+a1 saved)", TF, 2.0 * M * D * 2 * H, 1,
+             lambda i: K.up_gemm(xs[i % 3], m.W_in, eids, npp, 0, 0, True)),
             ("down_gemm+scale", TF, 2.0 * M * H * D, 1,
-             lambda i: K.down_gemm(hid[i % 3], m.W_out, eids, npp, -1, sids, tw, M)),
+             lambda i: K.down_gemm(hid[i % 3], m.W_out, eids, npp, 0, sids, tw, M)),
             ("combine", GE, M * D * 2 + M * 4 + 3 * T * D * 2, 2,
-             lambda i: K.combine(y[i % 3], inv, T, k, ys, ys)),
+             lambda i: K.combine(y[i % 3], inv, T, k, ys[0], ys[1])),
             ("dhidden+glu_bwd", TF, 2.0 * M * D * H, 1,
-             lambda i: K.dhidden_glu_bwd(xs[i % 3], m.W_out, eids, npp, -1, sids, tw, M, a1, 0,
+             lambda i: K.dhidden_glu_bwd(xs[i % 3], m.W_out, eids, npp, 0, sids, tw, M, a1, 0,
                                          True)),
             ("dx_gemm", TF, 2.0 * M * 2 * H * D, 1,
-             lambda i: K.dx_gemm(da1[i % 3], m.W_in, eids, npp, -1)),
+             lambda i: K.dx_gemm(da1[i % 3], m.W_in, eids, npp, 0)),
             ("wgrad_in", TF, 2.0 * M * D * 2 * H, 1,
              lambda i: K.wgrad(xs[i % 3], da1[i % 3], offs, E)),
             ("wgrad_out", TF, 2.0 * M * H * D, 1,
              lambda i: K.wgrad(hid[i % 3], xs[i % 3], offs, E)),
-            ("shared up_gemm (per expert)", TF, 2.0 * T * D * 2 * H, 2 * N_SHARED,
-             lambda i: K.up_gemm(xr[i % 3], m.W_sh_in, None, None, 0, False, 0)),
-            ("shared down_gemm (per expert)", TF, 2.0 * T * H * D, N_SHARED,
-             lambda i: K.down_gemm(hs[i % 3], m.W_sh_out, None, None, 0, None, None, 0)),
-            ("shared dhidden (per expert)", TF, 2.0 * T * D * H, N_SHARED,
-             lambda i: K.dhidden_glu_bwd(xr[i % 3], m.W_sh_out, None, None, 0, None, None, 0, a1s,
+            ("shared up_gemm+glu", TF, 2.0 * S * T * D * 2 * H, 1,
+             lambda i: K.up_gemm(xr[i % 3], m.W_sh_in, None, None, S, 0, True)),
+            ("shared down_gemm", TF, 2.0 * S * T * H * D, 1,
+             lambda i: K.down_gemm(hs[i % 3], m.W_sh_out, None, None, S, None, None, 0)),
+            ("shared dhidden+glu_bwd", TF, 2.0 * S * T * D * H, 1,
+             lambda i: K.dhidden_glu_bwd(xr[i % 3], m.W_sh_out, None, None, S, None, None, 0, a1s,
                                          0, False)),
-            ("shared dx_gemm (per expert)", TF, 2.0 * T * 2 * H * D, N_SHARED,
-             lambda i: K.dx_gemm(das[i % 3], m.W_sh_in, None, None, 0)),
-            ("shared wgrad_in (per expert)", TF, 2.0 * T * D * 2 * H, N_SHARED,
-             lambda i: K.wgrad(xr[i % 3], das[i % 3], None, 1)),
-            ("shared wgrad_out (per expert)", TF, 2.0 * T * H * D, N_SHARED,
-             lambda i: K.wgrad(hs[i % 3], xr[i % 3], None, 1)),
+            ("shared dx_gemm", TF, 2.0 * S * T * 2 * H * D, 1,
+             lambda i: K.dx_gemm(das[i % 3], m.W_sh_in, None, None, S)),
+            ("shared wgrad_in", TF, 2.0 * S * T * D * 2 * H, 1,
+             lambda i: K.wgrad(xr[i % 3], das[i % 3], None, S, b_grouped=True)),
+            ("shared wgrad_out", TF, 2.0 * S * T * H * D, 1,
+             lambda i: K.wgrad(hs[i % 3], xr[i % 3], None, S, a_grouped=True)),
         ]
     return stages
 

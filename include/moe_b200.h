@@ -132,54 +132,73 @@ int moe_b200_combine(const void* y, const int32_t* inv_ids, int64_t n_tokens, in
                      void* stream);
 
 /* Schedule arguments shared by the row-grouped GEMMs below:
- *   rows        rows of the slot-ordered A buffer (l_cap), or the token count when fixed_group >= 0
+ *   rows            rows of the slot-ordered A buffer (l_cap), or the token count when
+ *                   n_fixed_groups > 0
  *   expert_ids, n_post_pad   from moe_b200_dispatch
- *   fixed_group >= 0: every row uses weight matrix `fixed_group` (shared experts, rows in token
- *               order, `rows` need not be a multiple of 128); < 0: per-block owners from expert_ids. */
+ *   n_fixed_groups  0: routed schedule, per-block owners from expert_ids.
+ *                   S > 0: shared-expert schedule -- weight matrices 0..S-1 are each applied to all
+ *                   `rows` rows in token order (`rows` need not be a multiple of 128); outputs are
+ *                   stacked [S, rows, width]. */
 
-/* Up/gate GEMM with the GLU fused: for each live row, [g | u] = a[row] @ w_in[e] (w_in
- * [n_groups, d_model, 2*d_hidden]); out[row] = act(g) * u ([rows, d_hidden], row stride ld_out)
- * or, when write_raw != 0, out[row] = [g | u] ([rows, 2*d_hidden]).
- * Replaces _gemm1_kernel (src/model/moe_kernel.py:269-323). d_hidden must be 128. */
+/* Up/gate GEMM with the GLU fused: [g | u] = a[row] @ w_in[e] (w_in [n_groups, d_model,
+ * 2*d_hidden]); hid[row] = act(g) * u  ([rows, d_hidden]); when raw != NULL it also receives
+ * [g | u] ([rows, 2*d_hidden], kept for the backward). a is [rows, d_model] (shared by all fixed
+ * groups). Replaces _gemm1_kernel (src/model/moe_kernel.py:269-323). d_hidden must be 128. */
 int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w_in,
                      int32_t n_groups, int32_t d_hidden, const int32_t* expert_ids,
-                     const int32_t* n_post_pad, int32_t fixed_group, int32_t write_raw,
-                     int32_t activation, void* out, int64_t ld_out, int32_t* status, void* stream);
+                     const int32_t* n_post_pad, int32_t n_fixed_groups, int32_t activation,
+                     void* hid, void* raw, int32_t* status, void* stream);
 
 /* Down GEMM with the router weight fused: y[row] = (hid[row] @ w_out[e]) * pair_w[sorted_ids[row]]
- * (w_out [n_groups, k_dim, d_model]; weight 1 when pair_w is NULL).
- * Replaces the forward use of _gemm2_kernel (src/model/moe_kernel.py:339-402, 603-613). */
+ * (w_out [n_groups, k_dim, d_model]; weight 1 when pair_w is NULL). With fixed groups hid is
+ * [S, rows, k_dim]. Replaces the forward use of _gemm2_kernel
+ * (src/model/moe_kernel.py:339-402, 603-613). */
 int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void* w_out,
                        int32_t n_groups, int32_t d_model, const int32_t* expert_ids,
-                       const int32_t* n_post_pad, int32_t fixed_group, const int32_t* sorted_ids,
-                       const void* pair_w, int64_t n_pairs, void* y, int32_t* status, void* stream);
+                       const int32_t* n_post_pad, int32_t n_fixed_groups,
+                       const int32_t* sorted_ids, const void* pair_w, int64_t n_pairs, void* y,
+                       int32_t* status, void* stream);
 
 /* Backward through the down GEMM and the GLU in one kernel: G = douts[row] @ w_out[e]^T, then with
  * [g | u] = a1[row] and w = pair_w[pair]:  dtw[pair] = <G, act(g)*u>,
  * da1[row] = [w*G*u*act'(g) | w*G*act(g)],  hidw[row] = w * act(g) * u.
+ * douts is [rows, d_model] (shared by all fixed groups); a1, da1, hidw are stacked per fixed group.
  * Replaces the dH use of _gemm2_kernel plus _glu_bwd_kernel
  * (src/model/moe_kernel.py:676-692, 510-553). dtw may be NULL. */
 int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, const void* w_out,
                              int32_t n_groups, int32_t d_hidden, const int32_t* expert_ids,
-                             const int32_t* n_post_pad, int32_t fixed_group,
+                             const int32_t* n_post_pad, int32_t n_fixed_groups,
                              const int32_t* sorted_ids, const void* pair_w, int64_t n_pairs,
                              const void* a1, int32_t activation, void* da1, void* hidw, void* dtw,
                              int32_t* status, void* stream);
 
 /* dX GEMM: ydx[row] = da1[row] @ w_in[e]^T, reading w_in [n_groups, d_model, 2*d_hidden] in place
- * (no transposed copy). Replaces the dX use of _gemm2_kernel and the w_in.transpose copy
- * (src/model/moe_kernel.py:696-707). */
+ * (no transposed copy). With fixed groups da1 and ydx are stacked [S, rows, .]. Replaces the dX use
+ * of _gemm2_kernel and the w_in.transpose copy (src/model/moe_kernel.py:696-707). */
 int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,
                      int32_t n_groups, int32_t d_model, const int32_t* expert_ids,
-                     const int32_t* n_post_pad, int32_t fixed_group, void* ydx, int32_t* status,
-                     void* stream);
+                     const int32_t* n_post_pad, int32_t n_fixed_groups, void* ydx,
+                     int32_t* status, void* stream);
+
+/* Scratch sizes for moe_b200_wgrad: partial_bytes of fp32 partial tiles (contents arbitrary) and
+ * counter_bytes of int32 counters (must be ZERO before the first call; every call leaves them
+ * zero again). routed != 0: the pad_offsets schedule over `rows` = l_cap rows. */
+int moe_b200_wgrad_scratch(int32_t m_dim, int32_t n_dim, int64_t rows, int32_t n_groups,
+                           int32_t routed, int32_t ks_rows, size_t* partial_bytes,
+                           size_t* counter_bytes);
 
 /* Per-expert weight gradient dw[e] = a_e^T @ b_e over the rows of run e
  * (a [rows, m_dim], b [rows, n_dim], dw [n_groups, m_dim, n_dim]); empty runs give zeros.
- * pad_offsets NULL with n_groups == 1 means one run over rows [0, rows).
- * Replaces _dw_kernel (src/model/moe_kernel.py:453-507, 712-721). */
-int moe_b200_wgrad(const void* a, int32_t m_dim, const void* b, int32_t n_dim, int64_t rows,
-                   const int32_t* pad_offsets, int32_t n_groups, void* dw, int32_t* status,
+ * Routed schedule: pad_offsets [n_groups+1] from the dispatch. Fixed schedule: pad_offsets NULL,
+ * every group spans rows [0, rows); a_grouped / b_grouped say whether that operand is stacked
+ * [n_groups, rows, .] or shared by all groups. The contraction is split into chunks of ks_rows rows
+ * (a multiple of 64) so long runs spread over many SMs; partial tiles are summed in chunk order, so
+ * the result is deterministic. Replaces _dw_kernel (src/model/moe_kernel.py:453-507, 712-721),
+ * which has no split-K. */
+int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* b,
+                   int32_t b_grouped, int32_t n_dim, int64_t rows, const int32_t* pad_offsets,
+                   int32_t n_groups, int32_t ks_rows, void* dw, void* partials,
+                   size_t partial_bytes, void* counters, size_t counter_bytes, int32_t* status,
                    void* stream);
 
 #ifdef __cplusplus

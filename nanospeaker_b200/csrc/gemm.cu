@@ -51,19 +51,21 @@ static bool make_map(CUtensorMap* m, const void* base, int rank, const uint64_t*
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// [rows, cols] row-major activation buffer, K-major A operand: box = 64 cols x 128 rows.
-static bool map_rows_kmajor(CUtensorMap* m, const void* base, int64_t rows, int64_t cols) {
-  const uint64_t dims[2] = {uint64_t(cols), uint64_t(rows)};
-  const uint64_t strides[1] = {uint64_t(cols) * 2};
-  const uint32_t box[2] = {64, 128};
-  return make_map(m, base, 2, dims, strides, box);
+// [groups, rows, cols] row-major activation buffer as the K-major A operand: 64 cols x 128 rows.
+static bool map_rows_kmajor(CUtensorMap* m, const void* base, int64_t groups, int64_t rows,
+                            int64_t cols) {
+  const uint64_t dims[3] = {uint64_t(cols), uint64_t(rows), uint64_t(groups)};
+  const uint64_t strides[2] = {uint64_t(cols) * 2, uint64_t(cols) * uint64_t(rows) * 2};
+  const uint32_t box[3] = {64, 128, 1};
+  return make_map(m, base, 3, dims, strides, box);
 }
-// [rows, cols] row-major buffer read as an MN-major operand (contraction over rows): 64 x 64 boxes.
-static bool map_rows_mnmajor(CUtensorMap* m, const void* base, int64_t rows, int64_t cols) {
-  const uint64_t dims[2] = {uint64_t(cols), uint64_t(rows)};
-  const uint64_t strides[1] = {uint64_t(cols) * 2};
-  const uint32_t box[2] = {64, 64};
-  return make_map(m, base, 2, dims, strides, box);
+// [groups, rows, cols] buffer read as an MN-major operand (contraction over rows): 64 x 64 boxes.
+static bool map_rows_mnmajor(CUtensorMap* m, const void* base, int64_t groups, int64_t rows,
+                             int64_t cols) {
+  const uint64_t dims[3] = {uint64_t(cols), uint64_t(rows), uint64_t(groups)};
+  const uint64_t strides[2] = {uint64_t(cols) * 2, uint64_t(cols) * uint64_t(rows) * 2};
+  const uint32_t box[3] = {64, 64, 1};
+  return make_map(m, base, 3, dims, strides, box);
 }
 // Stacked weights [G, k_dim, n_dim] with n contiguous (the reference's W_in / W_out layout used
 // in the forward): MN-major B operand, 64 (n) x 64 (k) boxes.
@@ -84,104 +86,144 @@ static bool map_weight_kmajor(CUtensorMap* m, const void* base, int64_t groups, 
   return make_map(m, base, 3, dims, strides, box);
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, int MODE, int EPI>
-static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, dim3 grid,
-                  cudaStream_t st) {
-  auto kern = grouped_gemm_kernel<BN, STAGES, A_MN, B_MN, MODE, EPI>;
-  constexpr int smem = GemmSmem<BN, STAGES>::DYNAMIC;
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+  }
+  return n;
+}
+
+// Persistent launch: one CTA per SM (fewer if the tile list is shorter than that).
+template <int BN, int STAGES, bool B_MN, int EPI>
+static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const RowsArgs& args,
+                       int64_t max_tiles, cudaStream_t st) {
+  auto kern = rows_gemm_kernel<BN, STAGES, B_MN, EPI>;
+  constexpr int smem = RowsSmem<BN, STAGES>::DYNAMIC;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [&] {
     attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   });
   if (attr_err != cudaSuccess) return MOE_B200_ERR_CUDA;
-  kern<<<grid, 192, smem, st>>>(tmA, tmB, args);
+  const int64_t sms = sm_count();
+  const unsigned grid = unsigned(max_tiles < sms ? max_tiles : sms);
+  kern<<<grid, ROWS_THREADS, smem, st>>>(tmA, tmB, args);
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+template <int BN, int STAGES>
+static int launch_wgrad(const CUtensorMap& tmA, const CUtensorMap& tmB, const WgradArgs& args,
+                        dim3 grid, cudaStream_t st) {
+  auto kern = wgrad_gemm_kernel<BN, STAGES>;
+  constexpr int smem = WgradSmem<BN, STAGES>::DYNAMIC;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  });
+  if (attr_err != cudaSuccess) return MOE_B200_ERR_CUDA;
+  kern<<<grid, WGRAD_THREADS, smem, st>>>(tmA, tmB, args);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-static GemmArgs base_args(const int32_t* expert_ids, const int32_t* n_post_pad,
-                          int32_t fixed_group, int64_t rows, int32_t* status) {
-  GemmArgs a{};
+static RowsArgs base_args(const int32_t* expert_ids, const int32_t* n_post_pad,
+                          int32_t n_fixed_groups, int64_t rows, int32_t* status) {
+  RowsArgs a{};
   a.expert_ids = expert_ids;
   a.n_post_pad = n_post_pad;
-  a.fixed_group = fixed_group;
+  a.n_fixed_groups = n_fixed_groups;
   a.rows_host = int32_t(rows);
   a.status = status;
   return a;
+}
+
+// Upper bound on the tile count of a row-grouped launch (the live count is on the device).
+static int64_t max_tiles(int64_t rows, int n_chunks, int n_fixed_groups) {
+  return (rows + BM - 1) / BM * n_chunks * (n_fixed_groups > 0 ? n_fixed_groups : 1);
 }
 
 }  // namespace moe
 
 using namespace moe;
 
-#define CHECK_SCHED()                                                                       \
-  if (rows < 0 || n_groups < 1) return MOE_B200_ERR_SHAPE;                                  \
-  if (rows == 0) return MOE_B200_OK;                                                        \
-  if (!status) return MOE_B200_ERR_NULL;                                                    \
-  if (fixed_group < 0 && (!expert_ids || !n_post_pad)) return MOE_B200_ERR_NULL;            \
-  if (fixed_group >= n_groups) return MOE_B200_ERR_SHAPE;                                   \
-  if (fixed_group < 0 && rows % 128 != 0) return MOE_B200_ERR_SHAPE;
+#define CHECK_SCHED()                                                                        \
+  if (rows < 0 || n_groups < 1 || n_fixed_groups < 0) return MOE_B200_ERR_SHAPE;             \
+  if (rows == 0) return MOE_B200_OK;                                                         \
+  if (rows > (int64_t(1) << 30)) return MOE_B200_ERR_SHAPE;                                  \
+  if (!status) return MOE_B200_ERR_NULL;                                                     \
+  if (n_fixed_groups == 0 && (!expert_ids || !n_post_pad)) return MOE_B200_ERR_NULL;         \
+  if (n_fixed_groups > n_groups) return MOE_B200_ERR_SHAPE;                                  \
+  if (n_fixed_groups == 0 && rows % 128 != 0) return MOE_B200_ERR_SHAPE;
 
 extern "C" {
 
 int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w_in,
                      int32_t n_groups, int32_t d_hidden, const int32_t* expert_ids,
-                     const int32_t* n_post_pad, int32_t fixed_group, int32_t write_raw,
-                     int32_t activation, void* out, int64_t ld_out, int32_t* status, void* stream) {
+                     const int32_t* n_post_pad, int32_t n_fixed_groups, int32_t activation,
+                     void* hid, void* raw, int32_t* status, void* stream) {
   CHECK_SCHED();
   if (d_hidden != 128 || d_model % 8 != 0 || d_model < 64) return MOE_B200_ERR_UNSUPPORTED;
   if (activation < 0 || activation > 4) return MOE_B200_ERR_UNSUPPORTED;
-  if (!a || !w_in || !out) return MOE_B200_ERR_NULL;
-  if (!aligned16(a) || !aligned16(w_in) || !aligned16(out) || ld_out % 8 != 0)
+  if (!a || !w_in || !hid) return MOE_B200_ERR_NULL;
+  if (!aligned16(a) || !aligned16(w_in) || !aligned16(hid) || !aligned16(raw))
     return MOE_B200_ERR_ALIGN;
   CUtensorMap tmA, tmB;
-  if (!map_rows_kmajor(&tmA, a, rows, d_model) ||
+  if (!map_rows_kmajor(&tmA, a, 1, rows, d_model) ||
       !map_weight_mnmajor(&tmB, w_in, n_groups, d_model, 2 * d_hidden))
     return MOE_B200_ERR_TMA;
-  GemmArgs g = base_args(expert_ids, n_post_pad, fixed_group, rows, status);
+  RowsArgs g = base_args(expert_ids, n_post_pad, n_fixed_groups, rows, status);
   g.num_k = (d_model + BK - 1) / BK;
   g.n_dim = 2 * d_hidden;
-  g.out = static_cast<__nv_bfloat16*>(out);
-  g.ld_out = ld_out;
+  g.n_chunks = 1;
+  g.out = static_cast<__nv_bfloat16*>(hid);
+  g.ld_out = d_hidden;
+  g.out_gstride = rows * int64_t(d_hidden);
+  g.out2 = static_cast<__nv_bfloat16*>(raw);
+  g.out2_gstride = rows * int64_t(2 * d_hidden);
   g.act = activation;
-  const dim3 grid(unsigned((rows + BM - 1) / BM), 1, 1);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (write_raw) return launch<256, 3, false, true, MODE_ROWS, EPI_RAW>(tmA, tmB, g, grid, st);
-  return launch<256, 3, false, true, MODE_ROWS, EPI_GLU>(tmA, tmB, g, grid, st);
+  return launch_rows<256, 4, true, EPI_GLU>(tmA, tmB, g, max_tiles(rows, 1, n_fixed_groups),
+                                            static_cast<cudaStream_t>(stream));
 }
 
 int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void* w_out,
                        int32_t n_groups, int32_t d_model, const int32_t* expert_ids,
-                       const int32_t* n_post_pad, int32_t fixed_group, const int32_t* sorted_ids,
-                       const void* pair_w, int64_t n_pairs, void* y, int32_t* status,
-                       void* stream) {
+                       const int32_t* n_post_pad, int32_t n_fixed_groups,
+                       const int32_t* sorted_ids, const void* pair_w, int64_t n_pairs, void* y,
+                       int32_t* status, void* stream) {
   CHECK_SCHED();
   if (k_dim % 8 != 0 || k_dim < 64 || d_model % 32 != 0) return MOE_B200_ERR_UNSUPPORTED;
   if (!hid || !w_out || !y) return MOE_B200_ERR_NULL;
-  if (pair_w && fixed_group < 0 && !sorted_ids) return MOE_B200_ERR_NULL;
+  if (pair_w && n_fixed_groups == 0 && !sorted_ids) return MOE_B200_ERR_NULL;
   if (!aligned16(hid) || !aligned16(w_out) || !aligned16(y)) return MOE_B200_ERR_ALIGN;
+  const int gdim = n_fixed_groups > 0 ? n_fixed_groups : 1;
   CUtensorMap tmA, tmB;
-  if (!map_rows_kmajor(&tmA, hid, rows, k_dim) ||
+  if (!map_rows_kmajor(&tmA, hid, gdim, rows, k_dim) ||
       !map_weight_mnmajor(&tmB, w_out, n_groups, k_dim, d_model))
     return MOE_B200_ERR_TMA;
-  GemmArgs g = base_args(expert_ids, n_post_pad, fixed_group, rows, status);
+  RowsArgs g = base_args(expert_ids, n_post_pad, n_fixed_groups, rows, status);
+  g.a_grouped = n_fixed_groups > 0;
   g.num_k = (k_dim + BK - 1) / BK;
   g.n_dim = d_model;
+  g.n_chunks = (d_model + 191) / 192;
   g.sorted_ids = sorted_ids;
   g.n_pairs = int32_t(n_pairs);
   g.pair_w = static_cast<const __nv_bfloat16*>(pair_w);
   g.out = static_cast<__nv_bfloat16*>(y);
   g.ld_out = d_model;
-  const dim3 grid(unsigned((rows + BM - 1) / BM), unsigned((d_model + 191) / 192), 1);
-  return launch<192, 2, false, true, MODE_ROWS, EPI_SCALE>(tmA, tmB, g, grid,
-                                                           static_cast<cudaStream_t>(stream));
+  g.out_gstride = rows * int64_t(d_model);
+  return launch_rows<192, 4, true, EPI_SCALE>(
+      tmA, tmB, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
 }
 
 int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, const void* w_out,
                              int32_t n_groups, int32_t d_hidden, const int32_t* expert_ids,
-                             const int32_t* n_post_pad, int32_t fixed_group,
+                             const int32_t* n_post_pad, int32_t n_fixed_groups,
                              const int32_t* sorted_ids, const void* pair_w, int64_t n_pairs,
                              const void* a1, int32_t activation, void* da1, void* hidw, void* dtw,
                              int32_t* status, void* stream) {
@@ -189,81 +231,122 @@ int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, c
   if (d_hidden != 128 || d_model % 8 != 0 || d_model < 64) return MOE_B200_ERR_UNSUPPORTED;
   if (activation < 0 || activation > 4) return MOE_B200_ERR_UNSUPPORTED;
   if (!douts || !w_out || !a1 || !da1 || !hidw) return MOE_B200_ERR_NULL;
-  if (pair_w && fixed_group < 0 && !sorted_ids) return MOE_B200_ERR_NULL;
+  if (pair_w && n_fixed_groups == 0 && !sorted_ids) return MOE_B200_ERR_NULL;
   if (!aligned16(douts) || !aligned16(w_out) || !aligned16(a1) || !aligned16(da1) ||
       !aligned16(hidw))
     return MOE_B200_ERR_ALIGN;
   CUtensorMap tmA, tmB;
-  if (!map_rows_kmajor(&tmA, douts, rows, d_model) ||
+  if (!map_rows_kmajor(&tmA, douts, 1, rows, d_model) ||
       !map_weight_kmajor(&tmB, w_out, n_groups, d_hidden, d_model, 128))
     return MOE_B200_ERR_TMA;
-  GemmArgs g = base_args(expert_ids, n_post_pad, fixed_group, rows, status);
+  RowsArgs g = base_args(expert_ids, n_post_pad, n_fixed_groups, rows, status);
   g.num_k = (d_model + BK - 1) / BK;
   g.n_dim = d_hidden;
+  g.n_chunks = 1;
   g.sorted_ids = sorted_ids;
   g.n_pairs = int32_t(n_pairs);
   g.pair_w = static_cast<const __nv_bfloat16*>(pair_w);
   g.aux = static_cast<const __nv_bfloat16*>(a1);
+  g.aux_gstride = rows * int64_t(2 * d_hidden);
   g.out = static_cast<__nv_bfloat16*>(da1);
+  g.ld_out = 2 * d_hidden;
+  g.out_gstride = rows * int64_t(2 * d_hidden);
   g.out2 = static_cast<__nv_bfloat16*>(hidw);
+  g.out2_gstride = rows * int64_t(d_hidden);
   g.dtw = static_cast<__nv_bfloat16*>(dtw);
   g.act = activation;
-  const dim3 grid(unsigned((rows + BM - 1) / BM), 1, 1);
-  return launch<128, 4, false, false, MODE_ROWS, EPI_GLUBWD>(tmA, tmB, g, grid,
-                                                             static_cast<cudaStream_t>(stream));
+  return launch_rows<128, 6, false, EPI_GLUBWD>(tmA, tmB, g, max_tiles(rows, 1, n_fixed_groups),
+                                                static_cast<cudaStream_t>(stream));
 }
 
 int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,
                      int32_t n_groups, int32_t d_model, const int32_t* expert_ids,
-                     const int32_t* n_post_pad, int32_t fixed_group, void* ydx, int32_t* status,
-                     void* stream) {
+                     const int32_t* n_post_pad, int32_t n_fixed_groups, void* ydx,
+                     int32_t* status, void* stream) {
   CHECK_SCHED();
   if (d_hidden % 4 != 0 || d_hidden < 32 || d_model % 32 != 0) return MOE_B200_ERR_UNSUPPORTED;
   if (!da1 || !w_in || !ydx) return MOE_B200_ERR_NULL;
   if (!aligned16(da1) || !aligned16(w_in) || !aligned16(ydx)) return MOE_B200_ERR_ALIGN;
+  const int gdim = n_fixed_groups > 0 ? n_fixed_groups : 1;
   CUtensorMap tmA, tmB;
-  if (!map_rows_kmajor(&tmA, da1, rows, 2 * d_hidden) ||
+  if (!map_rows_kmajor(&tmA, da1, gdim, rows, 2 * d_hidden) ||
       !map_weight_kmajor(&tmB, w_in, n_groups, d_model, 2 * d_hidden, 192))
     return MOE_B200_ERR_TMA;
-  GemmArgs g = base_args(expert_ids, n_post_pad, fixed_group, rows, status);
+  RowsArgs g = base_args(expert_ids, n_post_pad, n_fixed_groups, rows, status);
+  g.a_grouped = n_fixed_groups > 0;
   g.num_k = (2 * d_hidden + BK - 1) / BK;
   g.n_dim = d_model;
+  g.n_chunks = (d_model + 191) / 192;
   g.out = static_cast<__nv_bfloat16*>(ydx);
   g.ld_out = d_model;
-  const dim3 grid(unsigned((rows + BM - 1) / BM), unsigned((d_model + 191) / 192), 1);
-  return launch<192, 3, false, false, MODE_ROWS, EPI_RAW>(tmA, tmB, g, grid,
-                                                          static_cast<cudaStream_t>(stream));
+  g.out_gstride = rows * int64_t(d_model);
+  return launch_rows<192, 5, false, EPI_RAW>(
+      tmA, tmB, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
 }
 
-int moe_b200_wgrad(const void* a, int32_t m_dim, const void* b, int32_t n_dim, int64_t rows,
-                   const int32_t* pad_offsets, int32_t n_groups, void* dw, int32_t* status,
+static int64_t wgrad_items(int64_t rows, int n_groups, int routed, int ks_rows) {
+  return routed ? rows / ks_rows + n_groups : int64_t(n_groups) * wgrad_chunks(int(rows), ks_rows);
+}
+
+int moe_b200_wgrad_scratch(int32_t m_dim, int32_t n_dim, int64_t rows, int32_t n_groups,
+                           int32_t routed, int32_t ks_rows, size_t* partial_bytes,
+                           size_t* counter_bytes) {
+  if (m_dim < 1 || n_dim < 1 || rows < 0 || n_groups < 1 || ks_rows < 64 || ks_rows % 64 != 0 ||
+      !partial_bytes || !counter_bytes)
+    return MOE_B200_ERR_SHAPE;
+  const int bn = n_dim % 256 == 0 ? 256 : 192;
+  const int64_t tiles_xy = int64_t((m_dim + BM - 1) / BM) * ((n_dim + bn - 1) / bn);
+  *partial_bytes = size_t(wgrad_items(rows, n_groups, routed, ks_rows)) * size_t(tiles_xy) * BM *
+                   bn * sizeof(float);
+  *counter_bytes = size_t(n_groups) * size_t(tiles_xy) * sizeof(int32_t);
+  return MOE_B200_OK;
+}
+
+int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* b,
+                   int32_t b_grouped, int32_t n_dim, int64_t rows, const int32_t* pad_offsets,
+                   int32_t n_groups, int32_t ks_rows, void* dw, void* partials,
+                   size_t partial_bytes, void* counters, size_t counter_bytes, int32_t* status,
                    void* stream) {
-  if (rows < 0 || n_groups < 1 || m_dim < 1 || n_dim < 1) return MOE_B200_ERR_SHAPE;
+  if (rows < 0 || rows > (int64_t(1) << 30) || n_groups < 1 || m_dim < 1 || n_dim < 1)
+    return MOE_B200_ERR_SHAPE;
+  if (ks_rows < 64 || ks_rows % 64 != 0) return MOE_B200_ERR_SHAPE;
   if (m_dim % 8 != 0 || n_dim % 32 != 0) return MOE_B200_ERR_UNSUPPORTED;
-  if (!pad_offsets && n_groups != 1) return MOE_B200_ERR_SHAPE;
-  if (!a || !b || !dw || !status) return MOE_B200_ERR_NULL;
-  if (!aligned16(a) || !aligned16(b) || !aligned16(dw)) return MOE_B200_ERR_ALIGN;
+  if (pad_offsets && (a_grouped || b_grouped)) return MOE_B200_ERR_SHAPE;
+  if (pad_offsets && rows % 128 != 0) return MOE_B200_ERR_SHAPE;
+  if (!a || !b || !dw || !status || !partials || !counters) return MOE_B200_ERR_NULL;
+  if (!aligned16(a) || !aligned16(b) || !aligned16(dw) || !aligned16(partials))
+    return MOE_B200_ERR_ALIGN;
+  size_t need_p = 0, need_c = 0;
+  const int routed = pad_offsets != nullptr;
+  moe_b200_wgrad_scratch(m_dim, n_dim, rows, n_groups, routed, ks_rows, &need_p, &need_c);
+  if (partial_bytes < need_p || counter_bytes < need_c) return MOE_B200_ERR_SCRATCH;
   CUtensorMap tmA, tmB;
   // rows == 0 still launches: every C[e] must be written (with zeros)
   const int64_t map_rows = rows > 0 ? rows : 1;
-  if (!map_rows_mnmajor(&tmA, a, map_rows, m_dim) || !map_rows_mnmajor(&tmB, b, map_rows, n_dim))
+  if (!map_rows_mnmajor(&tmA, a, a_grouped ? n_groups : 1, map_rows, m_dim) ||
+      !map_rows_mnmajor(&tmB, b, b_grouped ? n_groups : 1, map_rows, n_dim))
     return MOE_B200_ERR_TMA;
-  GemmArgs g{};
+  WgradArgs g{};
   g.pad_offsets = pad_offsets;
+  g.n_groups = n_groups;
   g.rows_host = int32_t(rows);
-  g.fixed_group = pad_offsets ? -1 : 0;
+  g.ks_rows = ks_rows;
+  g.a_grouped = a_grouped;
+  g.b_grouped = b_grouped;
   g.m_dim = m_dim;
   g.n_dim = n_dim;
   g.out = static_cast<__nv_bfloat16*>(dw);
+  g.partials = static_cast<float*>(partials);
+  g.counters = static_cast<int32_t*>(counters);
   g.status = status;
+  const unsigned items = unsigned(wgrad_items(rows, n_groups, routed, ks_rows));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (n_dim % 256 == 0) {
-    const dim3 grid(unsigned((m_dim + BM - 1) / BM), unsigned(n_dim / 256), unsigned(n_groups));
-    return launch<256, 3, true, true, MODE_WGRAD, EPI_WGRAD>(tmA, tmB, g, grid, st);
+    const dim3 grid(unsigned((m_dim + BM - 1) / BM), unsigned(n_dim / 256), items);
+    return launch_wgrad<256, 4>(tmA, tmB, g, grid, st);
   }
-  const dim3 grid(unsigned((m_dim + BM - 1) / BM), unsigned((n_dim + 191) / 192),
-                  unsigned(n_groups));
-  return launch<192, 3, true, true, MODE_WGRAD, EPI_WGRAD>(tmA, tmB, g, grid, st);
+  const dim3 grid(unsigned((m_dim + BM - 1) / BM), unsigned((n_dim + 191) / 192), items);
+  return launch_wgrad<192, 5>(tmA, tmB, g, grid, st);
 }
 
 }  // extern "C"

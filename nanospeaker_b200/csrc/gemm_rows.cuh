@@ -1,0 +1,294 @@
+// Persistent row-grouped GEMM (see gemm.cuh). 320 threads: warp 0 TMA, warp 1 MMA, warps 2..9
+// epilogue (two warps per TMEM lane quadrant, each taking half of the tile's column chunks).
+#pragma once
+
+namespace moe {
+
+constexpr int ROWS_THREADS = 320;
+constexpr int EPI_WARPS = 8;
+
+template <int BN, int STAGES>
+struct RowsSmem {
+  static constexpr int B_STAGE_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int N_BARS = 2 * STAGES + 4;  // full, empty, tmem_full[2], tmem_empty[2]
+  static constexpr int MISC_OFFSET = BAR_OFFSET + 8 * N_BARS;      // tmem slot, abort flag
+  static constexpr int PART_OFFSET = MISC_OFFSET + 16;             // float[128] dtw partials
+  static constexpr int TOTAL = PART_OFFSET + 128 * 4;
+  static constexpr int DYNAMIC = TOTAL + 1024;  // slack for manual 1024-byte alignment
+};
+
+struct TileCoord {
+  int m_tile, n0, group, z;
+};
+
+// t -> (group slice z, 128-row block, N chunk); N chunks of one row block are adjacent so its A
+// tile is still in L2 for the next chunk.
+__device__ __forceinline__ TileCoord decode_tile(const RowsArgs& p, int t, int m_tiles, int bn) {
+  TileCoord c;
+  const int nc = t % p.n_chunks;
+  const int rest = t / p.n_chunks;
+  c.m_tile = rest % m_tiles;
+  c.z = rest / m_tiles;
+  c.n0 = nc * bn;
+  c.group = p.n_fixed_groups > 0 ? c.z : __ldg(p.expert_ids + c.m_tile);
+  return c;
+}
+
+template <int ACT, int BN>
+__device__ __forceinline__ void epilogue_glu(uint32_t taddr, int c_lo, int c_hi, bool row_ok,
+                                             __nv_bfloat16* out_row, __nv_bfloat16* raw_row) {
+  constexpr int HALF = BN / 2;  // gate = accumulator cols [0, HALF), up = [HALF, BN)
+#pragma unroll 1
+  for (int c = c_lo; c < c_hi; ++c) {
+    float g[32], u[32];
+    tmem_ld32(taddr + c * 32, g);
+    tmem_ld32(taddr + HALF + c * 32, u);
+    tmem_ld_wait();
+    if (raw_row != nullptr && row_ok) {
+      store_bf16x32(raw_row + c * 32, g);
+      store_bf16x32(raw_row + HALF + c * 32, u);
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) g[i] = act_f<ACT>(g[i]) * u[i];
+    if (row_ok) store_bf16x32(out_row + c * 32, g);
+  }
+}
+
+// acc = G = dOut @ W_out^T for this row; a1 = [gate | up]; H = BN. Returns this thread's share of
+// <G, hidden>.
+template <int ACT, int BN>
+__device__ __forceinline__ float epilogue_glubwd(uint32_t taddr, int c_lo, int c_hi, bool row_ok,
+                                                 float w, const __nv_bfloat16* a1,
+                                                 __nv_bfloat16* da1, __nv_bfloat16* hw) {
+  float part = 0.f;
+#pragma unroll 1
+  for (int c = c_lo; c < c_hi; ++c) {
+    float G[32], g[32], u[32];
+    tmem_ld32(taddr + c * 32, G);
+    if (row_ok) {
+      load_bf16x32(a1 + c * 32, g);
+      load_bf16x32(a1 + BN + c * 32, u);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) g[i] = u[i] = 0.f;
+    }
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float a, d;
+      act_fd<ACT>(g[i], a, d);
+      const float hid = a * u[i];
+      part += G[i] * hid;
+      const float dh = w * G[i];
+      g[i] = dh * u[i] * d;  // d gate
+      u[i] = dh * a;         // d up
+      G[i] = w * hid;        // weighted hidden, the A operand of dW_out
+    }
+    if (row_ok) {
+      store_bf16x32(da1 + c * 32, g);
+      store_bf16x32(da1 + BN + c * 32, u);
+      store_bf16x32(hw + c * 32, G);
+    }
+  }
+  return part;
+}
+
+template <int BN, int STAGES, bool B_MN, int EPI>
+__global__ void __launch_bounds__(ROWS_THREADS, 1)
+    rows_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
+                     const __grid_constant__ CUtensorMap tmB, const RowsArgs p) {
+  using L = RowsSmem<BN, STAGES>;
+  static_assert(BN % 64 == 0 && BN <= 256, "BN must be a multiple of 64 up to 256");
+  constexpr uint32_t TMEM_BUF = BN <= 128 ? 128 : 256;  // columns per accumulator buffer
+  constexpr uint32_t TMEM_COLS = 2 * TMEM_BUF;
+
+  // ------------------------------------------------------------ tile list (before any barrier)
+  const int live = p.n_fixed_groups > 0 ? p.rows_host : __ldg(p.n_post_pad);
+  const int m_tiles = (live + BM - 1) / BM;
+  const int total_tiles = m_tiles * p.n_chunks * (p.n_fixed_groups > 0 ? p.n_fixed_groups : 1);
+  if (int(blockIdx.x) >= total_tiles) return;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::MISC_OFFSET);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* dtw_part = reinterpret_cast<float*>(smem + L::PART_OFFSET);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar + s, 1);
+      mbar_init(empty_bar + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar + b, 1);
+      mbar_init(tempty_bar + b, EPI_WARPS);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+        const TileCoord tc = decode_tile(p, t, m_tiles, BN);
+        for (int kt = 0; kt < p.num_k; ++kt, ++it) {
+          const int s = it % STAGES;
+          const uint32_t use = it / STAGES;
+          if (use > 0 && !mbar_wait(empty_bar + s, (use - 1) & 1, p.status)) {
+            *abort_flag = 1;
+            atomicExch(p.status, ST_WAIT_TIMEOUT);
+            break;
+          }
+          uint8_t* sA = smem + s * L::STAGE_BYTES;
+          uint8_t* sB = sA + A_STAGE_BYTES;
+          mbar_expect_tx(full_bar + s, L::STAGE_BYTES);
+          const int k0 = kt * BK;
+          tma_load_3d(sA, &tmA, full_bar + s, k0, tc.m_tile * BM, p.a_grouped ? tc.z : 0);
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sB + j * 8192, &tmB, full_bar + s, tc.n0 + 64 * j, k0, tc.group);
+          } else {
+            tma_load_3d(sB, &tmB, full_bar + s, k0, tc.n0, tc.group);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      uint32_t it = 0;
+      int j = 0;
+      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x, ++j) {
+        const int b = j & 1;
+        const uint32_t use = uint32_t(j) >> 1;
+        if (use > 0 && !mbar_wait(tempty_bar + b, (use - 1) & 1, p.status)) {
+          *abort_flag = 1;
+          atomicExch(p.status, ST_WAIT_TIMEOUT);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + b * TMEM_BUF;
+        for (int kt = 0; kt < p.num_k; ++kt, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(full_bar + s, (it / STAGES) & 1, p.status)) {
+            *abort_flag = 1;
+            atomicExch(p.status, ST_WAIT_TIMEOUT);
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + s * L::STAGE_BYTES);
+          issue_stage_mmas<BN, false, B_MN>(sA, sA + A_STAGE_BYTES, d_tmem, kt == 0);
+          umma_commit(empty_bar + s);  // stage reusable once these MMAs have read it
+        }
+        umma_commit(tfull_bar + b);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------------- epilogue
+    const int ew = warp - 2;
+    const int q = warp & 3;   // TMEM lane quadrant this warp may read
+    const int half = ew >> 2; // which half of the column chunks
+    const int row = q * 32 + lane;
+    constexpr int NCH = (EPI == EPI_GLU ? BN / 2 : BN) / 32;
+    static_assert(NCH % 2 == 0, "column chunks must split evenly over the two epilogue halves");
+    const int c_lo = half * (NCH / 2), c_hi = c_lo + NCH / 2;
+
+    int j = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++j) {
+      const TileCoord tc = decode_tile(p, t, m_tiles, BN);
+      const int b = j & 1;
+      // A wait that gives up (status already flagged) falls through: the epilogue keeps its
+      // barrier protocol intact and the host sees the status word.
+      if (!mbar_wait(tfull_bar + b, (uint32_t(j) >> 1) & 1, p.status))
+        atomicExch(p.status, ST_WAIT_TIMEOUT);
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + b * TMEM_BUF + (uint32_t(q * 32) << 16);
+
+      const int64_t grow = int64_t(tc.m_tile) * BM + row;
+      const bool fixed = p.n_fixed_groups > 0;
+      const bool row_ok = !fixed || grow < p.rows_host;
+      int pair = p.n_pairs;
+      if (!fixed && p.sorted_ids != nullptr) pair = __ldg(p.sorted_ids + grow);
+      float w = 1.f;
+      if (p.pair_w != nullptr) w = pair < p.n_pairs ? __bfloat162float(p.pair_w[pair]) : 0.f;
+      __nv_bfloat16* out_row = p.out + tc.z * p.out_gstride + grow * p.ld_out;
+
+      if constexpr (EPI == EPI_GLU) {
+        __nv_bfloat16* raw_row =
+            p.out2 ? p.out2 + tc.z * p.out2_gstride + grow * BN : nullptr;
+        switch (p.act) {
+          case ACT_SILU: epilogue_glu<ACT_SILU, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row); break;
+          case ACT_GELU: epilogue_glu<ACT_GELU, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row); break;
+          case ACT_RELU: epilogue_glu<ACT_RELU, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row); break;
+          case ACT_SIGMOID: epilogue_glu<ACT_SIGMOID, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row); break;
+          default: epilogue_glu<ACT_TANH, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row); break;
+        }
+      } else if constexpr (EPI == EPI_RAW || EPI == EPI_SCALE) {
+#pragma unroll 1
+        for (int c = c_lo; c < c_hi; ++c) {
+          float v[32];
+          tmem_ld32(taddr + c * 32, v);
+          tmem_ld_wait();
+          if constexpr (EPI == EPI_SCALE) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= w;
+          }
+          if (row_ok && tc.n0 + c * 32 < p.n_dim) store_bf16x32(out_row + tc.n0 + c * 32, v);
+        }
+      } else {  // EPI_GLUBWD
+        const __nv_bfloat16* a1 = p.aux + tc.z * p.aux_gstride + grow * (2 * BN);
+        __nv_bfloat16* da1 = out_row;  // ld_out == 2 * BN
+        __nv_bfloat16* hw = p.out2 + tc.z * p.out2_gstride + grow * BN;
+        float part;
+        switch (p.act) {
+          case ACT_SILU: part = epilogue_glubwd<ACT_SILU, BN>(taddr, c_lo, c_hi, row_ok, w, a1, da1, hw); break;
+          case ACT_GELU: part = epilogue_glubwd<ACT_GELU, BN>(taddr, c_lo, c_hi, row_ok, w, a1, da1, hw); break;
+          case ACT_RELU: part = epilogue_glubwd<ACT_RELU, BN>(taddr, c_lo, c_hi, row_ok, w, a1, da1, hw); break;
+          case ACT_SIGMOID: part = epilogue_glubwd<ACT_SIGMOID, BN>(taddr, c_lo, c_hi, row_ok, w, a1, da1, hw); break;
+          default: part = epilogue_glubwd<ACT_TANH, BN>(taddr, c_lo, c_hi, row_ok, w, a1, da1, hw); break;
+        }
+        // <G, hidden> of a row is split over the two column halves: fold half 1 into half 0
+        if (p.dtw != nullptr) {
+          if (half == 1) dtw_part[row] = part;
+          epi_bar_sync(EPI_WARPS * 32);
+          if (half == 0 && row_ok && pair < p.n_pairs)
+            p.dtw[pair] = __float2bfloat16(part + dtw_part[row]);
+          epi_bar_sync(EPI_WARPS * 32);
+        }
+      }
+      // this warp has drained its share of accumulator buffer b
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar + b);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+}  // namespace moe

@@ -150,78 +150,117 @@ def combine(y: torch.Tensor, inv_ids: torch.Tensor, n_tokens: int, top_k: int,
     return out
 
 
-def up_gemm(a, w_in, expert_ids, n_post_pad, fixed_group: int, write_raw: bool, act: int,
-            out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """a [rows, D] x w_in [G, D, 2H] -> act(g)*u [rows, H] (or raw [g|u] [rows, 2H])."""
+def _stack(n_fixed: int, rows: int, width: int, like: torch.Tensor) -> torch.Tensor:
+    shape = (rows, width) if n_fixed == 0 else (n_fixed, rows, width)
+    return torch.empty(shape, dtype=like.dtype, device=like.device)
+
+
+def up_gemm(a, w_in, expert_ids, n_post_pad, n_fixed: int, act: int, want_raw: bool):
+    """a [rows, D] x w_in [G, D, 2H] -> (act(g)*u [rows, H], raw [g|u] [rows, 2H] | None).
+    n_fixed = S > 0 applies weight matrices 0..S-1 to all rows; outputs are then [S, rows, .]."""
     _need_cuda(a, w_in)
     rows, d = a.shape
     g, _, h2 = w_in.shape
     h = h2 // 2
-    if out is None:
-        out = torch.empty((rows, h2 if write_raw else h), dtype=a.dtype, device=a.device)
+    hid = _stack(n_fixed, rows, h, a)
+    raw = _stack(n_fixed, rows, h2, a) if want_raw else None
     _lib.check(_lib.load().moe_b200_up_gemm(
         a.data_ptr(), rows, d, w_in.data_ptr(), g, h, _lib.ptr(expert_ids), _lib.ptr(n_post_pad),
-        fixed_group, int(write_raw), act, out.data_ptr(), out.stride(0),
-        status_word(a.device).data_ptr(), _stream(a)), "moe_b200_up_gemm")
+        n_fixed, act, hid.data_ptr(), _lib.ptr(raw), status_word(a.device).data_ptr(),
+        _stream(a)), "moe_b200_up_gemm")
     _count(1 if rows else 0)
-    return out
+    return hid, raw
 
 
-def down_gemm(hid, w_out, expert_ids, n_post_pad, fixed_group: int, sorted_ids, pair_w,
+def down_gemm(hid, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair_w,
               n_pairs: int) -> torch.Tensor:
-    """hid [rows, K] x w_out [G, K, D] -> y [rows, D], scaled per row by pair_w[sorted_ids[row]]."""
+    """hid [rows, K] (or [S, rows, K]) x w_out [G, K, D] -> y, scaled per row by
+    pair_w[sorted_ids[row]] on the routed schedule."""
     _need_cuda(hid, w_out)
-    rows, k = hid.shape
+    rows, k = hid.shape[-2:]
     g, _, d = w_out.shape
-    y = torch.empty((rows, d), dtype=hid.dtype, device=hid.device)
+    y = _stack(n_fixed, rows, d, hid)
     _lib.check(_lib.load().moe_b200_down_gemm(
         hid.data_ptr(), rows, k, w_out.data_ptr(), g, d, _lib.ptr(expert_ids),
-        _lib.ptr(n_post_pad), fixed_group, _lib.ptr(sorted_ids), _lib.ptr(pair_w), n_pairs,
+        _lib.ptr(n_post_pad), n_fixed, _lib.ptr(sorted_ids), _lib.ptr(pair_w), n_pairs,
         y.data_ptr(), status_word(hid.device).data_ptr(), _stream(hid)), "moe_b200_down_gemm")
     _count(1 if rows else 0)
     return y
 
 
-def dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, fixed_group: int, sorted_ids, pair_w,
+def dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair_w,
                     n_pairs: int, a1, act: int, want_dtw: bool):
-    """-> (da1 [rows, 2H], hidw [rows, H], dtw [n_pairs] | None)."""
+    """-> (da1 [.., rows, 2H], hidw [.., rows, H], dtw [n_pairs] | None)."""
     _need_cuda(douts, w_out, a1)
     rows, d = douts.shape
     g, h, _ = w_out.shape
-    da1 = torch.empty((rows, 2 * h), dtype=douts.dtype, device=douts.device)
-    hidw = torch.empty((rows, h), dtype=douts.dtype, device=douts.device)
+    da1 = _stack(n_fixed, rows, 2 * h, douts)
+    hidw = _stack(n_fixed, rows, h, douts)
     dtw = torch.empty(n_pairs, dtype=douts.dtype, device=douts.device) if want_dtw else None
     _lib.check(_lib.load().moe_b200_dhidden_glu_bwd(
         douts.data_ptr(), rows, d, w_out.data_ptr(), g, h, _lib.ptr(expert_ids),
-        _lib.ptr(n_post_pad), fixed_group, _lib.ptr(sorted_ids), _lib.ptr(pair_w), n_pairs,
+        _lib.ptr(n_post_pad), n_fixed, _lib.ptr(sorted_ids), _lib.ptr(pair_w), n_pairs,
         a1.data_ptr(), act, da1.data_ptr(), hidw.data_ptr(), _lib.ptr(dtw),
         status_word(douts.device).data_ptr(), _stream(douts)), "moe_b200_dhidden_glu_bwd")
     _count(1 if rows else 0)
     return da1, hidw, dtw
 
 
-def dx_gemm(da1, w_in, expert_ids, n_post_pad, fixed_group: int) -> torch.Tensor:
-    """da1 [rows, 2H] x w_in[e]^T -> ydx [rows, D]."""
+def dx_gemm(da1, w_in, expert_ids, n_post_pad, n_fixed: int) -> torch.Tensor:
+    """da1 [.., rows, 2H] x w_in[e]^T -> ydx [.., rows, D]."""
     _need_cuda(da1, w_in)
-    rows, h2 = da1.shape
+    rows, h2 = da1.shape[-2:]
     g, d, _ = w_in.shape
-    ydx = torch.empty((rows, d), dtype=da1.dtype, device=da1.device)
+    ydx = _stack(n_fixed, rows, d, da1)
     _lib.check(_lib.load().moe_b200_dx_gemm(
         da1.data_ptr(), rows, h2 // 2, w_in.data_ptr(), g, d, _lib.ptr(expert_ids),
-        _lib.ptr(n_post_pad), fixed_group, ydx.data_ptr(), status_word(da1.device).data_ptr(),
+        _lib.ptr(n_post_pad), n_fixed, ydx.data_ptr(), status_word(da1.device).data_ptr(),
         _stream(da1)), "moe_b200_dx_gemm")
     _count(1 if rows else 0)
     return ydx
 
 
-def wgrad(a, b, pad_offsets, n_groups: int) -> torch.Tensor:
-    """dw[e] = a_e^T @ b_e over run e's rows: a [rows, Mdim], b [rows, Ndim] -> [G, Mdim, Ndim]."""
+WGRAD_KS_ROUTED = 2048   # rows per split-K chunk: expert runs
+WGRAD_KS_SHARED = 1024   # rows per split-K chunk: shared experts (every token, few groups)
+
+_wgrad_counters = {}
+
+
+def _counters(device, nbytes: int) -> torch.Tensor:
+    """Persistent zeroed int32 counters for the split-K reduction (each launch leaves them zero)."""
+    dev = torch.device(device)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), nbytes)
+    c = _wgrad_counters.get(key)
+    if c is None:
+        c = torch.zeros(max(nbytes // 4, 1), dtype=torch.int32, device=dev)
+        _wgrad_counters[key] = c
+    return c
+
+
+def wgrad(a, b, pad_offsets, n_groups: int, ks_rows: Optional[int] = None,
+          a_grouped: bool = False, b_grouped: bool = False) -> torch.Tensor:
+    """dw[e] = a_e^T @ b_e over run e's rows -> [G, Mdim, Ndim]. Routed schedule: a [rows, Mdim],
+    b [rows, Ndim] in slot order plus pad_offsets. Fixed schedule (pad_offsets None): every group
+    spans all rows; a / b are [G, rows, .] when *_grouped, else shared by the groups."""
     _need_cuda(a, b)
-    rows, m_dim = a.shape
-    n_dim = b.shape[1]
+    import ctypes
+    rows, m_dim = a.shape[-2:]
+    n_dim = b.shape[-1]
+    routed = pad_offsets is not None
+    if ks_rows is None:
+        ks_rows = WGRAD_KS_ROUTED if routed else WGRAD_KS_SHARED
+    lib = _lib.load()
+    pb, cb = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    _lib.check(lib.moe_b200_wgrad_scratch(m_dim, n_dim, rows, n_groups, int(routed), ks_rows,
+                                          ctypes.byref(pb), ctypes.byref(cb)),
+               "moe_b200_wgrad_scratch")
+    partials = torch.empty(max(pb.value, 16), dtype=torch.uint8, device=a.device)
+    counters = _counters(a.device, cb.value)
     dw = torch.empty((n_groups, m_dim, n_dim), dtype=a.dtype, device=a.device)
-    _lib.check(_lib.load().moe_b200_wgrad(
-        a.data_ptr(), m_dim, b.data_ptr(), n_dim, rows, _lib.ptr(pad_offsets), n_groups,
-        dw.data_ptr(), status_word(a.device).data_ptr(), _stream(a)), "moe_b200_wgrad")
+    _lib.check(lib.moe_b200_wgrad(
+        a.data_ptr(), int(a_grouped), m_dim, b.data_ptr(), int(b_grouped), n_dim, rows,
+        _lib.ptr(pad_offsets), n_groups, ks_rows, dw.data_ptr(), partials.data_ptr(), pb.value,
+        counters.data_ptr(), cb.value, status_word(a.device).data_ptr(), _stream(a)),
+        "moe_b200_wgrad")
     _count(1)
     return dw

@@ -148,12 +148,19 @@ def moe_experts(
     n_post_pad: torch.Tensor,
     inv_ids: torch.Tensor,
     activation: str,
-) -> torch.Tensor:
+    save_for_backward: bool,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """out[t] = sum_j topk_w[t,j] * expert_{idx[t,j]}(x[t])  (+ sum_s shared_s(x[t])).
 
     permute -> up/gate GEMM with fused GLU -> down GEMM with fused router weight -> token-major
     fp32 combine; the shared experts run through the same GEMM kernels on the unpermuted tokens
     and join in the combine. All tensors share x's dtype (the wrapper casts).
+
+    Returns (out, xs, a1, a1_sh). xs [l_cap, D] is the permuted input; with save_for_backward the
+    up GEMM also stores its pre-activations a1 [l_cap, 2H] (routed) and a1_sh [S, T, 2H] (shared)
+    so the backward does not recompute them -- 180 GB of HBM make keeping ~180 MB per block the
+    cheaper side of the trade the reference settles the other way on a 4 GB card
+    (src/model/moe_kernel.py:663-664). Without it they are empty.
     """
     x, w_in, w_out = x.contiguous(), w_in.contiguous(), w_out.contiguous()
     _check_inputs(x, w_in, w_out, w_sh_in)
@@ -162,31 +169,47 @@ def moe_experts(
     topk = topk_w.shape[-1]
     m = n * topk
     if n == 0:
-        return x.new_zeros((0, d))
+        return x.new_zeros((0, d)), x.new_empty(0), x.new_empty(0), x.new_empty(0)
     tw = topk_w.reshape(-1).contiguous()
 
     xs = K.permute(x, topk, sorted_ids, n_post_pad)
-    hid = K.up_gemm(xs, w_in, expert_ids, n_post_pad, -1, False, act)
-    y = K.down_gemm(hid, w_out, expert_ids, n_post_pad, -1, sorted_ids, tw, m)
+    hid, a1 = K.up_gemm(xs, w_in, expert_ids, n_post_pad, 0, act, save_for_backward)
+    y = K.down_gemm(hid, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m)
     extras: List[Optional[torch.Tensor]] = [None, None]
+    a1_sh = None
     if w_sh_in is not None:
         w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
-        for s in range(w_sh_in.shape[0]):
-            hs = K.up_gemm(x, w_sh_in, None, None, s, False, act)
-            extras[s] = K.down_gemm(hs, w_sh_out, None, None, s, None, None, 0)
-    return K.combine(y, inv_ids, n, topk, extras[0], extras[1])
+        s_n = w_sh_in.shape[0]
+        hs, a1_sh = K.up_gemm(x, w_sh_in, None, None, s_n, act, save_for_backward)
+        ys = K.down_gemm(hs, w_sh_out, None, None, s_n, None, None, 0)
+        for s in range(s_n):
+            extras[s] = ys[s]
+    out = K.combine(y, inv_ids, n, topk, extras[0], extras[1])
+    return (out, xs, a1 if a1 is not None else x.new_empty(0),
+            a1_sh if a1_sh is not None else x.new_empty(0))
 
 
 @moe_experts.register_fake
 def _(x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
-      n_post_pad, inv_ids, activation):
-    return x.new_empty(x.shape)
+      n_post_pad, inv_ids, activation, save_for_backward):
+    n, d = x.shape
+    cap = sorted_ids.shape[0]
+    h2 = w_in.shape[2]
+    if n == 0:
+        return x.new_empty((0, d)), x.new_empty(0), x.new_empty(0), x.new_empty(0)
+    a1 = x.new_empty((cap, h2)) if save_for_backward else x.new_empty(0)
+    a1_sh = (x.new_empty((w_sh_in.shape[0], n, h2))
+             if save_for_backward and w_sh_in is not None else x.new_empty(0))
+    return x.new_empty(x.shape), x.new_empty((cap, d)), a1, a1_sh
 
 
 @torch.library.custom_op("moe_b200::moe_experts_bwd", mutates_args=())
 def moe_experts_bwd(
     grad_out: torch.Tensor,
     x: torch.Tensor,
+    xs: torch.Tensor,
+    a1: torch.Tensor,
+    a1_sh: torch.Tensor,
     w_in: torch.Tensor,
     w_out: torch.Tensor,
     topk_w: torch.Tensor,
@@ -201,7 +224,7 @@ def moe_experts_bwd(
     activation: str,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """(dx, dW_in, dW_out, dtopk_w, dW_sh_in, dW_sh_out); the last two are empty without shared
-    experts. Pre-activations are recomputed, as in src/model/moe_kernel.py:663-672."""
+    experts. xs / a1 / a1_sh are the tensors the forward kept."""
     grad_out = grad_out.to(x.dtype).contiguous()
     x, w_in, w_out = x.contiguous(), w_in.contiguous(), w_out.contiguous()
     _check_inputs(x, w_in, w_out, w_sh_in)
@@ -212,12 +235,10 @@ def moe_experts_bwd(
     m = n * topk
     tw = topk_w.reshape(-1).contiguous()
 
-    xs = K.permute(x, topk, sorted_ids, n_post_pad)
-    a1 = K.up_gemm(xs, w_in, expert_ids, n_post_pad, -1, True, act)
     douts = K.permute(grad_out, topk, sorted_ids, n_post_pad)
-    da1, hidw, dtw = K.dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, -1, sorted_ids, tw, m,
+    da1, hidw, dtw = K.dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m,
                                        a1, act, True)
-    ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, -1)
+    ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0)
     dw_in = K.wgrad(xs, da1, pad_offsets, e_n)
     dw_out = K.wgrad(hidw, douts, pad_offsets, e_n)
 
@@ -227,22 +248,20 @@ def moe_experts_bwd(
     if w_sh_in is not None:
         w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
         s_n = w_sh_in.shape[0]
-        dw_sh_in = torch.empty_like(w_sh_in)
-        dw_sh_out = torch.empty_like(w_sh_out)
+        da1s, hids, _ = K.dhidden_glu_bwd(grad_out, w_sh_out, None, None, s_n, None, None, 0,
+                                          a1_sh, act, False)
+        ydxs = K.dx_gemm(da1s, w_sh_in, None, None, s_n)
         for s in range(s_n):
-            a1s = K.up_gemm(x, w_sh_in, None, None, s, True, act)
-            da1s, hids, _ = K.dhidden_glu_bwd(grad_out, w_sh_out, None, None, s, None, None, 0,
-                                              a1s, act, False)
-            extras[s] = K.dx_gemm(da1s, w_sh_in, None, None, s)
-            dw_sh_in[s] = K.wgrad(x, da1s, None, 1)[0]
-            dw_sh_out[s] = K.wgrad(hids, grad_out, None, 1)[0]
+            extras[s] = ydxs[s]
+        dw_sh_in = K.wgrad(x, da1s, None, s_n, b_grouped=True)
+        dw_sh_out = K.wgrad(hids, grad_out, None, s_n, a_grouped=True)
     dx = K.combine(ydx, inv_ids, n, topk, extras[0], extras[1])
     return dx, dw_in, dw_out, dtw.view_as(topk_w), dw_sh_in, dw_sh_out
 
 
 @moe_experts_bwd.register_fake
-def _(grad_out, x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets,
-      counts, n_post_pad, inv_ids, activation):
+def _(grad_out, x, xs, a1, a1_sh, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
+      pad_offsets, counts, n_post_pad, inv_ids, activation):
     return (torch.empty_like(x), torch.empty_like(w_in), torch.empty_like(w_out),
             torch.empty_like(topk_w),
             torch.empty_like(w_sh_in) if w_sh_in is not None else x.new_empty(0),
@@ -251,9 +270,14 @@ def _(grad_out, x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_id
 
 def _experts_setup(ctx, inputs, output):
     (x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
-     n_post_pad, inv_ids, activation) = inputs
-    saved = [x, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts, n_post_pad,
-             inv_ids]
+     n_post_pad, inv_ids, activation, save_for_backward) = inputs
+    out, xs, a1, a1_sh = output
+    ctx.mark_non_differentiable(xs, a1, a1_sh)
+    if not save_for_backward:
+        raise RuntimeError("moe_experts was run with save_for_backward=False but a gradient is "
+                           "being recorded; call it through fused_moe_forward")
+    saved = [x, xs, a1, a1_sh, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts,
+             n_post_pad, inv_ids]
     ctx.has_shared = w_sh_in is not None
     if ctx.has_shared:
         saved += [w_sh_in, w_sh_out]
@@ -261,15 +285,15 @@ def _experts_setup(ctx, inputs, output):
     ctx.activation = activation
 
 
-def _experts_backward(ctx, grad_out):
-    (x, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts, n_post_pad, inv_ids,
-     *rest) = ctx.saved_tensors
+def _experts_backward(ctx, grad_out, g_xs, g_a1, g_a1_sh):
+    (x, xs, a1, a1_sh, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts,
+     n_post_pad, inv_ids, *rest) = ctx.saved_tensors
     w_sh_in, w_sh_out = (rest[0], rest[1]) if ctx.has_shared else (None, None)
     dx, dw_in, dw_out, dtw, dsi, dso = moe_experts_bwd(
-        grad_out, x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets,
-        counts, n_post_pad, inv_ids, ctx.activation)
+        grad_out, x, xs, a1, a1_sh, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids,
+        expert_ids, pad_offsets, counts, n_post_pad, inv_ids, ctx.activation)
     return (dx, dw_in, dw_out, dtw, dsi if ctx.has_shared else None,
-            dso if ctx.has_shared else None, None, None, None, None, None, None, None)
+            dso if ctx.has_shared else None, None, None, None, None, None, None, None, None)
 
 
 moe_experts.register_autograd(_experts_backward, setup_context=_experts_setup)
@@ -292,6 +316,9 @@ def fused_moe_forward(x, w_in, w_out, topk_w, topk_idx, b_in, b_out, activation,
             "or kernel=False")
     sids, eids, offs, counts, npp, inv = moe_dispatch(topk_idx, w_in.shape[0])
     cast = lambda t: None if t is None else t.to(x.dtype)
-    out = moe_experts(x, cast(w_in), cast(w_out), topk_w.to(x.dtype), cast(w_sh_in),
-                      cast(w_sh_out), sids, eids, offs, counts, npp, inv, activation)
+    tensors = (x, w_in, w_out, topk_w, w_sh_in, w_sh_out)
+    save = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
+    out, _, _, _ = moe_experts(x, cast(w_in), cast(w_out), topk_w.to(x.dtype), cast(w_sh_in),
+                               cast(w_sh_out), sids, eids, offs, counts, npp, inv, activation,
+                               save)
     return out, counts

@@ -280,5 +280,5 @@ def test_opcheck_and_fake_kernels():
     plan = moe_dispatch(idx, 4)
     rg = lambda t: t.detach().clone().requires_grad_(True)
     torch.library.opcheck(moe_experts, (rg(x), rg(m.W_in), rg(m.W_out), rg(w), rg(m.W_sh_in),
-                                        rg(m.W_sh_out), *plan, "silu"),
+                                        rg(m.W_sh_out), *plan, "silu", True),
                           test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))

@@ -82,18 +82,19 @@ def test_forward_gemm_stages(T, E, k, D, skew):
     xs = torch.zeros(sids.numel(), D, dtype=torch.bfloat16)
     xs[:nl] = xs_ref
     a1_ref = _per_expert(xs_ref, w_in, offs)
-    a1 = K().up_gemm(g(xs), g(w_in), g(eids), g(npp), -1, True, 0).cpu()
-    assert rel_l2(a1[:nl], a1_ref) < TOL
+    _, a1 = K().up_gemm(g(xs), g(w_in), g(eids), g(npp), 0, 0, True)
+    assert rel_l2(a1.cpu()[:nl], a1_ref) < TOL
     for name, act in [("silu", 0), ("gelu", 1), ("relu", 2), ("sigmoid", 3), ("tanh", 4)]:
-        hid = K().up_gemm(g(xs), g(w_in), g(eids), g(npp), -1, False, act).cpu()
+        hid, raw = K().up_gemm(g(xs), g(w_in), g(eids), g(npp), 0, act, False)
+        assert raw is None
         gate, up = a1_ref.chunk(2, -1)
-        assert rel_l2(hid[:nl], O.ACTS[name](gate) * up) < TOL, name
+        assert rel_l2(hid.cpu()[:nl], O.ACTS[name](gate) * up) < TOL, name
     gate, up = a1_ref.chunk(2, -1)
     hid_b = torch.zeros(sids.numel(), H, dtype=torch.bfloat16)
     hid_b[:nl] = (torch.nn.functional.silu(gate) * up).bfloat16()
     twf = tw.reshape(-1)
     wslot = torch.where(live, twf[sids[:nl].long().clamp(max=M - 1)].float(), torch.zeros(()))
-    y = K().down_gemm(g(hid_b), g(w_out), g(eids), g(npp), -1, g(sids), g(twf), M).cpu()
+    y = K().down_gemm(g(hid_b), g(w_out), g(eids), g(npp), 0, g(sids), g(twf), M).cpu()
     y_ref = _per_expert(hid_b[:nl], w_out, offs) * wslot[:, None]
     assert rel_l2(y[:nl], y_ref) < TOL
     assert (y[:nl][~live] == 0).all()                 # pad slots carry exact zeros
@@ -115,7 +116,7 @@ def test_backward_gemm_stages(T, E, k, D, skew):
     pad = lambda t, w: torch.cat([t, torch.zeros(cap - nl, w, dtype=t.dtype)])
     a1_b = pad(_per_expert(xs_ref, w_in, offs).bfloat16(), 2 * H)
 
-    da1, hidw, dtw = K().dhidden_glu_bwd(g(pad(douts_ref, D)), g(w_out), g(eids), g(npp), -1,
+    da1, hidw, dtw = K().dhidden_glu_bwd(g(pad(douts_ref, D)), g(w_out), g(eids), g(npp), 0,
                                          g(sids), g(twf), M, g(a1_b), 0, True)
     G = _per_expert(douts_ref, w_out, offs, transpose=True)
     gate, up = a1_b[:nl].float().chunk(2, -1)
@@ -129,7 +130,7 @@ def test_backward_gemm_stages(T, E, k, D, skew):
     assert rel_l2(dtw.cpu(), dtw_ref) < TOL
 
     da1_in = pad((torch.randn(nl, 2 * H) * live[:, None]).bfloat16(), 2 * H)
-    ydx = K().dx_gemm(g(da1_in), g(w_in), g(eids), g(npp), -1).cpu()
+    ydx = K().dx_gemm(g(da1_in), g(w_in), g(eids), g(npp), 0).cpu()
     assert rel_l2(ydx[:nl], _per_expert(da1_in[:nl], w_in, offs, transpose=True)) < TOL
 
     xs_b = pad(xs_ref, D)
@@ -148,23 +149,65 @@ def test_backward_gemm_stages(T, E, k, D, skew):
     K().check_status("cuda")
 
 
-@pytest.mark.parametrize("T", [1, 5, 127, 128, 129, 1000])
+@pytest.mark.parametrize("T", [1, 5, 127, 128, 129, 1000, 3000])
 def test_shared_expert_schedule_on_unpermuted_tokens(T):
-    """fixed_group: rows in token order, any row count, OOB rows masked."""
+    """Fixed-group schedule: all S weight matrices over the rows in token order, any row count,
+    out-of-range rows masked; forward and backward stages, incl. split-K weight gradients."""
     D, H, S = 576, 128, 2
     x = torch.randn(T, D).bfloat16()
+    dout = torch.randn(T, D).bfloat16()
     wsi = (torch.randn(S, D, 2 * H) * D ** -0.5).bfloat16()
     wso = (torch.randn(S, H, D) * H ** -0.5).bfloat16()
     g = lambda t: t.cuda()
+    hid, raw = K().up_gemm(g(x), g(wsi), None, None, S, 0, True)
+    y = K().down_gemm(hid, g(wso), None, None, S, None, None, 0)
+    da1, hidw, _ = K().dhidden_glu_bwd(g(dout), g(wso), None, None, S, None, None, 0, raw, 0, False)
+    ydx = K().dx_gemm(da1, g(wsi), None, None, S)
+    dwi = K().wgrad(g(x), da1, None, S, b_grouped=True)
+    dwo = K().wgrad(hidw, g(dout), None, S, a_grouped=True)
+    dwi_small_chunks = K().wgrad(g(x), da1, None, S, ks_rows=64, b_grouped=True)
+    assert hid.shape == (S, T, H) and y.shape == (S, T, D) and dwi.shape == (S, D, 2 * H)
     for s in range(S):
-        gate, up = (x.float() @ wsi[s].float()).chunk(2, -1)
-        hid_ref = torch.nn.functional.silu(gate) * up
-        hid = K().up_gemm(g(x), g(wsi), None, None, s, False, 0)
-        assert rel_l2(hid.cpu(), hid_ref) < TOL
-        y = K().down_gemm(hid, g(wso), None, None, s, None, None, 0).cpu()
-        assert rel_l2(y, hid.cpu().float() @ wso[s].float()) < TOL
-        dws = K().wgrad(g(x), hid, None, 1).cpu()
-        assert rel_l2(dws[0], x.float().t() @ hid.cpu().float()) < TOL
+        a1_ref = x.float() @ wsi[s].float()
+        gate, up = a1_ref.chunk(2, -1)
+        assert rel_l2(raw[s].cpu(), a1_ref) < TOL
+        assert rel_l2(hid[s].cpu(), torch.nn.functional.silu(gate) * up) < TOL
+        assert rel_l2(y[s].cpu(), hid[s].cpu().float() @ wso[s].float()) < TOL
+        gb, ub = raw[s].cpu().float().chunk(2, -1)
+        sg = torch.sigmoid(gb)
+        act, dact = gb * sg, sg * (1 + gb * (1 - sg))
+        G = dout.float() @ wso[s].float().t()
+        assert rel_l2(da1[s].cpu(), torch.cat([G * ub * dact, G * act], -1)) < TOL
+        assert rel_l2(hidw[s].cpu(), act * ub) < TOL
+        assert rel_l2(ydx[s].cpu(), da1[s].cpu().float() @ wsi[s].float().t()) < TOL
+        assert rel_l2(dwi[s].cpu(), x.float().t() @ da1[s].cpu().float()) < TOL
+        assert rel_l2(dwi_small_chunks[s].cpu(), x.float().t() @ da1[s].cpu().float()) < TOL
+        assert rel_l2(dwo[s].cpu(), hidw[s].cpu().float().t() @ dout.float()) < TOL
+    K().check_status("cuda")
+
+
+def test_wgrad_split_k_is_deterministic_and_chunk_size_independent():
+    """A hot expert (thousands of rows) is split over many CTAs; the partials are summed in chunk
+    order, so two runs agree bit for bit and chunk sizes only move fp32 rounding."""
+    torch.manual_seed(4)
+    T, E, k, D, H = 6000, 8, 2, 192, 128
+    idx = torch.stack([torch.zeros(T, dtype=torch.long), torch.randint(1, E, (T,))], 1)
+    sids, eids, offs, counts, npp, inv = O.dispatch(idx, E)
+    nl, cap = int(npp), sids.numel()
+    a = torch.zeros(cap, D).bfloat16()
+    b = torch.zeros(cap, 2 * H).bfloat16()
+    live = sids[:nl] < T * k
+    a[:nl] = (torch.randn(nl, D) * live[:, None]).bfloat16()
+    b[:nl] = (torch.randn(nl, 2 * H) * live[:, None]).bfloat16()
+    g = lambda t: t.cuda()
+    r1 = K().wgrad(g(a), g(b), g(offs), E, ks_rows=1024)
+    r2 = K().wgrad(g(a), g(b), g(offs), E, ks_rows=1024)
+    r3 = K().wgrad(g(a), g(b), g(offs), E, ks_rows=128)
+    assert torch.equal(r1, r2)
+    ref = torch.stack([a[int(offs[e]):int(offs[e + 1])].float().t()
+                       @ b[int(offs[e]):int(offs[e + 1])].float() for e in range(E)])
+    assert rel_l2(r1.cpu(), ref) < TOL and rel_l2(r3.cpu(), ref) < TOL
+    K().check_status("cuda")
 
 
 def test_entry_points_reject_bad_arguments():
@@ -174,6 +217,6 @@ def test_entry_points_reject_bad_arguments():
                     torch.zeros(1, dtype=torch.int32, device="cuda"))
     w = torch.randn(2, 64, 128, device="cuda").bfloat16()       # d_hidden 64: not covered
     with pytest.raises(RuntimeError, match="not covered"):
-        K().up_gemm(torch.randn(128, 64, device="cuda").bfloat16(), w, None, None, 0, False, 0)
+        K().up_gemm(torch.randn(128, 64, device="cuda").bfloat16(), w, None, None, 1, 0, False)
     with pytest.raises(RuntimeError, match="CUDA"):
         K().router_topk(torch.randn(4, 8), 2, True, False, False)   # CPU tensor: no fallback
