@@ -346,14 +346,40 @@ def run_ours(args):
             from nanospeaker_b200.parallel import all_reduce_gradients
             all_reduce_gradients(params)
 
-    def e2e_step(i):
+    # The step has no host sync and no data-dependent shape, so the whole forward+backward is
+    # captured once into a CUDA graph and replayed: the ~60 launches of a step then cost one
+    # submission instead of ~1 ms of Python and launch overhead.
+    static_x = dev_x[0].clone().requires_grad_(True)
+    static_dout = dev_dout[0].clone()
+
+    def capture(with_loss):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                for p in params:
+                    p.grad = None
+                static_x.grad = None
+                out = m(static_x)
+                if with_loss:
+                    (out.float().square().mean() + m.aux_loss).backward()
+                else:
+                    torch.autograd.backward([out, m.aux_loss], [static_dout, one])
+        torch.cuda.current_stream().wait_stream(side)
         for p in params:
             p.grad = None
-        x = host_x[i % N_INPUT_SETS].to(dev, non_blocking=True).requires_grad_(True)
-        out = m(x)
-        loss = out.float().square().mean() + m.aux_loss
-        loss.backward()
-        return loss.item()                              # device -> host read of the step's result
+        static_x.grad = None
+        graph = torch.cuda.CUDAGraph()
+        l0 = K.LAUNCHES
+        with torch.cuda.graph(graph):
+            out = m(static_x)
+            if with_loss:
+                loss = out.float().square().mean() + m.aux_loss
+                loss.backward()
+            else:
+                loss = None
+                torch.autograd.backward([out, m.aux_loss], [static_dout, one])
+        return graph, loss, K.LAUNCHES - l0
 
     def barrier():
         if world > 1:
@@ -379,10 +405,39 @@ def run_ours(args):
         return ms, t0, time.time()
 
     warmup = max(args.warmup, 3)
+    use_graph = not args.no_graph and not (args.grad_allreduce and world > 1)
+    eager_ms, _, _ = timed(step, args.steps, warmup)
+    if use_graph:
+        graph, _, per_step_launches = capture(with_loss=False)
+        graph_e2e, static_loss, _ = capture(with_loss=True)
+
+        def value_step(i):
+            static_x.detach().copy_(dev_x[i % N_INPUT_SETS])
+            static_dout.copy_(dev_dout[i % N_INPUT_SETS])
+            graph.replay()
+
+        def e2e_step(i):
+            static_x.detach().copy_(host_x[i % N_INPUT_SETS], non_blocking=True)  # H2D, pinned
+            graph_e2e.replay()
+            return static_loss.item()                     # D2H read of the step's result
+    else:
+        value_step = step
+        l0 = K.LAUNCHES
+        step(0)
+        per_step_launches = K.LAUNCHES - l0
+
+        def e2e_step(i):
+            for p in params:
+                p.grad = None
+            x = host_x[i % N_INPUT_SETS].to(dev, non_blocking=True).requires_grad_(True)
+            out = m(x)
+            loss = out.float().square().mean() + m.aux_loss
+            loss.backward()
+            return loss.item()
+
     sampler = ClockSampler(local)
-    l0 = K.LAUNCHES
-    ms, t0, t1 = timed(step, args.steps, warmup)
-    launches = (K.LAUNCHES - l0) * args.steps // (args.steps + warmup)
+    ms, t0, t1 = timed(value_step, args.steps, warmup)
+    launches = per_step_launches * args.steps
     clocks = sampler.stop(t0, t1)
     K.check_status(dev)
     e2e_ms, _, _ = timed(e2e_step, args.steps, warmup)
@@ -405,6 +460,8 @@ def run_ours(args):
                               / (pk["bf16_tflops"] * 1e12),
                               "nominal_2250": 100 * value / world * FLOP_PER_TOKEN_FWD_BWD / 2.25e15},
             "grad_allreduce": bool(args.grad_allreduce and world > 1),
+            "cuda_graph": use_graph,
+            "eager_ms_per_step": eager_ms / args.steps,
         }
         if not args.no_stages:
             stages = stage_rooflines(m, dev_x[0], pk)
@@ -439,6 +496,8 @@ def main():
                     help="also all-reduce the weight gradients across ranks inside the step")
     ap.add_argument("--no-stages", action="store_true", help="skip the per-kernel roofline pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="time eager module calls instead of a captured CUDA graph of the step")
     ap.add_argument("--profile-stage", default="",
                     help="run only the stage whose name contains this text, 3 launches (for ncu)")
     args = ap.parse_args()

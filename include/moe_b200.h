@@ -180,26 +180,23 @@ int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void
                      const int32_t* n_post_pad, int32_t n_fixed_groups, void* ydx,
                      int32_t* status, void* stream);
 
-/* Scratch sizes for moe_b200_wgrad: partial_bytes of fp32 partial tiles (contents arbitrary) and
- * counter_bytes of int32 counters (must be ZERO before the first call; every call leaves them
- * zero again). routed != 0: the pad_offsets schedule over `rows` = l_cap rows. */
-int moe_b200_wgrad_scratch(int32_t m_dim, int32_t n_dim, int64_t rows, int32_t n_groups,
-                           int32_t routed, int32_t ks_rows, size_t* partial_bytes,
-                           size_t* counter_bytes);
+/* Bytes of fp32 scratch moe_b200_wgrad needs for its partial tiles (contents arbitrary).
+ * routed != 0: the pad_offsets schedule over `rows` = l_cap rows. ks_rows as for moe_b200_wgrad. */
+int moe_b200_wgrad_scratch_bytes(int32_t m_dim, int32_t n_dim, int64_t rows, int32_t n_groups,
+                                 int32_t routed, int32_t ks_rows, size_t* partial_bytes);
 
 /* Per-expert weight gradient dw[e] = a_e^T @ b_e over the rows of run e
  * (a [rows, m_dim], b [rows, n_dim], dw [n_groups, m_dim, n_dim]); empty runs give zeros.
  * Routed schedule: pad_offsets [n_groups+1] from the dispatch. Fixed schedule: pad_offsets NULL,
  * every group spans rows [0, rows); a_grouped / b_grouped say whether that operand is stacked
  * [n_groups, rows, .] or shared by all groups. The contraction is split into chunks of ks_rows rows
- * (a multiple of 64) so long runs spread over many SMs; partial tiles are summed in chunk order, so
- * the result is deterministic. Replaces _dw_kernel (src/model/moe_kernel.py:453-507, 712-721),
- * which has no split-K. */
+ * (a multiple of 64; 0 = let the library choose) so long runs spread over many SMs; a run's partial
+ * tiles are added in chunk order by a second small kernel, so the result is deterministic.
+ * Replaces _dw_kernel (src/model/moe_kernel.py:453-507, 712-721), which has no split-K. */
 int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* b,
                    int32_t b_grouped, int32_t n_dim, int64_t rows, const int32_t* pad_offsets,
                    int32_t n_groups, int32_t ks_rows, void* dw, void* partials,
-                   size_t partial_bytes, void* counters, size_t counter_bytes, int32_t* status,
-                   void* stream);
+                   size_t partial_bytes, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -288,38 +288,51 @@ static int64_t wgrad_items(int64_t rows, int n_groups, int routed, int ks_rows) 
   return routed ? rows / ks_rows + n_groups : int64_t(n_groups) * wgrad_chunks(int(rows), ks_rows);
 }
 
-int moe_b200_wgrad_scratch(int32_t m_dim, int32_t n_dim, int64_t rows, int32_t n_groups,
-                           int32_t routed, int32_t ks_rows, size_t* partial_bytes,
-                           size_t* counter_bytes) {
-  if (m_dim < 1 || n_dim < 1 || rows < 0 || n_groups < 1 || ks_rows < 64 || ks_rows % 64 != 0 ||
-      !partial_bytes || !counter_bytes)
+// Rows per split-K chunk when the caller leaves the choice to the library: expert runs are cut at
+// 2048 rows; on the fixed schedule (few groups, every row) the chunks are sized so that the
+// work items fill the SMs about once.
+static int auto_ks_rows(int32_t m_dim, int32_t n_dim, int64_t rows, int n_groups, int routed) {
+  if (routed) return 2048;
+  const int bn = n_dim % 256 == 0 ? 256 : 192;
+  const int64_t tiles = int64_t((m_dim + BM - 1) / BM) * ((n_dim + bn - 1) / bn) * n_groups;
+  int64_t splits = sm_count() / (tiles > 0 ? tiles : 1);
+  if (splits < 1) splits = 1;
+  int64_t ks = ((rows + splits - 1) / splits + 63) / 64 * 64;
+  if (ks < 256) ks = 256;
+  return int(ks);
+}
+
+int moe_b200_wgrad_scratch_bytes(int32_t m_dim, int32_t n_dim, int64_t rows, int32_t n_groups,
+                                 int32_t routed, int32_t ks_rows, size_t* partial_bytes) {
+  if (m_dim < 1 || n_dim < 1 || rows < 0 || n_groups < 1 || ks_rows < 0 || ks_rows % 64 != 0 ||
+      !partial_bytes)
     return MOE_B200_ERR_SHAPE;
+  if (ks_rows == 0) ks_rows = auto_ks_rows(m_dim, n_dim, rows, n_groups, routed);
   const int bn = n_dim % 256 == 0 ? 256 : 192;
   const int64_t tiles_xy = int64_t((m_dim + BM - 1) / BM) * ((n_dim + bn - 1) / bn);
   *partial_bytes = size_t(wgrad_items(rows, n_groups, routed, ks_rows)) * size_t(tiles_xy) * BM *
                    bn * sizeof(float);
-  *counter_bytes = size_t(n_groups) * size_t(tiles_xy) * sizeof(int32_t);
   return MOE_B200_OK;
 }
 
 int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* b,
                    int32_t b_grouped, int32_t n_dim, int64_t rows, const int32_t* pad_offsets,
                    int32_t n_groups, int32_t ks_rows, void* dw, void* partials,
-                   size_t partial_bytes, void* counters, size_t counter_bytes, int32_t* status,
-                   void* stream) {
+                   size_t partial_bytes, int32_t* status, void* stream) {
   if (rows < 0 || rows > (int64_t(1) << 30) || n_groups < 1 || m_dim < 1 || n_dim < 1)
     return MOE_B200_ERR_SHAPE;
-  if (ks_rows < 64 || ks_rows % 64 != 0) return MOE_B200_ERR_SHAPE;
+  if (ks_rows < 0 || ks_rows % 64 != 0) return MOE_B200_ERR_SHAPE;
   if (m_dim % 8 != 0 || n_dim % 32 != 0) return MOE_B200_ERR_UNSUPPORTED;
   if (pad_offsets && (a_grouped || b_grouped)) return MOE_B200_ERR_SHAPE;
   if (pad_offsets && rows % 128 != 0) return MOE_B200_ERR_SHAPE;
-  if (!a || !b || !dw || !status || !partials || !counters) return MOE_B200_ERR_NULL;
+  if (!a || !b || !dw || !status || !partials) return MOE_B200_ERR_NULL;
   if (!aligned16(a) || !aligned16(b) || !aligned16(dw) || !aligned16(partials))
     return MOE_B200_ERR_ALIGN;
-  size_t need_p = 0, need_c = 0;
   const int routed = pad_offsets != nullptr;
-  moe_b200_wgrad_scratch(m_dim, n_dim, rows, n_groups, routed, ks_rows, &need_p, &need_c);
-  if (partial_bytes < need_p || counter_bytes < need_c) return MOE_B200_ERR_SCRATCH;
+  if (ks_rows == 0) ks_rows = auto_ks_rows(m_dim, n_dim, rows, n_groups, routed);
+  size_t need_p = 0;
+  moe_b200_wgrad_scratch_bytes(m_dim, n_dim, rows, n_groups, routed, ks_rows, &need_p);
+  if (partial_bytes < need_p) return MOE_B200_ERR_SCRATCH;
   CUtensorMap tmA, tmB;
   // rows == 0 still launches: every C[e] must be written (with zeros)
   const int64_t map_rows = rows > 0 ? rows : 1;
@@ -337,16 +350,28 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   g.n_dim = n_dim;
   g.out = static_cast<__nv_bfloat16*>(dw);
   g.partials = static_cast<float*>(partials);
-  g.counters = static_cast<int32_t*>(counters);
   g.status = status;
   const unsigned items = unsigned(wgrad_items(rows, n_groups, routed, ks_rows));
+  // the second pass can be skipped when no run can have more than one chunk
+  const bool may_split = rows > ks_rows;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned tx = unsigned((m_dim + BM - 1) / BM);
+  int rc;
   if (n_dim % 256 == 0) {
-    const dim3 grid(unsigned((m_dim + BM - 1) / BM), unsigned(n_dim / 256), items);
-    return launch_wgrad<256, 4>(tmA, tmB, g, grid, st);
+    const unsigned ty = unsigned(n_dim / 256);
+    rc = launch_wgrad<256, 4>(tmA, tmB, g, dim3(tx, ty, items), st);
+    if (rc == MOE_B200_OK && may_split)
+      wgrad_reduce_kernel<256><<<dim3(tx * ty * WGRAD_REDUCE_SPLIT, unsigned(n_groups)), 256, 0,
+                                 st>>>(g, int(tx), int(ty));
+  } else {
+    const unsigned ty = unsigned((n_dim + 191) / 192);
+    rc = launch_wgrad<192, 5>(tmA, tmB, g, dim3(tx, ty, items), st);
+    if (rc == MOE_B200_OK && may_split)
+      wgrad_reduce_kernel<192><<<dim3(tx * ty * WGRAD_REDUCE_SPLIT, unsigned(n_groups)), 256, 0,
+                                 st>>>(g, int(tx), int(ty));
   }
-  const dim3 grid(unsigned((m_dim + BM - 1) / BM), unsigned((n_dim + 191) / 192), items);
-  return launch_wgrad<192, 5>(tmA, tmB, g, grid, st);
+  if (rc != MOE_B200_OK) return rc;
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
 }  // extern "C"

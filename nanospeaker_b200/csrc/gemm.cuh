@@ -9,8 +9,8 @@
 //                     epilogue of tile i overlaps the loads and MMAs of tile i+1. Covers up/gate,
 //                     down, dHidden (+GLU backward) and dX, for routed and shared experts.
 // wgrad_gemm_kernel : per-expert weight gradient C[e] = A_e^T @ B_e; the contraction runs over the
-//                     rows of the expert's run, split into chunks of ks_rows; the CTA that finishes
-//                     a tile's last chunk sums the fp32 partials in chunk order (deterministic).
+//                     rows of the expert's run, split into chunks of ks_rows; a second small kernel
+//                     sums the fp32 partials of split runs in chunk order (deterministic).
 //
 // Warp roles (both kernels): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
 // warps 2.. = epilogue (one accumulator row per thread; a warp may only read the TMEM lane
@@ -70,8 +70,7 @@ struct WgradArgs {
   int32_t a_grouped, b_grouped;  // fixed schedule: operand has a leading group dim
   int32_t m_dim, n_dim;        // rows / cols of one C[e]
   __nv_bfloat16* out;          // [G, m_dim, n_dim]
-  float* partials;             // fp32 scratch for split tiles
-  int32_t* counters;           // one per (group, m tile, n chunk); zero on entry, left zero
+  float* partials;             // fp32 scratch for the partial tiles of split runs
   int32_t* status;
 };
 

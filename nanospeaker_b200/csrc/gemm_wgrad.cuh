@@ -3,10 +3,10 @@
 // boxes), the contraction index is the row. 192 threads: warp 0 TMA, warp 1 MMA, warps 2..5 epilogue.
 //
 // Work item = (m tile, n chunk, split-K chunk). A run longer than ks_rows is cut into chunks; each
-// chunk's CTA writes an fp32 partial tile, and the CTA that arrives last at the tile's counter adds
-// the partials in chunk order and writes bf16 -- the result does not depend on which CTA is last.
-// Runs that fit one chunk (the common case) store bf16 directly. An empty run still owns one
-// work item, which writes zeros.
+// chunk's CTA writes an fp32 partial tile and wgrad_reduce_kernel then adds a tile's partials in
+// chunk order and writes bf16 (deterministic, and the reduction is spread over many CTAs). Runs
+// that fit one chunk (the common case for routed experts) store bf16 directly and skip the second
+// pass. An empty run still owns one work item, which writes zeros.
 #pragma once
 
 namespace moe {
@@ -29,6 +29,88 @@ __host__ __device__ __forceinline__ int wgrad_chunks(int rows, int ks_rows) {
   return c > 0 ? c : 1;
 }
 
+
+// Warp-cooperative lookup of work item j: which run, which chunk of it. Writes
+// sched = {group (-1 if j is past the last item), chunk, chunks of the group, first row, rows}.
+__device__ __forceinline__ void wgrad_find_item(const WgradArgs& p, int j, int lane, int* sched) {
+  int group = -1, chunk = 0, n_c = 0, row0 = 0, rows = 0;
+  if (p.pad_offsets == nullptr) {
+    n_c = wgrad_chunks(p.rows_host, p.ks_rows);
+    if (j < n_c * p.n_groups) {
+      group = j / n_c;
+      chunk = j - group * n_c;
+      row0 = chunk * p.ks_rows;
+      rows = min(p.ks_rows, p.rows_host - row0);
+    }
+  } else {
+    int running = 0;
+    for (int base = 0; base < p.n_groups && group < 0; base += 32) {
+      const int g = base + lane;
+      int lo = 0, hi = 0;
+      if (g < p.n_groups) {
+        lo = __ldg(p.pad_offsets + g);
+        hi = __ldg(p.pad_offsets + g + 1);
+      }
+      const int mine = g < p.n_groups ? wgrad_chunks(hi - lo, p.ks_rows) : 0;
+      int incl = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      const int excl = incl - mine;
+      const bool owner = mine > 0 && j >= running + excl && j < running + incl;
+      const unsigned who = __ballot_sync(0xffffffffu, owner);
+      if (who) {
+        const int src = __ffs(who) - 1;
+        const int c = j - running - excl;
+        group = __shfl_sync(0xffffffffu, g, src);
+        chunk = __shfl_sync(0xffffffffu, c, src);
+        n_c = __shfl_sync(0xffffffffu, mine, src);
+        const int r0 = lo + c * p.ks_rows;
+        row0 = __shfl_sync(0xffffffffu, r0, src);
+        rows = __shfl_sync(0xffffffffu, max(0, min(p.ks_rows, hi - r0)), src);
+      }
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
+  if (lane == 0) {
+    sched[0] = group; sched[1] = chunk; sched[2] = n_c; sched[3] = row0; sched[4] = rows;
+  }
+}
+
+// First work-item index and chunk count of run `g` (warp-cooperative; result in out[0..1]).
+__device__ __forceinline__ void wgrad_find_group(const WgradArgs& p, int g, int lane, int* out) {
+  int first = 0, n_c = 0;
+  if (p.pad_offsets == nullptr) {
+    n_c = wgrad_chunks(p.rows_host, p.ks_rows);
+    first = g * n_c;
+  } else {
+    int running = 0;
+    for (int base = 0; base <= g; base += 32) {
+      const int gg = base + lane;
+      int mine = 0;
+      if (gg < p.n_groups)
+        mine = wgrad_chunks(__ldg(p.pad_offsets + gg + 1) - __ldg(p.pad_offsets + gg), p.ks_rows);
+      int incl = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      if (g >= base && g < base + 32) {
+        first = running + __shfl_sync(0xffffffffu, incl - mine, g - base);
+        n_c = __shfl_sync(0xffffffffu, mine, g - base);
+      }
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
+  if (lane == 0) {
+    out[0] = first;
+    out[1] = n_c;
+  }
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(WGRAD_THREADS)
     wgrad_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -41,57 +123,11 @@ __global__ void __launch_bounds__(WGRAD_THREADS)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int j = blockIdx.z;  // global work-item index along split-K
-
-  // ---------------------------------------------------------------- which run, which chunk
-  if (warp == 0) {
-    int group = -1, chunk = 0, n_c = 0, row0 = 0, rows = 0;
-    if (p.pad_offsets == nullptr) {
-      n_c = wgrad_chunks(p.rows_host, p.ks_rows);
-      if (j < n_c * p.n_groups) {
-        group = j / n_c;
-        chunk = j - group * n_c;
-        row0 = chunk * p.ks_rows;
-        rows = min(p.ks_rows, p.rows_host - row0);
-      }
-    } else {
-      int running = 0;
-      for (int base = 0; base < p.n_groups && group < 0; base += 32) {
-        const int g = base + lane;
-        int lo = 0, hi = 0;
-        if (g < p.n_groups) {
-          lo = __ldg(p.pad_offsets + g);
-          hi = __ldg(p.pad_offsets + g + 1);
-        }
-        const int mine = g < p.n_groups ? wgrad_chunks(hi - lo, p.ks_rows) : 0;
-        int incl = mine;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const int v = __shfl_up_sync(0xffffffffu, incl, o);
-          if (lane >= o) incl += v;
-        }
-        const int excl = incl - mine;
-        const bool owner = mine > 0 && j >= running + excl && j < running + incl;
-        const unsigned who = __ballot_sync(0xffffffffu, owner);
-        if (who) {
-          const int src = __ffs(who) - 1;
-          const int c = j - running - excl;
-          group = __shfl_sync(0xffffffffu, g, src);
-          chunk = __shfl_sync(0xffffffffu, c, src);
-          n_c = __shfl_sync(0xffffffffu, mine, src);
-          const int r0 = lo + c * p.ks_rows;
-          row0 = __shfl_sync(0xffffffffu, r0, src);
-          rows = __shfl_sync(0xffffffffu, max(0, min(p.ks_rows, hi - r0)), src);
-        }
-        running += __shfl_sync(0xffffffffu, incl, 31);
-      }
-    }
-    if (lane == 0) {
-      sched[0] = group; sched[1] = chunk; sched[2] = n_c; sched[3] = row0; sched[4] = rows;
-    }
-  }
+  if (warp == 0) wgrad_find_item(p, j, lane, sched);
   __syncthreads();
   const int group = sched[0], chunk = sched[1], n_c = sched[2], row0 = sched[3];
   if (group < 0) return;  // past the last work item (uniform over the CTA, nothing set up yet)
+  (void)chunk;
   const int num_k = (sched[4] + BK - 1) / BK;
 
   const int tile_m = blockIdx.x;
@@ -105,7 +141,6 @@ __global__ void __launch_bounds__(WGRAD_THREADS)
   uint64_t* accum_bar = empty_bar + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::MISC_OFFSET);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA);
@@ -116,7 +151,6 @@ __global__ void __launch_bounds__(WGRAD_THREADS)
     }
     mbar_init(accum_bar, 1);
     *abort_flag = 0;
-    *last_flag = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -214,47 +248,55 @@ __global__ void __launch_bounds__(WGRAD_THREADS)
         for (int i = 0; i < 8; ++i)
           d4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
       }
-      __threadfence();
-      epi_bar_sync(128);
-      if (warp == 2 && lane == 0) {
-        int32_t* ctr = p.counters + (int64_t(group) * tiles_xy + tile_xy);
-        const int old = atomicAdd(ctr, 1);
-        if (old == n_c - 1) {
-          atomicExch(ctr, 0);  // leave the counter ready for the next launch
-          *last_flag = 1;
-        }
-      }
-      epi_bar_sync(128);
-      if (*last_flag) {
-        __threadfence();
-        const int64_t first = int64_t(j - chunk);
-#pragma unroll 1
-        for (int c = 0; c < NCH; ++c) {
-          float acc[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-          for (int c2 = 0; c2 < n_c; ++c2) {
-            const float4* s4 = reinterpret_cast<const float4*>(
-                p.partials + ((first + c2) * tiles_xy + tile_xy) * slot_elems +
-                (int64_t(c) * BM + row) * 32);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float4 f = __ldcg(s4 + i);
-              acc[4 * i] += f.x;
-              acc[4 * i + 1] += f.y;
-              acc[4 * i + 2] += f.z;
-              acc[4 * i + 3] += f.w;
-            }
-          }
-          if (m_ok && n0 + c * 32 < p.n_dim) store_bf16x32(dst + c * 32, acc);
-        }
-      }
     }
   }
 
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+
+constexpr int WGRAD_REDUCE_SPLIT = 16;  // CTAs sharing the reduction of one output tile
+
+// Second pass of the split-K weight gradient: for every (run, tile) that was split, add the fp32
+// partial tiles in chunk order and write bf16. grid = (tiles_x * tiles_y * WGRAD_REDUCE_SPLIT,
+// n_groups); tiles_x / tiles_y / BN must be those of the first pass.
+template <int BN>
+__global__ void __launch_bounds__(256)
+    wgrad_reduce_kernel(const WgradArgs p, int tiles_x, int tiles_y) {
+  __shared__ int info[2];
+  const int g = blockIdx.y;
+  if (threadIdx.x < 32) wgrad_find_group(p, g, threadIdx.x, info);
+  __syncthreads();
+  const int first = info[0], n_c = info[1];
+  if (n_c <= 1) return;
+  const int tile_xy = blockIdx.x / WGRAD_REDUCE_SPLIT;
+  const int slice = blockIdx.x % WGRAD_REDUCE_SPLIT;
+  const int tile_m = tile_xy / tiles_y, n0 = (tile_xy % tiles_y) * BN;
+  const int64_t tiles_xy = int64_t(tiles_x) * tiles_y;
+  constexpr int64_t slot_elems = int64_t(BM) * BN;
+  constexpr int vecs = BM * BN / 4;                  // float4 per tile
+  constexpr int per_slice = vecs / WGRAD_REDUCE_SPLIT;
+  for (int f = slice * per_slice + threadIdx.x; f < (slice + 1) * per_slice; f += blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c2 = 0; c2 < n_c; ++c2) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(
+                                  p.partials + ((int64_t(first) + c2) * tiles_xy + tile_xy) * slot_elems) + f);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    // partial layout [column chunk][row][32 floats]
+    const int cc = f / (BM * 8), row = (f / 8) % BM, i4 = f % 8;
+    const int m = tile_m * BM + row, n = n0 + cc * 32 + i4 * 4;
+    if (m < p.m_dim && n < p.n_dim) {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
+      const __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
+      uint2 w;
+      w.x = *reinterpret_cast<const uint32_t*>(&lo);
+      w.y = *reinterpret_cast<const uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(p.out + (int64_t(g) * p.m_dim + m) * int64_t(p.n_dim) + n) = w;
+    }
+  }
 }
 
 }  // namespace moe

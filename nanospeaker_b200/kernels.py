@@ -220,47 +220,27 @@ def dx_gemm(da1, w_in, expert_ids, n_post_pad, n_fixed: int) -> torch.Tensor:
     return ydx
 
 
-WGRAD_KS_ROUTED = 2048   # rows per split-K chunk: expert runs
-WGRAD_KS_SHARED = 1024   # rows per split-K chunk: shared experts (every token, few groups)
-
-_wgrad_counters = {}
-
-
-def _counters(device, nbytes: int) -> torch.Tensor:
-    """Persistent zeroed int32 counters for the split-K reduction (each launch leaves them zero)."""
-    dev = torch.device(device)
-    key = (dev.index if dev.index is not None else torch.cuda.current_device(), nbytes)
-    c = _wgrad_counters.get(key)
-    if c is None:
-        c = torch.zeros(max(nbytes // 4, 1), dtype=torch.int32, device=dev)
-        _wgrad_counters[key] = c
-    return c
-
-
-def wgrad(a, b, pad_offsets, n_groups: int, ks_rows: Optional[int] = None,
-          a_grouped: bool = False, b_grouped: bool = False) -> torch.Tensor:
+def wgrad(a, b, pad_offsets, n_groups: int, ks_rows: int = 0, a_grouped: bool = False,
+          b_grouped: bool = False) -> torch.Tensor:
     """dw[e] = a_e^T @ b_e over run e's rows -> [G, Mdim, Ndim]. Routed schedule: a [rows, Mdim],
     b [rows, Ndim] in slot order plus pad_offsets. Fixed schedule (pad_offsets None): every group
-    spans all rows; a / b are [G, rows, .] when *_grouped, else shared by the groups."""
+    spans all rows; a / b are [G, rows, .] when *_grouped, else shared by the groups.
+    ks_rows = rows per split-K chunk (0: chosen by the library)."""
     _need_cuda(a, b)
     import ctypes
     rows, m_dim = a.shape[-2:]
     n_dim = b.shape[-1]
     routed = pad_offsets is not None
-    if ks_rows is None:
-        ks_rows = WGRAD_KS_ROUTED if routed else WGRAD_KS_SHARED
     lib = _lib.load()
-    pb, cb = ctypes.c_size_t(0), ctypes.c_size_t(0)
-    _lib.check(lib.moe_b200_wgrad_scratch(m_dim, n_dim, rows, n_groups, int(routed), ks_rows,
-                                          ctypes.byref(pb), ctypes.byref(cb)),
-               "moe_b200_wgrad_scratch")
+    pb = ctypes.c_size_t(0)
+    _lib.check(lib.moe_b200_wgrad_scratch_bytes(m_dim, n_dim, rows, n_groups, int(routed),
+                                                ks_rows, ctypes.byref(pb)),
+               "moe_b200_wgrad_scratch_bytes")
     partials = torch.empty(max(pb.value, 16), dtype=torch.uint8, device=a.device)
-    counters = _counters(a.device, cb.value)
     dw = torch.empty((n_groups, m_dim, n_dim), dtype=a.dtype, device=a.device)
     _lib.check(lib.moe_b200_wgrad(
         a.data_ptr(), int(a_grouped), m_dim, b.data_ptr(), int(b_grouped), n_dim, rows,
         _lib.ptr(pad_offsets), n_groups, ks_rows, dw.data_ptr(), partials.data_ptr(), pb.value,
-        counters.data_ptr(), cb.value, status_word(a.device).data_ptr(), _stream(a)),
-        "moe_b200_wgrad")
-    _count(1)
+        status_word(a.device).data_ptr(), _stream(a)), "moe_b200_wgrad")
+    _count(2 if rows > (ks_rows or 256) else 1)
     return dw

@@ -76,13 +76,12 @@ def test_arguments_are_validated_before_any_launch(lib):
     assert lib.moe_b200_up_gemm(p, 128, 64, p, 4, 64, p, p, 1, 0, p, null, p, null) == -5   # H
     assert lib.moe_b200_up_gemm(p, 100, 64, p, 4, 128, p, p, 0, 0, p, null, p, null) == -1  # rows
     assert lib.moe_b200_up_gemm(p, 128, 64, p, 4, 128, p, p, 5, 0, p, null, p, null) == -1  # S > G
-    assert lib.moe_b200_wgrad(p, 0, 64, p, 0, 100, 128, p, 4, 2048, p, p, 0, p, 0, p, null) == -5
-    assert lib.moe_b200_wgrad(p, 0, 64, p, 0, 256, 128, p, 4, 100, p, p, 0, p, 0, p, null) == -1
-    assert lib.moe_b200_wgrad(p, 0, 64, p, 0, 256, 128, p, 4, 2048, p, p, 0, p, 0, p, null) == -4
-    pb, cb = ctypes.c_size_t(0), ctypes.c_size_t(0)
-    assert lib.moe_b200_wgrad_scratch(576, 256, 108032, 76, 1, 2048, ctypes.byref(pb),
-                                      ctypes.byref(cb)) == 0
-    assert pb.value == (108032 // 2048 + 76) * 5 * 128 * 256 * 4 and cb.value == 76 * 5 * 4
+    assert lib.moe_b200_wgrad(p, 0, 64, p, 0, 100, 128, p, 4, 2048, p, p, 0, p, null) == -5
+    assert lib.moe_b200_wgrad(p, 0, 64, p, 0, 256, 128, p, 4, 100, p, p, 0, p, null) == -1
+    assert lib.moe_b200_wgrad(p, 0, 64, p, 0, 256, 128, p, 4, 2048, p, p, 0, p, null) == -4
+    pb = ctypes.c_size_t(0)
+    assert lib.moe_b200_wgrad_scratch_bytes(576, 256, 108032, 76, 1, 2048, ctypes.byref(pb)) == 0
+    assert pb.value == (108032 // 2048 + 76) * 5 * 128 * 256 * 4
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
