@@ -366,6 +366,11 @@ def run_ours(args):
                 else:
                     torch.autograd.backward([out, m.aux_loss], [static_dout, one])
         torch.cuda.current_stream().wait_stream(side)
+        # Drop every reference to earlier autograd graphs (the block keeps its last aux_loss):
+        # their AccumulateGrad nodes are tied to the stream they ran on and would pull that
+        # stream into the capture.
+        del out
+        m.aux_loss = torch.zeros((), device=dev)
         for p in params:
             p.grad = None
         static_x.grad = None
