@@ -33,7 +33,7 @@ extern "C" {
 #define MOE_B200_OK 0
 #define MOE_B200_ERR_SHAPE (-1)       /* a size is negative, zero where it may not be, or inconsistent */
 #define MOE_B200_ERR_NULL (-2)        /* a required pointer is NULL */
-#define MOE_B200_ERR_ALIGN (-3)       /* a pointer or row stride is not 16-byte aligned */
+#define MOE_B200_ERR_ALIGN (-3)       /* a pointer or row stride is not aligned (16 bytes for inputs, 32 for GEMM operands and outputs) */
 #define MOE_B200_ERR_SCRATCH (-4)     /* scratch buffer missing or too small */
 #define MOE_B200_ERR_UNSUPPORTED (-5) /* shape / activation the kernels do not cover */
 #define MOE_B200_ERR_TMA (-6)         /* the driver refused a tensor map */

@@ -10,7 +10,7 @@ const char* moe_b200_error_string(int32_t code) {
     case MOE_B200_OK: return "ok";
     case MOE_B200_ERR_SHAPE: return "bad shape: a size is negative, zero or inconsistent";
     case MOE_B200_ERR_NULL: return "a required pointer is NULL";
-    case MOE_B200_ERR_ALIGN: return "a pointer or row stride is not 16-byte aligned";
+    case MOE_B200_ERR_ALIGN: return "a pointer or row stride is not aligned (16 bytes for inputs, 32 for GEMM operands and outputs)";
     case MOE_B200_ERR_SCRATCH: return "scratch buffer missing or too small";
     case MOE_B200_ERR_UNSUPPORTED: return "shape or activation not covered by the sm_100a kernels";
     case MOE_B200_ERR_TMA: return "cuTensorMapEncodeTiled refused a tensor map";

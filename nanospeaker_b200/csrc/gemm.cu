@@ -130,7 +130,8 @@ static int launch_wgrad(const CUtensorMap& tmA, const CUtensorMap& tmB, const Wg
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
-static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+// inputs feed TMA (16 bytes); outputs are written with 32-byte vectors
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 
 static RowsArgs base_args(const int32_t* expert_ids, const int32_t* n_post_pad,
                           int32_t n_fixed_groups, int64_t rows, int32_t* status) {

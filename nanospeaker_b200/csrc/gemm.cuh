@@ -105,34 +105,52 @@ __device__ __forceinline__ void act_fd(float g, float& a, float& d) {
   }
 }
 
-// 32 fp32 -> 32 bf16, stored as four 16-byte vectors (dst 16-byte aligned).
+// 256-bit global accesses (sm_100): one full 32-byte sector per thread and instruction, so a
+// thread that owns 64 contiguous bytes of a row touches each sector exactly once.
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t* w) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(w[0]), "r"(w[1]),
+               "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+__device__ __forceinline__ void ld_global_nc_v8(const void* p, uint32_t* w) {
+  asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]),
+                 "=r"(w[7])
+               : "l"(p));
+}
+
+// 32 fp32 -> 32 bf16 = 64 bytes, stored as two 32-byte vectors (dst 32-byte aligned).
 __device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float* v) {
-  uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    uint32_t w[4];
+  for (int q = 0; q < 2; ++q) {
+    uint32_t w[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      __nv_bfloat162 h = __floats2bfloat162_rn(v[q * 8 + 2 * i], v[q * 8 + 2 * i + 1]);
+    for (int i = 0; i < 8; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[q * 16 + 2 * i], v[q * 16 + 2 * i + 1]);
       w[i] = *reinterpret_cast<uint32_t*>(&h);
     }
-    d4[q] = make_uint4(w[0], w[1], w[2], w[3]);
+    st_global_v8(dst + q * 16, w);
   }
 }
 __device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, float* v) {
-  const uint4* s4 = reinterpret_cast<const uint4*>(src);
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    uint4 r = __ldg(s4 + q);
-    uint32_t w[4] = {r.x, r.y, r.z, r.w};
+  for (int q = 0; q < 2; ++q) {
+    uint32_t w[8];
+    ld_global_nc_v8(src + q * 16, w);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 8; ++i) {
       __nv_bfloat162 h = *reinterpret_cast<__nv_bfloat162*>(&w[i]);
       float2 f = __bfloat1622float2(h);
-      v[q * 8 + 2 * i] = f.x;
-      v[q * 8 + 2 * i + 1] = f.y;
+      v[q * 16 + 2 * i] = f.x;
+      v[q * 16 + 2 * i + 1] = f.y;
     }
   }
+}
+// 32 fp32 stored as four 32-byte vectors (dst 32-byte aligned).
+__device__ __forceinline__ void store_f32x32(float* dst, const float* v) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    st_global_v8(dst + q * 8, reinterpret_cast<const uint32_t*>(v) + q * 8);
 }
 
 __device__ __forceinline__ void epi_bar_sync(int nthreads) {

@@ -243,10 +243,7 @@ __global__ void __launch_bounds__(WGRAD_THREADS)
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0.f;
         }
-        float4* d4 = reinterpret_cast<float4*>(mine + (int64_t(c) * BM + row) * 32);
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          d4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        store_f32x32(mine + (int64_t(c) * BM + row) * 32, v);
       }
     }
   }

@@ -19,7 +19,6 @@ namespace moe {
 
 constexpr int ALIGN_M = 128;
 constexpr int MAX_EXPERTS = 256;            // router + dispatch kernels keep per-expert state on chip
-constexpr int ROUTER_VPL = MAX_EXPERTS / 32;  // logits held per lane
 constexpr int MAX_TOPK = 16;
 
 // ----------------------------------------------------------------------------- router top-k
@@ -32,12 +31,14 @@ __device__ __forceinline__ uint32_t float_key(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-// One warp per token. Selection key = (value desc, expert index asc): unique per expert, so a
-// 64-bit max-reduction over the warp finds each winner and the output is sorted the same way.
+// One warp per token; lane l holds experts l, l+32, ... (NSLOT of them). A winner is found with two
+// hardware warp reductions: the largest key, then the smallest expert index among the lanes that
+// hold it -- i.e. descending value, ties to the lowest index, and the output comes out sorted.
 // full_softmax != 0 : weights come from the softmax over all experts (renormalised over the k
 //                     winners when normalize != 0 and k > 1), and probs [T,E] is written if given.
 // full_softmax == 0 : normalize != 0 -> softmax over the k winning logits;
 //                     normalize == 0 -> the full-softmax probabilities of the winners.
+template <int NSLOT>
 __global__ void __launch_bounds__(256)
     router_topk_kernel(const float* __restrict__ logits, int64_t n_tokens, int n_experts, int top_k,
                        int normalize, int full_softmax, float* __restrict__ topk_w,
@@ -47,12 +48,17 @@ __global__ void __launch_bounds__(256)
   if (t >= n_tokens) return;
   const float* row = logits + t * n_experts;
 
-  float v[ROUTER_VPL];
+  float v[NSLOT];
+  uint32_t key[NSLOT];  // 0 = not a candidate (out of range or already taken)
   float mx = -CUDART_INF_F;
 #pragma unroll
-  for (int i = 0; i < ROUTER_VPL; ++i) {
+  for (int i = 0; i < NSLOT; ++i) {
     const int e = i * 32 + lane;
-    v[i] = e < n_experts ? row[e] : -CUDART_INF_F;
+    const bool in = e < n_experts;
+    v[i] = in ? row[e] : -CUDART_INF_F;
+    // float_key is never 0 for a real value except -NaN patterns; +1 saturating keeps 0 free
+    const uint32_t fk = float_key(v[i]);
+    key[i] = in ? (fk == 0u ? 1u : fk) : 0u;
     mx = fmaxf(mx, v[i]);
   }
 #pragma unroll
@@ -62,47 +68,40 @@ __global__ void __launch_bounds__(256)
   float denom = 0.f;
   if (need_full) {
 #pragma unroll
-    for (int i = 0; i < ROUTER_VPL; ++i)
+    for (int i = 0; i < NSLOT; ++i)
       if (i * 32 + lane < n_experts) denom += expf(v[i] - mx);
 #pragma unroll
     for (int o = 16; o; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
     if (probs != nullptr) {
 #pragma unroll
-      for (int i = 0; i < ROUTER_VPL; ++i) {
+      for (int i = 0; i < NSLOT; ++i) {
         const int e = i * 32 + lane;
         if (e < n_experts) probs[t * n_experts + e] = expf(v[i] - mx) / denom;
       }
     }
   }
 
-  uint32_t taken = 0;  // bit i: this lane's i-th logit already selected
-  float sel_val = 0.f; // lane j < top_k keeps the j-th winner
+  float sel_val = 0.f;  // lane j < top_k keeps the j-th winner
   int sel_idx = 0;
   for (int j = 0; j < top_k; ++j) {
-    unsigned long long best = 0ull;
+    uint32_t best = 0u;
 #pragma unroll
-    for (int i = 0; i < ROUTER_VPL; ++i) {
-      const int e = i * 32 + lane;
-      if (e < n_experts && !((taken >> i) & 1u)) {
-        const unsigned long long key =
-            (static_cast<unsigned long long>(float_key(v[i])) << 32) | (0xFFFFFFFFu - uint32_t(e));
-        // a real candidate is never 0 (its low word is at least 0xFFFFFFFF - 255)
-        best = key > best ? key : best;
-      }
-    }
+    for (int i = 0; i < NSLOT; ++i) best = key[i] > best ? key[i] : best;
+    const uint32_t top = __reduce_max_sync(0xffffffffu, best);
+    uint32_t cand = 0xFFFFFFFFu;  // lowest expert index in this lane that holds the top key
 #pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
-      best = other > best ? other : best;
-    }
-    const int e_win = int(0xFFFFFFFFu - uint32_t(best & 0xFFFFFFFFull));
+    for (int i = NSLOT - 1; i >= 0; --i)
+      if (key[i] == top) cand = uint32_t(i * 32 + lane);
+    const int e_win = int(__reduce_min_sync(0xffffffffu, cand));
     const int owner = e_win & 31, slot = e_win >> 5;
     float val = 0.f;
 #pragma unroll
-    for (int i = 0; i < ROUTER_VPL; ++i)
-      if (i == slot) val = v[i];
+    for (int i = 0; i < NSLOT; ++i)
+      if (i == slot) {
+        val = v[i];
+        if (lane == owner) key[i] = 0u;
+      }
     val = __shfl_sync(0xffffffffu, val, owner);
-    if (lane == owner) taken |= 1u << slot;
     if (lane == j) {
       sel_val = val;
       sel_idx = e_win;
@@ -141,6 +140,7 @@ __global__ void __launch_bounds__(256)
 //   full_softmax, else           : dp_i = dw_i on S (+ d_probs), same softmax Jacobian
 //   !full_softmax, normalize     : dl_i = w_i (dw_i - sum_j w_j dw_j) on S, 0 elsewhere
 //   !full_softmax, !normalize    : dp_i = dw_i on S, softmax Jacobian
+template <int NSLOT>
 __global__ void __launch_bounds__(256)
     router_topk_bwd_kernel(const float* __restrict__ logits, const int64_t* __restrict__ topk_idx,
                            const float* __restrict__ d_topk_w, const float* __restrict__ d_probs,
@@ -151,10 +151,10 @@ __global__ void __launch_bounds__(256)
   if (t >= n_tokens) return;
   const float* row = logits + t * n_experts;
 
-  float v[ROUTER_VPL], pr[ROUTER_VPL], dp[ROUTER_VPL];
+  float v[NSLOT], pr[NSLOT], dp[NSLOT];
   float mx = -CUDART_INF_F;
 #pragma unroll
-  for (int i = 0; i < ROUTER_VPL; ++i) {
+  for (int i = 0; i < NSLOT; ++i) {
     const int e = i * 32 + lane;
     v[i] = e < n_experts ? row[e] : -CUDART_INF_F;
     mx = fmaxf(mx, v[i]);
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(256)
     for (int o = 16; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
     // zero the row, then scatter the k entries
 #pragma unroll
-    for (int i = 0; i < ROUTER_VPL; ++i) {
+    for (int i = 0; i < NSLOT; ++i) {
       const int e = i * 32 + lane;
       if (e < n_experts) d_logits[t * n_experts + e] = 0.f;
     }
@@ -199,14 +199,14 @@ __global__ void __launch_bounds__(256)
 
   float denom = 0.f;
 #pragma unroll
-  for (int i = 0; i < ROUTER_VPL; ++i) {
+  for (int i = 0; i < NSLOT; ++i) {
     pr[i] = (i * 32 + lane < n_experts) ? expf(v[i] - mx) : 0.f;
     denom += pr[i];
   }
 #pragma unroll
   for (int o = 16; o; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
 #pragma unroll
-  for (int i = 0; i < ROUTER_VPL; ++i) pr[i] /= denom;
+  for (int i = 0; i < NSLOT; ++i) pr[i] /= denom;
 
   // probability of my winner
   float my_p = active ? expf(row[my_idx] - mx) / denom : 0.f;
@@ -227,24 +227,24 @@ __global__ void __launch_bounds__(256)
     const float d = __shfl_sync(0xffffffffu, my_dp, j);
     if ((e & 31) == lane) {
 #pragma unroll
-      for (int i = 0; i < ROUTER_VPL; ++i)
+      for (int i = 0; i < NSLOT; ++i)
         if (i == (e >> 5)) dp[i] += d;
     }
   }
   if (d_probs != nullptr) {
 #pragma unroll
-    for (int i = 0; i < ROUTER_VPL; ++i) {
+    for (int i = 0; i < NSLOT; ++i) {
       const int e = i * 32 + lane;
       if (e < n_experts) dp[i] += d_probs[t * n_experts + e];
     }
   }
   float inner = 0.f;
 #pragma unroll
-  for (int i = 0; i < ROUTER_VPL; ++i) inner += pr[i] * dp[i];
+  for (int i = 0; i < NSLOT; ++i) inner += pr[i] * dp[i];
 #pragma unroll
   for (int o = 16; o; o >>= 1) inner += __shfl_xor_sync(0xffffffffu, inner, o);
 #pragma unroll
-  for (int i = 0; i < ROUTER_VPL; ++i) {
+  for (int i = 0; i < NSLOT; ++i) {
     const int e = i * 32 + lane;
     if (e < n_experts) d_logits[t * n_experts + e] = pr[i] * (dp[i] - inner);
   }
@@ -418,8 +418,17 @@ int moe_b200_router_topk(const float* logits, int64_t n_tokens, int32_t n_expert
   if (!logits || !topk_w || !topk_idx) return MOE_B200_ERR_NULL;
   const int64_t threads = n_tokens * 32;
   const unsigned grid = unsigned((threads + 255) / 256);
-  router_topk_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      logits, n_tokens, n_experts, top_k, normalize, full_softmax, topk_w, topk_idx, probs);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define LAUNCH(NS)                                                                          \
+  router_topk_kernel<NS><<<grid, 256, 0, st>>>(logits, n_tokens, n_experts, top_k, normalize, \
+                                               full_softmax, topk_w, topk_idx, probs)
+  const int nslot = (n_experts + 31) / 32;
+  if (nslot <= 1) LAUNCH(1);
+  else if (nslot <= 2) LAUNCH(2);
+  else if (nslot <= 3) LAUNCH(3);
+  else if (nslot <= 4) LAUNCH(4);
+  else LAUNCH(8);
+#undef LAUNCH
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
@@ -434,9 +443,18 @@ int moe_b200_router_topk_bwd(const float* logits, const int64_t* topk_idx, const
   if (!logits || !topk_idx || !d_topk_w || !d_logits) return MOE_B200_ERR_NULL;
   const int64_t threads = n_tokens * 32;
   const unsigned grid = unsigned((threads + 255) / 256);
-  router_topk_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      logits, topk_idx, d_topk_w, d_probs, n_tokens, n_experts, top_k, normalize, full_softmax,
-      d_logits);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define LAUNCH(NS)                                                                             \
+  router_topk_bwd_kernel<NS><<<grid, 256, 0, st>>>(logits, topk_idx, d_topk_w, d_probs, n_tokens, \
+                                                   n_experts, top_k, normalize, full_softmax,     \
+                                                   d_logits)
+  const int nslot = (n_experts + 31) / 32;
+  if (nslot <= 1) LAUNCH(1);
+  else if (nslot <= 2) LAUNCH(2);
+  else if (nslot <= 3) LAUNCH(3);
+  else if (nslot <= 4) LAUNCH(4);
+  else LAUNCH(8);
+#undef LAUNCH
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 

@@ -273,6 +273,9 @@ def _experts_setup(ctx, inputs, output):
      n_post_pad, inv_ids, activation, save_for_backward) = inputs
     out, xs, a1, a1_sh = output
     ctx.mark_non_differentiable(xs, a1, a1_sh)
+    # without this autograd would hand the backward zero-filled gradients for the three kept
+    # buffers (hundreds of MB of memset per step)
+    ctx.set_materialize_grads(False)
     if not save_for_backward:
         raise RuntimeError("moe_experts was run with save_for_backward=False but a gradient is "
                            "being recorded; call it through fused_moe_forward")
@@ -289,6 +292,8 @@ def _experts_backward(ctx, grad_out, g_xs, g_a1, g_a1_sh):
     (x, xs, a1, a1_sh, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts,
      n_post_pad, inv_ids, *rest) = ctx.saved_tensors
     w_sh_in, w_sh_out = (rest[0], rest[1]) if ctx.has_shared else (None, None)
+    if grad_out is None:
+        grad_out = torch.zeros_like(x)
     dx, dw_in, dw_out, dtw, dsi, dso = moe_experts_bwd(
         grad_out, x, xs, a1, a1_sh, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids,
         expert_ids, pad_offsets, counts, n_post_pad, inv_ids, ctx.activation)
