@@ -117,7 +117,7 @@ static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const Row
 
 template <int BN, int STAGES>
 static int launch_wgrad(const CUtensorMap& tmA, const CUtensorMap& tmB, const WgradArgs& args,
-                        dim3 grid, cudaStream_t st) {
+                        int tiles_x, int tiles_y, int64_t max_items, cudaStream_t st) {
   auto kern = wgrad_gemm_kernel<BN, STAGES>;
   constexpr int smem = WgradSmem<BN, STAGES>::DYNAMIC;
   static std::once_flag once;
@@ -126,7 +126,9 @@ static int launch_wgrad(const CUtensorMap& tmA, const CUtensorMap& tmB, const Wg
     attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   });
   if (attr_err != cudaSuccess) return MOE_B200_ERR_CUDA;
-  kern<<<grid, WGRAD_THREADS, smem, st>>>(tmA, tmB, args);
+  const int64_t tiles = max_items * tiles_x * tiles_y, sms = sm_count();
+  const unsigned grid = unsigned(tiles < sms ? tiles : sms);
+  kern<<<grid, WGRAD_THREADS, smem, st>>>(tmA, tmB, args, tiles_x, tiles_y);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
@@ -320,7 +322,8 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
                    int32_t b_grouped, int32_t n_dim, int64_t rows, const int32_t* pad_offsets,
                    int32_t n_groups, int32_t ks_rows, void* dw, void* partials,
                    size_t partial_bytes, int32_t* status, void* stream) {
-  if (rows < 0 || rows > (int64_t(1) << 30) || n_groups < 1 || m_dim < 1 || n_dim < 1)
+  if (rows < 0 || rows > (int64_t(1) << 30) || n_groups < 1 || n_groups > WGRAD_MAX_GROUPS ||
+      m_dim < 1 || n_dim < 1)
     return MOE_B200_ERR_SHAPE;
   if (ks_rows < 0 || ks_rows % 64 != 0) return MOE_B200_ERR_SHAPE;
   if (m_dim % 8 != 0 || n_dim % 32 != 0) return MOE_B200_ERR_UNSUPPORTED;
@@ -360,13 +363,13 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   int rc;
   if (n_dim % 256 == 0) {
     const unsigned ty = unsigned(n_dim / 256);
-    rc = launch_wgrad<256, 4>(tmA, tmB, g, dim3(tx, ty, items), st);
+    rc = launch_wgrad<256, 4>(tmA, tmB, g, int(tx), int(ty), items, st);
     if (rc == MOE_B200_OK && may_split)
       wgrad_reduce_kernel<256><<<dim3(tx * ty * WGRAD_REDUCE_SPLIT, unsigned(n_groups)), 256, 0,
                                  st>>>(g, int(tx), int(ty));
   } else {
     const unsigned ty = unsigned((n_dim + 191) / 192);
-    rc = launch_wgrad<192, 5>(tmA, tmB, g, dim3(tx, ty, items), st);
+    rc = launch_wgrad<192, 5>(tmA, tmB, g, int(tx), int(ty), items, st);
     if (rc == MOE_B200_OK && may_split)
       wgrad_reduce_kernel<192><<<dim3(tx * ty * WGRAD_REDUCE_SPLIT, unsigned(n_groups)), 256, 0,
                                  st>>>(g, int(tx), int(ty));

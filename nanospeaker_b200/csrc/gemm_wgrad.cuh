@@ -11,15 +11,18 @@
 
 namespace moe {
 
-constexpr int WGRAD_THREADS = 192;
+constexpr int WGRAD_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+constexpr int WGRAD_MAX_GROUPS = 256;
 
 template <int BN, int STAGES>
 struct WgradSmem {
   static constexpr int B_STAGE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int MISC_OFFSET = BAR_OFFSET + 8 * (2 * STAGES + 1);
-  static constexpr int TOTAL = MISC_OFFSET + 32;
+  static constexpr int N_BARS = 2 * STAGES + 4;  // full, empty, tmem_full[2], tmem_empty[2]
+  static constexpr int MISC_OFFSET = BAR_OFFSET + 8 * N_BARS;
+  static constexpr int TABLE_OFFSET = MISC_OFFSET + 16;  // int first_item[G+1], int run_start[G+1]
+  static constexpr int TOTAL = TABLE_OFFSET + 2 * (WGRAD_MAX_GROUPS + 1) * 4;
   static constexpr int DYNAMIC = TOTAL + 1024;
 };
 
@@ -29,119 +32,95 @@ __host__ __device__ __forceinline__ int wgrad_chunks(int rows, int ks_rows) {
   return c > 0 ? c : 1;
 }
 
-
-// Warp-cooperative lookup of work item j: which run, which chunk of it. Writes
-// sched = {group (-1 if j is past the last item), chunk, chunks of the group, first row, rows}.
-__device__ __forceinline__ void wgrad_find_item(const WgradArgs& p, int j, int lane, int* sched) {
-  int group = -1, chunk = 0, n_c = 0, row0 = 0, rows = 0;
-  if (p.pad_offsets == nullptr) {
-    n_c = wgrad_chunks(p.rows_host, p.ks_rows);
-    if (j < n_c * p.n_groups) {
-      group = j / n_c;
-      chunk = j - group * n_c;
-      row0 = chunk * p.ks_rows;
-      rows = min(p.ks_rows, p.rows_host - row0);
-    }
-  } else {
-    int running = 0;
-    for (int base = 0; base < p.n_groups && group < 0; base += 32) {
-      const int g = base + lane;
-      int lo = 0, hi = 0;
-      if (g < p.n_groups) {
+// Exclusive prefix of the per-run work-item counts into first_item[0..G] and the run starts into
+// run_start[0..G]; executed by one full warp.
+__device__ __forceinline__ void wgrad_build_table(const WgradArgs& p, int lane, int* first_item,
+                                                  int* run_start) {
+  int running = 0;
+  for (int base = 0; base < p.n_groups; base += 32) {
+    const int g = base + lane;
+    int lo = 0, hi = 0;
+    if (g < p.n_groups) {
+      if (p.pad_offsets != nullptr) {
         lo = __ldg(p.pad_offsets + g);
         hi = __ldg(p.pad_offsets + g + 1);
+      } else {
+        hi = p.rows_host;
       }
-      const int mine = g < p.n_groups ? wgrad_chunks(hi - lo, p.ks_rows) : 0;
-      int incl = mine;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += v;
-      }
-      const int excl = incl - mine;
-      const bool owner = mine > 0 && j >= running + excl && j < running + incl;
-      const unsigned who = __ballot_sync(0xffffffffu, owner);
-      if (who) {
-        const int src = __ffs(who) - 1;
-        const int c = j - running - excl;
-        group = __shfl_sync(0xffffffffu, g, src);
-        chunk = __shfl_sync(0xffffffffu, c, src);
-        n_c = __shfl_sync(0xffffffffu, mine, src);
-        const int r0 = lo + c * p.ks_rows;
-        row0 = __shfl_sync(0xffffffffu, r0, src);
-        rows = __shfl_sync(0xffffffffu, max(0, min(p.ks_rows, hi - r0)), src);
-      }
-      running += __shfl_sync(0xffffffffu, incl, 31);
     }
+    const int mine = g < p.n_groups ? wgrad_chunks(hi - lo, p.ks_rows) : 0;
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (g < p.n_groups) {
+      first_item[g] = running + incl - mine;
+      run_start[g] = lo;
+    }
+    running += __shfl_sync(0xffffffffu, incl, 31);
   }
   if (lane == 0) {
-    sched[0] = group; sched[1] = chunk; sched[2] = n_c; sched[3] = row0; sched[4] = rows;
+    first_item[p.n_groups] = running;
+    run_start[p.n_groups] = p.pad_offsets != nullptr ? __ldg(p.pad_offsets + p.n_groups)
+                                                     : p.rows_host;
   }
 }
 
-// First work-item index and chunk count of run `g` (warp-cooperative; result in out[0..1]).
-__device__ __forceinline__ void wgrad_find_group(const WgradArgs& p, int g, int lane, int* out) {
-  int first = 0, n_c = 0;
-  if (p.pad_offsets == nullptr) {
-    n_c = wgrad_chunks(p.rows_host, p.ks_rows);
-    first = g * n_c;
-  } else {
-    int running = 0;
-    for (int base = 0; base <= g; base += 32) {
-      const int gg = base + lane;
-      int mine = 0;
-      if (gg < p.n_groups)
-        mine = wgrad_chunks(__ldg(p.pad_offsets + gg + 1) - __ldg(p.pad_offsets + gg), p.ks_rows);
-      int incl = mine;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += v;
-      }
-      if (g >= base && g < base + 32) {
-        first = running + __shfl_sync(0xffffffffu, incl - mine, g - base);
-        n_c = __shfl_sync(0xffffffffu, mine, g - base);
-      }
-      running += __shfl_sync(0xffffffffu, incl, 31);
-    }
+struct WgradItem {
+  int group, first, n_c, row0, num_k;
+};
+
+// Work item j -> its run, its chunk and the rows it contracts over (binary search in the table).
+__device__ __forceinline__ WgradItem wgrad_item(const WgradArgs& p, const int* first_item,
+                                                const int* run_start, int j) {
+  int lo = 0, hi = p.n_groups;  // first_item[lo] <= j < first_item[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (first_item[mid] <= j) lo = mid; else hi = mid;
   }
-  if (lane == 0) {
-    out[0] = first;
-    out[1] = n_c;
-  }
+  WgradItem it;
+  it.group = lo;
+  it.first = first_item[lo];
+  it.n_c = first_item[lo + 1] - it.first;
+  const int start = run_start[lo];
+  const int end = p.pad_offsets != nullptr ? run_start[lo + 1] : p.rows_host;
+  it.row0 = start + (j - it.first) * p.ks_rows;
+  int rows = end - it.row0;
+  rows = rows < 0 ? 0 : (rows > p.ks_rows ? p.ks_rows : rows);
+  it.num_k = (rows + BK - 1) / BK;
+  return it;
 }
 
+// Persistent: one CTA per SM walks the list of (work item, m tile, n chunk); the accumulator is
+// double-buffered in TMEM so a tile's store overlaps the next tile's loads and MMAs.
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(WGRAD_THREADS)
+__global__ void __launch_bounds__(WGRAD_THREADS, 1)
     wgrad_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
-                      const __grid_constant__ CUtensorMap tmB, const WgradArgs p) {
+                      const __grid_constant__ CUtensorMap tmB, const WgradArgs p, int tiles_x,
+                      int tiles_y) {
   using L = WgradSmem<BN, STAGES>;
-  constexpr uint32_t TMEM_COLS = BN <= 128 ? 128 : 256;
+  constexpr uint32_t TMEM_BUF = BN <= 128 ? 128 : 256;
+  constexpr uint32_t TMEM_COLS = 2 * TMEM_BUF;
   static_assert(BN % 64 == 0 && BN <= 256, "BN must be a multiple of 64 up to 256");
-
-  __shared__ int sched[5];  // group, chunk, chunks of the group, first row, rows in this chunk
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const int j = blockIdx.z;  // global work-item index along split-K
-  if (warp == 0) wgrad_find_item(p, j, lane, sched);
-  __syncthreads();
-  const int group = sched[0], chunk = sched[1], n_c = sched[2], row0 = sched[3];
-  if (group < 0) return;  // past the last work item (uniform over the CTA, nothing set up yet)
-  (void)chunk;
-  const int num_k = (sched[4] + BK - 1) / BK;
-
-  const int tile_m = blockIdx.x;
-  const int n0 = blockIdx.y * BN;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
   uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* accum_bar = empty_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::MISC_OFFSET);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* first_item = reinterpret_cast<int*>(smem + L::TABLE_OFFSET);
+  int* run_start = first_item + WGRAD_MAX_GROUPS + 1;
 
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (warp == 2) wgrad_build_table(p, lane, first_item, run_start);
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -149,7 +128,10 @@ __global__ void __launch_bounds__(WGRAD_THREADS)
       mbar_init(full_bar + s, 1);
       mbar_init(empty_bar + s, 1);
     }
-    mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar + b, 1);
+      mbar_init(tempty_bar + b, EPI_WARPS);
+    }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -161,80 +143,101 @@ __global__ void __launch_bounds__(WGRAD_THREADS)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const int tiles_xy = tiles_x * tiles_y;
+  const int total = first_item[p.n_groups] * tiles_xy;  // t = item * tiles_xy + tile
 
   if (warp == 0) {
     if (elect_one()) {
-      const int ga = p.a_grouped ? group : 0, gb = p.b_grouped ? group : 0;
-      for (int kt = 0; kt < num_k; ++kt) {
-        const int s = kt % STAGES;
-        if (kt >= STAGES && !mbar_wait(empty_bar + s, ((kt / STAGES) - 1) & 1, p.status)) {
-          *abort_flag = 1;
-          atomicExch(p.status, ST_WAIT_TIMEOUT);
-          break;
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total && !*abort_flag; t += gridDim.x) {
+        const WgradItem w = wgrad_item(p, first_item, run_start, t / tiles_xy);
+        const int txy = t % tiles_xy;
+        const int m0 = (txy / tiles_y) * BM, n0 = (txy % tiles_y) * BN;
+        const int ga = p.a_grouped ? w.group : 0, gb = p.b_grouped ? w.group : 0;
+        for (int kt = 0; kt < w.num_k; ++kt, ++it) {
+          const int s = it % STAGES;
+          const uint32_t use = it / STAGES;
+          if (use > 0 && !mbar_wait(empty_bar + s, (use - 1) & 1, p.status)) {
+            *abort_flag = 1;
+            atomicExch(p.status, ST_WAIT_TIMEOUT);
+            break;
+          }
+          uint8_t* sA = smem + s * L::STAGE_BYTES;
+          uint8_t* sB = sA + A_STAGE_BYTES;
+          mbar_expect_tx(full_bar + s, L::STAGE_BYTES);
+          const int r = w.row0 + kt * BK;
+#pragma unroll
+          for (int i = 0; i < BM / 64; ++i)
+            tma_load_3d(sA + i * 8192, &tmA, full_bar + s, m0 + 64 * i, r, ga);
+#pragma unroll
+          for (int jj = 0; jj < BN / 64; ++jj)
+            tma_load_3d(sB + jj * 8192, &tmB, full_bar + s, n0 + 64 * jj, r, gb);
         }
-        uint8_t* sA = smem + s * L::STAGE_BYTES;
-        uint8_t* sB = sA + A_STAGE_BYTES;
-        mbar_expect_tx(full_bar + s, L::STAGE_BYTES);
-        const int r = row0 + kt * BK;
-#pragma unroll
-        for (int i = 0; i < BM / 64; ++i)
-          tma_load_3d(sA + i * 8192, &tmA, full_bar + s, tile_m * BM + 64 * i, r, ga);
-#pragma unroll
-        for (int jj = 0; jj < BN / 64; ++jj)
-          tma_load_3d(sB + jj * 8192, &tmB, full_bar + s, n0 + 64 * jj, r, gb);
       }
     }
   } else if (warp == 1) {
     if (elect_one()) {
-      for (int kt = 0; kt < num_k; ++kt) {
-        const int s = kt % STAGES;
-        if (!mbar_wait(full_bar + s, (kt / STAGES) & 1, p.status)) {
+      uint32_t it = 0;
+      int ju = 0;  // tiles that really used an accumulator buffer so far
+      for (int t = blockIdx.x; t < total && !*abort_flag; t += gridDim.x) {
+        const WgradItem w = wgrad_item(p, first_item, run_start, t / tiles_xy);
+        if (w.num_k == 0) continue;  // empty run: the epilogue writes zeros, no accumulator used
+        const int b = ju & 1;
+        const uint32_t use = uint32_t(ju) >> 1;
+        ++ju;
+        if (use > 0 && !mbar_wait(tempty_bar + b, (use - 1) & 1, p.status)) {
           *abort_flag = 1;
           atomicExch(p.status, ST_WAIT_TIMEOUT);
           break;
         }
         tc_fence_after();
-        const uint32_t sA = smem_u32(smem + s * L::STAGE_BYTES);
-        issue_stage_mmas<BN, true, true>(sA, sA + A_STAGE_BYTES, tmem_base, kt == 0);
-        umma_commit(empty_bar + s);
+        const uint32_t d_tmem = tmem_base + b * TMEM_BUF;
+        for (int kt = 0; kt < w.num_k; ++kt, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(full_bar + s, (it / STAGES) & 1, p.status)) {
+            *abort_flag = 1;
+            atomicExch(p.status, ST_WAIT_TIMEOUT);
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + s * L::STAGE_BYTES);
+          issue_stage_mmas<BN, true, true>(sA, sA + A_STAGE_BYTES, d_tmem, kt == 0);
+          umma_commit(empty_bar + s);
+        }
+        umma_commit(tfull_bar + b);
       }
-      umma_commit(accum_bar);
     }
   } else {
+    const int ew = warp - 2;
     const int q = warp & 3;
+    const int half = ew >> 2;
     const int row = q * 32 + lane;
-    const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16);
-    const bool have_acc = num_k > 0;
-    if (have_acc) {
-      if (!mbar_wait(accum_bar, 0, p.status)) atomicExch(p.status, ST_WAIT_TIMEOUT);
-      tc_fence_after();
-    }
-    const int m = tile_m * BM + row;
-    const bool m_ok = m < p.m_dim;
-    __nv_bfloat16* dst = p.out + (int64_t(group) * p.m_dim + m) * int64_t(p.n_dim) + n0;
     constexpr int NCH = BN / 32;
+    static_assert(NCH % 2 == 0, "column chunks must split evenly over the two epilogue halves");
+    const int c_lo = half * (NCH / 2), c_hi = c_lo + NCH / 2;
 
-    if (n_c == 1) {
-#pragma unroll 1
-      for (int c = 0; c < NCH; ++c) {
-        float v[32];
-        if (have_acc) {
-          tmem_ld32(taddr + c * 32, v);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0.f;
-        }
-        if (m_ok && n0 + c * 32 < p.n_dim) store_bf16x32(dst + c * 32, v);
+    int ju = 0;  // tiles that really used an accumulator buffer so far (same count as the MMA warp)
+    for (int t = blockIdx.x; t < total; t += gridDim.x) {
+      const int j = t / tiles_xy, txy = t % tiles_xy;
+      const WgradItem w = wgrad_item(p, first_item, run_start, j);
+      const int m0 = (txy / tiles_y) * BM, n0 = (txy % tiles_y) * BN;
+      const bool have_acc = w.num_k > 0;
+      // The MMA warp skips empty runs without touching a buffer, so the epilogue neither waits
+      // nor arrives for them: buffer choice and barrier phases count real uses only.
+      const int b = ju & 1;
+      if (have_acc) {
+        if (!mbar_wait(tfull_bar + b, (uint32_t(ju) >> 1) & 1, p.status))
+          atomicExch(p.status, ST_WAIT_TIMEOUT);
+        tc_fence_after();
+        ++ju;
       }
-    } else {
-      // fp32 partial of this chunk; slot layout [column chunk][row][32]
-      const int64_t slot_elems = int64_t(BM) * BN;
-      const int64_t tiles_xy = int64_t(gridDim.x) * gridDim.y;
-      const int64_t tile_xy = int64_t(tile_m) * gridDim.y + blockIdx.y;
-      float* mine = p.partials + (int64_t(j) * tiles_xy + tile_xy) * slot_elems;
+      const uint32_t taddr = tmem_base + b * TMEM_BUF + (uint32_t(q * 32) << 16);
+      const int m = m0 + row;
+      const bool m_ok = m < p.m_dim;
+      __nv_bfloat16* dst = p.out + (int64_t(w.group) * p.m_dim + m) * int64_t(p.n_dim) + n0;
+      float* mine = p.partials + (int64_t(j) * tiles_xy + txy) * (int64_t(BM) * BN);
 #pragma unroll 1
-      for (int c = 0; c < NCH; ++c) {
+      for (int c = c_lo; c < c_hi; ++c) {
         float v[32];
         if (have_acc) {
           tmem_ld32(taddr + c * 32, v);
@@ -243,7 +246,16 @@ __global__ void __launch_bounds__(WGRAD_THREADS)
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0.f;
         }
-        store_f32x32(mine + (int64_t(c) * BM + row) * 32, v);
+        if (w.n_c == 1) {
+          if (m_ok && n0 + c * 32 < p.n_dim) store_bf16x32(dst + c * 32, v);
+        } else {
+          store_f32x32(mine + (int64_t(c) * BM + row) * 32, v);  // [column chunk][row][32]
+        }
+      }
+      if (have_acc) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar + b);
       }
     }
   }
@@ -262,11 +274,12 @@ constexpr int WGRAD_REDUCE_SPLIT = 16;  // CTAs sharing the reduction of one out
 template <int BN>
 __global__ void __launch_bounds__(256)
     wgrad_reduce_kernel(const WgradArgs p, int tiles_x, int tiles_y) {
-  __shared__ int info[2];
+  __shared__ int first_item[WGRAD_MAX_GROUPS + 1];
+  __shared__ int run_start[WGRAD_MAX_GROUPS + 1];
   const int g = blockIdx.y;
-  if (threadIdx.x < 32) wgrad_find_group(p, g, threadIdx.x, info);
+  if (threadIdx.x < 32) wgrad_build_table(p, threadIdx.x, first_item, run_start);
   __syncthreads();
-  const int first = info[0], n_c = info[1];
+  const int first = first_item[g], n_c = first_item[g + 1] - first;
   if (n_c <= 1) return;
   const int tile_xy = blockIdx.x / WGRAD_REDUCE_SPLIT;
   const int slice = blockIdx.x % WGRAD_REDUCE_SPLIT;
