@@ -140,14 +140,22 @@ int moe_b200_combine(const void* y, const int32_t* inv_ids, int64_t n_tokens, in
  *                   `rows` rows in token order (`rows` need not be a multiple of 128); outputs are
  *                   stacked [S, rows, width]. */
 
+/* Gathered A operand (routed schedule only): with gather_top_k > 0 the A argument is the
+ * token-major matrix [n_pairs / gather_top_k, width] and the kernel itself reads row
+ * sorted_ids[slot] / gather_top_k for slot `slot` (zero rows in pad slots), so no permuted copy has
+ * to exist -- the gather loads of _gemm1_kernel (src/model/moe_kernel.py:295-305). With
+ * gather_top_k == 0 A is a slot-ordered [rows, width] buffer (e.g. from moe_b200_permute). */
+
 /* Up/gate GEMM with the GLU fused: [g | u] = a[row] @ w_in[e] (w_in [n_groups, d_model,
  * 2*d_hidden]); hid[row] = act(g) * u  ([rows, d_hidden]); when raw != NULL it also receives
  * [g | u] ([rows, 2*d_hidden], kept for the backward). a is [rows, d_model] (shared by all fixed
- * groups). Replaces _gemm1_kernel (src/model/moe_kernel.py:269-323). d_hidden must be 128. */
+ * groups) or gathered. Replaces _gemm1_kernel (src/model/moe_kernel.py:269-323).
+ * d_hidden must be 128. */
 int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w_in,
                      int32_t n_groups, int32_t d_hidden, const int32_t* expert_ids,
-                     const int32_t* n_post_pad, int32_t n_fixed_groups, int32_t activation,
-                     void* hid, void* raw, int32_t* status, void* stream);
+                     const int32_t* n_post_pad, int32_t n_fixed_groups,
+                     const int32_t* sorted_ids, int32_t gather_top_k, int64_t n_pairs,
+                     int32_t activation, void* hid, void* raw, int32_t* status, void* stream);
 
 /* Down GEMM with the router weight fused: y[row] = (hid[row] @ w_out[e]) * pair_w[sorted_ids[row]]
  * (w_out [n_groups, k_dim, d_model]; weight 1 when pair_w is NULL). With fixed groups hid is
@@ -162,15 +170,16 @@ int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void*
 /* Backward through the down GEMM and the GLU in one kernel: G = douts[row] @ w_out[e]^T, then with
  * [g | u] = a1[row] and w = pair_w[pair]:  dtw[pair] = <G, act(g)*u>,
  * da1[row] = [w*G*u*act'(g) | w*G*act(g)],  hidw[row] = w * act(g) * u.
- * douts is [rows, d_model] (shared by all fixed groups); a1, da1, hidw are stacked per fixed group.
+ * douts is [rows, d_model] (shared by all fixed groups) or, with gather_top_k > 0, the token-major
+ * dOut gathered through sorted_ids; a1, da1, hidw are stacked per fixed group.
  * Replaces the dH use of _gemm2_kernel plus _glu_bwd_kernel
  * (src/model/moe_kernel.py:676-692, 510-553). dtw may be NULL. */
 int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, const void* w_out,
                              int32_t n_groups, int32_t d_hidden, const int32_t* expert_ids,
                              const int32_t* n_post_pad, int32_t n_fixed_groups,
-                             const int32_t* sorted_ids, const void* pair_w, int64_t n_pairs,
-                             const void* a1, int32_t activation, void* da1, void* hidw, void* dtw,
-                             int32_t* status, void* stream);
+                             const int32_t* sorted_ids, int32_t gather_top_k, const void* pair_w,
+                             int64_t n_pairs, const void* a1, int32_t activation, void* da1,
+                             void* hidw, void* dtw, int32_t* status, void* stream);
 
 /* dX GEMM: ydx[row] = da1[row] @ w_in[e]^T, reading w_in [n_groups, d_model, 2*d_hidden] in place
  * (no transposed copy). With fixed groups da1 and ydx are stacked [S, rows, .]. Replaces the dX use
@@ -192,11 +201,15 @@ int moe_b200_wgrad_scratch_bytes(int32_t m_dim, int32_t n_dim, int64_t rows, int
  * [n_groups, rows, .] or shared by all groups. The contraction is split into chunks of ks_rows rows
  * (a multiple of 64; 0 = let the library choose) so long runs spread over many SMs; a run's partial
  * tiles are added in chunk order by a second small kernel, so the result is deterministic.
+ * gather_which = 1 (a) or 2 (b), routed schedule only: that operand is the token-major matrix
+ * [n_pairs / gather_top_k, width] and its rows are gathered through sorted_ids inside the kernel
+ * (0 = both operands are slot-ordered buffers).
  * Replaces _dw_kernel (src/model/moe_kernel.py:453-507, 712-721), which has no split-K. */
 int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* b,
                    int32_t b_grouped, int32_t n_dim, int64_t rows, const int32_t* pad_offsets,
-                   int32_t n_groups, int32_t ks_rows, void* dw, void* partials,
-                   size_t partial_bytes, int32_t* status, void* stream);
+                   int32_t n_groups, int32_t ks_rows, const int32_t* sorted_ids,
+                   int32_t gather_top_k, int64_t n_pairs, int32_t gather_which, void* dw,
+                   void* partials, size_t partial_bytes, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

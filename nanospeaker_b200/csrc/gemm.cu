@@ -98,10 +98,10 @@ static int sm_count() {
 }
 
 // Persistent launch: one CTA per SM (fewer if the tile list is shorter than that).
-template <int BN, int STAGES, bool B_MN, int EPI>
+template <int BN, int STAGES, bool B_MN, int EPI, bool GATHER_A = false>
 static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const RowsArgs& args,
                        int64_t max_tiles, cudaStream_t st) {
-  auto kern = rows_gemm_kernel<BN, STAGES, B_MN, EPI>;
+  auto kern = rows_gemm_kernel<BN, STAGES, B_MN, EPI, GATHER_A>;
   constexpr int smem = RowsSmem<BN, STAGES>::DYNAMIC;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
@@ -168,17 +168,22 @@ extern "C" {
 
 int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w_in,
                      int32_t n_groups, int32_t d_hidden, const int32_t* expert_ids,
-                     const int32_t* n_post_pad, int32_t n_fixed_groups, int32_t activation,
-                     void* hid, void* raw, int32_t* status, void* stream) {
+                     const int32_t* n_post_pad, int32_t n_fixed_groups,
+                     const int32_t* sorted_ids, int32_t gather_top_k, int64_t n_pairs,
+                     int32_t activation, void* hid, void* raw, int32_t* status, void* stream) {
   CHECK_SCHED();
   if (d_hidden != 128 || d_model % 8 != 0 || d_model < 64) return MOE_B200_ERR_UNSUPPORTED;
   if (activation < 0 || activation > 4) return MOE_B200_ERR_UNSUPPORTED;
   if (!a || !w_in || !hid) return MOE_B200_ERR_NULL;
+  if (gather_top_k < 0 || (gather_top_k > 0 && (n_fixed_groups > 0 || !sorted_ids || n_pairs < 0)))
+    return MOE_B200_ERR_SHAPE;
   if (!aligned16(a) || !aligned16(w_in) || !aligned16(hid) || !aligned16(raw))
     return MOE_B200_ERR_ALIGN;
   CUtensorMap tmA, tmB;
-  if (!map_rows_kmajor(&tmA, a, 1, rows, d_model) ||
-      !map_weight_mnmajor(&tmB, w_in, n_groups, d_model, 2 * d_hidden))
+  if (!map_weight_mnmajor(&tmB, w_in, n_groups, d_model, 2 * d_hidden)) return MOE_B200_ERR_TMA;
+  if (gather_top_k > 0)
+    tmA = tmB;  // unused: A rows are gathered with cp.async
+  else if (!map_rows_kmajor(&tmA, a, 1, rows, d_model))
     return MOE_B200_ERR_TMA;
   RowsArgs g = base_args(expert_ids, n_post_pad, n_fixed_groups, rows, status);
   g.num_k = (d_model + BK - 1) / BK;
@@ -190,8 +195,15 @@ int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w
   g.out2 = static_cast<__nv_bfloat16*>(raw);
   g.out2_gstride = rows * int64_t(2 * d_hidden);
   g.act = activation;
-  return launch_rows<256, 4, true, EPI_GLU>(tmA, tmB, g, max_tiles(rows, 1, n_fixed_groups),
-                                            static_cast<cudaStream_t>(stream));
+  g.sorted_ids = sorted_ids;
+  g.n_pairs = int32_t(n_pairs);
+  g.a_src = static_cast<const __nv_bfloat16*>(a);
+  g.a_cols = d_model;
+  g.top_k = gather_top_k;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t tiles = max_tiles(rows, 1, n_fixed_groups);
+  if (gather_top_k > 0) return launch_rows<256, 4, true, EPI_GLU, true>(tmA, tmB, g, tiles, st);
+  return launch_rows<256, 4, true, EPI_GLU>(tmA, tmB, g, tiles, st);
 }
 
 int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void* w_out,
@@ -227,10 +239,12 @@ int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void*
 int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, const void* w_out,
                              int32_t n_groups, int32_t d_hidden, const int32_t* expert_ids,
                              const int32_t* n_post_pad, int32_t n_fixed_groups,
-                             const int32_t* sorted_ids, const void* pair_w, int64_t n_pairs,
-                             const void* a1, int32_t activation, void* da1, void* hidw, void* dtw,
-                             int32_t* status, void* stream) {
+                             const int32_t* sorted_ids, int32_t gather_top_k, const void* pair_w,
+                             int64_t n_pairs, const void* a1, int32_t activation, void* da1,
+                             void* hidw, void* dtw, int32_t* status, void* stream) {
   CHECK_SCHED();
+  if (gather_top_k < 0 || (gather_top_k > 0 && (n_fixed_groups > 0 || !sorted_ids)))
+    return MOE_B200_ERR_SHAPE;
   if (d_hidden != 128 || d_model % 8 != 0 || d_model < 64) return MOE_B200_ERR_UNSUPPORTED;
   if (activation < 0 || activation > 4) return MOE_B200_ERR_UNSUPPORTED;
   if (!douts || !w_out || !a1 || !da1 || !hidw) return MOE_B200_ERR_NULL;
@@ -239,8 +253,10 @@ int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, c
       !aligned16(hidw))
     return MOE_B200_ERR_ALIGN;
   CUtensorMap tmA, tmB;
-  if (!map_rows_kmajor(&tmA, douts, 1, rows, d_model) ||
-      !map_weight_kmajor(&tmB, w_out, n_groups, d_hidden, d_model, 128))
+  if (!map_weight_kmajor(&tmB, w_out, n_groups, d_hidden, d_model, 128)) return MOE_B200_ERR_TMA;
+  if (gather_top_k > 0)
+    tmA = tmB;  // unused: dOut rows are gathered with cp.async
+  else if (!map_rows_kmajor(&tmA, douts, 1, rows, d_model))
     return MOE_B200_ERR_TMA;
   RowsArgs g = base_args(expert_ids, n_post_pad, n_fixed_groups, rows, status);
   g.num_k = (d_model + BK - 1) / BK;
@@ -258,8 +274,13 @@ int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, c
   g.out2_gstride = rows * int64_t(d_hidden);
   g.dtw = static_cast<__nv_bfloat16*>(dtw);
   g.act = activation;
-  return launch_rows<128, 6, false, EPI_GLUBWD>(tmA, tmB, g, max_tiles(rows, 1, n_fixed_groups),
-                                                static_cast<cudaStream_t>(stream));
+  g.a_src = static_cast<const __nv_bfloat16*>(douts);
+  g.a_cols = d_model;
+  g.top_k = gather_top_k;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t tiles = max_tiles(rows, 1, n_fixed_groups);
+  if (gather_top_k > 0) return launch_rows<128, 6, false, EPI_GLUBWD, true>(tmA, tmB, g, tiles, st);
+  return launch_rows<128, 6, false, EPI_GLUBWD>(tmA, tmB, g, tiles, st);
 }
 
 int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,
@@ -320,8 +341,9 @@ int moe_b200_wgrad_scratch_bytes(int32_t m_dim, int32_t n_dim, int64_t rows, int
 
 int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* b,
                    int32_t b_grouped, int32_t n_dim, int64_t rows, const int32_t* pad_offsets,
-                   int32_t n_groups, int32_t ks_rows, void* dw, void* partials,
-                   size_t partial_bytes, int32_t* status, void* stream) {
+                   int32_t n_groups, int32_t ks_rows, const int32_t* sorted_ids,
+                   int32_t gather_top_k, int64_t n_pairs, int32_t gather_which, void* dw,
+                   void* partials, size_t partial_bytes, int32_t* status, void* stream) {
   if (rows < 0 || rows > (int64_t(1) << 30) || n_groups < 1 || n_groups > WGRAD_MAX_GROUPS ||
       m_dim < 1 || n_dim < 1)
     return MOE_B200_ERR_SHAPE;
@@ -329,6 +351,9 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   if (m_dim % 8 != 0 || n_dim % 32 != 0) return MOE_B200_ERR_UNSUPPORTED;
   if (pad_offsets && (a_grouped || b_grouped)) return MOE_B200_ERR_SHAPE;
   if (pad_offsets && rows % 128 != 0) return MOE_B200_ERR_SHAPE;
+  if (gather_which < 0 || gather_which > 2) return MOE_B200_ERR_SHAPE;
+  if (gather_which && (!pad_offsets || !sorted_ids || gather_top_k < 1 || n_pairs < 0))
+    return MOE_B200_ERR_SHAPE;
   if (!a || !b || !dw || !status || !partials) return MOE_B200_ERR_NULL;
   if (!aligned16(a) || !aligned16(b) || !aligned16(dw) || !aligned16(partials))
     return MOE_B200_ERR_ALIGN;
@@ -340,9 +365,13 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   CUtensorMap tmA, tmB;
   // rows == 0 still launches: every C[e] must be written (with zeros)
   const int64_t map_rows = rows > 0 ? rows : 1;
-  if (!map_rows_mnmajor(&tmA, a, a_grouped ? n_groups : 1, map_rows, m_dim) ||
-      !map_rows_mnmajor(&tmB, b, b_grouped ? n_groups : 1, map_rows, n_dim))
+  // a gathered operand is token-major and copied with cp.async: it gets the other one's map
+  if (gather_which != 1 && !map_rows_mnmajor(&tmA, a, a_grouped ? n_groups : 1, map_rows, m_dim))
     return MOE_B200_ERR_TMA;
+  if (gather_which != 2 && !map_rows_mnmajor(&tmB, b, b_grouped ? n_groups : 1, map_rows, n_dim))
+    return MOE_B200_ERR_TMA;
+  if (gather_which == 1) tmA = tmB;
+  if (gather_which == 2) tmB = tmA;
   WgradArgs g{};
   g.pad_offsets = pad_offsets;
   g.n_groups = n_groups;
@@ -355,24 +384,31 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   g.out = static_cast<__nv_bfloat16*>(dw);
   g.partials = static_cast<float*>(partials);
   g.status = status;
+  g.gather_a = gather_which == 1;
+  g.gather_b = gather_which == 2;
+  g.gather_src = static_cast<const __nv_bfloat16*>(gather_which == 1 ? a : b);
+  g.sorted_ids = sorted_ids;
+  g.top_k = gather_top_k;
+  g.n_pairs = int32_t(n_pairs);
   const unsigned items = unsigned(wgrad_items(rows, n_groups, routed, ks_rows));
   // the second pass can be skipped when no run can have more than one chunk
   const bool may_split = rows > ks_rows;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned tx = unsigned((m_dim + BM - 1) / BM);
+  const unsigned gy = unsigned(n_groups < 4 ? n_groups : 4);  // reduce CTAs striding over groups
   int rc;
   if (n_dim % 256 == 0) {
     const unsigned ty = unsigned(n_dim / 256);
     rc = launch_wgrad<256, 4>(tmA, tmB, g, int(tx), int(ty), items, st);
     if (rc == MOE_B200_OK && may_split)
-      wgrad_reduce_kernel<256><<<dim3(tx * ty * WGRAD_REDUCE_SPLIT, unsigned(n_groups)), 256, 0,
-                                 st>>>(g, int(tx), int(ty));
+      wgrad_reduce_kernel<256><<<dim3(tx * ty * WGRAD_REDUCE_SPLIT, gy), 256, 0, st>>>(g, int(tx),
+                                                                                   int(ty));
   } else {
     const unsigned ty = unsigned((n_dim + 191) / 192);
     rc = launch_wgrad<192, 5>(tmA, tmB, g, int(tx), int(ty), items, st);
     if (rc == MOE_B200_OK && may_split)
-      wgrad_reduce_kernel<192><<<dim3(tx * ty * WGRAD_REDUCE_SPLIT, unsigned(n_groups)), 256, 0,
-                                 st>>>(g, int(tx), int(ty));
+      wgrad_reduce_kernel<192><<<dim3(tx * ty * WGRAD_REDUCE_SPLIT, gy), 256, 0, st>>>(g, int(tx),
+                                                                                   int(ty));
   }
   if (rc != MOE_B200_OK) return rc;
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;

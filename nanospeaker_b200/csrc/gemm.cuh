@@ -44,6 +44,11 @@ struct RowsArgs {
                                // token order (shared experts)
   int32_t rows_host;           // row count of the fixed-group schedule
   int32_t a_grouped;           // fixed schedule: A has a leading group dim ([G, rows, K])
+  // gathered A (routed schedule only): row `slot` of the tile list is row sorted_ids[slot] / top_k
+  // of the token-major matrix a_src [n_tokens, a_cols]; pad slots read as zero rows
+  const __nv_bfloat16* a_src;
+  int32_t a_cols;
+  int32_t top_k;
   int32_t n_pairs;             // sentinel value in sorted_ids
   int32_t num_k;               // K / 64 (rounded up; the tail reads as zeros)
   int32_t n_dim;               // valid accumulator columns over all N chunks
@@ -68,6 +73,12 @@ struct WgradArgs {
   int32_t rows_host;           // fixed schedule: every group spans rows [0, rows_host)
   int32_t ks_rows;             // rows per split-K chunk (multiple of 64)
   int32_t a_grouped, b_grouped;  // fixed schedule: operand has a leading group dim
+  // gathered operand (routed schedule only): its row `slot` is row sorted_ids[slot] / top_k of the
+  // token-major matrix gather_src [n_tokens, m_dim or n_dim]; pad slots read as zero rows
+  int32_t gather_a, gather_b;
+  const __nv_bfloat16* gather_src;
+  const int32_t* sorted_ids;
+  int32_t top_k, n_pairs;
   int32_t m_dim, n_dim;        // rows / cols of one C[e]
   __nv_bfloat16* out;          // [G, m_dim, n_dim]
   float* partials;             // fp32 scratch for the partial tiles of split runs

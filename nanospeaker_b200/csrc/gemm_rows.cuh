@@ -15,7 +15,8 @@ struct RowsSmem {
   static constexpr int N_BARS = 2 * STAGES + 4;  // full, empty, tmem_full[2], tmem_empty[2]
   static constexpr int MISC_OFFSET = BAR_OFFSET + 8 * N_BARS;      // tmem slot, abort flag
   static constexpr int PART_OFFSET = MISC_OFFSET + 16;             // float[128] dtw partials
-  static constexpr int TOTAL = PART_OFFSET + 128 * 4;
+  static constexpr int TOK_OFFSET = PART_OFFSET + 128 * 4;         // int[128] gathered row ids
+  static constexpr int TOTAL = TOK_OFFSET + 128 * 4;
   static constexpr int DYNAMIC = TOTAL + 1024;  // slack for manual 1024-byte alignment
 };
 
@@ -95,7 +96,7 @@ __device__ __forceinline__ float epilogue_glubwd(uint32_t taddr, int c_lo, int c
   return part;
 }
 
-template <int BN, int STAGES, bool B_MN, int EPI>
+template <int BN, int STAGES, bool B_MN, int EPI, bool GATHER_A>
 __global__ void __launch_bounds__(ROWS_THREADS, 1)
     rows_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB, const RowsArgs p) {
@@ -120,6 +121,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::MISC_OFFSET);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* dtw_part = reinterpret_cast<float*>(smem + L::PART_OFFSET);
+  int* tok_s = reinterpret_cast<int*>(smem + L::TOK_OFFSET);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -128,7 +130,8 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1)
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar + s, 1);
+      // gathered A: every lane of warp 0 arrives (through its cp.async) next to the TMA transaction
+      mbar_init(full_bar + s, GATHER_A ? 33 : 1);
       mbar_init(empty_bar + s, 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -147,7 +150,58 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == 0 && GATHER_A) {
+    // ------------------------------------------- producer, gathered A: the whole warp copies rows
+    // Lane (r4 = lane / 8, c = lane % 8) moves 16-byte chunk c of tile rows r4, r4 + 4, ...: eight
+    // lanes cover one row's 128-byte k slice, so global reads are whole lines. The chunk lands at
+    // (c ^ (row & 7)), which is the 128-byte swizzle the UMMA descriptor expects.
+    uint32_t it = 0;
+    const int r4 = lane >> 3, c = lane & 7;
+    for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+      const TileCoord tc = decode_tile(p, t, m_tiles, BN);
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int pair = __ldg(p.sorted_ids + int64_t(tc.m_tile) * BM + i * 32 + lane);
+        tok_s[i * 32 + lane] = pair < p.n_pairs ? pair / p.top_k : -1;
+      }
+      __syncwarp();
+      for (int kt = 0; kt < p.num_k; ++kt, ++it) {
+        const int s = it % STAGES;
+        const uint32_t use = it / STAGES;
+        if (use > 0 && !mbar_wait(empty_bar + s, (use - 1) & 1, p.status)) {
+          *abort_flag = 1;
+          atomicExch(p.status, ST_WAIT_TIMEOUT);
+        }
+        if (__any_sync(0xffffffffu, *abort_flag)) break;
+        uint8_t* sA = smem + s * L::STAGE_BYTES;
+        uint8_t* sB = sA + A_STAGE_BYTES;
+        const int k0 = kt * BK;
+        if (lane == 0) {
+          mbar_expect_tx(full_bar + s, L::B_STAGE_BYTES);
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sB + j * 8192, &tmB, full_bar + s, tc.n0 + 64 * j, k0, tc.group);
+          } else {
+            tma_load_3d(sB, &tmB, full_bar + s, k0, tc.n0, tc.group);
+          }
+        }
+        const int col = k0 + c * 8;
+        const bool col_ok = col < p.a_cols;
+        const uint32_t sA_u = smem_u32(sA);
+#pragma unroll 8
+        for (int i = 0; i < 32; ++i) {
+          const int row = i * 4 + r4;
+          const int tok = tok_s[row];
+          const bool ok = tok >= 0 && col_ok;
+          const __nv_bfloat16* src = ok ? p.a_src + int64_t(tok) * p.a_cols + col : p.a_src;
+          cp_async_16(sA_u + row * 128 + ((c ^ (row & 7)) << 4), src, ok ? 16u : 0u);
+        }
+        cp_async_arrive(full_bar + s);
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       uint32_t it = 0;
@@ -199,6 +253,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1)
             break;
           }
           tc_fence_after();
+          if constexpr (GATHER_A) fence_proxy_async();  // cp.async wrote A through the generic proxy
           const uint32_t sA = smem_u32(smem + s * L::STAGE_BYTES);
           issue_stage_mmas<BN, false, B_MN>(sA, sA + A_STAGE_BYTES, d_tmem, kt == 0);
           umma_commit(empty_bar + s);  // stage reusable once these MMAs have read it

@@ -22,7 +22,8 @@ struct WgradSmem {
   static constexpr int N_BARS = 2 * STAGES + 4;  // full, empty, tmem_full[2], tmem_empty[2]
   static constexpr int MISC_OFFSET = BAR_OFFSET + 8 * N_BARS;
   static constexpr int TABLE_OFFSET = MISC_OFFSET + 16;  // int first_item[G+1], int run_start[G+1]
-  static constexpr int TOTAL = TABLE_OFFSET + 2 * (WGRAD_MAX_GROUPS + 1) * 4;
+  static constexpr int TOK_OFFSET = TABLE_OFFSET + 2 * (WGRAD_MAX_GROUPS + 1) * 4;  // int[64]
+  static constexpr int TOTAL = TOK_OFFSET + 64 * 4;
   static constexpr int DYNAMIC = TOTAL + 1024;
 };
 
@@ -116,6 +117,8 @@ __global__ void __launch_bounds__(WGRAD_THREADS, 1)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* first_item = reinterpret_cast<int*>(smem + L::TABLE_OFFSET);
   int* run_start = first_item + WGRAD_MAX_GROUPS + 1;
+  int* tok_s = reinterpret_cast<int*>(smem + L::TOK_OFFSET);
+  const bool gather = p.gather_a || p.gather_b;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -125,7 +128,8 @@ __global__ void __launch_bounds__(WGRAD_THREADS, 1)
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar + s, 1);
+      // a gathered operand: every lane of warp 0 arrives (through its cp.async) next to the TMA
+      mbar_init(full_bar + s, gather ? 33 : 1);
       mbar_init(empty_bar + s, 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -147,7 +151,10 @@ __global__ void __launch_bounds__(WGRAD_THREADS, 1)
   const int total = first_item[p.n_groups] * tiles_xy;  // t = item * tiles_xy + tile
 
   if (warp == 0) {
-    if (elect_one()) {
+    // Producer. Plain operands arrive by TMA (lane 0). A gathered operand is copied by the whole
+    // warp with 16-byte cp.async: row `slot` of the stage is row sorted_ids[slot] / top_k of the
+    // token-major source, and 64-column groups land as the same swizzled 64 x 64 boxes TMA makes.
+    if (gather || lane == 0) {
       uint32_t it = 0;
       for (int t = blockIdx.x; t < total && !*abort_flag; t += gridDim.x) {
         const WgradItem w = wgrad_item(p, first_item, run_start, t / tiles_xy);
@@ -160,18 +167,49 @@ __global__ void __launch_bounds__(WGRAD_THREADS, 1)
           if (use > 0 && !mbar_wait(empty_bar + s, (use - 1) & 1, p.status)) {
             *abort_flag = 1;
             atomicExch(p.status, ST_WAIT_TIMEOUT);
-            break;
           }
+          if (gather ? __any_sync(0xffffffffu, *abort_flag) : *abort_flag) break;
           uint8_t* sA = smem + s * L::STAGE_BYTES;
           uint8_t* sB = sA + A_STAGE_BYTES;
-          mbar_expect_tx(full_bar + s, L::STAGE_BYTES);
           const int r = w.row0 + kt * BK;
+          if (lane == 0) {
+            mbar_expect_tx(full_bar + s, (p.gather_a ? 0 : A_STAGE_BYTES) +
+                                             (p.gather_b ? 0 : L::B_STAGE_BYTES));
+            if (!p.gather_a) {
 #pragma unroll
-          for (int i = 0; i < BM / 64; ++i)
-            tma_load_3d(sA + i * 8192, &tmA, full_bar + s, m0 + 64 * i, r, ga);
+              for (int i = 0; i < BM / 64; ++i)
+                tma_load_3d(sA + i * 8192, &tmA, full_bar + s, m0 + 64 * i, r, ga);
+            }
+            if (!p.gather_b) {
 #pragma unroll
-          for (int jj = 0; jj < BN / 64; ++jj)
-            tma_load_3d(sB + jj * 8192, &tmB, full_bar + s, n0 + 64 * jj, r, gb);
+              for (int jj = 0; jj < BN / 64; ++jj)
+                tma_load_3d(sB + jj * 8192, &tmB, full_bar + s, n0 + 64 * jj, r, gb);
+            }
+          }
+          if (gather) {
+            __syncwarp();
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int pair = __ldg(p.sorted_ids + r + h * 32 + lane);
+              tok_s[h * 32 + lane] = pair < p.n_pairs ? pair / p.top_k : -1;
+            }
+            __syncwarp();
+            const int cpr = p.gather_a ? BM / 8 : BN / 8;        // 16-byte chunks per row
+            const int col0 = p.gather_a ? m0 : n0;
+            const int width = p.gather_a ? p.m_dim : p.n_dim;
+            const uint32_t dst0 = smem_u32(p.gather_a ? sA : sB);
+            for (int idx = lane; idx < BK * cpr; idx += 32) {
+              const int kr = idx / cpr, c = idx - kr * cpr;
+              const int tok = tok_s[kr];
+              const int col = col0 + c * 8;
+              const bool ok = tok >= 0 && col < width;
+              const __nv_bfloat16* src = ok ? p.gather_src + int64_t(tok) * width + col
+                                            : p.gather_src;
+              cp_async_16(dst0 + (c >> 3) * 8192 + kr * 128 + (((c & 7) ^ (kr & 7)) << 4), src,
+                          ok ? 16u : 0u);
+            }
+            cp_async_arrive(full_bar + s);
+          }
         }
       }
     }
@@ -200,6 +238,7 @@ __global__ void __launch_bounds__(WGRAD_THREADS, 1)
             break;
           }
           tc_fence_after();
+          if (gather) fence_proxy_async();  // cp.async wrote through the generic proxy
           const uint32_t sA = smem_u32(smem + s * L::STAGE_BYTES);
           issue_stage_mmas<BN, true, true>(sA, sA + A_STAGE_BYTES, d_tmem, kt == 0);
           umma_commit(empty_bar + s);
@@ -276,11 +315,8 @@ __global__ void __launch_bounds__(256)
     wgrad_reduce_kernel(const WgradArgs p, int tiles_x, int tiles_y) {
   __shared__ int first_item[WGRAD_MAX_GROUPS + 1];
   __shared__ int run_start[WGRAD_MAX_GROUPS + 1];
-  const int g = blockIdx.y;
   if (threadIdx.x < 32) wgrad_build_table(p, threadIdx.x, first_item, run_start);
   __syncthreads();
-  const int first = first_item[g], n_c = first_item[g + 1] - first;
-  if (n_c <= 1) return;
   const int tile_xy = blockIdx.x / WGRAD_REDUCE_SPLIT;
   const int slice = blockIdx.x % WGRAD_REDUCE_SPLIT;
   const int tile_m = tile_xy / tiles_y, n0 = (tile_xy % tiles_y) * BN;
@@ -288,23 +324,29 @@ __global__ void __launch_bounds__(256)
   constexpr int64_t slot_elems = int64_t(BM) * BN;
   constexpr int vecs = BM * BN / 4;                  // float4 per tile
   constexpr int per_slice = vecs / WGRAD_REDUCE_SPLIT;
-  for (int f = slice * per_slice + threadIdx.x; f < (slice + 1) * per_slice; f += blockDim.x) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int c2 = 0; c2 < n_c; ++c2) {
-      const float4 v = __ldcs(reinterpret_cast<const float4*>(
-                                  p.partials + ((int64_t(first) + c2) * tiles_xy + tile_xy) * slot_elems) + f);
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-    }
-    // partial layout [column chunk][row][32 floats]
-    const int cc = f / (BM * 8), row = (f / 8) % BM, i4 = f % 8;
-    const int m = tile_m * BM + row, n = n0 + cc * 32 + i4 * 4;
-    if (m < p.m_dim && n < p.n_dim) {
-      const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
-      const __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
-      uint2 w;
-      w.x = *reinterpret_cast<const uint32_t*>(&lo);
-      w.y = *reinterpret_cast<const uint32_t*>(&hi);
-      *reinterpret_cast<uint2*>(p.out + (int64_t(g) * p.m_dim + m) * int64_t(p.n_dim) + n) = w;
+  // the table is built once per CTA; the CTA then walks the runs that were actually split
+  for (int g = blockIdx.y; g < p.n_groups; g += gridDim.y) {
+    const int first = first_item[g], n_c = first_item[g + 1] - first;
+    if (n_c <= 1) continue;
+    for (int f = slice * per_slice + threadIdx.x; f < (slice + 1) * per_slice; f += blockDim.x) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int c2 = 0; c2 < n_c; ++c2) {
+        const float4 v = __ldcs(
+            reinterpret_cast<const float4*>(
+                p.partials + ((int64_t(first) + c2) * tiles_xy + tile_xy) * slot_elems) + f);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      // partial layout [column chunk][row][32 floats]
+      const int cc = f / (BM * 8), row = (f / 8) % BM, i4 = f % 8;
+      const int m = tile_m * BM + row, n = n0 + cc * 32 + i4 * 4;
+      if (m < p.m_dim && n < p.n_dim) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
+        uint2 w;
+        w.x = *reinterpret_cast<const uint32_t*>(&lo);
+        w.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p.out + (int64_t(g) * p.m_dim + m) * int64_t(p.n_dim) + n) = w;
+      }
     }
   }
 }

@@ -66,6 +66,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   return false;
 }
 
+// ------------------------------------------------------------- cp.async (gathered rows)
+// 16-byte global -> shared copy without registers; src_bytes = 0 writes 16 zero bytes instead.
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src),
+               "r"(src_bytes)
+               : "memory");
+}
+// Arrive on the mbarrier once all cp.async issued so far by this thread have landed; the arrival is
+// one of the barrier's expected count (noinc).
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
 // --------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

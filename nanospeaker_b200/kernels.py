@@ -155,19 +155,25 @@ def _stack(n_fixed: int, rows: int, width: int, like: torch.Tensor) -> torch.Ten
     return torch.empty(shape, dtype=like.dtype, device=like.device)
 
 
-def up_gemm(a, w_in, expert_ids, n_post_pad, n_fixed: int, act: int, want_raw: bool):
-    """a [rows, D] x w_in [G, D, 2H] -> (act(g)*u [rows, H], raw [g|u] [rows, 2H] | None).
-    n_fixed = S > 0 applies weight matrices 0..S-1 to all rows; outputs are then [S, rows, .]."""
+def up_gemm(a, w_in, expert_ids, n_post_pad, n_fixed: int, act: int, want_raw: bool,
+            gather=None):
+    """a x w_in [G, D, 2H] -> (act(g)*u [rows, H], raw [g|u] [rows, 2H] | None).
+    a is slot-ordered [rows, D]; or, with gather=(sorted_ids, top_k), the token-major x [T, D] whose
+    rows the kernel gathers itself (rows = len(sorted_ids)). n_fixed = S > 0 applies weight
+    matrices 0..S-1 to all rows of a; outputs are then [S, rows, .]."""
     _need_cuda(a, w_in)
-    rows, d = a.shape
+    d = a.shape[1]
+    sids, top_k = gather if gather is not None else (None, 0)
+    rows = sids.numel() if gather is not None else a.shape[0]
+    n_pairs = a.shape[0] * top_k
     g, _, h2 = w_in.shape
     h = h2 // 2
     hid = _stack(n_fixed, rows, h, a)
     raw = _stack(n_fixed, rows, h2, a) if want_raw else None
     _lib.check(_lib.load().moe_b200_up_gemm(
         a.data_ptr(), rows, d, w_in.data_ptr(), g, h, _lib.ptr(expert_ids), _lib.ptr(n_post_pad),
-        n_fixed, act, hid.data_ptr(), _lib.ptr(raw), status_word(a.device).data_ptr(),
-        _stream(a)), "moe_b200_up_gemm")
+        n_fixed, _lib.ptr(sids), top_k, n_pairs, act, hid.data_ptr(), _lib.ptr(raw),
+        status_word(a.device).data_ptr(), _stream(a)), "moe_b200_up_gemm")
     _count(1 if rows else 0)
     return hid, raw
 
@@ -189,18 +195,20 @@ def down_gemm(hid, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair
 
 
 def dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair_w,
-                    n_pairs: int, a1, act: int, want_dtw: bool):
-    """-> (da1 [.., rows, 2H], hidw [.., rows, H], dtw [n_pairs] | None)."""
+                    n_pairs: int, a1, act: int, want_dtw: bool, gather_top_k: int = 0):
+    """-> (da1 [.., rows, 2H], hidw [.., rows, H], dtw [n_pairs] | None). douts is slot-ordered
+    [rows, D], or with gather_top_k > 0 the token-major dOut [T, D] gathered through sorted_ids."""
     _need_cuda(douts, w_out, a1)
-    rows, d = douts.shape
+    d = douts.shape[1]
+    rows = sorted_ids.numel() if gather_top_k else douts.shape[0]
     g, h, _ = w_out.shape
     da1 = _stack(n_fixed, rows, 2 * h, douts)
     hidw = _stack(n_fixed, rows, h, douts)
     dtw = torch.empty(n_pairs, dtype=douts.dtype, device=douts.device) if want_dtw else None
     _lib.check(_lib.load().moe_b200_dhidden_glu_bwd(
         douts.data_ptr(), rows, d, w_out.data_ptr(), g, h, _lib.ptr(expert_ids),
-        _lib.ptr(n_post_pad), n_fixed, _lib.ptr(sorted_ids), _lib.ptr(pair_w), n_pairs,
-        a1.data_ptr(), act, da1.data_ptr(), hidw.data_ptr(), _lib.ptr(dtw),
+        _lib.ptr(n_post_pad), n_fixed, _lib.ptr(sorted_ids), gather_top_k, _lib.ptr(pair_w),
+        n_pairs, a1.data_ptr(), act, da1.data_ptr(), hidw.data_ptr(), _lib.ptr(dtw),
         status_word(douts.device).data_ptr(), _stream(douts)), "moe_b200_dhidden_glu_bwd")
     _count(1 if rows else 0)
     return da1, hidw, dtw
@@ -221,26 +229,35 @@ def dx_gemm(da1, w_in, expert_ids, n_post_pad, n_fixed: int) -> torch.Tensor:
 
 
 def wgrad(a, b, pad_offsets, n_groups: int, ks_rows: int = 0, a_grouped: bool = False,
-          b_grouped: bool = False) -> torch.Tensor:
+          b_grouped: bool = False, gather=None) -> torch.Tensor:
     """dw[e] = a_e^T @ b_e over run e's rows -> [G, Mdim, Ndim]. Routed schedule: a [rows, Mdim],
     b [rows, Ndim] in slot order plus pad_offsets. Fixed schedule (pad_offsets None): every group
     spans all rows; a / b are [G, rows, .] when *_grouped, else shared by the groups.
-    ks_rows = rows per split-K chunk (0: chosen by the library)."""
+    ks_rows = rows per split-K chunk (0: chosen by the library).
+    gather=("a" | "b", sorted_ids, top_k): that operand is token-major [T, .] and gathered inside
+    the kernel (routed schedule only)."""
     _need_cuda(a, b)
     import ctypes
-    rows, m_dim = a.shape[-2:]
-    n_dim = b.shape[-1]
+    which, sids, top_k = 0, None, 0
+    if gather is not None:
+        which = 1 if gather[0] == "a" else 2
+        sids, top_k = gather[1], gather[2]
+    slot_op = b if which == 1 else a
+    rows = slot_op.shape[-2]
+    m_dim, n_dim = a.shape[-1], b.shape[-1]
+    n_pairs = (a if which == 1 else b).shape[0] * top_k if which else 0
     routed = pad_offsets is not None
     lib = _lib.load()
     pb = ctypes.c_size_t(0)
     _lib.check(lib.moe_b200_wgrad_scratch_bytes(m_dim, n_dim, rows, n_groups, int(routed),
                                                 ks_rows, ctypes.byref(pb)),
                "moe_b200_wgrad_scratch_bytes")
-    partials = torch.empty(max(pb.value, 16), dtype=torch.uint8, device=a.device)
+    partials = torch.empty(max(pb.value, 32), dtype=torch.uint8, device=a.device)
     dw = torch.empty((n_groups, m_dim, n_dim), dtype=a.dtype, device=a.device)
     _lib.check(lib.moe_b200_wgrad(
         a.data_ptr(), int(a_grouped), m_dim, b.data_ptr(), int(b_grouped), n_dim, rows,
-        _lib.ptr(pad_offsets), n_groups, ks_rows, dw.data_ptr(), partials.data_ptr(), pb.value,
-        status_word(a.device).data_ptr(), _stream(a)), "moe_b200_wgrad")
+        _lib.ptr(pad_offsets), n_groups, ks_rows, _lib.ptr(sids), top_k, n_pairs, which,
+        dw.data_ptr(), partials.data_ptr(), pb.value, status_word(a.device).data_ptr(),
+        _stream(a)), "moe_b200_wgrad")
     _count(2 if rows > (ks_rows or 256) else 1)
     return dw

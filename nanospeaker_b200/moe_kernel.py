@@ -149,18 +149,19 @@ def moe_experts(
     inv_ids: torch.Tensor,
     activation: str,
     save_for_backward: bool,
-) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """out[t] = sum_j topk_w[t,j] * expert_{idx[t,j]}(x[t])  (+ sum_s shared_s(x[t])).
 
-    permute -> up/gate GEMM with fused GLU -> down GEMM with fused router weight -> token-major
-    fp32 combine; the shared experts run through the same GEMM kernels on the unpermuted tokens
-    and join in the combine. All tensors share x's dtype (the wrapper casts).
+    up/gate GEMM (token rows gathered inside the kernel, GLU fused) -> down GEMM with fused router
+    weight -> token-major fp32 combine; the shared experts run through the same GEMM kernels on
+    the unpermuted tokens and join in the combine. No permuted copy of x is materialised. All
+    tensors share x's dtype (the wrapper casts).
 
-    Returns (out, xs, a1, a1_sh). xs [l_cap, D] is the permuted input; with save_for_backward the
-    up GEMM also stores its pre-activations a1 [l_cap, 2H] (routed) and a1_sh [S, T, 2H] (shared)
-    so the backward does not recompute them -- 180 GB of HBM make keeping ~180 MB per block the
-    cheaper side of the trade the reference settles the other way on a 4 GB card
-    (src/model/moe_kernel.py:663-664). Without it they are empty.
+    Returns (out, a1, a1_sh). With save_for_backward the up GEMM also stores its pre-activations
+    a1 [l_cap, 2H] (routed) and a1_sh [S, T, 2H] (shared) so the backward does not recompute them
+    -- 180 GB of HBM make keeping ~70 MB per block the cheaper side of the trade the reference
+    settles the other way on a 4 GB card (src/model/moe_kernel.py:663-664). Without it they are
+    empty.
     """
     x, w_in, w_out = x.contiguous(), w_in.contiguous(), w_out.contiguous()
     _check_inputs(x, w_in, w_out, w_sh_in)
@@ -169,11 +170,11 @@ def moe_experts(
     topk = topk_w.shape[-1]
     m = n * topk
     if n == 0:
-        return x.new_zeros((0, d)), x.new_empty(0), x.new_empty(0), x.new_empty(0)
+        return x.new_zeros((0, d)), x.new_empty(0), x.new_empty(0)
     tw = topk_w.reshape(-1).contiguous()
 
-    xs = K.permute(x, topk, sorted_ids, n_post_pad)
-    hid, a1 = K.up_gemm(xs, w_in, expert_ids, n_post_pad, 0, act, save_for_backward)
+    hid, a1 = K.up_gemm(x, w_in, expert_ids, n_post_pad, 0, act, save_for_backward,
+                        gather=(sorted_ids, topk))
     y = K.down_gemm(hid, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m)
     extras: List[Optional[torch.Tensor]] = [None, None]
     a1_sh = None
@@ -185,7 +186,7 @@ def moe_experts(
         for s in range(s_n):
             extras[s] = ys[s]
     out = K.combine(y, inv_ids, n, topk, extras[0], extras[1])
-    return (out, xs, a1 if a1 is not None else x.new_empty(0),
+    return (out, a1 if a1 is not None else x.new_empty(0),
             a1_sh if a1_sh is not None else x.new_empty(0))
 
 
@@ -196,18 +197,17 @@ def _(x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_off
     cap = sorted_ids.shape[0]
     h2 = w_in.shape[2]
     if n == 0:
-        return x.new_empty((0, d)), x.new_empty(0), x.new_empty(0), x.new_empty(0)
+        return x.new_empty((0, d)), x.new_empty(0), x.new_empty(0)
     a1 = x.new_empty((cap, h2)) if save_for_backward else x.new_empty(0)
     a1_sh = (x.new_empty((w_sh_in.shape[0], n, h2))
              if save_for_backward and w_sh_in is not None else x.new_empty(0))
-    return x.new_empty(x.shape), x.new_empty((cap, d)), a1, a1_sh
+    return x.new_empty(x.shape), a1, a1_sh
 
 
 @torch.library.custom_op("moe_b200::moe_experts_bwd", mutates_args=())
 def moe_experts_bwd(
     grad_out: torch.Tensor,
     x: torch.Tensor,
-    xs: torch.Tensor,
     a1: torch.Tensor,
     a1_sh: torch.Tensor,
     w_in: torch.Tensor,
@@ -224,7 +224,8 @@ def moe_experts_bwd(
     activation: str,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """(dx, dW_in, dW_out, dtopk_w, dW_sh_in, dW_sh_out); the last two are empty without shared
-    experts. xs / a1 / a1_sh are the tensors the forward kept."""
+    experts. a1 / a1_sh are the pre-activations the forward kept; rows of x and grad_out are
+    gathered inside the kernels that need them in slot order."""
     grad_out = grad_out.to(x.dtype).contiguous()
     x, w_in, w_out = x.contiguous(), w_in.contiguous(), w_out.contiguous()
     _check_inputs(x, w_in, w_out, w_sh_in)
@@ -235,12 +236,11 @@ def moe_experts_bwd(
     m = n * topk
     tw = topk_w.reshape(-1).contiguous()
 
-    douts = K.permute(grad_out, topk, sorted_ids, n_post_pad)
-    da1, hidw, dtw = K.dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m,
-                                       a1, act, True)
+    da1, hidw, dtw = K.dhidden_glu_bwd(grad_out, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw,
+                                       m, a1, act, True, gather_top_k=topk)
     ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0)
-    dw_in = K.wgrad(xs, da1, pad_offsets, e_n)
-    dw_out = K.wgrad(hidw, douts, pad_offsets, e_n)
+    dw_in = K.wgrad(x, da1, pad_offsets, e_n, gather=("a", sorted_ids, topk))
+    dw_out = K.wgrad(hidw, grad_out, pad_offsets, e_n, gather=("b", sorted_ids, topk))
 
     extras: List[Optional[torch.Tensor]] = [None, None]
     dw_sh_in = x.new_empty(0)
@@ -260,7 +260,7 @@ def moe_experts_bwd(
 
 
 @moe_experts_bwd.register_fake
-def _(grad_out, x, xs, a1, a1_sh, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
+def _(grad_out, x, a1, a1_sh, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
       pad_offsets, counts, n_post_pad, inv_ids, activation):
     return (torch.empty_like(x), torch.empty_like(w_in), torch.empty_like(w_out),
             torch.empty_like(topk_w),
@@ -271,15 +271,15 @@ def _(grad_out, x, xs, a1, a1_sh, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted
 def _experts_setup(ctx, inputs, output):
     (x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
      n_post_pad, inv_ids, activation, save_for_backward) = inputs
-    out, xs, a1, a1_sh = output
-    ctx.mark_non_differentiable(xs, a1, a1_sh)
+    out, a1, a1_sh = output
+    ctx.mark_non_differentiable(a1, a1_sh)
     # without this autograd would hand the backward zero-filled gradients for the three kept
     # buffers (hundreds of MB of memset per step)
     ctx.set_materialize_grads(False)
     if not save_for_backward:
         raise RuntimeError("moe_experts was run with save_for_backward=False but a gradient is "
                            "being recorded; call it through fused_moe_forward")
-    saved = [x, xs, a1, a1_sh, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts,
+    saved = [x, a1, a1_sh, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts,
              n_post_pad, inv_ids]
     ctx.has_shared = w_sh_in is not None
     if ctx.has_shared:
@@ -288,14 +288,14 @@ def _experts_setup(ctx, inputs, output):
     ctx.activation = activation
 
 
-def _experts_backward(ctx, grad_out, g_xs, g_a1, g_a1_sh):
-    (x, xs, a1, a1_sh, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts,
+def _experts_backward(ctx, grad_out, g_a1, g_a1_sh):
+    (x, a1, a1_sh, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts,
      n_post_pad, inv_ids, *rest) = ctx.saved_tensors
     w_sh_in, w_sh_out = (rest[0], rest[1]) if ctx.has_shared else (None, None)
     if grad_out is None:
         grad_out = torch.zeros_like(x)
     dx, dw_in, dw_out, dtw, dsi, dso = moe_experts_bwd(
-        grad_out, x, xs, a1, a1_sh, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids,
+        grad_out, x, a1, a1_sh, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids,
         expert_ids, pad_offsets, counts, n_post_pad, inv_ids, ctx.activation)
     return (dx, dw_in, dw_out, dtw, dsi if ctx.has_shared else None,
             dso if ctx.has_shared else None, None, None, None, None, None, None, None, None)
@@ -323,7 +323,7 @@ def fused_moe_forward(x, w_in, w_out, topk_w, topk_idx, b_in, b_out, activation,
     cast = lambda t: None if t is None else t.to(x.dtype)
     tensors = (x, w_in, w_out, topk_w, w_sh_in, w_sh_out)
     save = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
-    out, _, _, _ = moe_experts(x, cast(w_in), cast(w_out), topk_w.to(x.dtype), cast(w_sh_in),
+    out, _, _ = moe_experts(x, cast(w_in), cast(w_out), topk_w.to(x.dtype), cast(w_sh_in),
                                cast(w_sh_out), sids, eids, offs, counts, npp, inv, activation,
                                save)
     return out, counts

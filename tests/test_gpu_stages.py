@@ -82,8 +82,11 @@ def test_forward_gemm_stages(T, E, k, D, skew):
     xs = torch.zeros(sids.numel(), D, dtype=torch.bfloat16)
     xs[:nl] = xs_ref
     a1_ref = _per_expert(xs_ref, w_in, offs)
-    _, a1 = K().up_gemm(g(xs), g(w_in), g(eids), g(npp), 0, 0, True)
+    hid0, a1 = K().up_gemm(g(xs), g(w_in), g(eids), g(npp), 0, 0, True)
     assert rel_l2(a1.cpu()[:nl], a1_ref) < TOL
+    # rows gathered inside the kernel (no permuted copy) give the same bits as the permuted input
+    hid_g, a1_g = K().up_gemm(g(x), g(w_in), g(eids), g(npp), 0, 0, True, gather=(g(sids), k))
+    assert torch.equal(hid_g[:nl], hid0[:nl]) and torch.equal(a1_g[:nl], a1[:nl])
     for name, act in [("silu", 0), ("gelu", 1), ("relu", 2), ("sigmoid", 3), ("tanh", 4)]:
         hid, raw = K().up_gemm(g(xs), g(w_in), g(eids), g(npp), 0, act, False)
         assert raw is None
@@ -118,6 +121,10 @@ def test_backward_gemm_stages(T, E, k, D, skew):
 
     da1, hidw, dtw = K().dhidden_glu_bwd(g(pad(douts_ref, D)), g(w_out), g(eids), g(npp), 0,
                                          g(sids), g(twf), M, g(a1_b), 0, True)
+    da1_g, hidw_g, dtw_g = K().dhidden_glu_bwd(g(dout), g(w_out), g(eids), g(npp), 0, g(sids),
+                                               g(twf), M, g(a1_b), 0, True, gather_top_k=k)
+    assert torch.equal(da1_g[:nl], da1[:nl]) and torch.equal(hidw_g[:nl], hidw[:nl])
+    assert torch.equal(dtw_g, dtw)
     G = _per_expert(douts_ref, w_out, offs, transpose=True)
     gate, up = a1_b[:nl].float().chunk(2, -1)
     sg = torch.sigmoid(gate)
@@ -136,6 +143,10 @@ def test_backward_gemm_stages(T, E, k, D, skew):
     xs_b = pad(xs_ref, D)
     dw_in = K().wgrad(g(xs_b), g(da1_in), g(offs), E).cpu()
     dw_out = K().wgrad(g(pad((act * up).bfloat16(), H)), g(pad(douts_ref, D)), g(offs), E).cpu()
+    dw_in_g = K().wgrad(g(x), g(da1_in), g(offs), E, gather=("a", g(sids), k)).cpu()
+    dw_out_g = K().wgrad(g(pad((act * up).bfloat16(), H)), g(dout), g(offs), E,
+                         gather=("b", g(sids), k)).cpu()
+    assert torch.equal(dw_in_g, dw_in) and torch.equal(dw_out_g, dw_out)
     for e in range(E):
         lo, hi = int(offs[e]), int(offs[e + 1])
         if hi == lo:
