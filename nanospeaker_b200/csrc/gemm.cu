@@ -111,7 +111,7 @@ static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const Row
   if (attr_err != cudaSuccess) return MOE_B200_ERR_CUDA;
   const int64_t sms = sm_count();
   const unsigned grid = unsigned(max_tiles < sms ? max_tiles : sms);
-  kern<<<grid, ROWS_THREADS, smem, st>>>(tmA, tmB, args);
+  kern<<<grid, GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS, smem, st>>>(tmA, tmB, args);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
@@ -128,7 +128,8 @@ static int launch_wgrad(const CUtensorMap& tmA, const CUtensorMap& tmB, const Wg
   if (attr_err != cudaSuccess) return MOE_B200_ERR_CUDA;
   const int64_t tiles = max_items * tiles_x * tiles_y, sms = sm_count();
   const unsigned grid = unsigned(tiles < sms ? tiles : sms);
-  kern<<<grid, WGRAD_THREADS, smem, st>>>(tmA, tmB, args, tiles_x, tiles_y);
+  const int threads = (args.gather_a || args.gather_b) ? WGRAD_THREADS_GATHER : WGRAD_THREADS;
+  kern<<<grid, threads, smem, st>>>(tmA, tmB, args, tiles_x, tiles_y);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 

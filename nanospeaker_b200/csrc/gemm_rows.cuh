@@ -6,6 +6,10 @@ namespace moe {
 
 constexpr int ROWS_THREADS = 320;
 constexpr int EPI_WARPS = 8;
+// A gathered with cp.async needs many loads in flight, and a warp only keeps a few outstanding:
+// three more producer warps (10..12) join warp 0, each copying 32 of a stage's 128 rows.
+constexpr int GATHER_WARPS = 4;
+constexpr int ROWS_THREADS_GATHER = ROWS_THREADS + (GATHER_WARPS - 1) * 32;
 
 template <int BN, int STAGES>
 struct RowsSmem {
@@ -97,7 +101,7 @@ __device__ __forceinline__ float epilogue_glubwd(uint32_t taddr, int c_lo, int c
 }
 
 template <int BN, int STAGES, bool B_MN, int EPI, bool GATHER_A>
-__global__ void __launch_bounds__(ROWS_THREADS, 1)
+__global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS, 1)
     rows_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB, const RowsArgs p) {
   using L = RowsSmem<BN, STAGES>;
@@ -131,7 +135,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1)
     tma_prefetch_desc(&tmB);
     for (int s = 0; s < STAGES; ++s) {
       // gathered A: every lane of warp 0 arrives (through its cp.async) next to the TMA transaction
-      mbar_init(full_bar + s, GATHER_A ? 33 : 1);
+      mbar_init(full_bar + s, GATHER_A ? GATHER_WARPS * 32 + 1 : 1);
       mbar_init(empty_bar + s, 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -150,22 +154,19 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0 && GATHER_A) {
-    // ------------------------------------------- producer, gathered A: the whole warp copies rows
-    // Lane (r4 = lane / 8, c = lane % 8) moves 16-byte chunk c of tile rows r4, r4 + 4, ...: eight
-    // lanes cover one row's 128-byte k slice, so global reads are whole lines. The chunk lands at
-    // (c ^ (row & 7)), which is the 128-byte swizzle the UMMA descriptor expects.
+  if (GATHER_A && (warp == 0 || warp >= 2 + EPI_WARPS)) {
+    // --------------------------------- producers, gathered A: four warps copy 32 rows each
+    // Lane (r4 = lane / 8, c = lane % 8) moves 16-byte chunk c of rows r4, r4 + 4, ... of its
+    // warp's 32 rows: eight lanes cover one row's 128-byte k slice, so global reads are whole
+    // lines. The chunk lands at (c ^ (row & 7)), the 128-byte swizzle the UMMA descriptor expects.
+    // Warp 0's lane 0 also issues the TMA loads of B.
+    const int gw = warp == 0 ? 0 : warp - (1 + EPI_WARPS);
     uint32_t it = 0;
     const int r4 = lane >> 3, c = lane & 7;
     for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
       const TileCoord tc = decode_tile(p, t, m_tiles, BN);
-      __syncwarp();
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int pair = __ldg(p.sorted_ids + int64_t(tc.m_tile) * BM + i * 32 + lane);
-        tok_s[i * 32 + lane] = pair < p.n_pairs ? pair / p.top_k : -1;
-      }
-      __syncwarp();
+      const int pair = __ldg(p.sorted_ids + int64_t(tc.m_tile) * BM + gw * 32 + lane);
+      const int my_tok = pair < p.n_pairs ? pair / p.top_k : -1;  // token of row gw*32 + lane
       for (int kt = 0; kt < p.num_k; ++kt, ++it) {
         const int s = it % STAGES;
         const uint32_t use = it / STAGES;
@@ -177,7 +178,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1)
         uint8_t* sA = smem + s * L::STAGE_BYTES;
         uint8_t* sB = sA + A_STAGE_BYTES;
         const int k0 = kt * BK;
-        if (lane == 0) {
+        if (warp == 0 && lane == 0) {
           mbar_expect_tx(full_bar + s, L::B_STAGE_BYTES);
           if constexpr (B_MN) {
 #pragma unroll
@@ -190,10 +191,11 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1)
         const int col = k0 + c * 8;
         const bool col_ok = col < p.a_cols;
         const uint32_t sA_u = smem_u32(sA);
-#pragma unroll 8
-        for (int i = 0; i < 32; ++i) {
-          const int row = i * 4 + r4;
-          const int tok = tok_s[row];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int lrow = i * 4 + r4;
+          const int tok = __shfl_sync(0xffffffffu, my_tok, lrow);
+          const int row = gw * 32 + lrow;
           const bool ok = tok >= 0 && col_ok;
           const __nv_bfloat16* src = ok ? p.a_src + int64_t(tok) * p.a_cols + col : p.a_src;
           cp_async_16(sA_u + row * 128 + ((c ^ (row & 7)) << 4), src, ok ? 16u : 0u);
@@ -261,7 +263,7 @@ __global__ void __launch_bounds__(ROWS_THREADS, 1)
         umma_commit(tfull_bar + b);
       }
     }
-  } else {
+  } else if (warp < 2 + EPI_WARPS) {
     // ---------------------------------------------------------------------- epilogue
     const int ew = warp - 2;
     const int q = warp & 3;   // TMEM lane quadrant this warp may read

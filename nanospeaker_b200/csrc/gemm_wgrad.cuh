@@ -12,6 +12,7 @@
 namespace moe {
 
 constexpr int WGRAD_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+constexpr int WGRAD_THREADS_GATHER = 320 + (GATHER_WARPS - 1) * 32;  // + producer warps 10..12
 constexpr int WGRAD_MAX_GROUPS = 256;
 
 template <int BN, int STAGES>
@@ -97,7 +98,7 @@ __device__ __forceinline__ WgradItem wgrad_item(const WgradArgs& p, const int* f
 // Persistent: one CTA per SM walks the list of (work item, m tile, n chunk); the accumulator is
 // double-buffered in TMEM so a tile's store overlaps the next tile's loads and MMAs.
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(WGRAD_THREADS, 1)
+__global__ void __launch_bounds__(WGRAD_THREADS_GATHER, 1)
     wgrad_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                       const __grid_constant__ CUtensorMap tmB, const WgradArgs p, int tiles_x,
                       int tiles_y) {
@@ -117,7 +118,6 @@ __global__ void __launch_bounds__(WGRAD_THREADS, 1)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* first_item = reinterpret_cast<int*>(smem + L::TABLE_OFFSET);
   int* run_start = first_item + WGRAD_MAX_GROUPS + 1;
-  int* tok_s = reinterpret_cast<int*>(smem + L::TOK_OFFSET);
   const bool gather = p.gather_a || p.gather_b;
 
   const int warp = threadIdx.x >> 5;
@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(WGRAD_THREADS, 1)
     tma_prefetch_desc(&tmB);
     for (int s = 0; s < STAGES; ++s) {
       // a gathered operand: every lane of warp 0 arrives (through its cp.async) next to the TMA
-      mbar_init(full_bar + s, gather ? 33 : 1);
+      mbar_init(full_bar + s, gather ? GATHER_WARPS * 32 + 1 : 1);
       mbar_init(empty_bar + s, 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -150,11 +150,13 @@ __global__ void __launch_bounds__(WGRAD_THREADS, 1)
   const int tiles_xy = tiles_x * tiles_y;
   const int total = first_item[p.n_groups] * tiles_xy;  // t = item * tiles_xy + tile
 
-  if (warp == 0) {
-    // Producer. Plain operands arrive by TMA (lane 0). A gathered operand is copied by the whole
-    // warp with 16-byte cp.async: row `slot` of the stage is row sorted_ids[slot] / top_k of the
-    // token-major source, and 64-column groups land as the same swizzled 64 x 64 boxes TMA makes.
-    if (gather || lane == 0) {
+  if (warp == 0 || warp >= 2 + EPI_WARPS) {
+    // Producers. Plain operands arrive by TMA (warp 0, lane 0). A gathered operand is copied with
+    // 16-byte cp.async by four warps (0 and 10..12; a warp only keeps a few loads in flight), 16 of
+    // the stage's 64 rows each: row `slot` is row sorted_ids[slot] / top_k of the token-major
+    // source, and 64-column groups land as the same swizzled 64 x 64 boxes TMA makes.
+    const int gw = warp == 0 ? 0 : warp - (1 + EPI_WARPS);
+    if (gather || (warp == 0 && lane == 0)) {
       uint32_t it = 0;
       for (int t = blockIdx.x; t < total && !*abort_flag; t += gridDim.x) {
         const WgradItem w = wgrad_item(p, first_item, run_start, t / tiles_xy);
@@ -172,7 +174,7 @@ __global__ void __launch_bounds__(WGRAD_THREADS, 1)
           uint8_t* sA = smem + s * L::STAGE_BYTES;
           uint8_t* sB = sA + A_STAGE_BYTES;
           const int r = w.row0 + kt * BK;
-          if (lane == 0) {
+          if (warp == 0 && lane == 0) {
             mbar_expect_tx(full_bar + s, (p.gather_a ? 0 : A_STAGE_BYTES) +
                                              (p.gather_b ? 0 : L::B_STAGE_BYTES));
             if (!p.gather_a) {
@@ -187,20 +189,20 @@ __global__ void __launch_bounds__(WGRAD_THREADS, 1)
             }
           }
           if (gather) {
-            __syncwarp();
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int pair = __ldg(p.sorted_ids + r + h * 32 + lane);
-              tok_s[h * 32 + lane] = pair < p.n_pairs ? pair / p.top_k : -1;
+            constexpr int ROWS_PER_WARP = BK / GATHER_WARPS;  // 16
+            int my_tok = -1;                                  // token of row gw*16 + lane
+            if (lane < ROWS_PER_WARP) {
+              const int pair = __ldg(p.sorted_ids + r + gw * ROWS_PER_WARP + lane);
+              my_tok = pair < p.n_pairs ? pair / p.top_k : -1;
             }
-            __syncwarp();
-            const int cpr = p.gather_a ? BM / 8 : BN / 8;        // 16-byte chunks per row
+            const int cpr = p.gather_a ? BM / 8 : BN / 8;     // 16-byte chunks per row
             const int col0 = p.gather_a ? m0 : n0;
             const int width = p.gather_a ? p.m_dim : p.n_dim;
             const uint32_t dst0 = smem_u32(p.gather_a ? sA : sB);
-            for (int idx = lane; idx < BK * cpr; idx += 32) {
-              const int kr = idx / cpr, c = idx - kr * cpr;
-              const int tok = tok_s[kr];
+            for (int idx = lane; idx < ROWS_PER_WARP * cpr; idx += 32) {
+              const int lr = idx / cpr, c = idx - lr * cpr;
+              const int tok = __shfl_sync(0xffffffffu, my_tok, lr);
+              const int kr = gw * ROWS_PER_WARP + lr;
               const int col = col0 + c * 8;
               const bool ok = tok >= 0 && col < width;
               const __nv_bfloat16* src = ok ? p.gather_src + int64_t(tok) * width + col
@@ -246,7 +248,7 @@ __global__ void __launch_bounds__(WGRAD_THREADS, 1)
         umma_commit(tfull_bar + b);
       }
     }
-  } else {
+  } else if (warp < 2 + EPI_WARPS) {
     const int ew = warp - 2;
     const int q = warp & 3;
     const int half = ew >> 2;
