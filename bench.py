@@ -215,6 +215,7 @@ def build_stages(m, x):
         copies = lambda t: [t.clone() for _ in range(3)]
         S = N_SHARED
         xr = copies(x)
+        xs = copies(K.permute(x, k, sids, npp))
         hid0, a1 = K.up_gemm(x, m.W_in, eids, npp, 0, 0, True, gather=(sids, k))
         hid = copies(hid0)
         y = copies(K.down_gemm(hid[0], m.W_out, eids, npp, 0, sids, tw, M))
@@ -254,6 +255,10 @@ def build_stages(m, x):
              lambda i: K.wgrad(xr[i % 3], da1[i % 3], offs, E, gather=("a", sids, k))),
             ("wgrad_out (gather)", TF, 2.0 * M * H * D, 1,
              lambda i: K.wgrad(hid[i % 3], xr[i % 3], offs, E, gather=("b", sids, k))),
+            ("wgrad_in (slot-ordered operands)", TF, 2.0 * M * D * 2 * H, 0,
+             lambda i: K.wgrad(xs[i % 3], da1[i % 3], offs, E)),
+            ("wgrad_out (slot-ordered operands)", TF, 2.0 * M * H * D, 0,
+             lambda i: K.wgrad(hid[i % 3], xs[i % 3], offs, E)),
             ("shared up_gemm+glu", TF, 2.0 * S * T * D * 2 * H, 1,
              lambda i: K.up_gemm(xr[i % 3], m.W_sh_in, None, None, S, 0, True)),
             ("shared down_gemm", TF, 2.0 * S * T * H * D, 1,

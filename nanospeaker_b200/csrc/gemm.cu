@@ -115,10 +115,10 @@ static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const Row
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
-template <int BN, int STAGES>
-static int launch_wgrad(const CUtensorMap& tmA, const CUtensorMap& tmB, const WgradArgs& args,
+template <int BN, int STAGES, int GATHER>
+static int launch_wgrad_g(const CUtensorMap& tmA, const CUtensorMap& tmB, const WgradArgs& args,
                         int tiles_x, int tiles_y, int64_t max_items, cudaStream_t st) {
-  auto kern = wgrad_gemm_kernel<BN, STAGES>;
+  auto kern = wgrad_gemm_kernel<BN, STAGES, GATHER>;
   constexpr int smem = WgradSmem<BN, STAGES>::DYNAMIC;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
@@ -128,9 +128,19 @@ static int launch_wgrad(const CUtensorMap& tmA, const CUtensorMap& tmB, const Wg
   if (attr_err != cudaSuccess) return MOE_B200_ERR_CUDA;
   const int64_t tiles = max_items * tiles_x * tiles_y, sms = sm_count();
   const unsigned grid = unsigned(tiles < sms ? tiles : sms);
-  const int threads = (args.gather_a || args.gather_b) ? WGRAD_THREADS_GATHER : WGRAD_THREADS;
+  const int threads = GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS;
   kern<<<grid, threads, smem, st>>>(tmA, tmB, args, tiles_x, tiles_y);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+template <int BN, int STAGES>
+static int launch_wgrad(const CUtensorMap& tmA, const CUtensorMap& tmB, const WgradArgs& args,
+                        int tiles_x, int tiles_y, int64_t max_items, cudaStream_t st) {
+  if (args.gather_a)
+    return launch_wgrad_g<BN, STAGES, 1>(tmA, tmB, args, tiles_x, tiles_y, max_items, st);
+  if (args.gather_b)
+    return launch_wgrad_g<BN, STAGES, 2>(tmA, tmB, args, tiles_x, tiles_y, max_items, st);
+  return launch_wgrad_g<BN, STAGES, 0>(tmA, tmB, args, tiles_x, tiles_y, max_items, st);
 }
 
 // inputs feed TMA (16 bytes); outputs are written with 32-byte vectors

@@ -97,8 +97,8 @@ __device__ __forceinline__ WgradItem wgrad_item(const WgradArgs& p, const int* f
 
 // Persistent: one CTA per SM walks the list of (work item, m tile, n chunk); the accumulator is
 // double-buffered in TMEM so a tile's store overlaps the next tile's loads and MMAs.
-template <int BN, int STAGES>
-__global__ void __launch_bounds__(WGRAD_THREADS_GATHER, 1)
+template <int BN, int STAGES, int GATHER>  // GATHER: 0 none, 1 = A gathered, 2 = B gathered
+__global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS, 1)
     wgrad_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                       const __grid_constant__ CUtensorMap tmB, const WgradArgs p, int tiles_x,
                       int tiles_y) {
@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(WGRAD_THREADS_GATHER, 1)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* first_item = reinterpret_cast<int*>(smem + L::TABLE_OFFSET);
   int* run_start = first_item + WGRAD_MAX_GROUPS + 1;
-  const bool gather = p.gather_a || p.gather_b;
+  constexpr bool gather = GATHER != 0;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -163,9 +163,23 @@ __global__ void __launch_bounds__(WGRAD_THREADS_GATHER, 1)
         const int txy = t % tiles_xy;
         const int m0 = (txy / tiles_y) * BM, n0 = (txy % tiles_y) * BN;
         const int ga = p.a_grouped ? w.group : 0, gb = p.b_grouped ? w.group : 0;
+        constexpr int ROWS_PER_WARP = BK / GATHER_WARPS;  // 16 rows of a stage per producer warp
+        // token of row gw*16 + lane of the NEXT stage, fetched one stage ahead of its use
+        int next_tok = -1;
+        auto fetch_tok = [&](int kt) {
+          int tok = -1;
+          if (gather && lane < ROWS_PER_WARP && kt < w.num_k) {
+            const int pair = __ldg(p.sorted_ids + w.row0 + kt * BK + gw * ROWS_PER_WARP + lane);
+            tok = pair < p.n_pairs ? pair / p.top_k : -1;
+          }
+          return tok;
+        };
+        next_tok = fetch_tok(0);
         for (int kt = 0; kt < w.num_k; ++kt, ++it) {
           const int s = it % STAGES;
           const uint32_t use = it / STAGES;
+          const int my_tok = next_tok;
+          next_tok = fetch_tok(kt + 1);
           if (use > 0 && !mbar_wait(empty_bar + s, (use - 1) & 1, p.status)) {
             *abort_flag = 1;
             atomicExch(p.status, ST_WAIT_TIMEOUT);
@@ -175,30 +189,25 @@ __global__ void __launch_bounds__(WGRAD_THREADS_GATHER, 1)
           uint8_t* sB = sA + A_STAGE_BYTES;
           const int r = w.row0 + kt * BK;
           if (warp == 0 && lane == 0) {
-            mbar_expect_tx(full_bar + s, (p.gather_a ? 0 : A_STAGE_BYTES) +
-                                             (p.gather_b ? 0 : L::B_STAGE_BYTES));
-            if (!p.gather_a) {
+            mbar_expect_tx(full_bar + s, (GATHER == 1 ? 0 : A_STAGE_BYTES) +
+                                             (GATHER == 2 ? 0 : L::B_STAGE_BYTES));
+            if (GATHER != 1) {
 #pragma unroll
               for (int i = 0; i < BM / 64; ++i)
                 tma_load_3d(sA + i * 8192, &tmA, full_bar + s, m0 + 64 * i, r, ga);
             }
-            if (!p.gather_b) {
+            if (GATHER != 2) {
 #pragma unroll
               for (int jj = 0; jj < BN / 64; ++jj)
                 tma_load_3d(sB + jj * 8192, &tmB, full_bar + s, n0 + 64 * jj, r, gb);
             }
           }
           if (gather) {
-            constexpr int ROWS_PER_WARP = BK / GATHER_WARPS;  // 16
-            int my_tok = -1;                                  // token of row gw*16 + lane
-            if (lane < ROWS_PER_WARP) {
-              const int pair = __ldg(p.sorted_ids + r + gw * ROWS_PER_WARP + lane);
-              my_tok = pair < p.n_pairs ? pair / p.top_k : -1;
-            }
-            const int cpr = p.gather_a ? BM / 8 : BN / 8;     // 16-byte chunks per row
-            const int col0 = p.gather_a ? m0 : n0;
-            const int width = p.gather_a ? p.m_dim : p.n_dim;
-            const uint32_t dst0 = smem_u32(p.gather_a ? sA : sB);
+            constexpr int cpr = GATHER == 1 ? BM / 8 : BN / 8;  // 16-byte chunks per row
+            const int col0 = GATHER == 1 ? m0 : n0;
+            const int width = GATHER == 1 ? p.m_dim : p.n_dim;
+            const uint32_t dst0 = smem_u32(GATHER == 1 ? sA : sB);
+#pragma unroll
             for (int idx = lane; idx < ROWS_PER_WARP * cpr; idx += 32) {
               const int lr = idx / cpr, c = idx - lr * cpr;
               const int tok = __shfl_sync(0xffffffffu, my_tok, lr);
