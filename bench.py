@@ -205,73 +205,60 @@ def build_stages(m, x):
     """Every kernel of the step as a standalone callable with its algorithmic work per launch.
     Operands are rotated through 3 buffer copies so a launch does not find its input in L2."""
     from nanospeaker_b200 import kernels as K
-    T, D, H, E, k = x.shape[0], D_MODEL, D_HIDDEN, N_EXPERTS, TOP_K
-    M = T * k
+    T, D, H, E, k, S = x.shape[0], D_MODEL, D_HIDDEN, N_EXPERTS, TOP_K, N_SHARED
     with torch.no_grad():
         w, idx, _ = m.router(x)
-        sids, eids, offs, counts, npp, inv = K.dispatch(idx, E)
-        tw = w.reshape(-1).contiguous()
         logits = (x @ m.router.W).float() + m.router.logit_bias
+        # the block dispatches the shared experts as experts E..E+S-1 that every token visits
+        ids = torch.arange(E, E + S, device=x.device)
+        idx_all = torch.cat([idx, ids.expand(T, S)], 1)
+        w_all = torch.cat([w, w.new_ones((T, S))], 1)
+        ka, Ea = k + S, E + S
+        M = T * ka
+        sids, eids, offs, counts, npp, inv = K.dispatch(idx_all, Ea)
+        tw = w_all.reshape(-1).contiguous()
         copies = lambda t: [t.clone() for _ in range(3)]
-        S = N_SHARED
         xr = copies(x)
-        xs = copies(K.permute(x, k, sids, npp))
-        hid0, a1 = K.up_gemm(x, m.W_in, eids, npp, 0, 0, True, gather=(sids, k))
+        gather = (sids, ka)
+        hid0, a1 = K.up_gemm(x, m.W_in, eids, npp, 0, 0, True, gather=gather, w_extra=m.W_sh_in)
         hid = copies(hid0)
-        y = copies(K.down_gemm(hid[0], m.W_out, eids, npp, 0, sids, tw, M))
+        y = copies(K.down_gemm(hid[0], m.W_out, eids, npp, 0, sids, tw, M, w_extra=m.W_sh_out))
         da1 = copies(K.dhidden_glu_bwd(x, m.W_out, eids, npp, 0, sids, tw, M, a1, 0, True,
-                                       gather_top_k=k)[0])
-        hs0, a1s = K.up_gemm(x, m.W_sh_in, None, None, S, 0, True)
-        hs = copies(hs0)
-        das = copies(K.dhidden_glu_bwd(x, m.W_sh_out, None, None, S, None, None, 0, a1s, 0,
-                                       False)[0])
-        ys = K.down_gemm(hs[0], m.W_sh_out, None, None, S, None, None, 0)
+                                       gather_top_k=ka, w_extra=m.W_sh_out)[0])
         dwl = torch.randn_like(w, dtype=torch.float32)
 
         GE, TF = "hbm", "tensor"
+        # M counts routed and shared pairs alike: (k + S) * T rows go through every GEMM
         stages = [
             # name, bound, work per launch (bytes or flop), launches per step, callable(i)
             ("router_topk", GE, T * E * 4 * 2 + T * k * 12, 1,
              lambda i: K.router_topk(logits, k, True, True, True)),
             ("router_topk_bwd", GE, T * E * 4 * 3 + T * k * 12, 1,
              lambda i: K.router_topk_bwd(logits, idx, dwl, logits, True, True)),
-            ("dispatch(3 kernels)", GE, M * 8 * 2 + M * 4 * 3, 1, lambda i: K.dispatch(idx, E)),
-            # the materialised permute is not on the block's path any more (the GEMMs gather rows
-            # themselves); it stays measurable as a stand-alone entry point
+            ("dispatch(3 kernels)", GE, M * 8 * 2 + M * 4 * 3, 1,
+             lambda i: K.dispatch(idx_all, Ea)),
+            # the materialised permute is not on the block's path (the GEMMs gather rows themselves);
+            # it stays measurable as a stand-alone entry point
             ("permute (stand-alone, fused away)", GE, 2 * M * D * 2 + M * 4, 0,
-             lambda i: K.permute(xr[i % 3], k, sids, npp)),
+             lambda i: K.permute(xr[i % 3], ka, sids, npp)),
             ("up_gemm+glu (gather, +a1 saved)", TF, 2.0 * M * D * 2 * H, 1,
-             lambda i: K.up_gemm(xr[i % 3], m.W_in, eids, npp, 0, 0, True, gather=(sids, k))),
+             lambda i: K.up_gemm(xr[i % 3], m.W_in, eids, npp, 0, 0, True, gather=gather,
+                                 w_extra=m.W_sh_in)),
             ("down_gemm+scale", TF, 2.0 * M * H * D, 1,
-             lambda i: K.down_gemm(hid[i % 3], m.W_out, eids, npp, 0, sids, tw, M)),
-            ("combine", GE, M * D * 2 + M * 4 + 3 * T * D * 2, 2,
-             lambda i: K.combine(y[i % 3], inv, T, k, ys[0], ys[1])),
+             lambda i: K.down_gemm(hid[i % 3], m.W_out, eids, npp, 0, sids, tw, M,
+                                   w_extra=m.W_sh_out)),
+            ("combine", GE, M * D * 2 + M * 4 + T * D * 2, 2,
+             lambda i: K.combine(y[i % 3], inv, T, ka)),
             ("dhidden+glu_bwd (gather)", TF, 2.0 * M * D * H, 1,
              lambda i: K.dhidden_glu_bwd(xr[i % 3], m.W_out, eids, npp, 0, sids, tw, M, a1, 0,
-                                         True, gather_top_k=k)),
+                                         True, gather_top_k=ka, w_extra=m.W_sh_out)),
             ("dx_gemm", TF, 2.0 * M * 2 * H * D, 1,
-             lambda i: K.dx_gemm(da1[i % 3], m.W_in, eids, npp, 0)),
+             lambda i: K.dx_gemm(da1[i % 3], m.W_in, eids, npp, 0, w_extra=m.W_sh_in)),
             ("wgrad_in (gather)", TF, 2.0 * M * D * 2 * H, 1,
-             lambda i: K.wgrad(xr[i % 3], da1[i % 3], offs, E, gather=("a", sids, k))),
+             lambda i: K.wgrad(xr[i % 3], da1[i % 3], offs, Ea, gather=("a", sids, ka), n_extra=S)),
             ("wgrad_out (gather)", TF, 2.0 * M * H * D, 1,
-             lambda i: K.wgrad(hid[i % 3], xr[i % 3], offs, E, gather=("b", sids, k))),
-            ("wgrad_in (slot-ordered operands)", TF, 2.0 * M * D * 2 * H, 0,
-             lambda i: K.wgrad(xs[i % 3], da1[i % 3], offs, E)),
-            ("wgrad_out (slot-ordered operands)", TF, 2.0 * M * H * D, 0,
-             lambda i: K.wgrad(hid[i % 3], xs[i % 3], offs, E)),
-            ("shared up_gemm+glu", TF, 2.0 * S * T * D * 2 * H, 1,
-             lambda i: K.up_gemm(xr[i % 3], m.W_sh_in, None, None, S, 0, True)),
-            ("shared down_gemm", TF, 2.0 * S * T * H * D, 1,
-             lambda i: K.down_gemm(hs[i % 3], m.W_sh_out, None, None, S, None, None, 0)),
-            ("shared dhidden+glu_bwd", TF, 2.0 * S * T * D * H, 1,
-             lambda i: K.dhidden_glu_bwd(xr[i % 3], m.W_sh_out, None, None, S, None, None, 0, a1s,
-                                         0, False)),
-            ("shared dx_gemm", TF, 2.0 * S * T * 2 * H * D, 1,
-             lambda i: K.dx_gemm(das[i % 3], m.W_sh_in, None, None, S)),
-            ("shared wgrad_in", TF, 2.0 * S * T * D * 2 * H, 1,
-             lambda i: K.wgrad(xr[i % 3], das[i % 3], None, S, b_grouped=True)),
-            ("shared wgrad_out", TF, 2.0 * S * T * H * D, 1,
-             lambda i: K.wgrad(hs[i % 3], xr[i % 3], None, S, a_grouped=True)),
+             lambda i: K.wgrad(hid[i % 3], xr[i % 3], offs, Ea, gather=("b", sids, ka),
+                               n_extra=S)),
         ]
     return stages
 

@@ -138,7 +138,12 @@ int moe_b200_combine(const void* y, const int32_t* inv_ids, int64_t n_tokens, in
  *   n_fixed_groups  0: routed schedule, per-block owners from expert_ids.
  *                   S > 0: shared-expert schedule -- weight matrices 0..S-1 are each applied to all
  *                   `rows` rows in token order (`rows` need not be a multiple of 128); outputs are
- *                   stacked [S, rows, width]. */
+ *                   stacked [S, rows, width].
+ *   w_extra, n_extra  optional second weight stack (routed schedule only): expert ids in
+ *                   [n_groups, n_groups + n_extra) index it. This is how the shared experts ride in
+ *                   the same launches as the routed ones: the dispatch sees them as n_extra more
+ *                   experts that every token is routed to, and their weights stay in their own
+ *                   tensors (W_sh_in / W_sh_out, src/model/moe.py:160-168). */
 
 /* Gathered A operand (routed schedule only): with gather_top_k > 0 the A argument is the
  * token-major matrix [n_pairs / gather_top_k, width] and the kernel itself reads row
@@ -152,7 +157,7 @@ int moe_b200_combine(const void* y, const int32_t* inv_ids, int64_t n_tokens, in
  * groups) or gathered. Replaces _gemm1_kernel (src/model/moe_kernel.py:269-323).
  * d_hidden must be 128. */
 int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w_in,
-                     int32_t n_groups, int32_t d_hidden, const int32_t* expert_ids,
+                     int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_hidden, const int32_t* expert_ids,
                      const int32_t* n_post_pad, int32_t n_fixed_groups,
                      const int32_t* sorted_ids, int32_t gather_top_k, int64_t n_pairs,
                      int32_t activation, void* hid, void* raw, int32_t* status, void* stream);
@@ -162,7 +167,7 @@ int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w
  * [S, rows, k_dim]. Replaces the forward use of _gemm2_kernel
  * (src/model/moe_kernel.py:339-402, 603-613). */
 int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void* w_out,
-                       int32_t n_groups, int32_t d_model, const int32_t* expert_ids,
+                       int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_model, const int32_t* expert_ids,
                        const int32_t* n_post_pad, int32_t n_fixed_groups,
                        const int32_t* sorted_ids, const void* pair_w, int64_t n_pairs, void* y,
                        int32_t* status, void* stream);
@@ -175,7 +180,8 @@ int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void*
  * Replaces the dH use of _gemm2_kernel plus _glu_bwd_kernel
  * (src/model/moe_kernel.py:676-692, 510-553). dtw may be NULL. */
 int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, const void* w_out,
-                             int32_t n_groups, int32_t d_hidden, const int32_t* expert_ids,
+                             int32_t n_groups, const void* w_extra, int32_t n_extra,
+                             int32_t d_hidden, const int32_t* expert_ids,
                              const int32_t* n_post_pad, int32_t n_fixed_groups,
                              const int32_t* sorted_ids, int32_t gather_top_k, const void* pair_w,
                              int64_t n_pairs, const void* a1, int32_t activation, void* da1,
@@ -185,7 +191,7 @@ int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, c
  * (no transposed copy). With fixed groups da1 and ydx are stacked [S, rows, .]. Replaces the dX use
  * of _gemm2_kernel and the w_in.transpose copy (src/model/moe_kernel.py:696-707). */
 int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,
-                     int32_t n_groups, int32_t d_model, const int32_t* expert_ids,
+                     int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_model, const int32_t* expert_ids,
                      const int32_t* n_post_pad, int32_t n_fixed_groups, void* ydx,
                      int32_t* status, void* stream);
 
@@ -204,12 +210,15 @@ int moe_b200_wgrad_scratch_bytes(int32_t m_dim, int32_t n_dim, int64_t rows, int
  * gather_which = 1 (a) or 2 (b), routed schedule only: that operand is the token-major matrix
  * [n_pairs / gather_top_k, width] and its rows are gathered through sorted_ids inside the kernel
  * (0 = both operands are slot-ordered buffers).
+ * dw holds groups [0, n_first); with n_first < n_groups the remaining groups are written to
+ * dw_extra [n_groups - n_first, m_dim, n_dim] (the shared experts' gradients).
  * Replaces _dw_kernel (src/model/moe_kernel.py:453-507, 712-721), which has no split-K. */
 int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* b,
                    int32_t b_grouped, int32_t n_dim, int64_t rows, const int32_t* pad_offsets,
                    int32_t n_groups, int32_t ks_rows, const int32_t* sorted_ids,
                    int32_t gather_top_k, int64_t n_pairs, int32_t gather_which, void* dw,
-                   void* partials, size_t partial_bytes, int32_t* status, void* stream);
+                   int32_t n_first, void* dw_extra, void* partials, size_t partial_bytes,
+                   int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -37,26 +37,27 @@ SIGNATURES = {
         ctypes.c_int, [_c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp]),
     "moe_b200_up_gemm": (
         ctypes.c_int,
-        [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp, _c_i32, _c_i64,
-         _c_i32, _c_vp, _c_vp, _c_vp, _c_vp]),
+        [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,
+         _c_i32, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp]),
     "moe_b200_down_gemm": (
         ctypes.c_int,
-        [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp, _c_vp, _c_i64,
-         _c_vp, _c_vp, _c_vp]),
+        [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,
+         _c_vp, _c_i64, _c_vp, _c_vp, _c_vp]),
     "moe_b200_dhidden_glu_bwd": (
         ctypes.c_int,
-        [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp, _c_i32, _c_vp,
-         _c_i64, _c_vp, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp]),
+        [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,
+         _c_i32, _c_vp, _c_i64, _c_vp, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp]),
     "moe_b200_dx_gemm": (
         ctypes.c_int,
-        [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp, _c_vp, _c_vp]),
+        [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,
+         _c_vp, _c_vp]),
     "moe_b200_wgrad_scratch_bytes": (
         ctypes.c_int,
         [_c_i32, _c_i32, _c_i64, _c_i32, _c_i32, _c_i32, ctypes.POINTER(_c_sz)]),
     "moe_b200_wgrad": (
         ctypes.c_int,
         [_c_vp, _c_i32, _c_i32, _c_vp, _c_i32, _c_i32, _c_i64, _c_vp, _c_i32, _c_i32, _c_vp, _c_i32,
-         _c_i64, _c_i32, _c_vp, _c_vp, _c_sz, _c_vp, _c_vp]),
+         _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_vp, _c_sz, _c_vp, _c_vp]),
 }
 
 _lib = None

@@ -5,6 +5,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <climits>
+#include <cstdint>
 #include <cstdlib>
 #include <mutex>
 
@@ -99,8 +101,8 @@ static int sm_count() {
 
 // Persistent launch: one CTA per SM (fewer if the tile list is shorter than that).
 template <int BN, int STAGES, bool B_MN, int EPI, bool GATHER_A = false>
-static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const RowsArgs& args,
-                       int64_t max_tiles, cudaStream_t st) {
+static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2,
+                       const RowsArgs& args, int64_t max_tiles, cudaStream_t st) {
   auto kern = rows_gemm_kernel<BN, STAGES, B_MN, EPI, GATHER_A>;
   constexpr int smem = RowsSmem<BN, STAGES>::DYNAMIC;
   static std::once_flag once;
@@ -111,7 +113,7 @@ static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const Row
   if (attr_err != cudaSuccess) return MOE_B200_ERR_CUDA;
   const int64_t sms = sm_count();
   const unsigned grid = unsigned(max_tiles < sms ? max_tiles : sms);
-  kern<<<grid, GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS, smem, st>>>(tmA, tmB, args);
+  kern<<<grid, GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS, smem, st>>>(tmA, tmB, tmB2, args);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
@@ -175,10 +177,16 @@ using namespace moe;
   if (n_fixed_groups > n_groups) return MOE_B200_ERR_SHAPE;                                  \
   if (n_fixed_groups == 0 && rows % 128 != 0) return MOE_B200_ERR_SHAPE;
 
+// A second weight stack (the shared experts') serves expert ids >= n_groups on the routed schedule.
+#define CHECK_EXTRA()                                                               \
+  if (n_extra < 0 || (n_extra > 0 && (!w_extra || n_fixed_groups > 0)))            \
+    return n_extra < 0 || n_fixed_groups > 0 ? MOE_B200_ERR_SHAPE : MOE_B200_ERR_NULL; \
+  if (n_extra > 0 && !aligned16(w_extra)) return MOE_B200_ERR_ALIGN;
+
 extern "C" {
 
 int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w_in,
-                     int32_t n_groups, int32_t d_hidden, const int32_t* expert_ids,
+                     int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_hidden, const int32_t* expert_ids,
                      const int32_t* n_post_pad, int32_t n_fixed_groups,
                      const int32_t* sorted_ids, int32_t gather_top_k, int64_t n_pairs,
                      int32_t activation, void* hid, void* raw, int32_t* status, void* stream) {
@@ -190,8 +198,12 @@ int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w
     return MOE_B200_ERR_SHAPE;
   if (!aligned16(a) || !aligned16(w_in) || !aligned16(hid) || !aligned16(raw))
     return MOE_B200_ERR_ALIGN;
-  CUtensorMap tmA, tmB;
+  CHECK_EXTRA();
+  CUtensorMap tmA, tmB, tmB2;
   if (!map_weight_mnmajor(&tmB, w_in, n_groups, d_model, 2 * d_hidden)) return MOE_B200_ERR_TMA;
+  tmB2 = tmB;
+  if (n_extra > 0 && !map_weight_mnmajor(&tmB2, w_extra, n_extra, d_model, 2 * d_hidden))
+    return MOE_B200_ERR_TMA;
   if (gather_top_k > 0)
     tmA = tmB;  // unused: A rows are gathered with cp.async
   else if (!map_rows_kmajor(&tmA, a, 1, rows, d_model))
@@ -206,6 +218,7 @@ int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w
   g.out2 = static_cast<__nv_bfloat16*>(raw);
   g.out2_gstride = rows * int64_t(2 * d_hidden);
   g.act = activation;
+  g.n_groups_b1 = n_extra > 0 ? n_groups : INT32_MAX;
   g.sorted_ids = sorted_ids;
   g.n_pairs = int32_t(n_pairs);
   g.a_src = static_cast<const __nv_bfloat16*>(a);
@@ -213,12 +226,13 @@ int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w
   g.top_k = gather_top_k;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t tiles = max_tiles(rows, 1, n_fixed_groups);
-  if (gather_top_k > 0) return launch_rows<256, 4, true, EPI_GLU, true>(tmA, tmB, g, tiles, st);
-  return launch_rows<256, 4, true, EPI_GLU>(tmA, tmB, g, tiles, st);
+  if (gather_top_k > 0)
+    return launch_rows<256, 4, true, EPI_GLU, true>(tmA, tmB, tmB2, g, tiles, st);
+  return launch_rows<256, 4, true, EPI_GLU>(tmA, tmB, tmB2, g, tiles, st);
 }
 
 int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void* w_out,
-                       int32_t n_groups, int32_t d_model, const int32_t* expert_ids,
+                       int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_model, const int32_t* expert_ids,
                        const int32_t* n_post_pad, int32_t n_fixed_groups,
                        const int32_t* sorted_ids, const void* pair_w, int64_t n_pairs, void* y,
                        int32_t* status, void* stream) {
@@ -227,10 +241,14 @@ int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void*
   if (!hid || !w_out || !y) return MOE_B200_ERR_NULL;
   if (pair_w && n_fixed_groups == 0 && !sorted_ids) return MOE_B200_ERR_NULL;
   if (!aligned16(hid) || !aligned16(w_out) || !aligned16(y)) return MOE_B200_ERR_ALIGN;
+  CHECK_EXTRA();
   const int gdim = n_fixed_groups > 0 ? n_fixed_groups : 1;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmB2;
   if (!map_rows_kmajor(&tmA, hid, gdim, rows, k_dim) ||
       !map_weight_mnmajor(&tmB, w_out, n_groups, k_dim, d_model))
+    return MOE_B200_ERR_TMA;
+  tmB2 = tmB;
+  if (n_extra > 0 && !map_weight_mnmajor(&tmB2, w_extra, n_extra, k_dim, d_model))
     return MOE_B200_ERR_TMA;
   RowsArgs g = base_args(expert_ids, n_post_pad, n_fixed_groups, rows, status);
   g.a_grouped = n_fixed_groups > 0;
@@ -243,12 +261,14 @@ int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void*
   g.out = static_cast<__nv_bfloat16*>(y);
   g.ld_out = d_model;
   g.out_gstride = rows * int64_t(d_model);
+  g.n_groups_b1 = n_extra > 0 ? n_groups : INT32_MAX;
   return launch_rows<192, 4, true, EPI_SCALE>(
-      tmA, tmB, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
+      tmA, tmB, tmB2, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
 }
 
 int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, const void* w_out,
-                             int32_t n_groups, int32_t d_hidden, const int32_t* expert_ids,
+                             int32_t n_groups, const void* w_extra, int32_t n_extra,
+                             int32_t d_hidden, const int32_t* expert_ids,
                              const int32_t* n_post_pad, int32_t n_fixed_groups,
                              const int32_t* sorted_ids, int32_t gather_top_k, const void* pair_w,
                              int64_t n_pairs, const void* a1, int32_t activation, void* da1,
@@ -263,8 +283,12 @@ int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, c
   if (!aligned16(douts) || !aligned16(w_out) || !aligned16(a1) || !aligned16(da1) ||
       !aligned16(hidw))
     return MOE_B200_ERR_ALIGN;
-  CUtensorMap tmA, tmB;
+  CHECK_EXTRA();
+  CUtensorMap tmA, tmB, tmB2;
   if (!map_weight_kmajor(&tmB, w_out, n_groups, d_hidden, d_model, 128)) return MOE_B200_ERR_TMA;
+  tmB2 = tmB;
+  if (n_extra > 0 && !map_weight_kmajor(&tmB2, w_extra, n_extra, d_hidden, d_model, 128))
+    return MOE_B200_ERR_TMA;
   if (gather_top_k > 0)
     tmA = tmB;  // unused: dOut rows are gathered with cp.async
   else if (!map_rows_kmajor(&tmA, douts, 1, rows, d_model))
@@ -285,27 +309,33 @@ int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, c
   g.out2_gstride = rows * int64_t(d_hidden);
   g.dtw = static_cast<__nv_bfloat16*>(dtw);
   g.act = activation;
+  g.n_groups_b1 = n_extra > 0 ? n_groups : INT32_MAX;
   g.a_src = static_cast<const __nv_bfloat16*>(douts);
   g.a_cols = d_model;
   g.top_k = gather_top_k;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t tiles = max_tiles(rows, 1, n_fixed_groups);
-  if (gather_top_k > 0) return launch_rows<128, 6, false, EPI_GLUBWD, true>(tmA, tmB, g, tiles, st);
-  return launch_rows<128, 6, false, EPI_GLUBWD>(tmA, tmB, g, tiles, st);
+  if (gather_top_k > 0)
+    return launch_rows<128, 6, false, EPI_GLUBWD, true>(tmA, tmB, tmB2, g, tiles, st);
+  return launch_rows<128, 6, false, EPI_GLUBWD>(tmA, tmB, tmB2, g, tiles, st);
 }
 
 int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,
-                     int32_t n_groups, int32_t d_model, const int32_t* expert_ids,
+                     int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_model, const int32_t* expert_ids,
                      const int32_t* n_post_pad, int32_t n_fixed_groups, void* ydx,
                      int32_t* status, void* stream) {
   CHECK_SCHED();
   if (d_hidden % 4 != 0 || d_hidden < 32 || d_model % 32 != 0) return MOE_B200_ERR_UNSUPPORTED;
   if (!da1 || !w_in || !ydx) return MOE_B200_ERR_NULL;
   if (!aligned16(da1) || !aligned16(w_in) || !aligned16(ydx)) return MOE_B200_ERR_ALIGN;
+  CHECK_EXTRA();
   const int gdim = n_fixed_groups > 0 ? n_fixed_groups : 1;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmB2;
   if (!map_rows_kmajor(&tmA, da1, gdim, rows, 2 * d_hidden) ||
       !map_weight_kmajor(&tmB, w_in, n_groups, d_model, 2 * d_hidden, 192))
+    return MOE_B200_ERR_TMA;
+  tmB2 = tmB;
+  if (n_extra > 0 && !map_weight_kmajor(&tmB2, w_extra, n_extra, d_model, 2 * d_hidden, 192))
     return MOE_B200_ERR_TMA;
   RowsArgs g = base_args(expert_ids, n_post_pad, n_fixed_groups, rows, status);
   g.a_grouped = n_fixed_groups > 0;
@@ -315,8 +345,9 @@ int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void
   g.out = static_cast<__nv_bfloat16*>(ydx);
   g.ld_out = d_model;
   g.out_gstride = rows * int64_t(d_model);
+  g.n_groups_b1 = n_extra > 0 ? n_groups : INT32_MAX;
   return launch_rows<192, 5, false, EPI_RAW>(
-      tmA, tmB, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
+      tmA, tmB, tmB2, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
 }
 
 static int64_t wgrad_items(int64_t rows, int n_groups, int routed, int ks_rows) {
@@ -354,7 +385,8 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
                    int32_t b_grouped, int32_t n_dim, int64_t rows, const int32_t* pad_offsets,
                    int32_t n_groups, int32_t ks_rows, const int32_t* sorted_ids,
                    int32_t gather_top_k, int64_t n_pairs, int32_t gather_which, void* dw,
-                   void* partials, size_t partial_bytes, int32_t* status, void* stream) {
+                   int32_t n_first, void* dw_extra, void* partials, size_t partial_bytes,
+                   int32_t* status, void* stream) {
   if (rows < 0 || rows > (int64_t(1) << 30) || n_groups < 1 || n_groups > WGRAD_MAX_GROUPS ||
       m_dim < 1 || n_dim < 1)
     return MOE_B200_ERR_SHAPE;
@@ -366,7 +398,10 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   if (gather_which && (!pad_offsets || !sorted_ids || gather_top_k < 1 || n_pairs < 0))
     return MOE_B200_ERR_SHAPE;
   if (!a || !b || !dw || !status || !partials) return MOE_B200_ERR_NULL;
-  if (!aligned16(a) || !aligned16(b) || !aligned16(dw) || !aligned16(partials))
+  if (n_first < 1 || n_first > n_groups || (n_first < n_groups && !dw_extra))
+    return MOE_B200_ERR_SHAPE;
+  if (!aligned16(a) || !aligned16(b) || !aligned16(dw) || !aligned16(partials) ||
+      !aligned16(dw_extra))
     return MOE_B200_ERR_ALIGN;
   const int routed = pad_offsets != nullptr;
   if (ks_rows == 0) ks_rows = auto_ks_rows(m_dim, n_dim, rows, n_groups, routed);
@@ -393,6 +428,8 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   g.m_dim = m_dim;
   g.n_dim = n_dim;
   g.out = static_cast<__nv_bfloat16*>(dw);
+  g.out_extra = static_cast<__nv_bfloat16*>(dw_extra);
+  g.n_out1 = n_first;
   g.partials = static_cast<float*>(partials);
   g.status = status;
   g.gather_a = gather_which == 1;

@@ -53,6 +53,7 @@ struct RowsArgs {
   int32_t num_k;               // K / 64 (rounded up; the tail reads as zeros)
   int32_t n_dim;               // valid accumulator columns over all N chunks
   int32_t n_chunks;            // ceil(n_dim / BN)
+  int32_t n_groups_b1;         // groups [0, n_groups_b1) read the first B stack, the rest the second
   // epilogue
   __nv_bfloat16* out;          // main output
   int64_t ld_out;              // elements between rows of out
@@ -80,7 +81,9 @@ struct WgradArgs {
   const int32_t* sorted_ids;
   int32_t top_k, n_pairs;
   int32_t m_dim, n_dim;        // rows / cols of one C[e]
-  __nv_bfloat16* out;          // [G, m_dim, n_dim]
+  __nv_bfloat16* out;          // [n_out1, m_dim, n_dim]: groups [0, n_out1)
+  __nv_bfloat16* out_extra;    // [G - n_out1, m_dim, n_dim]: the remaining groups (may be null)
+  int32_t n_out1;
   float* partials;             // fp32 scratch for the partial tiles of split runs
   int32_t* status;
 };

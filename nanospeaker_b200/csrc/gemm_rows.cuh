@@ -103,7 +103,8 @@ __device__ __forceinline__ float epilogue_glubwd(uint32_t taddr, int c_lo, int c
 template <int BN, int STAGES, bool B_MN, int EPI, bool GATHER_A>
 __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS, 1)
     rows_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
-                     const __grid_constant__ CUtensorMap tmB, const RowsArgs p) {
+                     const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmB2, const RowsArgs p) {
   using L = RowsSmem<BN, STAGES>;
   static_assert(BN % 64 == 0 && BN <= 256, "BN must be a multiple of 64 up to 256");
   constexpr uint32_t TMEM_BUF = BN <= 128 ? 128 : 256;  // columns per accumulator buffer
@@ -133,6 +134,7 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmB2);
     for (int s = 0; s < STAGES; ++s) {
       // gathered A: every lane of warp 0 arrives (through its cp.async) next to the TMA transaction
       mbar_init(full_bar + s, GATHER_A ? GATHER_WARPS * 32 + 1 : 1);
@@ -180,12 +182,16 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
         const int k0 = kt * BK;
         if (warp == 0 && lane == 0) {
           mbar_expect_tx(full_bar + s, L::B_STAGE_BYTES);
+          // the tile's expert lives in the first weight stack or (shared experts) the second
+          const bool first = tc.group < p.n_groups_b1;
+          const CUtensorMap* mb = first ? &tmB : &tmB2;
+          const int gb = first ? tc.group : tc.group - p.n_groups_b1;
           if constexpr (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_3d(sB + j * 8192, &tmB, full_bar + s, tc.n0 + 64 * j, k0, tc.group);
+              tma_load_3d(sB + j * 8192, mb, full_bar + s, tc.n0 + 64 * j, k0, gb);
           } else {
-            tma_load_3d(sB, &tmB, full_bar + s, k0, tc.n0, tc.group);
+            tma_load_3d(sB, mb, full_bar + s, k0, tc.n0, gb);
           }
         }
         const int col = k0 + c * 8;
@@ -222,12 +228,16 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
           mbar_expect_tx(full_bar + s, L::STAGE_BYTES);
           const int k0 = kt * BK;
           tma_load_3d(sA, &tmA, full_bar + s, k0, tc.m_tile * BM, p.a_grouped ? tc.z : 0);
+          // the tile's expert lives in the first weight stack or (shared experts) the second
+          const bool first = tc.group < p.n_groups_b1;
+          const CUtensorMap* mb = first ? &tmB : &tmB2;
+          const int gb = first ? tc.group : tc.group - p.n_groups_b1;
           if constexpr (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_3d(sB + j * 8192, &tmB, full_bar + s, tc.n0 + 64 * j, k0, tc.group);
+              tma_load_3d(sB + j * 8192, mb, full_bar + s, tc.n0 + 64 * j, k0, gb);
           } else {
-            tma_load_3d(sB, &tmB, full_bar + s, k0, tc.n0, tc.group);
+            tma_load_3d(sB, mb, full_bar + s, k0, tc.n0, gb);
           }
         }
       }

@@ -284,7 +284,10 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
       const uint32_t taddr = tmem_base + b * TMEM_BUF + (uint32_t(q * 32) << 16);
       const int m = m0 + row;
       const bool m_ok = m < p.m_dim;
-      __nv_bfloat16* dst = p.out + (int64_t(w.group) * p.m_dim + m) * int64_t(p.n_dim) + n0;
+      __nv_bfloat16* dst = (w.group < p.n_out1 ? p.out + int64_t(w.group) * p.m_dim * p.n_dim
+                                               : p.out_extra + int64_t(w.group - p.n_out1) *
+                                                                   p.m_dim * p.n_dim) +
+                           int64_t(m) * p.n_dim + n0;
       float* mine = p.partials + (int64_t(j) * tiles_xy + txy) * (int64_t(BM) * BN);
 #pragma unroll 1
       for (int c = c_lo; c < c_hi; ++c) {
@@ -356,7 +359,9 @@ __global__ void __launch_bounds__(256)
         uint2 w;
         w.x = *reinterpret_cast<const uint32_t*>(&lo);
         w.y = *reinterpret_cast<const uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(p.out + (int64_t(g) * p.m_dim + m) * int64_t(p.n_dim) + n) = w;
+        __nv_bfloat16* base = g < p.n_out1 ? p.out + int64_t(g) * p.m_dim * p.n_dim
+                                           : p.out_extra + int64_t(g - p.n_out1) * p.m_dim * p.n_dim;
+        *reinterpret_cast<uint2*>(base + int64_t(m) * p.n_dim + n) = w;
       }
     }
   }

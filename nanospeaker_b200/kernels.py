@@ -155,14 +155,20 @@ def _stack(n_fixed: int, rows: int, width: int, like: torch.Tensor) -> torch.Ten
     return torch.empty(shape, dtype=like.dtype, device=like.device)
 
 
+def _extra(w_extra):
+    return (0, 0) if w_extra is None else (w_extra.data_ptr(), w_extra.shape[0])
+
+
 def up_gemm(a, w_in, expert_ids, n_post_pad, n_fixed: int, act: int, want_raw: bool,
-            gather=None):
+            gather=None, w_extra=None):
     """a x w_in [G, D, 2H] -> (act(g)*u [rows, H], raw [g|u] [rows, 2H] | None).
     a is slot-ordered [rows, D]; or, with gather=(sorted_ids, top_k), the token-major x [T, D] whose
     rows the kernel gathers itself (rows = len(sorted_ids)). n_fixed = S > 0 applies weight
-    matrices 0..S-1 to all rows of a; outputs are then [S, rows, .]."""
+    matrices 0..S-1 to all rows of a; outputs are then [S, rows, .]. w_extra is an optional second
+    weight stack for expert ids >= G (the shared experts on the routed schedule)."""
     _need_cuda(a, w_in)
     d = a.shape[1]
+    xp, xn = _extra(w_extra)
     sids, top_k = gather if gather is not None else (None, 0)
     rows = sids.numel() if gather is not None else a.shape[0]
     n_pairs = a.shape[0] * top_k
@@ -171,23 +177,24 @@ def up_gemm(a, w_in, expert_ids, n_post_pad, n_fixed: int, act: int, want_raw: b
     hid = _stack(n_fixed, rows, h, a)
     raw = _stack(n_fixed, rows, h2, a) if want_raw else None
     _lib.check(_lib.load().moe_b200_up_gemm(
-        a.data_ptr(), rows, d, w_in.data_ptr(), g, h, _lib.ptr(expert_ids), _lib.ptr(n_post_pad),
-        n_fixed, _lib.ptr(sids), top_k, n_pairs, act, hid.data_ptr(), _lib.ptr(raw),
+        a.data_ptr(), rows, d, w_in.data_ptr(), g, xp, xn, h, _lib.ptr(expert_ids),
+        _lib.ptr(n_post_pad), n_fixed, _lib.ptr(sids), top_k, n_pairs, act, hid.data_ptr(), _lib.ptr(raw),
         status_word(a.device).data_ptr(), _stream(a)), "moe_b200_up_gemm")
     _count(1 if rows else 0)
     return hid, raw
 
 
 def down_gemm(hid, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair_w,
-              n_pairs: int) -> torch.Tensor:
+              n_pairs: int, w_extra=None) -> torch.Tensor:
     """hid [rows, K] (or [S, rows, K]) x w_out [G, K, D] -> y, scaled per row by
     pair_w[sorted_ids[row]] on the routed schedule."""
     _need_cuda(hid, w_out)
     rows, k = hid.shape[-2:]
     g, _, d = w_out.shape
     y = _stack(n_fixed, rows, d, hid)
+    xp, xn = _extra(w_extra)
     _lib.check(_lib.load().moe_b200_down_gemm(
-        hid.data_ptr(), rows, k, w_out.data_ptr(), g, d, _lib.ptr(expert_ids),
+        hid.data_ptr(), rows, k, w_out.data_ptr(), g, xp, xn, d, _lib.ptr(expert_ids),
         _lib.ptr(n_post_pad), n_fixed, _lib.ptr(sorted_ids), _lib.ptr(pair_w), n_pairs,
         y.data_ptr(), status_word(hid.device).data_ptr(), _stream(hid)), "moe_b200_down_gemm")
     _count(1 if rows else 0)
@@ -195,7 +202,8 @@ def down_gemm(hid, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair
 
 
 def dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair_w,
-                    n_pairs: int, a1, act: int, want_dtw: bool, gather_top_k: int = 0):
+                    n_pairs: int, a1, act: int, want_dtw: bool, gather_top_k: int = 0,
+                    w_extra=None):
     """-> (da1 [.., rows, 2H], hidw [.., rows, H], dtw [n_pairs] | None). douts is slot-ordered
     [rows, D], or with gather_top_k > 0 the token-major dOut [T, D] gathered through sorted_ids."""
     _need_cuda(douts, w_out, a1)
@@ -205,8 +213,9 @@ def dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_i
     da1 = _stack(n_fixed, rows, 2 * h, douts)
     hidw = _stack(n_fixed, rows, h, douts)
     dtw = torch.empty(n_pairs, dtype=douts.dtype, device=douts.device) if want_dtw else None
+    xp, xn = _extra(w_extra)
     _lib.check(_lib.load().moe_b200_dhidden_glu_bwd(
-        douts.data_ptr(), rows, d, w_out.data_ptr(), g, h, _lib.ptr(expert_ids),
+        douts.data_ptr(), rows, d, w_out.data_ptr(), g, xp, xn, h, _lib.ptr(expert_ids),
         _lib.ptr(n_post_pad), n_fixed, _lib.ptr(sorted_ids), gather_top_k, _lib.ptr(pair_w),
         n_pairs, a1.data_ptr(), act, da1.data_ptr(), hidw.data_ptr(), _lib.ptr(dtw),
         status_word(douts.device).data_ptr(), _stream(douts)), "moe_b200_dhidden_glu_bwd")
@@ -214,14 +223,15 @@ def dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_i
     return da1, hidw, dtw
 
 
-def dx_gemm(da1, w_in, expert_ids, n_post_pad, n_fixed: int) -> torch.Tensor:
+def dx_gemm(da1, w_in, expert_ids, n_post_pad, n_fixed: int, w_extra=None) -> torch.Tensor:
     """da1 [.., rows, 2H] x w_in[e]^T -> ydx [.., rows, D]."""
     _need_cuda(da1, w_in)
     rows, h2 = da1.shape[-2:]
     g, d, _ = w_in.shape
     ydx = _stack(n_fixed, rows, d, da1)
+    xp, xn = _extra(w_extra)
     _lib.check(_lib.load().moe_b200_dx_gemm(
-        da1.data_ptr(), rows, h2 // 2, w_in.data_ptr(), g, d, _lib.ptr(expert_ids),
+        da1.data_ptr(), rows, h2 // 2, w_in.data_ptr(), g, xp, xn, d, _lib.ptr(expert_ids),
         _lib.ptr(n_post_pad), n_fixed, ydx.data_ptr(), status_word(da1.device).data_ptr(),
         _stream(da1)), "moe_b200_dx_gemm")
     _count(1 if rows else 0)
@@ -229,13 +239,14 @@ def dx_gemm(da1, w_in, expert_ids, n_post_pad, n_fixed: int) -> torch.Tensor:
 
 
 def wgrad(a, b, pad_offsets, n_groups: int, ks_rows: int = 0, a_grouped: bool = False,
-          b_grouped: bool = False, gather=None) -> torch.Tensor:
+          b_grouped: bool = False, gather=None, n_extra: int = 0):
     """dw[e] = a_e^T @ b_e over run e's rows -> [G, Mdim, Ndim]. Routed schedule: a [rows, Mdim],
     b [rows, Ndim] in slot order plus pad_offsets. Fixed schedule (pad_offsets None): every group
     spans all rows; a / b are [G, rows, .] when *_grouped, else shared by the groups.
     ks_rows = rows per split-K chunk (0: chosen by the library).
     gather=("a" | "b", sorted_ids, top_k): that operand is token-major [T, .] and gathered inside
-    the kernel (routed schedule only)."""
+    the kernel (routed schedule only).
+    n_extra > 0: the last n_extra groups are returned as a second tensor (dw, dw_extra)."""
     _need_cuda(a, b)
     import ctypes
     which, sids, top_k = 0, None, 0
@@ -253,11 +264,14 @@ def wgrad(a, b, pad_offsets, n_groups: int, ks_rows: int = 0, a_grouped: bool = 
                                                 ks_rows, ctypes.byref(pb)),
                "moe_b200_wgrad_scratch_bytes")
     partials = torch.empty(max(pb.value, 32), dtype=torch.uint8, device=a.device)
-    dw = torch.empty((n_groups, m_dim, n_dim), dtype=a.dtype, device=a.device)
+    n_first = n_groups - n_extra
+    dw = torch.empty((n_first, m_dim, n_dim), dtype=a.dtype, device=a.device)
+    dw_extra = (torch.empty((n_extra, m_dim, n_dim), dtype=a.dtype, device=a.device)
+                if n_extra else None)
     _lib.check(lib.moe_b200_wgrad(
         a.data_ptr(), int(a_grouped), m_dim, b.data_ptr(), int(b_grouped), n_dim, rows,
         _lib.ptr(pad_offsets), n_groups, ks_rows, _lib.ptr(sids), top_k, n_pairs, which,
-        dw.data_ptr(), partials.data_ptr(), pb.value, status_word(a.device).data_ptr(),
-        _stream(a)), "moe_b200_wgrad")
+        dw.data_ptr(), n_first, _lib.ptr(dw_extra), partials.data_ptr(), pb.value,
+        status_word(a.device).data_ptr(), _stream(a)), "moe_b200_wgrad")
     _count(2 if rows > (ks_rows or 256) else 1)
-    return dw
+    return (dw, dw_extra) if n_extra else dw

@@ -24,7 +24,7 @@ KERNEL_DTYPES = (torch.bfloat16,)
 
 MAX_EXPERTS = 256  # per-expert state of the routing kernels lives on chip
 MAX_TOPK = 16
-MAX_SHARED = 2     # the combine kernel adds at most two extra token-major row sets
+MAX_SHARED = 8     # shared experts are dispatched as extra experts: E + S <= MAX_EXPERTS
 
 
 def kernel_supported(t: torch.Tensor) -> bool:
@@ -36,8 +36,8 @@ def shapes_supported(d_model: int, d_hidden: int, n_experts: int, top_k: int,
                      n_shared: int = 0) -> bool:
     """Shape half of the gate: what the tile shapes of the sm_100a kernels cover."""
     return (d_hidden == 128 and d_model >= 64 and d_model % 32 == 0
-            and 1 <= n_experts <= MAX_EXPERTS and 1 <= top_k <= min(MAX_TOPK, n_experts)
-            and 0 <= n_shared <= MAX_SHARED)
+            and 1 <= n_experts and 1 <= top_k <= min(MAX_TOPK - n_shared, n_experts)
+            and 0 <= n_shared <= MAX_SHARED and n_experts + n_shared <= MAX_EXPERTS)
 
 
 # ------------------------------------------------------------------------------ router top-k
@@ -149,19 +149,22 @@ def moe_experts(
     inv_ids: torch.Tensor,
     activation: str,
     save_for_backward: bool,
-) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """out[t] = sum_j topk_w[t,j] * expert_{idx[t,j]}(x[t])  (+ sum_s shared_s(x[t])).
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """out[t] = sum_j topk_w[t,j] * expert_{idx[t,j]}(x[t]) on pre-dispatched pairs.
 
     up/gate GEMM (token rows gathered inside the kernel, GLU fused) -> down GEMM with fused router
-    weight -> token-major fp32 combine; the shared experts run through the same GEMM kernels on
-    the unpermuted tokens and join in the combine. No permuted copy of x is materialised. All
-    tensors share x's dtype (the wrapper casts).
+    weight -> token-major fp32 combine. No permuted copy of x is materialised. All tensors share
+    x's dtype (the wrapper casts).
 
-    Returns (out, a1, a1_sh). With save_for_backward the up GEMM also stores its pre-activations
-    a1 [l_cap, 2H] (routed) and a1_sh [S, T, 2H] (shared) so the backward does not recompute them
-    -- 180 GB of HBM make keeping ~70 MB per block the cheaper side of the trade the reference
-    settles the other way on a 4 GB card (src/model/moe_kernel.py:663-664). Without it they are
-    empty.
+    Shared experts: when w_sh_in / w_sh_out [S, ...] are given, the plan must have been built over
+    E + S experts with every token also routed (weight 1) to experts E .. E+S-1; those ids read the
+    shared weight stacks, so the always-on experts run inside the same launches as the routed ones
+    (`fused_moe_forward` builds that plan).
+
+    Returns (out, a1). With save_for_backward the up GEMM also stores its pre-activations
+    a1 [l_cap, 2H] so the backward does not recompute them -- 180 GB of HBM make keeping ~70 MB per
+    block the cheaper side of the trade the reference settles the other way on a 4 GB card
+    (src/model/moe_kernel.py:663-664). Without it a1 is empty.
     """
     x, w_in, w_out = x.contiguous(), w_in.contiguous(), w_out.contiguous()
     _check_inputs(x, w_in, w_out, w_sh_in)
@@ -170,38 +173,27 @@ def moe_experts(
     topk = topk_w.shape[-1]
     m = n * topk
     if n == 0:
-        return x.new_zeros((0, d)), x.new_empty(0), x.new_empty(0)
+        return x.new_zeros((0, d)), x.new_empty(0)
     tw = topk_w.reshape(-1).contiguous()
-
-    hid, a1 = K.up_gemm(x, w_in, expert_ids, n_post_pad, 0, act, save_for_backward,
-                        gather=(sorted_ids, topk))
-    y = K.down_gemm(hid, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m)
-    extras: List[Optional[torch.Tensor]] = [None, None]
-    a1_sh = None
     if w_sh_in is not None:
         w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
-        s_n = w_sh_in.shape[0]
-        hs, a1_sh = K.up_gemm(x, w_sh_in, None, None, s_n, act, save_for_backward)
-        ys = K.down_gemm(hs, w_sh_out, None, None, s_n, None, None, 0)
-        for s in range(s_n):
-            extras[s] = ys[s]
-    out = K.combine(y, inv_ids, n, topk, extras[0], extras[1])
-    return (out, a1 if a1 is not None else x.new_empty(0),
-            a1_sh if a1_sh is not None else x.new_empty(0))
+
+    hid, a1 = K.up_gemm(x, w_in, expert_ids, n_post_pad, 0, act, save_for_backward,
+                        gather=(sorted_ids, topk), w_extra=w_sh_in)
+    y = K.down_gemm(hid, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m, w_extra=w_sh_out)
+    out = K.combine(y, inv_ids, n, topk)
+    return out, a1 if a1 is not None else x.new_empty(0)
 
 
 @moe_experts.register_fake
 def _(x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
       n_post_pad, inv_ids, activation, save_for_backward):
     n, d = x.shape
-    cap = sorted_ids.shape[0]
-    h2 = w_in.shape[2]
     if n == 0:
-        return x.new_empty((0, d)), x.new_empty(0), x.new_empty(0)
-    a1 = x.new_empty((cap, h2)) if save_for_backward else x.new_empty(0)
-    a1_sh = (x.new_empty((w_sh_in.shape[0], n, h2))
-             if save_for_backward and w_sh_in is not None else x.new_empty(0))
-    return x.new_empty(x.shape), a1, a1_sh
+        return x.new_empty((0, d)), x.new_empty(0)
+    a1 = (x.new_empty((sorted_ids.shape[0], w_in.shape[2])) if save_for_backward
+          else x.new_empty(0))
+    return x.new_empty(x.shape), a1
 
 
 @torch.library.custom_op("moe_b200::moe_experts_bwd", mutates_args=())
@@ -209,7 +201,6 @@ def moe_experts_bwd(
     grad_out: torch.Tensor,
     x: torch.Tensor,
     a1: torch.Tensor,
-    a1_sh: torch.Tensor,
     w_in: torch.Tensor,
     w_out: torch.Tensor,
     topk_w: torch.Tensor,
@@ -224,43 +215,38 @@ def moe_experts_bwd(
     activation: str,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """(dx, dW_in, dW_out, dtopk_w, dW_sh_in, dW_sh_out); the last two are empty without shared
-    experts. a1 / a1_sh are the pre-activations the forward kept; rows of x and grad_out are
-    gathered inside the kernels that need them in slot order."""
+    experts. a1 holds the pre-activations the forward kept; rows of x and grad_out are gathered
+    inside the kernels that need them in slot order."""
     grad_out = grad_out.to(x.dtype).contiguous()
     x, w_in, w_out = x.contiguous(), w_in.contiguous(), w_out.contiguous()
     _check_inputs(x, w_in, w_out, w_sh_in)
     act = _act_id(activation)
     n, d = x.shape
     e_n = w_in.shape[0]
+    s_n = 0
+    if w_sh_in is not None:
+        w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
+        s_n = w_sh_in.shape[0]
     topk = topk_w.shape[-1]
     m = n * topk
     tw = topk_w.reshape(-1).contiguous()
 
     da1, hidw, dtw = K.dhidden_glu_bwd(grad_out, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw,
-                                       m, a1, act, True, gather_top_k=topk)
-    ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0)
-    dw_in = K.wgrad(x, da1, pad_offsets, e_n, gather=("a", sorted_ids, topk))
-    dw_out = K.wgrad(hidw, grad_out, pad_offsets, e_n, gather=("b", sorted_ids, topk))
-
-    extras: List[Optional[torch.Tensor]] = [None, None]
-    dw_sh_in = x.new_empty(0)
-    dw_sh_out = x.new_empty(0)
-    if w_sh_in is not None:
-        w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
-        s_n = w_sh_in.shape[0]
-        da1s, hids, _ = K.dhidden_glu_bwd(grad_out, w_sh_out, None, None, s_n, None, None, 0,
-                                          a1_sh, act, False)
-        ydxs = K.dx_gemm(da1s, w_sh_in, None, None, s_n)
-        for s in range(s_n):
-            extras[s] = ydxs[s]
-        dw_sh_in = K.wgrad(x, da1s, None, s_n, b_grouped=True)
-        dw_sh_out = K.wgrad(hids, grad_out, None, s_n, a_grouped=True)
-    dx = K.combine(ydx, inv_ids, n, topk, extras[0], extras[1])
+                                       m, a1, act, True, gather_top_k=topk, w_extra=w_sh_out)
+    ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
+    dx = K.combine(ydx, inv_ids, n, topk)
+    g_in = K.wgrad(x, da1, pad_offsets, e_n + s_n, gather=("a", sorted_ids, topk), n_extra=s_n)
+    g_out = K.wgrad(hidw, grad_out, pad_offsets, e_n + s_n, gather=("b", sorted_ids, topk),
+                    n_extra=s_n)
+    if s_n:
+        (dw_in, dw_sh_in), (dw_out, dw_sh_out) = g_in, g_out
+    else:
+        dw_in, dw_out, dw_sh_in, dw_sh_out = g_in, g_out, x.new_empty(0), x.new_empty(0)
     return dx, dw_in, dw_out, dtw.view_as(topk_w), dw_sh_in, dw_sh_out
 
 
 @moe_experts_bwd.register_fake
-def _(grad_out, x, a1, a1_sh, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
+def _(grad_out, x, a1, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
       pad_offsets, counts, n_post_pad, inv_ids, activation):
     return (torch.empty_like(x), torch.empty_like(w_in), torch.empty_like(w_out),
             torch.empty_like(topk_w),
@@ -271,15 +257,14 @@ def _(grad_out, x, a1, a1_sh, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids
 def _experts_setup(ctx, inputs, output):
     (x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
      n_post_pad, inv_ids, activation, save_for_backward) = inputs
-    out, a1, a1_sh = output
-    ctx.mark_non_differentiable(a1, a1_sh)
-    # without this autograd would hand the backward zero-filled gradients for the three kept
-    # buffers (hundreds of MB of memset per step)
+    out, a1 = output
+    ctx.mark_non_differentiable(a1)
+    # without this autograd would hand the backward a zero-filled gradient for the kept buffer
     ctx.set_materialize_grads(False)
     if not save_for_backward:
         raise RuntimeError("moe_experts was run with save_for_backward=False but a gradient is "
                            "being recorded; call it through fused_moe_forward")
-    saved = [x, a1, a1_sh, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts,
+    saved = [x, a1, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts,
              n_post_pad, inv_ids]
     ctx.has_shared = w_sh_in is not None
     if ctx.has_shared:
@@ -288,15 +273,15 @@ def _experts_setup(ctx, inputs, output):
     ctx.activation = activation
 
 
-def _experts_backward(ctx, grad_out, g_a1, g_a1_sh):
-    (x, a1, a1_sh, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts,
-     n_post_pad, inv_ids, *rest) = ctx.saved_tensors
+def _experts_backward(ctx, grad_out, g_a1):
+    (x, a1, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts, n_post_pad,
+     inv_ids, *rest) = ctx.saved_tensors
     w_sh_in, w_sh_out = (rest[0], rest[1]) if ctx.has_shared else (None, None)
     if grad_out is None:
         grad_out = torch.zeros_like(x)
     dx, dw_in, dw_out, dtw, dsi, dso = moe_experts_bwd(
-        grad_out, x, a1, a1_sh, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids,
-        expert_ids, pad_offsets, counts, n_post_pad, inv_ids, ctx.activation)
+        grad_out, x, a1, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
+        pad_offsets, counts, n_post_pad, inv_ids, ctx.activation)
     return (dx, dw_in, dw_out, dtw, dsi if ctx.has_shared else None,
             dso if ctx.has_shared else None, None, None, None, None, None, None, None, None)
 
@@ -319,11 +304,19 @@ def fused_moe_forward(x, w_in, w_out, topk_w, topk_idx, b_in, b_out, activation,
         raise NotImplementedError(
             "moe_b200 kernels do not apply per-expert biases; build the block with bias=False "
             "or kernel=False")
-    sids, eids, offs, counts, npp, inv = moe_dispatch(topk_idx, w_in.shape[0])
+    n_experts = w_in.shape[0]
+    topk_w = topk_w.to(x.dtype)
+    if w_sh_in is not None:
+        # the shared experts become experts E .. E+S-1 that every token is routed to with weight 1
+        s_n, t = w_sh_in.shape[0], topk_idx.shape[0]
+        ids = torch.arange(n_experts, n_experts + s_n, device=topk_idx.device, dtype=topk_idx.dtype)
+        topk_idx = torch.cat([topk_idx, ids.expand(t, s_n)], dim=1)
+        topk_w = torch.cat([topk_w, topk_w.new_ones((t, s_n))], dim=1)
+        n_experts += s_n
+    sids, eids, offs, counts, npp, inv = moe_dispatch(topk_idx, n_experts)
     cast = lambda t: None if t is None else t.to(x.dtype)
     tensors = (x, w_in, w_out, topk_w, w_sh_in, w_sh_out)
     save = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
-    out, _, _ = moe_experts(x, cast(w_in), cast(w_out), topk_w.to(x.dtype), cast(w_sh_in),
-                               cast(w_sh_out), sids, eids, offs, counts, npp, inv, activation,
-                               save)
-    return out, counts
+    out, _ = moe_experts(x, cast(w_in), cast(w_out), topk_w, cast(w_sh_in), cast(w_sh_out), sids,
+                         eids, offs, counts, npp, inv, activation, save)
+    return out, counts[: w_in.shape[0]]

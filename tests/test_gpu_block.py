@@ -277,7 +277,10 @@ def test_opcheck_and_fake_kernels():
     x = torch.randn(10, 64, device="cuda").bfloat16()
     with torch.no_grad():
         w, idx, _ = m.router(x)
-    plan = moe_dispatch(idx, 4)
+        # one shared expert = expert id 4 that every token is routed to with weight 1
+        idx = torch.cat([idx, torch.full((10, 1), 4, device="cuda")], 1)
+        w = torch.cat([w, torch.ones(10, 1, device="cuda", dtype=w.dtype)], 1)
+    plan = moe_dispatch(idx, 5)
     rg = lambda t: t.detach().clone().requires_grad_(True)
     torch.library.opcheck(moe_experts, (rg(x), rg(m.W_in), rg(m.W_out), rg(w), rg(m.W_sh_in),
                                         rg(m.W_sh_out), *plan, "silu", True),
