@@ -162,8 +162,13 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
     // warp's 32 rows: eight lanes cover one row's 128-byte k slice, so global reads are whole
     // lines. The chunk lands at (c ^ (row & 7)), the 128-byte swizzle the UMMA descriptor expects.
     // Warp 0's lane 0 also issues the TMA loads of B.
+    // Completion protocol: a lane's copies of stage i are known to have landed after
+    // cp.async.wait_group; the lane then makes them visible to the async proxy (the tensor core
+    // reads shared memory through it) with fence.proxy.async and arrives on the stage's barrier.
+    // That hand-over trails the issue loop by one stage so the wait is normally already over.
     const int gw = warp == 0 ? 0 : warp - (1 + EPI_WARPS);
     uint32_t it = 0;
+    int pending = -1;  // stage whose copies are issued but not yet handed over
     const int r4 = lane >> 3, c = lane & 7;
     for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
       const TileCoord tc = decode_tile(p, t, m_tiles, BN);
@@ -206,8 +211,19 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
           const __nv_bfloat16* src = ok ? p.a_src + int64_t(tok) * p.a_cols + col : p.a_src;
           cp_async_16(sA_u + row * 128 + ((c ^ (row & 7)) << 4), src, ok ? 16u : 0u);
         }
-        cp_async_arrive(full_bar + s);
+        cp_async_commit();
+        if (pending >= 0) {
+          cp_async_wait<1>();
+          fence_proxy_async();
+          mbar_arrive(full_bar + pending);
+        }
+        pending = s;
       }
+    }
+    if (pending >= 0) {
+      cp_async_wait<0>();
+      fence_proxy_async();
+      mbar_arrive(full_bar + pending);
     }
   } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -265,7 +281,6 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
             break;
           }
           tc_fence_after();
-          if constexpr (GATHER_A) fence_proxy_async();  // cp.async wrote A through the generic proxy
           const uint32_t sA = smem_u32(smem + s * L::STAGE_BYTES);
           issue_stage_mmas<BN, false, B_MN>(sA, sA + A_STAGE_BYTES, d_tmem, kt == 0);
           umma_commit(empty_bar + s);  // stage reusable once these MMAs have read it

@@ -158,6 +158,7 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
     const int gw = warp == 0 ? 0 : warp - (1 + EPI_WARPS);
     if (gather || (warp == 0 && lane == 0)) {
       uint32_t it = 0;
+      int pending = -1;  // stage whose cp.async copies are issued but not yet handed over
       for (int t = blockIdx.x; t < total && !*abort_flag; t += gridDim.x) {
         const WgradItem w = wgrad_item(p, first_item, run_start, t / tiles_xy);
         const int txy = t % tiles_xy;
@@ -219,9 +220,22 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
               cp_async_16(dst0 + (c >> 3) * 8192 + kr * 128 + (((c & 7) ^ (kr & 7)) << 4), src,
                           ok ? 16u : 0u);
             }
-            cp_async_arrive(full_bar + s);
+            // hand over the PREVIOUS stage: its copies have landed after wait_group, the proxy
+            // fence makes them visible to the tensor core's async-proxy reads, then arrive
+            cp_async_commit();
+            if (pending >= 0) {
+              cp_async_wait<1>();
+              fence_proxy_async();
+              mbar_arrive(full_bar + pending);
+            }
+            pending = s;
           }
         }
+      }
+      if (gather && pending >= 0) {
+        cp_async_wait<0>();
+        fence_proxy_async();
+        mbar_arrive(full_bar + pending);
       }
     }
   } else if (warp == 1) {
@@ -249,7 +263,6 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
             break;
           }
           tc_fence_after();
-          if (gather) fence_proxy_async();  // cp.async wrote through the generic proxy
           const uint32_t sA = smem_u32(smem + s * L::STAGE_BYTES);
           issue_stage_mmas<BN, true, true>(sA, sA + A_STAGE_BYTES, d_tmem, kt == 0);
           umma_commit(empty_bar + s);

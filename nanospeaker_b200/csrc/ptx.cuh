@@ -73,11 +73,13 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src, 
                "r"(src_bytes)
                : "memory");
 }
-// Arrive on the mbarrier once all cp.async issued so far by this thread have landed; the arrival is
-// one of the barrier's expected count (noinc).
-__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+// Wait until at most N of this thread's committed cp.async groups are still in flight.
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // --------------------------------------------------------------------- TMA
