@@ -220,15 +220,18 @@ def build_stages(m, x):
         copies = lambda t: [t.clone() for _ in range(3)]
         xr = copies(x)
         gather = (sids, ka)
-        hid0, a1 = K.up_gemm(x, m.W_in, eids, npp, 0, 0, True, gather=gather, w_extra=m.W_sh_in)
+        xs = copies(K.permute(x, ka, sids, npp))
+        hid0, a1 = K.up_gemm(xs[0], m.W_in, eids, npp, 0, 0, True, w_extra=m.W_sh_in)
         hid = copies(hid0)
         y = copies(K.down_gemm(hid[0], m.W_out, eids, npp, 0, sids, tw, M, w_extra=m.W_sh_out))
-        da1 = copies(K.dhidden_glu_bwd(x, m.W_out, eids, npp, 0, sids, tw, M, a1, 0, True,
-                                       gather_top_k=ka, w_extra=m.W_sh_out)[0])
+        da1 = copies(K.dhidden_glu_bwd(xs[0], m.W_out, eids, npp, 0, sids, tw, M, a1, 0, True,
+                                       w_extra=m.W_sh_out)[0])
         dwl = torch.randn_like(w, dtype=torch.float32)
 
         GE, TF = "hbm", "tensor"
-        # M counts routed and shared pairs alike: (k + S) * T rows go through every GEMM
+        # M counts routed and shared pairs alike: (k + S) * T rows go through every GEMM.
+        # Training path: permute once per direction, TMA-fed GEMMs. The gathered variants (used by
+        # the inference forward) are listed with 0 launches per step.
         stages = [
             # name, bound, work per launch (bytes or flop), launches per step, callable(i)
             ("router_topk", GE, T * E * 4 * 2 + T * k * 12, 1,
@@ -237,28 +240,27 @@ def build_stages(m, x):
              lambda i: K.router_topk_bwd(logits, idx, dwl, logits, True, True)),
             ("dispatch(3 kernels)", GE, M * 8 * 2 + M * 4 * 3, 1,
              lambda i: K.dispatch(idx_all, Ea)),
-            # the materialised permute is not on the block's path (the GEMMs gather rows themselves);
-            # it stays measurable as a stand-alone entry point
-            ("permute (stand-alone, fused away)", GE, 2 * M * D * 2 + M * 4, 0,
+            ("permute", GE, 2 * M * D * 2 + M * 4, 2,
              lambda i: K.permute(xr[i % 3], ka, sids, npp)),
-            ("up_gemm+glu (gather, +a1 saved)", TF, 2.0 * M * D * 2 * H, 1,
-             lambda i: K.up_gemm(xr[i % 3], m.W_in, eids, npp, 0, 0, True, gather=gather,
+            ("up_gemm+glu (+a1 saved)", TF, 2.0 * M * D * 2 * H, 1,
+             lambda i: K.up_gemm(xs[i % 3], m.W_in, eids, npp, 0, 0, True, w_extra=m.W_sh_in)),
+            ("up_gemm+glu (gathered rows, inference)", TF, 2.0 * M * D * 2 * H, 0,
+             lambda i: K.up_gemm(xr[i % 3], m.W_in, eids, npp, 0, 0, False, gather=gather,
                                  w_extra=m.W_sh_in)),
             ("down_gemm+scale", TF, 2.0 * M * H * D, 1,
              lambda i: K.down_gemm(hid[i % 3], m.W_out, eids, npp, 0, sids, tw, M,
                                    w_extra=m.W_sh_out)),
             ("combine", GE, M * D * 2 + M * 4 + T * D * 2, 2,
              lambda i: K.combine(y[i % 3], inv, T, ka)),
-            ("dhidden+glu_bwd (gather)", TF, 2.0 * M * D * H, 1,
-             lambda i: K.dhidden_glu_bwd(xr[i % 3], m.W_out, eids, npp, 0, sids, tw, M, a1, 0,
-                                         True, gather_top_k=ka, w_extra=m.W_sh_out)),
+            ("dhidden+glu_bwd", TF, 2.0 * M * D * H, 1,
+             lambda i: K.dhidden_glu_bwd(xs[i % 3], m.W_out, eids, npp, 0, sids, tw, M, a1, 0,
+                                         True, w_extra=m.W_sh_out)),
             ("dx_gemm", TF, 2.0 * M * 2 * H * D, 1,
              lambda i: K.dx_gemm(da1[i % 3], m.W_in, eids, npp, 0, w_extra=m.W_sh_in)),
-            ("wgrad_in (gather)", TF, 2.0 * M * D * 2 * H, 1,
-             lambda i: K.wgrad(xr[i % 3], da1[i % 3], offs, Ea, gather=("a", sids, ka), n_extra=S)),
-            ("wgrad_out (gather)", TF, 2.0 * M * H * D, 1,
-             lambda i: K.wgrad(hid[i % 3], xr[i % 3], offs, Ea, gather=("b", sids, ka),
-                               n_extra=S)),
+            ("wgrad_in", TF, 2.0 * M * D * 2 * H, 1,
+             lambda i: K.wgrad(xs[i % 3], da1[i % 3], offs, Ea, n_extra=S)),
+            ("wgrad_out", TF, 2.0 * M * H * D, 1,
+             lambda i: K.wgrad(hid[i % 3], xs[i % 3], offs, Ea, n_extra=S)),
         ]
     return stages
 

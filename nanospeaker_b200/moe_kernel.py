@@ -149,22 +149,26 @@ def moe_experts(
     inv_ids: torch.Tensor,
     activation: str,
     save_for_backward: bool,
-) -> Tuple[torch.Tensor, torch.Tensor]:
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """out[t] = sum_j topk_w[t,j] * expert_{idx[t,j]}(x[t]) on pre-dispatched pairs.
 
-    up/gate GEMM (token rows gathered inside the kernel, GLU fused) -> down GEMM with fused router
-    weight -> token-major fp32 combine. No permuted copy of x is materialised. All tensors share
-    x's dtype (the wrapper casts).
+    up/gate GEMM with the GLU fused -> down GEMM with fused router weight -> token-major fp32
+    combine. All tensors share x's dtype (the wrapper casts). Two ways to feed the up GEMM:
+      * inference (save_for_backward False): its producer warps gather the token rows themselves,
+        no permuted copy of x exists;
+      * training: x is permuted once into slot order (xs) and kept, because the weight-gradient
+        GEMM reads the same rows again and TMA tiles of a materialised buffer stream several times
+        faster than per-row cp.async gathers.
 
     Shared experts: when w_sh_in / w_sh_out [S, ...] are given, the plan must have been built over
     E + S experts with every token also routed (weight 1) to experts E .. E+S-1; those ids read the
     shared weight stacks, so the always-on experts run inside the same launches as the routed ones
     (`fused_moe_forward` builds that plan).
 
-    Returns (out, a1). With save_for_backward the up GEMM also stores its pre-activations
-    a1 [l_cap, 2H] so the backward does not recompute them -- 180 GB of HBM make keeping ~70 MB per
-    block the cheaper side of the trade the reference settles the other way on a 4 GB card
-    (src/model/moe_kernel.py:663-664). Without it a1 is empty.
+    Returns (out, xs, a1). With save_for_backward the forward keeps xs [l_cap, D] and the up GEMM's
+    pre-activations a1 [l_cap, 2H] so the backward neither re-permutes nor recomputes -- 180 GB of
+    HBM make keeping ~250 MB per block the cheaper side of the trade the reference settles the
+    other way on a 4 GB card (src/model/moe_kernel.py:663-664). Without it both are empty.
     """
     x, w_in, w_out = x.contiguous(), w_in.contiguous(), w_out.contiguous()
     _check_inputs(x, w_in, w_out, w_sh_in)
@@ -173,33 +177,38 @@ def moe_experts(
     topk = topk_w.shape[-1]
     m = n * topk
     if n == 0:
-        return x.new_zeros((0, d)), x.new_empty(0)
+        return x.new_zeros((0, d)), x.new_empty(0), x.new_empty(0)
     tw = topk_w.reshape(-1).contiguous()
     if w_sh_in is not None:
         w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
 
-    hid, a1 = K.up_gemm(x, w_in, expert_ids, n_post_pad, 0, act, save_for_backward,
-                        gather=(sorted_ids, topk), w_extra=w_sh_in)
+    if save_for_backward:
+        xs = K.permute(x, topk, sorted_ids, n_post_pad)
+        hid, a1 = K.up_gemm(xs, w_in, expert_ids, n_post_pad, 0, act, True, w_extra=w_sh_in)
+    else:
+        xs, a1 = x.new_empty(0), x.new_empty(0)
+        hid, _ = K.up_gemm(x, w_in, expert_ids, n_post_pad, 0, act, False,
+                           gather=(sorted_ids, topk), w_extra=w_sh_in)
     y = K.down_gemm(hid, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m, w_extra=w_sh_out)
     out = K.combine(y, inv_ids, n, topk)
-    return out, a1 if a1 is not None else x.new_empty(0)
+    return out, xs, a1
 
 
 @moe_experts.register_fake
 def _(x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
       n_post_pad, inv_ids, activation, save_for_backward):
     n, d = x.shape
-    if n == 0:
-        return x.new_empty((0, d)), x.new_empty(0)
-    a1 = (x.new_empty((sorted_ids.shape[0], w_in.shape[2])) if save_for_backward
-          else x.new_empty(0))
-    return x.new_empty(x.shape), a1
+    if n == 0 or not save_for_backward:
+        return x.new_empty((n, d)), x.new_empty(0), x.new_empty(0)
+    cap = sorted_ids.shape[0]
+    return x.new_empty(x.shape), x.new_empty((cap, d)), x.new_empty((cap, w_in.shape[2]))
 
 
 @torch.library.custom_op("moe_b200::moe_experts_bwd", mutates_args=())
 def moe_experts_bwd(
     grad_out: torch.Tensor,
     x: torch.Tensor,
+    xs: torch.Tensor,
     a1: torch.Tensor,
     w_in: torch.Tensor,
     w_out: torch.Tensor,
@@ -215,8 +224,8 @@ def moe_experts_bwd(
     activation: str,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """(dx, dW_in, dW_out, dtopk_w, dW_sh_in, dW_sh_out); the last two are empty without shared
-    experts. a1 holds the pre-activations the forward kept; rows of x and grad_out are gathered
-    inside the kernels that need them in slot order."""
+    experts. xs (x in slot order) and a1 (pre-activations) are what the forward kept; grad_out is
+    permuted once and feeds both the dHidden GEMM and the dW_out GEMM."""
     grad_out = grad_out.to(x.dtype).contiguous()
     x, w_in, w_out = x.contiguous(), w_in.contiguous(), w_out.contiguous()
     _check_inputs(x, w_in, w_out, w_sh_in)
@@ -231,13 +240,13 @@ def moe_experts_bwd(
     m = n * topk
     tw = topk_w.reshape(-1).contiguous()
 
-    da1, hidw, dtw = K.dhidden_glu_bwd(grad_out, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw,
-                                       m, a1, act, True, gather_top_k=topk, w_extra=w_sh_out)
+    douts = K.permute(grad_out, topk, sorted_ids, n_post_pad)
+    da1, hidw, dtw = K.dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m,
+                                       a1, act, True, w_extra=w_sh_out)
     ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
     dx = K.combine(ydx, inv_ids, n, topk)
-    g_in = K.wgrad(x, da1, pad_offsets, e_n + s_n, gather=("a", sorted_ids, topk), n_extra=s_n)
-    g_out = K.wgrad(hidw, grad_out, pad_offsets, e_n + s_n, gather=("b", sorted_ids, topk),
-                    n_extra=s_n)
+    g_in = K.wgrad(xs, da1, pad_offsets, e_n + s_n, n_extra=s_n)
+    g_out = K.wgrad(hidw, douts, pad_offsets, e_n + s_n, n_extra=s_n)
     if s_n:
         (dw_in, dw_sh_in), (dw_out, dw_sh_out) = g_in, g_out
     else:
@@ -246,7 +255,7 @@ def moe_experts_bwd(
 
 
 @moe_experts_bwd.register_fake
-def _(grad_out, x, a1, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
+def _(grad_out, x, xs, a1, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
       pad_offsets, counts, n_post_pad, inv_ids, activation):
     return (torch.empty_like(x), torch.empty_like(w_in), torch.empty_like(w_out),
             torch.empty_like(topk_w),
@@ -257,14 +266,14 @@ def _(grad_out, x, a1, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, exper
 def _experts_setup(ctx, inputs, output):
     (x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
      n_post_pad, inv_ids, activation, save_for_backward) = inputs
-    out, a1 = output
-    ctx.mark_non_differentiable(a1)
-    # without this autograd would hand the backward a zero-filled gradient for the kept buffer
+    out, xs, a1 = output
+    ctx.mark_non_differentiable(xs, a1)
+    # without this autograd would hand the backward zero-filled gradients for the kept buffers
     ctx.set_materialize_grads(False)
     if not save_for_backward:
         raise RuntimeError("moe_experts was run with save_for_backward=False but a gradient is "
                            "being recorded; call it through fused_moe_forward")
-    saved = [x, a1, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts,
+    saved = [x, xs, a1, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts,
              n_post_pad, inv_ids]
     ctx.has_shared = w_sh_in is not None
     if ctx.has_shared:
@@ -273,14 +282,14 @@ def _experts_setup(ctx, inputs, output):
     ctx.activation = activation
 
 
-def _experts_backward(ctx, grad_out, g_a1):
-    (x, a1, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts, n_post_pad,
+def _experts_backward(ctx, grad_out, g_xs, g_a1):
+    (x, xs, a1, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts, n_post_pad,
      inv_ids, *rest) = ctx.saved_tensors
     w_sh_in, w_sh_out = (rest[0], rest[1]) if ctx.has_shared else (None, None)
     if grad_out is None:
         grad_out = torch.zeros_like(x)
     dx, dw_in, dw_out, dtw, dsi, dso = moe_experts_bwd(
-        grad_out, x, a1, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
+        grad_out, x, xs, a1, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
         pad_offsets, counts, n_post_pad, inv_ids, ctx.activation)
     return (dx, dw_in, dw_out, dtw, dsi if ctx.has_shared else None,
             dso if ctx.has_shared else None, None, None, None, None, None, None, None, None)
@@ -317,6 +326,6 @@ def fused_moe_forward(x, w_in, w_out, topk_w, topk_idx, b_in, b_out, activation,
     cast = lambda t: None if t is None else t.to(x.dtype)
     tensors = (x, w_in, w_out, topk_w, w_sh_in, w_sh_out)
     save = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
-    out, _ = moe_experts(x, cast(w_in), cast(w_out), topk_w, cast(w_sh_in), cast(w_sh_out), sids,
+    out, _, _ = moe_experts(x, cast(w_in), cast(w_out), topk_w, cast(w_sh_in), cast(w_sh_out), sids,
                          eids, offs, counts, npp, inv, activation, save)
     return out, counts[: w_in.shape[0]]
