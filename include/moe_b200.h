@@ -80,6 +80,34 @@ int moe_b200_router_topk_bwd(const float* logits, const int64_t* topk_idx, const
                              int32_t top_k, int32_t normalize, int32_t full_softmax,
                              float* d_logits, void* stream);
 
+/* Fused router step of the whole-block path: the selection / softmax arithmetic of
+ * moe_b200_router_topk, reading the bf16 logits [n_tokens, ld] the router GEMM wrote (plus an
+ * optional fp32 per-expert bias), writing w_all / idx_all [n_tokens, top_k + n_shared] (bf16 /
+ * int64) whose last n_shared columns are the shared experts as (expert n_experts + s, weight 1)
+ * pairs, and -- when full_softmax != 0 and colsum != NULL -- ADDING sum_t softmax(l_t)[e] into
+ * colsum[e] (fp32 [n_experts], zero it first), the only statistic balance_loss needs
+ * (src/model/router.py:100-111). No [T, E] fp32 tensor is written. */
+int moe_b200_router_fused(const void* logits, int32_t ld, const float* bias, int64_t n_tokens,
+                          int32_t n_experts, int32_t top_k, int32_t n_shared, int32_t normalize,
+                          int32_t full_softmax, void* w_all, int64_t* idx_all, float* colsum,
+                          void* stream);
+
+/* Backward of moe_b200_router_fused: d(logits) as bf16 [n_tokens, ld_out] (columns >= n_experts
+ * zero) from d(w_all) (bf16; the shared columns are ignored) and, when d_aux != NULL, the
+ * balance loss's gradient d_aux[0] * aux_coef * n_experts / n_tokens * counts[e] / sum(counts)
+ * on every probability of expert e (counts int32 [n_experts] from the dispatch). */
+int moe_b200_router_fused_bwd(const void* logits, int32_t ld, const float* bias,
+                              const int64_t* idx_all, const void* dw_all, int64_t n_tokens,
+                              int32_t n_experts, int32_t top_k, int32_t n_shared,
+                              int32_t normalize, int32_t full_softmax, const float* d_aux,
+                              const int32_t* counts, float aux_coef, void* d_logits,
+                              int32_t ld_out, void* stream);
+
+/* aux[0] = aux_coef * n_experts * sum_e (counts[e] / sum counts) * (colsum[e] / n_tokens):
+ * TopKRouter.balance_loss (src/model/router.py:100-111) from the column sums. */
+int moe_b200_balance_loss(const float* colsum, const int32_t* counts, int32_t n_experts,
+                          int64_t n_tokens, float aux_coef, float* aux, void* stream);
+
 /* Dispatch plan from topk_idx (flat [n_pairs] int64): replaces moe_dispatch and its four kernels
  * (src/model/moe_kernel.py:113-209) and MoEBlock._plan (src/model/moe.py:208-223).
  *   sorted_ids  [l_cap]      slot -> pair id, sentinel n_pairs in pad slots

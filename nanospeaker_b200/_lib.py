@@ -23,6 +23,16 @@ SIGNATURES = {
     "moe_b200_router_topk_bwd": (
         ctypes.c_int,
         [_c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp]),
+    "moe_b200_router_fused": (
+        ctypes.c_int,
+        [_c_vp, _c_i32, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp,
+         _c_vp]),
+    "moe_b200_router_fused_bwd": (
+        ctypes.c_int,
+        [_c_vp, _c_i32, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp,
+         _c_vp, ctypes.c_float, _c_vp, _c_i32, _c_vp]),
+    "moe_b200_balance_loss": (
+        ctypes.c_int, [_c_vp, _c_vp, _c_i32, _c_i64, ctypes.c_float, _c_vp, _c_vp]),
     "moe_b200_dispatch": (
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_sz, _c_vp,

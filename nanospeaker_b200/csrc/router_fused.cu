@@ -1,0 +1,384 @@
+// Router kernels of the whole-block op: the same selection and softmax arithmetic as
+// router_topk_kernel (routing.cu), but reading the bf16 logits the router GEMM wrote (row stride
+// `ld`, optional fp32 per-expert bias), writing weights in the activation dtype, appending the
+// shared experts as extra (expert E+s, weight 1) pairs, and reducing the balance-loss statistics
+// on the fly -- so that no [T, E] fp32 tensor (logits, probs, d_probs) ever goes through HBM.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "../../include/moe_b200.h"
+#include "routing.cuh"
+
+namespace moe {
+
+constexpr int RF_WARPS = 8;
+
+// Warps stride over tokens. Per token: winners by (value desc, index asc); weights as in
+// router_topk_kernel. colsum[e] += sum_t softmax(l_t)[e] (only when full_softmax and colsum given):
+// lane-local partial sums, one shared-memory reduction per block, one atomic per block and expert.
+template <int NSLOT>
+__global__ void __launch_bounds__(RF_WARPS * 32)
+    router_fused_kernel(const __nv_bfloat16* __restrict__ logits, int ld,
+                        const float* __restrict__ bias, int64_t n_tokens, int n_experts, int top_k,
+                        int n_shared, int normalize, int full_softmax,
+                        __nv_bfloat16* __restrict__ w_all, int64_t* __restrict__ idx_all,
+                        float* __restrict__ colsum) {
+  __shared__ float cs[RF_WARPS][NSLOT * 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int kS = top_k + n_shared;
+  const bool need_full = full_softmax || !normalize;
+  const bool want_colsum = full_softmax && colsum != nullptr;
+
+  float b[NSLOT], csum[NSLOT];
+#pragma unroll
+  for (int i = 0; i < NSLOT; ++i) {
+    const int e = i * 32 + lane;
+    b[i] = (bias != nullptr && e < n_experts) ? bias[e] : 0.f;
+    csum[i] = 0.f;
+  }
+
+  for (int64_t t = int64_t(blockIdx.x) * RF_WARPS + warp; t < n_tokens;
+       t += int64_t(gridDim.x) * RF_WARPS) {
+    const __nv_bfloat16* row = logits + t * ld;
+    float v[NSLOT];
+    uint32_t key[NSLOT];  // 0 = not a candidate (out of range or already taken)
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int i = 0; i < NSLOT; ++i) {
+      const int e = i * 32 + lane;
+      const bool in = e < n_experts;
+      v[i] = in ? __bfloat162float(row[e]) + b[i] : -CUDART_INF_F;
+      const uint32_t fk = float_key(v[i]);
+      key[i] = in ? (fk == 0u ? 1u : fk) : 0u;
+      mx = fmaxf(mx, v[i]);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+
+    float denom = 0.f;
+    if (need_full) {
+      float ex[NSLOT];
+#pragma unroll
+      for (int i = 0; i < NSLOT; ++i) {
+        ex[i] = (i * 32 + lane < n_experts) ? expf(v[i] - mx) : 0.f;
+        denom += ex[i];
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+      if (want_colsum) {
+#pragma unroll
+        for (int i = 0; i < NSLOT; ++i) csum[i] += ex[i] / denom;
+      }
+    }
+
+    float sel_val = 0.f;
+    int sel_idx = 0;
+    for (int j = 0; j < top_k; ++j) {
+      uint32_t best = 0u;
+#pragma unroll
+      for (int i = 0; i < NSLOT; ++i) best = key[i] > best ? key[i] : best;
+      const uint32_t top = __reduce_max_sync(0xffffffffu, best);
+      uint32_t cand = 0xFFFFFFFFu;
+#pragma unroll
+      for (int i = NSLOT - 1; i >= 0; --i)
+        if (key[i] == top) cand = uint32_t(i * 32 + lane);
+      const int e_win = int(__reduce_min_sync(0xffffffffu, cand));
+      const int owner = e_win & 31, slot = e_win >> 5;
+      float val = 0.f;
+#pragma unroll
+      for (int i = 0; i < NSLOT; ++i)
+        if (i == slot) {
+          val = v[i];
+          if (lane == owner) key[i] = 0u;
+        }
+      val = __shfl_sync(0xffffffffu, val, owner);
+      if (lane == j) {
+        sel_val = val;
+        sel_idx = e_win;
+      }
+    }
+
+    float wgt;
+    const bool active = lane < top_k;
+    if (need_full) {
+      wgt = active ? expf(sel_val - mx) / denom : 0.f;
+      if (normalize && top_k > 1 && full_softmax) {
+        float s = wgt;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        wgt = wgt / s;
+      }
+    } else {
+      const float top = __shfl_sync(0xffffffffu, sel_val, 0);
+      const float ex = active ? expf(sel_val - top) : 0.f;
+      float s = ex;
+#pragma unroll
+      for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      wgt = ex / s;
+    }
+    if (active) {
+      w_all[t * kS + lane] = __float2bfloat16(wgt);
+      idx_all[t * kS + lane] = sel_idx;
+    } else if (lane < kS) {  // the shared experts: every token, weight 1
+      w_all[t * kS + lane] = __float2bfloat16(1.f);
+      idx_all[t * kS + lane] = n_experts + (lane - top_k);
+    }
+  }
+
+  if (want_colsum) {
+#pragma unroll
+    for (int i = 0; i < NSLOT; ++i) cs[warp][i * 32 + lane] = csum[i];
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < RF_WARPS; ++w) s += cs[w][e];
+      atomicAdd(colsum + e, s);
+    }
+  }
+}
+
+// d(logits) as bf16 [T, ld_out] (columns >= n_experts zero) from d(w_all) (first top_k columns of
+// [T, top_k + n_shared], activation dtype) and the balance loss's gradient:
+//   aux = aux_scale_T * sum_e counts[e] / sum(counts) * colsum[e]
+//   => d colsum[e] = d_aux * aux_scale_T * counts[e] / (T * top_k), added to every d p[t, e].
+template <int NSLOT>
+__global__ void __launch_bounds__(RF_WARPS * 32)
+    router_fused_bwd_kernel(const __nv_bfloat16* __restrict__ logits, int ld,
+                            const float* __restrict__ bias, const int64_t* __restrict__ idx_all,
+                            const __nv_bfloat16* __restrict__ dw_all, int64_t n_tokens,
+                            int n_experts, int top_k, int n_shared, int normalize,
+                            int full_softmax, const float* __restrict__ d_aux,
+                            const int32_t* __restrict__ counts, float aux_scale_T,
+                            __nv_bfloat16* __restrict__ dl, int ld_out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int kS = top_k + n_shared;
+  const bool need_full = full_softmax || !normalize;
+
+  float b[NSLOT], dcs[NSLOT];
+  {
+    const float g = (d_aux != nullptr && full_softmax) ? *d_aux : 0.f;
+    const float denom_c = float(n_tokens) * float(top_k);
+#pragma unroll
+    for (int i = 0; i < NSLOT; ++i) {
+      const int e = i * 32 + lane;
+      b[i] = (bias != nullptr && e < n_experts) ? bias[e] : 0.f;
+      dcs[i] = (e < n_experts && g != 0.f) ? g * aux_scale_T * float(counts[e]) / denom_c : 0.f;
+    }
+  }
+
+  for (int64_t t = int64_t(blockIdx.x) * RF_WARPS + warp; t < n_tokens;
+       t += int64_t(gridDim.x) * RF_WARPS) {
+    const __nv_bfloat16* row = logits + t * ld;
+    __nv_bfloat16* out = dl + t * ld_out;
+    float v[NSLOT], dp[NSLOT];
+    float mx = -CUDART_INF_F;
+#pragma unroll
+    for (int i = 0; i < NSLOT; ++i) {
+      const int e = i * 32 + lane;
+      v[i] = e < n_experts ? __bfloat162float(row[e]) + b[i] : -CUDART_INF_F;
+      mx = fmaxf(mx, v[i]);
+      dp[i] = dcs[i];
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+
+    const bool active = lane < top_k;
+    const int my_idx = active ? int(idx_all[t * kS + lane]) : -1;
+    const float my_dw = active ? __bfloat162float(dw_all[t * kS + lane]) : 0.f;
+    // my winner's logit, taken from the lane that holds it
+    float my_l = -CUDART_INF_F;
+    for (int j = 0; j < top_k; ++j) {
+      const int e = __shfl_sync(0xffffffffu, my_idx, j);
+      float val = 0.f;
+#pragma unroll
+      for (int i = 0; i < NSLOT; ++i)
+        if (i == (e >> 5)) val = v[i];
+      val = __shfl_sync(0xffffffffu, val, e & 31);
+      if (lane == j) my_l = val;
+    }
+
+    float res[NSLOT];
+    if (!need_full) {
+      float top = my_l;
+#pragma unroll
+      for (int o = 16; o; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+      const float ex = active ? expf(my_l - top) : 0.f;
+      float s = ex;
+#pragma unroll
+      for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      const float w = ex / s;
+      float dot = w * my_dw;
+#pragma unroll
+      for (int o = 16; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float mine = w * (my_dw - dot);
+#pragma unroll
+      for (int i = 0; i < NSLOT; ++i) res[i] = 0.f;
+      for (int j = 0; j < top_k; ++j) {
+        const int e = __shfl_sync(0xffffffffu, my_idx, j);
+        const float d = __shfl_sync(0xffffffffu, mine, j);
+        if ((e & 31) == lane) {
+#pragma unroll
+          for (int i = 0; i < NSLOT; ++i)
+            if (i == (e >> 5)) res[i] = d;
+        }
+      }
+    } else {
+      float pr[NSLOT];
+      float denom = 0.f;
+#pragma unroll
+      for (int i = 0; i < NSLOT; ++i) {
+        pr[i] = (i * 32 + lane < n_experts) ? expf(v[i] - mx) : 0.f;
+        denom += pr[i];
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+#pragma unroll
+      for (int i = 0; i < NSLOT; ++i) pr[i] /= denom;
+      const float my_p = active ? expf(my_l - mx) / denom : 0.f;
+      float my_dp = my_dw;
+      if (normalize && top_k > 1 && full_softmax) {
+        float s = my_p;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float w = my_p / s;
+        float dot = my_dw * w;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        my_dp = (my_dw - dot) / s;
+      }
+      for (int j = 0; j < top_k; ++j) {
+        const int e = __shfl_sync(0xffffffffu, my_idx, j);
+        const float d = __shfl_sync(0xffffffffu, my_dp, j);
+        if ((e & 31) == lane) {
+#pragma unroll
+          for (int i = 0; i < NSLOT; ++i)
+            if (i == (e >> 5)) dp[i] += d;
+        }
+      }
+      float inner = 0.f;
+#pragma unroll
+      for (int i = 0; i < NSLOT; ++i) inner += pr[i] * dp[i];
+#pragma unroll
+      for (int o = 16; o; o >>= 1) inner += __shfl_xor_sync(0xffffffffu, inner, o);
+#pragma unroll
+      for (int i = 0; i < NSLOT; ++i) res[i] = pr[i] * (dp[i] - inner);
+    }
+#pragma unroll
+    for (int i = 0; i < NSLOT; ++i) {
+      const int e = i * 32 + lane;
+      if (e < n_experts) out[e] = __float2bfloat16(res[i]);
+    }
+    for (int e = NSLOT * 32 + lane; e < ld_out; e += 32) out[e] = __float2bfloat16(0.f);
+    // pad columns inside the NSLOT range
+#pragma unroll
+    for (int i = 0; i < NSLOT; ++i) {
+      const int e = i * 32 + lane;
+      if (e >= n_experts && e < ld_out) out[e] = __float2bfloat16(0.f);
+    }
+  }
+}
+
+// aux[0] = coef * E * sum_e (counts[e] / sum counts) * (colsum[e] / T)   (one warp)
+__global__ void balance_loss_kernel(const float* __restrict__ colsum,
+                                    const int32_t* __restrict__ counts, int n_experts,
+                                    int64_t n_tokens, float coef, float* __restrict__ aux) {
+  const int lane = threadIdx.x;
+  float dot = 0.f, tot = 0.f;
+  for (int e = lane; e < n_experts; e += 32) {
+    const float c = float(counts[e]);
+    dot += c * colsum[e];
+    tot += c;
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    tot += __shfl_xor_sync(0xffffffffu, tot, o);
+  }
+  if (lane == 0)
+    aux[0] = coef * float(n_experts) * dot / fmaxf(tot, 1.f) / float(n_tokens > 0 ? n_tokens : 1);
+}
+
+static unsigned rf_grid(int64_t n_tokens) {
+  const int64_t want = (n_tokens + RF_WARPS - 1) / RF_WARPS;
+  const int64_t cap = 148 * 4;  // a few blocks per SM; warps stride over the tokens
+  return unsigned(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
+}  // namespace moe
+
+using namespace moe;
+
+extern "C" {
+
+int moe_b200_router_fused(const void* logits, int32_t ld, const float* bias, int64_t n_tokens,
+                          int32_t n_experts, int32_t top_k, int32_t n_shared, int32_t normalize,
+                          int32_t full_softmax, void* w_all, int64_t* idx_all, float* colsum,
+                          void* stream) {
+  if (n_experts < 1 || n_experts > MAX_EXPERTS || top_k < 1 || top_k > n_experts ||
+      n_shared < 0 || top_k + n_shared > 32 || top_k > MAX_TOPK || n_tokens < 0 || ld < n_experts)
+    return MOE_B200_ERR_SHAPE;
+  if (n_tokens == 0) return MOE_B200_OK;
+  if (!logits || !w_all || !idx_all) return MOE_B200_ERR_NULL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = rf_grid(n_tokens);
+  const __nv_bfloat16* lg = static_cast<const __nv_bfloat16*>(logits);
+  __nv_bfloat16* w = static_cast<__nv_bfloat16*>(w_all);
+#define LAUNCH(NS)                                                                              \
+  router_fused_kernel<NS><<<grid, RF_WARPS * 32, 0, st>>>(lg, ld, bias, n_tokens, n_experts, top_k, \
+                                                          n_shared, normalize, full_softmax, w,    \
+                                                          idx_all, colsum)
+  const int nslot = (n_experts + 31) / 32;
+  if (nslot <= 1) LAUNCH(1);
+  else if (nslot <= 2) LAUNCH(2);
+  else if (nslot <= 3) LAUNCH(3);
+  else if (nslot <= 4) LAUNCH(4);
+  else LAUNCH(8);
+#undef LAUNCH
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+int moe_b200_router_fused_bwd(const void* logits, int32_t ld, const float* bias,
+                              const int64_t* idx_all, const void* dw_all, int64_t n_tokens,
+                              int32_t n_experts, int32_t top_k, int32_t n_shared,
+                              int32_t normalize, int32_t full_softmax, const float* d_aux,
+                              const int32_t* counts, float aux_coef, void* d_logits,
+                              int32_t ld_out, void* stream) {
+  if (n_experts < 1 || n_experts > MAX_EXPERTS || top_k < 1 || top_k > n_experts ||
+      n_shared < 0 || top_k + n_shared > 32 || top_k > MAX_TOPK || n_tokens < 0 ||
+      ld < n_experts || ld_out < n_experts)
+    return MOE_B200_ERR_SHAPE;
+  if (n_tokens == 0) return MOE_B200_OK;
+  if (!logits || !idx_all || !dw_all || !d_logits || (d_aux && !counts)) return MOE_B200_ERR_NULL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = rf_grid(n_tokens);
+  const float scale = aux_coef * float(n_experts) / float(n_tokens);
+  const __nv_bfloat16* lg = static_cast<const __nv_bfloat16*>(logits);
+  const __nv_bfloat16* dw = static_cast<const __nv_bfloat16*>(dw_all);
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(d_logits);
+#define LAUNCH(NS)                                                                               \
+  router_fused_bwd_kernel<NS><<<grid, RF_WARPS * 32, 0, st>>>(                                    \
+      lg, ld, bias, idx_all, dw, n_tokens, n_experts, top_k, n_shared, normalize, full_softmax,   \
+      d_aux, counts, scale, out, ld_out)
+  const int nslot = (n_experts + 31) / 32;
+  if (nslot <= 1) LAUNCH(1);
+  else if (nslot <= 2) LAUNCH(2);
+  else if (nslot <= 3) LAUNCH(3);
+  else if (nslot <= 4) LAUNCH(4);
+  else LAUNCH(8);
+#undef LAUNCH
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+int moe_b200_balance_loss(const float* colsum, const int32_t* counts, int32_t n_experts,
+                          int64_t n_tokens, float aux_coef, float* aux, void* stream) {
+  if (n_experts < 1 || n_tokens < 0) return MOE_B200_ERR_SHAPE;
+  if (!colsum || !counts || !aux) return MOE_B200_ERR_NULL;
+  balance_loss_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(colsum, counts, n_experts,
+                                                                        n_tokens, aux_coef, aux);
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -14,22 +14,11 @@
 
 #include "../../include/moe_b200.h"
 #include "gemm.cuh"  // DevStatus
+#include "routing.cuh"
 
 namespace moe {
 
 constexpr int ALIGN_M = 128;
-constexpr int MAX_EXPERTS = 256;            // router + dispatch kernels keep per-expert state on chip
-constexpr int MAX_TOPK = 16;
-
-// ----------------------------------------------------------------------------- router top-k
-// Order-preserving map fp32 -> uint32 (larger float -> larger key); NaN sorts above +inf and
-// -0.0 ties with +0.0, so ties between equal values fall to the lowest expert index below.
-__device__ __forceinline__ uint32_t float_key(float f) {
-  if (f != f) return 0xFFFFFFFFu;
-  if (f == 0.f) f = 0.f;
-  uint32_t u = __float_as_uint(f);
-  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
 
 // One warp per token; lane l holds experts l, l+32, ... (NSLOT of them). A winner is found with two
 // hardware warp reductions: the largest key, then the smallest expert index among the lanes that

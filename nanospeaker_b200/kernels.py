@@ -97,6 +97,51 @@ def router_topk_bwd(logits, topk_idx, d_topk_w, d_probs, normalize: bool,
     return out
 
 
+def router_fused(logits, bias, n_experts: int, top_k: int, n_shared: int, normalize: bool,
+                 full_softmax: bool):
+    """bf16 logits [T, ld] (+ fp32 bias [E]) -> (w_all bf16 [T, k+S], idx_all int64 [T, k+S],
+    colsum fp32 [E] or None). The last S columns are the shared experts (id E+s, weight 1)."""
+    _need_cuda(logits)
+    t, ld = logits.shape
+    ks = top_k + n_shared
+    w_all = torch.empty((t, ks), dtype=logits.dtype, device=logits.device)
+    idx_all = torch.empty((t, ks), dtype=torch.int64, device=logits.device)
+    colsum = (torch.zeros(n_experts, dtype=torch.float32, device=logits.device)
+              if full_softmax else None)
+    _lib.check(_lib.load().moe_b200_router_fused(
+        logits.data_ptr(), ld, _lib.ptr(bias), t, n_experts, top_k, n_shared, int(normalize),
+        int(full_softmax), w_all.data_ptr(), idx_all.data_ptr(), _lib.ptr(colsum),
+        _stream(logits)), "moe_b200_router_fused")
+    _count(1 if t else 0)
+    return w_all, idx_all, colsum
+
+
+def router_fused_bwd(logits, bias, idx_all, dw_all, n_experts: int, top_k: int, n_shared: int,
+                     normalize: bool, full_softmax: bool, d_aux, counts, aux_coef: float,
+                     ld_out: int) -> torch.Tensor:
+    """-> d(logits) bf16 [T, ld_out], zero in the pad columns."""
+    _need_cuda(logits, idx_all, dw_all)
+    t, ld = logits.shape
+    out = torch.empty((t, ld_out), dtype=logits.dtype, device=logits.device)
+    _lib.check(_lib.load().moe_b200_router_fused_bwd(
+        logits.data_ptr(), ld, _lib.ptr(bias), idx_all.data_ptr(), dw_all.data_ptr(), t,
+        n_experts, top_k, n_shared, int(normalize), int(full_softmax), _lib.ptr(d_aux),
+        _lib.ptr(counts), float(aux_coef), out.data_ptr(), ld_out, _stream(logits)),
+        "moe_b200_router_fused_bwd")
+    _count(1 if t else 0)
+    return out
+
+
+def balance_loss(colsum, counts, n_experts: int, n_tokens: int, aux_coef: float) -> torch.Tensor:
+    """0-dim fp32: aux_coef * E * sum_e share_e * mean_t probs[t, e], from the column sums."""
+    aux = torch.empty((), dtype=torch.float32, device=colsum.device)
+    _lib.check(_lib.load().moe_b200_balance_loss(
+        colsum.data_ptr(), counts.data_ptr(), n_experts, n_tokens, float(aux_coef),
+        aux.data_ptr(), _stream(colsum)), "moe_b200_balance_loss")
+    _count(1)
+    return aux
+
+
 def dispatch(topk_idx: torch.Tensor, n_experts: int):
     """int64 topk_idx [T, k] -> (sorted_ids, expert_ids, pad_offsets, counts, n_post_pad, inv_ids)."""
     _need_cuda(topk_idx)

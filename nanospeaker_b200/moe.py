@@ -23,7 +23,8 @@ from torch import nn
 
 from . import moe_kernel as MK
 from .glu import glu_hidden_dim, make_glu
-from .moe_kernel import KERNEL_ACTIVATIONS, fused_moe_forward, kernel_supported
+from .moe_kernel import (KERNEL_ACTIVATIONS, fused_moe_block, fused_moe_forward,
+                         kernel_supported)
 from .router import TopKRouter
 from .utils import ACTIVATIONS, resolve_activation
 
@@ -194,6 +195,16 @@ class MoEBlock(nn.Module):
         x = x.reshape(-1, self.d_model)
         if x.shape[0] == 0:
             return x.clone().view(shape)
+        if self._use_kernel(x) and not (self.training and self.router.noise_std):
+            # whole block as one op: router GEMM, top-k, dispatch, experts, combine, balance loss
+            full = self.router.wants_probs()
+            out, aux, counts = fused_moe_block(
+                x, self.router, self.W_in, self.W_out, self.W_sh_in, self.W_sh_out,
+                self._kernel_act, full)
+            self.expert_counts = counts.detach()
+            self.aux_loss = aux if full else torch.zeros((), device=x.device, dtype=x.dtype)
+            return out.view(shape)
+
         topk_w, topk_idx, probs = self.router(x)
 
         if self._use_kernel(x):

@@ -298,6 +298,219 @@ def _experts_backward(ctx, grad_out, g_xs, g_a1):
 moe_experts.register_autograd(_experts_backward, setup_context=_experts_setup)
 
 
+# ------------------------------------------------------------------------------- whole block
+_T15 = Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]
+_T6 = Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]
+
+
+def _router_ld(n_experts: int) -> int:
+    """Column count the router logits are padded to: TMA tiles of the padded router weight are
+    64 columns wide."""
+    return (n_experts + 63) // 64 * 64
+
+
+@torch.library.custom_op("moe_b200::moe_block", mutates_args=())
+def moe_block(
+    x: torch.Tensor,
+    router_w: torch.Tensor,
+    logit_bias: Optional[torch.Tensor],
+    w_in: torch.Tensor,
+    w_out: torch.Tensor,
+    w_sh_in: Optional[torch.Tensor],
+    w_sh_out: Optional[torch.Tensor],
+    top_k: int,
+    normalize: bool,
+    full_softmax: bool,
+    aux_coef: float,
+    activation: str,
+    save_for_backward: bool,
+) -> _T15:
+    """The whole MoE block as one op: router GEMM, top-k, dispatch, experts (routed + shared),
+    combine and the balance loss, with no PyTorch glue kernels in between
+    (MoEBlock.forward, src/model/moe.py:345-375, with TopKRouter.forward and balance_loss inlined).
+
+    Returns [out, aux (fp32, 0-dim), counts (int32 [E]), then what the backward needs: xs, a1,
+    logits, w_all, idx_all, sorted_ids, expert_ids, pad_offsets, counts_all, n_post_pad, inv_ids,
+    router_w_padded]. The router GEMM runs on the same tcgen05 kernels as the experts against a
+    copy of router_w zero-padded to a multiple of 64 columns, so the logits are [T, ld] bf16.
+    """
+    x, w_in, w_out = x.contiguous(), w_in.contiguous(), w_out.contiguous()
+    _check_inputs(x, w_in, w_out, w_sh_in)
+    act = _act_id(activation)
+    n, d = x.shape
+    e_n = w_in.shape[0]
+    s_n = 0 if w_sh_in is None else w_sh_in.shape[0]
+    if w_sh_in is not None:
+        w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
+    ld = _router_ld(e_n)
+    ks = top_k + s_n
+
+    wp = x.new_zeros((1, d, ld))
+    wp[0, :, :e_n] = router_w
+    logits = K.down_gemm(x, wp, None, None, 1, None, None, 0)[0]
+    w_all, idx_all, colsum = K.router_fused(logits, logit_bias, e_n, top_k, s_n, normalize,
+                                            full_softmax)
+    sids, eids, offs, counts_all, npp, inv = K.dispatch(idx_all, e_n + s_n)
+    tw = w_all.reshape(-1)
+    m = n * ks
+    if save_for_backward:
+        xs = K.permute(x, ks, sids, npp)
+        hid, a1 = K.up_gemm(xs, w_in, eids, npp, 0, act, True, w_extra=w_sh_in)
+    else:
+        xs, a1 = x.new_empty(0), x.new_empty(0)
+        hid, _ = K.up_gemm(x, w_in, eids, npp, 0, act, False, gather=(sids, ks), w_extra=w_sh_in)
+    y = K.down_gemm(hid, w_out, eids, npp, 0, sids, tw, m, w_extra=w_sh_out)
+    out = K.combine(y, inv, n, ks)
+    if full_softmax:
+        aux = K.balance_loss(colsum, counts_all, e_n, n, aux_coef)
+    else:
+        aux = torch.zeros((), dtype=torch.float32, device=x.device)
+    return (out, aux, counts_all[:e_n].clone(), xs, a1, logits, w_all, idx_all, sids, eids, offs,
+            counts_all, npp, inv, wp)
+
+
+@moe_block.register_fake
+def _(x, router_w, logit_bias, w_in, w_out, w_sh_in, w_sh_out, top_k, normalize, full_softmax,
+      aux_coef, activation, save_for_backward):
+    n, d = x.shape
+    e_n = w_in.shape[0]
+    s_n = 0 if w_sh_in is None else w_sh_in.shape[0]
+    ld, ks = _router_ld(e_n), top_k + s_n
+    cap = _l_cap(n * ks, e_n + s_n)
+    i32 = lambda *shape: x.new_empty(shape, dtype=torch.int32)
+    kept = (x.new_empty((cap, d)), x.new_empty((cap, w_in.shape[2]))) if save_for_backward \
+        else (x.new_empty(0), x.new_empty(0))
+    return (x.new_empty(x.shape), x.new_empty((), dtype=torch.float32), i32(e_n), kept[0], kept[1],
+            x.new_empty((n, ld)), x.new_empty((n, ks)), x.new_empty((n, ks), dtype=torch.int64),
+            i32(cap), i32(cap // ALIGN_M), i32(e_n + s_n + 1), i32(e_n + s_n), i32(1), i32(n * ks),
+            x.new_empty((1, d, ld)))
+
+
+@torch.library.custom_op("moe_b200::moe_block_bwd", mutates_args=())
+def moe_block_bwd(
+    grad_out: torch.Tensor,
+    grad_aux: Optional[torch.Tensor],
+    x: torch.Tensor,
+    logit_bias: Optional[torch.Tensor],
+    w_in: torch.Tensor,
+    w_out: torch.Tensor,
+    w_sh_in: Optional[torch.Tensor],
+    w_sh_out: Optional[torch.Tensor],
+    xs: torch.Tensor,
+    a1: torch.Tensor,
+    logits: torch.Tensor,
+    w_all: torch.Tensor,
+    idx_all: torch.Tensor,
+    sorted_ids: torch.Tensor,
+    expert_ids: torch.Tensor,
+    pad_offsets: torch.Tensor,
+    counts_all: torch.Tensor,
+    n_post_pad: torch.Tensor,
+    inv_ids: torch.Tensor,
+    router_w_padded: torch.Tensor,
+    top_k: int,
+    normalize: bool,
+    full_softmax: bool,
+    aux_coef: float,
+    activation: str,
+) -> _T6:
+    """[dx, d_router_w (padded [D, ld]), dW_in, dW_out, dW_sh_in, dW_sh_out] of moe_block."""
+    grad_out = grad_out.to(x.dtype).contiguous()
+    act = _act_id(activation)
+    n, d = x.shape
+    e_n = w_in.shape[0]
+    s_n = 0 if w_sh_in is None else w_sh_in.shape[0]
+    ks = top_k + s_n
+    m = n * ks
+    tw = w_all.reshape(-1)
+
+    douts = K.permute(grad_out, ks, sorted_ids, n_post_pad)
+    da1, hidw, dtw = K.dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m,
+                                       a1, act, True, w_extra=w_sh_out)
+    ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
+    g_in = K.wgrad(xs, da1, pad_offsets, e_n + s_n, n_extra=s_n)
+    g_out = K.wgrad(hidw, douts, pad_offsets, e_n + s_n, n_extra=s_n)
+    if s_n:
+        (dw_in, dw_sh_in), (dw_out, dw_sh_out) = g_in, g_out
+    else:
+        dw_in, dw_out, dw_sh_in, dw_sh_out = g_in, g_out, x.new_empty(0), x.new_empty(0)
+    # router: d(logits) from d(topk_w) and the balance loss, then the two router GEMMs
+    d_aux = None if grad_aux is None else grad_aux.to(torch.float32).reshape(1)
+    dl = K.router_fused_bwd(logits, logit_bias, idx_all, dtw.view(n, ks), e_n, top_k, s_n,
+                            normalize, full_softmax, d_aux, counts_all, aux_coef, logits.shape[1])
+    d_wp = K.wgrad(x, dl, None, 1)[0]
+    dx_router = K.dx_gemm(dl, router_w_padded, None, None, 1)[0]
+    dx = K.combine(ydx, inv_ids, n, ks, dx_router)
+    return dx, d_wp, dw_in, dw_out, dw_sh_in, dw_sh_out
+
+
+@moe_block_bwd.register_fake
+def _(grad_out, grad_aux, x, logit_bias, w_in, w_out, w_sh_in, w_sh_out, xs, a1, logits, w_all,
+      idx_all, sorted_ids, expert_ids, pad_offsets, counts_all, n_post_pad, inv_ids,
+      router_w_padded, top_k, normalize, full_softmax, aux_coef, activation):
+    return (torch.empty_like(x), x.new_empty(router_w_padded.shape[1:]), torch.empty_like(w_in),
+            torch.empty_like(w_out),
+            torch.empty_like(w_sh_in) if w_sh_in is not None else x.new_empty(0),
+            torch.empty_like(w_sh_out) if w_sh_out is not None else x.new_empty(0))
+
+
+def _block_setup(ctx, inputs, output):
+    (x, router_w, logit_bias, w_in, w_out, w_sh_in, w_sh_out, top_k, normalize, full_softmax,
+     aux_coef, activation, save_for_backward) = inputs
+    ctx.mark_non_differentiable(*output[2:])
+    ctx.set_materialize_grads(False)
+    if not save_for_backward:
+        raise RuntimeError("moe_block was run with save_for_backward=False but a gradient is "
+                           "being recorded")
+    ctx.has_shared = w_sh_in is not None
+    ctx.has_bias = logit_bias is not None
+    saved = [x, w_in, w_out] + list(output[3:])
+    if ctx.has_shared:
+        saved += [w_sh_in, w_sh_out]
+    if ctx.has_bias:
+        saved.append(logit_bias)
+    ctx.save_for_backward(*saved)
+    ctx.n_experts = w_in.shape[0]
+    ctx.router_dtype = router_w.dtype
+    ctx.args = (top_k, normalize, full_softmax, aux_coef, activation)
+
+
+def _block_backward(ctx, grad_out, grad_aux, *unused):
+    saved = list(ctx.saved_tensors)
+    x, w_in, w_out = saved[:3]
+    kept = saved[3:15]
+    rest = saved[15:]
+    w_sh_in, w_sh_out = (rest[0], rest[1]) if ctx.has_shared else (None, None)
+    bias = rest[-1] if ctx.has_bias else None
+    if grad_out is None:
+        grad_out = torch.zeros_like(x)
+    dx, d_wp, dw_in, dw_out, dsi, dso = moe_block_bwd(
+        grad_out, grad_aux, x, bias, w_in, w_out, w_sh_in, w_sh_out, *kept, *ctx.args)
+    d_router = d_wp[:, : ctx.n_experts].to(ctx.router_dtype)
+    return (dx, d_router, None, dw_in, dw_out, dsi if ctx.has_shared else None,
+            dso if ctx.has_shared else None, None, None, None, None, None, None)
+
+
+moe_block.register_autograd(_block_backward, setup_context=_block_setup)
+
+
+def fused_moe_block(x, router, w_in, w_out, w_sh_in, w_sh_out, activation, full_softmax):
+    """(out, aux_loss fp32, counts int32 [E]) for a TopKRouter-like `router` (attributes W,
+    logit_bias, top_k, normalize_weights, aux_loss_coef) -- the path MoEBlock.forward takes
+    whenever no exploration noise has to be added to the logits."""
+    _act_id(activation)
+    cast = lambda t: None if t is None else t.to(x.dtype)
+    tensors = (x, router.W, w_in, w_out, w_sh_in, w_sh_out)
+    save = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
+    bias = router.logit_bias
+    if bias is not None:
+        bias = bias.to(torch.float32).contiguous()
+    res = moe_block(x, cast(router.W), bias, cast(w_in), cast(w_out), cast(w_sh_in),
+                    cast(w_sh_out), router.top_k, bool(router.normalize_weights),
+                    bool(full_softmax), float(router.aux_loss_coef), activation, save)
+    return res[0], res[1], res[2]
+
+
 # ------------------------------------------------------------------------------- entry point
 def fused_moe_forward(x, w_in, w_out, topk_w, topk_idx, b_in, b_out, activation,
                       w_sh_in=None, w_sh_out=None):
