@@ -226,18 +226,27 @@ def build_stages(m, x):
         y = copies(K.down_gemm(hid[0], m.W_out, eids, npp, 0, sids, tw, M, w_extra=m.W_sh_out))
         da1 = copies(K.dhidden_glu_bwd(xs[0], m.W_out, eids, npp, 0, sids, tw, M, a1, 0, True,
                                        w_extra=m.W_sh_out)[0])
-        dwl = torch.randn_like(w, dtype=torch.float32)
+        from nanospeaker_b200.moe_kernel import _router_ld
+        ld = _router_ld(E)
+        wp = x.new_zeros((1, D, ld))
+        wp[0, :, :E] = m.router.W
+        logits_p = K.down_gemm(x, wp, None, None, 1, None, None, 0)[0]
+        bias = m.router.logit_bias
+        _, _, colsum = K.router_fused(logits_p, bias, E, k, S, True, True)
+        dtw = w_all.clone()
+        d_aux = torch.ones(1, device=x.device)
+        dl = copies(K.router_fused_bwd(logits_p, bias, idx_all, dtw, E, k, S, True, True, d_aux,
+                                       counts, 1e-2, ld))
 
         GE, TF = "hbm", "tensor"
-        # M counts routed and shared pairs alike: (k + S) * T rows go through every GEMM.
-        # Training path: permute once per direction, TMA-fed GEMMs. The gathered variants (used by
-        # the inference forward) are listed with 0 launches per step.
+        # One entry per kernel launch of the block op's forward + backward, in launch order.
+        # M counts routed and shared pairs alike: (k + S) * T rows go through every expert GEMM.
         stages = [
             # name, bound, work per launch (bytes or flop), launches per step, callable(i)
-            ("router_topk", GE, T * E * 4 * 2 + T * k * 12, 1,
-             lambda i: K.router_topk(logits, k, True, True, True)),
-            ("router_topk_bwd", GE, T * E * 4 * 3 + T * k * 12, 1,
-             lambda i: K.router_topk_bwd(logits, idx, dwl, logits, True, True)),
+            ("router GEMM x@W (padded to %d cols)" % ld, TF, 2.0 * T * D * E, 1,
+             lambda i: K.down_gemm(xr[i % 3], wp, None, None, 1, None, None, 0)),
+            ("router_fused (top-k, softmax, colsum)", GE, T * ld * 2 + T * ka * 10, 1,
+             lambda i: K.router_fused(logits_p, bias, E, k, S, True, True)),
             ("dispatch(3 kernels)", GE, M * 8 * 2 + M * 4 * 3, 1,
              lambda i: K.dispatch(idx_all, Ea)),
             ("permute", GE, 2 * M * D * 2 + M * 4, 2,
@@ -252,15 +261,23 @@ def build_stages(m, x):
                                    w_extra=m.W_sh_out)),
             ("combine", GE, M * D * 2 + M * 4 + T * D * 2, 2,
              lambda i: K.combine(y[i % 3], inv, T, ka)),
+            ("balance_loss", GE, E * 8, 1, lambda i: K.balance_loss(colsum, counts, E, T, 1e-2)),
             ("dhidden+glu_bwd", TF, 2.0 * M * D * H, 1,
              lambda i: K.dhidden_glu_bwd(xs[i % 3], m.W_out, eids, npp, 0, sids, tw, M, a1, 0,
                                          True, w_extra=m.W_sh_out)),
             ("dx_gemm", TF, 2.0 * M * 2 * H * D, 1,
              lambda i: K.dx_gemm(da1[i % 3], m.W_in, eids, npp, 0, w_extra=m.W_sh_in)),
-            ("wgrad_in", TF, 2.0 * M * D * 2 * H, 1,
+            ("wgrad_in (gemm + reduce)", TF, 2.0 * M * D * 2 * H, 1,
              lambda i: K.wgrad(xs[i % 3], da1[i % 3], offs, Ea, n_extra=S)),
-            ("wgrad_out", TF, 2.0 * M * H * D, 1,
+            ("wgrad_out (gemm + reduce)", TF, 2.0 * M * H * D, 1,
              lambda i: K.wgrad(hid[i % 3], xs[i % 3], offs, Ea, n_extra=S)),
+            ("router_fused_bwd", GE, T * ld * 2 * 2 + T * ka * 10, 1,
+             lambda i: K.router_fused_bwd(logits_p, bias, idx_all, dtw, E, k, S, True, True,
+                                          d_aux, counts, 1e-2, ld)),
+            ("router wgrad x^T@dl (gemm + reduce)", TF, 2.0 * T * D * E, 1,
+             lambda i: K.wgrad(xr[i % 3], dl[i % 3], None, 1)),
+            ("router dx dl@W^T", TF, 2.0 * T * D * E, 1,
+             lambda i: K.dx_gemm(dl[i % 3], wp, None, None, 1)),
         ]
     return stages
 
@@ -405,6 +422,7 @@ def run_ours(args):
             ms = float(t)
         return ms, t0, time.time()
 
+    torch.autograd.graph.set_warn_on_accumulate_grad_stream_mismatch(False)
     warmup = max(args.warmup, 3)
     use_graph = not args.no_graph and not (args.grad_allreduce and world > 1)
     eager_ms, _, _ = timed(step, args.steps, warmup)
