@@ -357,10 +357,22 @@ __global__ void __launch_bounds__(256)
     if (n_c <= 1) continue;
     for (int f = slice * per_slice + threadIdx.x; f < (slice + 1) * per_slice; f += blockDim.x) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int c2 = 0; c2 < n_c; ++c2) {
-        const float4 v = __ldcs(
-            reinterpret_cast<const float4*>(
-                p.partials + ((int64_t(first) + c2) * tiles_xy + tile_xy) * slot_elems) + f);
+      const float4* src = reinterpret_cast<const float4*>(
+                              p.partials + (int64_t(first) * tiles_xy + tile_xy) * slot_elems) + f;
+      const int64_t stride4 = tiles_xy * slot_elems / 4;  // float4 between consecutive chunks
+      // loads of 8 chunks are issued together (they are independent); the adds stay in chunk order
+      int c2 = 0;
+      for (; c2 + 8 <= n_c; c2 += 8) {
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = __ldcs(src + (c2 + u) * stride4);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
+        }
+      }
+      for (; c2 < n_c; ++c2) {
+        const float4 v = __ldcs(src + c2 * stride4);
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
       }
       // partial layout [column chunk][row][32 floats]

@@ -303,7 +303,7 @@ __global__ void balance_loss_kernel(const float* __restrict__ colsum,
 
 static unsigned rf_grid(int64_t n_tokens) {
   const int64_t want = (n_tokens + RF_WARPS - 1) / RF_WARPS;
-  const int64_t cap = 148 * 4;  // a few blocks per SM; warps stride over the tokens
+  const int64_t cap = 148 * 16;  // one wave of resident blocks; warps stride over the tokens
   return unsigned(want < cap ? (want > 0 ? want : 1) : cap);
 }
 

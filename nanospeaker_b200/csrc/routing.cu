@@ -287,7 +287,19 @@ __global__ void __launch_bounds__(1024)
   const int e = threadIdx.x;
   if (e < n_experts) {
     int32_t run = 0;
-    for (int b = 0; b < n_blocks; ++b) {
+    // loads are issued 8 blocks at a time so their latencies overlap
+    int b = 0;
+    for (; b + 8 <= n_blocks; b += 8) {
+      int32_t c[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) c[u] = block_hist[int64_t(b + u) * n_experts + e];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        block_hist[int64_t(b + u) * n_experts + e] = run;
+        run += c[u];
+      }
+    }
+    for (; b < n_blocks; ++b) {
       const int32_t c = block_hist[int64_t(b) * n_experts + e];
       block_hist[int64_t(b) * n_experts + e] = run;
       run += c;
