@@ -35,6 +35,10 @@ BIAS_STD = 0.27          # logit-bias spread that gives load CV ~ 1 with router 
 N_INPUT_SETS = 8         # x / dOut pairs cycled through so successive steps do not hit L2
 METRIC = "MoE-block tokens/s (fwd+bwd)"
 
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels that have
+# been captured with `ncu --set full` on this workload; see profiles/ncu_permute_and_wgrad_T16384.md.
+NCU_TRAFFIC_BYTES = {"permute": 176.1e6, "wgrad_in (gemm + reduce)": 265.3e6}
+
 FLOP_PER_TOKEN_FWD_BWD = 10_879_488   # 3 * (routed up 1 769 472 + down 884 736 + shared 884 736 + router 87 552)
 
 
@@ -511,7 +515,8 @@ def run_ours(args):
             top = max(stages, key=lambda s: s["us"] * s["launches_per_step"])
             line["roofline"] = {"kernel": top["kernel"], "bound": top["bound"],
                                 "achieved": top["achieved"], "peak": top["peak"],
-                                "unit": top["unit"], "frac": top["frac"], "traffic": None,
+                                "unit": top["unit"], "frac": top["frac"],
+                                "traffic": NCU_TRAFFIC_BYTES.get(top["kernel"]),
                                 "peak_source": pk["source"] + " (burst: kernel timed alone)"}
             line["stages"] = stages
     if world > 1:
