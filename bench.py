@@ -253,7 +253,8 @@ def build_stages(m, x):
              lambda i: K.router_fused(logits_p, bias, E, k, S, True, True)),
             ("dispatch(3 kernels)", GE, M * 8 * 2 + M * 4 * 3, 1,
              lambda i: K.dispatch(idx_all, Ea)),
-            ("permute", GE, 2 * M * D * 2 + M * 4, 2,
+            # compulsory traffic: x read once (its k + S re-reads hit L2), every slot row written
+            ("permute", GE, T * D * 2 + M * D * 2 + M * 4, 2,
              lambda i: K.permute(xr[i % 3], ka, sids, npp)),
             ("up_gemm+glu (+a1 saved)", TF, 2.0 * M * D * 2 * H, 1,
              lambda i: K.up_gemm(xs[i % 3], m.W_in, eids, npp, 0, 0, True, w_extra=m.W_sh_in)),
@@ -269,12 +270,19 @@ def build_stages(m, x):
             ("dhidden+glu_bwd", TF, 2.0 * M * D * H, 1,
              lambda i: K.dhidden_glu_bwd(xs[i % 3], m.W_out, eids, npp, 0, sids, tw, M, a1, 0,
                                          True, w_extra=m.W_sh_out)),
+            ("dhidden+glu_bwd (gathered rows)", TF, 2.0 * M * D * H, 0,
+             lambda i: K.dhidden_glu_bwd(xr[i % 3], m.W_out, eids, npp, 0, sids, tw, M, a1, 0,
+                                         True, gather_top_k=ka, w_extra=m.W_sh_out)),
             ("dx_gemm", TF, 2.0 * M * 2 * H * D, 1,
              lambda i: K.dx_gemm(da1[i % 3], m.W_in, eids, npp, 0, w_extra=m.W_sh_in)),
             ("wgrad_in (gemm + reduce)", TF, 2.0 * M * D * 2 * H, 1,
              lambda i: K.wgrad(xs[i % 3], da1[i % 3], offs, Ea, n_extra=S)),
             ("wgrad_out (gemm + reduce)", TF, 2.0 * M * H * D, 1,
              lambda i: K.wgrad(hid[i % 3], xs[i % 3], offs, Ea, n_extra=S)),
+            ("wgrad_in (gathered rows)", TF, 2.0 * M * D * 2 * H, 0,
+             lambda i: K.wgrad(xr[i % 3], da1[i % 3], offs, Ea, gather=("a", sids, ka), n_extra=S)),
+            ("wgrad_out (gathered rows)", TF, 2.0 * M * H * D, 0,
+             lambda i: K.wgrad(hid[i % 3], xr[i % 3], offs, Ea, gather=("b", sids, ka), n_extra=S)),
             ("router_fused_bwd", GE, T * ld * 2 * 2 + T * ka * 10, 1,
              lambda i: K.router_fused_bwd(logits_p, bias, idx_all, dtw, E, k, S, True, True,
                                           d_aux, counts, 1e-2, ld)),

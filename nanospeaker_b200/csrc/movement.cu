@@ -37,6 +37,64 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+struct alignas(32) Chunk32 {
+  uint32_t w[8];
+};
+// 32-byte load that asks L2 to keep the line: every token row is read top_k times, far apart, while
+// the rows being written stream through L2 in between.
+__device__ __forceinline__ Chunk32 ld_keep32(const Chunk32* p) {
+  Chunk32 r;
+  asm volatile(
+      "ld.global.nc.L1::no_allocate.L2::evict_last.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+      : "=r"(r.w[0]), "=r"(r.w[1]), "=r"(r.w[2]), "=r"(r.w[3]), "=r"(r.w[4]), "=r"(r.w[5]),
+        "=r"(r.w[6]), "=r"(r.w[7])
+      : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void st32(Chunk32* p, const Chunk32& r) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(r.w[0]),
+               "r"(r.w[1]), "r"(r.w[2]), "r"(r.w[3]), "r"(r.w[4]), "r"(r.w[5]), "r"(r.w[6]),
+               "r"(r.w[7])
+               : "memory");
+}
+
+// Same copy in 32-byte chunks (row_bytes a multiple of 32). A warp moves 8 consecutive slot rows as
+// one flat run of 8 * chunks_per_row chunks, PERMUTE_UNROLL independent loads per lane in flight.
+constexpr int PERMUTE_UNROLL = 3;
+__global__ void __launch_bounds__(256)
+    permute_rows32_kernel(const Chunk32* __restrict__ x, const int32_t* __restrict__ sorted_ids,
+                          const int32_t* __restrict__ n_post_pad, int32_t n_pairs, int32_t top_k,
+                          int32_t chunks_per_row, Chunk32* __restrict__ xs) {
+  const int32_t live = __ldg(n_post_pad);  // a multiple of 128
+  const int lane = threadIdx.x & 31;
+  const int warps = gridDim.x * (blockDim.x >> 5);
+  const int per_group = 8 * chunks_per_row;
+  for (int32_t row0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 8; row0 < live;
+       row0 += warps * 8) {
+    const int32_t pair = __ldg(sorted_ids + row0 + (lane & 7));
+    const int32_t my_tok = pair < n_pairs ? pair / top_k : -1;  // token of row row0 + lane % 8
+    Chunk32* dst = xs + int64_t(row0) * chunks_per_row;
+    for (int base = 0; base < per_group; base += 32 * PERMUTE_UNROLL) {
+      Chunk32 v[PERMUTE_UNROLL];
+#pragma unroll
+      for (int u = 0; u < PERMUTE_UNROLL; ++u) {
+        const int f = base + u * 32 + lane;
+        const int r = f / chunks_per_row;
+        const int tok = __shfl_sync(0xffffffffu, my_tok, r & 7);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) v[u].w[q] = 0u;
+        if (f < per_group && tok >= 0)
+          v[u] = ld_keep32(x + int64_t(tok) * chunks_per_row + (f - r * chunks_per_row));
+      }
+#pragma unroll
+      for (int u = 0; u < PERMUTE_UNROLL; ++u) {
+        const int f = base + u * 32 + lane;
+        if (f < per_group) st32(dst + f, v[u]);
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ void acc_bf16x8(float* acc, uint4 r) {
   const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
@@ -105,11 +163,21 @@ int moe_b200_permute(const void* x, int64_t n_tokens, int32_t d_model, int32_t t
   if (l_cap == 0 || n_tokens == 0) return MOE_B200_OK;
   if (!x || !sorted_ids || !n_post_pad || !xs) return MOE_B200_ERR_NULL;
   if (!aligned16(x) || !aligned16(xs)) return MOE_B200_ERR_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (d_model % 16 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(xs)) & 31u) == 0 &&
+      l_cap % 8 == 0) {
+    int64_t blocks = (l_cap / 8 + 7) / 8;  // 8 warps per block, 8 rows per warp and pass
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    permute_rows32_kernel<<<unsigned(blocks), 256, 0, st>>>(
+        static_cast<const Chunk32*>(x), sorted_ids, n_post_pad, int32_t(n_tokens * top_k), top_k,
+        d_model / 16, static_cast<Chunk32*>(xs));
+    return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+  }
   const int32_t cpr = d_model / 8;
   const int64_t total = l_cap * cpr;
   int64_t blocks = (total + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;  // grid-stride; a multiple of the SM count
-  permute_rows_kernel<<<unsigned(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  permute_rows_kernel<<<unsigned(blocks), 256, 0, st>>>(
       static_cast<const uint4*>(x), sorted_ids, n_post_pad, int32_t(n_tokens * top_k), top_k, cpr,
       static_cast<uint4*>(xs));
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
