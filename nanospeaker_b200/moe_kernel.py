@@ -303,6 +303,21 @@ _T15 = Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tenso
 _T6 = Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]
 
 
+_SIDE_STREAMS = {}
+
+
+def _side_streams(device: torch.device):
+    """Two extra streams per device for the independent branches of the block's backward. Work put
+    on them is fenced on both sides by wait_stream, so callers (and CUDA-graph capture) only ever
+    see the current stream."""
+    key = torch.device(device).index
+    if key is None:
+        key = torch.cuda.current_device()
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = (torch.cuda.Stream(device=key), torch.cuda.Stream(device=key))
+    return _SIDE_STREAMS[key]
+
+
 def _router_ld(n_experts: int) -> int:
     """Column count the router logits are padded to: TMA tiles of the padded router weight are
     64 columns wide."""
@@ -427,19 +442,31 @@ def moe_block_bwd(
     douts = K.permute(grad_out, ks, sorted_ids, n_post_pad)
     da1, hidw, dtw = K.dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m,
                                        a1, act, True, w_extra=w_sh_out)
-    ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
+    # Everything below only depends on the two launches above and meets again in the combine. Three
+    # branches on three streams: the small router kernels hide behind the expert GEMMs, and the
+    # tail of one persistent GEMM (SMs that ran out of tiles) is filled by the next one's CTAs.
+    main = torch.cuda.current_stream(x.device)
+    side_out, side_router = _side_streams(x.device)
+    side_out.wait_stream(main)
+    side_router.wait_stream(main)
     g_in = K.wgrad(xs, da1, pad_offsets, e_n + s_n, n_extra=s_n)
-    g_out = K.wgrad(hidw, douts, pad_offsets, e_n + s_n, n_extra=s_n)
+    ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
+    with torch.cuda.stream(side_out):
+        g_out = K.wgrad(hidw, douts, pad_offsets, e_n + s_n, n_extra=s_n)
+    with torch.cuda.stream(side_router):
+        # router: d(logits) from d(topk_w) and the balance loss, then the two router GEMMs
+        d_aux = None if grad_aux is None else grad_aux.to(torch.float32).reshape(1)
+        dl = K.router_fused_bwd(logits, logit_bias, idx_all, dtw.view(n, ks), e_n, top_k, s_n,
+                                normalize, full_softmax, d_aux, counts_all, aux_coef,
+                                logits.shape[1])
+        d_wp = K.wgrad(x, dl, None, 1)[0]
+        dx_router = K.dx_gemm(dl, router_w_padded, None, None, 1)[0]
+    main.wait_stream(side_out)
+    main.wait_stream(side_router)
     if s_n:
         (dw_in, dw_sh_in), (dw_out, dw_sh_out) = g_in, g_out
     else:
         dw_in, dw_out, dw_sh_in, dw_sh_out = g_in, g_out, x.new_empty(0), x.new_empty(0)
-    # router: d(logits) from d(topk_w) and the balance loss, then the two router GEMMs
-    d_aux = None if grad_aux is None else grad_aux.to(torch.float32).reshape(1)
-    dl = K.router_fused_bwd(logits, logit_bias, idx_all, dtw.view(n, ks), e_n, top_k, s_n,
-                            normalize, full_softmax, d_aux, counts_all, aux_coef, logits.shape[1])
-    d_wp = K.wgrad(x, dl, None, 1)[0]
-    dx_router = K.dx_gemm(dl, router_w_padded, None, None, 1)[0]
     dx = K.combine(ydx, inv_ids, n, ks, dx_router)
     return dx, d_wp, dw_in, dw_out, dw_sh_in, dw_sh_out
 
