@@ -113,8 +113,9 @@ static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   if (attr_err != cudaSuccess) return MOE_B200_ERR_CUDA;
   const int64_t sms = sm_count();
   const unsigned grid = unsigned(max_tiles < sms ? max_tiles : sms);
-  kern<<<grid, GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS, smem, st>>>(tmA, tmB, tmB2, args);
-  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+  const cudaError_t err = launch_pdl(kern, dim3(grid), dim3(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS),
+                                     size_t(smem), st, tmA, tmB, tmB2, args);
+  return err == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
 template <int BN, int STAGES, int GATHER>
@@ -131,8 +132,9 @@ static int launch_wgrad_g(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   const int64_t tiles = max_items * tiles_x * tiles_y, sms = sm_count();
   const unsigned grid = unsigned(tiles < sms ? tiles : sms);
   const int threads = GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS;
-  kern<<<grid, threads, smem, st>>>(tmA, tmB, args, tiles_x, tiles_y);
-  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+  const cudaError_t err =
+      launch_pdl(kern, dim3(grid), dim3(threads), size_t(smem), st, tmA, tmB, args, tiles_x, tiles_y);
+  return err == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
 template <int BN, int STAGES>
@@ -449,14 +451,14 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
     const unsigned ty = unsigned(n_dim / 256);
     rc = launch_wgrad<256, 4>(tmA, tmB, g, int(tx), int(ty), items, st);
     if (rc == MOE_B200_OK && may_split)
-      wgrad_reduce_kernel<256><<<dim3(tx * ty * WGRAD_REDUCE_SPLIT, gy), 256, 0, st>>>(g, int(tx),
-                                                                                   int(ty));
+      launch_pdl(wgrad_reduce_kernel<256>, dim3(tx * ty * WGRAD_REDUCE_SPLIT, gy), dim3(256), 0, st,
+                 g, int(tx), int(ty));
   } else {
     const unsigned ty = unsigned((n_dim + 191) / 192);
     rc = launch_wgrad<192, 5>(tmA, tmB, g, int(tx), int(ty), items, st);
     if (rc == MOE_B200_OK && may_split)
-      wgrad_reduce_kernel<192><<<dim3(tx * ty * WGRAD_REDUCE_SPLIT, gy), 256, 0, st>>>(g, int(tx),
-                                                                                   int(ty));
+      launch_pdl(wgrad_reduce_kernel<192>, dim3(tx * ty * WGRAD_REDUCE_SPLIT, gy), dim3(256), 0, st,
+                 g, int(tx), int(ty));
   }
   if (rc != MOE_B200_OK) return rc;
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;

@@ -16,6 +16,7 @@
 // warps 2.. = epilogue (one accumulator row per thread; a warp may only read the TMEM lane
 // quadrant 32*(warp%4)).
 #pragma once
+#include "pdl.cuh"
 #include "ptx.cuh"
 
 namespace moe {

@@ -105,6 +105,8 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
     rows_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmB2, const RowsArgs p) {
+  pdl_trigger();
+  pdl_wait();
   using L = RowsSmem<BN, STAGES>;
   static_assert(BN % 64 == 0 && BN <= 256, "BN must be a multiple of 64 up to 256");
   constexpr uint32_t TMEM_BUF = BN <= 128 ? 128 : 256;  // columns per accumulator buffer

@@ -102,6 +102,8 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
     wgrad_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                       const __grid_constant__ CUtensorMap tmB, const WgradArgs p, int tiles_x,
                       int tiles_y) {
+  pdl_trigger();
+  pdl_wait();
   using L = WgradSmem<BN, STAGES>;
   constexpr uint32_t TMEM_BUF = BN <= 128 ? 128 : 256;
   constexpr uint32_t TMEM_COLS = 2 * TMEM_BUF;
@@ -340,6 +342,8 @@ constexpr int WGRAD_REDUCE_SPLIT = 16;  // CTAs sharing the reduction of one out
 template <int BN>
 __global__ void __launch_bounds__(256)
     wgrad_reduce_kernel(const WgradArgs p, int tiles_x, int tiles_y) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ int first_item[WGRAD_MAX_GROUPS + 1];
   __shared__ int run_start[WGRAD_MAX_GROUPS + 1];
   if (threadIdx.x < 32) wgrad_build_table(p, threadIdx.x, first_item, run_start);

@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include "../../include/moe_b200.h"
+#include "pdl.cuh"
 
 namespace moe {
 
@@ -24,6 +25,8 @@ __global__ void __launch_bounds__(256)
     permute_rows_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ sorted_ids,
                         const int32_t* __restrict__ n_post_pad, int32_t n_pairs, int32_t top_k,
                         int32_t chunks_per_row, uint4* __restrict__ xs) {
+  pdl_trigger();
+  pdl_wait();
   const int32_t live = __ldg(n_post_pad);
   const int64_t total = int64_t(live) * chunks_per_row;
   for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -65,6 +68,8 @@ __global__ void __launch_bounds__(256)
     permute_rows32_kernel(const Chunk32* __restrict__ x, const int32_t* __restrict__ sorted_ids,
                           const int32_t* __restrict__ n_post_pad, int32_t n_pairs, int32_t top_k,
                           int32_t chunks_per_row, Chunk32* __restrict__ xs) {
+  pdl_trigger();
+  pdl_wait();
   const int32_t live = __ldg(n_post_pad);  // a multiple of 128
   const int lane = threadIdx.x & 31;
   const int warps = gridDim.x * (blockDim.x >> 5);
@@ -113,6 +118,8 @@ __global__ void __launch_bounds__(256)
                         int64_t n_tokens, int32_t top_k_rt, int32_t chunks_per_row,
                         const uint4* __restrict__ extra, const uint4* __restrict__ extra2,
                         uint4* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   const int top_k = TOPK > 0 ? TOPK : top_k_rt;
   const int64_t total = n_tokens * chunks_per_row;
   for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -168,7 +175,7 @@ int moe_b200_permute(const void* x, int64_t n_tokens, int32_t d_model, int32_t t
       l_cap % 8 == 0) {
     int64_t blocks = (l_cap / 8 + 7) / 8;  // 8 warps per block, 8 rows per warp and pass
     if (blocks > 148 * 8) blocks = 148 * 8;
-    permute_rows32_kernel<<<unsigned(blocks), 256, 0, st>>>(
+    launch_pdl(permute_rows32_kernel, dim3(unsigned(blocks)), dim3(256), 0, st, 
         static_cast<const Chunk32*>(x), sorted_ids, n_post_pad, int32_t(n_tokens * top_k), top_k,
         d_model / 16, static_cast<Chunk32*>(xs));
     return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
@@ -177,7 +184,7 @@ int moe_b200_permute(const void* x, int64_t n_tokens, int32_t d_model, int32_t t
   const int64_t total = l_cap * cpr;
   int64_t blocks = (total + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;  // grid-stride; a multiple of the SM count
-  permute_rows_kernel<<<unsigned(blocks), 256, 0, st>>>(
+  launch_pdl(permute_rows_kernel, dim3(unsigned(blocks)), dim3(256), 0, st, 
       static_cast<const uint4*>(x), sorted_ids, n_post_pad, int32_t(n_tokens * top_k), top_k, cpr,
       static_cast<uint4*>(xs));
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
@@ -201,7 +208,7 @@ int moe_b200_combine(const void* y, const int32_t* inv_ids, int64_t n_tokens, in
   const uint4* ex2 = static_cast<const uint4*>(extra2);
   uint4* oo = static_cast<uint4*>(out);
 #define LAUNCH(K) \
-  combine_rows_kernel<K><<<unsigned(blocks), 256, 0, st>>>(yy, inv_ids, n_tokens, top_k, cpr, ex, ex2, oo)
+  launch_pdl(combine_rows_kernel<K>, dim3(unsigned(blocks)), dim3(256), 0, st, yy, inv_ids, n_tokens, top_k, cpr, ex, ex2, oo)
   switch (top_k) {
     case 1: LAUNCH(1); break;
     case 2: LAUNCH(2); break;

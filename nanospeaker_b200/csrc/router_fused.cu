@@ -9,6 +9,7 @@
 #include <stdint.h>
 
 #include "../../include/moe_b200.h"
+#include "pdl.cuh"
 #include "routing.cuh"
 
 namespace moe {
@@ -25,6 +26,8 @@ __global__ void __launch_bounds__(RF_WARPS * 32)
                         int n_shared, int normalize, int full_softmax,
                         __nv_bfloat16* __restrict__ w_all, int64_t* __restrict__ idx_all,
                         float* __restrict__ colsum) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float cs[RF_WARPS][NSLOT * 32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int kS = top_k + n_shared;
@@ -153,6 +156,8 @@ __global__ void __launch_bounds__(RF_WARPS * 32)
                             int full_softmax, const float* __restrict__ d_aux,
                             const int32_t* __restrict__ counts, float aux_scale_T,
                             __nv_bfloat16* __restrict__ dl, int ld_out) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int kS = top_k + n_shared;
   const bool need_full = full_softmax || !normalize;
@@ -285,6 +290,8 @@ __global__ void __launch_bounds__(RF_WARPS * 32)
 __global__ void balance_loss_kernel(const float* __restrict__ colsum,
                                     const int32_t* __restrict__ counts, int n_experts,
                                     int64_t n_tokens, float coef, float* __restrict__ aux) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x;
   float dot = 0.f, tot = 0.f;
   for (int e = lane; e < n_experts; e += 32) {
@@ -301,9 +308,9 @@ __global__ void balance_loss_kernel(const float* __restrict__ colsum,
     aux[0] = coef * float(n_experts) * dot / fmaxf(tot, 1.f) / float(n_tokens > 0 ? n_tokens : 1);
 }
 
-static unsigned rf_grid(int64_t n_tokens) {
+static unsigned rf_grid(int64_t n_tokens, int blocks_per_sm = 16) {
   const int64_t want = (n_tokens + RF_WARPS - 1) / RF_WARPS;
-  const int64_t cap = 148 * 16;  // one wave of resident blocks; warps stride over the tokens
+  const int64_t cap = 148 * blocks_per_sm;  // resident blocks; warps stride over the tokens
   return unsigned(want < cap ? (want > 0 ? want : 1) : cap);
 }
 
@@ -323,11 +330,13 @@ int moe_b200_router_fused(const void* logits, int32_t ld, const float* bias, int
   if (n_tokens == 0) return MOE_B200_OK;
   if (!logits || !w_all || !idx_all) return MOE_B200_ERR_NULL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const unsigned grid = rf_grid(n_tokens);
+  // every block ends with one atomic per expert on the same few addresses: with the balance-loss
+  // statistics on, fewer blocks (each warp then takes a few tokens) keep that queue short
+  const unsigned grid = rf_grid(n_tokens, (full_softmax && colsum) ? 4 : 16);
   const __nv_bfloat16* lg = static_cast<const __nv_bfloat16*>(logits);
   __nv_bfloat16* w = static_cast<__nv_bfloat16*>(w_all);
 #define LAUNCH(NS)                                                                              \
-  router_fused_kernel<NS><<<grid, RF_WARPS * 32, 0, st>>>(lg, ld, bias, n_tokens, n_experts, top_k, \
+  launch_pdl(router_fused_kernel<NS>, dim3(grid), dim3(RF_WARPS * 32), 0, st, lg, ld, bias, n_tokens, n_experts, top_k, \
                                                           n_shared, normalize, full_softmax, w,    \
                                                           idx_all, colsum)
   const int nslot = (n_experts + 31) / 32;
@@ -359,7 +368,7 @@ int moe_b200_router_fused_bwd(const void* logits, int32_t ld, const float* bias,
   const __nv_bfloat16* dw = static_cast<const __nv_bfloat16*>(dw_all);
   __nv_bfloat16* out = static_cast<__nv_bfloat16*>(d_logits);
 #define LAUNCH(NS)                                                                               \
-  router_fused_bwd_kernel<NS><<<grid, RF_WARPS * 32, 0, st>>>(                                    \
+  launch_pdl(router_fused_bwd_kernel<NS>, dim3(grid), dim3(RF_WARPS * 32), 0, st,                                     \
       lg, ld, bias, idx_all, dw, n_tokens, n_experts, top_k, n_shared, normalize, full_softmax,   \
       d_aux, counts, scale, out, ld_out)
   const int nslot = (n_experts + 31) / 32;
@@ -376,8 +385,8 @@ int moe_b200_balance_loss(const float* colsum, const int32_t* counts, int32_t n_
                           int64_t n_tokens, float aux_coef, float* aux, void* stream) {
   if (n_experts < 1 || n_tokens < 0) return MOE_B200_ERR_SHAPE;
   if (!colsum || !counts || !aux) return MOE_B200_ERR_NULL;
-  balance_loss_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(colsum, counts, n_experts,
-                                                                        n_tokens, aux_coef, aux);
+  launch_pdl(balance_loss_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), colsum,
+             counts, n_experts, n_tokens, aux_coef, aux);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 

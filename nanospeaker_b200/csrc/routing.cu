@@ -13,6 +13,7 @@
 #include <mutex>
 
 #include "../../include/moe_b200.h"
+#include "pdl.cuh"
 #include "gemm.cuh"  // DevStatus
 #include "routing.cuh"
 
@@ -32,6 +33,8 @@ __global__ void __launch_bounds__(256)
     router_topk_kernel(const float* __restrict__ logits, int64_t n_tokens, int n_experts, int top_k,
                        int normalize, int full_softmax, float* __restrict__ topk_w,
                        int64_t* __restrict__ topk_idx, float* __restrict__ probs) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t t = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (t >= n_tokens) return;
@@ -135,6 +138,8 @@ __global__ void __launch_bounds__(256)
                            const float* __restrict__ d_topk_w, const float* __restrict__ d_probs,
                            int64_t n_tokens, int n_experts, int top_k, int normalize,
                            int full_softmax, float* __restrict__ d_logits) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t t = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (t >= n_tokens) return;
@@ -240,22 +245,32 @@ __global__ void __launch_bounds__(256)
 }
 
 // ------------------------------------------------------------------------------- dispatch
-constexpr int DISPATCH_THREADS = 512;
+// Stable counting sort of the pairs by expert in two launches. The pairs are cut into at most
+// DISPATCH_MAX_BLOCKS chunks of `chunk` pairs (a power-of-two multiple of 1024), one block each.
+constexpr int DISPATCH_THREADS = 256;
 constexpr int DISPATCH_WARPS = DISPATCH_THREADS / 32;
-constexpr int DISPATCH_CHUNK = 4096;  // pairs per block; a warp owns a contiguous 256-pair slice
-constexpr int WARP_SLICE = DISPATCH_CHUNK / DISPATCH_WARPS;
+constexpr int DISPATCH_MIN_CHUNK = 1024;
+constexpr int DISPATCH_MAX_BLOCKS = 128;
 
-// Pass 1: per-block histogram of expert ids -> block_hist[block][E]; also paints this block's
+static int64_t dispatch_chunk(int64_t n_pairs) {
+  int64_t chunk = DISPATCH_MIN_CHUNK;
+  while ((n_pairs + chunk - 1) / chunk > DISPATCH_MAX_BLOCKS) chunk *= 2;
+  return chunk;
+}
+
+// Pass 1: per-block histogram of expert ids -> block_hist[expert][block]; also paints this block's
 // share of sorted_ids with the sentinel so pad slots need no separate fill launch.
 __global__ void __launch_bounds__(DISPATCH_THREADS)
     dispatch_hist_kernel(const int64_t* __restrict__ topk_idx, int64_t n_pairs, int n_experts,
-                         int32_t* __restrict__ block_hist, int32_t* __restrict__ sorted_ids,
-                         int64_t l_cap, int32_t* status) {
+                         int chunk, int32_t* __restrict__ block_hist,
+                         int32_t* __restrict__ sorted_ids, int64_t l_cap, int32_t* status) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ int32_t hist[MAX_EXPERTS];
   for (int e = threadIdx.x; e < n_experts; e += blockDim.x) hist[e] = 0;
   __syncthreads();
-  const int64_t base = int64_t(blockIdx.x) * DISPATCH_CHUNK;
-  for (int i = threadIdx.x; i < DISPATCH_CHUNK; i += blockDim.x) {
+  const int64_t base = int64_t(blockIdx.x) * chunk;
+  for (int i = threadIdx.x; i < chunk; i += blockDim.x) {
     const int64_t pidx = base + i;
     if (pidx < n_pairs) {
       const int64_t e = topk_idx[pidx];
@@ -272,103 +287,126 @@ __global__ void __launch_bounds__(DISPATCH_THREADS)
   for (int64_t s = lo + threadIdx.x; s < hi; s += blockDim.x) sorted_ids[s] = int32_t(n_pairs);
   __syncthreads();
   for (int e = threadIdx.x; e < n_experts; e += blockDim.x)
-    block_hist[int64_t(blockIdx.x) * n_experts + e] = hist[e];
+    block_hist[int64_t(e) * gridDim.x + blockIdx.x] = hist[e];
 }
 
-// Pass 2 (one block): turn block histograms into exclusive prefixes over blocks, total counts,
-// 128-aligned run offsets, the live padded length and the tile -> expert map.
-__global__ void __launch_bounds__(1024)
-    dispatch_scan_kernel(int32_t* __restrict__ block_hist, int n_blocks, int n_experts,
-                         int32_t* __restrict__ counts, int32_t* __restrict__ pad_offsets,
-                         int32_t* __restrict__ n_post_pad, int32_t* __restrict__ expert_ids,
-                         int64_t n_tiles_cap) {
-  __shared__ int32_t off[MAX_EXPERTS + 1];
-  __shared__ int32_t padded[MAX_EXPERTS];
-  const int e = threadIdx.x;
-  if (e < n_experts) {
-    int32_t run = 0;
-    // loads are issued 8 blocks at a time so their latencies overlap
-    int b = 0;
-    for (; b + 8 <= n_blocks; b += 8) {
-      int32_t c[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) c[u] = block_hist[int64_t(b + u) * n_experts + e];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        block_hist[int64_t(b + u) * n_experts + e] = run;
-        run += c[u];
-      }
-    }
-    for (; b < n_blocks; ++b) {
-      const int32_t c = block_hist[int64_t(b) * n_experts + e];
-      block_hist[int64_t(b) * n_experts + e] = run;
-      run += c;
-    }
-    counts[e] = run;
-    padded[e] = (run + ALIGN_M - 1) / ALIGN_M * ALIGN_M;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int32_t acc = 0;
-    for (int i = 0; i < n_experts; ++i) {
-      off[i] = acc;
-      acc += padded[i];
-    }
-    off[n_experts] = acc;
-    *n_post_pad = acc;
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i <= n_experts; i += blockDim.x) pad_offsets[i] = off[i];
-  const int32_t total = off[n_experts];
-  for (int64_t tile = threadIdx.x; tile < n_tiles_cap; tile += blockDim.x) {
-    int32_t owner = 0;
-    const int64_t row = tile * ALIGN_M;
-    if (row < total) {
-      // last expert whose run starts at or before this row and is non-empty there
-      int lo = 0, hi = n_experts;  // invariant: off[lo] <= row < off[hi]
-      while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (off[mid] <= row) lo = mid; else hi = mid;
-      }
-      owner = lo;
-    }
-    expert_ids[tile] = owner;
-  }
-}
-
-// Pass 3: stable scatter. Pair i of expert e lands at
-//   pad_offsets[e] + (#pairs of e in earlier blocks) + (#pairs of e earlier in this block).
-// Inside the block each warp owns a contiguous slice; warps first count their slice, the counts are
+// Pass 2: plan + stable scatter. Every block first sums the histograms itself (n_blocks is at most
+// 128, the table sits in L2): per expert the total over all blocks and the share of the blocks
+// before this one; from the totals the 128-aligned run offsets. Each block writes its slice of the
+// tile -> expert map, block 0 the counts, offsets and the live padded length. Then pair i of
+// expert e lands at
+//   pad_offsets[e] + (#pairs of e in earlier blocks) + (#pairs of e earlier in this block):
+// inside the block each warp owns a contiguous slice; warps first count their slice, the counts are
 // prefix-summed over warps, then every warp walks its slice 32 pairs at a time and ranks equal
 // experts with __match_any_sync (lower lane = lower pair id = earlier slot).
+// Launched with one block and n_blocks = 0 for an empty input (the plan is still written).
 __global__ void __launch_bounds__(DISPATCH_THREADS)
     dispatch_scatter_kernel(const int64_t* __restrict__ topk_idx, int64_t n_pairs, int n_experts,
-                            const int32_t* __restrict__ block_prefix,
-                            const int32_t* __restrict__ pad_offsets,
-                            int32_t* __restrict__ sorted_ids, int32_t* __restrict__ inv_ids) {
+                            int chunk, int n_blocks, const int32_t* __restrict__ block_hist,
+                            int32_t* __restrict__ counts, int32_t* __restrict__ pad_offsets,
+                            int32_t* __restrict__ n_post_pad, int32_t* __restrict__ expert_ids,
+                            int64_t n_tiles_cap, int32_t* __restrict__ sorted_ids,
+                            int32_t* __restrict__ inv_ids) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ int32_t total[MAX_EXPERTS];
+  __shared__ int32_t before[MAX_EXPERTS];
+  __shared__ int32_t off[MAX_EXPERTS + 1];
   __shared__ int32_t cursor[DISPATCH_WARPS][MAX_EXPERTS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // totals and earlier-block shares: warp w takes experts w, w + 8, ...; lanes stride over blocks
+  for (int e = warp; e < n_experts; e += DISPATCH_WARPS) {
+    int32_t tot = 0, bef = 0;
+    for (int b = lane; b < n_blocks; b += 32) {
+      const int32_t v = block_hist[int64_t(e) * n_blocks + b];
+      tot += v;
+      if (b < int(blockIdx.x)) bef += v;
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      tot += __shfl_xor_sync(0xffffffffu, tot, o);
+      bef += __shfl_xor_sync(0xffffffffu, bef, o);
+    }
+    if (lane == 0) {
+      total[e] = tot;
+      before[e] = bef;
+    }
+  }
   for (int i = threadIdx.x; i < DISPATCH_WARPS * MAX_EXPERTS; i += blockDim.x)
     (&cursor[0][0])[i] = 0;
   __syncthreads();
-
-  const int64_t wbase = int64_t(blockIdx.x) * DISPATCH_CHUNK + int64_t(warp) * WARP_SLICE;
-  int32_t my_e[WARP_SLICE / 32];
+  // exclusive scan of the padded run lengths (one warp, 8 consecutive experts per lane)
+  if (warp == 0) {
+    constexpr int PER = MAX_EXPERTS / 32;
+    int32_t pad[PER];
+    int32_t mine = 0;
 #pragma unroll
-  for (int r = 0; r < WARP_SLICE / 32; ++r) {
-    const int64_t pidx = wbase + r * 32 + lane;
+    for (int i = 0; i < PER; ++i) {
+      const int e = lane * PER + i;
+      pad[i] = e < n_experts ? (total[e] + ALIGN_M - 1) / ALIGN_M * ALIGN_M : 0;
+      mine += pad[i];
+    }
+    int32_t incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    int32_t run = incl - mine;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = lane * PER + i;
+      if (e <= n_experts) off[e] = run;
+      run += pad[i];
+    }
+    if (lane == 31) off[MAX_EXPERTS] = run;  // n_experts == MAX_EXPERTS: no lane holds that index
+  }
+  __syncthreads();
+  const int32_t live = off[n_experts];
+  if (blockIdx.x == 0) {
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = total[e];
+    for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) pad_offsets[e] = off[e];
+    if (threadIdx.x == 0) *n_post_pad = live;
+  }
+  if (expert_ids != nullptr) {
+    const int64_t per = (n_tiles_cap + gridDim.x - 1) / gridDim.x;
+    const int64_t t_hi = per * (blockIdx.x + 1) < n_tiles_cap ? per * (blockIdx.x + 1) : n_tiles_cap;
+    for (int64_t tile = per * blockIdx.x + threadIdx.x; tile < t_hi; tile += blockDim.x) {
+      int32_t owner = 0;
+      const int64_t row = tile * ALIGN_M;
+      if (row < live) {
+        // last expert whose run starts at or before this row and is non-empty there
+        int lo = 0, hi = n_experts;  // invariant: off[lo] <= row < off[hi]
+        while (hi - lo > 1) {
+          const int mid = (lo + hi) >> 1;
+          if (off[mid] <= row) lo = mid; else hi = mid;
+        }
+        owner = lo;
+      }
+      expert_ids[tile] = owner;
+    }
+  }
+  if (n_blocks == 0) return;
+
+  const int slice = chunk / DISPATCH_WARPS;  // a multiple of 32
+  const int64_t wbase = int64_t(blockIdx.x) * chunk + int64_t(warp) * slice;
+  auto expert_of = [&](int64_t pidx) {
     int32_t e = -1;
     if (pidx < n_pairs) {
       const int64_t ee = topk_idx[pidx];
       e = (ee >= 0 && ee < n_experts) ? int32_t(ee) : -1;
     }
-    my_e[r] = e;
+    return e;
+  };
+  for (int r = 0; r < slice; r += 32) {
+    const int32_t e = expert_of(wbase + r + lane);
     if (e >= 0) atomicAdd(&cursor[warp][e], 1);
   }
   __syncthreads();
   // exclusive prefix over warps, seeded with the run start and the earlier blocks' share
   for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
-    int32_t run = pad_offsets[e] + block_prefix[int64_t(blockIdx.x) * n_experts + e];
+    int32_t run = off[e] + before[e];
     for (int w = 0; w < DISPATCH_WARPS; ++w) {
       const int32_t c = cursor[w][e];
       cursor[w][e] = run;
@@ -376,14 +414,13 @@ __global__ void __launch_bounds__(DISPATCH_THREADS)
     }
   }
   __syncthreads();
-#pragma unroll
-  for (int r = 0; r < WARP_SLICE / 32; ++r) {
-    const int32_t e = my_e[r];
+  for (int r = 0; r < slice; r += 32) {
+    const int64_t pidx = wbase + r + lane;
+    const int32_t e = expert_of(pidx);
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     if (e >= 0) {
       const int rank = __popc(peers & ((1u << lane) - 1u));
       const int32_t dst = cursor[warp][e] + rank;
-      const int64_t pidx = wbase + r * 32 + lane;
       sorted_ids[dst] = int32_t(pidx);
       inv_ids[pidx] = dst;
     }
@@ -391,6 +428,23 @@ __global__ void __launch_bounds__(DISPATCH_THREADS)
     if (e >= 0 && lane == 31 - __clz(peers)) cursor[warp][e] += __popc(peers);
     __syncwarp();
   }
+}
+
+// Both dispatch entry points: histogram pass, then plan + scatter.
+static int launch_dispatch(const int64_t* topk_idx, int64_t n_pairs, int32_t n_experts,
+                           int32_t* sorted_ids, int32_t* expert_ids, int32_t* pad_offsets,
+                           int32_t* counts, int32_t* n_post_pad, int32_t* inv_ids,
+                           int32_t* block_hist, int32_t* status, cudaStream_t st) {
+  const int64_t l_cap = moe_b200_l_cap(n_pairs, n_experts);
+  const int chunk = int(dispatch_chunk(n_pairs));
+  const int blocks = int((n_pairs + chunk - 1) / chunk);
+  if (blocks > 0)
+    launch_pdl(dispatch_hist_kernel, dim3(blocks), dim3(DISPATCH_THREADS), 0, st, topk_idx, n_pairs,
+               n_experts, chunk, block_hist, sorted_ids, l_cap, status);
+  launch_pdl(dispatch_scatter_kernel, dim3(blocks > 0 ? blocks : 1), dim3(DISPATCH_THREADS), 0, st,
+             topk_idx, n_pairs, n_experts, chunk, blocks, block_hist, counts, pad_offsets,
+             n_post_pad, expert_ids, l_cap / ALIGN_M, sorted_ids, inv_ids);
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
 }  // namespace moe
@@ -405,7 +459,9 @@ int64_t moe_b200_l_cap(int64_t n_pairs, int32_t n_experts) {
 }
 
 size_t moe_b200_dispatch_scratch_bytes(int64_t n_pairs, int32_t n_experts) {
-  const int64_t blocks = (n_pairs + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK;
+  if (n_pairs < 0) n_pairs = 0;
+  const int64_t chunk = dispatch_chunk(n_pairs);
+  const int64_t blocks = (n_pairs + chunk - 1) / chunk;
   return size_t(blocks > 0 ? blocks : 1) * size_t(n_experts) * sizeof(int32_t);
 }
 
@@ -421,7 +477,7 @@ int moe_b200_router_topk(const float* logits, int64_t n_tokens, int32_t n_expert
   const unsigned grid = unsigned((threads + 255) / 256);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define LAUNCH(NS)                                                                          \
-  router_topk_kernel<NS><<<grid, 256, 0, st>>>(logits, n_tokens, n_experts, top_k, normalize, \
+  launch_pdl(router_topk_kernel<NS>, dim3(grid), dim3(256), 0, st, logits, n_tokens, n_experts, top_k, normalize, \
                                                full_softmax, topk_w, topk_idx, probs)
   const int nslot = (n_experts + 31) / 32;
   if (nslot <= 1) LAUNCH(1);
@@ -446,7 +502,7 @@ int moe_b200_router_topk_bwd(const float* logits, const int64_t* topk_idx, const
   const unsigned grid = unsigned((threads + 255) / 256);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define LAUNCH(NS)                                                                             \
-  router_topk_bwd_kernel<NS><<<grid, 256, 0, st>>>(logits, topk_idx, d_topk_w, d_probs, n_tokens, \
+  launch_pdl(router_topk_bwd_kernel<NS>, dim3(grid), dim3(256), 0, st, logits, topk_idx, d_topk_w, d_probs, n_tokens, \
                                                    n_experts, top_k, normalize, full_softmax,     \
                                                    d_logits)
   const int nslot = (n_experts + 31) / 32;
@@ -469,19 +525,9 @@ int moe_b200_dispatch(const int64_t* topk_idx, int64_t n_pairs, int32_t n_expert
   if (!pad_offsets || !counts || !n_post_pad || !status) return MOE_B200_ERR_NULL;
   if (scratch_bytes < moe_b200_dispatch_scratch_bytes(n_pairs, n_experts) || !scratch)
     return MOE_B200_ERR_SCRATCH;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int64_t l_cap = moe_b200_l_cap(n_pairs, n_experts);
-  const int blocks = int((n_pairs + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK);
-  int32_t* block_hist = static_cast<int32_t*>(scratch);
-  if (blocks > 0)
-    dispatch_hist_kernel<<<blocks, DISPATCH_THREADS, 0, st>>>(topk_idx, n_pairs, n_experts,
-                                                               block_hist, sorted_ids, l_cap, status);
-  dispatch_scan_kernel<<<1, 1024, 0, st>>>(block_hist, blocks, n_experts, counts, pad_offsets,
-                                           n_post_pad, expert_ids, l_cap / ALIGN_M);
-  if (blocks > 0)
-    dispatch_scatter_kernel<<<blocks, DISPATCH_THREADS, 0, st>>>(
-        topk_idx, n_pairs, n_experts, block_hist, pad_offsets, sorted_ids, inv_ids);
-  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+  return launch_dispatch(topk_idx, n_pairs, n_experts, sorted_ids, expert_ids, pad_offsets, counts,
+                         n_post_pad, inv_ids, static_cast<int32_t*>(scratch), status,
+                         static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
@@ -522,7 +568,7 @@ extern "C" {
 
 int64_t moe_b200_dispatch_static_max_pairs(int32_t n_experts) {
   if (n_experts < 1 || n_experts > MAX_EXPERTS) return 0;
-  return int64_t(STATIC_SCRATCH_INTS / n_experts) * DISPATCH_CHUNK;
+  return int64_t(STATIC_SCRATCH_INTS / n_experts) * 4096;
 }
 
 int moe_b200_dispatch_static(const int64_t* topk_idx, int64_t n_pairs, int32_t n_experts,
@@ -536,20 +582,10 @@ int moe_b200_dispatch_static(const int64_t* topk_idx, int64_t n_pairs, int32_t n
   int32_t* block_hist = nullptr;
   const int rc = static_scratch_for_current_device(&block_hist);
   if (rc != MOE_B200_OK) return rc;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int64_t l_cap = moe_b200_l_cap(n_pairs, n_experts);
-  const int blocks = int((n_pairs + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK);
-  // Nothing in the array has to start at zero: pass 1 overwrites every (block, expert) entry that
-  // passes 2 and 3 read, so whatever the previous call left behind is never seen.
-  if (blocks > 0)
-    dispatch_hist_kernel<<<blocks, DISPATCH_THREADS, 0, st>>>(topk_idx, n_pairs, n_experts,
-                                                               block_hist, sorted_ids, l_cap, status);
-  dispatch_scan_kernel<<<1, 1024, 0, st>>>(block_hist, blocks, n_experts, counts, pad_offsets,
-                                           n_post_pad, expert_ids, l_cap / ALIGN_M);
-  if (blocks > 0)
-    dispatch_scatter_kernel<<<blocks, DISPATCH_THREADS, 0, st>>>(
-        topk_idx, n_pairs, n_experts, block_hist, pad_offsets, sorted_ids, inv_ids);
-  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+  // Nothing in the array has to start at zero: pass 1 overwrites every (expert, block) entry that
+  // pass 2 reads, so whatever the previous call left behind is never seen.
+  return launch_dispatch(topk_idx, n_pairs, n_experts, sorted_ids, expert_ids, pad_offsets, counts,
+                         n_post_pad, inv_ids, block_hist, status, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -53,7 +53,8 @@ def test_l_cap_matches_reference_formula(lib, m, e):
 
 def test_scratch_bytes_is_modest(lib):
     assert lib.moe_b200_dispatch_scratch_bytes(0, 76) > 0
-    assert lib.moe_b200_dispatch_scratch_bytes(98304, 76) == 24 * 76 * 4
+    assert lib.moe_b200_dispatch_scratch_bytes(98304, 76) == 96 * 76 * 4   # 1024-pair blocks
+    assert lib.moe_b200_dispatch_scratch_bytes(1 << 22, 76) == 128 * 76 * 4  # at most 128 blocks
 
 
 def test_arguments_are_validated_before_any_launch(lib):
