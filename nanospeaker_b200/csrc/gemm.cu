@@ -62,21 +62,29 @@ static bool map_rows_kmajor(CUtensorMap* m, const void* base, int64_t groups, in
   return make_map(m, base, 3, dims, strides, box);
 }
 // [groups, rows, cols] buffer read as an MN-major operand (contraction over rows): 64 x 64 boxes.
+// When cols is a multiple of 64 the map is 4-D (64 cols, row, col / 64, group) with `boxes` boxes
+// per copy (*fused = 1): one TMA instruction then fills a whole stage of the operand.
 static bool map_rows_mnmajor(CUtensorMap* m, const void* base, int64_t groups, int64_t rows,
-                             int64_t cols) {
+                             int64_t cols, int boxes, int32_t* fused) {
+  if (cols % 64 == 0) {
+    const uint64_t dims[4] = {64, uint64_t(rows), uint64_t(cols / 64), uint64_t(groups)};
+    const uint64_t strides[3] = {uint64_t(cols) * 2, 128, uint64_t(cols) * uint64_t(rows) * 2};
+    const uint32_t box[4] = {64, 64, uint32_t(boxes), 1};
+    *fused = 1;
+    return make_map(m, base, 4, dims, strides, box);
+  }
   const uint64_t dims[3] = {uint64_t(cols), uint64_t(rows), uint64_t(groups)};
   const uint64_t strides[2] = {uint64_t(cols) * 2, uint64_t(cols) * uint64_t(rows) * 2};
   const uint32_t box[3] = {64, 64, 1};
+  *fused = 0;
   return make_map(m, base, 3, dims, strides, box);
 }
 // Stacked weights [G, k_dim, n_dim] with n contiguous (the reference's W_in / W_out layout used
-// in the forward): MN-major B operand, 64 (n) x 64 (k) boxes.
+// in the forward): MN-major B operand, 64 (n) x 64 (k) boxes; 4-D with `boxes` boxes per copy when
+// n_dim is a multiple of 64, as above.
 static bool map_weight_mnmajor(CUtensorMap* m, const void* base, int64_t groups, int64_t k_dim,
-                               int64_t n_dim) {
-  const uint64_t dims[3] = {uint64_t(n_dim), uint64_t(k_dim), uint64_t(groups)};
-  const uint64_t strides[2] = {uint64_t(n_dim) * 2, uint64_t(n_dim) * uint64_t(k_dim) * 2};
-  const uint32_t box[3] = {64, 64, 1};
-  return make_map(m, base, 3, dims, strides, box);
+                               int64_t n_dim, int boxes, int32_t* fused) {
+  return map_rows_mnmajor(m, base, groups, k_dim, n_dim, boxes, fused);
 }
 // Stacked weights [G, n_dim, k_dim] with k contiguous (the same tensors read "transposed" in the
 // backward): K-major B operand, 64 (k) x BN (n) box.
@@ -102,9 +110,11 @@ static int sm_count() {
 // Persistent launch: one CTA per SM (fewer if the tile list is shorter than that).
 template <int BN, int STAGES, bool B_MN, int EPI, bool GATHER_A = false>
 static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2,
-                       const RowsArgs& args, int64_t max_tiles, cudaStream_t st) {
+                       const CUtensorMap& tmOut, const RowsArgs& args, int64_t max_tiles,
+                       cudaStream_t st) {
   auto kern = rows_gemm_kernel<BN, STAGES, B_MN, EPI, GATHER_A>;
-  constexpr int smem = RowsSmem<BN, STAGES>::DYNAMIC;
+  constexpr int smem = RowsSmem<BN, STAGES, EPI>::DYNAMIC;
+  static_assert(smem <= 232448, "shared memory of a row GEMM exceeds the 227 KB per-CTA limit");
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [&] {
@@ -114,7 +124,7 @@ static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   const int64_t sms = sm_count();
   const unsigned grid = unsigned(max_tiles < sms ? max_tiles : sms);
   const cudaError_t err = launch_pdl(kern, dim3(grid), dim3(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS),
-                                     size_t(smem), st, tmA, tmB, tmB2, args);
+                                     size_t(smem), st, tmA, tmB, tmB2, tmOut, args);
   return err == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
@@ -202,9 +212,11 @@ int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w
     return MOE_B200_ERR_ALIGN;
   CHECK_EXTRA();
   CUtensorMap tmA, tmB, tmB2;
-  if (!map_weight_mnmajor(&tmB, w_in, n_groups, d_model, 2 * d_hidden)) return MOE_B200_ERR_TMA;
+  int32_t fused = 0;
+  if (!map_weight_mnmajor(&tmB, w_in, n_groups, d_model, 2 * d_hidden, 4, &fused))
+    return MOE_B200_ERR_TMA;
   tmB2 = tmB;
-  if (n_extra > 0 && !map_weight_mnmajor(&tmB2, w_extra, n_extra, d_model, 2 * d_hidden))
+  if (n_extra > 0 && !map_weight_mnmajor(&tmB2, w_extra, n_extra, d_model, 2 * d_hidden, 4, &fused))
     return MOE_B200_ERR_TMA;
   if (gather_top_k > 0)
     tmA = tmB;  // unused: A rows are gathered with cp.async
@@ -214,6 +226,7 @@ int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w
   g.num_k = (d_model + BK - 1) / BK;
   g.n_dim = 2 * d_hidden;
   g.n_chunks = 1;
+  g.b_fused = fused;
   g.out = static_cast<__nv_bfloat16*>(hid);
   g.ld_out = d_hidden;
   g.out_gstride = rows * int64_t(d_hidden);
@@ -229,8 +242,8 @@ int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t tiles = max_tiles(rows, 1, n_fixed_groups);
   if (gather_top_k > 0)
-    return launch_rows<256, 4, true, EPI_GLU, true>(tmA, tmB, tmB2, g, tiles, st);
-  return launch_rows<256, 4, true, EPI_GLU>(tmA, tmB, tmB2, g, tiles, st);
+    return launch_rows<256, 4, true, EPI_GLU, true>(tmA, tmB, tmB2, tmB, g, tiles, st);
+  return launch_rows<256, 4, true, EPI_GLU>(tmA, tmB, tmB2, tmB, g, tiles, st);
 }
 
 int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void* w_out,
@@ -245,18 +258,21 @@ int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void*
   if (!aligned16(hid) || !aligned16(w_out) || !aligned16(y)) return MOE_B200_ERR_ALIGN;
   CHECK_EXTRA();
   const int gdim = n_fixed_groups > 0 ? n_fixed_groups : 1;
-  CUtensorMap tmA, tmB, tmB2;
+  CUtensorMap tmA, tmB, tmB2, tmOut;
+  int32_t fused = 0;
   if (!map_rows_kmajor(&tmA, hid, gdim, rows, k_dim) ||
-      !map_weight_mnmajor(&tmB, w_out, n_groups, k_dim, d_model))
+      !map_weight_mnmajor(&tmB, w_out, n_groups, k_dim, d_model, 3, &fused) ||
+      !map_rows_kmajor(&tmOut, y, gdim, rows, d_model))  // stored as 64-column x 128-row boxes
     return MOE_B200_ERR_TMA;
   tmB2 = tmB;
-  if (n_extra > 0 && !map_weight_mnmajor(&tmB2, w_extra, n_extra, k_dim, d_model))
+  if (n_extra > 0 && !map_weight_mnmajor(&tmB2, w_extra, n_extra, k_dim, d_model, 3, &fused))
     return MOE_B200_ERR_TMA;
   RowsArgs g = base_args(expert_ids, n_post_pad, n_fixed_groups, rows, status);
   g.a_grouped = n_fixed_groups > 0;
   g.num_k = (k_dim + BK - 1) / BK;
   g.n_dim = d_model;
   g.n_chunks = (d_model + 191) / 192;
+  g.b_fused = fused;
   g.sorted_ids = sorted_ids;
   g.n_pairs = int32_t(n_pairs);
   g.pair_w = static_cast<const __nv_bfloat16*>(pair_w);
@@ -265,7 +281,7 @@ int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void*
   g.out_gstride = rows * int64_t(d_model);
   g.n_groups_b1 = n_extra > 0 ? n_groups : INT32_MAX;
   return launch_rows<192, 4, true, EPI_SCALE>(
-      tmA, tmB, tmB2, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
+      tmA, tmB, tmB2, tmOut, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
 }
 
 int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, const void* w_out,
@@ -318,8 +334,8 @@ int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, c
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t tiles = max_tiles(rows, 1, n_fixed_groups);
   if (gather_top_k > 0)
-    return launch_rows<128, 6, false, EPI_GLUBWD, true>(tmA, tmB, tmB2, g, tiles, st);
-  return launch_rows<128, 6, false, EPI_GLUBWD>(tmA, tmB, tmB2, g, tiles, st);
+    return launch_rows<128, 6, false, EPI_GLUBWD, true>(tmA, tmB, tmB2, tmB, g, tiles, st);
+  return launch_rows<128, 6, false, EPI_GLUBWD>(tmA, tmB, tmB2, tmB, g, tiles, st);
 }
 
 int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,
@@ -332,9 +348,10 @@ int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void
   if (!aligned16(da1) || !aligned16(w_in) || !aligned16(ydx)) return MOE_B200_ERR_ALIGN;
   CHECK_EXTRA();
   const int gdim = n_fixed_groups > 0 ? n_fixed_groups : 1;
-  CUtensorMap tmA, tmB, tmB2;
+  CUtensorMap tmA, tmB, tmB2, tmOut;
   if (!map_rows_kmajor(&tmA, da1, gdim, rows, 2 * d_hidden) ||
-      !map_weight_kmajor(&tmB, w_in, n_groups, d_model, 2 * d_hidden, 192))
+      !map_weight_kmajor(&tmB, w_in, n_groups, d_model, 2 * d_hidden, 192) ||
+      !map_rows_kmajor(&tmOut, ydx, gdim, rows, d_model))  // stored as 64-column x 128-row boxes
     return MOE_B200_ERR_TMA;
   tmB2 = tmB;
   if (n_extra > 0 && !map_weight_kmajor(&tmB2, w_extra, n_extra, d_model, 2 * d_hidden, 192))
@@ -348,8 +365,8 @@ int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void
   g.ld_out = d_model;
   g.out_gstride = rows * int64_t(d_model);
   g.n_groups_b1 = n_extra > 0 ? n_groups : INT32_MAX;
-  return launch_rows<192, 5, false, EPI_RAW>(
-      tmA, tmB, tmB2, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
+  return launch_rows<192, 4, false, EPI_RAW>(
+      tmA, tmB, tmB2, tmOut, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
 }
 
 static int64_t wgrad_items(int64_t rows, int n_groups, int routed, int ks_rows) {
@@ -414,9 +431,13 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   // rows == 0 still launches: every C[e] must be written (with zeros)
   const int64_t map_rows = rows > 0 ? rows : 1;
   // a gathered operand is token-major and copied with cp.async: it gets the other one's map
-  if (gather_which != 1 && !map_rows_mnmajor(&tmA, a, a_grouped ? n_groups : 1, map_rows, m_dim))
+  const int bn_boxes = n_dim % 256 == 0 ? 4 : 3;
+  int32_t a_fused = 0, b_fused = 0;
+  if (gather_which != 1 &&
+      !map_rows_mnmajor(&tmA, a, a_grouped ? n_groups : 1, map_rows, m_dim, BM / 64, &a_fused))
     return MOE_B200_ERR_TMA;
-  if (gather_which != 2 && !map_rows_mnmajor(&tmB, b, b_grouped ? n_groups : 1, map_rows, n_dim))
+  if (gather_which != 2 &&
+      !map_rows_mnmajor(&tmB, b, b_grouped ? n_groups : 1, map_rows, n_dim, bn_boxes, &b_fused))
     return MOE_B200_ERR_TMA;
   if (gather_which == 1) tmA = tmB;
   if (gather_which == 2) tmB = tmA;
@@ -427,6 +448,8 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   g.ks_rows = ks_rows;
   g.a_grouped = a_grouped;
   g.b_grouped = b_grouped;
+  g.a_fused = a_fused;
+  g.b_fused = b_fused;
   g.m_dim = m_dim;
   g.n_dim = n_dim;
   g.out = static_cast<__nv_bfloat16*>(dw);

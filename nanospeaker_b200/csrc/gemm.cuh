@@ -55,6 +55,9 @@ struct RowsArgs {
   int32_t n_dim;               // valid accumulator columns over all N chunks
   int32_t n_chunks;            // ceil(n_dim / BN)
   int32_t n_groups_b1;         // groups [0, n_groups_b1) read the first B stack, the rest the second
+  int32_t b_fused;             // MN-major B: the maps are 4-D (64 n, k, n / 64, group) and one copy
+                               // brings all BN / 64 boxes of a stage (a TMA instruction costs the
+                               // issuing thread about as much as a whole stage of MMAs)
   // epilogue
   __nv_bfloat16* out;          // main output
   int64_t ld_out;              // elements between rows of out
@@ -75,6 +78,8 @@ struct WgradArgs {
   int32_t rows_host;           // fixed schedule: every group spans rows [0, rows_host)
   int32_t ks_rows;             // rows per split-K chunk (multiple of 64)
   int32_t a_grouped, b_grouped;  // fixed schedule: operand has a leading group dim
+  int32_t a_fused, b_fused;    // the operand's map is 4-D (64 cols, row, col / 64, group): one copy
+                               // brings all 64-column boxes of a stage
   // gathered operand (routed schedule only): its row `slot` is row sorted_ids[slot] / top_k of the
   // token-major matrix gather_src [n_tokens, m_dim or n_dim]; pad slots read as zero rows
   int32_t gather_a, gather_b;

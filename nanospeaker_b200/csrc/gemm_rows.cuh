@@ -11,11 +11,19 @@ constexpr int EPI_WARPS = 8;
 constexpr int GATHER_WARPS = 4;
 constexpr int ROWS_THREADS_GATHER = ROWS_THREADS + (GATHER_WARPS - 1) * 32;
 
-template <int BN, int STAGES>
+// Epilogues that leave through TMA stage the tile in shared memory one 64-column box (128 rows x
+// 128 bytes, swizzled) at a time, in two alternating buffers. Measured at T=16384: dX (K = 256)
+// 55 -> 51 us with TMA stores, the down GEMM (K = 128, epilogue-bound) 50 -> 54 us, so only the
+// plain-store epilogue uses them.
+constexpr int OUT_BOX_BYTES = BM * 128;
+__host__ __device__ constexpr bool epi_uses_tma_store(int epi) { return epi == EPI_RAW; }
+
+template <int BN, int STAGES, int EPI = EPI_GLU>
 struct RowsSmem {
   static constexpr int B_STAGE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int STAGING_OFFSET = STAGES * STAGE_BYTES;  // 1024-byte aligned
+  static constexpr int BAR_OFFSET = STAGING_OFFSET + (epi_uses_tma_store(EPI) ? 2 * OUT_BOX_BYTES : 0);
   static constexpr int N_BARS = 2 * STAGES + 4;  // full, empty, tmem_full[2], tmem_empty[2]
   static constexpr int MISC_OFFSET = BAR_OFFSET + 8 * N_BARS;      // tmem slot, abort flag
   static constexpr int PART_OFFSET = MISC_OFFSET + 16;             // float[128] dtw partials
@@ -39,6 +47,14 @@ __device__ __forceinline__ TileCoord decode_tile(const RowsArgs& p, int t, int m
   c.n0 = nc * bn;
   c.group = p.n_fixed_groups > 0 ? c.z : __ldg(p.expert_ids + c.m_tile);
   return c;
+}
+// The owner of tile t alone (-1 past the end of the list). The producers ask for the next tile's
+// owner while they work on the current one: the lookup is a global load whose latency would
+// otherwise sit at the head of every tile.
+__device__ __forceinline__ int tile_group(const RowsArgs& p, int t, int m_tiles, int total_tiles) {
+  if (t >= total_tiles) return -1;
+  const int rest = t / p.n_chunks;
+  return p.n_fixed_groups > 0 ? rest / m_tiles : __ldg(p.expert_ids + rest % m_tiles);
 }
 
 template <int ACT, int BN>
@@ -104,10 +120,12 @@ template <int BN, int STAGES, bool B_MN, int EPI, bool GATHER_A>
 __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS, 1)
     rows_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB,
-                     const __grid_constant__ CUtensorMap tmB2, const RowsArgs p) {
+                     const __grid_constant__ CUtensorMap tmB2,
+                     const __grid_constant__ CUtensorMap tmOut, const RowsArgs p) {
   pdl_trigger();
   pdl_wait();
-  using L = RowsSmem<BN, STAGES>;
+  using L = RowsSmem<BN, STAGES, EPI>;
+  constexpr bool TMA_OUT = epi_uses_tma_store(EPI);
   static_assert(BN % 64 == 0 && BN <= 256, "BN must be a multiple of 64 up to 256");
   constexpr uint32_t TMEM_BUF = BN <= 128 ? 128 : 256;  // columns per accumulator buffer
   constexpr uint32_t TMEM_COLS = 2 * TMEM_BUF;
@@ -137,6 +155,7 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmB2);
+    if constexpr (TMA_OUT) tma_prefetch_desc(&tmOut);
     for (int s = 0; s < STAGES; ++s) {
       // gathered A: every lane of warp 0 arrives (through its cp.async) next to the TMA transaction
       mbar_init(full_bar + s, GATHER_A ? GATHER_WARPS * 32 + 1 : 1);
@@ -172,8 +191,11 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
     uint32_t it = 0;
     int pending = -1;  // stage whose copies are issued but not yet handed over
     const int r4 = lane >> 3, c = lane & 7;
+    int group_next = tile_group(p, blockIdx.x, m_tiles, total_tiles);
     for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-      const TileCoord tc = decode_tile(p, t, m_tiles, BN);
+      TileCoord tc = decode_tile(p, t, m_tiles, BN);
+      tc.group = group_next;
+      group_next = tile_group(p, t + gridDim.x, m_tiles, total_tiles);
       const int pair = __ldg(p.sorted_ids + int64_t(tc.m_tile) * BM + gw * 32 + lane);
       const int my_tok = pair < p.n_pairs ? pair / p.top_k : -1;  // token of row gw*32 + lane
       for (int kt = 0; kt < p.num_k; ++kt, ++it) {
@@ -194,9 +216,13 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
           const CUtensorMap* mb = first ? &tmB : &tmB2;
           const int gb = first ? tc.group : tc.group - p.n_groups_b1;
           if constexpr (B_MN) {
+            if (p.b_fused) {
+              tma_load_4d(sB, mb, full_bar + s, 0, k0, tc.n0 / 64, gb);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_3d(sB + j * 8192, mb, full_bar + s, tc.n0 + 64 * j, k0, gb);
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_3d(sB + j * 8192, mb, full_bar + s, tc.n0 + 64 * j, k0, gb);
+            }
           } else {
             tma_load_3d(sB, mb, full_bar + s, k0, tc.n0, gb);
           }
@@ -231,8 +257,11 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       uint32_t it = 0;
+      int group_next = tile_group(p, blockIdx.x, m_tiles, total_tiles);
       for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
-        const TileCoord tc = decode_tile(p, t, m_tiles, BN);
+        TileCoord tc = decode_tile(p, t, m_tiles, BN);
+        tc.group = group_next;
+        group_next = tile_group(p, t + gridDim.x, m_tiles, total_tiles);
         for (int kt = 0; kt < p.num_k; ++kt, ++it) {
           const int s = it % STAGES;
           const uint32_t use = it / STAGES;
@@ -251,9 +280,13 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
           const CUtensorMap* mb = first ? &tmB : &tmB2;
           const int gb = first ? tc.group : tc.group - p.n_groups_b1;
           if constexpr (B_MN) {
+            if (p.b_fused) {
+              tma_load_4d(sB, mb, full_bar + s, 0, k0, tc.n0 / 64, gb);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_3d(sB + j * 8192, mb, full_bar + s, tc.n0 + 64 * j, k0, gb);
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_3d(sB + j * 8192, mb, full_bar + s, tc.n0 + 64 * j, k0, gb);
+            }
           } else {
             tma_load_3d(sB, mb, full_bar + s, k0, tc.n0, gb);
           }
@@ -301,6 +334,7 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
     const int c_lo = half * (NCH / 2), c_hi = c_lo + NCH / 2;
 
     int j = 0;
+    [[maybe_unused]] uint32_t box_count = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++j) {
       const TileCoord tc = decode_tile(p, t, m_tiles, BN);
       const int b = j & 1;
@@ -330,17 +364,51 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
           case ACT_SIGMOID: epilogue_glu<ACT_SIGMOID, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row); break;
           default: epilogue_glu<ACT_TANH, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row); break;
         }
-      } else if constexpr (EPI == EPI_RAW || EPI == EPI_SCALE) {
+      } else if constexpr (EPI == EPI_SCALE) {
 #pragma unroll 1
         for (int c = c_lo; c < c_hi; ++c) {
           float v[32];
           tmem_ld32(taddr + c * 32, v);
           tmem_ld_wait();
-          if constexpr (EPI == EPI_SCALE) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= w;
-          }
+          for (int i = 0; i < 32; ++i) v[i] *= w;
           if (row_ok && tc.n0 + c * 32 < p.n_dim) store_bf16x32(out_row + tc.n0 + c * 32, v);
+        }
+      } else if constexpr (EPI == EPI_RAW) {
+        // The tile leaves as 64-column boxes: the eight warps fill one box in shared memory (warp
+        // half h converts accumulator columns 32h..32h+31 of the box for its 32 rows, 16-byte
+        // pieces at the swizzled position a TMA load would have put them), then one thread hands
+        // the box to TMA, whose stores are whole 128-byte lines. Two buffers alternate; before a
+        // buffer is filled again the issuing thread has waited for the store that last read it.
+        const bool issuer = warp == 2 && lane == 0;
+        constexpr int NB = BN / 64;
+        float v[2][32];  // the next box's accumulator columns are in flight while this one is packed
+        tmem_ld32(taddr + half * 32, v[0]);
+#pragma unroll
+        for (int jb = 0; jb < NB; ++jb, ++box_count) {
+          tmem_ld_wait();
+          if (jb + 1 < NB) tmem_ld32(taddr + (jb + 1) * 64 + half * 32, v[(jb + 1) & 1]);
+          float* cur = v[jb & 1];
+          const uint32_t buf = smem_u32(smem + L::STAGING_OFFSET + (box_count & 1) * OUT_BOX_BYTES);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t wd[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(cur[8 * i + 2 * k], cur[8 * i + 2 * k + 1]);
+              wd[k] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            st_shared_v4(buf + row * 128 + (((half * 4 + i) ^ (row & 7)) << 4), wd[0], wd[1], wd[2],
+                         wd[3]);
+          }
+          fence_proxy_async();
+          if (issuer) bulk_wait_read<0>();  // the other buffer's last store has read its data
+          epi_bar_sync(EPI_WARPS * 32);
+          if (issuer && tc.n0 + jb * 64 < p.n_dim) {
+            tma_store_3d(&tmOut, smem + L::STAGING_OFFSET + (box_count & 1) * OUT_BOX_BYTES,
+                         tc.n0 + jb * 64, tc.m_tile * BM, tc.z);
+            bulk_commit();
+          }
         }
       } else {  // EPI_GLUBWD
         const __nv_bfloat16* a1 = p.aux + tc.z * p.aux_gstride + grow * (2 * BN);
@@ -367,6 +435,10 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar + b);
+    }
+    // shared memory must outlive the last stores' reads
+    if constexpr (TMA_OUT) {
+      if (warp == 2 && lane == 0) bulk_wait_read<0>();
     }
   }
 

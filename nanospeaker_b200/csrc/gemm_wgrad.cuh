@@ -14,6 +14,10 @@ namespace moe {
 constexpr int WGRAD_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
 constexpr int WGRAD_THREADS_GATHER = 320 + (GATHER_WARPS - 1) * 32;  // + producer warps 10..12
 constexpr int WGRAD_MAX_GROUPS = 256;
+// Work items are walked longest first (up to this many; beyond it, in list order): CTAs take items
+// round-robin, and with runs of very different lengths the list order left some CTAs with 1.6x the
+// mean work at the bench's skew, the sorted order with 1.2x.
+constexpr int WGRAD_SORT_MAX = 1024;
 
 template <int BN, int STAGES>
 struct WgradSmem {
@@ -24,7 +28,8 @@ struct WgradSmem {
   static constexpr int MISC_OFFSET = BAR_OFFSET + 8 * N_BARS;
   static constexpr int TABLE_OFFSET = MISC_OFFSET + 16;  // int first_item[G+1], int run_start[G+1]
   static constexpr int TOK_OFFSET = TABLE_OFFSET + 2 * (WGRAD_MAX_GROUPS + 1) * 4;  // int[64]
-  static constexpr int TOTAL = TOK_OFFSET + 64 * 4;
+  static constexpr int ORDER_OFFSET = TOK_OFFSET + 64 * 4;  // int order[SORT_MAX], int size[SORT_MAX]
+  static constexpr int TOTAL = ORDER_OFFSET + 2 * WGRAD_SORT_MAX * 4;
   static constexpr int DYNAMIC = TOTAL + 1024;
 };
 
@@ -150,7 +155,28 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int tiles_xy = tiles_x * tiles_y;
-  const int total = first_item[p.n_groups] * tiles_xy;  // t = item * tiles_xy + tile
+  const int n_items = first_item[p.n_groups];
+  const int total = n_items * tiles_xy;  // t = position in the walk order * tiles_xy + tile
+  // walk order: items by decreasing length, ties by index (the same permutation in every CTA)
+  int* order = reinterpret_cast<int*>(smem + L::ORDER_OFFSET);
+  int* isize = order + WGRAD_SORT_MAX;
+  const bool sorted = n_items <= WGRAD_SORT_MAX;
+  if (sorted) {
+    for (int i = threadIdx.x; i < n_items; i += blockDim.x)
+      isize[i] = wgrad_item(p, first_item, run_start, i).num_k;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_items; i += blockDim.x) {
+      const int mine = isize[i];
+      int rank = 0;
+      for (int k = 0; k < n_items; ++k) {
+        const int other = isize[k];
+        rank += (other > mine || (other == mine && k < i)) ? 1 : 0;
+      }
+      order[rank] = i;
+    }
+    __syncthreads();
+  }
+  auto item_at = [&](int pos) { return sorted ? order[pos] : pos; };
 
   if (warp == 0 || warp >= 2 + EPI_WARPS) {
     // Producers. Plain operands arrive by TMA (warp 0, lane 0). A gathered operand is copied with
@@ -162,7 +188,7 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
       uint32_t it = 0;
       int pending = -1;  // stage whose cp.async copies are issued but not yet handed over
       for (int t = blockIdx.x; t < total && !*abort_flag; t += gridDim.x) {
-        const WgradItem w = wgrad_item(p, first_item, run_start, t / tiles_xy);
+        const WgradItem w = wgrad_item(p, first_item, run_start, item_at(t / tiles_xy));
         const int txy = t % tiles_xy;
         const int m0 = (txy / tiles_y) * BM, n0 = (txy % tiles_y) * BN;
         const int ga = p.a_grouped ? w.group : 0, gb = p.b_grouped ? w.group : 0;
@@ -195,14 +221,22 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
             mbar_expect_tx(full_bar + s, (GATHER == 1 ? 0 : A_STAGE_BYTES) +
                                              (GATHER == 2 ? 0 : L::B_STAGE_BYTES));
             if (GATHER != 1) {
+              if (p.a_fused) {
+                tma_load_4d(sA, &tmA, full_bar + s, 0, r, m0 / 64, ga);
+              } else {
 #pragma unroll
-              for (int i = 0; i < BM / 64; ++i)
-                tma_load_3d(sA + i * 8192, &tmA, full_bar + s, m0 + 64 * i, r, ga);
+                for (int i = 0; i < BM / 64; ++i)
+                  tma_load_3d(sA + i * 8192, &tmA, full_bar + s, m0 + 64 * i, r, ga);
+              }
             }
             if (GATHER != 2) {
+              if (p.b_fused) {
+                tma_load_4d(sB, &tmB, full_bar + s, 0, r, n0 / 64, gb);
+              } else {
 #pragma unroll
-              for (int jj = 0; jj < BN / 64; ++jj)
-                tma_load_3d(sB + jj * 8192, &tmB, full_bar + s, n0 + 64 * jj, r, gb);
+                for (int jj = 0; jj < BN / 64; ++jj)
+                  tma_load_3d(sB + jj * 8192, &tmB, full_bar + s, n0 + 64 * jj, r, gb);
+              }
             }
           }
           if (gather) {
@@ -245,7 +279,7 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
       uint32_t it = 0;
       int ju = 0;  // tiles that really used an accumulator buffer so far
       for (int t = blockIdx.x; t < total && !*abort_flag; t += gridDim.x) {
-        const WgradItem w = wgrad_item(p, first_item, run_start, t / tiles_xy);
+        const WgradItem w = wgrad_item(p, first_item, run_start, item_at(t / tiles_xy));
         if (w.num_k == 0) continue;  // empty run: the epilogue writes zeros, no accumulator used
         const int b = ju & 1;
         const uint32_t use = uint32_t(ju) >> 1;
@@ -283,7 +317,7 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
 
     int ju = 0;  // tiles that really used an accumulator buffer so far (same count as the MMA warp)
     for (int t = blockIdx.x; t < total; t += gridDim.x) {
-      const int j = t / tiles_xy, txy = t % tiles_xy;
+      const int j = item_at(t / tiles_xy), txy = t % tiles_xy;
       const WgradItem w = wgrad_item(p, first_item, run_start, j);
       const int m0 = (txy / tiles_y) * BM, n0 = (txy % tiles_y) * BN;
       const bool have_acc = w.num_k > 0;
