@@ -385,7 +385,7 @@ def run_ours(args):
     static_x = dev_x[0].clone().requires_grad_(True)
     static_dout = dev_dout[0].clone()
 
-    def capture(with_loss, static_x=static_x):
+    def capture(with_loss, static_x=static_x, static_dout=static_dout):
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -395,7 +395,7 @@ def run_ours(args):
                 static_x.grad = None
                 out = m(static_x)
                 if with_loss:
-                    (out.float().square().mean() + m.aux_loss).backward()
+                    (out.mean(dtype=torch.float32) + m.aux_loss).backward()
                 else:
                     torch.autograd.backward([out, m.aux_loss], [static_dout, one])
         torch.cuda.current_stream().wait_stream(side)
@@ -412,7 +412,7 @@ def run_ours(args):
         with torch.cuda.graph(graph):
             out = m(static_x)
             if with_loss:
-                loss = out.float().square().mean() + m.aux_loss
+                loss = out.mean(dtype=torch.float32) + m.aux_loss
                 loss.backward()
             else:
                 loss = None
@@ -447,14 +447,26 @@ def run_ours(args):
     use_graph = not args.no_graph and not (args.grad_allreduce and world > 1)
     eager_ms, _, _ = timed(step, args.steps, warmup)
     if use_graph:
-        graph, _, per_step_launches = capture(with_loss=False)
-        # e2e: two input buffers / graphs in ping-pong, so the pinned-host -> device copy of step
-        # i+1 runs on a copy stream while step i computes (what an input pipeline does)
+        # value: one graph per resident input set (the sets are cycled so that no step finds its
+        # input in L2); nothing but the graph replay is inside a timed step
+        graph_sets = [capture(False, dev_x[i].clone().requires_grad_(True), dev_dout[i])
+                      for i in range(N_INPUT_SETS)]
+        per_step_launches = graph_sets[0][2]
+
+        def value_step(i):
+            graph_sets[i % N_INPUT_SETS][0].replay()
+
+        # e2e: two input buffers / graphs in ping-pong. The pinned-host -> device copy of step i+1
+        # runs on a copy stream while step i computes (what an input pipeline does), and the loss
+        # of step i is copied to pinned host memory on that stream too and read by the host one
+        # step later (what a logging training loop does), so the device never waits for the host.
         e2e_x = [static_x, dev_x[1].clone().requires_grad_(True)]
         e2e_graphs = [capture(with_loss=True, static_x=bx) for bx in e2e_x]
-        copy_stream = torch.cuda.Stream()
+        copy_stream, d2h_stream = torch.cuda.Stream(), torch.cuda.Stream()
         copied = [torch.cuda.Event(), torch.cuda.Event()]
         consumed = [torch.cuda.Event(), torch.cuda.Event()]
+        loss_read = [torch.cuda.Event(), torch.cuda.Event()]
+        loss_host = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(2)]
 
         def prefetch(i):
             b = i % 2
@@ -463,23 +475,27 @@ def run_ours(args):
                 e2e_x[b].detach().copy_(host_x[i % N_INPUT_SETS], non_blocking=True)
                 copied[b].record(copy_stream)
 
-        def value_step(i):
-            static_x.detach().copy_(dev_x[i % N_INPUT_SETS])
-            static_dout.copy_(dev_dout[i % N_INPUT_SETS])
-            graph.replay()
-
-        state = {"next": None}
+        state = {"next": None, "pending": None}
 
         def e2e_step(i):
             b = i % 2
             if state["next"] != i:                        # first step of a run: nothing prefetched
                 prefetch(i)
+                state["pending"] = None
             torch.cuda.current_stream().wait_event(copied[b])
             e2e_graphs[b][0].replay()
             consumed[b].record()
             prefetch(i + 1)                               # H2D of the next step's input
+            with torch.cuda.stream(d2h_stream):           # D2H of this step's loss
+                d2h_stream.wait_event(consumed[b])
+                loss_host[b].copy_(e2e_graphs[b][1].detach(), non_blocking=True)
+                loss_read[b].record(d2h_stream)
             state["next"] = i + 1
-            return e2e_graphs[b][1].item()                # D2H read of this step's loss
+            prev, state["pending"] = state["pending"], b
+            if prev is None:
+                return None
+            loss_read[prev].synchronize()                 # the previous step's loss has arrived
+            return float(loss_host[prev])
     else:
         value_step = step
         l0 = K.LAUNCHES
@@ -491,7 +507,7 @@ def run_ours(args):
                 p.grad = None
             x = host_x[i % N_INPUT_SETS].to(dev, non_blocking=True).requires_grad_(True)
             out = m(x)
-            loss = out.float().square().mean() + m.aux_loss
+            loss = out.mean(dtype=torch.float32) + m.aux_loss
             loss.backward()
             return loss.item()
 
@@ -517,7 +533,8 @@ def run_ours(args):
                     "ms_per_step": e2e_ms / args.steps,
                     "how": "MoEBlock.forward + loss.backward captured in a CUDA graph; every "
                            "step copies its x from pinned host memory (on a copy stream, "
-                           "overlapping the previous step) and reads its loss back"},
+                           "overlapping the previous step) and copies its loss to pinned host "
+                           "memory, which the host reads one step later"},
             "gpu_launches": launches, "clocks": clocks,
             "pct_bf16_peak": {"measured_burst": 100 * value / world * FLOP_PER_TOKEN_FWD_BWD
                               / (pk["bf16_tflops"] * 1e12),

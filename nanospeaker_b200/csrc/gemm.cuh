@@ -176,6 +176,13 @@ __device__ __forceinline__ void store_f32x32(float* dst, const float* v) {
 __device__ __forceinline__ void epi_bar_sync(int nthreads) {
   asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
 }
+// Named barrier `id` over nthreads threads in total: arrivers do not wait, syncers wait for all.
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 
 // Issue the four K=16 MMAs of one 64-wide k stage.
 template <int BN, bool A_MN, bool B_MN>

@@ -333,11 +333,28 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
     static_assert(NCH % 2 == 0, "column chunks must split evenly over the two epilogue halves");
     const int c_lo = half * (NCH / 2), c_hi = c_lo + NCH / 2;
 
+    // This row's pair id and router weight are two dependent global loads: they are issued two
+    // tiles / one tile ahead so that their latency is spent under the previous tiles' work.
+    const bool fixed = p.n_fixed_groups > 0;
+    auto load_pair = [&](int t) {
+      if (t >= total_tiles || fixed || p.sorted_ids == nullptr) return p.n_pairs;
+      return __ldg(p.sorted_ids + int64_t((t / p.n_chunks) % m_tiles) * BM + row);
+    };
+    auto load_w = [&](int pr) {
+      if (p.pair_w == nullptr) return 1.f;
+      return pr < p.n_pairs ? __bfloat162float(__ldg(p.pair_w + pr)) : 0.f;
+    };
+    int pair = load_pair(blockIdx.x);
+    int pair_n = load_pair(blockIdx.x + gridDim.x);
+    float w = load_w(pair);
+
     int j = 0;
     [[maybe_unused]] uint32_t box_count = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++j) {
       const TileCoord tc = decode_tile(p, t, m_tiles, BN);
       const int b = j & 1;
+      const float w_n = load_w(pair_n);                    // next tile's weight
+      const int pair_nn = load_pair(t + 2 * gridDim.x);    // the pair id of the tile after that
       // A wait that gives up (status already flagged) falls through: the epilogue keeps its
       // barrier protocol intact and the host sees the status word.
       if (!mbar_wait(tfull_bar + b, (uint32_t(j) >> 1) & 1, p.status))
@@ -346,12 +363,7 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
       const uint32_t taddr = tmem_base + b * TMEM_BUF + (uint32_t(q * 32) << 16);
 
       const int64_t grow = int64_t(tc.m_tile) * BM + row;
-      const bool fixed = p.n_fixed_groups > 0;
       const bool row_ok = !fixed || grow < p.rows_host;
-      int pair = p.n_pairs;
-      if (!fixed && p.sorted_ids != nullptr) pair = __ldg(p.sorted_ids + grow);
-      float w = 1.f;
-      if (p.pair_w != nullptr) w = pair < p.n_pairs ? __bfloat162float(p.pair_w[pair]) : 0.f;
       __nv_bfloat16* out_row = p.out + tc.z * p.out_gstride + grow * p.ld_out;
 
       if constexpr (EPI == EPI_GLU) {
@@ -423,18 +435,27 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
           default: part = epilogue_glubwd<ACT_TANH, BN>(taddr, c_lo, c_hi, row_ok, w, a1, da1, hw); break;
         }
         // <G, hidden> of a row is split over the two column halves: fold half 1 into half 0
+        // Barrier 1 hands half 1's partials to half 0, barrier 2 hands the buffer back; each half
+        // only ever waits for the other one's previous step.
         if (p.dtw != nullptr) {
-          if (half == 1) dtw_part[row] = part;
-          epi_bar_sync(EPI_WARPS * 32);
-          if (half == 0 && row_ok && pair < p.n_pairs)
-            p.dtw[pair] = __float2bfloat16(part + dtw_part[row]);
-          epi_bar_sync(EPI_WARPS * 32);
+          if (half == 1) {
+            if (j > 0) named_bar_sync(2, EPI_WARPS * 32);
+            dtw_part[row] = part;
+            named_bar_arrive(1, EPI_WARPS * 32);
+          } else {
+            named_bar_sync(1, EPI_WARPS * 32);
+            if (row_ok && pair < p.n_pairs) p.dtw[pair] = __float2bfloat16(part + dtw_part[row]);
+            if (t + int(gridDim.x) < total_tiles) named_bar_arrive(2, EPI_WARPS * 32);
+          }
         }
       }
       // this warp has drained its share of accumulator buffer b
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar + b);
+      pair = pair_n;
+      pair_n = pair_nn;
+      w = w_n;
     }
     // shared memory must outlive the last stores' reads
     if constexpr (TMA_OUT) {
