@@ -123,3 +123,39 @@ def test_dispatch_flags_out_of_range_expert():
     with pytest.raises(RuntimeError, match="expert id"):
         K().check_status("cuda")
     K().check_status("cuda")  # cleared by the failed check
+
+
+@pytest.mark.parametrize("T,E,k,S,full,norm", [(777, 76, 6, 2, True, True), (64, 76, 6, 2, False, True),
+                                              (300, 8, 2, 0, True, False), (129, 200, 8, 1, True, True)])
+def test_router_fused_matches_router_topk_on_the_same_logits(T, E, k, S, full, norm):
+    """The whole-block router kernels (bf16 logits with a padded row stride + fp32 bias, shared
+    experts appended, column sums) against the fp32 stand-alone router on identical values."""
+    from nanospeaker_b200 import kernels as K
+    torch.manual_seed(E + k)
+    ld = (E + 63) // 64 * 64
+    logits = torch.zeros(T, ld, device="cuda", dtype=torch.bfloat16)
+    logits[:, :E] = torch.randn(T, E, device="cuda").bfloat16()
+    bias = torch.randn(E, device="cuda") * 0.3
+    w_all, idx_all, colsum = K.router_fused(logits, bias, E, k, S, norm, full)
+    ref_logits = logits[:, :E].float() + bias
+    w, idx, probs = K.router_topk(ref_logits, k, norm, full, True)
+    assert torch.equal(idx_all[:, :k], idx)                                # bit-exact selection
+    assert torch.equal(idx_all[:, k:], torch.arange(E, E + S, device="cuda").expand(T, S))
+    assert torch.equal(w_all[:, k:].float(), torch.ones(T, S, device="cuda"))
+    assert torch.allclose(w_all[:, :k].float(), w, atol=4e-3, rtol=8e-3)   # bf16 rounding of w
+    if full:
+        assert torch.allclose(colsum, probs.sum(0), rtol=1e-4, atol=1e-4)
+        counts = torch.bincount(idx.reshape(-1), minlength=E).int()
+        aux = K.balance_loss(colsum, counts, E, T, 1e-2)
+        share = counts.float() / counts.sum()
+        ref_aux = 1e-2 * E * (share * probs.mean(0)).sum()
+        assert abs(float(aux) - float(ref_aux)) < 1e-5
+        # backward: d(logits) of  sum(w * g) + aux  from both kernels
+        g = torch.randn(T, k + S, device="cuda").bfloat16()
+        d_aux = torch.ones(1, device="cuda")
+        dl = K.router_fused_bwd(logits, bias, idx_all, g, E, k, S, norm, full, d_aux, counts, 1e-2, ld)
+        d_probs = (1e-2 * E / T) * share.expand(T, E).contiguous()
+        ref_dl = K.router_topk_bwd(ref_logits, idx, g[:, :k].float(), d_probs, norm, full)
+        assert torch.all(dl[:, E:] == 0)
+        assert rel_l2(dl[:, :E].float(), ref_dl) < 1e-2
+    K.check_status("cuda")
