@@ -159,6 +159,13 @@ int moe_b200_combine(const void* y, const int32_t* inv_ids, int64_t n_tokens, in
                      int32_t d_model, const void* extra, const void* extra2, void* out,
                      void* stream);
 
+/* dst[r, c] = c < cols ? src[r, c] : 0 for 0 <= c < dst_ld; 16-bit elements, row strides src_ld /
+ * dst_ld elements. Pads the router weight [d_model, n_experts] (src/model/router.py:51) to the
+ * 64-column multiple the GEMM kernels' tensor maps need, and strips the pad columns from its
+ * gradient. No reference counterpart (the reference's router is a plain matmul). */
+int moe_b200_copy_cols(const void* src, int64_t rows, int32_t cols, int32_t src_ld, void* dst,
+                       int32_t dst_ld, void* stream);
+
 /* Schedule arguments shared by the row-grouped GEMMs below:
  *   rows            rows of the slot-ordered A buffer (l_cap), or the token count when
  *                   n_fixed_groups > 0

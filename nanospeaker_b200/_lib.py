@@ -45,6 +45,8 @@ SIGNATURES = {
         ctypes.c_int, [_c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp, _c_i64, _c_vp, _c_vp]),
     "moe_b200_combine": (
         ctypes.c_int, [_c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp]),
+    "moe_b200_copy_cols": (
+        ctypes.c_int, [_c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_i32, _c_vp]),
     "moe_b200_up_gemm": (
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,

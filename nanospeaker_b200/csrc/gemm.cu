@@ -369,6 +369,10 @@ int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void
       tmA, tmB, tmB2, tmOut, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
 }
 
+// The scratch buffer starts with the item table ([G + 1] int32), the partial tiles follow.
+constexpr size_t WGRAD_TABLE_BYTES = 4096;
+static_assert((WGRAD_MAX_GROUPS + 1) * sizeof(int32_t) <= WGRAD_TABLE_BYTES, "item table too small");
+
 static int64_t wgrad_items(int64_t rows, int n_groups, int routed, int ks_rows) {
   return routed ? rows / ks_rows + n_groups : int64_t(n_groups) * wgrad_chunks(int(rows), ks_rows);
 }
@@ -395,8 +399,8 @@ int moe_b200_wgrad_scratch_bytes(int32_t m_dim, int32_t n_dim, int64_t rows, int
   if (ks_rows == 0) ks_rows = auto_ks_rows(m_dim, n_dim, rows, n_groups, routed);
   const int bn = n_dim % 256 == 0 ? 256 : 192;
   const int64_t tiles_xy = int64_t((m_dim + BM - 1) / BM) * ((n_dim + bn - 1) / bn);
-  *partial_bytes = size_t(wgrad_items(rows, n_groups, routed, ks_rows)) * size_t(tiles_xy) * BM *
-                   bn * sizeof(float);
+  *partial_bytes = WGRAD_TABLE_BYTES + size_t(wgrad_items(rows, n_groups, routed, ks_rows)) *
+                                           size_t(tiles_xy) * BM * bn * sizeof(float);
   return MOE_B200_OK;
 }
 
@@ -455,7 +459,8 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   g.out = static_cast<__nv_bfloat16*>(dw);
   g.out_extra = static_cast<__nv_bfloat16*>(dw_extra);
   g.n_out1 = n_first;
-  g.partials = static_cast<float*>(partials);
+  g.item_table = static_cast<int32_t*>(partials);
+  g.partials = reinterpret_cast<float*>(static_cast<char*>(partials) + WGRAD_TABLE_BYTES);
   g.status = status;
   g.gather_a = gather_which == 1;
   g.gather_b = gather_which == 2;
@@ -468,7 +473,7 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   const bool may_split = rows > ks_rows;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned tx = unsigned((m_dim + BM - 1) / BM);
-  const unsigned gy = unsigned(n_groups < 4 ? n_groups : 4);  // reduce CTAs striding over groups
+  const unsigned gy = unsigned(n_groups);  // one reduce CTA per (tile slice, run)
   int rc;
   if (n_dim % 256 == 0) {
     const unsigned ty = unsigned(n_dim / 256);

@@ -91,6 +91,8 @@ struct WgradArgs {
   __nv_bfloat16* out_extra;    // [G - n_out1, m_dim, n_dim]: the remaining groups (may be null)
   int32_t n_out1;
   float* partials;             // fp32 scratch for the partial tiles of split runs
+  int32_t* item_table;         // scratch [G + 1]: first work item of every run, written by the GEMM
+                               // pass for the reduction pass
   int32_t* status;
 };
 

@@ -130,7 +130,14 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  if (warp == 2) wgrad_build_table(p, lane, first_item, run_start);
+  if (warp == 2) {
+    wgrad_build_table(p, lane, first_item, run_start);
+    // the reduction pass reads the item counts from global memory instead of rebuilding them
+    if (blockIdx.x == 0) {
+      __syncwarp();
+      for (int g = lane; g <= p.n_groups; g += 32) p.item_table[g] = first_item[g];
+    }
+  }
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -372,16 +379,13 @@ constexpr int WGRAD_REDUCE_SPLIT = 16;  // CTAs sharing the reduction of one out
 
 // Second pass of the split-K weight gradient: for every (run, tile) that was split, add the fp32
 // partial tiles in chunk order and write bf16. grid = (tiles_x * tiles_y * WGRAD_REDUCE_SPLIT,
-// n_groups); tiles_x / tiles_y / BN must be those of the first pass.
+// n_groups); tiles_x / tiles_y / BN must be those of the first pass, which also left the item
+// table in p.item_table.
 template <int BN>
 __global__ void __launch_bounds__(256)
     wgrad_reduce_kernel(const WgradArgs p, int tiles_x, int tiles_y) {
   pdl_trigger();
   pdl_wait();
-  __shared__ int first_item[WGRAD_MAX_GROUPS + 1];
-  __shared__ int run_start[WGRAD_MAX_GROUPS + 1];
-  if (threadIdx.x < 32) wgrad_build_table(p, threadIdx.x, first_item, run_start);
-  __syncthreads();
   const int tile_xy = blockIdx.x / WGRAD_REDUCE_SPLIT;
   const int slice = blockIdx.x % WGRAD_REDUCE_SPLIT;
   const int tile_m = tile_xy / tiles_y, n0 = (tile_xy % tiles_y) * BN;
@@ -389,9 +393,9 @@ __global__ void __launch_bounds__(256)
   constexpr int64_t slot_elems = int64_t(BM) * BN;
   constexpr int vecs = BM * BN / 4;                  // float4 per tile
   constexpr int per_slice = vecs / WGRAD_REDUCE_SPLIT;
-  // the table is built once per CTA; the CTA then walks the runs that were actually split
+  // one CTA per (tile slice, run); CTAs of runs that were not split leave at once
   for (int g = blockIdx.y; g < p.n_groups; g += gridDim.y) {
-    const int first = first_item[g], n_c = first_item[g + 1] - first;
+    const int first = __ldg(p.item_table + g), n_c = __ldg(p.item_table + g + 1) - first;
     if (n_c <= 1) continue;
     for (int f = slice * per_slice + threadIdx.x; f < (slice + 1) * per_slice; f += blockDim.x) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);

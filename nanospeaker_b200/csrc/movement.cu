@@ -154,6 +154,22 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// dst[r, c] = c < cols ? src[r, c] : 0 for c < dst_ld: pads a matrix's rows to a TMA-friendly
+// stride (the router weight [D, E] -> [D, ld]) or drops the pad columns again.
+__global__ void __launch_bounds__(256)
+    copy_cols_kernel(const uint16_t* __restrict__ src, int64_t rows, int32_t cols, int32_t src_ld,
+                     uint16_t* __restrict__ dst, int32_t dst_ld) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t total = rows * dst_ld;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t r = i / dst_ld;
+    const int32_t c = int32_t(i - r * dst_ld);
+    dst[i] = c < cols ? src[r * src_ld + c] : uint16_t(0);
+  }
+}
+
 }  // namespace moe
 
 using namespace moe;
@@ -218,6 +234,20 @@ int moe_b200_combine(const void* y, const int32_t* inv_ids, int64_t n_tokens, in
     default: LAUNCH(0); break;
   }
 #undef LAUNCH
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+int moe_b200_copy_cols(const void* src, int64_t rows, int32_t cols, int32_t src_ld, void* dst,
+                       int32_t dst_ld, void* stream) {
+  if (rows < 0 || cols < 0 || src_ld < cols || dst_ld < 1) return MOE_B200_ERR_SHAPE;
+  if (rows == 0) return MOE_B200_OK;
+  if (!src || !dst) return MOE_B200_ERR_NULL;
+  const int64_t total = rows * dst_ld;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  launch_pdl(copy_cols_kernel, dim3(unsigned(blocks)), dim3(256), 0,
+             static_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(src), rows, cols,
+             src_ld, static_cast<uint16_t*>(dst), dst_ld);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 

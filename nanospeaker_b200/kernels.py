@@ -204,6 +204,20 @@ def _extra(w_extra):
     return (0, 0) if w_extra is None else (w_extra.data_ptr(), w_extra.shape[0])
 
 
+def copy_cols(src: torch.Tensor, dst_ld: int) -> torch.Tensor:
+    """[rows, cols] 16-bit matrix -> [rows, dst_ld]: zero-padded columns (dst_ld > cols) or the
+    first dst_ld columns (dst_ld < cols)."""
+    _need_cuda(src)
+    assert src.dim() == 2 and src.element_size() == 2 and src.stride(1) == 1
+    rows, cols = src.shape
+    dst = torch.empty((rows, dst_ld), dtype=src.dtype, device=src.device)
+    _lib.check(_lib.load().moe_b200_copy_cols(
+        src.data_ptr(), rows, min(cols, dst_ld), src.stride(0), dst.data_ptr(), dst_ld,
+        _stream(src)), "moe_b200_copy_cols")
+    _count(1 if rows else 0)
+    return dst
+
+
 def up_gemm(a, w_in, expert_ids, n_post_pad, n_fixed: int, act: int, want_raw: bool,
             gather=None, w_extra=None):
     """a x w_in [G, D, 2H] -> (act(g)*u [rows, H], raw [g|u] [rows, 2H] | None).

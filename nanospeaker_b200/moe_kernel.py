@@ -360,8 +360,7 @@ def moe_block(
     ld = _router_ld(e_n)
     ks = top_k + s_n
 
-    wp = x.new_zeros((1, d, ld))
-    wp[0, :, :e_n] = router_w
+    wp = K.copy_cols(router_w, ld).unsqueeze(0)   # [1, D, ld], zero pad columns
     logits = K.down_gemm(x, wp, None, None, 1, None, None, 0)[0]
     w_all, idx_all, colsum = K.router_fused(logits, logit_bias, e_n, top_k, s_n, normalize,
                                             full_softmax)
@@ -429,7 +428,7 @@ def moe_block_bwd(
     aux_coef: float,
     activation: str,
 ) -> _T6:
-    """[dx, d_router_w (padded [D, ld]), dW_in, dW_out, dW_sh_in, dW_sh_out] of moe_block."""
+    """[dx, d_router_w [D, E], dW_in, dW_out, dW_sh_in, dW_sh_out] of moe_block."""
     grad_out = grad_out.to(x.dtype).contiguous()
     act = _act_id(activation)
     n, d = x.shape
@@ -459,7 +458,7 @@ def moe_block_bwd(
         dl = K.router_fused_bwd(logits, logit_bias, idx_all, dtw.view(n, ks), e_n, top_k, s_n,
                                 normalize, full_softmax, d_aux, counts_all, aux_coef,
                                 logits.shape[1])
-        d_wp = K.wgrad(x, dl, None, 1)[0]
+        d_router = K.copy_cols(K.wgrad(x, dl, None, 1)[0], e_n)   # pad columns dropped
         dx_router = K.dx_gemm(dl, router_w_padded, None, None, 1)[0]
     main.wait_stream(side_out)
     main.wait_stream(side_router)
@@ -468,14 +467,14 @@ def moe_block_bwd(
     else:
         dw_in, dw_out, dw_sh_in, dw_sh_out = g_in, g_out, x.new_empty(0), x.new_empty(0)
     dx = K.combine(ydx, inv_ids, n, ks, dx_router)
-    return dx, d_wp, dw_in, dw_out, dw_sh_in, dw_sh_out
+    return dx, d_router, dw_in, dw_out, dw_sh_in, dw_sh_out
 
 
 @moe_block_bwd.register_fake
 def _(grad_out, grad_aux, x, logit_bias, w_in, w_out, w_sh_in, w_sh_out, xs, a1, logits, w_all,
       idx_all, sorted_ids, expert_ids, pad_offsets, counts_all, n_post_pad, inv_ids,
       router_w_padded, top_k, normalize, full_softmax, aux_coef, activation):
-    return (torch.empty_like(x), x.new_empty(router_w_padded.shape[1:]), torch.empty_like(w_in),
+    return (torch.empty_like(x), x.new_empty((x.shape[1], w_in.shape[0])), torch.empty_like(w_in),
             torch.empty_like(w_out),
             torch.empty_like(w_sh_in) if w_sh_in is not None else x.new_empty(0),
             torch.empty_like(w_sh_out) if w_sh_out is not None else x.new_empty(0))
@@ -511,9 +510,9 @@ def _block_backward(ctx, grad_out, grad_aux, *unused):
     bias = rest[-1] if ctx.has_bias else None
     if grad_out is None:
         grad_out = torch.zeros_like(x)
-    dx, d_wp, dw_in, dw_out, dsi, dso = moe_block_bwd(
+    dx, d_router, dw_in, dw_out, dsi, dso = moe_block_bwd(
         grad_out, grad_aux, x, bias, w_in, w_out, w_sh_in, w_sh_out, *kept, *ctx.args)
-    d_router = d_wp[:, : ctx.n_experts].to(ctx.router_dtype)
+    d_router = d_router.to(ctx.router_dtype)
     return (dx, d_router, None, dw_in, dw_out, dsi if ctx.has_shared else None,
             dso if ctx.has_shared else None, None, None, None, None, None, None)
 

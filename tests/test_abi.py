@@ -91,7 +91,7 @@ def test_arguments_are_validated_before_any_launch(lib):
     assert wg(256, 2048, 0, p) == -4    # scratch too small
     pb = ctypes.c_size_t(0)
     assert lib.moe_b200_wgrad_scratch_bytes(576, 256, 108032, 76, 1, 2048, ctypes.byref(pb)) == 0
-    assert pb.value == (108032 // 2048 + 76) * 5 * 128 * 256 * 4
+    assert pb.value == 4096 + (108032 // 2048 + 76) * 5 * 128 * 256 * 4   # item table + tiles
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
