@@ -108,12 +108,12 @@ static int sm_count() {
 }
 
 // Persistent launch: one CTA per SM (fewer if the tile list is shorter than that).
-template <int BN, int STAGES, bool B_MN, int EPI, bool GATHER_A = false>
+template <int BN, int STAGES, bool B_MN, int EPI, bool GATHER_A = false, int OUT_BOXES = 4>
 static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2,
                        const CUtensorMap& tmOut, const RowsArgs& args, int64_t max_tiles,
                        cudaStream_t st) {
-  auto kern = rows_gemm_kernel<BN, STAGES, B_MN, EPI, GATHER_A>;
-  constexpr int smem = RowsSmem<BN, STAGES, EPI>::DYNAMIC;
+  auto kern = rows_gemm_kernel<BN, STAGES, B_MN, EPI, GATHER_A, OUT_BOXES>;
+  constexpr int smem = RowsSmem<BN, STAGES, EPI, OUT_BOXES>::DYNAMIC;
   static_assert(smem <= 232448, "shared memory of a row GEMM exceeds the 227 KB per-CTA limit");
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
@@ -280,7 +280,7 @@ int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void*
   g.ld_out = d_model;
   g.out_gstride = rows * int64_t(d_model);
   g.n_groups_b1 = n_extra > 0 ? n_groups : INT32_MAX;
-  return launch_rows<192, 4, true, EPI_SCALE>(
+  return launch_rows<192, 4, true, EPI_SCALE, false, 4>(
       tmA, tmB, tmB2, tmOut, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
 }
 
@@ -365,7 +365,7 @@ int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void
   g.ld_out = d_model;
   g.out_gstride = rows * int64_t(d_model);
   g.n_groups_b1 = n_extra > 0 ? n_groups : INT32_MAX;
-  return launch_rows<192, 4, false, EPI_RAW>(
+  return launch_rows<192, 4, false, EPI_RAW, false, 3>(
       tmA, tmB, tmB2, tmOut, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
 }
 

@@ -12,18 +12,23 @@ constexpr int GATHER_WARPS = 4;
 constexpr int ROWS_THREADS_GATHER = ROWS_THREADS + (GATHER_WARPS - 1) * 32;
 
 // Epilogues that leave through TMA stage the tile in shared memory one 64-column box (128 rows x
-// 128 bytes, swizzled) at a time, in two alternating buffers. Measured at T=16384: dX (K = 256)
-// 55 -> 51 us with TMA stores, the down GEMM (K = 128, epilogue-bound) 50 -> 54 us, so only the
-// plain-store epilogue uses them.
+// 128 bytes, swizzled) at a time, in OUT_BOXES buffers used in turn.
 constexpr int OUT_BOX_BYTES = BM * 128;
-__host__ __device__ constexpr bool epi_uses_tma_store(int epi) { return epi == EPI_RAW; }
+__host__ __device__ constexpr bool epi_uses_tma_store(int epi) {
+  return epi == EPI_RAW || epi == EPI_SCALE;
+}
+// OUT_BOXES = number of staging boxes. The stores are asynchronous: the epilogue warps only wait when a buffer
+// comes round again, so the boxes in flight are what keeps HBM writing while the warps already
+// work on the next tile. (With direct stores, and with two boxes, the time to write the output
+// simply added to the rest of the kernel: down GEMM 24 us without its stores, 47 us with them.)
 
-template <int BN, int STAGES, int EPI = EPI_GLU>
+template <int BN, int STAGES, int EPI = EPI_GLU, int OUT_BOXES = 4>
 struct RowsSmem {
   static constexpr int B_STAGE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int STAGING_OFFSET = STAGES * STAGE_BYTES;  // 1024-byte aligned
-  static constexpr int BAR_OFFSET = STAGING_OFFSET + (epi_uses_tma_store(EPI) ? 2 * OUT_BOX_BYTES : 0);
+  static constexpr int STAGING_BYTES = epi_uses_tma_store(EPI) ? OUT_BOXES * OUT_BOX_BYTES : 0;
+  static constexpr int BAR_OFFSET = STAGING_OFFSET + STAGING_BYTES;
   static constexpr int N_BARS = 2 * STAGES + 4;  // full, empty, tmem_full[2], tmem_empty[2]
   static constexpr int MISC_OFFSET = BAR_OFFSET + 8 * N_BARS;      // tmem slot, abort flag
   static constexpr int PART_OFFSET = MISC_OFFSET + 16;             // float[128] dtw partials
@@ -116,7 +121,7 @@ __device__ __forceinline__ float epilogue_glubwd(uint32_t taddr, int c_lo, int c
   return part;
 }
 
-template <int BN, int STAGES, bool B_MN, int EPI, bool GATHER_A>
+template <int BN, int STAGES, bool B_MN, int EPI, bool GATHER_A, int OUT_BOXES = 4>
 __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS, 1)
     rows_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB,
@@ -124,7 +129,7 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
                      const __grid_constant__ CUtensorMap tmOut, const RowsArgs p) {
   pdl_trigger();
   pdl_wait();
-  using L = RowsSmem<BN, STAGES, EPI>;
+  using L = RowsSmem<BN, STAGES, EPI, OUT_BOXES>;
   constexpr bool TMA_OUT = epi_uses_tma_store(EPI);
   static_assert(BN % 64 == 0 && BN <= 256, "BN must be a multiple of 64 up to 256");
   constexpr uint32_t TMEM_BUF = BN <= 128 ? 128 : 256;  // columns per accumulator buffer
@@ -376,22 +381,13 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
           case ACT_SIGMOID: epilogue_glu<ACT_SIGMOID, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row); break;
           default: epilogue_glu<ACT_TANH, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row); break;
         }
-      } else if constexpr (EPI == EPI_SCALE) {
-#pragma unroll 1
-        for (int c = c_lo; c < c_hi; ++c) {
-          float v[32];
-          tmem_ld32(taddr + c * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] *= w;
-          if (row_ok && tc.n0 + c * 32 < p.n_dim) store_bf16x32(out_row + tc.n0 + c * 32, v);
-        }
-      } else if constexpr (EPI == EPI_RAW) {
+      } else if constexpr (EPI == EPI_RAW || EPI == EPI_SCALE) {
         // The tile leaves as 64-column boxes: the eight warps fill one box in shared memory (warp
         // half h converts accumulator columns 32h..32h+31 of the box for its 32 rows, 16-byte
         // pieces at the swizzled position a TMA load would have put them), then one thread hands
-        // the box to TMA, whose stores are whole 128-byte lines. Two buffers alternate; before a
-        // buffer is filled again the issuing thread has waited for the store that last read it.
+        // the box to TMA, whose stores are whole 128-byte lines. OUT_BOXES buffers take turns;
+        // before a buffer is filled again the issuing thread has waited for the store that last
+        // read it.
         const bool issuer = warp == 2 && lane == 0;
         constexpr int NB = BN / 64;
         float v[2][32];  // the next box's accumulator columns are in flight while this one is packed
@@ -401,7 +397,11 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
           tmem_ld_wait();
           if (jb + 1 < NB) tmem_ld32(taddr + (jb + 1) * 64 + half * 32, v[(jb + 1) & 1]);
           float* cur = v[jb & 1];
-          const uint32_t buf = smem_u32(smem + L::STAGING_OFFSET + (box_count & 1) * OUT_BOX_BYTES);
+          if constexpr (EPI == EPI_SCALE) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) cur[i] *= w;
+          }
+          const uint32_t buf = smem_u32(smem + L::STAGING_OFFSET + (box_count % OUT_BOXES) * OUT_BOX_BYTES);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             uint32_t wd[4];
@@ -414,10 +414,11 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
                          wd[3]);
           }
           fence_proxy_async();
-          if (issuer) bulk_wait_read<0>();  // the other buffer's last store has read its data
+          // the buffer filled next was handed to TMA OUT_BOXES - 1 stores ago: wait for that read
+          if (issuer) bulk_wait_read<OUT_BOXES - 2>();
           epi_bar_sync(EPI_WARPS * 32);
           if (issuer && tc.n0 + jb * 64 < p.n_dim) {
-            tma_store_3d(&tmOut, smem + L::STAGING_OFFSET + (box_count & 1) * OUT_BOX_BYTES,
+            tma_store_3d(&tmOut, smem + L::STAGING_OFFSET + (box_count % OUT_BOXES) * OUT_BOX_BYTES,
                          tc.n0 + jb * 64, tc.m_tile * BM, tc.z);
             bulk_commit();
           }
