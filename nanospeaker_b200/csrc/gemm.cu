@@ -123,7 +123,7 @@ static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   if (attr_err != cudaSuccess) return MOE_B200_ERR_CUDA;
   const int64_t sms = sm_count();
   const unsigned grid = unsigned(max_tiles < sms ? max_tiles : sms);
-  const cudaError_t err = launch_pdl(kern, dim3(grid), dim3(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS),
+  const cudaError_t err = launch_pdl(kern, dim3(grid), dim3(rows_threads(EPI, GATHER_A)),
                                      size_t(smem), st, tmA, tmB, tmB2, tmOut, args);
   return err == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
@@ -333,9 +333,13 @@ int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, c
   g.top_k = gather_top_k;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t tiles = max_tiles(rows, 1, n_fixed_groups);
+  // the pre-activations reach the epilogue through shared memory: 64-column x 128-row boxes
+  CUtensorMap tmAux;
+  if (!map_rows_kmajor(&tmAux, a1, n_fixed_groups > 0 ? n_fixed_groups : 1, rows, 2 * d_hidden))
+    return MOE_B200_ERR_TMA;
   if (gather_top_k > 0)
-    return launch_rows<128, 6, false, EPI_GLUBWD, true>(tmA, tmB, tmB2, tmB, g, tiles, st);
-  return launch_rows<128, 6, false, EPI_GLUBWD>(tmA, tmB, tmB2, tmB, g, tiles, st);
+    return launch_rows<128, 3, false, EPI_GLUBWD, true>(tmA, tmB, tmB2, tmAux, g, tiles, st);
+  return launch_rows<128, 3, false, EPI_GLUBWD>(tmA, tmB, tmB2, tmAux, g, tiles, st);
 }
 
 int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,

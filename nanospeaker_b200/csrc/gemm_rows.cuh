@@ -10,6 +10,13 @@ constexpr int EPI_WARPS = 8;
 // three more producer warps (10..12) join warp 0, each copying 32 of a stage's 128 rows.
 constexpr int GATHER_WARPS = 4;
 constexpr int ROWS_THREADS_GATHER = ROWS_THREADS + (GATHER_WARPS - 1) * 32;
+// The GLU-backward epilogue reads a tile of pre-activations [128 x 2 BN]: one more warp brings it
+// into shared memory by TMA one tile ahead (with per-thread global loads the epilogue waited for
+// them tile after tile: dHidden took 77 us with those loads, 50 us without).
+__host__ __device__ constexpr bool epi_loads_aux(int epi) { return epi == EPI_GLUBWD; }
+__host__ __device__ constexpr int rows_threads(int epi, bool gather) {
+  return (gather ? ROWS_THREADS_GATHER : ROWS_THREADS) + (epi_loads_aux(epi) ? 32 : 0);
+}
 
 // Epilogues that leave through TMA stage the tile in shared memory one 64-column box (128 rows x
 // 128 bytes, swizzled) at a time, in OUT_BOXES buffers used in turn.
@@ -28,8 +35,11 @@ struct RowsSmem {
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int STAGING_OFFSET = STAGES * STAGE_BYTES;  // 1024-byte aligned
   static constexpr int STAGING_BYTES = epi_uses_tma_store(EPI) ? OUT_BOXES * OUT_BOX_BYTES : 0;
-  static constexpr int BAR_OFFSET = STAGING_OFFSET + STAGING_BYTES;
-  static constexpr int N_BARS = 2 * STAGES + 4;  // full, empty, tmem_full[2], tmem_empty[2]
+  static constexpr int AUX_OFFSET = STAGING_OFFSET + STAGING_BYTES;  // 1024-byte aligned
+  static constexpr int AUX_TILE_BYTES = BM * 2 * BN * 2;             // [128 x 2 BN] bf16
+  static constexpr int BAR_OFFSET = AUX_OFFSET + (epi_loads_aux(EPI) ? 2 * AUX_TILE_BYTES : 0);
+  // full, empty, tmem_full[2], tmem_empty[2], aux_full[2], aux_empty[2]
+  static constexpr int N_BARS = 2 * STAGES + 8;
   static constexpr int MISC_OFFSET = BAR_OFFSET + 8 * N_BARS;      // tmem slot, abort flag
   static constexpr int PART_OFFSET = MISC_OFFSET + 16;             // float[128] dtw partials
   static constexpr int TOK_OFFSET = PART_OFFSET + 128 * 4;         // int[128] gathered row ids
@@ -82,24 +92,37 @@ __device__ __forceinline__ void epilogue_glu(uint32_t taddr, int c_lo, int c_hi,
   }
 }
 
-// acc = G = dOut @ W_out^T for this row; a1 = [gate | up]; H = BN. Returns this thread's share of
-// <G, hidden>.
+// 32 bf16 of row `row`, columns [col, col + 32), from a tile that TMA loaded as 64-column boxes of
+// 128 rows (128-byte swizzle): four 16-byte pieces at their swizzled positions.
+__device__ __forceinline__ void load_tile_bf16x32(uint32_t tile, int row, int col, float* v) {
+  const uint32_t base = tile + (col >> 6) * OUT_BOX_BYTES + row * 128;
+  const int piece0 = (col & 63) >> 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t w[4];
+    ld_shared_v4(base + (((piece0 + i) ^ (row & 7)) << 4), w[0], w[1], w[2], w[3]);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w[k]));
+      v[8 * i + 2 * k] = f.x;
+      v[8 * i + 2 * k + 1] = f.y;
+    }
+  }
+}
+
+// acc = G = dOut @ W_out^T for this row; a1_tile = the tile's [gate | up] pre-activations in shared
+// memory; H = BN. Returns this thread's share of <G, hidden>.
 template <int ACT, int BN>
 __device__ __forceinline__ float epilogue_glubwd(uint32_t taddr, int c_lo, int c_hi, bool row_ok,
-                                                 float w, const __nv_bfloat16* a1,
+                                                 float w, uint32_t a1_tile, int row,
                                                  __nv_bfloat16* da1, __nv_bfloat16* hw) {
   float part = 0.f;
 #pragma unroll 1
   for (int c = c_lo; c < c_hi; ++c) {
     float G[32], g[32], u[32];
     tmem_ld32(taddr + c * 32, G);
-    if (row_ok) {
-      load_bf16x32(a1 + c * 32, g);
-      load_bf16x32(a1 + BN + c * 32, u);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) g[i] = u[i] = 0.f;
-    }
+    load_tile_bf16x32(a1_tile, row, c * 32, g);
+    load_tile_bf16x32(a1_tile, row, BN + c * 32, u);
     tmem_ld_wait();
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
@@ -122,7 +145,7 @@ __device__ __forceinline__ float epilogue_glubwd(uint32_t taddr, int c_lo, int c
 }
 
 template <int BN, int STAGES, bool B_MN, int EPI, bool GATHER_A, int OUT_BOXES = 4>
-__global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS, 1)
+__global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
     rows_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmB2,
@@ -148,6 +171,10 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
+  [[maybe_unused]] uint64_t* afull_bar = tempty_bar + 2;
+  [[maybe_unused]] uint64_t* aempty_bar = afull_bar + 2;
+  constexpr bool AUX_IN = epi_loads_aux(EPI);
+  constexpr int AUX_WARP = 2 + EPI_WARPS + (GATHER_A ? GATHER_WARPS - 1 : 0);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::MISC_OFFSET);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* dtw_part = reinterpret_cast<float*>(smem + L::PART_OFFSET);
@@ -169,6 +196,8 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar + b, 1);
       mbar_init(tempty_bar + b, EPI_WARPS);
+      mbar_init(afull_bar + b, 1);
+      mbar_init(aempty_bar + b, EPI_WARPS);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -182,7 +211,27 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (GATHER_A && (warp == 0 || warp >= 2 + EPI_WARPS)) {
+  if (AUX_IN && warp == AUX_WARP) {
+    // ------------------------------------------------ pre-activation tiles for the epilogue
+    if (elect_one()) {
+      int j = 0;
+      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x, ++j) {
+        const TileCoord tc = decode_tile(p, t, m_tiles, BN);
+        const int b = j & 1;
+        const uint32_t use = uint32_t(j) >> 1;
+        if (use > 0 && !mbar_wait(aempty_bar + b, (use - 1) & 1, p.status)) {
+          *abort_flag = 1;
+          atomicExch(p.status, ST_WAIT_TIMEOUT);
+          break;
+        }
+        uint8_t* dst = smem + L::AUX_OFFSET + b * L::AUX_TILE_BYTES;
+        mbar_expect_tx(afull_bar + b, L::AUX_TILE_BYTES);
+#pragma unroll
+        for (int i = 0; i < 2 * BN / 64; ++i)  // 64-column boxes of [gate | up], rows past the end read 0
+          tma_load_3d(dst + i * OUT_BOX_BYTES, &tmOut, afull_bar + b, 64 * i, tc.m_tile * BM, tc.z);
+      }
+    }
+  } else if (GATHER_A && (warp == 0 || (warp >= 2 + EPI_WARPS && warp != AUX_WARP))) {
     // --------------------------------- producers, gathered A: four warps copy 32 rows each
     // Lane (r4 = lane / 8, c = lane % 8) moves 16-byte chunk c of rows r4, r4 + 4, ... of its
     // warp's 32 rows: eight lanes cover one row's 128-byte k slice, so global reads are whole
@@ -424,17 +473,22 @@ __global__ void __launch_bounds__(GATHER_A ? ROWS_THREADS_GATHER : ROWS_THREADS,
           }
         }
       } else {  // EPI_GLUBWD
-        const __nv_bfloat16* a1 = p.aux + tc.z * p.aux_gstride + grow * (2 * BN);
         __nv_bfloat16* da1 = out_row;  // ld_out == 2 * BN
         __nv_bfloat16* hw = p.out2 + tc.z * p.out2_gstride + grow * BN;
+        // this tile's pre-activations were brought in by the aux warp
+        if (!mbar_wait(afull_bar + b, (uint32_t(j) >> 1) & 1, p.status))
+          atomicExch(p.status, ST_WAIT_TIMEOUT);
+        const uint32_t a1_tile = smem_u32(smem + L::AUX_OFFSET + b * L::AUX_TILE_BYTES);
         float part;
         switch (p.act) {
-          case ACT_SILU: part = epilogue_glubwd<ACT_SILU, BN>(taddr, c_lo, c_hi, row_ok, w, a1, da1, hw); break;
-          case ACT_GELU: part = epilogue_glubwd<ACT_GELU, BN>(taddr, c_lo, c_hi, row_ok, w, a1, da1, hw); break;
-          case ACT_RELU: part = epilogue_glubwd<ACT_RELU, BN>(taddr, c_lo, c_hi, row_ok, w, a1, da1, hw); break;
-          case ACT_SIGMOID: part = epilogue_glubwd<ACT_SIGMOID, BN>(taddr, c_lo, c_hi, row_ok, w, a1, da1, hw); break;
-          default: part = epilogue_glubwd<ACT_TANH, BN>(taddr, c_lo, c_hi, row_ok, w, a1, da1, hw); break;
+          case ACT_SILU: part = epilogue_glubwd<ACT_SILU, BN>(taddr, c_lo, c_hi, row_ok, w, a1_tile, row, da1, hw); break;
+          case ACT_GELU: part = epilogue_glubwd<ACT_GELU, BN>(taddr, c_lo, c_hi, row_ok, w, a1_tile, row, da1, hw); break;
+          case ACT_RELU: part = epilogue_glubwd<ACT_RELU, BN>(taddr, c_lo, c_hi, row_ok, w, a1_tile, row, da1, hw); break;
+          case ACT_SIGMOID: part = epilogue_glubwd<ACT_SIGMOID, BN>(taddr, c_lo, c_hi, row_ok, w, a1_tile, row, da1, hw); break;
+          default: part = epilogue_glubwd<ACT_TANH, BN>(taddr, c_lo, c_hi, row_ok, w, a1_tile, row, da1, hw); break;
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(aempty_bar + b);  // this warp is done with the tile's buffer
         // <G, hidden> of a row is split over the two column halves: fold half 1 into half 0
         // Barrier 1 hands half 1's partials to half 0, barrier 2 hands the buffer back; each half
         // only ever waits for the other one's previous step.
