@@ -451,8 +451,9 @@ def run_ours(args):
     if use_graph:
         # value: one graph per resident input set (the sets are cycled so that no step finds its
         # input in L2); nothing but the graph replay is inside a timed step
-        graph_sets = [capture(False, dev_x[i].clone().requires_grad_(True), dev_dout[i])
-                      for i in range(N_INPUT_SETS)]
+        # (the graphs hold raw pointers: their input tensors must stay alive next to them)
+        value_x = [dev_x[i].clone().requires_grad_(True) for i in range(N_INPUT_SETS)]
+        graph_sets = [capture(False, value_x[i], dev_dout[i]) for i in range(N_INPUT_SETS)]
         per_step_launches = graph_sets[0][2]
 
         def value_step(i):

@@ -14,6 +14,8 @@ stays in a 1-element device tensor that the kernels read.
 """
 from typing import List, Optional, Tuple
 
+import os
+
 import torch
 
 from . import kernels as K
@@ -446,6 +448,8 @@ def moe_block_bwd(
     # tail of one persistent GEMM (SMs that ran out of tiles) is filled by the next one's CTAs.
     main = torch.cuda.current_stream(x.device)
     side_out, side_router = _side_streams(x.device)
+    if os.environ.get("MOE_B200_ONE_STREAM"):      # debugging aid: everything on the caller's stream
+        side_out = side_router = main
     side_out.wait_stream(main)
     side_router.wait_stream(main)
     g_in = K.wgrad(xs, da1, pad_offsets, e_n + s_n, n_extra=s_n)
