@@ -6,11 +6,12 @@ from .moe import AUTO_CAPACITY, MoEBlock
 from .moe_kernel import (ALIGN_M, KERNEL_ACTIVATIONS, KERNEL_DTYPES, fused_moe_forward,
                          kernel_supported, moe_dispatch, moe_experts, router_topk,
                          shapes_supported)
+from .expert_parallel import ep_block_forward, expert_partition
 from .router import TopKRouter
 from .utils import ACTIVATIONS, resolve_activation
 
 __all__ = [
     "MoEBlock", "TopKRouter", "AUTO_CAPACITY", "ALIGN_M", "KERNEL_ACTIVATIONS", "KERNEL_DTYPES",
     "fused_moe_forward", "kernel_supported", "shapes_supported", "moe_dispatch", "moe_experts",
-    "router_topk", "glu_hidden_dim", "make_glu", "ACTIVATIONS", "resolve_activation",
+    "router_topk", "ep_block_forward", "expert_partition", "glu_hidden_dim", "make_glu", "ACTIVATIONS", "resolve_activation",
 ]

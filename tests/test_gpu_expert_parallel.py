@@ -1,0 +1,139 @@
+"""Expert-parallel block on the GPU: G virtual ranks run in lock step on one device (the exchanges
+are tensor shuffles, the per-rank expert compute is the CUDA kernels) and must reproduce the
+single-GPU block on the concatenated tokens, forward and backward. With two or more GPUs the same
+step also runs over NCCL (see the distributed test at the end)."""
+import pytest
+import torch
+
+from conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _block(seed=0, E=76, k=6, S=2, D=576):
+    from nanospeaker_b200 import MoEBlock
+    torch.manual_seed(seed)
+    m = MoEBlock(D, E, d_ff=192, top_k=k, n_shared=S, capacity_factor=None)
+    with torch.no_grad():
+        m.router.W.copy_(torch.randn(D, E) * 0.02)
+        m.W_in.copy_(torch.randn(E, D, 256) * D ** -0.5)
+        m.W_out.copy_(torch.randn(E, 128, D) * 128 ** -0.5)
+        m.W_sh_in.copy_(torch.randn(S, D, 256) * D ** -0.5)
+        m.W_sh_out.copy_(torch.randn(S, 128, D) * 128 ** -0.5)
+    return m.to(torch.bfloat16).cuda().eval()
+
+
+@pytest.mark.parametrize("world,tokens", [(2, 1024), (8, 300), (4, 1)])
+def test_loopback_ranks_match_the_single_gpu_block(world, tokens):
+    from nanospeaker_b200 import expert_parallel as EP
+    m = _block(seed=world)
+    E = m.router.n_experts
+    x_all = torch.randn(world * tokens, 576, device="cuda").bfloat16()
+    gout = torch.randn_like(x_all)
+
+    # one routing decision for both sides (bf16 logits tie easily; the same rows routed in
+    # differently shaped batches could round differently)
+    from nanospeaker_b200 import fused_moe_forward
+    xr = x_all.clone().requires_grad_(True)
+    w_r, idx_r, _ = m.router(xr)
+    ref, _ = fused_moe_forward(xr, m.W_in, m.W_out, w_r, idx_r, None, None, "silu",
+                               w_sh_in=m.W_sh_in, w_sh_out=m.W_sh_out)
+    ref.backward(gout)
+    ref_grads = {n: p.grad.clone() for n, p in m.named_parameters()}
+    for p in m.parameters():
+        p.grad = None
+
+    xe = x_all.clone().requires_grad_(True)
+    w_e, idx_e, _ = m.router(xe)
+    assert torch.equal(idx_e, idx_r)
+    bounds = EP.expert_partition(E, world)
+    gens = []
+    for r in range(world):
+        sl = slice(r * tokens, (r + 1) * tokens)
+        lo, hi = bounds[r]
+        gens.append(EP.ep_forward_steps(xe[sl], w_e[sl], idx_e[sl], m.W_in[lo:hi], m.W_out[lo:hi],
+                                        m.W_sh_in, m.W_sh_out, r, bounds, "silu"))
+    out = torch.cat(EP.run_loopback(gens))
+    assert rel_l2(out.detach(), ref.detach().float()) < TOL
+    out.backward(gout)
+    assert rel_l2(xe.grad, xr.grad.float()) < TOL
+    for n, p in m.named_parameters():
+        assert p.grad is not None, n
+        assert rel_l2(p.grad, ref_grads[n].float()) < (2e-2 if n == "router.W" else TOL), n
+    from nanospeaker_b200 import kernels
+    kernels.check_status("cuda")
+
+
+def _nccl_worker(rank, world, port, tokens, q):
+    try:
+        import os
+        import torch.distributed as dist
+        from nanospeaker_b200 import expert_parallel as EP
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", rank))
+        m = _block(seed=5)
+        E = m.router.n_experts
+        g = torch.Generator().manual_seed(11)
+        x_all = torch.randn(world * tokens, 576, generator=g).bfloat16()
+        gout_all = torch.randn(world * tokens, 576, generator=g).bfloat16()
+        sl = slice(rank * tokens, (rank + 1) * tokens)
+        lo, hi = EP.expert_partition(E, world)[rank]
+        x = x_all[sl].cuda().requires_grad_(True)
+        w_in = m.W_in.detach()[lo:hi].clone().requires_grad_(True)
+        w_out = m.W_out.detach()[lo:hi].clone().requires_grad_(True)
+        out, _ = EP.ep_block_forward(x, m.router, w_in, w_out, m.W_sh_in, m.W_sh_out, "silu")
+        out.backward(gout_all[sl].cuda())
+        EP.all_reduce_replicated_grads([m.router.W, m.W_sh_in, m.W_sh_out])
+        torch.cuda.synchronize()
+        q.put((rank, out.detach().float().cpu().numpy(), x.grad.float().cpu().numpy(),
+               w_in.grad.float().cpu().numpy(), m.W_sh_in.grad.float().cpu().numpy()))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as exc:  # surface the failure instead of hanging the parent
+        q.put((rank, repr(exc)))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpus_over_nccl_match_the_single_gpu_block():
+    import socket
+    import torch.multiprocessing as mp
+    from nanospeaker_b200 import expert_parallel as EP
+    world, tokens = 2, 2048
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_nccl_worker, args=(r, world, port, tokens, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(world):
+        item = q.get(timeout=300)
+        assert len(item) == 5, item
+        got[item[0]] = item[1:]
+    for p in procs:
+        p.join(timeout=60)
+    m = _block(seed=5)
+    g = torch.Generator().manual_seed(11)
+    x_all = torch.randn(world * tokens, 576, generator=g).bfloat16()
+    gout_all = torch.randn(world * tokens, 576, generator=g).bfloat16()
+    from nanospeaker_b200 import fused_moe_forward
+    xr = x_all.cuda().requires_grad_(True)
+    routed = [m.router(xr[r * tokens:(r + 1) * tokens]) for r in range(world)]   # as the ranks do
+    ref, _ = fused_moe_forward(xr, m.W_in, m.W_out, torch.cat([w for w, _, _ in routed]),
+                               torch.cat([i for _, i, _ in routed]), None, None, "silu",
+                               w_sh_in=m.W_sh_in, w_sh_out=m.W_sh_out)
+    ref.backward(gout_all.cuda())
+    bounds = EP.expert_partition(m.router.n_experts, world)
+    for r in range(world):
+        out, dx, dw_in, dw_sh = (torch.from_numpy(a) for a in got[r])
+        sl = slice(r * tokens, (r + 1) * tokens)
+        lo, hi = bounds[r]
+        assert rel_l2(out, ref.detach().float().cpu()[sl]) < TOL
+        assert rel_l2(dx, xr.grad.float().cpu()[sl]) < TOL
+        assert rel_l2(dw_in, m.W_in.grad.float().cpu()[lo:hi]) < TOL
+        assert rel_l2(dw_sh, m.W_sh_in.grad.float().cpu()) < TOL
