@@ -251,9 +251,11 @@ def build_stages(m, x):
             # name, bound, work per launch (bytes or flop), launches per step, callable(i)
             ("router GEMM x@W (padded to %d cols)" % ld, TF, 2.0 * T * D * E, 1,
              lambda i: K.down_gemm(xr[i % 3], wp, None, None, 1, None, None, 0)),
-            ("router_fused (top-k, softmax, colsum)", GE, T * ld * 2 + T * ka * 10, 1,
+            ("router top-k + dispatch (2 kernels)", GE, T * ld * 2 + T * ka * 10 + M * 8 + M * 4 * 3, 1,
+             lambda i: K.router_dispatch(logits_p, bias, E, k, S, True, True)),
+            ("router_fused alone (top-k, softmax, colsum)", GE, T * ld * 2 + T * ka * 10, 0,
              lambda i: K.router_fused(logits_p, bias, E, k, S, True, True)),
-            ("dispatch(3 kernels)", GE, M * 8 * 2 + M * 4 * 3, 1,
+            ("dispatch alone (histogram, plan + scatter)", GE, M * 8 * 2 + M * 4 * 3, 0,
              lambda i: K.dispatch(idx_all, Ea)),
             # compulsory traffic: x read once (its k + S re-reads hit L2), every slot row written
             ("permute", GE, T * D * 2 + M * D * 2 + M * 4, 2,

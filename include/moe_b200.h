@@ -123,6 +123,23 @@ int moe_b200_dispatch(const int64_t* topk_idx, int64_t n_pairs, int32_t n_expert
                       int32_t* counts, int32_t* n_post_pad, int32_t* inv_ids, void* scratch,
                       size_t scratch_bytes, int32_t* status, void* stream);
 
+/* Router top-k and dispatch in two launches for the whole-block path: the router kernel
+ * (moe_b200_router_fused's arithmetic and outputs) runs with one block per chunk of 128+ tokens and
+ * leaves that chunk's histogram of expert ids, so the dispatch's histogram pass is not needed; the
+ * plan + scatter kernel follows over idx_all [n_tokens, top_k + n_shared] with n_experts + n_shared
+ * experts (outputs as moe_b200_dispatch; l_cap = moe_b200_l_cap(n_tokens * (top_k + n_shared),
+ * n_experts + n_shared)). scratch: moe_b200_router_dispatch_scratch_bytes(n_tokens,
+ * n_experts + n_shared) bytes. Replaces TopKRouter.forward's selection (src/model/router.py:79-97)
+ * followed by moe_dispatch (src/model/moe_kernel.py:180-218). */
+size_t moe_b200_router_dispatch_scratch_bytes(int64_t n_tokens, int32_t n_experts_total);
+int moe_b200_router_dispatch(const void* logits, int32_t ld, const float* bias, int64_t n_tokens,
+                             int32_t n_experts, int32_t top_k, int32_t n_shared,
+                             int32_t normalize, int32_t full_softmax, void* w_all,
+                             int64_t* idx_all, float* colsum, int32_t* sorted_ids,
+                             int32_t* expert_ids, int32_t* pad_offsets, int32_t* counts,
+                             int32_t* n_post_pad, int32_t* inv_ids, void* scratch,
+                             size_t scratch_bytes, int32_t* status, void* stream);
+
 /* moe_b200_dispatch for callers that cannot supply scratch memory. (No counterpart in the
  * reference: its dispatch allocates through torch.) Meant for hosts that may not allocate device
  * memory at call time -- a process whose memory plan was frozen at start-up, or a foreign-function

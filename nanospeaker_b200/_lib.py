@@ -39,6 +39,11 @@ SIGNATURES = {
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_sz, _c_vp,
          _c_vp]),
     "moe_b200_dispatch_static_max_pairs": (_c_i64, [_c_i32]),
+    "moe_b200_router_dispatch_scratch_bytes": (_c_sz, [_c_i64, _c_i32]),
+    "moe_b200_router_dispatch": (
+        ctypes.c_int,
+        [_c_vp, _c_i32, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp,
+         _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_sz, _c_vp, _c_vp]),
     "moe_b200_dispatch_static": (
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp]),

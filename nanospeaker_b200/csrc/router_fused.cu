@@ -19,17 +19,29 @@ constexpr int RF_WARPS = 8;
 // Warps stride over tokens. Per token: winners by (value desc, index asc); weights as in
 // router_topk_kernel. colsum[e] += sum_t softmax(l_t)[e] (only when full_softmax and colsum given):
 // lane-local partial sums, one shared-memory reduction per block, one atomic per block and expert.
-template <int NSLOT>
-__global__ void __launch_bounds__(RF_WARPS * 32)
+// With tokens_per_block > 0 the kernel also does the first pass of the dispatch: block b owns tokens
+// [b * tokens_per_block, ...) -- one chunk of the counting sort -- and leaves the chunk's histogram
+// of expert ids (shared experts included) in block_hist[expert][block] and its share of the sentinel
+// fill of sorted_ids, so that dispatch_scatter_kernel can follow directly.
+template <int NSLOT, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
     router_fused_kernel(const __nv_bfloat16* __restrict__ logits, int ld,
                         const float* __restrict__ bias, int64_t n_tokens, int n_experts, int top_k,
                         int n_shared, int normalize, int full_softmax,
                         __nv_bfloat16* __restrict__ w_all, int64_t* __restrict__ idx_all,
-                        float* __restrict__ colsum) {
+                        float* __restrict__ colsum, int tokens_per_block,
+                        int32_t* __restrict__ block_hist, int32_t* __restrict__ sorted_ids,
+                        int64_t l_cap) {
   pdl_trigger();
   pdl_wait();
-  __shared__ float cs[RF_WARPS][NSLOT * 32];
+  __shared__ float cs[WARPS][NSLOT * 32];
+  __shared__ int32_t hist[MAX_EXPERTS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool chunked = tokens_per_block > 0;
+  if (chunked) {
+    for (int e = threadIdx.x; e < n_experts + n_shared; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+  }
   const int kS = top_k + n_shared;
   const bool need_full = full_softmax || !normalize;
   const bool want_colsum = full_softmax && colsum != nullptr;
@@ -42,8 +54,11 @@ __global__ void __launch_bounds__(RF_WARPS * 32)
     csum[i] = 0.f;
   }
 
-  for (int64_t t = int64_t(blockIdx.x) * RF_WARPS + warp; t < n_tokens;
-       t += int64_t(gridDim.x) * RF_WARPS) {
+  const int64_t t_first = chunked ? int64_t(blockIdx.x) * tokens_per_block + warp
+                                  : int64_t(blockIdx.x) * WARPS + warp;
+  const int64_t t_stride = chunked ? WARPS : int64_t(gridDim.x) * WARPS;
+  const int64_t t_hi = chunked ? min(int64_t(blockIdx.x + 1) * tokens_per_block, n_tokens) : n_tokens;
+  for (int64_t t = t_first; t < t_hi; t += t_stride) {
     const __nv_bfloat16* row = logits + t * ld;
     float v[NSLOT];
     uint32_t key[NSLOT];  // 0 = not a candidate (out of range or already taken)
@@ -124,6 +139,7 @@ __global__ void __launch_bounds__(RF_WARPS * 32)
     if (active) {
       w_all[t * kS + lane] = __float2bfloat16(wgt);
       idx_all[t * kS + lane] = sel_idx;
+      if (chunked) atomicAdd(&hist[sel_idx], 1);
     } else if (lane < kS) {  // the shared experts: every token, weight 1
       w_all[t * kS + lane] = __float2bfloat16(1.f);
       idx_all[t * kS + lane] = n_experts + (lane - top_k);
@@ -137,9 +153,22 @@ __global__ void __launch_bounds__(RF_WARPS * 32)
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
       float s = 0.f;
 #pragma unroll
-      for (int w = 0; w < RF_WARPS; ++w) s += cs[w][e];
+      for (int w = 0; w < WARPS; ++w) s += cs[w][e];
       atomicAdd(colsum + e, s);
     }
+  }
+  if (chunked) {
+    __syncthreads();
+    const int64_t t_lo = int64_t(blockIdx.x) * tokens_per_block;
+    const int32_t mine = int32_t(t_hi > t_lo ? t_hi - t_lo : 0);  // every token visits every shared expert
+    for (int e = threadIdx.x; e < n_experts + n_shared; e += blockDim.x)
+      block_hist[int64_t(e) * gridDim.x + blockIdx.x] = e < n_experts ? hist[e] : mine;
+    // sentinel fill: each block paints an equal slice of [0, l_cap)
+    const int64_t n_pairs = n_tokens * kS;
+    const int64_t per = (l_cap + gridDim.x - 1) / gridDim.x;
+    const int64_t lo = per * blockIdx.x;
+    const int64_t hi = lo + per < l_cap ? lo + per : l_cap;
+    for (int64_t sl = lo + threadIdx.x; sl < hi; sl += blockDim.x) sorted_ids[sl] = int32_t(n_pairs);
   }
 }
 
@@ -314,6 +343,29 @@ static unsigned rf_grid(int64_t n_tokens, int blocks_per_sm = 16) {
   return unsigned(want < cap ? (want > 0 ? want : 1) : cap);
 }
 
+// 32 warps per block in chunked mode: a block owns 128+ consecutive tokens, a warp takes every 32nd.
+constexpr int RF_CHUNK_WARPS = 32;
+
+int launch_router_fused_chunked(const __nv_bfloat16* logits, int ld, const float* bias,
+                                int64_t n_tokens, int n_experts, int top_k, int n_shared,
+                                int normalize, int full_softmax, __nv_bfloat16* w_all,
+                                int64_t* idx_all, float* colsum, int tokens_per_block, int n_blocks,
+                                int32_t* block_hist, int32_t* sorted_ids, int64_t l_cap,
+                                cudaStream_t st) {
+#define LAUNCH(NS)                                                                              \
+  launch_pdl(router_fused_kernel<NS, RF_CHUNK_WARPS>, dim3(n_blocks), dim3(RF_CHUNK_WARPS * 32), 0, \
+             st, logits, ld, bias, n_tokens, n_experts, top_k, n_shared, normalize, full_softmax,   \
+             w_all, idx_all, colsum, tokens_per_block, block_hist, sorted_ids, l_cap)
+  const int nslot = (n_experts + 31) / 32;
+  if (nslot <= 1) LAUNCH(1);
+  else if (nslot <= 2) LAUNCH(2);
+  else if (nslot <= 3) LAUNCH(3);
+  else if (nslot <= 4) LAUNCH(4);
+  else LAUNCH(8);
+#undef LAUNCH
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
 }  // namespace moe
 
 using namespace moe;
@@ -335,10 +387,10 @@ int moe_b200_router_fused(const void* logits, int32_t ld, const float* bias, int
   const unsigned grid = rf_grid(n_tokens, (full_softmax && colsum) ? 4 : 16);
   const __nv_bfloat16* lg = static_cast<const __nv_bfloat16*>(logits);
   __nv_bfloat16* w = static_cast<__nv_bfloat16*>(w_all);
-#define LAUNCH(NS)                                                                              \
-  launch_pdl(router_fused_kernel<NS>, dim3(grid), dim3(RF_WARPS * 32), 0, st, lg, ld, bias, n_tokens, n_experts, top_k, \
-                                                          n_shared, normalize, full_softmax, w,    \
-                                                          idx_all, colsum)
+#define LAUNCH(NS)                                                                          \
+  launch_pdl(router_fused_kernel<NS, RF_WARPS>, dim3(grid), dim3(RF_WARPS * 32), 0, st, lg, ld,    \
+             bias, n_tokens, n_experts, top_k, n_shared, normalize, full_softmax, w, idx_all,      \
+             colsum, 0, static_cast<int32_t*>(nullptr), static_cast<int32_t*>(nullptr), int64_t(0))
   const int nslot = (n_experts + 31) / 32;
   if (nslot <= 1) LAUNCH(1);
   else if (nslot <= 2) LAUNCH(2);

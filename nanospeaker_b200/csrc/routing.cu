@@ -389,11 +389,12 @@ __global__ void __launch_bounds__(DISPATCH_THREADS)
   }
   if (n_blocks == 0) return;
 
-  const int slice = chunk / DISPATCH_WARPS;  // a multiple of 32
+  const int slice = chunk / DISPATCH_WARPS;  // chunk is a multiple of the warp count
   const int64_t wbase = int64_t(blockIdx.x) * chunk + int64_t(warp) * slice;
+  const int64_t wend = wbase + slice;          // a slice need not be a multiple of 32
   auto expert_of = [&](int64_t pidx) {
     int32_t e = -1;
-    if (pidx < n_pairs) {
+    if (pidx < n_pairs && pidx < wend) {
       const int64_t ee = topk_idx[pidx];
       e = (ee >= 0 && ee < n_experts) ? int32_t(ee) : -1;
     }
@@ -528,6 +529,63 @@ int moe_b200_dispatch(const int64_t* topk_idx, int64_t n_pairs, int32_t n_expert
   return launch_dispatch(topk_idx, n_pairs, n_experts, sorted_ids, expert_ids, pad_offsets, counts,
                          n_post_pad, inv_ids, static_cast<int32_t*>(scratch), status,
                          static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
+
+namespace moe {
+// Tokens per block of the fused router + dispatch: a multiple of 128, at most DISPATCH_MAX_BLOCKS
+// blocks.
+static int64_t router_tokens_per_block(int64_t n_tokens) {
+  int64_t tpb = 128;
+  while ((n_tokens + tpb - 1) / tpb > DISPATCH_MAX_BLOCKS) tpb *= 2;
+  return tpb;
+}
+}  // namespace moe
+
+extern "C" {
+
+size_t moe_b200_router_dispatch_scratch_bytes(int64_t n_tokens, int32_t n_experts_total) {
+  if (n_tokens < 0) n_tokens = 0;
+  const int64_t tpb = router_tokens_per_block(n_tokens);
+  const int64_t blocks = (n_tokens + tpb - 1) / tpb;
+  return size_t(blocks > 0 ? blocks : 1) * size_t(n_experts_total) * sizeof(int32_t);
+}
+
+int moe_b200_router_dispatch(const void* logits, int32_t ld, const float* bias, int64_t n_tokens,
+                             int32_t n_experts, int32_t top_k, int32_t n_shared,
+                             int32_t normalize, int32_t full_softmax, void* w_all,
+                             int64_t* idx_all, float* colsum, int32_t* sorted_ids,
+                             int32_t* expert_ids, int32_t* pad_offsets, int32_t* counts,
+                             int32_t* n_post_pad, int32_t* inv_ids, void* scratch,
+                             size_t scratch_bytes, int32_t* status, void* stream) {
+  const int32_t n_all = n_experts + n_shared;
+  if (n_experts < 1 || n_all > MAX_EXPERTS || top_k < 1 || top_k > n_experts || n_shared < 0 ||
+      top_k + n_shared > 32 || top_k > MAX_TOPK || n_tokens < 1 || ld < n_experts ||
+      n_tokens * (top_k + n_shared) > (int64_t(1) << 30))
+    return MOE_B200_ERR_SHAPE;
+  if (!logits || !w_all || !idx_all || !sorted_ids || !pad_offsets || !counts || !n_post_pad ||
+      !inv_ids || !status)
+    return MOE_B200_ERR_NULL;
+  if (!scratch || scratch_bytes < moe_b200_router_dispatch_scratch_bytes(n_tokens, n_all))
+    return MOE_B200_ERR_SCRATCH;
+  const int kS = top_k + n_shared;
+  const int64_t n_pairs = n_tokens * kS;
+  const int64_t l_cap = moe_b200_l_cap(n_pairs, n_all);
+  const int tpb = int(router_tokens_per_block(n_tokens));
+  const int blocks = int((n_tokens + tpb - 1) / tpb);
+  int32_t* block_hist = static_cast<int32_t*>(scratch);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int rc = launch_router_fused_chunked(
+      static_cast<const __nv_bfloat16*>(logits), ld, bias, n_tokens, n_experts, top_k, n_shared,
+      normalize, full_softmax, static_cast<__nv_bfloat16*>(w_all), idx_all, colsum, tpb, blocks,
+      block_hist, sorted_ids, l_cap, st);
+  if (rc != MOE_B200_OK) return rc;
+  launch_pdl(dispatch_scatter_kernel, dim3(blocks), dim3(DISPATCH_THREADS), 0, st,
+             static_cast<const int64_t*>(idx_all), n_pairs, int(n_all), tpb * kS, blocks,
+             static_cast<const int32_t*>(block_hist), counts, pad_offsets, n_post_pad, expert_ids,
+             l_cap / ALIGN_M, sorted_ids, inv_ids);
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
 }  // extern "C"

@@ -17,5 +17,18 @@ __device__ __forceinline__ uint32_t float_key(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+}  // namespace moe
 
+#include <cuda_bf16.h>
+
+namespace moe {
+// router_fused.cu: router top-k in chunked mode (block b owns tokens [b * tokens_per_block, ...))
+// that also leaves the dispatch's per-block histograms and the sentinel fill. Returns an error code
+// of include/moe_b200.h.
+int launch_router_fused_chunked(const __nv_bfloat16* logits, int ld, const float* bias,
+                                int64_t n_tokens, int n_experts, int top_k, int n_shared,
+                                int normalize, int full_softmax, __nv_bfloat16* w_all,
+                                int64_t* idx_all, float* colsum, int tokens_per_block, int n_blocks,
+                                int32_t* block_hist, int32_t* sorted_ids, int64_t l_cap,
+                                cudaStream_t st);
 }  // namespace moe

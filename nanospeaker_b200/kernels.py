@@ -116,6 +116,39 @@ def router_fused(logits, bias, n_experts: int, top_k: int, n_shared: int, normal
     return w_all, idx_all, colsum
 
 
+def router_dispatch(logits, bias, n_experts: int, top_k: int, n_shared: int, normalize: bool,
+                    full_softmax: bool):
+    """router_fused + dispatch in two launches (the router kernel leaves the dispatch's per-block
+    histograms): -> (w_all, idx_all, colsum | None, sorted_ids, expert_ids, pad_offsets, counts,
+    n_post_pad, inv_ids) with counts / pad_offsets over the n_experts + n_shared experts."""
+    _need_cuda(logits)
+    t, ld = logits.shape
+    ks, n_all = top_k + n_shared, n_experts + n_shared
+    dev, i32 = logits.device, torch.int32
+    lib = _lib.load()
+    m = t * ks
+    cap = l_cap(m, n_all)
+    w_all = torch.empty((t, ks), dtype=logits.dtype, device=dev)
+    idx_all = torch.empty((t, ks), dtype=torch.int64, device=dev)
+    colsum = torch.zeros(n_experts, dtype=torch.float32, device=dev) if full_softmax else None
+    sids = torch.empty(cap, dtype=i32, device=dev)
+    eids = torch.empty(cap // ALIGN_M, dtype=i32, device=dev)
+    offs = torch.empty(n_all + 1, dtype=i32, device=dev)
+    counts = torch.empty(n_all, dtype=i32, device=dev)
+    npp = torch.empty(1, dtype=i32, device=dev)
+    inv = torch.empty(m, dtype=i32, device=dev)
+    nbytes = lib.moe_b200_router_dispatch_scratch_bytes(t, n_all)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    _lib.check(lib.moe_b200_router_dispatch(
+        logits.data_ptr(), ld, _lib.ptr(bias), t, n_experts, top_k, n_shared, int(normalize),
+        int(full_softmax), w_all.data_ptr(), idx_all.data_ptr(), _lib.ptr(colsum), sids.data_ptr(),
+        eids.data_ptr(), offs.data_ptr(), counts.data_ptr(), npp.data_ptr(), inv.data_ptr(),
+        scratch.data_ptr(), nbytes, status_word(dev).data_ptr(), _stream(logits)),
+        "moe_b200_router_dispatch")
+    _count(2)
+    return w_all, idx_all, colsum, sids, eids, offs, counts, npp, inv
+
+
 def router_fused_bwd(logits, bias, idx_all, dw_all, n_experts: int, top_k: int, n_shared: int,
                      normalize: bool, full_softmax: bool, d_aux, counts, aux_coef: float,
                      ld_out: int) -> torch.Tensor:

@@ -364,9 +364,8 @@ def moe_block(
 
     wp = K.copy_cols(router_w, ld).unsqueeze(0)   # [1, D, ld], zero pad columns
     logits = K.down_gemm(x, wp, None, None, 1, None, None, 0)[0]
-    w_all, idx_all, colsum = K.router_fused(logits, logit_bias, e_n, top_k, s_n, normalize,
-                                            full_softmax)
-    sids, eids, offs, counts_all, npp, inv = K.dispatch(idx_all, e_n + s_n)
+    w_all, idx_all, colsum, sids, eids, offs, counts_all, npp, inv = K.router_dispatch(
+        logits, logit_bias, e_n, top_k, s_n, normalize, full_softmax)
     tw = w_all.reshape(-1)
     m = n * ks
     if save_for_backward:

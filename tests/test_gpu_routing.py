@@ -159,3 +159,28 @@ def test_router_fused_matches_router_topk_on_the_same_logits(T, E, k, S, full, n
         assert torch.all(dl[:, E:] == 0)
         assert rel_l2(dl[:, :E].float(), ref_dl) < 1e-2
     K.check_status("cuda")
+
+
+@pytest.mark.parametrize("T,E,k,S", [(16384, 76, 6, 2), (1000, 76, 6, 1), (129, 8, 2, 0),
+                                     (1, 200, 8, 2), (40000, 16, 3, 2)])
+def test_router_dispatch_equals_router_fused_then_dispatch(T, E, k, S):
+    """The two-launch router + dispatch of the whole-block path against the separate entry points:
+    every output bit for bit."""
+    from nanospeaker_b200 import kernels as K
+    torch.manual_seed(T + E)
+    ld = (E + 63) // 64 * 64
+    logits = torch.zeros(T, ld, device="cuda", dtype=torch.bfloat16)
+    logits[:, :E] = torch.randn(T, E, device="cuda").bfloat16()
+    bias = torch.randn(E, device="cuda") * 0.3
+    w_all, idx_all, colsum = K.router_fused(logits, bias, E, k, S, True, True)
+    ref = K.dispatch(idx_all, E + S)
+    got = K.router_dispatch(logits, bias, E, k, S, True, True)
+    assert torch.equal(got[0], w_all) and torch.equal(got[1], idx_all)
+    assert torch.allclose(got[2], colsum, rtol=1e-5, atol=1e-4)       # atomics: order may differ
+    live = int(ref[4])
+    assert int(got[7]) == live
+    assert torch.equal(got[3][:live], ref[0][:live])                  # sorted_ids
+    assert torch.equal(got[4][: live // 128], ref[1][: live // 128])  # expert_ids
+    for a, b in ((5, 2), (6, 3), (8, 5)):                             # pad_offsets, counts, inv_ids
+        assert torch.equal(got[a], ref[b])
+    K.check_status("cuda")
