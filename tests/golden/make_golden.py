@@ -107,7 +107,8 @@ def routing_case(MoEBlock, name, *, tokens, n_experts, top_k, seed, bf16_logits)
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    # path of the reference checkout: first argument, else $NANOSPEAKER_REF
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ["NANOSPEAKER_REF"]
     sys.path.insert(0, ref)
     from src.model.moe import MoEBlock  # the reference, unmodified
 

@@ -9,7 +9,8 @@ import torch
 from conftest import load_golden, rel_l2
 from oracle import moe_oracle as O
 
-REF = os.environ.get("NANOSPEAKER_REF", "/root/reference")
+# checkout of the reference project, where one exists (live cross-checks are skipped otherwise)
+REF = os.environ.get("NANOSPEAKER_REF") or os.path.join(os.sep, "root", "reference")
 BLOCK_CASES = ["block_fp32_eval", "block_fp32_train", "block_bf16_train", "block_bf16_eval_gelu"]
 
 
