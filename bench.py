@@ -572,6 +572,79 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_side_workload(args):
+    """The two forward-only workloads of the block's other callers, one JSON line each (not the
+    headline): `decode` = 20 stacked blocks on T=64 tokens replayed from one CUDA graph
+    (BASELINE config 3), `prefill` = one block on T=131072 tokens (BASELINE config 4, one GPU's
+    view). Single GPU."""
+    from nanospeaker_b200 import MoEBlock, kernels as K
+    from nanospeaker_b200.decode import StackedMoEDecoder
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the MoE block has no CPU implementation")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    def make_block(seed):
+        g = torch.Generator().manual_seed(seed)
+        r = lambda *sh: torch.randn(*sh, generator=g)
+        m = MoEBlock(D_MODEL, N_EXPERTS, d_ff=D_FF, top_k=TOP_K, n_shared=N_SHARED,
+                     capacity_factor=None).to(torch.bfloat16)
+        with torch.no_grad():
+            m.router.W.copy_(r(D_MODEL, N_EXPERTS) * 0.02)
+            m.W_in.copy_(r(N_EXPERTS, D_MODEL, 2 * D_HIDDEN) * D_MODEL ** -0.5)
+            m.W_out.copy_(r(N_EXPERTS, D_HIDDEN, D_MODEL) * D_HIDDEN ** -0.5)
+            m.W_sh_in.copy_(r(N_SHARED, D_MODEL, 2 * D_HIDDEN) * D_MODEL ** -0.5)
+            m.W_sh_out.copy_(r(N_SHARED, D_HIDDEN, D_MODEL) * D_HIDDEN ** -0.5)
+        return m.to(dev).eval()
+
+    def time_loop(fn):
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    g = torch.Generator().manual_seed(100)
+    if args.workload == "decode":
+        layers, T = 20, 64
+        stack = StackedMoEDecoder([make_block(1000 + i) for i in range(layers)])
+        xs = [torch.randn(T, D_MODEL, generator=g).bfloat16().to(dev) for _ in range(8)]
+        l0 = K.LAUNCHES
+        stack.eager(xs[0])
+        launches = K.LAUNCHES - l0
+        eager_ms = time_loop(lambda i: stack.eager(xs[i % 8]))
+        ms = time_loop(lambda i: stack.step(xs[i % 8]))
+        line = {"metric": "MoE decode stack latency (20 blocks, forward)", "value": ms,
+                "unit": "ms", "higher_is_better": False, "tokens_per_s": T / (ms / 1e3),
+                "eager_ms": eager_ms, "gpu_launches_per_step": launches,
+                "config": {"workload": "BASELINE config 3: 20 stacked MoE blocks (independent "
+                                       "weights), T=64 tokens, bf16, forward, one CUDA graph"}}
+    else:
+        T = 131072
+        m = make_block(7)
+        xs = [torch.randn(T, D_MODEL, generator=g).bfloat16().to(dev) for _ in range(4)]
+        with torch.no_grad():
+            l0 = K.LAUNCHES
+            m(xs[0])
+            launches = K.LAUNCHES - l0
+            ms = time_loop(lambda i: m(xs[i % 4]))
+        line = {"metric": "MoE-block tokens/s (forward, prefill)", "value": T / (ms / 1e3),
+                "unit": "tokens/s", "higher_is_better": True, "ms_per_step": ms,
+                "gpu_launches_per_step": launches,
+                "config": {"workload": "BASELINE config 4 (one GPU's view): one MoE block forward, "
+                                       "T=131072 tokens, bf16, eager launches"}}
+    K.check_status(dev)
+    line.update({"n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16",
+                 "data": "synthetic"})
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -586,8 +659,13 @@ def main():
                     help="time eager module calls instead of a captured CUDA graph of the step")
     ap.add_argument("--profile-stage", default="",
                     help="run only the stage whose name contains this text, 3 launches (for ncu)")
+    ap.add_argument("--workload", default="train", choices=["train", "decode", "prefill"],
+                    help="train = the headline (forward + backward, T=16384); decode / prefill = "
+                         "the forward-only workloads of the block's other callers")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload != "train":
+        run_side_workload(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -1,0 +1,64 @@
+"""Decode-shaped use of the MoE block: a stack of blocks on a small, fixed batch of tokens (one
+token per sequence), forward only, replayed from one CUDA graph.
+
+At T = 64 every expert sees a handful of rows and each block's ten launches take a few
+microseconds: the cost is launch latency, not arithmetic, so the whole stack is captured once and
+replayed. The caller loop this stands for is `generate` -> `Block.forward` -> `MoEBlock.forward`
+with T = batch size in eval mode (src/model/nanospeaker.py:254-269, 165-169); attention, norms and
+the KV cache of that loop are outside this package, so the stack here chains the blocks through
+the residual only: x <- x + block_l(x).
+"""
+from typing import List, Sequence
+
+import torch
+
+from .moe import MoEBlock
+
+
+class StackedMoEDecoder:
+    """`x + block(x)` over a list of MoE blocks (eval mode, CUDA, bf16), graph-replayed per batch
+    size.
+
+    step(x) runs the stack on x [T, d_model] and returns the result (a tensor owned by the runner:
+    it is overwritten by the next step with the same T). The first call for a given T captures the
+    graph; later calls copy x into the graph's input and replay."""
+
+    def __init__(self, blocks: Sequence[MoEBlock]):
+        self.blocks: List[MoEBlock] = list(blocks)
+        if not self.blocks:
+            raise ValueError("need at least one block")
+        for b in self.blocks:
+            b.eval()
+        self._graphs = {}
+
+    @torch.no_grad()
+    def eager(self, x: torch.Tensor) -> torch.Tensor:
+        for b in self.blocks:
+            x = x + b(x)
+        return x
+
+    @torch.no_grad()
+    def _capture(self, x: torch.Tensor):
+        static_x = x.clone()
+        side = torch.cuda.Stream(device=x.device)
+        side.wait_stream(torch.cuda.current_stream(x.device))
+        with torch.cuda.stream(side):           # warm-up outside the capture (lazy initialisations)
+            for _ in range(2):
+                self.eager(static_x)
+        torch.cuda.current_stream(x.device).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = self.eager(static_x)
+        return graph, static_x, out
+
+    @torch.no_grad()
+    def step(self, x: torch.Tensor) -> torch.Tensor:
+        if not x.is_cuda:
+            raise RuntimeError("StackedMoEDecoder runs on CUDA tensors only")
+        key = (tuple(x.shape), x.dtype, x.device)
+        if key not in self._graphs:
+            self._graphs[key] = self._capture(x)
+        graph, static_x, out = self._graphs[key]
+        static_x.copy_(x)
+        graph.replay()
+        return out

@@ -348,3 +348,19 @@ def test_config4_prefill_forward_T131072_token_slices():
     from nanospeaker_b200 import kernels
     kernels.check_status("cuda")
     assert torch.isfinite(out.float()).all()
+
+
+def test_stacked_decoder_graph_replay_equals_eager_stack():
+    """The graph-replayed stack of blocks (decode-shaped batch) gives the eager stack's bits, for
+    several inputs through the same captured graph."""
+    from nanospeaker_b200.decode import StackedMoEDecoder
+    blocks = [_model_shape_pair(64, train=False, seed=200 + i)[1] for i in range(4)]
+    stack = StackedMoEDecoder(blocks)
+    for seed in (1, 2, 3):
+        torch.manual_seed(seed)
+        x = torch.randn(64, 576, device="cuda").bfloat16()
+        want = stack.eager(x)
+        got = stack.step(x)
+        assert torch.equal(got, want)
+    from nanospeaker_b200 import kernels
+    kernels.check_status("cuda")
