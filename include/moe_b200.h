@@ -183,6 +183,22 @@ int moe_b200_combine(const void* y, const int32_t* inv_ids, int64_t n_tokens, in
 int moe_b200_copy_cols(const void* src, int64_t rows, int32_t cols, int32_t src_ld, void* dst,
                        int32_t dst_ld, void* stream);
 
+/* RMSNorm in front of the block: h[t] = x[t] * rstd[t] * gamma, rstd[t] = rsqrt(mean(x[t]^2) + eps)
+ * (x, gamma, h bf16; rstd fp32 [n_rows], kept for the backward). d_model % 8 == 0, <= 2048.
+ * Replaces RMSNorm.forward (src/model/ln.py:31-38) as used by Block.forward's
+ * `x + self.ffn(self.norm_ffn(x))` (src/model/nanospeaker.py:165-169). */
+int moe_b200_rmsnorm(const void* x, const void* gamma, int64_t n_rows, int32_t d_model, float eps,
+                     void* h, float* rstd, void* stream);
+
+/* Its backward, with the residual branch's gradient folded in:
+ *   dx[t] = rstd * (gamma * dh[t]) - x[t] * rstd^3 / d_model * <gamma * dh[t], x[t]>  (+ add[t])
+ *   dgamma += sum_t dh[t] * x[t] * rstd[t]        (fp32 [d_model], accumulated: zero it first)
+ * add may be NULL. Replaces autograd through F.rms_norm (src/model/ln.py:33) and the residual's
+ * gradient add. */
+int moe_b200_rmsnorm_bwd(const void* dh, const void* x, const float* rstd, const void* gamma,
+                         const void* add, int64_t n_rows, int32_t d_model, void* dx,
+                         float* dgamma, void* stream);
+
 /* Schedule arguments shared by the row-grouped GEMMs below:
  *   rows            rows of the slot-ordered A buffer (l_cap), or the token count when
  *                   n_fixed_groups > 0

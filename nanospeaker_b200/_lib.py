@@ -51,6 +51,10 @@ SIGNATURES = {
         ctypes.c_int, [_c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp, _c_i64, _c_vp, _c_vp]),
     "moe_b200_combine": (
         ctypes.c_int, [_c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp]),
+    "moe_b200_rmsnorm": (
+        ctypes.c_int, [_c_vp, _c_vp, _c_i64, _c_i32, ctypes.c_float, _c_vp, _c_vp, _c_vp]),
+    "moe_b200_rmsnorm_bwd": (
+        ctypes.c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp]),
     "moe_b200_copy_cols": (
         ctypes.c_int, [_c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_i32, _c_vp]),
     "moe_b200_up_gemm": (

@@ -237,6 +237,33 @@ def _extra(w_extra):
     return (0, 0) if w_extra is None else (w_extra.data_ptr(), w_extra.shape[0])
 
 
+def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float):
+    """x [T, D] bf16, gamma [D] bf16 -> (h = x * rstd * gamma [T, D] bf16, rstd [T] fp32)."""
+    _need_cuda(x, gamma)
+    t, d = x.shape
+    h = torch.empty_like(x)
+    rstd = torch.empty(t, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().moe_b200_rmsnorm(
+        x.data_ptr(), gamma.data_ptr(), t, d, float(eps), h.data_ptr(), rstd.data_ptr(),
+        _stream(x)), "moe_b200_rmsnorm")
+    _count(1 if t else 0)
+    return h, rstd
+
+
+def rmsnorm_bwd(dh, x, rstd, gamma, add=None):
+    """-> (dx [T, D] bf16 including `add` (the residual branch's gradient) when given,
+    dgamma [D] fp32)."""
+    _need_cuda(dh, x, rstd, gamma)
+    t, d = x.shape
+    dx = torch.empty_like(x)
+    dgamma = torch.zeros(d, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().moe_b200_rmsnorm_bwd(
+        dh.data_ptr(), x.data_ptr(), rstd.data_ptr(), gamma.data_ptr(), _lib.ptr(add), t, d,
+        dx.data_ptr(), dgamma.data_ptr(), _stream(x)), "moe_b200_rmsnorm_bwd")
+    _count(1 if t else 0)
+    return dx, dgamma
+
+
 def copy_cols(src: torch.Tensor, dst_ld: int) -> torch.Tensor:
     """[rows, cols] 16-bit matrix -> [rows, dst_ld]: zero-padded columns (dst_ld > cols) or the
     first dst_ld columns (dst_ld < cols)."""

@@ -341,6 +341,7 @@ def moe_block(
     aux_coef: float,
     activation: str,
     save_for_backward: bool,
+    residual: Optional[torch.Tensor] = None,
 ) -> _T15:
     """The whole MoE block as one op: router GEMM, top-k, dispatch, experts (routed + shared),
     combine and the balance loss, with no PyTorch glue kernels in between
@@ -375,7 +376,7 @@ def moe_block(
         xs, a1 = x.new_empty(0), x.new_empty(0)
         hid, _ = K.up_gemm(x, w_in, eids, npp, 0, act, False, gather=(sids, ks), w_extra=w_sh_in)
     y = K.down_gemm(hid, w_out, eids, npp, 0, sids, tw, m, w_extra=w_sh_out)
-    out = K.combine(y, inv, n, ks)
+    out = K.combine(y, inv, n, ks, residual)   # + residual [T, D] in the same fp32 sum when given
     if full_softmax:
         aux = K.balance_loss(colsum, counts_all, e_n, n, aux_coef)
     else:
@@ -386,7 +387,7 @@ def moe_block(
 
 @moe_block.register_fake
 def _(x, router_w, logit_bias, w_in, w_out, w_sh_in, w_sh_out, top_k, normalize, full_softmax,
-      aux_coef, activation, save_for_backward):
+      aux_coef, activation, save_for_backward, residual=None):
     n, d = x.shape
     e_n = w_in.shape[0]
     s_n = 0 if w_sh_in is None else w_sh_in.shape[0]
@@ -485,7 +486,8 @@ def _(grad_out, grad_aux, x, logit_bias, w_in, w_out, w_sh_in, w_sh_out, xs, a1,
 
 def _block_setup(ctx, inputs, output):
     (x, router_w, logit_bias, w_in, w_out, w_sh_in, w_sh_out, top_k, normalize, full_softmax,
-     aux_coef, activation, save_for_backward) = inputs
+     aux_coef, activation, save_for_backward, residual) = inputs
+    ctx.has_residual = residual is not None
     ctx.mark_non_differentiable(*output[2:])
     ctx.set_materialize_grads(False)
     if not save_for_backward:
@@ -517,7 +519,8 @@ def _block_backward(ctx, grad_out, grad_aux, *unused):
         grad_out, grad_aux, x, bias, w_in, w_out, w_sh_in, w_sh_out, *kept, *ctx.args)
     d_router = d_router.to(ctx.router_dtype)
     return (dx, d_router, None, dw_in, dw_out, dsi if ctx.has_shared else None,
-            dso if ctx.has_shared else None, None, None, None, None, None, None)
+            dso if ctx.has_shared else None, None, None, None, None, None, None,
+            grad_out if ctx.has_residual else None)
 
 
 moe_block.register_autograd(_block_backward, setup_context=_block_setup)

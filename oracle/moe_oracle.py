@@ -306,3 +306,36 @@ class OracleBlock(torch.nn.Module):
         out = experts_forward(x, self.W_in, self.W_out, w, idx, self.activation, self.W_sh_in,
                               self.W_sh_out)
         return out.view(shape)
+
+
+# ------------------------------------------------------------------------- the FFN sublayer
+def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """RMSNorm.forward of the reference (src/model/ln.py:31-38): the row is rescaled by the
+    reciprocal RMS of its features and multiplied by gamma; no mean, no shift."""
+    return F.rms_norm(x, (x.shape[-1],), gamma, eps)
+
+
+def rmsnorm_backward(dh: torch.Tensor, x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6):
+    """Closed form of the gradient through rmsnorm, in fp32: (dx, dgamma).
+    With r = rsqrt(mean(x^2) + eps):  dx = r * (gamma * dh) - x * r^3 / D * <gamma * dh, x>,
+    dgamma = sum over rows of dh * x * r."""
+    xf, df, gf = x.float(), dh.float(), gamma.float()
+    r = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    dot = (gf * df * xf).sum(-1, keepdim=True)
+    dx = r * gf * df - xf * r.pow(3) * dot / x.shape[-1]
+    return dx, (df * xf * r).sum(0)
+
+
+class OracleSublayer(torch.nn.Module):
+    """x + ffn(norm_ffn(x)) with the balance loss next to it: the tail of Block.forward
+    (src/model/nanospeaker.py:165-169)."""
+
+    def __init__(self, block: "OracleBlock", eps: float = 1e-6):
+        super().__init__()
+        self.block = block
+        self.eps = eps
+        self.gamma = torch.nn.Parameter(torch.ones(block.router_W.shape[0]))
+
+    def forward(self, x: torch.Tensor):
+        out = x + self.block(rmsnorm(x, self.gamma, self.eps))
+        return out, self.block.aux_loss

@@ -1,7 +1,7 @@
 """Generate the golden vectors in this directory by running the UNMODIFIED reference.
 
 Usage (needs a checkout of Osmansiddiquer/nanospeaker):
-    python tests/golden/make_golden.py /path/to/nanospeaker
+    python tests/golden/make_golden.py /path/to/nanospeaker [--sublayer-only]
 
 Each .npz holds the inputs and everything the reference's pure-PyTorch MoE path
 (MoEBlock(..., fused=False, kernel=False, capacity_factor=None) on CPU) computes from them:
@@ -89,6 +89,52 @@ def block_case(MoEBlock, name, *, d_model, n_experts, d_ff, top_k, n_shared, tok
     print(name, {k: v.shape for k, v in s.items() if hasattr(v, "shape") and v.ndim})
 
 
+def sublayer_case(MoEBlock, RMSNorm, name, *, d_model, n_experts, d_ff, top_k, n_shared, tokens,
+                  dtype, seed):
+    """The FFN sublayer of the reference's Block: x + ffn(norm_ffn(x)), training mode, all
+    gradients of out^2.mean() + aux_loss (src/model/nanospeaker.py:165-169)."""
+    torch.manual_seed(seed)
+    m = MoEBlock(d_model, n_experts, d_ff=d_ff, top_k=top_k, n_shared=n_shared,
+                 capacity_factor=None, normalize_weights=True, fused=False, kernel=False)
+    norm = RMSNorm(d_model)
+    with torch.no_grad():
+        m.router.W.copy_(torch.randn_like(m.router.W) * 0.3)
+        m.W_in.copy_(torch.randn_like(m.W_in) * d_model ** -0.5)
+        m.W_out.copy_(torch.randn_like(m.W_out) * m.d_hidden ** -0.5)
+        m.W_sh_in.copy_(torch.randn_like(m.W_sh_in) * d_model ** -0.5)
+        m.W_sh_out.copy_(torch.randn_like(m.W_sh_out) * m.d_hidden ** -0.5)
+        norm.gamma.copy_(1.0 + 0.2 * torch.randn(d_model))
+    x = (torch.randn(tokens, d_model) * 1.7).to(dtype).requires_grad_(True)
+    m, norm = m.to(dtype).train(), norm.to(dtype).train()
+    s = {}
+    put(s, "x", x)
+    put(s, "gamma", norm.gamma)
+    put(s, "router_W", m.router.W)
+    put(s, "W_in", m.W_in)
+    put(s, "W_out", m.W_out)
+    put(s, "W_sh_in", m.W_sh_in)
+    put(s, "W_sh_out", m.W_sh_out)
+    s["meta"] = np.array([d_model, n_experts, d_ff, top_k, n_shared, tokens], dtype=np.int64)
+    s["epsilon"] = np.array(norm.epsilon)
+    s["dtype"] = np.array(str(dtype).replace("torch.", ""))
+    h = norm(x)
+    put(s, "h", h)
+    put(s, "logits", (h.detach() @ m.router.W.detach()).float())
+    out = x + m(h)
+    put(s, "out", out)
+    put(s, "aux_loss", m.aux_loss.float())
+    (out.float().square().mean() + m.aux_loss).backward()
+    put(s, "grad_x", x.grad)
+    put(s, "grad_gamma", norm.gamma.grad)
+    put(s, "grad_router_W", m.router.W.grad)
+    put(s, "grad_W_in", m.W_in.grad)
+    put(s, "grad_W_out", m.W_out.grad)
+    put(s, "grad_W_sh_in", m.W_sh_in.grad)
+    put(s, "grad_W_sh_out", m.W_sh_out.grad)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **s)
+    print(name, tuple(out.shape))
+
+
 def routing_case(MoEBlock, name, *, tokens, n_experts, top_k, seed, bf16_logits):
     """Routing only at nanoSpeaker's width: logits -> torch.topk -> stable-sort plan."""
     torch.manual_seed(seed)
@@ -111,6 +157,13 @@ def main():
     ref = sys.argv[1] if len(sys.argv) > 1 else os.environ["NANOSPEAKER_REF"]
     sys.path.insert(0, ref)
     from src.model.moe import MoEBlock  # the reference, unmodified
+    from src.model.ln import RMSNorm
+
+    sub = dict(d_model=64, n_experts=4, d_ff=192, top_k=2, n_shared=1, tokens=80)
+    sublayer_case(MoEBlock, RMSNorm, "sublayer_fp32_train", dtype=torch.float32, seed=7, **sub)
+    sublayer_case(MoEBlock, RMSNorm, "sublayer_bf16_train", dtype=torch.bfloat16, seed=8, **sub)
+    if "--sublayer-only" in sys.argv:
+        return
 
     common = dict(d_model=64, n_experts=4, d_ff=192, top_k=2, n_shared=1, tokens=80)
     block_case(MoEBlock, "block_fp32_eval", dtype=torch.float32, train=False, seed=1, **common)
