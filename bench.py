@@ -244,6 +244,9 @@ def build_stages(m, x):
         dl = copies(K.router_fused_bwd(logits_p, bias, idx_all, dtw, E, k, S, True, True, d_aux,
                                        counts, 1e-2, ld))
 
+        gamma = torch.ones(D, device=x.device, dtype=x.dtype)
+        _, rstd = K.rmsnorm(x, gamma, 1e-6)
+
         GE, TF = "hbm", "tensor"
         # One entry per kernel launch of the block op's forward + backward, in launch order.
         # M counts routed and shared pairs alike: (k + S) * T rows go through every expert GEMM.
@@ -287,6 +290,10 @@ def build_stages(m, x):
              lambda i: K.wgrad(xr[i % 3], da1[i % 3], offs, Ea, gather=("a", sids, ka), n_extra=S)),
             ("wgrad_out (gathered rows)", TF, 2.0 * M * H * D, 0,
              lambda i: K.wgrad(hid[i % 3], xr[i % 3], offs, Ea, gather=("b", sids, ka), n_extra=S)),
+            ("rmsnorm forward (FFN sublayer only)", GE, 2 * T * D * 2, 0,
+             lambda i: K.rmsnorm(xr[i % 3], gamma, 1e-6)),
+            ("rmsnorm backward + residual gradient (FFN sublayer only)", GE, 4 * T * D * 2, 0,
+             lambda i: K.rmsnorm_bwd(xr[(i + 1) % 3], xr[i % 3], rstd, gamma, add=xr[(i + 2) % 3])),
             ("router_fused_bwd", GE, T * ld * 2 * 2 + T * ka * 10, 1,
              lambda i: K.router_fused_bwd(logits_p, bias, idx_all, dtw, E, k, S, True, True,
                                           d_aux, counts, 1e-2, ld)),
@@ -611,7 +618,57 @@ def run_side_workload(args):
         return e0.elapsed_time(e1) / steps
 
     g = torch.Generator().manual_seed(100)
-    if args.workload == "decode":
+    if args.workload == "sublayer":
+        from nanospeaker_b200.sublayer import MoEFFNSublayer
+        T = TOKENS
+        sub = MoEFFNSublayer(make_block(7)).to(torch.bfloat16).to(dev).train()
+        with torch.no_grad():
+            sub.norm_gamma.copy_(1 + 0.1 * torch.randn(D_MODEL, generator=g))
+        params = list(sub.parameters())
+        one = torch.ones((), device=dev)
+
+        def graph_of(fn):
+            xs = [torch.randn(T, D_MODEL, generator=g).bfloat16().to(dev).requires_grad_(True)
+                  for _ in range(4)]
+            gos = [torch.randn(T, D_MODEL, generator=g).bfloat16().to(dev) for _ in range(4)]
+            graphs = []
+            for x, go in zip(xs, gos):
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    for _ in range(3):
+                        for p in params:
+                            p.grad = None
+                        x.grad = None
+                        out, aux = fn(x)
+                        torch.autograd.backward([out, aux], [go, one])
+                torch.cuda.current_stream().wait_stream(side)
+                del out, aux
+                sub.ffn.aux_loss = torch.zeros((), device=dev)
+                for p in params:
+                    p.grad = None
+                x.grad = None
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    out, aux = fn(x)
+                    torch.autograd.backward([out, aux], [go, one])
+                graphs.append((gr, x, go, out))
+            return graphs
+
+        def unfused(x):
+            h = torch.nn.functional.rms_norm(x, (D_MODEL,), sub.norm_gamma, sub.epsilon)
+            return x + sub.ffn(h), sub.ffn.aux_loss
+
+        fused_graphs = graph_of(lambda x: sub(x))
+        ms = time_loop(lambda i: fused_graphs[i % 4][0].replay())
+        unfused_graphs = graph_of(unfused)
+        ms_unfused = time_loop(lambda i: unfused_graphs[i % 4][0].replay())
+        line = {"metric": "FFN sublayer tokens/s (fwd+bwd)", "value": T / (ms / 1e3),
+                "unit": "tokens/s", "higher_is_better": True, "ms_per_step": ms,
+                "unfused_ms_per_step": ms_unfused,
+                "config": {"workload": "x + ffn(rmsnorm(x)) forward + backward, T=16384, bf16: the "
+                                       "fused autograd node against torch rms_norm + block + add"}}
+    elif args.workload == "decode":
         layers, T = 20, 64
         stack = StackedMoEDecoder([make_block(1000 + i) for i in range(layers)])
         xs = [torch.randn(T, D_MODEL, generator=g).bfloat16().to(dev) for _ in range(8)]
@@ -659,9 +716,11 @@ def main():
                     help="time eager module calls instead of a captured CUDA graph of the step")
     ap.add_argument("--profile-stage", default="",
                     help="run only the stage whose name contains this text, 3 launches (for ncu)")
-    ap.add_argument("--workload", default="train", choices=["train", "decode", "prefill"],
+    ap.add_argument("--workload", default="train", choices=["train", "decode", "prefill", "sublayer"],
                     help="train = the headline (forward + backward, T=16384); decode / prefill = "
-                         "the forward-only workloads of the block's other callers")
+                         "the forward-only workloads of the block's other callers; sublayer = "
+                         "x + ffn(rmsnorm(x)) forward + backward at T=16384, fused node against "
+                         "norm, block and add as separate steps")
     args = ap.parse_args()
     if args.workload != "train":
         run_side_workload(args)

@@ -13,6 +13,8 @@ namespace moe {
 
 constexpr int NORM_WARPS = 8;
 constexpr int NORM_MAX_CHUNKS = 8;  // 16-byte chunks per lane: rows up to 32 * 8 * 8 = 2048 columns
+// The kernels are instantiated for 1, 2, 3, 4 or 8 chunks per lane: the per-lane row state lives in
+// registers, and sizing it for the widest row would leave one resident block per SM.
 
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -39,6 +41,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // h[t, :] = x[t, :] * rstd[t] * gamma,  rstd[t] = rsqrt(mean(x[t, :]^2) + eps)  (kept for the backward)
+template <int NCH>
 __global__ void __launch_bounds__(NORM_WARPS * 32)
     rmsnorm_fwd_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gamma,
                        int64_t n_rows, int32_t chunks_per_row, float eps, float inv_d,
@@ -48,10 +51,10 @@ __global__ void __launch_bounds__(NORM_WARPS * 32)
   const int lane = threadIdx.x & 31;
   const int64_t warps = int64_t(gridDim.x) * NORM_WARPS;
   for (int64_t t = int64_t(blockIdx.x) * NORM_WARPS + (threadIdx.x >> 5); t < n_rows; t += warps) {
-    uint4 v[NORM_MAX_CHUNKS];
+    uint4 v[NCH];
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_CHUNKS; ++i) {
+    for (int i = 0; i < NCH; ++i) {
       const int c = i * 32 + lane;
       if (c < chunks_per_row) {
         v[i] = x[t * chunks_per_row + c];
@@ -64,7 +67,7 @@ __global__ void __launch_bounds__(NORM_WARPS * 32)
     const float r = rsqrtf(warp_sum(ss) * inv_d + eps);
     if (lane == 0) rstd[t] = r;
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_CHUNKS; ++i) {
+    for (int i = 0; i < NCH; ++i) {
       const int c = i * 32 + lane;
       if (c < chunks_per_row) {
         float f[8], g[8];
@@ -81,6 +84,7 @@ __global__ void __launch_bounds__(NORM_WARPS * 32)
 // dx[t] = rstd * (gamma * dh) - x * rstd^3 / D * <gamma * dh, x>  (+ add[t], the residual branch)
 // dgamma += sum_t dh[t] * x[t] * rstd[t]   (fp32; per-block partial sums in shared memory, then
 // one atomic per block and column)
+template <int NCH>
 __global__ void __launch_bounds__(NORM_WARPS * 32)
     rmsnorm_bwd_kernel(const uint4* __restrict__ dh, const uint4* __restrict__ x,
                        const float* __restrict__ rstd, const uint4* __restrict__ gamma,
@@ -93,19 +97,19 @@ __global__ void __launch_bounds__(NORM_WARPS * 32)
   const int n_cols = chunks_per_row * 8;
   for (int i = threadIdx.x; i < n_cols; i += blockDim.x) dg_s[i] = 0.f;
   __syncthreads();
-  float dg[NORM_MAX_CHUNKS][8];
+  float dg[NCH][8];
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_CHUNKS; ++i)
+  for (int i = 0; i < NCH; ++i)
 #pragma unroll
     for (int k = 0; k < 8; ++k) dg[i][k] = 0.f;
 
   const int64_t warps = int64_t(gridDim.x) * NORM_WARPS;
   for (int64_t t = int64_t(blockIdx.x) * NORM_WARPS + (threadIdx.x >> 5); t < n_rows; t += warps) {
-    uint4 vd[NORM_MAX_CHUNKS], vx[NORM_MAX_CHUNKS];
+    uint4 vd[NCH], vx[NCH];
     const float r = rstd[t];
     float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_CHUNKS; ++i) {
+    for (int i = 0; i < NCH; ++i) {
       const int c = i * 32 + lane;
       if (c < chunks_per_row) {
         vd[i] = dh[t * chunks_per_row + c];
@@ -123,7 +127,7 @@ __global__ void __launch_bounds__(NORM_WARPS * 32)
     }
     const float coef = warp_sum(dot) * r * r * r * inv_d;
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_CHUNKS; ++i) {
+    for (int i = 0; i < NCH; ++i) {
       const int c = i * 32 + lane;
       if (c < chunks_per_row) {
         float d[8], xx[8], g[8], o[8];
@@ -143,7 +147,7 @@ __global__ void __launch_bounds__(NORM_WARPS * 32)
     }
   }
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_CHUNKS; ++i) {
+  for (int i = 0; i < NCH; ++i) {
     const int c = i * 32 + lane;
     if (c < chunks_per_row) {
 #pragma unroll
@@ -175,10 +179,18 @@ int moe_b200_rmsnorm(const void* x, const void* gamma, int64_t n_rows, int32_t d
   if (n_rows == 0) return MOE_B200_OK;
   if (!x || !gamma || !h || !rstd) return MOE_B200_ERR_NULL;
   if (!aligned16(x) || !aligned16(gamma) || !aligned16(h)) return MOE_B200_ERR_ALIGN;
-  launch_pdl(rmsnorm_fwd_kernel, dim3(norm_grid(n_rows, 8)), dim3(NORM_WARPS * 32), 0,
-             static_cast<cudaStream_t>(stream), static_cast<const uint4*>(x),
-             static_cast<const uint4*>(gamma), n_rows, d_model / 8, eps, 1.f / float(d_model),
-             static_cast<uint4*>(h), rstd);
+  const int nch = (d_model / 8 + 31) / 32;
+#define LAUNCH(N)                                                                              \
+  launch_pdl(rmsnorm_fwd_kernel<N>, dim3(norm_grid(n_rows, 8)), dim3(NORM_WARPS * 32), 0,         \
+             static_cast<cudaStream_t>(stream), static_cast<const uint4*>(x),                     \
+             static_cast<const uint4*>(gamma), n_rows, d_model / 8, eps, 1.f / float(d_model),    \
+             static_cast<uint4*>(h), rstd)
+  if (nch <= 1) LAUNCH(1);
+  else if (nch <= 2) LAUNCH(2);
+  else if (nch <= 3) LAUNCH(3);
+  else if (nch <= 4) LAUNCH(4);
+  else LAUNCH(8);
+#undef LAUNCH
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
@@ -192,11 +204,19 @@ int moe_b200_rmsnorm_bwd(const void* dh, const void* x, const float* rstd, const
   if (!aligned16(dh) || !aligned16(x) || !aligned16(gamma) || !aligned16(add) || !aligned16(dx))
     return MOE_B200_ERR_ALIGN;
   // few blocks: every block ends with one atomic per column on dgamma
-  launch_pdl(rmsnorm_bwd_kernel, dim3(norm_grid(n_rows, 4)), dim3(NORM_WARPS * 32),
-             size_t(d_model) * sizeof(float), static_cast<cudaStream_t>(stream),
-             static_cast<const uint4*>(dh), static_cast<const uint4*>(x), rstd,
-             static_cast<const uint4*>(gamma), static_cast<const uint4*>(add), n_rows,
-             d_model / 8, 1.f / float(d_model), static_cast<uint4*>(dx), dgamma);
+  const int nch = (d_model / 8 + 31) / 32;
+#define LAUNCH(N)                                                                              \
+  launch_pdl(rmsnorm_bwd_kernel<N>, dim3(norm_grid(n_rows, 3)), dim3(NORM_WARPS * 32),            \
+             size_t(d_model) * sizeof(float), static_cast<cudaStream_t>(stream),                  \
+             static_cast<const uint4*>(dh), static_cast<const uint4*>(x), rstd,                   \
+             static_cast<const uint4*>(gamma), static_cast<const uint4*>(add), n_rows,            \
+             d_model / 8, 1.f / float(d_model), static_cast<uint4*>(dx), dgamma)
+  if (nch <= 1) LAUNCH(1);
+  else if (nch <= 2) LAUNCH(2);
+  else if (nch <= 3) LAUNCH(3);
+  else if (nch <= 4) LAUNCH(4);
+  else LAUNCH(8);
+#undef LAUNCH
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
