@@ -579,6 +579,75 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_ep_workload(args):
+    """BASELINE config 5: expert-parallel forward + backward. 76 routed experts partitioned over the
+    ranks, shared experts and router replicated, T=65536 tokens per GPU, uniform routing. One rank
+    per GPU under torchrun; eager launches (the split sizes of the all-to-all are read on the
+    host); CUDA events, max over ranks."""
+    import torch.distributed as dist
+    from nanospeaker_b200 import MoEBlock, expert_parallel as EP, kernels as K
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        raise SystemExit("--workload ep needs torchrun with at least 2 ranks")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    T = 65536
+    w, _ = init_weights()
+    m = MoEBlock(D_MODEL, N_EXPERTS, d_ff=D_FF, top_k=TOP_K, n_shared=N_SHARED,
+                 capacity_factor=None).to(torch.bfloat16)
+    with torch.no_grad():
+        m.router.W.copy_(w["router_W"])
+        m.W_sh_in.copy_(w["W_sh_in"])
+        m.W_sh_out.copy_(w["W_sh_out"])
+    m = m.to(dev).eval()           # eval: top-k softmax router, no balance loss in this workload
+    lo, hi = EP.expert_partition(N_EXPERTS, world)[rank]
+    w_in = w["W_in"][lo:hi].bfloat16().to(dev).requires_grad_(True)
+    w_out = w["W_out"][lo:hi].bfloat16().to(dev).requires_grad_(True)
+    g = torch.Generator().manual_seed(100 + rank)
+    xs = [torch.randn(T, D_MODEL, generator=g).bfloat16().to(dev).requires_grad_(True)
+          for _ in range(2)]
+    gout = torch.randn(T, D_MODEL, generator=g).bfloat16().to(dev)
+    replicated = [m.router.W, m.W_sh_in, m.W_sh_out]
+
+    def step(i):
+        x = xs[i % 2]
+        x.grad = None
+        out, _ = EP.ep_block_forward(x, m.router, w_in, w_out, m.W_sh_in, m.W_sh_out, "silu")
+        out.backward(gout)
+        EP.all_reduce_replicated_grads(replicated)
+
+    steps, warmup = args.steps, max(args.warmup, 3)
+    for i in range(warmup):
+        step(i)
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(warmup + i)
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t) / steps
+    K.check_status(dev)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "MoE-block tokens/s (fwd+bwd, expert parallel)",
+            "value": T * world / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "BASELINE config 5: experts partitioned over the ranks, "
+                                   f"T={T} tokens per GPU, uniform routing, forward + backward, "
+                                   "dispatch / combine by NCCL all-to-all (first version)"}}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def run_side_workload(args):
     """The two forward-only workloads of the block's other callers, one JSON line each (not the
     headline): `decode` = 20 stacked blocks on T=64 tokens replayed from one CUDA graph
@@ -716,13 +785,15 @@ def main():
                     help="time eager module calls instead of a captured CUDA graph of the step")
     ap.add_argument("--profile-stage", default="",
                     help="run only the stage whose name contains this text, 3 launches (for ncu)")
-    ap.add_argument("--workload", default="train", choices=["train", "decode", "prefill", "sublayer"],
+    ap.add_argument("--workload", default="train", choices=["train", "decode", "prefill", "sublayer", "ep"],
                     help="train = the headline (forward + backward, T=16384); decode / prefill = "
                          "the forward-only workloads of the block's other callers; sublayer = "
                          "x + ffn(rmsnorm(x)) forward + backward at T=16384, fused node against "
                          "norm, block and add as separate steps")
     args = ap.parse_args()
-    if args.workload != "train":
+    if args.workload == "ep":
+        run_ep_workload(args)
+    elif args.workload != "train":
         run_side_workload(args)
     elif args.impl == "reference":
         run_reference(args)

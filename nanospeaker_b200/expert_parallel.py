@@ -113,10 +113,11 @@ def ep_forward_steps(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tens
     inv = torch.empty_like(order)
     inv[order] = torch.arange(order.numel(), device=order.device)
     y_pairs = y_sorted[inv].view(t, k, -1)                           # pair (t, j) at [t, j]
-    acc = torch.promote_types(x.dtype, torch.float32)               # sum in fp32 at least
-    out = (y_pairs.to(acc) * topk_w.to(acc).unsqueeze(-1)).sum(1)
+    # weighted sum over the k pairs of a token as a batched [1, k] x [k, D] product: accumulates in
+    # fp32 without materialising a [T, k, D] fp32 temporary
+    out = torch.bmm(topk_w.to(y_pairs.dtype).unsqueeze(1), y_pairs).squeeze(1)
     if w_sh_in is not None:
-        out = out + shared_fn(x, w_sh_in, w_sh_out, activation).to(acc)
+        out = out + shared_fn(x, w_sh_in, w_sh_out, activation)
     return out.to(x.dtype)
 
 
