@@ -80,6 +80,65 @@ def shared_experts_cuda(x: torch.Tensor, w_sh_in: torch.Tensor, w_sh_out: torch.
     return out
 
 
+# ------------------------------------------------ home-side row movement on the block's kernels
+def _kernel_rows(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0
+
+
+def _plan_tensors(order: torch.Tensor, n_pairs: int):
+    """order (pair ids grouped by owner) as the permute kernel's slot list: int32, padded with the
+    sentinel to a multiple of 8 rows, plus the device scalar holding the padded length."""
+    cap = (n_pairs + 7) // 8 * 8
+    sids = torch.full((cap,), n_pairs, dtype=torch.int32, device=order.device)
+    sids[:n_pairs] = order
+    npp = torch.full((1,), cap, dtype=torch.int32, device=order.device)
+    return sids, npp
+
+
+class _GatherPairRows(torch.autograd.Function):
+    """rows[i] = x[order[i] // k] (permute kernel); backward: dx[t] = sum of its k pair rows
+    (combine kernel through the inverse permutation)."""
+
+    @staticmethod
+    def forward(ctx, x, sids, npp, inv32, k, n_pairs):
+        from . import kernels as K
+        ctx.save_for_backward(inv32)
+        ctx.k, ctx.t = k, x.shape[0]
+        return K.permute(x, k, sids, npp)[:n_pairs]
+
+    @staticmethod
+    def backward(ctx, grad_rows):
+        from . import kernels as K
+        (inv32,) = ctx.saved_tensors
+        return K.combine(grad_rows.contiguous(), inv32, ctx.t, ctx.k), None, None, None, None, None
+
+
+class _WeightedCombine(torch.autograd.Function):
+    """out[t] = sum_j w[t, j] * y_sorted[inv[t k + j]]: rows scaled by their weight, then the
+    combine kernel's fp32 sum. Backward: dOut rows gathered back into pair order (permute kernel)."""
+
+    @staticmethod
+    def forward(ctx, y_sorted, topk_w, order, sids, npp, inv32):
+        from . import kernels as K
+        t, k = topk_w.shape
+        w_sorted = topk_w.reshape(-1)[order]
+        ctx.save_for_backward(y_sorted, w_sorted, order, sids, npp)
+        ctx.shape = (t, k)
+        return K.combine(y_sorted * w_sorted.unsqueeze(1), inv32, t, k)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        from . import kernels as K
+        y_sorted, w_sorted, order, sids, npp = ctx.saved_tensors
+        t, k = ctx.shape
+        g_rows = K.permute(grad_out.contiguous(), k, sids, npp)[: t * k]
+        d_y = g_rows * w_sorted.unsqueeze(1)
+        d_w_sorted = (y_sorted * g_rows).sum(-1, dtype=torch.float32)   # no fp32 [M, D] temporaries
+        d_w = torch.empty(t * k, dtype=torch.float32, device=grad_out.device)
+        d_w[order] = d_w_sorted
+        return d_y, d_w.view(t, k).to(w_sorted.dtype), None, None, None, None
+
+
 # ------------------------------------------------------------------------ the step, as a generator
 def ep_forward_steps(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor,
                      w_in_local: torch.Tensor, w_out_local: torch.Tensor,
@@ -101,7 +160,16 @@ def ep_forward_steps(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tens
     recv_counts = yield ("counts", send_counts)
 
     lo_of_dest = torch.tensor([lo for lo, _ in bounds], device=x.device)[dest]
-    rows_send = x[order // k]                                        # [T*k, D], differentiable
+    n_pairs = t * k
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(order.numel(), device=order.device)
+    use_kernels = _kernel_rows(x) and n_pairs > 0
+    if use_kernels:
+        sids, npp = _plan_tensors(order, n_pairs)
+        inv32 = inv.to(torch.int32)
+        rows_send = _GatherPairRows.apply(x.contiguous(), sids, npp, inv32, k, n_pairs)
+    else:
+        rows_send = x[order // k]                                    # [T*k, D], differentiable
     idx_send = (flat_idx - lo_of_dest)[order]                        # expert id local to its owner
     send_list = send_counts.tolist()
     rows_recv = yield ("rows", rows_send, send_list, recv_counts)
@@ -110,14 +178,14 @@ def ep_forward_steps(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tens
     y_recv = expert_fn(rows_recv, idx_recv, w_in_local, w_out_local, activation)
     y_sorted = yield ("rows", y_recv, recv_counts, send_list)        # back home, in send order
 
-    inv = torch.empty_like(order)
-    inv[order] = torch.arange(order.numel(), device=order.device)
-    y_pairs = y_sorted[inv].view(t, k, -1)                           # pair (t, j) at [t, j]
-    # weighted sum over the k pairs of a token as a batched [1, k] x [k, D] product: accumulates in
-    # fp32 without materialising a [T, k, D] fp32 temporary
-    out = torch.bmm(topk_w.to(y_pairs.dtype).unsqueeze(1), y_pairs).squeeze(1)
+    if use_kernels:
+        out = _WeightedCombine.apply(y_sorted.contiguous(), topk_w, order, sids, npp, inv32)
+    else:
+        y_pairs = y_sorted[inv].view(t, k, -1)                       # pair (t, j) at [t, j]
+        acc = torch.promote_types(x.dtype, torch.float32)           # sum in fp32 at least
+        out = (y_pairs.to(acc) * topk_w.to(acc).unsqueeze(-1)).sum(1).to(x.dtype)
     if w_sh_in is not None:
-        out = out + shared_fn(x, w_sh_in, w_sh_out, activation)
+        out = out + shared_fn(x, w_sh_in, w_sh_out, activation).to(out.dtype)
     return out.to(x.dtype)
 
 
