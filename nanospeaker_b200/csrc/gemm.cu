@@ -382,10 +382,12 @@ static int64_t wgrad_items(int64_t rows, int n_groups, int routed, int ks_rows) 
 }
 
 // Rows per split-K chunk when the caller leaves the choice to the library: expert runs are cut at
-// 2048 rows; on the fixed schedule (few groups, every row) the chunks are sized so that the
+// 3072 rows (measured at T=16384, 78 experts: dW_in 98 / 82 / 78 / 72 / 75 / 89 us for chunks of
+// 1024 / 1536 / 2048 / 3072 / 4096 / 8192 rows -- shorter chunks mean more fp32 partial tiles,
+// longer ones a longer tail); on the fixed schedule (few groups, every row) the chunks are sized so that the
 // work items fill the SMs about once.
 static int auto_ks_rows(int32_t m_dim, int32_t n_dim, int64_t rows, int n_groups, int routed) {
-  if (routed) return 2048;
+  if (routed) return 3072;
   const int bn = n_dim % 256 == 0 ? 256 : 192;
   const int64_t tiles = int64_t((m_dim + BM - 1) / BM) * ((n_dim + bn - 1) / bn) * n_groups;
   int64_t splits = sm_count() / (tiles > 0 ? tiles : 1);
