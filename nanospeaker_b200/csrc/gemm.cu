@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <climits>
 #include <cstdint>
 #include <cstdlib>
@@ -479,7 +480,8 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   const bool may_split = rows > ks_rows;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned tx = unsigned((m_dim + BM - 1) / BM);
-  const unsigned gy = unsigned(n_groups);  // one reduce CTA per (tile slice, run)
+  // reduce CTAs per tile slice: they share the split runs (at most rows / ks_rows of them)
+  const unsigned gy = unsigned(std::min<int64_t>(n_groups, std::min<int64_t>(8, rows / ks_rows + 1)));
   int rc;
   if (n_dim % 256 == 0) {
     const unsigned ty = unsigned(n_dim / 256);

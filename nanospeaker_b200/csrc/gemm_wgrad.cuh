@@ -393,10 +393,27 @@ __global__ void __launch_bounds__(256)
   constexpr int64_t slot_elems = int64_t(BM) * BN;
   constexpr int vecs = BM * BN / 4;                  // float4 per tile
   constexpr int per_slice = vecs / WGRAD_REDUCE_SPLIT;
-  // one CTA per (tile slice, run); CTAs of runs that were not split leave at once
-  for (int g = blockIdx.y; g < p.n_groups; g += gridDim.y) {
+  // The runs that were split, in run order (one warp compacts the item table by ballot). A CTA takes
+  // every gridDim.y-th of them: the grid is sized for the few runs that can be split, not for one
+  // CTA per run (launching thousands of CTAs that leave at once cost more than the sums).
+  __shared__ int split_runs[WGRAD_MAX_GROUPS];
+  __shared__ int n_split_s;
+  if (threadIdx.x < 32) {
+    int n = 0;
+    for (int base = 0; base < p.n_groups; base += 32) {
+      const int g = base + int(threadIdx.x);
+      const bool split = g < p.n_groups && __ldg(p.item_table + g + 1) - __ldg(p.item_table + g) > 1;
+      const unsigned m = __ballot_sync(0xffffffffu, split);
+      if (split) split_runs[n + __popc(m & ((1u << threadIdx.x) - 1u))] = g;
+      n += __popc(m);
+    }
+    if (threadIdx.x == 0) n_split_s = n;
+  }
+  __syncthreads();
+  const int n_split = n_split_s;
+  for (int i = blockIdx.y; i < n_split; i += gridDim.y) {
+    const int g = split_runs[i];
     const int first = __ldg(p.item_table + g), n_c = __ldg(p.item_table + g + 1) - first;
-    if (n_c <= 1) continue;
     for (int f = slice * per_slice + threadIdx.x; f < (slice + 1) * per_slice; f += blockDim.x) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       const float4* src = reinterpret_cast<const float4*>(
