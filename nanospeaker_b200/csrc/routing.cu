@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(256)
 // ------------------------------------------------------------------------------- dispatch
 // Stable counting sort of the pairs by expert in two launches. The pairs are cut into at most
 // DISPATCH_MAX_BLOCKS chunks of `chunk` pairs (a power-of-two multiple of 1024), one block each.
-constexpr int DISPATCH_THREADS = 256;
+constexpr int DISPATCH_THREADS = 512;
 constexpr int DISPATCH_WARPS = DISPATCH_THREADS / 32;
 constexpr int DISPATCH_MIN_CHUNK = 1024;
 constexpr int DISPATCH_MAX_BLOCKS = 128;
@@ -315,22 +315,39 @@ __global__ void __launch_bounds__(DISPATCH_THREADS)
   __shared__ int32_t cursor[DISPATCH_WARPS][MAX_EXPERTS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // totals and earlier-block shares: warp w takes experts w, w + 8, ...; lanes stride over blocks
-  for (int e = warp; e < n_experts; e += DISPATCH_WARPS) {
-    int32_t tot = 0, bef = 0;
-    for (int b = lane; b < n_blocks; b += 32) {
-      const int32_t v = block_hist[int64_t(e) * n_blocks + b];
-      tot += v;
-      if (b < int(blockIdx.x)) bef += v;
+  // totals and earlier-block shares: warp w takes experts w, w + WARPS, ...; lanes stride over the
+  // blocks. Four experts per round with every load issued before the first sum (the table is small
+  // and the kernel latency-bound: one expert at a time left ten dependent round trips per warp).
+  static_assert(DISPATCH_MAX_BLOCKS <= 128, "a lane reads at most four blocks per expert");
+  for (int e0 = warp; e0 < n_experts; e0 += 4 * DISPATCH_WARPS) {
+    int32_t v[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int e = e0 + u * DISPATCH_WARPS;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int b = lane + 32 * j;
+        v[u][j] = (e < n_experts && b < n_blocks) ? __ldg(block_hist + int64_t(e) * n_blocks + b) : 0;
+      }
     }
 #pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      tot += __shfl_xor_sync(0xffffffffu, tot, o);
-      bef += __shfl_xor_sync(0xffffffffu, bef, o);
-    }
-    if (lane == 0) {
-      total[e] = tot;
-      before[e] = bef;
+    for (int u = 0; u < 4; ++u) {
+      const int e = e0 + u * DISPATCH_WARPS;
+      int32_t tot = 0, bef = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        tot += v[u][j];
+        if (lane + 32 * j < int(blockIdx.x)) bef += v[u][j];
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) {
+        tot += __shfl_xor_sync(0xffffffffu, tot, o);
+        bef += __shfl_xor_sync(0xffffffffu, bef, o);
+      }
+      if (lane == 0 && e < n_experts) {
+        total[e] = tot;
+        before[e] = bef;
+      }
     }
   }
   for (int i = threadIdx.x; i < DISPATCH_WARPS * MAX_EXPERTS; i += blockDim.x)
@@ -400,9 +417,15 @@ __global__ void __launch_bounds__(DISPATCH_THREADS)
     }
     return e;
   };
-  for (int r = 0; r < slice; r += 32) {
-    const int32_t e = expert_of(wbase + r + lane);
-    if (e >= 0) atomicAdd(&cursor[warp][e], 1);
+  // the pairs' expert ids are fetched four rounds at a time, ahead of the counting / ranking
+  constexpr int UB = 4;
+  for (int r = 0; r < slice; r += 32 * UB) {
+    int32_t ev[UB];
+#pragma unroll
+    for (int u = 0; u < UB; ++u) ev[u] = expert_of(wbase + r + 32 * u + lane);
+#pragma unroll
+    for (int u = 0; u < UB; ++u)
+      if (ev[u] >= 0) atomicAdd(&cursor[warp][ev[u]], 1);
   }
   __syncthreads();
   // exclusive prefix over warps, seeded with the run start and the earlier blocks' share
@@ -415,19 +438,25 @@ __global__ void __launch_bounds__(DISPATCH_THREADS)
     }
   }
   __syncthreads();
-  for (int r = 0; r < slice; r += 32) {
-    const int64_t pidx = wbase + r + lane;
-    const int32_t e = expert_of(pidx);
-    const unsigned peers = __match_any_sync(0xffffffffu, e);
-    if (e >= 0) {
-      const int rank = __popc(peers & ((1u << lane) - 1u));
-      const int32_t dst = cursor[warp][e] + rank;
-      sorted_ids[dst] = int32_t(pidx);
-      inv_ids[pidx] = dst;
+  for (int r = 0; r < slice; r += 32 * UB) {
+    int32_t ev[UB];
+#pragma unroll
+    for (int u = 0; u < UB; ++u) ev[u] = expert_of(wbase + r + 32 * u + lane);
+#pragma unroll
+    for (int u = 0; u < UB; ++u) {
+      const int64_t pidx = wbase + r + 32 * u + lane;
+      const int32_t e = ev[u];
+      const unsigned peers = __match_any_sync(0xffffffffu, e);
+      if (e >= 0) {
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        const int32_t dst = cursor[warp][e] + rank;
+        sorted_ids[dst] = int32_t(pidx);
+        inv_ids[pidx] = dst;
+      }
+      __syncwarp();
+      if (e >= 0 && lane == 31 - __clz(peers)) cursor[warp][e] += __popc(peers);
+      __syncwarp();
     }
-    __syncwarp();
-    if (e >= 0 && lane == 31 - __clz(peers)) cursor[warp][e] += __popc(peers);
-    __syncwarp();
   }
 }
 
