@@ -226,6 +226,10 @@ def build_stages(m, x):
         copies = lambda t: [t.clone() for _ in range(3)]
         xr = copies(x)
         gather = (sids, ka)
+        # as in the block op: the permute stops at the first shared run, the shared experts read
+        # their rows from the token-major matrix itself
+        live = offs[E:E + 1]
+        Mr = T * k                                   # routed pairs: the rows the permute copies
         xs = copies(K.permute(x, ka, sids, npp))
         hid0, a1 = K.up_gemm(xs[0], m.W_in, eids, npp, 0, 0, True, w_extra=m.W_sh_in)
         hid = copies(hid0)
@@ -261,10 +265,15 @@ def build_stages(m, x):
             ("dispatch alone (histogram, plan + scatter)", GE, M * 8 * 2 + M * 4 * 3, 0,
              lambda i: K.dispatch(idx_all, Ea)),
             # compulsory traffic: x read once (its k + S re-reads hit L2), every slot row written
-            ("permute", GE, T * D * 2 + M * D * 2 + M * 4, 2,
+            ("permute (routed rows; shared experts read x in place)", GE,
+             T * D * 2 + Mr * D * 2 + Mr * 4, 2,
+             lambda i: K.permute(xr[i % 3], ka, sids, live)),
+            ("permute, every row (without the shared-row shortcut)", GE,
+             T * D * 2 + M * D * 2 + M * 4, 0,
              lambda i: K.permute(xr[i % 3], ka, sids, npp)),
             ("up_gemm+glu (+a1 saved)", TF, 2.0 * M * D * 2 * H, 1,
-             lambda i: K.up_gemm(xs[i % 3], m.W_in, eids, npp, 0, 0, True, w_extra=m.W_sh_in)),
+             lambda i: K.up_gemm(xs[i % 3], m.W_in, eids, npp, 0, 0, True, w_extra=m.W_sh_in,
+                                 token_rows=(xr[i % 3], offs))),
             ("up_gemm+glu (gathered rows, inference)", TF, 2.0 * M * D * 2 * H, 0,
              lambda i: K.up_gemm(xr[i % 3], m.W_in, eids, npp, 0, 0, False, gather=gather,
                                  w_extra=m.W_sh_in)),
@@ -276,16 +285,19 @@ def build_stages(m, x):
             ("balance_loss", GE, E * 8, 1, lambda i: K.balance_loss(colsum, counts, E, T, 1e-2)),
             ("dhidden+glu_bwd", TF, 2.0 * M * D * H, 1,
              lambda i: K.dhidden_glu_bwd(xs[i % 3], m.W_out, eids, npp, 0, sids, tw, M, a1, 0,
-                                         True, w_extra=m.W_sh_out)),
+                                         True, w_extra=m.W_sh_out,
+                                         token_rows=(xr[i % 3], offs))),
             ("dhidden+glu_bwd (gathered rows)", TF, 2.0 * M * D * H, 0,
              lambda i: K.dhidden_glu_bwd(xr[i % 3], m.W_out, eids, npp, 0, sids, tw, M, a1, 0,
                                          True, gather_top_k=ka, w_extra=m.W_sh_out)),
             ("dx_gemm", TF, 2.0 * M * 2 * H * D, 1,
              lambda i: K.dx_gemm(da1[i % 3], m.W_in, eids, npp, 0, w_extra=m.W_sh_in)),
             ("wgrad_in (gemm + reduce)", TF, 2.0 * M * D * 2 * H, 1,
-             lambda i: K.wgrad(xs[i % 3], da1[i % 3], offs, Ea, n_extra=S)),
+             lambda i: K.wgrad(xs[i % 3], da1[i % 3], offs, Ea, n_extra=S,
+                               token_rows=("a", xr[i % 3]))),
             ("wgrad_out (gemm + reduce)", TF, 2.0 * M * H * D, 1,
-             lambda i: K.wgrad(hid[i % 3], xs[i % 3], offs, Ea, n_extra=S)),
+             lambda i: K.wgrad(hid[i % 3], xs[i % 3], offs, Ea, n_extra=S,
+                               token_rows=("b", xr[i % 3]))),
             ("wgrad_in (gathered rows)", TF, 2.0 * M * D * 2 * H, 0,
              lambda i: K.wgrad(xr[i % 3], da1[i % 3], offs, Ea, gather=("a", sids, ka), n_extra=S)),
             ("wgrad_out (gathered rows)", TF, 2.0 * M * H * D, 0,
@@ -305,11 +317,32 @@ def build_stages(m, x):
     return stages
 
 
+def gemm_stage_bytes(T, ld):
+    """Compulsory HBM bytes per launch of the GEMM stages: every operand read once, every output
+    written once (bf16). The GEMMs of this block sit below the ridge of the measured roofline
+    (about 250 flop per byte), so this floor, not the tensor peak, is what bounds them."""
+    D, H, k, S = D_MODEL, D_HIDDEN, TOP_K, N_SHARED
+    M, G = T * (k + S), N_EXPERTS + S
+    w_in, w_out = G * D * 2 * H * 2, G * H * D * 2
+    return {
+        "router GEMM": T * D * 2 + D * ld * 2 + T * ld * 2,
+        "up_gemm+glu (+a1 saved)": M * D * 2 + w_in + M * 3 * H * 2,
+        "up_gemm+glu (gathered rows, inference)": T * D * 2 + w_in + M * H * 2,
+        "down_gemm+scale": M * H * 2 + w_out + M * D * 2,
+        "dhidden+glu_bwd": M * D * 2 + M * 2 * H * 2 + w_out + M * 3 * H * 2 + M * 2,
+        "dx_gemm": M * 2 * H * 2 + w_in + M * D * 2,
+        "wgrad_in (gemm + reduce)": M * D * 2 + M * 2 * H * 2 + w_in,
+        "wgrad_out (gemm + reduce)": M * H * 2 + M * D * 2 + w_out,
+    }
+
+
 def stage_rooflines(m, x, pk):
     """Time every kernel of the step alone (CUDA events on the current stream) and put each next
     to its algorithmic work."""
     GE = "hbm"
     stages = build_stages(m, x)
+    from nanospeaker_b200.moe_kernel import _router_ld
+    floor_bytes = gemm_stage_bytes(x.shape[0], _router_ld(N_EXPERTS))
     with torch.no_grad():
         out = []
         for name, bound, work, per_step, fn in stages:
@@ -339,6 +372,11 @@ def stage_rooflines(m, x, pk):
             out.append({"kernel": name, "bound": bound, "us": round(us, 2),
                         "launches_per_step": per_step, "achieved": round(ach, 1), "peak": peak,
                         "unit": unit, "frac": round(ach / peak, 4)})
+            hb = next((b for key, b in floor_bytes.items() if name.startswith(key)), None)
+            if hb is not None:      # a GEMM stage: its HBM byte floor beside the tensor fraction
+                out[-1]["hbm_bytes"] = hb
+                out[-1]["hbm_gbs"] = round(hb / us / 1e3, 1)
+                out[-1]["hbm_frac"] = round(hb / us / 1e3 / pk["hbm_gbs"], 4)
     return out
 
 
@@ -563,6 +601,8 @@ def run_ours(args):
                                 "unit": top["unit"], "frac": top["frac"],
                                 "traffic": NCU_TRAFFIC_BYTES.get(top["kernel"]),
                                 "peak_source": pk["source"] + " (burst: kernel timed alone)"}
+            if "hbm_frac" in top:   # a GEMM below the ridge: its compulsory-byte floor as well
+                line["roofline"].update({k: top[k] for k in ("hbm_bytes", "hbm_gbs", "hbm_frac")})
             line["stages"] = stages
     if world > 1:
         dist.barrier()

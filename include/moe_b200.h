@@ -223,12 +223,19 @@ int moe_b200_rmsnorm_bwd(const void* dh, const void* x, const float* rstd, const
  * 2*d_hidden]); hid[row] = act(g) * u  ([rows, d_hidden]); when raw != NULL it also receives
  * [g | u] ([rows, 2*d_hidden], kept for the backward). a is [rows, d_model] (shared by all fixed
  * groups) or gathered. Replaces _gemm1_kernel (src/model/moe_kernel.py:269-323).
- * d_hidden must be 128. */
+ * d_hidden must be 128.
+ * a_tokens (may be NULL; routed schedule with a second weight stack, no gather): the token-major
+ * matrix [n_tokens, d_model] the slot-ordered rows were copied from. The groups of the second stack
+ * (shared experts: every token once, in token order) then read row `slot - pad_offsets[group]` of
+ * a_tokens instead of row `slot` of a, so their rows of a need not have been written at all (see
+ * moe_b200_permute: pass pad_offsets + n_groups as its live-row count). Rows past n_tokens read as
+ * zeros. */
 int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w_in,
                      int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_hidden, const int32_t* expert_ids,
                      const int32_t* n_post_pad, int32_t n_fixed_groups,
                      const int32_t* sorted_ids, int32_t gather_top_k, int64_t n_pairs,
-                     int32_t activation, void* hid, void* raw, int32_t* status, void* stream);
+                     int32_t activation, void* hid, void* raw, const void* a_tokens,
+                     int64_t n_tokens, const int32_t* pad_offsets, int32_t* status, void* stream);
 
 /* Down GEMM with the router weight fused: y[row] = (hid[row] @ w_out[e]) * pair_w[sorted_ids[row]]
  * (w_out [n_groups, k_dim, d_model]; weight 1 when pair_w is NULL). With fixed groups hid is
@@ -246,14 +253,16 @@ int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void*
  * douts is [rows, d_model] (shared by all fixed groups) or, with gather_top_k > 0, the token-major
  * dOut gathered through sorted_ids; a1, da1, hidw are stacked per fixed group.
  * Replaces the dH use of _gemm2_kernel plus _glu_bwd_kernel
- * (src/model/moe_kernel.py:676-692, 510-553). dtw may be NULL. */
+ * (src/model/moe_kernel.py:676-692, 510-553). dtw may be NULL.
+ * dout_tokens / n_tokens / pad_offsets: as a_tokens of moe_b200_up_gemm, for the rows of douts. */
 int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, const void* w_out,
                              int32_t n_groups, const void* w_extra, int32_t n_extra,
                              int32_t d_hidden, const int32_t* expert_ids,
                              const int32_t* n_post_pad, int32_t n_fixed_groups,
                              const int32_t* sorted_ids, int32_t gather_top_k, const void* pair_w,
                              int64_t n_pairs, const void* a1, int32_t activation, void* da1,
-                             void* hidw, void* dtw, int32_t* status, void* stream);
+                             void* hidw, void* dtw, const void* dout_tokens, int64_t n_tokens,
+                             const int32_t* pad_offsets, int32_t* status, void* stream);
 
 /* dX GEMM: ydx[row] = da1[row] @ w_in[e]^T, reading w_in [n_groups, d_model, 2*d_hidden] in place
  * (no transposed copy). With fixed groups da1 and ydx are stacked [S, rows, .]. Replaces the dX use
@@ -280,13 +289,17 @@ int moe_b200_wgrad_scratch_bytes(int32_t m_dim, int32_t n_dim, int64_t rows, int
  * (0 = both operands are slot-ordered buffers).
  * dw holds groups [0, n_first); with n_first < n_groups the remaining groups are written to
  * dw_extra [n_groups - n_first, m_dim, n_dim] (the shared experts' gradients).
+ * alt (may be NULL; routed schedule, no gather, n_first < n_groups): token-major matrix
+ * [alt_rows, m_dim] (alt_which = 1) or [alt_rows, n_dim] (alt_which = 2). The runs from n_first on
+ * read that operand's row `slot - pad_offsets[run]` from alt instead of row `slot` of a / b.
  * Replaces _dw_kernel (src/model/moe_kernel.py:453-507, 712-721), which has no split-K. */
 int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* b,
                    int32_t b_grouped, int32_t n_dim, int64_t rows, const int32_t* pad_offsets,
                    int32_t n_groups, int32_t ks_rows, const int32_t* sorted_ids,
                    int32_t gather_top_k, int64_t n_pairs, int32_t gather_which, void* dw,
                    int32_t n_first, void* dw_extra, void* partials, size_t partial_bytes,
-                   int32_t* status, void* stream);
+                   const void* alt, int64_t alt_rows, int32_t alt_which, int32_t* status,
+                   void* stream);
 
 #ifdef __cplusplus
 }

@@ -60,7 +60,7 @@ SIGNATURES = {
     "moe_b200_up_gemm": (
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,
-         _c_i32, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp]),
+         _c_i32, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp]),
     "moe_b200_down_gemm": (
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,
@@ -68,7 +68,8 @@ SIGNATURES = {
     "moe_b200_dhidden_glu_bwd": (
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,
-         _c_i32, _c_vp, _c_i64, _c_vp, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp]),
+         _c_i32, _c_vp, _c_i64, _c_vp, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_vp, _c_vp,
+         _c_vp]),
     "moe_b200_dx_gemm": (
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,
@@ -79,7 +80,7 @@ SIGNATURES = {
     "moe_b200_wgrad": (
         ctypes.c_int,
         [_c_vp, _c_i32, _c_i32, _c_vp, _c_i32, _c_i32, _c_i64, _c_vp, _c_i32, _c_i32, _c_vp, _c_i32,
-         _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_vp, _c_sz, _c_vp, _c_vp]),
+         _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_vp, _c_sz, _c_vp, _c_i64, _c_i32, _c_vp, _c_vp]),
 }
 
 _lib = None

@@ -112,7 +112,7 @@ static int sm_count() {
 template <int BN, int STAGES, bool B_MN, int EPI, bool GATHER_A = false, int OUT_BOXES = 4>
 static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2,
                        const CUtensorMap& tmOut, const RowsArgs& args, int64_t max_tiles,
-                       cudaStream_t st) {
+                       cudaStream_t st, const CUtensorMap* tmA2 = nullptr) {
   auto kern = rows_gemm_kernel<BN, STAGES, B_MN, EPI, GATHER_A, OUT_BOXES>;
   constexpr int smem = RowsSmem<BN, STAGES, EPI, OUT_BOXES>::DYNAMIC;
   static_assert(smem <= 232448, "shared memory of a row GEMM exceeds the 227 KB per-CTA limit");
@@ -125,13 +125,15 @@ static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   const int64_t sms = sm_count();
   const unsigned grid = unsigned(max_tiles < sms ? max_tiles : sms);
   const cudaError_t err = launch_pdl(kern, dim3(grid), dim3(rows_threads(EPI, GATHER_A)),
-                                     size_t(smem), st, tmA, tmB, tmB2, tmOut, args);
+                                     size_t(smem), st, tmA, tmA2 ? *tmA2 : tmA, tmB, tmB2, tmOut,
+                                     args);
   return err == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
 template <int BN, int STAGES, int GATHER>
-static int launch_wgrad_g(const CUtensorMap& tmA, const CUtensorMap& tmB, const WgradArgs& args,
-                        int tiles_x, int tiles_y, int64_t max_items, cudaStream_t st) {
+static int launch_wgrad_g(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmAlt,
+                          const WgradArgs& args, int tiles_x, int tiles_y, int64_t max_items,
+                          cudaStream_t st) {
   auto kern = wgrad_gemm_kernel<BN, STAGES, GATHER>;
   constexpr int smem = WgradSmem<BN, STAGES>::DYNAMIC;
   static std::once_flag once;
@@ -144,18 +146,20 @@ static int launch_wgrad_g(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   const unsigned grid = unsigned(tiles < sms ? tiles : sms);
   const int threads = GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS;
   const cudaError_t err =
-      launch_pdl(kern, dim3(grid), dim3(threads), size_t(smem), st, tmA, tmB, args, tiles_x, tiles_y);
+      launch_pdl(kern, dim3(grid), dim3(threads), size_t(smem), st, tmA, tmB, tmAlt, args, tiles_x,
+                 tiles_y);
   return err == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
 template <int BN, int STAGES>
-static int launch_wgrad(const CUtensorMap& tmA, const CUtensorMap& tmB, const WgradArgs& args,
-                        int tiles_x, int tiles_y, int64_t max_items, cudaStream_t st) {
+static int launch_wgrad(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmAlt,
+                        const WgradArgs& args, int tiles_x, int tiles_y, int64_t max_items,
+                        cudaStream_t st) {
   if (args.gather_a)
-    return launch_wgrad_g<BN, STAGES, 1>(tmA, tmB, args, tiles_x, tiles_y, max_items, st);
+    return launch_wgrad_g<BN, STAGES, 1>(tmA, tmB, tmAlt, args, tiles_x, tiles_y, max_items, st);
   if (args.gather_b)
-    return launch_wgrad_g<BN, STAGES, 2>(tmA, tmB, args, tiles_x, tiles_y, max_items, st);
-  return launch_wgrad_g<BN, STAGES, 0>(tmA, tmB, args, tiles_x, tiles_y, max_items, st);
+    return launch_wgrad_g<BN, STAGES, 2>(tmA, tmB, tmAlt, args, tiles_x, tiles_y, max_items, st);
+  return launch_wgrad_g<BN, STAGES, 0>(tmA, tmB, tmAlt, args, tiles_x, tiles_y, max_items, st);
 }
 
 // inputs feed TMA (16 bytes); outputs are written with 32-byte vectors
@@ -168,8 +172,24 @@ static RowsArgs base_args(const int32_t* expert_ids, const int32_t* n_post_pad,
   a.n_post_pad = n_post_pad;
   a.n_fixed_groups = n_fixed_groups;
   a.rows_host = int32_t(rows);
+  a.a2_first_group = INT32_MAX;
   a.status = status;
   return a;
+}
+
+// Token-major A rows for the groups of the second weight stack (the shared experts): the map over
+// a_tokens [n_tokens, k_dim] and the schedule fields that switch those groups over to it.
+static int use_token_rows(RowsArgs* g, CUtensorMap* tmA2, const void* a_tokens, int64_t n_tokens,
+                          const int32_t* pad_offsets, int32_t n_groups, int32_t n_extra,
+                          int32_t n_fixed_groups, int32_t gather_top_k, int32_t k_dim) {
+  if (!a_tokens) return MOE_B200_OK;
+  if (n_extra < 1 || n_fixed_groups > 0 || gather_top_k > 0 || n_tokens < 1) return MOE_B200_ERR_SHAPE;
+  if (!pad_offsets) return MOE_B200_ERR_NULL;
+  if ((reinterpret_cast<uintptr_t>(a_tokens) & 15u) != 0) return MOE_B200_ERR_ALIGN;
+  if (!map_rows_kmajor(tmA2, a_tokens, 1, n_tokens, k_dim)) return MOE_B200_ERR_TMA;
+  g->a2_first_group = n_groups;
+  g->a2_offsets = pad_offsets;
+  return MOE_B200_OK;
 }
 
 // Upper bound on the tile count of a row-grouped launch (the live count is on the device).
@@ -202,7 +222,8 @@ int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w
                      int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_hidden, const int32_t* expert_ids,
                      const int32_t* n_post_pad, int32_t n_fixed_groups,
                      const int32_t* sorted_ids, int32_t gather_top_k, int64_t n_pairs,
-                     int32_t activation, void* hid, void* raw, int32_t* status, void* stream) {
+                     int32_t activation, void* hid, void* raw, const void* a_tokens,
+                     int64_t n_tokens, const int32_t* pad_offsets, int32_t* status, void* stream) {
   CHECK_SCHED();
   if (d_hidden != 128 || d_model % 8 != 0 || d_model < 64) return MOE_B200_ERR_UNSUPPORTED;
   if (activation < 0 || activation > 4) return MOE_B200_ERR_UNSUPPORTED;
@@ -242,9 +263,13 @@ int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w
   g.top_k = gather_top_k;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t tiles = max_tiles(rows, 1, n_fixed_groups);
+  CUtensorMap tmA2 = tmA;
+  const int rc2 = use_token_rows(&g, &tmA2, a_tokens, n_tokens, pad_offsets, n_groups, n_extra,
+                                 n_fixed_groups, gather_top_k, d_model);
+  if (rc2 != MOE_B200_OK) return rc2;
   if (gather_top_k > 0)
     return launch_rows<256, 4, true, EPI_GLU, true>(tmA, tmB, tmB2, tmB, g, tiles, st);
-  return launch_rows<256, 4, true, EPI_GLU>(tmA, tmB, tmB2, tmB, g, tiles, st);
+  return launch_rows<256, 4, true, EPI_GLU>(tmA, tmB, tmB2, tmB, g, tiles, st, &tmA2);
 }
 
 int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void* w_out,
@@ -291,7 +316,8 @@ int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, c
                              const int32_t* n_post_pad, int32_t n_fixed_groups,
                              const int32_t* sorted_ids, int32_t gather_top_k, const void* pair_w,
                              int64_t n_pairs, const void* a1, int32_t activation, void* da1,
-                             void* hidw, void* dtw, int32_t* status, void* stream) {
+                             void* hidw, void* dtw, const void* dout_tokens, int64_t n_tokens,
+                             const int32_t* pad_offsets, int32_t* status, void* stream) {
   CHECK_SCHED();
   if (gather_top_k < 0 || (gather_top_k > 0 && (n_fixed_groups > 0 || !sorted_ids)))
     return MOE_B200_ERR_SHAPE;
@@ -338,9 +364,13 @@ int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, c
   CUtensorMap tmAux;
   if (!map_rows_kmajor(&tmAux, a1, n_fixed_groups > 0 ? n_fixed_groups : 1, rows, 2 * d_hidden))
     return MOE_B200_ERR_TMA;
+  CUtensorMap tmA2 = tmA;
+  const int rc2 = use_token_rows(&g, &tmA2, dout_tokens, n_tokens, pad_offsets, n_groups, n_extra,
+                                 n_fixed_groups, gather_top_k, d_model);
+  if (rc2 != MOE_B200_OK) return rc2;
   if (gather_top_k > 0)
     return launch_rows<128, 3, false, EPI_GLUBWD, true>(tmA, tmB, tmB2, tmAux, g, tiles, st);
-  return launch_rows<128, 3, false, EPI_GLUBWD>(tmA, tmB, tmB2, tmAux, g, tiles, st);
+  return launch_rows<128, 3, false, EPI_GLUBWD>(tmA, tmB, tmB2, tmAux, g, tiles, st, &tmA2);
 }
 
 int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,
@@ -416,7 +446,8 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
                    int32_t n_groups, int32_t ks_rows, const int32_t* sorted_ids,
                    int32_t gather_top_k, int64_t n_pairs, int32_t gather_which, void* dw,
                    int32_t n_first, void* dw_extra, void* partials, size_t partial_bytes,
-                   int32_t* status, void* stream) {
+                   const void* alt, int64_t alt_rows, int32_t alt_which, int32_t* status,
+                   void* stream) {
   if (rows < 0 || rows > (int64_t(1) << 30) || n_groups < 1 || n_groups > WGRAD_MAX_GROUPS ||
       m_dim < 1 || n_dim < 1)
     return MOE_B200_ERR_SHAPE;
@@ -452,7 +483,21 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
     return MOE_B200_ERR_TMA;
   if (gather_which == 1) tmA = tmB;
   if (gather_which == 2) tmB = tmA;
+  // runs [n_first, n_groups) may read one operand from a token-major matrix (row = slot - run start)
+  CUtensorMap tmAlt = tmA;
+  if (alt) {
+    if (alt_which < 1 || alt_which > 2 || !routed || gather_which || n_first >= n_groups || alt_rows < 1)
+      return MOE_B200_ERR_SHAPE;
+    if (!aligned16(alt)) return MOE_B200_ERR_ALIGN;
+    int32_t alt_fused = 0;
+    if (!map_rows_mnmajor(&tmAlt, alt, 1, alt_rows, alt_which == 1 ? m_dim : n_dim,
+                          alt_which == 1 ? BM / 64 : bn_boxes, &alt_fused))
+      return MOE_B200_ERR_TMA;
+    if (alt_fused != (alt_which == 1 ? a_fused : b_fused)) return MOE_B200_ERR_TMA;
+  }
   WgradArgs g{};
+  g.alt_which = alt ? alt_which : 0;
+  g.alt_first_group = n_first;
   g.pad_offsets = pad_offsets;
   g.n_groups = n_groups;
   g.rows_host = int32_t(rows);
@@ -485,13 +530,13 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   int rc;
   if (n_dim % 256 == 0) {
     const unsigned ty = unsigned(n_dim / 256);
-    rc = launch_wgrad<256, 4>(tmA, tmB, g, int(tx), int(ty), items, st);
+    rc = launch_wgrad<256, 4>(tmA, tmB, tmAlt, g, int(tx), int(ty), items, st);
     if (rc == MOE_B200_OK && may_split)
       launch_pdl(wgrad_reduce_kernel<256>, dim3(tx * ty * WGRAD_REDUCE_SPLIT, gy), dim3(256), 0, st,
                  g, int(tx), int(ty));
   } else {
     const unsigned ty = unsigned((n_dim + 191) / 192);
-    rc = launch_wgrad<192, 5>(tmA, tmB, g, int(tx), int(ty), items, st);
+    rc = launch_wgrad<192, 5>(tmA, tmB, tmAlt, g, int(tx), int(ty), items, st);
     if (rc == MOE_B200_OK && may_split)
       launch_pdl(wgrad_reduce_kernel<192>, dim3(tx * ty * WGRAD_REDUCE_SPLIT, gy), dim3(256), 0, st,
                  g, int(tx), int(ty));

@@ -55,6 +55,10 @@ struct RowsArgs {
   int32_t n_dim;               // valid accumulator columns over all N chunks
   int32_t n_chunks;            // ceil(n_dim / BN)
   int32_t n_groups_b1;         // groups [0, n_groups_b1) read the first B stack, the rest the second
+  int32_t a2_first_group;      // routed schedule: groups from here on read their A rows from the
+                               // token-major second A map (row = slot - a2_offsets[group]);
+                               // INT32_MAX = every group reads the slot-ordered buffer
+  const int32_t* a2_offsets;   // [G + 1] run starts (pad_offsets), used with a2_first_group
   int32_t b_fused;             // MN-major B: the maps are 4-D (64 n, k, n / 64, group) and one copy
                                // brings all BN / 64 boxes of a stage (a TMA instruction costs the
                                // issuing thread about as much as a whole stage of MMAs)
@@ -91,6 +95,8 @@ struct WgradArgs {
   __nv_bfloat16* out_extra;    // [G - n_out1, m_dim, n_dim]: the remaining groups (may be null)
   int32_t n_out1;
   float* partials;             // fp32 scratch for the partial tiles of split runs
+  int32_t alt_which;           // 0 none; 1 / 2: runs from alt_first_group on read operand A / B from
+  int32_t alt_first_group;     // the token-major alternative map, row = slot row - run start
   int32_t* item_table;         // scratch [G + 1]: first work item of every run, written by the GEMM
                                // pass for the reduction pass
   int32_t* status;

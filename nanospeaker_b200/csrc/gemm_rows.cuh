@@ -147,6 +147,7 @@ __device__ __forceinline__ float epilogue_glubwd(uint32_t taddr, int c_lo, int c
 template <int BN, int STAGES, bool B_MN, int EPI, bool GATHER_A, int OUT_BOXES = 4>
 __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
     rows_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
+                     const __grid_constant__ CUtensorMap tmA2,
                      const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmB2,
                      const __grid_constant__ CUtensorMap tmOut, const RowsArgs p) {
@@ -185,6 +186,7 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmA2);
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmB2);
     if constexpr (TMA_OUT) tma_prefetch_desc(&tmOut);
@@ -311,11 +313,21 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       uint32_t it = 0;
+      // Groups from a2_first_group on (the shared experts: every token, in token order) have no
+      // rows in the slot-ordered buffer; their A rows are the token-major source itself, row =
+      // slot - start of the group's run. The run start is fetched with the next tile's owner.
+      auto run_start_of = [&](int group) {
+        return (group >= p.a2_first_group && group >= 0) ? __ldg(p.a2_offsets + group) : 0;
+      };
       int group_next = tile_group(p, blockIdx.x, m_tiles, total_tiles);
+      int start_next = run_start_of(group_next);
       for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
         TileCoord tc = decode_tile(p, t, m_tiles, BN);
         tc.group = group_next;
+        const int a_start = start_next;
+        const bool a_alt = tc.group >= p.a2_first_group;
         group_next = tile_group(p, t + gridDim.x, m_tiles, total_tiles);
+        start_next = run_start_of(group_next);
         for (int kt = 0; kt < p.num_k; ++kt, ++it) {
           const int s = it % STAGES;
           const uint32_t use = it / STAGES;
@@ -328,7 +340,10 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
           uint8_t* sB = sA + A_STAGE_BYTES;
           mbar_expect_tx(full_bar + s, L::STAGE_BYTES);
           const int k0 = kt * BK;
-          tma_load_3d(sA, &tmA, full_bar + s, k0, tc.m_tile * BM, p.a_grouped ? tc.z : 0);
+          if (a_alt)
+            tma_load_3d(sA, &tmA2, full_bar + s, k0, tc.m_tile * BM - a_start, 0);
+          else
+            tma_load_3d(sA, &tmA, full_bar + s, k0, tc.m_tile * BM, p.a_grouped ? tc.z : 0);
           // the tile's expert lives in the first weight stack or (shared experts) the second
           const bool first = tc.group < p.n_groups_b1;
           const CUtensorMap* mb = first ? &tmB : &tmB2;

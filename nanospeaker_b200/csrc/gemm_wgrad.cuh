@@ -105,7 +105,8 @@ __device__ __forceinline__ WgradItem wgrad_item(const WgradArgs& p, const int* f
 template <int BN, int STAGES, int GATHER>  // GATHER: 0 none, 1 = A gathered, 2 = B gathered
 __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS, 1)
     wgrad_gemm_kernel(const __grid_constant__ CUtensorMap tmA,
-                      const __grid_constant__ CUtensorMap tmB, const WgradArgs p, int tiles_x,
+                      const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmAlt, const WgradArgs p, int tiles_x,
                       int tiles_y) {
   pdl_trigger();
   pdl_wait();
@@ -141,6 +142,7 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmAlt);
     for (int s = 0; s < STAGES; ++s) {
       // a gathered operand: every lane of warp 0 arrives (through its cp.async) next to the TMA
       mbar_init(full_bar + s, gather ? GATHER_WARPS * 32 + 1 : 1);
@@ -227,22 +229,30 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
           if (warp == 0 && lane == 0) {
             mbar_expect_tx(full_bar + s, (GATHER == 1 ? 0 : A_STAGE_BYTES) +
                                              (GATHER == 2 ? 0 : L::B_STAGE_BYTES));
+            // runs from alt_first_group on (the shared experts) take one operand from the
+            // token-major matrix: its row is the slot row minus the start of the run
+            const bool alt = p.alt_which != 0 && w.group >= p.alt_first_group;
+            const int r_alt = r - run_start[w.group];
+            const bool a_alt = alt && p.alt_which == 1, b_alt = alt && p.alt_which == 2;
+            const CUtensorMap* ma = a_alt ? &tmAlt : &tmA;
+            const CUtensorMap* mb = b_alt ? &tmAlt : &tmB;
+            const int ra = a_alt ? r_alt : r, rb = b_alt ? r_alt : r;
             if (GATHER != 1) {
               if (p.a_fused) {
-                tma_load_4d(sA, &tmA, full_bar + s, 0, r, m0 / 64, ga);
+                tma_load_4d(sA, ma, full_bar + s, 0, ra, m0 / 64, a_alt ? 0 : ga);
               } else {
 #pragma unroll
                 for (int i = 0; i < BM / 64; ++i)
-                  tma_load_3d(sA + i * 8192, &tmA, full_bar + s, m0 + 64 * i, r, ga);
+                  tma_load_3d(sA + i * 8192, ma, full_bar + s, m0 + 64 * i, ra, a_alt ? 0 : ga);
               }
             }
             if (GATHER != 2) {
               if (p.b_fused) {
-                tma_load_4d(sB, &tmB, full_bar + s, 0, r, n0 / 64, gb);
+                tma_load_4d(sB, mb, full_bar + s, 0, rb, n0 / 64, b_alt ? 0 : gb);
               } else {
 #pragma unroll
                 for (int jj = 0; jj < BN / 64; ++jj)
-                  tma_load_3d(sB + jj * 8192, &tmB, full_bar + s, n0 + 64 * jj, r, gb);
+                  tma_load_3d(sB + jj * 8192, mb, full_bar + s, n0 + 64 * jj, rb, b_alt ? 0 : gb);
               }
             }
           }

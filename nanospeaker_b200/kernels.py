@@ -279,13 +279,17 @@ def copy_cols(src: torch.Tensor, dst_ld: int) -> torch.Tensor:
 
 
 def up_gemm(a, w_in, expert_ids, n_post_pad, n_fixed: int, act: int, want_raw: bool,
-            gather=None, w_extra=None):
+            gather=None, w_extra=None, token_rows=None):
     """a x w_in [G, D, 2H] -> (act(g)*u [rows, H], raw [g|u] [rows, 2H] | None).
     a is slot-ordered [rows, D]; or, with gather=(sorted_ids, top_k), the token-major x [T, D] whose
     rows the kernel gathers itself (rows = len(sorted_ids)). n_fixed = S > 0 applies weight
     matrices 0..S-1 to all rows of a; outputs are then [S, rows, .]. w_extra is an optional second
-    weight stack for expert ids >= G (the shared experts on the routed schedule)."""
+    weight stack for expert ids >= G (the shared experts on the routed schedule).
+    token_rows=(x, pad_offsets): the experts of the second stack read their rows from the token-major
+    x [T, D] (row = slot - start of the expert's run) instead of from a, whose rows in those runs
+    need not have been written."""
     _need_cuda(a, w_in)
+    tok, offs = token_rows if token_rows is not None else (None, None)
     d = a.shape[1]
     xp, xn = _extra(w_extra)
     sids, top_k = gather if gather is not None else (None, 0)
@@ -298,6 +302,7 @@ def up_gemm(a, w_in, expert_ids, n_post_pad, n_fixed: int, act: int, want_raw: b
     _lib.check(_lib.load().moe_b200_up_gemm(
         a.data_ptr(), rows, d, w_in.data_ptr(), g, xp, xn, h, _lib.ptr(expert_ids),
         _lib.ptr(n_post_pad), n_fixed, _lib.ptr(sids), top_k, n_pairs, act, hid.data_ptr(), _lib.ptr(raw),
+        _lib.ptr(tok), tok.shape[0] if tok is not None else 0, _lib.ptr(offs),
         status_word(a.device).data_ptr(), _stream(a)), "moe_b200_up_gemm")
     _count(1 if rows else 0)
     return hid, raw
@@ -322,10 +327,12 @@ def down_gemm(hid, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair
 
 def dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair_w,
                     n_pairs: int, a1, act: int, want_dtw: bool, gather_top_k: int = 0,
-                    w_extra=None):
+                    w_extra=None, token_rows=None):
     """-> (da1 [.., rows, 2H], hidw [.., rows, H], dtw [n_pairs] | None). douts is slot-ordered
-    [rows, D], or with gather_top_k > 0 the token-major dOut [T, D] gathered through sorted_ids."""
+    [rows, D], or with gather_top_k > 0 the token-major dOut [T, D] gathered through sorted_ids.
+    token_rows=(dout, pad_offsets): as for up_gemm, for the rows of douts."""
     _need_cuda(douts, w_out, a1)
+    tok, offs = token_rows if token_rows is not None else (None, None)
     d = douts.shape[1]
     rows = sorted_ids.numel() if gather_top_k else douts.shape[0]
     g, h, _ = w_out.shape
@@ -337,6 +344,7 @@ def dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_i
         douts.data_ptr(), rows, d, w_out.data_ptr(), g, xp, xn, h, _lib.ptr(expert_ids),
         _lib.ptr(n_post_pad), n_fixed, _lib.ptr(sorted_ids), gather_top_k, _lib.ptr(pair_w),
         n_pairs, a1.data_ptr(), act, da1.data_ptr(), hidw.data_ptr(), _lib.ptr(dtw),
+        _lib.ptr(tok), tok.shape[0] if tok is not None else 0, _lib.ptr(offs),
         status_word(douts.device).data_ptr(), _stream(douts)), "moe_b200_dhidden_glu_bwd")
     _count(1 if rows else 0)
     return da1, hidw, dtw
@@ -358,15 +366,18 @@ def dx_gemm(da1, w_in, expert_ids, n_post_pad, n_fixed: int, w_extra=None) -> to
 
 
 def wgrad(a, b, pad_offsets, n_groups: int, ks_rows: int = 0, a_grouped: bool = False,
-          b_grouped: bool = False, gather=None, n_extra: int = 0):
+          b_grouped: bool = False, gather=None, n_extra: int = 0, token_rows=None):
     """dw[e] = a_e^T @ b_e over run e's rows -> [G, Mdim, Ndim]. Routed schedule: a [rows, Mdim],
     b [rows, Ndim] in slot order plus pad_offsets. Fixed schedule (pad_offsets None): every group
     spans all rows; a / b are [G, rows, .] when *_grouped, else shared by the groups.
     ks_rows = rows per split-K chunk (0: chosen by the library).
     gather=("a" | "b", sorted_ids, top_k): that operand is token-major [T, .] and gathered inside
     the kernel (routed schedule only).
-    n_extra > 0: the last n_extra groups are returned as a second tensor (dw, dw_extra)."""
+    n_extra > 0: the last n_extra groups are returned as a second tensor (dw, dw_extra).
+    token_rows=("a" | "b", m): the last n_extra runs read that operand from the token-major matrix m
+    (row = slot - start of the run) instead of from the slot-ordered buffer."""
     _need_cuda(a, b)
+    alt_which, alt = (0, None) if token_rows is None else (1 if token_rows[0] == "a" else 2, token_rows[1])
     import ctypes
     which, sids, top_k = 0, None, 0
     if gather is not None:
@@ -391,6 +402,7 @@ def wgrad(a, b, pad_offsets, n_groups: int, ks_rows: int = 0, a_grouped: bool = 
         a.data_ptr(), int(a_grouped), m_dim, b.data_ptr(), int(b_grouped), n_dim, rows,
         _lib.ptr(pad_offsets), n_groups, ks_rows, _lib.ptr(sids), top_k, n_pairs, which,
         dw.data_ptr(), n_first, _lib.ptr(dw_extra), partials.data_ptr(), pb.value,
+        _lib.ptr(alt), alt.shape[0] if alt is not None else 0, alt_which,
         status_word(a.device).data_ptr(), _stream(a)), "moe_b200_wgrad")
     _count(2 if rows > (ks_rows or 256) else 1)
     return (dw, dw_extra) if n_extra else dw

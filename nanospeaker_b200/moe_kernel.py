@@ -185,8 +185,10 @@ def moe_experts(
         w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
 
     if save_for_backward:
-        xs = K.permute(x, topk, sorted_ids, n_post_pad)
-        hid, a1 = K.up_gemm(xs, w_in, expert_ids, n_post_pad, 0, act, True, w_extra=w_sh_in)
+        live, tok = _routed_rows(x, w_in, w_sh_in, pad_offsets, n_post_pad)
+        xs = K.permute(x, topk, sorted_ids, live)
+        hid, a1 = K.up_gemm(xs, w_in, expert_ids, n_post_pad, 0, act, True, w_extra=w_sh_in,
+                            token_rows=tok)
     else:
         xs, a1 = x.new_empty(0), x.new_empty(0)
         hid, _ = K.up_gemm(x, w_in, expert_ids, n_post_pad, 0, act, False,
@@ -204,6 +206,19 @@ def _(x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_off
         return x.new_empty((n, d)), x.new_empty(0), x.new_empty(0)
     cap = sorted_ids.shape[0]
     return x.new_empty(x.shape), x.new_empty((cap, d)), x.new_empty((cap, w_in.shape[2]))
+
+
+def _routed_rows(src, w_in, w_sh_in, pad_offsets, n_post_pad):
+    """How far the permute has to copy, and where the shared experts read their rows from.
+    The shared experts visit every token once, in token order, and own the last runs of the slot
+    order: their slot rows would be a plain copy of the token-major matrix `src`. So the permute
+    stops at the start of the first shared run (a device scalar inside pad_offsets) and the GEMMs
+    read those runs from `src` itself. Returns (live-row count tensor for the permute,
+    token_rows argument for the GEMM wrappers)."""
+    if w_sh_in is None:
+        return n_post_pad, None
+    e_n = w_in.shape[0]
+    return pad_offsets[e_n:e_n + 1], (src, pad_offsets)
 
 
 @torch.library.custom_op("moe_b200::moe_experts_bwd", mutates_args=())
@@ -242,13 +257,16 @@ def moe_experts_bwd(
     m = n * topk
     tw = topk_w.reshape(-1).contiguous()
 
-    douts = K.permute(grad_out, topk, sorted_ids, n_post_pad)
+    live, tok = _routed_rows(grad_out, w_in, w_sh_in, pad_offsets, n_post_pad)
+    douts = K.permute(grad_out, topk, sorted_ids, live)
     da1, hidw, dtw = K.dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m,
-                                       a1, act, True, w_extra=w_sh_out)
+                                       a1, act, True, w_extra=w_sh_out, token_rows=tok)
     ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
     dx = K.combine(ydx, inv_ids, n, topk)
-    g_in = K.wgrad(xs, da1, pad_offsets, e_n + s_n, n_extra=s_n)
-    g_out = K.wgrad(hidw, douts, pad_offsets, e_n + s_n, n_extra=s_n)
+    g_in = K.wgrad(xs, da1, pad_offsets, e_n + s_n, n_extra=s_n,
+                   token_rows=("a", x) if s_n else None)
+    g_out = K.wgrad(hidw, douts, pad_offsets, e_n + s_n, n_extra=s_n,
+                    token_rows=("b", grad_out) if s_n else None)
     if s_n:
         (dw_in, dw_sh_in), (dw_out, dw_sh_out) = g_in, g_out
     else:
@@ -370,8 +388,9 @@ def moe_block(
     tw = w_all.reshape(-1)
     m = n * ks
     if save_for_backward:
-        xs = K.permute(x, ks, sids, npp)
-        hid, a1 = K.up_gemm(xs, w_in, eids, npp, 0, act, True, w_extra=w_sh_in)
+        live, tok = _routed_rows(x, w_in, w_sh_in, offs, npp)
+        xs = K.permute(x, ks, sids, live)
+        hid, a1 = K.up_gemm(xs, w_in, eids, npp, 0, act, True, w_extra=w_sh_in, token_rows=tok)
     else:
         xs, a1 = x.new_empty(0), x.new_empty(0)
         hid, _ = K.up_gemm(x, w_in, eids, npp, 0, act, False, gather=(sids, ks), w_extra=w_sh_in)
@@ -440,9 +459,10 @@ def moe_block_bwd(
     m = n * ks
     tw = w_all.reshape(-1)
 
-    douts = K.permute(grad_out, ks, sorted_ids, n_post_pad)
+    live, tok = _routed_rows(grad_out, w_in, w_sh_in, pad_offsets, n_post_pad)
+    douts = K.permute(grad_out, ks, sorted_ids, live)
     da1, hidw, dtw = K.dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m,
-                                       a1, act, True, w_extra=w_sh_out)
+                                       a1, act, True, w_extra=w_sh_out, token_rows=tok)
     # Everything below only depends on the two launches above and meets again in the combine. Three
     # branches on three streams: the small router kernels hide behind the expert GEMMs, and the
     # tail of one persistent GEMM (SMs that ran out of tiles) is filled by the next one's CTAs.
@@ -452,10 +472,12 @@ def moe_block_bwd(
         side_out = side_router = main
     side_out.wait_stream(main)
     side_router.wait_stream(main)
-    g_in = K.wgrad(xs, da1, pad_offsets, e_n + s_n, n_extra=s_n)
+    g_in = K.wgrad(xs, da1, pad_offsets, e_n + s_n, n_extra=s_n,
+                   token_rows=("a", x) if s_n else None)
     ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
     with torch.cuda.stream(side_out):
-        g_out = K.wgrad(hidw, douts, pad_offsets, e_n + s_n, n_extra=s_n)
+        g_out = K.wgrad(hidw, douts, pad_offsets, e_n + s_n, n_extra=s_n,
+                        token_rows=("b", grad_out) if s_n else None)
     with torch.cuda.stream(side_router):
         # router: d(logits) from d(topk_w) and the balance loss, then the two router GEMMs
         d_aux = None if grad_aux is None else grad_aux.to(torch.float32).reshape(1)

@@ -231,3 +231,52 @@ def test_entry_points_reject_bad_arguments():
         K().up_gemm(torch.randn(128, 64, device="cuda").bfloat16(), w, None, None, 1, 0, False)
     with pytest.raises(RuntimeError, match="CUDA"):
         K().router_topk(torch.randn(4, 8), 2, True, False, False)   # CPU tensor: no fallback
+
+
+@pytest.mark.parametrize("T,E,S,k,D", [(300, 8, 2, 2, 576), (129, 4, 1, 2, 96), (2048, 76, 2, 6, 576)])
+def test_shared_experts_read_token_rows_in_place(T, E, S, k, D):
+    """The shared experts' runs are the token-major matrix itself: with token_rows the up GEMM, the
+    dHidden GEMM and both weight gradients give the same bits as on fully permuted buffers, although
+    the permute stopped at the first shared run (rows of those runs hold garbage). T not a multiple
+    of 128 makes the last tile of a shared run read past the matrix (zero rows)."""
+    H, ks = 128, k + S
+    torch.manual_seed(T + S)
+    idx = torch.cat([torch.randn(T, E).topk(k, -1).indices,
+                     torch.arange(E, E + S).expand(T, S)], 1)
+    sids, eids, offs, counts, npp, inv = [t.cuda() for t in O.dispatch(idx, E + S)]
+    g = lambda *shape, s=1.0: (torch.randn(*shape, device="cuda") * s).bfloat16()
+    x, dout = g(T, D), g(T, D)
+    w_in, w_sh_in = g(E, D, 2 * H, s=D ** -0.5), g(S, D, 2 * H, s=D ** -0.5)
+    w_out, w_sh_out = g(E, H, D, s=H ** -0.5), g(S, H, D, s=H ** -0.5)
+    tw = torch.rand(T * ks, device="cuda").bfloat16()
+    nl, M = int(npp), T * ks
+    first_shared = offs[E:E + 1]
+    assert int(first_shared) < nl
+
+    def poisoned(src):
+        part = K().permute(src, ks, sids, first_shared)
+        part[int(first_shared):] = float("nan")       # whatever the allocator left there
+        return part
+
+    xs_full, douts_full = K().permute(x, ks, sids, npp), K().permute(dout, ks, sids, npp)
+    hid0, a10 = K().up_gemm(xs_full, w_in, eids, npp, 0, 0, True, w_extra=w_sh_in)
+    hid1, a11 = K().up_gemm(poisoned(x), w_in, eids, npp, 0, 0, True, w_extra=w_sh_in,
+                            token_rows=(x, offs))
+    assert torch.equal(hid0[:nl], hid1[:nl]) and torch.equal(a10[:nl], a11[:nl])
+
+    args = (w_out, eids, npp, 0, sids, tw, M, a10, 0, True)
+    ref = K().dhidden_glu_bwd(douts_full, *args, w_extra=w_sh_out)
+    got = K().dhidden_glu_bwd(poisoned(dout), *args, w_extra=w_sh_out, token_rows=(dout, offs))
+    for a, b in zip(ref, got):
+        assert torch.equal(a[:nl] if a.shape[0] != M else a, b[:nl] if b.shape[0] != M else b)
+
+    da1, hidw = ref[0], ref[1]
+    for ks_rows in (0, 64):
+        ref_in = K().wgrad(xs_full, da1, offs, E + S, ks_rows, n_extra=S)
+        got_in = K().wgrad(poisoned(x), da1, offs, E + S, ks_rows, n_extra=S, token_rows=("a", x))
+        ref_out = K().wgrad(hidw, douts_full, offs, E + S, ks_rows, n_extra=S)
+        got_out = K().wgrad(hidw, poisoned(dout), offs, E + S, ks_rows, n_extra=S,
+                            token_rows=("b", dout))
+        for a, b in zip(ref_in + ref_out, got_in + got_out):
+            assert torch.equal(a, b)
+    K().check_status("cuda")
