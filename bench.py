@@ -31,7 +31,12 @@ if ROOT not in sys.path:
 
 D_MODEL, N_EXPERTS, TOP_K, N_SHARED, D_FF, D_HIDDEN = 576, 76, 6, 2, 192, 128
 TOKENS = 16384
-BIAS_STD = 0.27          # logit-bias spread that gives load CV ~ 1 with router W ~ N(0, 0.02)
+# Per-expert logit bias N(0, std), seed 1. With router W ~ N(0, 0.02) the logits have std 0.48, so
+# std 0.27 gives the expert-load CV ~ 1 that the workload describes (the default, and the headline);
+# the literal std 1.5 gives CV ~ 3 with more than half of the experts empty (--skew literal1.5).
+SKEWS = {"cv1": 0.27, "literal1.5": 1.5}
+SKEW_NAME = "cv1"
+BIAS_STD = SKEWS[SKEW_NAME]
 N_INPUT_SETS = 8         # x / dOut pairs cycled through so successive steps do not hit L2
 METRIC = "MoE-block tokens/s (fwd+bwd)"
 
@@ -183,7 +188,7 @@ def workload_config(n_gpus, tokens_per_gpu=TOKENS):
         "workload": "BASELINE config 2: dropless MoE block fwd+bwd, T=16384 (8x2048) per GPU, "
                     "d_model 576, 76 routed + 2 shared SwiGLU experts, d_expert 128, top-6",
         "tokens_per_gpu": tokens_per_gpu, "global_tokens": tokens_per_gpu * n_gpus,
-        "skew": f"cv1: per-expert logit bias N(0,{BIAS_STD}), seed 1",
+        "skew": f"{SKEW_NAME}: per-expert logit bias N(0,{BIAS_STD}), seed 1",
         "parallelism": f"token-sharded replicas x{n_gpus}, no data-path collective",
         "l2": f"{N_INPUT_SETS} input/dOut sets cycled (302 MB) and ~1 GB of intermediates per "
               "step, both beyond the 126 MB L2; no explicit flush",
@@ -621,7 +626,7 @@ def run_ours(args):
 
 def run_ep_workload(args):
     """BASELINE config 5: expert-parallel forward + backward. 76 routed experts partitioned over the
-    ranks, shared experts and router replicated, T=65536 tokens per GPU, uniform routing. One rank
+    ranks, shared experts and router replicated, T=65536 tokens per GPU, uniform or hot-spot routing (--routing). One rank
     per GPU under torchrun; eager launches (the split sizes of the all-to-all are read on the
     host); CUDA events, max over ranks."""
     import torch.distributed as dist
@@ -643,6 +648,12 @@ def run_ep_workload(args):
         m.W_sh_in.copy_(w["W_sh_in"])
         m.W_sh_out.copy_(w["W_sh_out"])
     m = m.to(dev).eval()           # eval: top-k softmax router, no balance loss in this workload
+    if args.routing == "hotspot":
+        # +1.14 on the logits of experts 0..3 gives them 0.50 of all assignments with this router
+        # initialisation (1.10 -> 0.487, 1.15 -> 0.506); all four belong to rank 0
+        hot = torch.zeros(N_EXPERTS, device=dev)
+        hot[:4] = 1.14
+        m.router.logit_bias = hot
     lo, hi = EP.expert_partition(N_EXPERTS, world)[rank]
     w_in = w["W_in"][lo:hi].bfloat16().to(dev).requires_grad_(True)
     w_out = w["W_out"][lo:hi].bfloat16().to(dev).requires_grad_(True)
@@ -682,7 +693,7 @@ def run_ep_workload(args):
             "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "BASELINE config 5: experts partitioned over the ranks, "
-                                   f"T={T} tokens per GPU, uniform routing, forward + backward, "
+                                   f"T={T} tokens per GPU, {args.routing} routing, forward + backward, "
                                    "dispatch / combine by NCCL all-to-all (first version)"}}))
     dist.barrier()
     dist.destroy_process_group()
@@ -830,7 +841,14 @@ def main():
                          "the forward-only workloads of the block's other callers; sublayer = "
                          "x + ffn(rmsnorm(x)) forward + backward at T=16384, fused node against "
                          "norm, block and add as separate steps")
+    ap.add_argument("--skew", default="cv1", choices=sorted(SKEWS),
+                    help="train workload: spread of the per-expert routing bias (see SKEWS)")
+    ap.add_argument("--routing", default="uniform", choices=["uniform", "hotspot"],
+                    help="ep workload: no routing bias, or a bias on experts 0-3 that sends half "
+                         "of all assignments to them (all four live on rank 0)")
     args = ap.parse_args()
+    global SKEW_NAME, BIAS_STD
+    SKEW_NAME, BIAS_STD = args.skew, SKEWS[args.skew]
     if args.workload == "ep":
         run_ep_workload(args)
     elif args.workload != "train":
