@@ -163,7 +163,10 @@ int moe_b200_dispatch_static(const int64_t* topk_idx, int64_t n_pairs, int32_t n
 /* Token permute: xs[slot, :] = x[sorted_ids[slot] / top_k, :], zero rows in pad slots, for slots
  * below n_post_pad. Replaces x.index_select(0, token_idx) (src/model/moe.py:397) and the gather
  * loads inside _gemm1_kernel (src/model/moe_kernel.py:295-305). x [n_tokens, d_model],
- * xs [l_cap, d_model]. */
+ * xs [l_cap, d_model]. n_post_pad points at any device int32 that holds the number of slot rows to
+ * fill (a multiple of 8): the dispatch's n_post_pad for all of them, or pad_offsets + E to stop at
+ * the first shared expert's run when the GEMMs read those runs from x in place (a_tokens of
+ * moe_b200_up_gemm). */
 int moe_b200_permute(const void* x, int64_t n_tokens, int32_t d_model, int32_t top_k,
                      const int32_t* sorted_ids, const int32_t* n_post_pad, int64_t l_cap, void* xs,
                      void* stream);
