@@ -172,6 +172,233 @@ __global__ void __launch_bounds__(WARPS * 32)
   }
 }
 
+// ---------------------------------------------------------------- four lanes per token
+// The same routine for the common shapes (at most 96 experts, top_k <= 8), with four lanes per
+// token instead of a warp: lane q of a group holds experts [q * EPL, (q + 1) * EPL) in registers,
+// so a warp routes eight tokens at once and the cross-lane steps shrink to two shuffle rounds. The
+// warp-per-token kernel above spends 611 warp instructions per token on E = 76 (three values per
+// lane, every reduction five shuffles deep, most lanes idle in the top-k rounds) and is bound by
+// instruction issue; this one needs about a quarter of that.
+// Selection rule, softmax arithmetic and outputs are those of router_fused_kernel; sums run in a
+// different order, so weights may differ in the last fp32 bit before they are rounded to bf16.
+constexpr int RF4_THREADS = 512;
+constexpr int RF4_TOKENS = RF4_THREADS / 4;   // tokens per block and pass
+constexpr int RF4_MAX_TOPK = 8;
+
+__device__ __forceinline__ float key_float(uint32_t k) {   // inverse of float_key
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+}
+
+template <int EPL, bool COLSUM>
+__global__ void __launch_bounds__(RF4_THREADS)
+    router_fused4_kernel(const __nv_bfloat16* __restrict__ logits, int ld,
+                         const float* __restrict__ bias, int64_t n_tokens, int n_experts, int top_k,
+                         int n_shared, int normalize, int full_softmax,
+                         __nv_bfloat16* __restrict__ w_all, int64_t* __restrict__ idx_all,
+                         float* __restrict__ colsum, int tokens_per_block,
+                         int32_t* __restrict__ block_hist, int32_t* __restrict__ sorted_ids,
+                         int64_t l_cap) {
+  pdl_trigger();
+  pdl_wait();
+  static_assert(EPL % 8 == 0, "a lane loads its experts as 16-byte pieces");
+  __shared__ float cs[RF4_THREADS / 32][4 * EPL];
+  __shared__ int32_t hist[MAX_EXPERTS];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int q = lane & 3, sub = lane >> 2;
+  const int e0 = q * EPL;
+  const bool chunked = tokens_per_block > 0;
+  if (chunked) {
+    for (int e = threadIdx.x; e < n_experts + n_shared; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+  }
+  const int kS = top_k + n_shared;
+  const bool need_full = full_softmax || !normalize;
+
+  float b[EPL];
+  [[maybe_unused]] float csum[EPL];
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int e = e0 + i;
+    b[i] = (bias != nullptr && e < n_experts) ? bias[e] : 0.f;
+    if constexpr (COLSUM) csum[i] = 0.f;
+  }
+
+  // block-uniform loop bounds: every warp makes the same number of passes
+  const int64_t t_lo = chunked ? int64_t(blockIdx.x) * tokens_per_block
+                               : int64_t(blockIdx.x) * RF4_TOKENS;
+  const int64_t t_hi = chunked ? min(t_lo + tokens_per_block, n_tokens) : n_tokens;
+  const int64_t t_step = chunked ? RF4_TOKENS : int64_t(gridDim.x) * RF4_TOKENS;
+  for (int64_t base = t_lo; base < t_hi; base += t_step) {
+    const int64_t t = base + warp * 8 + sub;
+    const bool valid = t < t_hi;
+    const int64_t tc = valid ? t : t_hi - 1;   // lanes past the end repeat the last token, write nothing
+    uint32_t key[EPL];   // first the values (as float bits), then the order-preserving keys
+    float mx = -CUDART_INF_F;
+    {
+      const uint4* rp = reinterpret_cast<const uint4*>(logits + tc * ld + e0);
+#pragma unroll
+      for (int c = 0; c < EPL / 8; ++c) {
+        const uint4 r = __ldg(rp + c);
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[h]));
+          const int i = c * 8 + 2 * h;
+          const float v0 = (e0 + i < n_experts) ? f.x + b[i] : -CUDART_INF_F;
+          const float v1 = (e0 + i + 1 < n_experts) ? f.y + b[i + 1] : -CUDART_INF_F;
+          key[i] = __float_as_uint(v0);
+          key[i + 1] = __float_as_uint(v1);
+          mx = fmaxf(mx, fmaxf(v0, v1));
+        }
+      }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+
+    float denom = 0.f;
+    if (need_full) {
+      float ex[EPL];
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        ex[i] = (e0 + i < n_experts) ? expf(__uint_as_float(key[i]) - mx) : 0.f;
+        denom += ex[i];
+      }
+      denom += __shfl_xor_sync(0xffffffffu, denom, 1);
+      denom += __shfl_xor_sync(0xffffffffu, denom, 2);
+      if constexpr (COLSUM) {
+        const float inv = valid ? 1.f / denom : 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) csum[i] += ex[i] * inv;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const uint32_t fk = float_key(__uint_as_float(key[i]));
+      key[i] = (e0 + i < n_experts) ? (fk == 0u ? 1u : fk) : 0u;
+    }
+
+    // top-k: local best (lowest index among equal keys), then two rounds across the four lanes
+    float sv[RF4_MAX_TOPK];
+    int si[RF4_MAX_TOPK];
+#pragma unroll
+    for (int j = 0; j < RF4_MAX_TOPK; ++j) {
+      sv[j] = 0.f;
+      si[j] = 0;
+      if (j < top_k) {
+        uint32_t bk = 0u;
+        int be = 0x7FFFFFFF;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i)
+          if (key[i] > bk) {
+            bk = key[i];
+            be = e0 + i;
+          }
+#pragma unroll
+        for (int o = 1; o <= 2; o <<= 1) {
+          const uint32_t ok = __shfl_xor_sync(0xffffffffu, bk, o);
+          const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+          if (ok > bk || (ok == bk && oe < be)) {
+            bk = ok;
+            be = oe;
+          }
+        }
+        const int slot = be - e0;   // only the owner's slot is in range
+#pragma unroll
+        for (int i = 0; i < EPL; ++i)
+          if (i == slot) key[i] = 0u;
+        sv[j] = key_float(bk);
+        si[j] = be;
+      }
+    }
+
+    // weights of the selected experts (every lane of the group computes all of them)
+    float p[RF4_MAX_TOPK];
+    if (need_full) {
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < RF4_MAX_TOPK; ++j) {
+        p[j] = j < top_k ? expf(sv[j] - mx) / denom : 0.f;
+        s += p[j];
+      }
+      if (normalize && top_k > 1 && full_softmax) {
+#pragma unroll
+        for (int j = 0; j < RF4_MAX_TOPK; ++j) p[j] = p[j] / s;
+      }
+    } else {
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < RF4_MAX_TOPK; ++j) {
+        p[j] = j < top_k ? expf(sv[j] - sv[0]) : 0.f;
+        s += p[j];
+      }
+#pragma unroll
+      for (int j = 0; j < RF4_MAX_TOPK; ++j) p[j] = p[j] / s;
+    }
+    if (valid) {
+#pragma unroll
+      for (int j = 0; j < RF4_MAX_TOPK; ++j)
+        if (j < top_k && (j & 3) == q) {
+          w_all[t * kS + j] = __float2bfloat16(p[j]);
+          idx_all[t * kS + j] = si[j];
+          if (chunked) atomicAdd(&hist[si[j]], 1);
+        }
+      for (int jj = top_k + q; jj < kS; jj += 4) {   // the shared experts: every token, weight 1
+        w_all[t * kS + jj] = __float2bfloat16(1.f);
+        idx_all[t * kS + jj] = n_experts + (jj - top_k);
+      }
+    }
+  }
+
+  if constexpr (COLSUM) {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      float s = csum[i];
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      s += __shfl_xor_sync(0xffffffffu, s, 8);
+      s += __shfl_xor_sync(0xffffffffu, s, 16);
+      if (lane < 4) cs[warp][e0 + i] = s;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < RF4_THREADS / 32; ++w) s += cs[w][e];
+      atomicAdd(colsum + e, s);
+    }
+  }
+  if (chunked) {
+    __syncthreads();
+    const int32_t mine = int32_t(t_hi > t_lo ? t_hi - t_lo : 0);  // every token visits every shared expert
+    for (int e = threadIdx.x; e < n_experts + n_shared; e += blockDim.x)
+      block_hist[int64_t(e) * gridDim.x + blockIdx.x] = e < n_experts ? hist[e] : mine;
+    // sentinel fill: each block paints an equal slice of [0, l_cap)
+    const int64_t n_pairs = n_tokens * kS;
+    const int64_t per = (l_cap + gridDim.x - 1) / gridDim.x;
+    const int64_t lo = per * blockIdx.x;
+    const int64_t hi = lo + per < l_cap ? lo + per : l_cap;
+    for (int64_t sl = lo + threadIdx.x; sl < hi; sl += blockDim.x) sorted_ids[sl] = int32_t(n_pairs);
+  }
+}
+
+// Whether the four-lane kernel covers a call, and with how many experts per lane (0 = no).
+static int rf4_experts_per_lane(const void* logits, int ld, int n_experts, int top_k) {
+  if (top_k > RF4_MAX_TOPK || ld % 8 != 0 || (reinterpret_cast<uintptr_t>(logits) & 15u) != 0) return 0;
+  if (n_experts <= 64 && ld >= 64) return 16;
+  if (n_experts <= 96 && ld >= 96) return 24;
+  return 0;
+}
+
+template <typename... Args>
+static void launch_rf4(int epl, bool want_colsum, unsigned grid, cudaStream_t st, Args... args) {
+  if (epl == 16) {
+    if (want_colsum) launch_pdl(router_fused4_kernel<16, true>, dim3(grid), dim3(RF4_THREADS), 0, st, args...);
+    else launch_pdl(router_fused4_kernel<16, false>, dim3(grid), dim3(RF4_THREADS), 0, st, args...);
+  } else {
+    if (want_colsum) launch_pdl(router_fused4_kernel<24, true>, dim3(grid), dim3(RF4_THREADS), 0, st, args...);
+    else launch_pdl(router_fused4_kernel<24, false>, dim3(grid), dim3(RF4_THREADS), 0, st, args...);
+  }
+}
+
 // d(logits) as bf16 [T, ld_out] (columns >= n_experts zero) from d(w_all) (first top_k columns of
 // [T, top_k + n_shared], activation dtype) and the balance loss's gradient:
 //   aux = aux_scale_T * sum_e counts[e] / sum(counts) * colsum[e]
@@ -352,6 +579,12 @@ int launch_router_fused_chunked(const __nv_bfloat16* logits, int ld, const float
                                 int64_t* idx_all, float* colsum, int tokens_per_block, int n_blocks,
                                 int32_t* block_hist, int32_t* sorted_ids, int64_t l_cap,
                                 cudaStream_t st) {
+  if (const int epl = rf4_experts_per_lane(logits, ld, n_experts, top_k)) {
+    launch_rf4(epl, full_softmax && colsum != nullptr, unsigned(n_blocks), st, logits, ld, bias,
+               n_tokens, n_experts, top_k, n_shared, normalize, full_softmax, w_all, idx_all, colsum,
+               tokens_per_block, block_hist, sorted_ids, l_cap);
+    return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+  }
 #define LAUNCH(NS)                                                                              \
   launch_pdl(router_fused_kernel<NS, RF_CHUNK_WARPS>, dim3(n_blocks), dim3(RF_CHUNK_WARPS * 32), 0, \
              st, logits, ld, bias, n_tokens, n_experts, top_k, n_shared, normalize, full_softmax,   \
@@ -387,6 +620,14 @@ int moe_b200_router_fused(const void* logits, int32_t ld, const float* bias, int
   const unsigned grid = rf_grid(n_tokens, (full_softmax && colsum) ? 4 : 16);
   const __nv_bfloat16* lg = static_cast<const __nv_bfloat16*>(logits);
   __nv_bfloat16* w = static_cast<__nv_bfloat16*>(w_all);
+  if (const int epl = rf4_experts_per_lane(logits, ld, n_experts, top_k)) {
+    int64_t blocks = (n_tokens + RF4_TOKENS - 1) / RF4_TOKENS;
+    if (blocks > 148 * 2) blocks = 148 * 2;
+    launch_rf4(epl, full_softmax && colsum != nullptr, unsigned(blocks), st, lg, ld, bias, n_tokens,
+               n_experts, top_k, n_shared, normalize, full_softmax, w, idx_all, colsum, 0,
+               static_cast<int32_t*>(nullptr), static_cast<int32_t*>(nullptr), int64_t(0));
+    return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+  }
 #define LAUNCH(NS)                                                                          \
   launch_pdl(router_fused_kernel<NS, RF_WARPS>, dim3(grid), dim3(RF_WARPS * 32), 0, st, lg, ld,    \
              bias, n_tokens, n_experts, top_k, n_shared, normalize, full_softmax, w, idx_all,      \
