@@ -1,7 +1,7 @@
 """Decode-shaped use of the MoE block: a stack of blocks on a small, fixed batch of tokens (one
 token per sequence), forward only, replayed from one CUDA graph.
 
-At T = 64 every expert sees a handful of rows and each block's ten launches take a few
+At T = 64 every expert sees a handful of rows and each block's launches take a few
 microseconds: the cost is launch latency, not arithmetic, so the whole stack is captured once and
 replayed. The caller loop this stands for is `generate` -> `Block.forward` -> `MoEBlock.forward`
 with T = batch size in eval mode (src/model/nanospeaker.py:254-269, 165-169); attention, norms and
@@ -30,11 +30,36 @@ class StackedMoEDecoder:
         for b in self.blocks:
             b.eval()
         self._graphs = {}
+        self._consts = {}
+
+    def _fast_args(self, b: MoEBlock, x: torch.Tensor):
+        """Per-block constants of the kernel path (weights are fixed while decoding): the padded
+        router weight and the weights in x.dtype, built on first use. None when the block's
+        kernels decline this input (then the block's own forward runs)."""
+        if not b._use_kernel(x):
+            return None
+        key = (id(b), x.dtype, x.device)
+        if key not in self._consts:
+            from . import moe_kernel as MK
+            cast = lambda t: None if t is None else t.detach().to(x.dtype).contiguous()
+            bias = b.router.logit_bias
+            self._consts[key] = (
+                MK.pad_router_weight(b.router.W.detach(), x.dtype),
+                None if bias is None else bias.detach().to(torch.float32).contiguous(),
+                cast(b.W_in), cast(b.W_out), cast(b.W_sh_in), cast(b.W_sh_out),
+                b.n_experts, b.router.top_k, bool(b.router.normalize_weights), b._kernel_act)
+        return self._consts[key]
 
     @torch.no_grad()
     def eager(self, x: torch.Tensor) -> torch.Tensor:
+        """x <- x + block(x) through the stack. On the kernel path a block is six launches: the
+        residual is added inside the combine, the padded router weight is kept between steps,
+        and the per-call bookkeeping of MoEBlock.forward (expert_counts, aux_loss) is skipped."""
+        from . import moe_kernel as MK
+        x = x.contiguous()
         for b in self.blocks:
-            x = x + b(x)
+            args = self._fast_args(b, x)
+            x = x + b(x) if args is None else MK.moe_block_inference(x, *args, residual=x)
         return x
 
     @torch.no_grad()

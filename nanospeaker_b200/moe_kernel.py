@@ -565,6 +565,33 @@ def fused_moe_block(x, router, w_in, w_out, w_sh_in, w_sh_out, activation, full_
     return res[0], res[1], res[2]
 
 
+def pad_router_weight(router_w: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """router.W [D, E] as the [1, D, ld] zero-padded operand of the logits GEMM (what moe_block
+    builds on every call; an inference loop with fixed weights builds it once)."""
+    return K.copy_cols(router_w.to(dtype).contiguous(), _router_ld(router_w.shape[1])).unsqueeze(0)
+
+
+@torch.no_grad()
+def moe_block_inference(x, router_w_padded, logit_bias, w_in, w_out, w_sh_in, w_sh_out,
+                        n_experts: int, top_k: int, normalize: bool, activation: str,
+                        residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Forward of the whole block for a caller that wants nothing but `out` (+ residual): the
+    launches of moe_block's inference branch without its per-call extras (the padded copy of the
+    router weight, the counts tensor, the zero balance loss). Six launches: logits GEMM, router
+    top-k, dispatch, up/gate GEMM on gathered rows, down GEMM, combine (the residual rides in its
+    fp32 sum). x [T, D] bf16 contiguous; weights already in x.dtype."""
+    act = _act_id(activation)
+    n, _ = x.shape
+    s_n = 0 if w_sh_in is None else w_sh_in.shape[0]
+    ks = top_k + s_n
+    logits = K.down_gemm(x, router_w_padded, None, None, 1, None, None, 0)[0]
+    w_all, _, _, sids, eids, _, _, npp, inv = K.router_dispatch(
+        logits, logit_bias, n_experts, top_k, s_n, normalize, False)
+    hid, _ = K.up_gemm(x, w_in, eids, npp, 0, act, False, gather=(sids, ks), w_extra=w_sh_in)
+    y = K.down_gemm(hid, w_out, eids, npp, 0, sids, w_all.reshape(-1), n * ks, w_extra=w_sh_out)
+    return K.combine(y, inv, n, ks, residual)
+
+
 # ------------------------------------------------------------------------------- entry point
 def fused_moe_forward(x, w_in, w_out, topk_w, topk_idx, b_in, b_out, activation,
                       w_sh_in=None, w_sh_out=None):

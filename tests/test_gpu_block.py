@@ -362,5 +362,14 @@ def test_stacked_decoder_graph_replay_equals_eager_stack():
         want = stack.eager(x)
         got = stack.step(x)
         assert torch.equal(got, want)
+        # the runner's six-launch block (residual inside the combine's fp32 sum, cached padded
+        # router weight) against the blocks' own forward chained with a bf16 add
+        # (block by block on the same input: chained, a rounding difference may flip a routing
+        # decision further down the stack)
+        from nanospeaker_b200 import moe_kernel as MK
+        with torch.no_grad():
+            for b in blocks:
+                fast = MK.moe_block_inference(x, *stack._fast_args(b, x), residual=x)
+                assert rel_l2(fast.float(), (x + b(x)).float()) < 4e-3
     from nanospeaker_b200 import kernels
     kernels.check_status("cuda")
