@@ -232,23 +232,29 @@ int moe_b200_rmsnorm_bwd(const void* dh, const void* x, const float* rstd, const
  * (shared experts: every token once, in token order) then read row `slot - pad_offsets[group]` of
  * a_tokens instead of row `slot` of a, so their rows of a need not have been written at all (see
  * moe_b200_permute: pass pad_offsets + n_groups as its live-row count). Rows past n_tokens read as
- * zeros. */
+ * zeros.
+ * bias (may be NULL; routed schedule): b_in [n_groups, 2*d_hidden] in the activation dtype, added
+ * to [g | u] before the GLU (src/model/moe_kernel.py:311-313); raw then holds the biased values.
+ * The groups of the second weight stack have no bias. */
 int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w_in,
                      int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_hidden, const int32_t* expert_ids,
                      const int32_t* n_post_pad, int32_t n_fixed_groups,
                      const int32_t* sorted_ids, int32_t gather_top_k, int64_t n_pairs,
                      int32_t activation, void* hid, void* raw, const void* a_tokens,
-                     int64_t n_tokens, const int32_t* pad_offsets, int32_t* status, void* stream);
+                     int64_t n_tokens, const int32_t* pad_offsets, const void* bias,
+                     int32_t* status, void* stream);
 
 /* Down GEMM with the router weight fused: y[row] = (hid[row] @ w_out[e]) * pair_w[sorted_ids[row]]
  * (w_out [n_groups, k_dim, d_model]; weight 1 when pair_w is NULL). With fixed groups hid is
  * [S, rows, k_dim]. Replaces the forward use of _gemm2_kernel
- * (src/model/moe_kernel.py:339-402, 603-613). */
+ * (src/model/moe_kernel.py:339-402, 603-613). 
+ * bias (may be NULL; routed schedule): b_out [n_groups, d_model], added before the weight scale
+ * (src/model/moe_kernel.py:395-399); the groups of the second weight stack have none. */
 int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void* w_out,
                        int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_model, const int32_t* expert_ids,
                        const int32_t* n_post_pad, int32_t n_fixed_groups,
                        const int32_t* sorted_ids, const void* pair_w, int64_t n_pairs, void* y,
-                       int32_t* status, void* stream);
+                       const void* bias, int32_t* status, void* stream);
 
 /* Backward through the down GEMM and the GLU in one kernel: G = douts[row] @ w_out[e]^T, then with
  * [g | u] = a1[row] and w = pair_w[pair]:  dtw[pair] = <G, act(g)*u>,

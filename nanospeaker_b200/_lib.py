@@ -60,11 +60,11 @@ SIGNATURES = {
     "moe_b200_up_gemm": (
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,
-         _c_i32, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp]),
+         _c_i32, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp]),
     "moe_b200_down_gemm": (
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,
-         _c_vp, _c_i64, _c_vp, _c_vp, _c_vp]),
+         _c_vp, _c_i64, _c_vp, _c_vp, _c_vp, _c_vp]),
     "moe_b200_dhidden_glu_bwd": (
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,

@@ -223,8 +223,11 @@ int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w
                      const int32_t* n_post_pad, int32_t n_fixed_groups,
                      const int32_t* sorted_ids, int32_t gather_top_k, int64_t n_pairs,
                      int32_t activation, void* hid, void* raw, const void* a_tokens,
-                     int64_t n_tokens, const int32_t* pad_offsets, int32_t* status, void* stream) {
+                     int64_t n_tokens, const int32_t* pad_offsets, const void* bias,
+                     int32_t* status, void* stream) {
   CHECK_SCHED();
+  if (bias && (n_fixed_groups > 0 || (reinterpret_cast<uintptr_t>(bias) & 15u) != 0))
+    return n_fixed_groups > 0 ? MOE_B200_ERR_SHAPE : MOE_B200_ERR_ALIGN;
   if (d_hidden != 128 || d_model % 8 != 0 || d_model < 64) return MOE_B200_ERR_UNSUPPORTED;
   if (activation < 0 || activation > 4) return MOE_B200_ERR_UNSUPPORTED;
   if (!a || !w_in || !hid) return MOE_B200_ERR_NULL;
@@ -255,6 +258,7 @@ int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w
   g.out2 = static_cast<__nv_bfloat16*>(raw);
   g.out2_gstride = rows * int64_t(2 * d_hidden);
   g.act = activation;
+  g.bias = static_cast<const __nv_bfloat16*>(bias);
   g.n_groups_b1 = n_extra > 0 ? n_groups : INT32_MAX;
   g.sorted_ids = sorted_ids;
   g.n_pairs = int32_t(n_pairs);
@@ -276,8 +280,10 @@ int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void*
                        int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_model, const int32_t* expert_ids,
                        const int32_t* n_post_pad, int32_t n_fixed_groups,
                        const int32_t* sorted_ids, const void* pair_w, int64_t n_pairs, void* y,
-                       int32_t* status, void* stream) {
+                       const void* bias, int32_t* status, void* stream) {
   CHECK_SCHED();
+  if (bias && (n_fixed_groups > 0 || (reinterpret_cast<uintptr_t>(bias) & 15u) != 0))
+    return n_fixed_groups > 0 ? MOE_B200_ERR_SHAPE : MOE_B200_ERR_ALIGN;
   if (k_dim % 8 != 0 || k_dim < 64 || d_model % 32 != 0) return MOE_B200_ERR_UNSUPPORTED;
   if (!hid || !w_out || !y) return MOE_B200_ERR_NULL;
   if (pair_w && n_fixed_groups == 0 && !sorted_ids) return MOE_B200_ERR_NULL;
@@ -302,6 +308,7 @@ int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void*
   g.sorted_ids = sorted_ids;
   g.n_pairs = int32_t(n_pairs);
   g.pair_w = static_cast<const __nv_bfloat16*>(pair_w);
+  g.bias = static_cast<const __nv_bfloat16*>(bias);
   g.out = static_cast<__nv_bfloat16*>(y);
   g.ld_out = d_model;
   g.out_gstride = rows * int64_t(d_model);

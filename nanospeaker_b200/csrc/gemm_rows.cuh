@@ -53,14 +53,15 @@ struct TileCoord {
 
 // t -> (group slice z, 128-row block, N chunk); N chunks of one row block are adjacent so its A
 // tile is still in L2 for the next chunk.
-__device__ __forceinline__ TileCoord decode_tile(const RowsArgs& p, int t, int m_tiles, int bn) {
+__device__ __forceinline__ TileCoord decode_tile(const RowsArgs& p, int t, int m_tiles, int bn,
+                                                 bool want_group = true) {
   TileCoord c;
   const int nc = t % p.n_chunks;
   const int rest = t / p.n_chunks;
   c.m_tile = rest % m_tiles;
   c.z = rest / m_tiles;
   c.n0 = nc * bn;
-  c.group = p.n_fixed_groups > 0 ? c.z : __ldg(p.expert_ids + c.m_tile);
+  c.group = !want_group ? -1 : p.n_fixed_groups > 0 ? c.z : __ldg(p.expert_ids + c.m_tile);
   return c;
 }
 // The owner of tile t alone (-1 past the end of the list). The producers ask for the next tile's
@@ -72,9 +73,25 @@ __device__ __forceinline__ int tile_group(const RowsArgs& p, int t, int m_tiles,
   return p.n_fixed_groups > 0 ? rest / m_tiles : __ldg(p.expert_ids + rest % m_tiles);
 }
 
+// v[0..31] += bias[0..31] (bf16, 16-byte aligned; the same address in every lane: a broadcast load)
+__device__ __forceinline__ void add_bias32(float* v, const __nv_bfloat16* bias) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 r = __ldg(reinterpret_cast<const uint4*>(bias) + i);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]));
+      v[8 * i + 2 * k] += f.x;
+      v[8 * i + 2 * k + 1] += f.y;
+    }
+  }
+}
+
 template <int ACT, int BN>
 __device__ __forceinline__ void epilogue_glu(uint32_t taddr, int c_lo, int c_hi, bool row_ok,
-                                             __nv_bfloat16* out_row, __nv_bfloat16* raw_row) {
+                                             __nv_bfloat16* out_row, __nv_bfloat16* raw_row,
+                                             const __nv_bfloat16* bias) {
   constexpr int HALF = BN / 2;  // gate = accumulator cols [0, HALF), up = [HALF, BN)
 #pragma unroll 1
   for (int c = c_lo; c < c_hi; ++c) {
@@ -82,6 +99,10 @@ __device__ __forceinline__ void epilogue_glu(uint32_t taddr, int c_lo, int c_hi,
     tmem_ld32(taddr + c * 32, g);
     tmem_ld32(taddr + HALF + c * 32, u);
     tmem_ld_wait();
+    if (bias != nullptr) {   // the kept pre-activations include it, as the backward expects
+      add_bias32(g, bias + c * 32);
+      add_bias32(u, bias + HALF + c * 32);
+    }
     if (raw_row != nullptr && row_ok) {
       store_bf16x32(raw_row + c * 32, g);
       store_bf16x32(raw_row + HALF + c * 32, u);
@@ -420,7 +441,7 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
     int j = 0;
     [[maybe_unused]] uint32_t box_count = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++j) {
-      const TileCoord tc = decode_tile(p, t, m_tiles, BN);
+      const TileCoord tc = decode_tile(p, t, m_tiles, BN, false);
       const int b = j & 1;
       const float w_n = load_w(pair_n);                    // next tile's weight
       const int pair_nn = load_pair(t + 2 * gridDim.x);    // the pair id of the tile after that
@@ -435,15 +456,25 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
       const bool row_ok = !fixed || grow < p.rows_host;
       __nv_bfloat16* out_row = p.out + tc.z * p.out_gstride + grow * p.ld_out;
 
+      // this tile's bias row: only the groups of the first weight stack have one
+      // (the tile's owner is looked up only when there is a bias: the epilogue has no other use
+      // for it, and the load would sit at the head of every tile)
+      [[maybe_unused]] const __nv_bfloat16* bias_row = nullptr;
+      if constexpr (EPI == EPI_GLU || EPI == EPI_SCALE) {
+        if (p.bias != nullptr) {
+          const int grp = fixed ? tc.z : __ldg(p.expert_ids + tc.m_tile);
+          if (grp < p.n_groups_b1) bias_row = p.bias + int64_t(grp) * p.n_dim;
+        }
+      }
       if constexpr (EPI == EPI_GLU) {
         __nv_bfloat16* raw_row =
             p.out2 ? p.out2 + tc.z * p.out2_gstride + grow * BN : nullptr;
         switch (p.act) {
-          case ACT_SILU: epilogue_glu<ACT_SILU, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row); break;
-          case ACT_GELU: epilogue_glu<ACT_GELU, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row); break;
-          case ACT_RELU: epilogue_glu<ACT_RELU, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row); break;
-          case ACT_SIGMOID: epilogue_glu<ACT_SIGMOID, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row); break;
-          default: epilogue_glu<ACT_TANH, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row); break;
+          case ACT_SILU: epilogue_glu<ACT_SILU, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row, bias_row); break;
+          case ACT_GELU: epilogue_glu<ACT_GELU, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row, bias_row); break;
+          case ACT_RELU: epilogue_glu<ACT_RELU, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row, bias_row); break;
+          case ACT_SIGMOID: epilogue_glu<ACT_SIGMOID, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row, bias_row); break;
+          default: epilogue_glu<ACT_TANH, BN>(taddr, c_lo, c_hi, row_ok, out_row, raw_row, bias_row); break;
         }
       } else if constexpr (EPI == EPI_RAW || EPI == EPI_SCALE) {
         // The tile leaves as 64-column boxes: the eight warps fill one box in shared memory (warp
@@ -462,6 +493,9 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
           if (jb + 1 < NB) tmem_ld32(taddr + (jb + 1) * 64 + half * 32, v[(jb + 1) & 1]);
           float* cur = v[jb & 1];
           if constexpr (EPI == EPI_SCALE) {
+            // (columns past n_dim belong to boxes that are never stored; n_dim is a multiple of 32)
+            if (bias_row != nullptr && tc.n0 + jb * 64 + half * 32 < p.n_dim)
+              add_bias32(cur, bias_row + tc.n0 + jb * 64 + half * 32);
 #pragma unroll
             for (int i = 0; i < 32; ++i) cur[i] *= w;
           }

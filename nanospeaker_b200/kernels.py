@@ -279,7 +279,7 @@ def copy_cols(src: torch.Tensor, dst_ld: int) -> torch.Tensor:
 
 
 def up_gemm(a, w_in, expert_ids, n_post_pad, n_fixed: int, act: int, want_raw: bool,
-            gather=None, w_extra=None, token_rows=None):
+            gather=None, w_extra=None, token_rows=None, bias=None):
     """a x w_in [G, D, 2H] -> (act(g)*u [rows, H], raw [g|u] [rows, 2H] | None).
     a is slot-ordered [rows, D]; or, with gather=(sorted_ids, top_k), the token-major x [T, D] whose
     rows the kernel gathers itself (rows = len(sorted_ids)). n_fixed = S > 0 applies weight
@@ -302,14 +302,14 @@ def up_gemm(a, w_in, expert_ids, n_post_pad, n_fixed: int, act: int, want_raw: b
     _lib.check(_lib.load().moe_b200_up_gemm(
         a.data_ptr(), rows, d, w_in.data_ptr(), g, xp, xn, h, _lib.ptr(expert_ids),
         _lib.ptr(n_post_pad), n_fixed, _lib.ptr(sids), top_k, n_pairs, act, hid.data_ptr(), _lib.ptr(raw),
-        _lib.ptr(tok), tok.shape[0] if tok is not None else 0, _lib.ptr(offs),
+        _lib.ptr(tok), tok.shape[0] if tok is not None else 0, _lib.ptr(offs), _lib.ptr(bias),
         status_word(a.device).data_ptr(), _stream(a)), "moe_b200_up_gemm")
     _count(1 if rows else 0)
     return hid, raw
 
 
 def down_gemm(hid, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair_w,
-              n_pairs: int, w_extra=None) -> torch.Tensor:
+              n_pairs: int, w_extra=None, bias=None) -> torch.Tensor:
     """hid [rows, K] (or [S, rows, K]) x w_out [G, K, D] -> y, scaled per row by
     pair_w[sorted_ids[row]] on the routed schedule."""
     _need_cuda(hid, w_out)
@@ -320,7 +320,8 @@ def down_gemm(hid, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair
     _lib.check(_lib.load().moe_b200_down_gemm(
         hid.data_ptr(), rows, k, w_out.data_ptr(), g, xp, xn, d, _lib.ptr(expert_ids),
         _lib.ptr(n_post_pad), n_fixed, _lib.ptr(sorted_ids), _lib.ptr(pair_w), n_pairs,
-        y.data_ptr(), status_word(hid.device).data_ptr(), _stream(hid)), "moe_b200_down_gemm")
+        y.data_ptr(), _lib.ptr(bias), status_word(hid.device).data_ptr(), _stream(hid)),
+        "moe_b200_down_gemm")
     _count(1 if rows else 0)
     return y
 

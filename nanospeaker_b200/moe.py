@@ -7,14 +7,14 @@ the reference, so its callers (Block in src/model/nanospeaker.py:153-169, moe_he
 src/train/metrics.py:84-97) and its checkpoints work unchanged.
 
 Paths, in the order `forward` tries them:
-  1. kernel    CUDA + bf16 + a named activation + no capacity cap + no bias + shapes the tiles
+  1. kernel    CUDA + bf16 + a named activation + no capacity cap + shapes the tiles
                cover: router top-k, dispatch, permute, grouped GEMMs, combine and the shared
                experts all run as the `moe_b200` ops. No host sync. A missing or failing library
                raises; nothing is silently rerouted.
   2. padded    a capacity_factor is set: fixed-capacity batched GEMM in torch
                (src/model/moe.py:225-283); not a dropless path and not accelerated here.
   3. eager     the ragged per-expert loop in torch (src/model/moe.py:377-418) for everything the
-               kernels decline (CPU, fp32/fp64, custom activations, biases).
+               kernels decline (CPU, fp32/fp64, custom activations).
 """
 import math
 
@@ -92,7 +92,7 @@ class MoEBlock(nn.Module):
     # ------------------------------------------------------------------------------ gating
     def _kernel_config_ok(self) -> bool:
         """Everything about this block, other than the tensor it is handed, that the kernels need."""
-        return (self.kernel and self._kernel_act is not None and self.b_in is None
+        return (self.kernel and self._kernel_act is not None
                 and MK.shapes_supported(self.d_model, self.d_hidden, self.n_experts, self.top_k,
                                         self.n_shared))
 
@@ -195,7 +195,8 @@ class MoEBlock(nn.Module):
         x = x.reshape(-1, self.d_model)
         if x.shape[0] == 0:
             return x.clone().view(shape)
-        if self._use_kernel(x) and not (self.training and self.router.noise_std):
+        if (self._use_kernel(x) and self.b_in is None
+                and not (self.training and self.router.noise_std)):
             # whole block as one op: router GEMM, top-k, dispatch, experts, combine, balance loss
             full = self.router.wants_probs()
             out, aux, counts = fused_moe_block(

@@ -151,8 +151,13 @@ def moe_experts(
     inv_ids: torch.Tensor,
     activation: str,
     save_for_backward: bool,
+    b_in: Optional[torch.Tensor] = None,
+    b_out: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """out[t] = sum_j topk_w[t,j] * expert_{idx[t,j]}(x[t]) on pre-dispatched pairs.
+
+    Optional per-expert biases of the routed experts, b_in [E, 2H] and b_out [E, D], are added in
+    the GEMM epilogues (before the GLU / before the weight scale, src/model/moe.py:295-305).
 
     up/gate GEMM with the GLU fused -> down GEMM with fused router weight -> token-major fp32
     combine. All tensors share x's dtype (the wrapper casts). Two ways to feed the up GEMM:
@@ -183,24 +188,27 @@ def moe_experts(
     tw = topk_w.reshape(-1).contiguous()
     if w_sh_in is not None:
         w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
+    b_in = None if b_in is None else b_in.to(x.dtype).contiguous()
+    b_out = None if b_out is None else b_out.to(x.dtype).contiguous()
 
     if save_for_backward:
         live, tok = _routed_rows(x, w_in, w_sh_in, pad_offsets, n_post_pad)
         xs = K.permute(x, topk, sorted_ids, live)
         hid, a1 = K.up_gemm(xs, w_in, expert_ids, n_post_pad, 0, act, True, w_extra=w_sh_in,
-                            token_rows=tok)
+                            token_rows=tok, bias=b_in)
     else:
         xs, a1 = x.new_empty(0), x.new_empty(0)
         hid, _ = K.up_gemm(x, w_in, expert_ids, n_post_pad, 0, act, False,
-                           gather=(sorted_ids, topk), w_extra=w_sh_in)
-    y = K.down_gemm(hid, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m, w_extra=w_sh_out)
+                           gather=(sorted_ids, topk), w_extra=w_sh_in, bias=b_in)
+    y = K.down_gemm(hid, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m, w_extra=w_sh_out,
+                    bias=b_out)
     out = K.combine(y, inv_ids, n, topk)
     return out, xs, a1
 
 
 @moe_experts.register_fake
 def _(x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
-      n_post_pad, inv_ids, activation, save_for_backward):
+      n_post_pad, inv_ids, activation, save_for_backward, b_in=None, b_out=None):
     n, d = x.shape
     if n == 0 or not save_for_backward:
         return x.new_empty((n, d)), x.new_empty(0), x.new_empty(0)
@@ -239,9 +247,15 @@ def moe_experts_bwd(
     n_post_pad: torch.Tensor,
     inv_ids: torch.Tensor,
     activation: str,
-) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
-    """(dx, dW_in, dW_out, dtopk_w, dW_sh_in, dW_sh_out); the last two are empty without shared
-    experts. xs (x in slot order) and a1 (pre-activations) are what the forward kept; grad_out is
+    b_out: Optional[torch.Tensor] = None,
+    need_db_in: bool = False,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
+           torch.Tensor, torch.Tensor]:
+    """(dx, dW_in, dW_out, dtopk_w, dW_sh_in, dW_sh_out, db_in, db_out); the shared-expert and bias
+    gradients are empty when the forward had none. The kept pre-activations a1 already include
+    b_in, so only b_out's value enters the backward (through dtopk_w); the bias gradients are
+    segment sums over each expert's run, done with sync-free torch ops as the reference does
+    (src/model/moe_kernel.py:723-737). xs (x in slot order) and a1 (pre-activations) are what the forward kept; grad_out is
     permuted once and feeds both the dHidden GEMM and the dW_out GEMM."""
     grad_out = grad_out.to(x.dtype).contiguous()
     x, w_in, w_out = x.contiguous(), w_in.contiguous(), w_out.contiguous()
@@ -271,21 +285,46 @@ def moe_experts_bwd(
         (dw_in, dw_sh_in), (dw_out, dw_sh_out) = g_in, g_out
     else:
         dw_in, dw_out, dw_sh_in, dw_sh_out = g_in, g_out, x.new_empty(0), x.new_empty(0)
-    return dx, dw_in, dw_out, dtw.view_as(topk_w), dw_sh_in, dw_sh_out
+    dtw = dtw.view_as(topk_w)
+    db_in, db_out = x.new_empty(0), x.new_empty(0)
+    if need_db_in:
+        # column sums of dA1 over each expert's run: per 128-row tile first (the tiles past the live
+        # length hold whatever the allocator left there and are masked out), then per expert
+        tiles = da1.shape[0] // ALIGN_M
+        sums = da1.view(tiles, ALIGN_M, -1).sum(1, dtype=torch.float32)
+        live_tile = (torch.arange(tiles, device=x.device) * ALIGN_M < n_post_pad).unsqueeze(1)
+        sums = torch.where(live_tile, sums, torch.zeros((), device=x.device))
+        db_in = torch.zeros((e_n + s_n, da1.shape[1]), dtype=torch.float32, device=x.device) \
+            .index_add_(0, expert_ids.long(), sums)[:e_n].to(x.dtype)
+    if b_out is not None:
+        # y_pair = (hid W_out + b_out[e]) * w: dtopk_w gains <dOut[t], b_out[e]>, and
+        # db_out[e] = sum over e's pairs of w * dOut[t]
+        e_of_pair = expert_ids.long()[inv_ids.long() // ALIGN_M].view(n, topk)
+        gb = grad_out.float() @ b_out.float().t()                       # [T, E]
+        if s_n:
+            gb = torch.cat([gb, gb.new_zeros((n, s_n))], 1)             # shared experts: no bias
+        dtw = (dtw.float() + gb.gather(1, e_of_pair)).to(topk_w.dtype)
+        gates = torch.zeros((n, e_n + s_n), dtype=torch.float32, device=x.device) \
+            .scatter_add_(1, e_of_pair, topk_w.float())
+        db_out = (gates[:, :e_n].t() @ grad_out.float()).to(x.dtype)
+    return dx, dw_in, dw_out, dtw, dw_sh_in, dw_sh_out, db_in, db_out
 
 
 @moe_experts_bwd.register_fake
 def _(grad_out, x, xs, a1, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
-      pad_offsets, counts, n_post_pad, inv_ids, activation):
+      pad_offsets, counts, n_post_pad, inv_ids, activation, b_out=None, need_db_in=False):
+    e_n = w_in.shape[0]
     return (torch.empty_like(x), torch.empty_like(w_in), torch.empty_like(w_out),
             torch.empty_like(topk_w),
             torch.empty_like(w_sh_in) if w_sh_in is not None else x.new_empty(0),
-            torch.empty_like(w_sh_out) if w_sh_out is not None else x.new_empty(0))
+            torch.empty_like(w_sh_out) if w_sh_out is not None else x.new_empty(0),
+            x.new_empty((e_n, w_in.shape[2])) if need_db_in else x.new_empty(0),
+            x.new_empty((e_n, x.shape[1])) if b_out is not None else x.new_empty(0))
 
 
 def _experts_setup(ctx, inputs, output):
     (x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
-     n_post_pad, inv_ids, activation, save_for_backward) = inputs
+     n_post_pad, inv_ids, activation, save_for_backward, b_in, b_out) = inputs
     out, xs, a1 = output
     ctx.mark_non_differentiable(xs, a1)
     # without this autograd would hand the backward zero-filled gradients for the kept buffers
@@ -298,6 +337,10 @@ def _experts_setup(ctx, inputs, output):
     ctx.has_shared = w_sh_in is not None
     if ctx.has_shared:
         saved += [w_sh_in, w_sh_out]
+    # b_in's value is not needed again (a1 was kept with it inside), b_out's is (for dtopk_w)
+    ctx.has_b_in, ctx.has_b_out = b_in is not None, b_out is not None
+    if ctx.has_b_out:
+        saved.append(b_out)
     ctx.save_for_backward(*saved)
     ctx.activation = activation
 
@@ -306,13 +349,15 @@ def _experts_backward(ctx, grad_out, g_xs, g_a1):
     (x, xs, a1, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts, n_post_pad,
      inv_ids, *rest) = ctx.saved_tensors
     w_sh_in, w_sh_out = (rest[0], rest[1]) if ctx.has_shared else (None, None)
+    b_out = rest[-1] if ctx.has_b_out else None
     if grad_out is None:
         grad_out = torch.zeros_like(x)
-    dx, dw_in, dw_out, dtw, dsi, dso = moe_experts_bwd(
+    dx, dw_in, dw_out, dtw, dsi, dso, db_in, db_out = moe_experts_bwd(
         grad_out, x, xs, a1, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
-        pad_offsets, counts, n_post_pad, inv_ids, ctx.activation)
+        pad_offsets, counts, n_post_pad, inv_ids, ctx.activation, b_out, ctx.has_b_in)
     return (dx, dw_in, dw_out, dtw, dsi if ctx.has_shared else None,
-            dso if ctx.has_shared else None, None, None, None, None, None, None, None, None)
+            dso if ctx.has_shared else None, None, None, None, None, None, None, None, None,
+            db_in if ctx.has_b_in else None, db_out if ctx.has_b_out else None)
 
 
 moe_experts.register_autograd(_experts_backward, setup_context=_experts_setup)
@@ -600,13 +645,10 @@ def fused_moe_forward(x, w_in, w_out, topk_w, topk_idx, b_in, b_out, activation,
     Same contract as src/model/moe_kernel.py:785-803, plus optional stacked shared-expert weights
     (`w_sh_in [S, D, 2H]`, `w_sh_out [S, H, D]`) whose outputs are then included in `out`.
     Parameters are cast to x.dtype here (what autocast would do); gradients flow back through
-    the cast. Per-expert biases are not implemented by the kernels.
+    the cast. Per-expert biases b_in [E, 2H] / b_out [E, D] (either may be None) are applied in
+    the GEMM epilogues and get gradients.
     """
     _act_id(activation)
-    if b_in is not None or b_out is not None:
-        raise NotImplementedError(
-            "moe_b200 kernels do not apply per-expert biases; build the block with bias=False "
-            "or kernel=False")
     n_experts = w_in.shape[0]
     topk_w = topk_w.to(x.dtype)
     if w_sh_in is not None:
@@ -618,8 +660,8 @@ def fused_moe_forward(x, w_in, w_out, topk_w, topk_idx, b_in, b_out, activation,
         n_experts += s_n
     sids, eids, offs, counts, npp, inv = moe_dispatch(topk_idx, n_experts)
     cast = lambda t: None if t is None else t.to(x.dtype)
-    tensors = (x, w_in, w_out, topk_w, w_sh_in, w_sh_out)
+    tensors = (x, w_in, w_out, topk_w, w_sh_in, w_sh_out, b_in, b_out)
     save = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
     out, _, _ = moe_experts(x, cast(w_in), cast(w_out), topk_w, cast(w_sh_in), cast(w_sh_out), sids,
-                         eids, offs, counts, npp, inv, activation, save)
+                         eids, offs, counts, npp, inv, activation, save, cast(b_in), cast(b_out))
     return out, counts[: w_in.shape[0]]

@@ -156,9 +156,13 @@ def shared_forward(x, w_sh_in, w_sh_out, act="silu"):
     return total
 
 
-def experts_forward(x, w_in, w_out, topk_w, topk_idx, act="silu", w_sh_in=None, w_sh_out=None):
+def experts_forward(x, w_in, w_out, topk_w, topk_idx, act="silu", w_sh_in=None, w_sh_out=None,
+                    b_in=None, b_out=None):
     """Eager ragged dispatch (src/model/moe.py:377-418): gather per expert, two matmuls with the GLU
-    between, scale by the router weight, index_add_ into the output, then the shared experts."""
+    between, scale by the router weight, index_add_ into the output, then the shared experts.
+    Optional per-expert biases b_in [E, 2H] / b_out [E, D] as in src/model/moe.py:295-305 (added
+    after each matmul; b_out before the weight scale). Differentiable: the bias tests take its
+    gradients from autograd."""
     fn = ACTS[act]
     n_experts, k = w_in.shape[0], topk_idx.shape[1]
     _, order, token_idx, counts = plan(topk_idx, n_experts)
@@ -170,9 +174,14 @@ def experts_forward(x, w_in, w_out, topk_w, topk_idx, act="silu", w_sh_in=None, 
     for e in range(n_experts):
         if sizes[e] == 0:
             continue
-        gate, up = (xs[e] @ w_in[e]).chunk(2, dim=-1)
+        h = xs[e] @ w_in[e]
+        if b_in is not None:
+            h = h + b_in[e]
+        gate, up = h.chunk(2, dim=-1)
         y = (fn(gate) * up) @ w_out[e]
-        out.index_add_(0, rows[e], y * ws[e][:, None])
+        if b_out is not None:
+            y = y + b_out[e]
+        out = out.index_add(0, rows[e], y * ws[e][:, None])
     if w_sh_in is not None:
         out = out + shared_forward(x, w_sh_in, w_sh_out, act)
     return out

@@ -1,7 +1,7 @@
 """Generate the golden vectors in this directory by running the UNMODIFIED reference.
 
 Usage (needs a checkout of Osmansiddiquer/nanospeaker):
-    python tests/golden/make_golden.py /path/to/nanospeaker [--sublayer-only]
+    python tests/golden/make_golden.py /path/to/nanospeaker [--sublayer-only | --bias-only]
 
 Each .npz holds the inputs and everything the reference's pure-PyTorch MoE path
 (MoEBlock(..., fused=False, kernel=False, capacity_factor=None) on CPU) computes from them:
@@ -27,11 +27,11 @@ def put(store, name, t):
 
 
 def block_case(MoEBlock, name, *, d_model, n_experts, d_ff, top_k, n_shared, tokens, dtype, train,
-               seed, activation="silu", normalize=True):
+               seed, activation="silu", normalize=True, bias=False):
     torch.manual_seed(seed)
     m = MoEBlock(d_model, n_experts, d_ff=d_ff, top_k=top_k, n_shared=n_shared,
                  capacity_factor=None, activation=activation, normalize_weights=normalize,
-                 fused=False, kernel=False)
+                 fused=False, kernel=False, bias=bias)
     with torch.no_grad():
         m.router.W.copy_(torch.randn_like(m.router.W) * 0.3)
         m.W_in.copy_(torch.randn_like(m.W_in) * d_model ** -0.5)
@@ -40,6 +40,10 @@ def block_case(MoEBlock, name, *, d_model, n_experts, d_ff, top_k, n_shared, tok
             m.W_sh_in.copy_(torch.randn_like(m.W_sh_in) * d_model ** -0.5)
             m.W_sh_out.copy_(torch.randn_like(m.W_sh_out) * m.d_hidden ** -0.5)
     x = torch.randn(tokens, d_model)
+    if bias:   # drawn after everything else so the other cases keep their values
+        with torch.no_grad():
+            m.b_in.copy_(torch.randn_like(m.b_in) * 0.5)
+            m.b_out.copy_(torch.randn_like(m.b_out) * 0.5)
     m = m.to(dtype)
     x = x.to(dtype).requires_grad_(train)
     m.train(train)
@@ -52,6 +56,9 @@ def block_case(MoEBlock, name, *, d_model, n_experts, d_ff, top_k, n_shared, tok
     if n_shared:
         put(s, "W_sh_in", m.W_sh_in)
         put(s, "W_sh_out", m.W_sh_out)
+    if bias:
+        put(s, "b_in", m.b_in)
+        put(s, "b_out", m.b_out)
     s["meta"] = np.array([d_model, n_experts, d_ff, top_k, n_shared, tokens, int(train),
                           int(normalize)], dtype=np.int64)
     s["activation"] = np.array(activation)
@@ -85,6 +92,9 @@ def block_case(MoEBlock, name, *, d_model, n_experts, d_ff, top_k, n_shared, tok
         if n_shared:
             put(s, "grad_W_sh_in", m.W_sh_in.grad)
             put(s, "grad_W_sh_out", m.W_sh_out.grad)
+        if bias:
+            put(s, "grad_b_in", m.b_in.grad)
+            put(s, "grad_b_out", m.b_out.grad)
     np.savez_compressed(os.path.join(HERE, name + ".npz"), **s)
     print(name, {k: v.shape for k, v in s.items() if hasattr(v, "shape") and v.ndim})
 
@@ -163,6 +173,13 @@ def main():
     sublayer_case(MoEBlock, RMSNorm, "sublayer_fp32_train", dtype=torch.float32, seed=7, **sub)
     sublayer_case(MoEBlock, RMSNorm, "sublayer_bf16_train", dtype=torch.bfloat16, seed=8, **sub)
     if "--sublayer-only" in sys.argv:
+        return
+    common = dict(d_model=64, n_experts=4, d_ff=192, top_k=2, n_shared=1, tokens=80)
+    block_case(MoEBlock, "block_fp32_train_bias", dtype=torch.float32, train=True, seed=9,
+               bias=True, **common)
+    block_case(MoEBlock, "block_bf16_train_bias", dtype=torch.bfloat16, train=True, seed=10,
+               bias=True, **common)
+    if "--bias-only" in sys.argv:
         return
 
     common = dict(d_model=64, n_experts=4, d_ff=192, top_k=2, n_shared=1, tokens=80)

@@ -71,11 +71,12 @@ def test_arguments_are_validated_before_any_launch(lib):
     assert lib.moe_b200_permute(null, 4, 64, 2, null, null, 128, null, null) == -2
     assert lib.moe_b200_combine(null, null, 4, 2, 64, null, null, null, null) == -2
     assert lib.moe_b200_up_gemm(null, 128, 64, null, 4, null, 0, 64, null, null, 1, null, 0, 0, 0,
-                                null, null, null, 0, null, null, null) == -2
+                                null, null, null, 0, null, null, null, null) == -2
     buf = ctypes.create_string_buffer(96)
     p = ctypes.c_void_p((ctypes.addressof(buf) + 31) & ~31)
     up = lambda rows, h, fixed, topk, n_extra=0: lib.moe_b200_up_gemm(
-        p, rows, 64, p, 4, p, n_extra, h, p, p, fixed, p, topk, 8, 0, p, null, null, 0, null, p, null)
+        p, rows, 64, p, 4, p, n_extra, h, p, p, fixed, p, topk, 8, 0, p, null, null, 0, null, null,
+        p, null)
     assert up(128, 64, 1, 0) == -5      # d_hidden the tiles do not cover
     assert up(100, 128, 0, 0) == -1     # routed rows must be a multiple of 128
     assert up(128, 128, 5, 0) == -1     # more fixed groups than weight matrices

@@ -70,6 +70,42 @@ def test_module_forward_backward_matches_reference_golden():
         assert rel_l2(got.cpu(), g[key]) < (2e-2 if key == "grad_router_W" else TOL), key
 
 
+def test_module_with_expert_biases_matches_reference_golden():
+    """bias=True: b_in before the GLU, b_out before the weight scale, in the kernels' epilogues;
+    output and every gradient of the reference's bf16 training case, the two bias gradients and
+    the router's (whose dtopk_w carries <dOut, b_out>) included."""
+    from nanospeaker_b200 import MoEBlock, fused_moe_forward
+    g = load_golden("block_bf16_train_bias")
+    d_model, n_experts, d_ff, top_k, n_shared, tokens, train, normalize = g["meta"].tolist()
+    m = MoEBlock(d_model, n_experts, d_ff=d_ff, top_k=top_k, n_shared=n_shared, bias=True,
+                 capacity_factor=None).to(torch.bfloat16)
+    with torch.no_grad():
+        for name, key in [("router.W", "router_W"), ("W_in", "W_in"), ("W_out", "W_out"),
+                          ("W_sh_in", "W_sh_in"), ("W_sh_out", "W_sh_out"), ("b_in", "b_in"),
+                          ("b_out", "b_out")]:
+            m.get_parameter(name).copy_(g[key])
+    m = m.cuda().train()
+    x = g["x"].cuda().requires_grad_(True)
+    assert m._use_kernel(x), "kernel path was not taken"
+    # experts alone on the reference's routing, forward
+    out_e, _ = fused_moe_forward(x.detach(), m.W_in, m.W_out, g["topk_w"].cuda(),
+                                 g["topk_idx"].cuda(), m.b_in, m.b_out, "silu",
+                                 w_sh_in=m.W_sh_in, w_sh_out=m.W_sh_out)
+    assert rel_l2(out_e.detach().cpu(), g["out"]) < TOL
+    # whole module, forward + backward
+    out = m(x)
+    assert torch.equal(m.expert_counts.cpu().long(), g["plan_counts"])
+    (out.float().square().mean() + m.aux_loss).backward()
+    assert rel_l2(out.detach().cpu(), g["out"]) < TOL
+    for got, key in [(x.grad, "grad_x"), (m.W_in.grad, "grad_W_in"), (m.W_out.grad, "grad_W_out"),
+                     (m.W_sh_in.grad, "grad_W_sh_in"), (m.W_sh_out.grad, "grad_W_sh_out"),
+                     (m.b_in.grad, "grad_b_in"), (m.b_out.grad, "grad_b_out"),
+                     (m.router.W.grad, "grad_router_W")]:
+        assert rel_l2(got.cpu(), g[key]) < (2e-2 if key == "grad_router_W" else TOL), key
+    from nanospeaker_b200 import kernels
+    kernels.check_status("cuda")
+
+
 def _model_shape_pair(T, train, bias_std=0.0, seed=0):
     """nanoSpeaker's block (D=576, E=76, k=6, S=2, d_ff=192) with the benchmark's init, as a CUDA
     module and a CPU oracle twin sharing bf16 weights."""
@@ -243,8 +279,8 @@ def test_module_contract_on_cuda():
     assert set(m.state_dict()) == {"router.W", "W_in", "W_out", "W_sh_in", "W_sh_out"}
     # what the kernels decline runs the eager loop, never a wrong kernel
     assert not m.float()._use_kernel(torch.zeros(1, 64, device="cuda"))
-    assert not MoEBlock(64, 8, d_ff=192, bias=True).to(torch.bfloat16).cuda()._use_kernel(
-        torch.zeros(1, 64, device="cuda").bfloat16())
+    assert MoEBlock(64, 8, d_ff=192, bias=True).to(torch.bfloat16).cuda()._use_kernel(
+        torch.zeros(1, 64, device="cuda").bfloat16())      # biases ride in the GEMM epilogues
     assert not MoEBlock(64, 8, d_ff=192, capacity_factor=1.25).to(torch.bfloat16).cuda()._use_kernel(
         torch.zeros(1, 64, device="cuda").bfloat16())
     assert not MoEBlock(64, 8, d_ff=192, activation=lambda t: t * torch.sigmoid(t))._kernel_act

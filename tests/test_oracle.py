@@ -187,3 +187,19 @@ def test_oracle_matches_live_reference_at_model_shape(dtype, train):
         assert torch.equal(ref.W_out.grad, m.W_out.grad)
         assert torch.equal(ref.router.W.grad, m.router_W.grad)
         assert torch.equal(ref.W_sh_in.grad, m.W_sh_in.grad)
+
+
+@pytest.mark.parametrize("case", ["block_fp32_train_bias", "block_bf16_train_bias"])
+def test_expert_biases_match_golden(case):
+    """experts_forward with per-expert biases (src/model/moe.py:295-305) on the reference's own
+    routing: the reference's output, and through autograd its bias and weight gradients."""
+    g = load_golden(case)
+    leaf = lambda k: g[k].clone().requires_grad_(True)
+    p = {k: leaf(k) for k in ("x", "W_in", "W_out", "W_sh_in", "W_sh_out", "b_in", "b_out")}
+    out = O.experts_forward(p["x"], p["W_in"], p["W_out"], g["topk_w"], g["topk_idx"], "silu",
+                            p["W_sh_in"], p["W_sh_out"], p["b_in"], p["b_out"])
+    fp32 = g["x"].dtype == torch.float32
+    assert rel_l2(out, g["out"]) < (1e-6 if fp32 else 1e-2)
+    out.float().square().mean().backward()       # the balance loss does not reach these gradients
+    for k in ("W_in", "W_out", "W_sh_in", "W_sh_out", "b_in", "b_out"):
+        assert rel_l2(p[k].grad, g["grad_" + k]) < (1e-5 if fp32 else 2e-2), k
