@@ -310,6 +310,63 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
                    const void* alt, int64_t alt_rows, int32_t alt_which, int32_t* status,
                    void* stream);
 
+/* ---- Expert parallelism over peer memory (one node, up to 8 ranks) --------------------------------
+ * The routed experts are partitioned contiguously over the ranks; rank r owns experts
+ * [bounds[r], bounds[r+1]). The reference is single-GPU and has no counterpart for these entry
+ * points; they are the multi-GPU form of its dispatch / gather / combine
+ * (src/model/moe_kernel.py:113-218, 295-305, 415-437). No entry point waits on another GPU: the
+ * caller separates the phases with a collective. Pointer tables are HOST arrays of device pointers
+ * that are valid in the calling process (peer mappings of the other ranks' buffers, 16-byte
+ * aligned); only plain loads and stores touch peer memory. */
+
+/* From the all-gathered counts cnt_all [n_ranks, n_experts] (pairs per home rank and routed
+ * expert): for this rank as a sender owner_of [E] and send_row0 [E] (row, in the owner's
+ * slot-ordered buffer, of this rank's first pair of expert e; an owner's runs are 128-aligned and
+ * hold the home ranks' pairs in rank order); as an owner own_offs [E_r+1], own_counts [E_r],
+ * own_npp [1], own_eids [cap_tiles] -- the pad_offsets / counts / n_post_pad / expert_ids the
+ * grouped GEMMs take. All arrays on the device; bounds [n_ranks+1] too. */
+int moe_b200_ep_plan(const int32_t* cnt_all, const int32_t* bounds, int32_t n_ranks,
+                     int32_t n_experts, int32_t rank, int32_t* owner_of, int32_t* send_row0,
+                     int32_t* own_offs, int32_t* own_counts, int32_t* own_npp, int32_t* own_eids,
+                     int64_t cap_tiles, void* stream);
+
+/* Per pair p = t * k_all + j of the home rank: pair_rank[p], pair_row[p] = where its row lives
+ * (owner and row in the owner's buffer). Pairs of the shared experts (idx_all >= n_experts) get
+ * rank n_ranks (the local extra table entry) and row s * n_tokens + t. local_offs = the home
+ * rank's own pad_offsets, inv_ids its inverse permutation (moe_b200_dispatch). */
+int moe_b200_ep_pair_map(const int64_t* idx_all, const int32_t* inv_ids, const int32_t* local_offs,
+                         const int32_t* owner_of, const int32_t* send_row0, int64_t n_tokens,
+                         int32_t k_all, int32_t n_experts, int32_t n_ranks, int32_t* pair_rank,
+                         int32_t* pair_row, void* stream);
+
+/* The token permute fused with the dispatch exchange: row src[sorted_ids[s] / k_all] goes to row
+ * pair_row[pair] of dst_rows[pair_rank[pair]], for the slots s < *n_live_slots of the home plan
+ * (pass pad_offsets + n_experts: the shared experts' runs stay at home). With dst_sid / dst_w (may
+ * be NULL) the destination row also gets its own index and the pair's weight w_all[pair]. */
+int moe_b200_ep_push_rows(const void* src, int64_t n_tokens, int32_t d_model, int32_t k_all,
+                          const int32_t* sorted_ids, const int32_t* n_live_slots, int64_t max_slots,
+                          const int32_t* pair_rank, const int32_t* pair_row,
+                          const void* const* dst_rows, const void* const* dst_sid,
+                          const void* const* dst_w, int32_t n_ranks, const void* w_all,
+                          void* stream);
+
+/* Owner side: zero rows (and, with sid, the sentinel id) in the pad slots
+ * [own_offs[e] + own_counts[e], own_offs[e+1]) of every local run. */
+int moe_b200_ep_pad_fix(const int32_t* own_offs, const int32_t* own_counts, int32_t n_local,
+                        void* rows, int32_t d_model, int32_t* sid, int32_t sentinel, void* stream);
+
+/* The combine fused with the return exchange: out[t] = sum_j y[pair_rank[p]][pair_row[p]]
+ * (+ extra[t]) in fp32, pair order as moe_b200_combine. y holds n_tables pointers (the ranks'
+ * output buffers, then the local shared-expert buffer). */
+int moe_b200_ep_pull_combine(const void* const* y, int32_t n_tables, const int32_t* pair_rank,
+                             const int32_t* pair_row, int64_t n_tokens, int32_t k_all,
+                             int32_t d_model, const void* extra, void* out, void* stream);
+
+/* out[p] = v[pair_rank[p]][pair_row[p]] (bf16) for the routed columns j < top_k, 0 elsewhere. */
+int moe_b200_ep_pull_vec(const void* const* v, int32_t n_ranks, const int32_t* pair_rank,
+                         const int32_t* pair_row, int64_t n_tokens, int32_t k_all, int32_t top_k,
+                         void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -77,6 +77,21 @@ SIGNATURES = {
     "moe_b200_wgrad_scratch_bytes": (
         ctypes.c_int,
         [_c_i32, _c_i32, _c_i64, _c_i32, _c_i32, _c_i32, ctypes.POINTER(_c_sz)]),
+    "moe_b200_ep_plan": (
+        ctypes.c_int, [_c_vp, _c_vp, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp,
+                       _c_vp, _c_i64, _c_vp]),
+    "moe_b200_ep_pair_map": (
+        ctypes.c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_vp,
+                       _c_vp, _c_vp]),
+    "moe_b200_ep_push_rows": (
+        ctypes.c_int, [_c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp,
+                       _c_vp, _c_vp, _c_i32, _c_vp, _c_vp]),
+    "moe_b200_ep_pad_fix": (
+        ctypes.c_int, [_c_vp, _c_vp, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_vp]),
+    "moe_b200_ep_pull_combine": (
+        ctypes.c_int, [_c_vp, _c_i32, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp]),
+    "moe_b200_ep_pull_vec": (
+        ctypes.c_int, [_c_vp, _c_i32, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp]),
     "moe_b200_wgrad": (
         ctypes.c_int,
         [_c_vp, _c_i32, _c_i32, _c_vp, _c_i32, _c_i32, _c_i64, _c_vp, _c_i32, _c_i32, _c_vp, _c_i32,

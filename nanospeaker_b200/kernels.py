@@ -309,13 +309,13 @@ def up_gemm(a, w_in, expert_ids, n_post_pad, n_fixed: int, act: int, want_raw: b
 
 
 def down_gemm(hid, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair_w,
-              n_pairs: int, w_extra=None, bias=None) -> torch.Tensor:
+              n_pairs: int, w_extra=None, bias=None, out=None) -> torch.Tensor:
     """hid [rows, K] (or [S, rows, K]) x w_out [G, K, D] -> y, scaled per row by
     pair_w[sorted_ids[row]] on the routed schedule."""
     _need_cuda(hid, w_out)
     rows, k = hid.shape[-2:]
     g, _, d = w_out.shape
-    y = _stack(n_fixed, rows, d, hid)
+    y = _stack(n_fixed, rows, d, hid) if out is None else out   # out: a caller-owned [rows, D] buffer
     xp, xn = _extra(w_extra)
     _lib.check(_lib.load().moe_b200_down_gemm(
         hid.data_ptr(), rows, k, w_out.data_ptr(), g, xp, xn, d, _lib.ptr(expert_ids),
@@ -328,7 +328,7 @@ def down_gemm(hid, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair
 
 def dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair_w,
                     n_pairs: int, a1, act: int, want_dtw: bool, gather_top_k: int = 0,
-                    w_extra=None, token_rows=None):
+                    w_extra=None, token_rows=None, dtw_out=None):
     """-> (da1 [.., rows, 2H], hidw [.., rows, H], dtw [n_pairs] | None). douts is slot-ordered
     [rows, D], or with gather_top_k > 0 the token-major dOut [T, D] gathered through sorted_ids.
     token_rows=(dout, pad_offsets): as for up_gemm, for the rows of douts."""
@@ -339,7 +339,10 @@ def dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_i
     g, h, _ = w_out.shape
     da1 = _stack(n_fixed, rows, 2 * h, douts)
     hidw = _stack(n_fixed, rows, h, douts)
-    dtw = torch.empty(n_pairs, dtype=douts.dtype, device=douts.device) if want_dtw else None
+    dtw = None
+    if want_dtw:
+        dtw = dtw_out if dtw_out is not None else torch.empty(n_pairs, dtype=douts.dtype,
+                                                              device=douts.device)
     xp, xn = _extra(w_extra)
     _lib.check(_lib.load().moe_b200_dhidden_glu_bwd(
         douts.data_ptr(), rows, d, w_out.data_ptr(), g, xp, xn, h, _lib.ptr(expert_ids),
@@ -351,12 +354,12 @@ def dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_i
     return da1, hidw, dtw
 
 
-def dx_gemm(da1, w_in, expert_ids, n_post_pad, n_fixed: int, w_extra=None) -> torch.Tensor:
+def dx_gemm(da1, w_in, expert_ids, n_post_pad, n_fixed: int, w_extra=None, out=None) -> torch.Tensor:
     """da1 [.., rows, 2H] x w_in[e]^T -> ydx [.., rows, D]."""
     _need_cuda(da1, w_in)
     rows, h2 = da1.shape[-2:]
     g, d, _ = w_in.shape
-    ydx = _stack(n_fixed, rows, d, da1)
+    ydx = _stack(n_fixed, rows, d, da1) if out is None else out
     xp, xn = _extra(w_extra)
     _lib.check(_lib.load().moe_b200_dx_gemm(
         da1.data_ptr(), rows, h2 // 2, w_in.data_ptr(), g, xp, xn, d, _lib.ptr(expert_ids),
@@ -407,3 +410,78 @@ def wgrad(a, b, pad_offsets, n_groups: int, ks_rows: int = 0, a_grouped: bool = 
         status_word(a.device).data_ptr(), _stream(a)), "moe_b200_wgrad")
     _count(2 if rows > (ks_rows or 256) else 1)
     return (dw, dw_extra) if n_extra else dw
+
+
+# ---------------------------------------------------------------- expert parallelism, peer memory
+def _ptr_array(ptrs):
+    import ctypes
+    return (ctypes.c_void_p * len(ptrs))(*ptrs) if ptrs is not None else None
+
+
+def ep_plan(cnt_all, bounds, rank: int, n_local: int, cap_tiles: int):
+    """cnt_all [G, E] int32, bounds [G+1] int32 (both on the device) -> (owner_of [E], send_row0 [E],
+    own_offs [n_local+1], own_counts [n_local], own_npp [1], own_eids [cap_tiles])."""
+    _need_cuda(cnt_all, bounds)
+    g, e = cnt_all.shape
+    i32 = lambda n: torch.empty(n, dtype=torch.int32, device=cnt_all.device)
+    owner_of, send_row0 = i32(e), i32(e)
+    own_offs, own_counts, own_npp, own_eids = i32(n_local + 1), i32(max(n_local, 1)), i32(1), i32(cap_tiles)
+    _lib.check(_lib.load().moe_b200_ep_plan(
+        cnt_all.data_ptr(), bounds.data_ptr(), g, e, rank, owner_of.data_ptr(),
+        send_row0.data_ptr(), own_offs.data_ptr(), own_counts.data_ptr(), own_npp.data_ptr(),
+        own_eids.data_ptr(), cap_tiles, _stream(cnt_all)), "moe_b200_ep_plan")
+    _count(1)
+    return owner_of, send_row0, own_offs, own_counts, own_npp, own_eids
+
+
+def ep_pair_map(idx_all, inv_ids, local_offs, owner_of, send_row0, n_experts: int, n_ranks: int):
+    _need_cuda(idx_all)
+    t, k_all = idx_all.shape
+    pair_rank = torch.empty(t * k_all, dtype=torch.int32, device=idx_all.device)
+    pair_row = torch.empty_like(pair_rank)
+    _lib.check(_lib.load().moe_b200_ep_pair_map(
+        idx_all.data_ptr(), inv_ids.data_ptr(), local_offs.data_ptr(), owner_of.data_ptr(),
+        send_row0.data_ptr(), t, k_all, n_experts, n_ranks, pair_rank.data_ptr(),
+        pair_row.data_ptr(), _stream(idx_all)), "moe_b200_ep_pair_map")
+    _count(1 if t else 0)
+    return pair_rank, pair_row
+
+
+def ep_push_rows(src, k_all: int, sorted_ids, n_live_slots, pair_rank, pair_row, dst_rows,
+                 dst_sid=None, dst_w=None, w_all=None) -> None:
+    """dst_* are lists of device pointers (ints), one per rank."""
+    _need_cuda(src)
+    t, d = src.shape
+    _lib.check(_lib.load().moe_b200_ep_push_rows(
+        src.data_ptr(), t, d, k_all, sorted_ids.data_ptr(), n_live_slots.data_ptr(),
+        sorted_ids.numel(), pair_rank.data_ptr(), pair_row.data_ptr(), _ptr_array(dst_rows),
+        _ptr_array(dst_sid), _ptr_array(dst_w), len(dst_rows), _lib.ptr(w_all), _stream(src)),
+        "moe_b200_ep_push_rows")
+    _count(1 if t else 0)
+
+
+def ep_pad_fix(own_offs, own_counts, n_local: int, rows, sid=None, sentinel: int = 0) -> None:
+    _need_cuda(rows)
+    _lib.check(_lib.load().moe_b200_ep_pad_fix(
+        own_offs.data_ptr(), own_counts.data_ptr(), n_local, rows.data_ptr(), rows.shape[1],
+        _lib.ptr(sid), sentinel, _stream(rows)), "moe_b200_ep_pad_fix")
+    _count(1 if n_local else 0)
+
+
+def ep_pull_combine(y_ptrs, pair_rank, pair_row, n_tokens: int, k_all: int, d_model: int, like,
+                    extra=None) -> torch.Tensor:
+    out = torch.empty((n_tokens, d_model), dtype=like.dtype, device=like.device)
+    _lib.check(_lib.load().moe_b200_ep_pull_combine(
+        _ptr_array(y_ptrs), len(y_ptrs), pair_rank.data_ptr(), pair_row.data_ptr(), n_tokens,
+        k_all, d_model, _lib.ptr(extra), out.data_ptr(), _stream(like)), "moe_b200_ep_pull_combine")
+    _count(1 if n_tokens else 0)
+    return out
+
+
+def ep_pull_vec(v_ptrs, pair_rank, pair_row, n_tokens: int, k_all: int, top_k: int, like):
+    out = torch.empty((n_tokens, k_all), dtype=like.dtype, device=like.device)
+    _lib.check(_lib.load().moe_b200_ep_pull_vec(
+        _ptr_array(v_ptrs), len(v_ptrs), pair_rank.data_ptr(), pair_row.data_ptr(), n_tokens,
+        k_all, top_k, out.data_ptr(), _stream(like)), "moe_b200_ep_pull_vec")
+    _count(1 if n_tokens else 0)
+    return out

@@ -137,3 +137,41 @@ def test_two_gpus_over_nccl_match_the_single_gpu_block():
         assert rel_l2(dx, xr.grad.float().cpu()[sl]) < TOL
         assert rel_l2(dw_in, m.W_in.grad.float().cpu()[lo:hi]) < TOL
         assert rel_l2(dw_sh, m.W_sh_in.grad.float().cpu()) < TOL
+
+
+@pytest.mark.parametrize("world,tokens", [(2, 1024), (8, 300), (4, 1), (3, 777)])
+def test_push_pull_ranks_match_the_single_gpu_block(world, tokens):
+    """The peer-memory path (rows pushed straight into the owners' slot-ordered buffers, combine
+    pulling from them) with G virtual ranks on one device, against the single-GPU block on the
+    concatenated tokens: outputs, dX, and every weight gradient."""
+    from nanospeaker_b200 import ep_push, kernels
+    from nanospeaker_b200 import expert_parallel as EP
+    m = _block(seed=10 + world)
+    E, k, S, D = m.router.n_experts, m.router.top_k, 2, 576
+    x_all = torch.randn(world * tokens, D, device="cuda").bfloat16()
+    gout = torch.randn_like(x_all)
+
+    xr = x_all.clone().requires_grad_(True)
+    ref = m(xr)                                   # whole-block op, eval mode
+    ref.backward(gout)
+    ref_grads = {n: p.grad.clone() for n, p in m.named_parameters()}
+
+    grp = ep_push.LoopbackGroup(world, E, k, S, D, tokens, x_all.device)
+    xs = list(x_all.split(tokens))
+    for step in range(2):                         # twice: the buffers keep the last step's rows
+        outs = grp.forward(xs, m.router, m.W_in.detach(), m.W_out.detach(), m.W_sh_in.detach(),
+                           m.W_sh_out.detach(), "silu")
+        out = torch.cat([o for o, _ in outs])
+        assert rel_l2(out, ref.detach().float()) < TOL
+        grads = grp.backward(list(gout.split(tokens)))
+        dx = torch.cat([g[0] for g in grads])
+        assert rel_l2(dx, xr.grad.float()) < TOL
+        bounds = EP.expert_partition(E, world)
+        for r, (lo, hi) in enumerate(bounds):
+            assert rel_l2(grads[r][2], ref_grads["W_in"][lo:hi].float()) < TOL
+            assert rel_l2(grads[r][3], ref_grads["W_out"][lo:hi].float()) < TOL
+        total = lambda i: sum(g[i].float() for g in grads)
+        assert rel_l2(total(1), ref_grads["router.W"].float()) < 2e-2
+        assert rel_l2(total(4), ref_grads["W_sh_in"].float()) < TOL
+        assert rel_l2(total(5), ref_grads["W_sh_out"].float()) < TOL
+    kernels.check_status("cuda")
