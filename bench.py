@@ -687,10 +687,19 @@ def run_ep_workload(args):
     gout = torch.randn(T, D_MODEL, generator=g).bfloat16().to(dev)
     replicated = [m.router.W, m.W_sh_in, m.W_sh_out]
 
+    push = args.ep_impl == "push"
+    if push:
+        from nanospeaker_b200 import ep_push
+        grp = ep_push.SymmetricGroup(N_EXPERTS, TOP_K, N_SHARED, D_MODEL, T, dev)
+
     def step(i):
         x = xs[i % 2]
         x.grad = None
-        out, _ = EP.ep_block_forward(x, m.router, w_in, w_out, m.W_sh_in, m.W_sh_out, "silu")
+        if push:
+            out, _, _ = ep_push.ep_push_block_forward(x, m.router, w_in, w_out, m.W_sh_in,
+                                                      m.W_sh_out, "silu", grp)
+        else:
+            out, _ = EP.ep_block_forward(x, m.router, w_in, w_out, m.W_sh_in, m.W_sh_out, "silu")
         out.backward(gout)
         EP.all_reduce_replicated_grads(replicated)
 
@@ -718,7 +727,9 @@ def run_ep_workload(args):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "BASELINE config 5: experts partitioned over the ranks, "
                                    f"T={T} tokens per GPU, {args.routing} routing, forward + backward, "
-                                   "dispatch / combine by NCCL all-to-all (first version)"}}))
+                                   + ("rows pushed into / pulled from the owners' buffers "
+                                      "through peer pointers (symmetric memory)" if push else
+                                      "dispatch / combine by NCCL all-to-all")}}))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -867,6 +878,9 @@ def main():
                          "norm, block and add as separate steps")
     ap.add_argument("--skew", default="cv1", choices=sorted(SKEWS),
                     help="train workload: spread of the per-expert routing bias (see SKEWS)")
+    ap.add_argument("--ep-impl", default="push", choices=["push", "nccl"],
+                    help="ep workload: rows moved by the push / pull kernels over peer memory, or "
+                         "by NCCL all-to-all around the single-GPU kernels")
     ap.add_argument("--routing", default="uniform", choices=["uniform", "hotspot"],
                     help="ep workload: no routing bias, or a bias on experts 0-3 that sends half "
                          "of all assignments to them (all four live on rank 0)")

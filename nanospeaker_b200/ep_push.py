@@ -235,7 +235,10 @@ class SymmetricGroup:
 
     def __init__(self, n_experts: int, top_k: int, n_shared: int, d_model: int,
                  tokens_per_rank: int, device, group=None):
+        import os
         import torch.distributed as dist
+        # only plain peer loads / stores are used here: no multicast mapping of the arena is needed
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         self.dist, self.group = dist, group
         world, rank = dist.get_world_size(group), dist.get_rank(group)

@@ -175,3 +175,84 @@ def test_push_pull_ranks_match_the_single_gpu_block(world, tokens):
         assert rel_l2(total(4), ref_grads["W_sh_in"].float()) < TOL
         assert rel_l2(total(5), ref_grads["W_sh_out"].float()) < TOL
     kernels.check_status("cuda")
+
+
+def _push_worker(rank, world, port, tokens, q):
+    try:
+        import os
+        import torch.distributed as dist
+        from nanospeaker_b200 import ep_push
+        from nanospeaker_b200 import expert_parallel as EP
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        m = _block(seed=5)
+        E = m.router.n_experts
+        g = torch.Generator().manual_seed(11)
+        x_all = torch.randn(world * tokens, 576, generator=g).bfloat16()
+        gout_all = torch.randn(world * tokens, 576, generator=g).bfloat16()
+        sl = slice(rank * tokens, (rank + 1) * tokens)
+        lo, hi = EP.expert_partition(E, world)[rank]
+        grp = ep_push.SymmetricGroup(E, m.router.top_k, 2, 576, tokens, dev)
+        w_in = m.W_in.detach()[lo:hi].clone().requires_grad_(True)
+        w_out = m.W_out.detach()[lo:hi].clone().requires_grad_(True)
+        for step in range(2):                    # the second step reuses the exchange buffers
+            x = x_all[sl].cuda().requires_grad_(True)
+            for p in (w_in, w_out, m.router.W, m.W_sh_in, m.W_sh_out):
+                p.grad = None
+            out, _, _ = ep_push.ep_push_block_forward(x, m.router, w_in, w_out, m.W_sh_in,
+                                                      m.W_sh_out, "silu", grp)
+            out.backward(gout_all[sl].cuda())
+        EP.all_reduce_replicated_grads([m.router.W, m.W_sh_in, m.W_sh_out])
+        torch.cuda.synchronize()
+        from nanospeaker_b200 import kernels
+        kernels.check_status(dev)
+        q.put((rank, out.detach().float().cpu().numpy(), x.grad.float().cpu().numpy(),
+               w_in.grad.float().cpu().numpy(), m.W_sh_in.grad.float().cpu().numpy()))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as exc:  # surface the failure instead of hanging the parent
+        import traceback
+        q.put((rank, repr(exc) + traceback.format_exc()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpus_over_peer_memory_match_the_single_gpu_block():
+    """One process per GPU, exchange buffers in symmetric memory, rows pushed and pulled through
+    peer pointers: outputs and gradients of two steps against the single-GPU block."""
+    import socket
+    import torch.multiprocessing as mp
+    from nanospeaker_b200 import expert_parallel as EP
+    world, tokens = 2, 2048
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_push_worker, args=(r, world, port, tokens, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(world):
+        item = q.get(timeout=300)
+        assert len(item) == 5, item
+        got[item[0]] = item[1:]
+    for p in procs:
+        p.join(timeout=60)
+    m = _block(seed=5)
+    g = torch.Generator().manual_seed(11)
+    x_all = torch.randn(world * tokens, 576, generator=g).bfloat16()
+    gout_all = torch.randn(world * tokens, 576, generator=g).bfloat16()
+    xr = x_all.cuda().requires_grad_(True)
+    ref = m(xr)
+    ref.backward(gout_all.cuda())
+    bounds = EP.expert_partition(m.router.n_experts, world)
+    for r in range(world):
+        out, dx, dw_in, dw_sh = (torch.from_numpy(a) for a in got[r])
+        sl = slice(r * tokens, (r + 1) * tokens)
+        lo, hi = bounds[r]
+        assert rel_l2(out, ref.detach().float().cpu()[sl]) < TOL
+        assert rel_l2(dx, xr.grad.float().cpu()[sl]) < TOL
+        assert rel_l2(dw_in, m.W_in.grad.float().cpu()[lo:hi]) < TOL
+        assert rel_l2(dw_sh, m.W_sh_in.grad.float().cpu()) < TOL
