@@ -74,6 +74,9 @@ class EPRank:
         self.pw = view("pw", torch.bfloat16, (self.cap,))
         self.dtw = view("dtw", torch.bfloat16, (self.cap,))
         self.peer_base: List[int] = []        # arena base pointer of every rank, set by the group
+        # the shared experts only need this rank's own tokens: they run on a second stream, under
+        # the pushes, the phase boundaries and the owner's GEMMs
+        self.side = torch.cuda.Stream(device=dev)
 
     @staticmethod
     def capacity(world: int, tokens_per_rank: int, top_k: int, n_experts: int) -> int:
@@ -113,22 +116,37 @@ class EPRank:
                        self.w_all)
 
     def f3_experts(self, w_in, w_out, w_sh_in, w_sh_out, activation: str, keep: bool):
-        """Owner: the grouped GEMMs over the rows that were pushed here; home: the shared experts
-        on x in place (fixed-group schedule)."""
+        """Owner: the grouped GEMMs over the rows that were pushed here. Home: the shared experts
+        on x in place (fixed-group schedule), on the side stream -- call `f3_shared` first if they
+        should also run under the push and the phase boundary."""
         act = MK._act_id(activation)
         self.act = act
+        if getattr(self, "_shared_for", None) is not self.x:
+            self.f3_shared(w_sh_in, w_sh_out, activation, keep)
         hid, a1 = K.up_gemm(self.xs, w_in, self.own_eids, self.own_npp, 0, act, keep)
         K.down_gemm(hid, w_out, self.own_eids, self.own_npp, 0, self.sid, self.pw, self.cap,
                     out=self.y)
         self.a1 = a1
-        self.w_in, self.w_out, self.w_sh_in, self.w_sh_out = w_in, w_out, w_sh_in, w_sh_out
+        self.w_in, self.w_out = w_in, w_out
+
+    def f3_shared(self, w_sh_in, w_sh_out, activation: str, keep: bool):
+        """The shared experts' forward on the side stream (needs only f1's x)."""
+        self.w_sh_in, self.w_sh_out = w_sh_in, w_sh_out
         self.y_sh, self.a1_sh = None, None
-        if self.S:
+        self._shared_for = self.x
+        if not self.S:
+            return
+        act = MK._act_id(activation)
+        main = torch.cuda.current_stream(self.x.device)
+        self.side.wait_stream(main)
+        with torch.cuda.stream(self.side):
             hid_s, self.a1_sh = K.up_gemm(self.x, w_sh_in, None, None, self.S, act, keep)
             self.y_sh = K.down_gemm(hid_s, w_sh_out, None, None, self.S, None, None, 0)
+        self.y_sh.record_stream(main)
 
     def f4_pull(self, aux_coef: float = 0.0, residual: Optional[torch.Tensor] = None):
         """Home: combine, reading every pair's row where it was computed. Returns (out, aux)."""
+        torch.cuda.current_stream(self.x.device).wait_stream(self.side)
         tables = self._peers("y") + ([self.y_sh.data_ptr()] if self.S else [])
         out = K.ep_pull_combine(tables, self.pair_rank, self.pair_row, self.T, self.k + self.S,
                                 self.D, self.x, residual)
@@ -144,6 +162,19 @@ class EPRank:
         K.ep_pad_fix(self.own_offs, self.own_counts, self.n_local, self.douts)
         K.ep_push_rows(self.grad_out, self.k + self.S, self.sids, self.routed_live, self.pair_rank,
                        self.pair_row, self._peers("douts"))
+        self.ydx_sh = None
+        if self.S:      # the shared experts' backward, on the side stream from here on
+            main = torch.cuda.current_stream(self.x.device)
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                da1_s, hidw_s, _ = K.dhidden_glu_bwd(self.grad_out, self.w_sh_out, None, None,
+                                                     self.S, None, None, 0, self.a1_sh, self.act,
+                                                     False)
+                self.ydx_sh = K.dx_gemm(da1_s, self.w_sh_in, None, None, self.S)
+                self.dw_sh_in = K.wgrad(self.x, da1_s, None, self.S, b_grouped=True)
+                self.dw_sh_out = K.wgrad(hidw_s, self.grad_out, None, self.S, a_grouped=True)
+            for t in (self.ydx_sh, self.dw_sh_in, self.dw_sh_out):
+                t.record_stream(main)
 
     def b2_experts(self):
         """Owner: dHidden + GLU backward, dX, both weight gradients of its experts (they stay
@@ -154,18 +185,12 @@ class EPRank:
         K.dx_gemm(da1, self.w_in, self.own_eids, self.own_npp, 0, out=self.ydx)
         self.dw_in = K.wgrad(self.xs, da1, self.own_offs, self.n_local)
         self.dw_out = K.wgrad(hidw, self.douts, self.own_offs, self.n_local)
-        self.ydx_sh = None
-        if self.S:
-            da1_s, hidw_s, _ = K.dhidden_glu_bwd(self.grad_out, self.w_sh_out, None, None, self.S,
-                                                 None, None, 0, self.a1_sh, self.act, False)
-            self.ydx_sh = K.dx_gemm(da1_s, self.w_sh_in, None, None, self.S)
-            self.dw_sh_in = K.wgrad(self.x, da1_s, None, self.S, b_grouped=True)
-            self.dw_sh_out = K.wgrad(hidw_s, self.grad_out, None, self.S, a_grouped=True)
 
     def b3_pull(self, grad_aux: Optional[torch.Tensor] = None):
         """Home: d topk_w and dX rows from the owners, the router's backward, the combine.
         Returns (dx, d_router_w [D, E])."""
         ks = self.k + self.S
+        torch.cuda.current_stream(self.x.device).wait_stream(self.side)
         dtw = K.ep_pull_vec(self._peers("dtw"), self.pair_rank, self.pair_row, self.T, ks, self.k,
                             self.x)
         d_aux = None if grad_aux is None else grad_aux.to(torch.float32).reshape(1)
@@ -273,6 +298,7 @@ class _EPPushBlock(torch.autograd.Function):
         cast = lambda t: None if t is None else t.detach().to(x.dtype).contiguous()
         counts = me.f1_route(x.detach(), router_w.detach(), logit_bias, normalize, full_softmax)
         cnt_all = grp.gather_counts(counts)
+        me.f3_shared(cast(w_sh_in), cast(w_sh_out), activation, keep)
         me.f2_push(cnt_all)
         grp.boundary()
         me.f3_experts(cast(w_in_local), cast(w_out_local), cast(w_sh_in), cast(w_sh_out),
