@@ -719,6 +719,24 @@ def run_ep_workload(args):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t) / steps
     K.check_status(dev)
+    phases = None
+    if push:
+        # a few more steps with an event at every phase start: where the step's time goes on each
+        # rank (pushes and pulls = NVLink, owner phases = GEMMs, waits = the other ranks), and how
+        # many rows each rank owns
+        grp.timing = True
+        for i in range(3):
+            step(i)
+        mine = grp.phase_times()
+        names = list(mine)
+        local = torch.tensor([mine[n] for n in names] + [float(grp.me.own_npp.item())], device=dev)
+        every = [torch.empty_like(local) for _ in range(world)]
+        dist.all_gather(every, local)
+        grp.timing = False
+        table = torch.stack(every).cpu()
+        phases = {"per_rank_ms": {n: [round(float(v), 3) for v in table[:, i]]
+                                  for i, n in enumerate(names)},
+                  "rows_owned_per_rank": [int(v) for v in table[:, -1]]}
     if rank == 0:
         print(json.dumps({
             "metric": "MoE-block tokens/s (fwd+bwd, expert parallel)",
@@ -729,7 +747,8 @@ def run_ep_workload(args):
                                    f"T={T} tokens per GPU, {args.routing} routing, forward + backward, "
                                    + ("rows pushed into / pulled from the owners' buffers "
                                       "through peer pointers (symmetric memory)" if push else
-                                      "dispatch / combine by NCCL all-to-all")}}))
+                                      "dispatch / combine by NCCL all-to-all")},
+            "phases": phases}))
     dist.barrier()
     dist.destroy_process_group()
 

@@ -276,6 +276,29 @@ class SymmetricGroup:
         self.me.peer_base = [int(p) for p in handle.buffer_ptrs]
         self.flag = torch.zeros(1, device=device)
         self.n_experts, self.world = n_experts, world
+        self.timing = False          # set True to collect per-phase CUDA events (see phase_times)
+        self._marks = []
+
+    def mark(self, name: str) -> None:
+        """Start of a phase on the compute stream (only when `timing` is on)."""
+        if self.timing:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._marks.append((name, ev))
+
+    def phase_times(self):
+        """Mean milliseconds per phase over the steps marked so far ({name: ms}), then forgets
+        them. A phase lasts from its mark to the next one; "end" closes the last phase of a step.
+        Synchronises."""
+        torch.cuda.synchronize()
+        total, count = {}, {}
+        for (name, ev), (nxt, ev2) in zip(self._marks, self._marks[1:]):
+            if name == "end":
+                continue
+            total[name] = total.get(name, 0.0) + ev.elapsed_time(ev2)
+            count[name] = count.get(name, 0) + 1
+        self._marks = []
+        return {n: total[n] / count[n] for n in total}
 
     def boundary(self) -> None:
         self.dist.all_reduce(self.flag, group=self.group)
@@ -296,15 +319,22 @@ class _EPPushBlock(torch.autograd.Function):
         keep = any(t is not None and t.requires_grad
                    for t in (x, router_w, w_in_local, w_out_local, w_sh_in, w_sh_out))
         cast = lambda t: None if t is None else t.detach().to(x.dtype).contiguous()
+        grp.mark("route")
         counts = me.f1_route(x.detach(), router_w.detach(), logit_bias, normalize, full_softmax)
         cnt_all = grp.gather_counts(counts)
         me.f3_shared(cast(w_sh_in), cast(w_sh_out), activation, keep)
+        grp.mark("push x")
         me.f2_push(cnt_all)
+        grp.mark("wait 1")
         grp.boundary()
+        grp.mark("owner fwd")
         me.f3_experts(cast(w_in_local), cast(w_out_local), cast(w_sh_in), cast(w_sh_out),
                       activation, keep)
+        grp.mark("wait 2")
         grp.boundary()
+        grp.mark("pull y")
         out, aux = me.f4_pull(aux_coef)
+        grp.mark("end")
         ctx.grp = grp
         ctx.has_shared = w_sh_in is not None
         ctx.router_dtype = router_w.dtype
@@ -318,11 +348,17 @@ class _EPPushBlock(torch.autograd.Function):
         grp, me = ctx.grp, ctx.grp.me
         if grad_out is None:
             grad_out = torch.zeros_like(me.x)
+        grp.mark("push dOut")
         me.b1_push(grad_out)
+        grp.mark("wait 3")
         grp.boundary()
+        grp.mark("owner bwd")
         me.b2_experts()
+        grp.mark("wait 4")
         grp.boundary()
+        grp.mark("pull dX + router bwd")
         dx, d_router = me.b3_pull(grad_aux if me.full_softmax else None)
+        grp.mark("end")
         dsi = me.dw_sh_in if ctx.has_shared else None
         dso = me.dw_sh_out if ctx.has_shared else None
         return (dx, d_router.to(ctx.router_dtype), me.dw_in, me.dw_out, dsi, dso, None, None, None,
