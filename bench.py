@@ -708,10 +708,33 @@ def run_ep_workload(args):
         step(i)
     dist.barrier()
     torch.cuda.synchronize()
+    use_graph = push and not args.no_graph
+    run = step
+    if use_graph:
+        # The peer-memory step has no host read and no data-dependent shape: forward + backward of
+        # both input sets are captured once (collectives included) and replayed, so the ~70
+        # launches of a step cost one submission (eight eager ranks on one host are launch-bound).
+        graphs = []
+        for i in range(2):
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step(i)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            g_i = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_i):
+                step(i)
+            graphs.append(g_i)
+        run = lambda i: graphs[i % 2].replay()
+        for i in range(3):
+            run(i)
+        dist.barrier()
+        torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(steps):
-        step(warmup + i)
+        run(warmup + i)
     e1.record()
     dist.barrier()
     torch.cuda.synchronize()
@@ -748,8 +771,15 @@ def run_ep_workload(args):
                                    + ("rows pushed into / pulled from the owners' buffers "
                                       "through peer pointers (symmetric memory)" if push else
                                       "dispatch / combine by NCCL all-to-all")},
-            "phases": phases}))
+            "cuda_graph": use_graph, "phases": phases}), flush=True)
     dist.barrier()
+    torch.cuda.synchronize()
+    if use_graph:
+        # Graphs that captured collectives are still alive: tearing the process group down under
+        # them did not return (both ranks sat in destroy_process_group until the launcher's
+        # timeout). The results are out and every rank has passed the barrier: leave directly.
+        sys.stdout.flush()
+        os._exit(0)
     dist.destroy_process_group()
 
 

@@ -342,13 +342,16 @@ int moe_b200_ep_pair_map(const int64_t* idx_all, const int32_t* inv_ids, const i
 /* The token permute fused with the dispatch exchange: row src[sorted_ids[s] / k_all] goes to row
  * pair_row[pair] of dst_rows[pair_rank[pair]], for the slots s < *n_live_slots of the home plan
  * (pass pad_offsets + n_experts: the shared experts' runs stay at home). With dst_sid / dst_w (may
- * be NULL) the destination row also gets its own index and the pair's weight w_all[pair]. */
+ * be NULL) the destination row also gets its own index and the pair's weight w_all[pair].
+ * first_slot (device int32, may be NULL = 0): the slot the walk starts at before it wraps around;
+ * pass pad_offsets + bounds[(rank + 1) % n_ranks] so that the ranks write to different owners at
+ * any one time instead of all to the same one. */
 int moe_b200_ep_push_rows(const void* src, int64_t n_tokens, int32_t d_model, int32_t k_all,
-                          const int32_t* sorted_ids, const int32_t* n_live_slots, int64_t max_slots,
-                          const int32_t* pair_rank, const int32_t* pair_row,
-                          const void* const* dst_rows, const void* const* dst_sid,
-                          const void* const* dst_w, int32_t n_ranks, const void* w_all,
-                          void* stream);
+                          const int32_t* sorted_ids, const int32_t* n_live_slots,
+                          const int32_t* first_slot, int64_t max_slots, const int32_t* pair_rank,
+                          const int32_t* pair_row, const void* const* dst_rows,
+                          const void* const* dst_sid, const void* const* dst_w, int32_t n_ranks,
+                          const void* w_all, void* stream);
 
 /* Owner side: zero rows (and, with sid, the sentinel id) in the pad slots
  * [own_offs[e] + own_counts[e], own_offs[e+1]) of every local run. */

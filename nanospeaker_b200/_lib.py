@@ -84,8 +84,8 @@ SIGNATURES = {
         ctypes.c_int, [_c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_vp,
                        _c_vp, _c_vp]),
     "moe_b200_ep_push_rows": (
-        ctypes.c_int, [_c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp,
-                       _c_vp, _c_vp, _c_i32, _c_vp, _c_vp]),
+        ctypes.c_int, [_c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp, _c_i64, _c_vp, _c_vp,
+                       _c_vp, _c_vp, _c_vp, _c_i32, _c_vp, _c_vp]),
     "moe_b200_ep_pad_fix": (
         ctypes.c_int, [_c_vp, _c_vp, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_vp]),
     "moe_b200_ep_pull_combine": (

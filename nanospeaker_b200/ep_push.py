@@ -57,6 +57,7 @@ class EPRank:
         self.E, self.k, self.S, self.D, self.T = n_experts, top_k, n_shared, d_model, tokens_per_rank
         bounds = expert_partition(n_experts, world)
         self.lo, self.hi = bounds[rank]
+        self.next_lo = bounds[(rank + 1) % world][0]
         self.n_local = self.hi - self.lo
         self.cap = self.capacity(world, tokens_per_rank, top_k, n_experts)
         dev = arena.device
@@ -111,9 +112,12 @@ class EPRank:
                                                       self.world)
         K.ep_pad_fix(self.own_offs, self.own_counts, self.n_local, self.xs, self.sid, self.cap)
         self.routed_live = self.offs[self.E: self.E + 1]     # start of the first shared run
+        # every rank starts its walk at its pairs for the next rank's experts, so that at any one
+        # time the ranks write to different owners
+        self.first_slot = self.offs[self.next_lo: self.next_lo + 1]
         K.ep_push_rows(self.x, self.k + self.S, self.sids, self.routed_live, self.pair_rank,
                        self.pair_row, self._peers("xs"), self._peers("sid"), self._peers("pw"),
-                       self.w_all)
+                       self.w_all, first_slot=self.first_slot)
 
     def f3_experts(self, w_in, w_out, w_sh_in, w_sh_out, activation: str, keep: bool):
         """Owner: the grouped GEMMs over the rows that were pushed here. Home: the shared experts
@@ -161,7 +165,7 @@ class EPRank:
         self.grad_out = grad_out.to(self.x.dtype).contiguous()
         K.ep_pad_fix(self.own_offs, self.own_counts, self.n_local, self.douts)
         K.ep_push_rows(self.grad_out, self.k + self.S, self.sids, self.routed_live, self.pair_rank,
-                       self.pair_row, self._peers("douts"))
+                       self.pair_row, self._peers("douts"), first_slot=self.first_slot)
         self.ydx_sh = None
         if self.S:      # the shared experts' backward, on the side stream from here on
             main = torch.cuda.current_stream(self.x.device)

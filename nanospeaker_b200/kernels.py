@@ -448,13 +448,14 @@ def ep_pair_map(idx_all, inv_ids, local_offs, owner_of, send_row0, n_experts: in
 
 
 def ep_push_rows(src, k_all: int, sorted_ids, n_live_slots, pair_rank, pair_row, dst_rows,
-                 dst_sid=None, dst_w=None, w_all=None) -> None:
-    """dst_* are lists of device pointers (ints), one per rank."""
+                 dst_sid=None, dst_w=None, w_all=None, first_slot=None) -> None:
+    """dst_* are lists of device pointers (ints), one per rank; first_slot (1-element int32 device
+    tensor) is where the walk over the slots starts before it wraps around."""
     _need_cuda(src)
     t, d = src.shape
     _lib.check(_lib.load().moe_b200_ep_push_rows(
         src.data_ptr(), t, d, k_all, sorted_ids.data_ptr(), n_live_slots.data_ptr(),
-        sorted_ids.numel(), pair_rank.data_ptr(), pair_row.data_ptr(), _ptr_array(dst_rows),
+        _lib.ptr(first_slot), sorted_ids.numel(), pair_rank.data_ptr(), pair_row.data_ptr(), _ptr_array(dst_rows),
         _ptr_array(dst_sid), _ptr_array(dst_w), len(dst_rows), _lib.ptr(w_all), _stream(src)),
         "moe_b200_ep_push_rows")
     _count(1 if t else 0)
