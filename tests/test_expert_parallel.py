@@ -151,3 +151,23 @@ def test_gloo_two_ranks_match_single_rank():
         assert torch.allclose(dx, x.grad[sl], atol=1e-9)
         assert torch.allclose(dw_in, W_in.grad[lo:hi], atol=1e-9)     # owner-local, no all-reduce
         assert torch.allclose(dw_sh, W_sh.grad, atol=1e-9)            # replicated, all-reduced
+
+
+def test_peer_memory_arena_layout_and_capacity():
+    """Host-side arithmetic of the peer-memory path: the exchange buffers of a rank tile its arena
+    without overlap, 256-byte aligned, and an owner's capacity covers every pair of every rank
+    landing on its experts plus the 128-row padding of each local run."""
+    from nanospeaker_b200 import ep_push, kernels
+    from nanospeaker_b200.expert_parallel import expert_partition
+    world, tokens, k, E, D = 8, 65536, 6, 76, 576
+    cap = ep_push.EPRank.capacity(world, tokens, k, E)
+    n_local = max(hi - lo for lo, hi in expert_partition(E, world))
+    assert cap == kernels.l_cap(world * tokens * k, n_local) and cap % 128 == 0
+    assert cap >= world * tokens * k + n_local * 127
+    layout, size = ep_push.arena_layout(cap, D)
+    sizes = {"xs": cap * D * 2, "douts": cap * D * 2, "y": cap * D * 2, "ydx": cap * D * 2,
+             "sid": cap * 4, "pw": cap * 2, "dtw": cap * 2}
+    spans = sorted((layout[n], layout[n] + sizes[n]) for n in sizes)
+    assert all(lo % 256 == 0 for lo, _ in spans)
+    assert all(a_hi <= b_lo for (_, a_hi), (b_lo, _) in zip(spans, spans[1:]))
+    assert spans[-1][1] <= size and size % 256 == 0
