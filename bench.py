@@ -630,8 +630,22 @@ def run_ours(args):
                                 "unit": top["unit"], "frac": top["frac"],
                                 "traffic": NCU_TRAFFIC_BYTES.get(top["kernel"]),
                                 "peak_source": pk["source"] + " (burst: kernel timed alone)"}
-            if "hbm_frac" in top:   # a GEMM below the ridge: its compulsory-byte floor as well
-                line["roofline"].update({k: top[k] for k in ("hbm_bytes", "hbm_gbs", "hbm_frac")})
+            if "hbm_frac" in top:
+                # A GEMM stage: report the roof that binds it. Its flop per compulsory HBM byte
+                # against the ridge of the measured peaks decides; every GEMM of this block is
+                # below the ridge (~250 flop/B), so the byte floor binds and the tensor figures
+                # ride along.
+                work_flop = top["achieved"] * 1e12 * top["us"] * 1e-6
+                ridge = pk["bf16_tflops"] * 1e12 / (pk["hbm_gbs"] * 1e9)
+                line["roofline"].update({"tensor_tflops": top["achieved"],
+                                         "tensor_frac": top["frac"],
+                                         "flop_per_hbm_byte": round(work_flop / top["hbm_bytes"], 1),
+                                         "ridge_flop_per_byte": round(ridge, 1)})
+                if work_flop / top["hbm_bytes"] < ridge:
+                    line["roofline"].update({"bound": "hbm", "achieved": top["hbm_gbs"],
+                                             "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                             "frac": top["hbm_frac"],
+                                             "algorithmic_bytes": top["hbm_bytes"]})
             line["stages"] = stages
     if world > 1:
         dist.barrier()

@@ -32,7 +32,7 @@ from . import kernels as K
 from . import moe_kernel as MK
 from .expert_parallel import expert_partition
 
-_BUFFERS = (            # name, per-row bytes factor: (columns or None for a vector, dtype)
+_BUFFERS = (            # (name, kind): "rows" = [cap, d_model] bf16, "i32" / "b16" = [cap] vectors
     ("xs", "rows"), ("douts", "rows"), ("y", "rows"), ("ydx", "rows"),
     ("sid", "i32"), ("pw", "b16"), ("dtw", "b16"),
 )
@@ -66,7 +66,11 @@ class EPRank:
         layout, size = arena_layout(self.cap, d_model)
         assert arena.dtype == torch.uint8 and arena.numel() >= size
         self.arena, self.layout = arena, layout
-        view = lambda name, dtype, shape: arena[layout[name]:].view(dtype)[: shape[0] * (shape[1] if len(shape) > 1 else 1)].view(shape)
+
+        def view(name, dtype, shape):
+            n = shape[0] * (shape[1] if len(shape) > 1 else 1)
+            return arena[layout[name]:].view(dtype)[:n].view(shape)
+
         self.xs = view("xs", torch.bfloat16, (self.cap, d_model))
         self.douts = view("douts", torch.bfloat16, (self.cap, d_model))
         self.y = view("y", torch.bfloat16, (self.cap, d_model))

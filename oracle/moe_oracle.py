@@ -348,3 +348,40 @@ class OracleSublayer(torch.nn.Module):
     def forward(self, x: torch.Tensor):
         out = x + self.block(rmsnorm(x, self.gamma, self.eps))
         return out, self.block.aux_loss
+
+
+# --------------------------------------------------------------------- expert-parallel plan
+def ep_plan(cnt_all, bounds, rank: int, cap_tiles: int):
+    """Where the pairs of every home rank live in the owners' slot-ordered buffers, in numpy
+    integers (the reference is single-GPU; this restates the layout rule the peer-memory path
+    defines, to check the CUDA plan kernel bit for bit).
+
+    cnt_all [G, E]: pairs of home rank g routed to expert e. bounds [G+1]: rank r owns experts
+    [bounds[r], bounds[r+1]). An owner's buffer holds its experts' runs in expert order, each run
+    padded to a multiple of 128 rows, and inside a run the home ranks' pairs in rank order (each
+    rank's pairs in the order of its own stable sort, as `plan` gives them).
+
+    Returns for `rank`: owner_of [E], send_row0 [E] (row of its first pair of expert e in the
+    owner's buffer), own_offs [E_r+1], own_counts [E_r], own_npp, own_eids [cap_tiles]."""
+    cnt_all = np.asarray(cnt_all, dtype=np.int64)
+    n_ranks, n_experts = cnt_all.shape
+    tot = cnt_all.sum(0)
+    before = cnt_all[:rank].sum(0)
+    owner_of = np.zeros(n_experts, dtype=np.int32)
+    start = np.zeros(n_experts, dtype=np.int64)
+    for r in range(n_ranks):
+        run = 0
+        for e in range(bounds[r], bounds[r + 1]):
+            owner_of[e] = r
+            start[e] = run
+            run += (tot[e] + ALIGN_M - 1) // ALIGN_M * ALIGN_M
+        if r == rank:
+            live = run
+    lo, hi = bounds[rank], bounds[rank + 1]
+    own_offs = np.concatenate([start[lo:hi], [live]]).astype(np.int32)
+    own_eids = np.zeros(cap_tiles, dtype=np.int32)
+    for e in range(lo, hi):
+        own_eids[start[e] // ALIGN_M: (start[e] + (tot[e] + ALIGN_M - 1) // ALIGN_M * ALIGN_M)
+                 // ALIGN_M] = e - lo
+    return (owner_of, (start + before).astype(np.int32), own_offs, tot[lo:hi].astype(np.int32),
+            int(live), own_eids)

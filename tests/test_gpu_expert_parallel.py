@@ -256,3 +256,34 @@ def test_two_gpus_over_peer_memory_match_the_single_gpu_block():
         assert rel_l2(dx, xr.grad.float().cpu()[sl]) < TOL
         assert rel_l2(dw_in, m.W_in.grad.float().cpu()[lo:hi]) < TOL
         assert rel_l2(dw_sh, m.W_sh_in.grad.float().cpu()) < TOL
+
+
+@pytest.mark.parametrize("world,E,seed", [(8, 76, 0), (2, 76, 1), (3, 7, 2), (4, 200, 3)])
+def test_plan_kernel_matches_the_numpy_plan(world, E, seed):
+    """ep_plan's integers (owner of every expert, first destination row of this rank's pairs,
+    the owner's own 128-aligned offsets / counts / live length / tile map) bit for bit, with empty
+    experts and empty ranks in the count matrix."""
+    import numpy as np
+    from nanospeaker_b200 import kernels as K
+    from nanospeaker_b200.expert_parallel import expert_partition
+    from oracle import moe_oracle as O
+    rng = np.random.default_rng(seed)
+    cnt = rng.integers(0, 700, size=(world, E)).astype(np.int32)
+    cnt[:, rng.integers(0, E, size=max(E // 5, 1))] = 0          # experts nobody picked
+    cnt[rng.integers(0, world)] = 0                              # a rank without tokens
+    bounds = [lo for lo, _ in expert_partition(E, world)] + [E]
+    cap = K.l_cap(int(cnt.sum()), max(b - a for a, b in zip(bounds, bounds[1:])))
+    cnt_d = torch.from_numpy(cnt).cuda()
+    bounds_d = torch.tensor(bounds, dtype=torch.int32, device="cuda")
+    for rank in range(world):
+        n_local = bounds[rank + 1] - bounds[rank]
+        got = K.ep_plan(cnt_d, bounds_d, rank, n_local, cap // 128)
+        want = O.ep_plan(cnt, bounds, rank, cap // 128)
+        live = want[4]
+        assert np.array_equal(got[0].cpu().numpy(), want[0])
+        assert np.array_equal(got[1].cpu().numpy(), want[1])
+        assert np.array_equal(got[2].cpu().numpy(), want[2])
+        assert np.array_equal(got[3].cpu().numpy()[:n_local], want[3])
+        assert int(got[4]) == live
+        assert np.array_equal(got[5].cpu().numpy()[: live // 128], want[5][: live // 128])
+        assert not got[5].cpu().numpy()[live // 128:].any()
