@@ -797,6 +797,71 @@ def run_ep_workload(args):
     dist.destroy_process_group()
 
 
+def run_ep_loopback(args):
+    """The peer-memory expert-parallel step with G virtual ranks on ONE GPU (`--gpus G`, default 2):
+    every "peer" buffer is local, so this times the kernels and the plan without NVLink, phase by
+    phase (CUDA events; ms per rank), and gives ncu something to capture on a single GPU."""
+    from nanospeaker_b200 import MoEBlock, ep_push, kernels as K
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    world, T = max(args.gpus, 2), args.ep_tokens
+    w, _ = init_weights()
+    m = MoEBlock(D_MODEL, N_EXPERTS, d_ff=D_FF, top_k=TOP_K, n_shared=N_SHARED,
+                 capacity_factor=None).to(torch.bfloat16)
+    with torch.no_grad():
+        for name in ("W_in", "W_out", "W_sh_in", "W_sh_out"):
+            getattr(m, name).copy_(w[name])
+        m.router.W.copy_(w["router_W"])
+    m = m.to(dev).eval()
+    grp = ep_push.LoopbackGroup(world, N_EXPERTS, TOP_K, N_SHARED, D_MODEL, T, dev)
+    g = torch.Generator().manual_seed(100)
+    xs = [torch.randn(T, D_MODEL, generator=g).bfloat16().to(dev) for _ in range(world)]
+    gs = [torch.randn(T, D_MODEL, generator=g).bfloat16().to(dev) for _ in range(world)]
+    R = grp.ranks
+    names = ["route", "plan + push x", "owner fwd", "pull y", "push dOut", "owner bwd",
+             "pull dX + router bwd"]
+    total = [0.0] * len(names)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    W_in, W_out = m.W_in.detach(), m.W_out.detach()
+    local = [(W_in[r.lo:r.hi].contiguous(), W_out[r.lo:r.hi].contiguous()) for r in R]
+    for it in range(warmup + steps):
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
+        e[0].record()
+        cnt = torch.stack([r.f1_route(x, m.router.W.detach(), None, True, False)
+                           for r, x in zip(R, xs)])
+        e[1].record()
+        for r in R:
+            r.f2_push(cnt)
+        e[2].record()
+        for r, (wi, wo) in zip(R, local):
+            r.f3_experts(wi, wo, m.W_sh_in.detach(), m.W_sh_out.detach(), "silu", True)
+        e[3].record()
+        for r in R:
+            r.f4_pull(0.0)
+        e[4].record()
+        for r, go in zip(R, gs):
+            r.b1_push(go)
+        e[5].record()
+        for r in R:
+            r.b2_experts()
+        e[6].record()
+        for r in R:
+            r.b3_pull()
+        e[7].record()
+        torch.cuda.synchronize()
+        if it >= warmup:
+            for i in range(len(names)):
+                total[i] += e[i].elapsed_time(e[i + 1]) / world / steps
+    K.check_status(dev)
+    print(json.dumps({
+        "metric": "expert-parallel step, virtual ranks on one GPU (ms per rank)",
+        "value": sum(total), "unit": "ms", "higher_is_better": False, "n_gpus": 1,
+        "steps": steps, "warmup": warmup,
+        "config": {"workload": f"{world} virtual ranks x T={T} tokens, 76 experts partitioned, "
+                               "forward + backward, peer buffers local (no NVLink)"},
+        "phases_ms_per_rank": {n: round(v, 3) for n, v in zip(names, total)}}))
+
+
 def run_side_workload(args):
     """The two forward-only workloads of the block's other callers, one JSON line each (not the
     headline): `decode` = 20 stacked blocks on T=64 tokens replayed from one CUDA graph
@@ -934,7 +999,10 @@ def main():
                     help="time eager module calls instead of a captured CUDA graph of the step")
     ap.add_argument("--profile-stage", default="",
                     help="run only the stage whose name contains this text, 3 launches (for ncu)")
-    ap.add_argument("--workload", default="train", choices=["train", "decode", "prefill", "sublayer", "ep"],
+    ap.add_argument("--ep-tokens", type=int, default=16384,
+                    help="ep-loopback workload: tokens per virtual rank")
+    ap.add_argument("--workload", default="train",
+                    choices=["train", "decode", "prefill", "sublayer", "ep", "ep-loopback"],
                     help="train = the headline (forward + backward, T=16384); decode / prefill = "
                          "the forward-only workloads of the block's other callers; sublayer = "
                          "x + ffn(rmsnorm(x)) forward + backward at T=16384, fused node against "
@@ -950,7 +1018,9 @@ def main():
     args = ap.parse_args()
     global SKEW_NAME, BIAS_STD
     SKEW_NAME, BIAS_STD = args.skew, SKEWS[args.skew]
-    if args.workload == "ep":
+    if args.workload == "ep-loopback":
+        run_ep_loopback(args)
+    elif args.workload == "ep":
         run_ep_workload(args)
     elif args.workload != "train":
         run_side_workload(args)

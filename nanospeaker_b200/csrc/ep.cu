@@ -165,7 +165,8 @@ __global__ void __launch_bounds__(256)
     if (lane == 0 && sid.p[r] != nullptr) static_cast<int32_t*>(sid.p[r])[row] = int32_t(row);
     if (lane == 1 && pw.p[r] != nullptr) static_cast<__nv_bfloat16*>(pw.p[r])[row] = w_all[pair];
   }
-  __threadfence_system();
+  // no fence here: the rows are read by other GPUs only after this kernel has completed and a
+  // stream-ordered collective has passed, which makes its stores visible system-wide
 }
 
 // Owner side: the pad slots of every local run -- rows [offs[e] + counts[e], offs[e + 1]) -- get
@@ -211,10 +212,11 @@ __global__ void __launch_bounds__(256)
     const int64_t t = i / chunks_per_row;
     const int c = int(i - t * chunks_per_row);
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int j0 = 0; j0 < k_all; j0 += 4) {   // four rows in flight
-      Chunk16 v[4];
+    constexpr int INFLIGHT = 8;   // rows in flight per thread (a remote load takes microseconds)
+    for (int j0 = 0; j0 < k_all; j0 += INFLIGHT) {
+      Chunk16 v[INFLIGHT];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < INFLIGHT; ++u) {
         v[u].w[0] = v[u].w[1] = v[u].w[2] = v[u].w[3] = 0u;
         if (j0 + u < k_all) {
           const int64_t p = t * k_all + j0 + u;
@@ -222,7 +224,7 @@ __global__ void __launch_bounds__(256)
         }
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < INFLIGHT; ++u)
         if (j0 + u < k_all) ep_acc8(acc, v[u]);
     }
     if (extra != nullptr) ep_acc8(acc, extra[i]);
