@@ -13,6 +13,12 @@ Prints ONE JSON line (rank 0). `value` times K steps with inputs resident in HBM
 the same step through MoEBlock.forward/backward with the step's input copied from pinned host
 memory and the loss read back. `--impl reference` times the CPU oracle (the reference's
 pure-PyTorch path restated, see oracle/moe_oracle.py) on the host cores instead.
+
+Side workloads, one JSON line each, not the headline (`--workload`): `decode` (20 stacked blocks,
+T=64, one CUDA graph), `prefill` (T=131072 forward), `sublayer` (x + ffn(rmsnorm(x))), `ep` (experts
+partitioned over the ranks under torchrun: `--ep-impl push | nccl`, `--routing uniform | hotspot`),
+`ep-loopback` (the same step with virtual ranks on one GPU). `--skew literal1.5` switches the
+headline's routing bias to the literal N(0, 1.5).
 """
 import argparse
 import json
