@@ -171,3 +171,37 @@ def test_peer_memory_arena_layout_and_capacity():
     assert all(lo % 256 == 0 for lo, _ in spans)
     assert all(a_hi <= b_lo for (_, a_hi), (b_lo, _) in zip(spans, spans[1:]))
     assert spans[-1][1] <= size and size % 256 == 0
+
+
+@pytest.mark.parametrize("world,E,seed", [(8, 76, 0), (3, 7, 1), (2, 5, 2)])
+def test_numpy_plan_of_the_peer_memory_layout_tiles_every_run(world, E, seed):
+    """The layout rule itself (oracle.ep_plan; the reference has no multi-GPU form to pin it to):
+    for every expert the home ranks' row ranges [send_row0, send_row0 + count) follow one another
+    in rank order and fill exactly the first `total` rows of the owner's 128-aligned run; runs of an
+    owner follow one another without gaps; the tile map names the run every live tile lies in."""
+    import numpy as np
+    from nanospeaker_b200.expert_parallel import expert_partition
+    from oracle import moe_oracle as O
+    rng = np.random.default_rng(seed)
+    cnt = rng.integers(0, 400, size=(world, E))
+    cnt[:, rng.integers(0, E)] = 0
+    bounds = [lo for lo, _ in expert_partition(E, world)] + [E]
+    plans = [O.ep_plan(cnt, bounds, r, 4096) for r in range(world)]
+    tot = cnt.sum(0)
+    for e in range(E):
+        owner = int(plans[0][0][e])
+        assert bounds[owner] <= e < bounds[owner + 1]
+        assert all(int(p[0][e]) == owner for p in plans)
+        run_start = int(plans[owner][2][e - bounds[owner]])
+        nxt = run_start
+        for r in range(world):                       # rank order inside the run, no gaps
+            assert int(plans[r][1][e]) == nxt
+            nxt += int(cnt[r, e])
+        assert nxt == run_start + tot[e]
+        assert int(plans[owner][3][e - bounds[owner]]) == tot[e]
+    for r in range(world):
+        _, _, offs, counts, live, eids = plans[r]
+        assert offs[0] == 0 and offs[-1] == live and live % 128 == 0
+        for i in range(len(counts)):
+            assert offs[i + 1] - offs[i] == (counts[i] + 127) // 128 * 128
+            assert (eids[offs[i] // 128: offs[i + 1] // 128] == i).all()
