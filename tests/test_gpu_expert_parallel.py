@@ -287,3 +287,34 @@ def test_plan_kernel_matches_the_numpy_plan(world, E, seed):
         assert int(got[4]) == live
         assert np.array_equal(got[5].cpu().numpy()[: live // 128], want[5][: live // 128])
         assert not got[5].cpu().numpy()[live // 128:].any()
+
+
+def test_push_pull_ranks_without_shared_experts():
+    """The same comparison for a block without shared experts (no local extra buffer, the whole
+    slot order is pushed) and with other sizes: E=16 over 4 ranks, top-2, D=192."""
+    from nanospeaker_b200 import MoEBlock, ep_push, kernels
+    from nanospeaker_b200 import expert_parallel as EP
+    torch.manual_seed(3)
+    world, tokens, E, k, D = 4, 500, 16, 2, 192
+    m = MoEBlock(D, E, d_ff=192, top_k=k, n_shared=0, capacity_factor=None)
+    with torch.no_grad():
+        m.router.W.copy_(torch.randn(D, E) * 0.05)
+        m.W_in.copy_(torch.randn(E, D, 256) * D ** -0.5)
+        m.W_out.copy_(torch.randn(E, 128, D) * 128 ** -0.5)
+    m = m.to(torch.bfloat16).cuda().eval()
+    x_all = torch.randn(world * tokens, D, device="cuda").bfloat16()
+    gout = torch.randn_like(x_all)
+    xr = x_all.clone().requires_grad_(True)
+    ref = m(xr)
+    ref.backward(gout)
+    grp = ep_push.LoopbackGroup(world, E, k, 0, D, tokens, x_all.device)
+    outs = grp.forward(list(x_all.split(tokens)), m.router, m.W_in.detach(), m.W_out.detach(),
+                       None, None, "silu")
+    assert rel_l2(torch.cat([o for o, _ in outs]), ref.detach().float()) < TOL
+    grads = grp.backward(list(gout.split(tokens)))
+    assert rel_l2(torch.cat([g[0] for g in grads]), xr.grad.float()) < TOL
+    for r, (lo, hi) in enumerate(EP.expert_partition(E, world)):
+        assert rel_l2(grads[r][2], m.W_in.grad[lo:hi].float()) < TOL
+        assert rel_l2(grads[r][3], m.W_out.grad[lo:hi].float()) < TOL
+    assert rel_l2(sum(g[1].float() for g in grads), m.router.W.grad.float()) < 2e-2
+    kernels.check_status("cuda")
