@@ -7,7 +7,9 @@ the reference. Only tests/, __graft_entry__.smoke() and the CPU-baseline leg of 
 
 Parity pinning: tests/test_oracle.py checks every function here (a) against golden vectors that
 tests/golden/make_golden.py produced by running the unmodified reference modules, and (b), when a
-checkout of the reference is present, against the reference imported live.
+checkout of the reference is present, against the reference imported live. One exception:
+`ep_plan` at the end restates this repository's own multi-GPU layout rule (the reference is
+single-GPU and has nothing to pin it to); its properties are checked in tests/test_expert_parallel.py.
 
 Everything takes and returns CPU tensors. fp32 in -> the reference's fp32 path; bf16 in -> its
 bf16 path (each op rounds to bf16 as eager PyTorch does).
