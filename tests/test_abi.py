@@ -91,6 +91,26 @@ def test_arguments_are_validated_before_any_launch(lib):
     assert wg(256, 2048, 1, null) == -1 # gather needs the routed schedule
     assert wg(256, 2048, 0, p, 3) == -1 # groups beyond n_first need dw_extra
     assert wg(256, 2048, 0, p) == -4    # scratch too small
+    # expert-parallel entry points: shapes first, then NULL / misaligned pointers, nothing launched
+    assert lib.moe_b200_ep_plan(p, p, 9, 76, 0, p, p, p, p, p, p, 8, null) == -1     # > 8 ranks
+    assert lib.moe_b200_ep_plan(p, p, 8, 76, 8, p, p, p, p, p, p, 8, null) == -1     # rank >= world
+    assert lib.moe_b200_ep_plan(null, p, 8, 76, 0, p, p, p, p, p, p, 8, null) == -2
+    assert lib.moe_b200_ep_pair_map(p, p, p, p, p, 0, 8, 76, 8, p, p, null) == 0     # no tokens
+    assert lib.moe_b200_ep_pair_map(p, p, p, p, p, 4, 8, 76, 9, p, p, null) == -1
+    assert lib.moe_b200_ep_pair_map(null, p, p, p, p, 4, 8, 76, 8, p, p, null) == -2
+    two = (ctypes.c_void_p * 2)(p.value, p.value + 8)                                # 2nd misaligned
+    ok2 = (ctypes.c_void_p * 2)(p.value, p.value)
+    assert lib.moe_b200_ep_push_rows(p, 4, 100, 8, p, p, null, 128, p, p, ok2, null, null, 2, null,
+                                     null) == -1                                      # D % 8
+    assert lib.moe_b200_ep_push_rows(p, 4, 64, 8, p, p, null, 128, p, p, two, null, null, 2, null,
+                                     null) == -3                                      # alignment
+    assert lib.moe_b200_ep_push_rows(p, 4, 64, 8, p, p, null, 128, p, p, ok2, null, ok2, 2, null,
+                                     null) == -2                                      # weights missing
+    assert lib.moe_b200_ep_pad_fix(p, p, 0, null, 64, null, 0, null) == 0             # no local experts
+    assert lib.moe_b200_ep_pad_fix(p, p, 3, null, 64, null, 0, null) == -2
+    assert lib.moe_b200_ep_pull_combine(ok2, 10, p, p, 4, 8, 64, null, p, null) == -1  # > 9 tables
+    assert lib.moe_b200_ep_pull_combine(two, 2, p, p, 4, 8, 64, null, p, null) == -3
+    assert lib.moe_b200_ep_pull_vec(ok2, 2, p, p, 4, 8, 9, p, null) == -1             # top_k > k_all
     pb = ctypes.c_size_t(0)
     assert lib.moe_b200_wgrad_scratch_bytes(576, 256, 108032, 76, 1, 2048, ctypes.byref(pb)) == 0
     assert pb.value == 4096 + (108032 // 2048 + 76) * 5 * 128 * 256 * 4   # item table + tiles
