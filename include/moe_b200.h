@@ -256,6 +256,23 @@ int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void*
                        const int32_t* sorted_ids, const void* pair_w, int64_t n_pairs, void* y,
                        const void* bias, int32_t* status, void* stream);
 
+/* The down GEMM fused with the combine: instead of storing per-pair rows, every live row is ADDED to
+ * row sorted_ids[row] / top_k of the token-major matrix acc [n_tokens, d_model] (bf16; the caller
+ * fills it first: zeros, or a residual / other summand). One asynchronous bulk reduction per row
+ * and 192-column tile; the adds are bf16 atomics performed in L2, so the k rows of a token are
+ * summed in bf16 in whatever order they arrive (what out.index_add_ does in the reference's eager
+ * path, src/model/moe.py:407-413, there in expert order) and no y [l_cap, d_model] is written or
+ * read back. The store-then-reduce pair moe_b200_down_gemm + moe_b200_combine (fp32 sum in pair
+ * order, bitwise reproducible) is the reference's choice (src/model/moe_kernel.py:26-30, 362-365,
+ * 579-582); this is the atomic variant it weighs it against. Fixed schedule: row r of every group
+ * is added to row r of acc (rows <= n_tokens). Other arguments as moe_b200_down_gemm. */
+int moe_b200_down_gemm_acc(const void* hid, int64_t rows, int32_t k_dim, const void* w_out,
+                           int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_model,
+                           const int32_t* expert_ids, const int32_t* n_post_pad,
+                           int32_t n_fixed_groups, const int32_t* sorted_ids, const void* pair_w,
+                           int64_t n_pairs, int32_t top_k, void* acc, int64_t n_tokens,
+                           const void* bias, int32_t* status, void* stream);
+
 /* Backward through the down GEMM and the GLU in one kernel: G = douts[row] @ w_out[e]^T, then with
  * [g | u] = a1[row] and w = pair_w[pair]:  dtw[pair] = <G, act(g)*u>,
  * da1[row] = [w*G*u*act'(g) | w*G*act(g)],  hidw[row] = w * act(g) * u.
@@ -280,6 +297,17 @@ int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void
                      int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_model, const int32_t* expert_ids,
                      const int32_t* n_post_pad, int32_t n_fixed_groups, void* ydx,
                      int32_t* status, void* stream);
+
+/* The dX GEMM fused with the combine: row `row` of da1 @ w_in[e]^T is added to row
+ * sorted_ids[row] / top_k of acc [n_tokens, d_model] (bf16, filled by the caller), as
+ * moe_b200_down_gemm_acc does for the forward. Replaces the dX use of _gemm2_kernel together with
+ * the _reduce_kernel pass behind it (src/model/moe_kernel.py:696-710). */
+int moe_b200_dx_gemm_acc(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,
+                         int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_model,
+                         const int32_t* expert_ids, const int32_t* n_post_pad,
+                         int32_t n_fixed_groups, const int32_t* sorted_ids, int64_t n_pairs,
+                         int32_t top_k, void* acc, int64_t n_tokens, int32_t* status,
+                         void* stream);
 
 /* Bytes of fp32 scratch moe_b200_wgrad needs for its partial tiles (contents arbitrary).
  * routed != 0: the pad_offsets schedule over `rows` = l_cap rows. ks_rows as for moe_b200_wgrad. */

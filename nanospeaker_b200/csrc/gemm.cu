@@ -411,6 +411,114 @@ int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void
       tmA, tmB, tmB2, tmOut, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
 }
 
+// Ring stages / staging buffers of the two accumulating row GEMMs (shared memory per CTA: stages x
+// 40 KB + buffers x 50 KB at 192-column tiles).
+#ifndef MOE_RED_DOWN_STAGES
+#define MOE_RED_DOWN_STAGES 3
+#endif
+#ifndef MOE_RED_DOWN_BUFS
+#define MOE_RED_DOWN_BUFS 2
+#endif
+#ifndef MOE_RED_DX_STAGES
+#define MOE_RED_DX_STAGES 3
+#endif
+#ifndef MOE_RED_DX_BUFS
+#define MOE_RED_DX_BUFS 2
+#endif
+
+// Where an accumulating GEMM adds its rows: routed schedule -> row sorted_ids[slot] / top_k of
+// acc [n_tokens, d_model]; fixed schedule -> row `row` (every group adds to the same rows).
+static int check_acc(int32_t n_fixed_groups, int64_t rows, const int32_t* sorted_ids, int32_t top_k,
+                     int64_t n_pairs, const void* acc, int64_t n_tokens, int32_t d_model) {
+  if (!acc) return MOE_B200_ERR_NULL;
+  if ((reinterpret_cast<uintptr_t>(acc) & 15u) != 0) return MOE_B200_ERR_ALIGN;
+  if (d_model % 32 != 0 || n_tokens < 1) return MOE_B200_ERR_SHAPE;
+  if (n_fixed_groups > 0) return rows <= n_tokens ? MOE_B200_OK : MOE_B200_ERR_SHAPE;
+  if (!sorted_ids) return MOE_B200_ERR_NULL;
+  if (top_k < 1 || n_pairs < 0 || n_pairs > n_tokens * int64_t(top_k)) return MOE_B200_ERR_SHAPE;
+  return MOE_B200_OK;
+}
+
+int moe_b200_down_gemm_acc(const void* hid, int64_t rows, int32_t k_dim, const void* w_out,
+                           int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_model,
+                           const int32_t* expert_ids, const int32_t* n_post_pad,
+                           int32_t n_fixed_groups, const int32_t* sorted_ids, const void* pair_w,
+                           int64_t n_pairs, int32_t top_k, void* acc, int64_t n_tokens,
+                           const void* bias, int32_t* status, void* stream) {
+  CHECK_SCHED();
+  if (bias && (n_fixed_groups > 0 || (reinterpret_cast<uintptr_t>(bias) & 15u) != 0))
+    return n_fixed_groups > 0 ? MOE_B200_ERR_SHAPE : MOE_B200_ERR_ALIGN;
+  if (k_dim % 8 != 0 || k_dim < 64 || d_model % 32 != 0) return MOE_B200_ERR_UNSUPPORTED;
+  if (!hid || !w_out) return MOE_B200_ERR_NULL;
+  if (!aligned16(hid) || !aligned16(w_out)) return MOE_B200_ERR_ALIGN;
+  const int rca = check_acc(n_fixed_groups, rows, sorted_ids, top_k, n_pairs, acc, n_tokens, d_model);
+  if (rca != MOE_B200_OK) return rca;
+  CHECK_EXTRA();
+  const int gdim = n_fixed_groups > 0 ? n_fixed_groups : 1;
+  CUtensorMap tmA, tmB, tmB2;
+  int32_t fused = 0;
+  if (!map_rows_kmajor(&tmA, hid, gdim, rows, k_dim) ||
+      !map_weight_mnmajor(&tmB, w_out, n_groups, k_dim, d_model, 3, &fused))
+    return MOE_B200_ERR_TMA;
+  tmB2 = tmB;
+  if (n_extra > 0 && !map_weight_mnmajor(&tmB2, w_extra, n_extra, k_dim, d_model, 3, &fused))
+    return MOE_B200_ERR_TMA;
+  RowsArgs g = base_args(expert_ids, n_post_pad, n_fixed_groups, rows, status);
+  g.a_grouped = n_fixed_groups > 0;
+  g.num_k = (k_dim + BK - 1) / BK;
+  g.n_dim = d_model;
+  g.n_chunks = (d_model + 191) / 192;
+  g.b_fused = fused;
+  g.sorted_ids = sorted_ids;
+  g.n_pairs = int32_t(n_pairs);
+  g.top_k = top_k;
+  g.pair_w = static_cast<const __nv_bfloat16*>(pair_w);
+  g.bias = static_cast<const __nv_bfloat16*>(bias);
+  g.out = static_cast<__nv_bfloat16*>(acc);
+  g.ld_out = d_model;
+  g.n_groups_b1 = n_extra > 0 ? n_groups : INT32_MAX;
+  return launch_rows<192, MOE_RED_DOWN_STAGES, true, EPI_SCALE_RED, false, MOE_RED_DOWN_BUFS>(
+      tmA, tmB, tmB2, tmB, g, max_tiles(rows, g.n_chunks, n_fixed_groups),
+      static_cast<cudaStream_t>(stream));
+}
+
+int moe_b200_dx_gemm_acc(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,
+                         int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_model,
+                         const int32_t* expert_ids, const int32_t* n_post_pad,
+                         int32_t n_fixed_groups, const int32_t* sorted_ids, int64_t n_pairs,
+                         int32_t top_k, void* acc, int64_t n_tokens, int32_t* status,
+                         void* stream) {
+  CHECK_SCHED();
+  if (d_hidden % 4 != 0 || d_hidden < 32 || d_model % 32 != 0) return MOE_B200_ERR_UNSUPPORTED;
+  if (!da1 || !w_in) return MOE_B200_ERR_NULL;
+  if (!aligned16(da1) || !aligned16(w_in)) return MOE_B200_ERR_ALIGN;
+  const int rca = check_acc(n_fixed_groups, rows, sorted_ids, top_k, n_pairs, acc, n_tokens, d_model);
+  if (rca != MOE_B200_OK) return rca;
+  CHECK_EXTRA();
+  const int gdim = n_fixed_groups > 0 ? n_fixed_groups : 1;
+  CUtensorMap tmA, tmB, tmB2;
+  if (!map_rows_kmajor(&tmA, da1, gdim, rows, 2 * d_hidden) ||
+      !map_weight_kmajor(&tmB, w_in, n_groups, d_model, 2 * d_hidden, 192))
+    return MOE_B200_ERR_TMA;
+  tmB2 = tmB;
+  if (n_extra > 0 && !map_weight_kmajor(&tmB2, w_extra, n_extra, d_model, 2 * d_hidden, 192))
+    return MOE_B200_ERR_TMA;
+  RowsArgs g = base_args(expert_ids, n_post_pad, n_fixed_groups, rows, status);
+  g.a_grouped = n_fixed_groups > 0;
+  g.num_k = (2 * d_hidden + BK - 1) / BK;
+  g.n_dim = d_model;
+  g.n_chunks = (d_model + 191) / 192;
+  g.sorted_ids = sorted_ids;
+  g.n_pairs = int32_t(n_pairs);
+  g.top_k = top_k;
+  g.out = static_cast<__nv_bfloat16*>(acc);
+  g.ld_out = d_model;
+  g.n_groups_b1 = n_extra > 0 ? n_groups : INT32_MAX;
+  return launch_rows<192, MOE_RED_DX_STAGES, false, EPI_RAW_RED, false, MOE_RED_DX_BUFS>(
+      tmA, tmB, tmB2, tmB, g, max_tiles(rows, g.n_chunks, n_fixed_groups),
+      static_cast<cudaStream_t>(stream));
+}
+
 // The scratch buffer starts with the item table ([G + 1] int32), the partial tiles follow.
 constexpr size_t WGRAD_TABLE_BYTES = 4096;
 static_assert((WGRAD_MAX_GROUPS + 1) * sizeof(int32_t) <= WGRAD_TABLE_BYTES, "item table too small");

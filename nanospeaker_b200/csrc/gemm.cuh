@@ -25,7 +25,11 @@ constexpr int BM = 128;  // UMMA M: one TMEM lane per output row
 constexpr int BK = 64;   // 64 bf16 = one 128-byte swizzle span
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 
-enum GemmEpi { EPI_RAW = 0, EPI_GLU = 1, EPI_SCALE = 2, EPI_GLUBWD = 3 };
+// EPI_RAW_RED / EPI_SCALE_RED: as EPI_RAW / EPI_SCALE, but a row is not stored in slot order: it is
+// added (bf16 atomics in L2, one bulk reduction per row and tile) to row `token` of a token-major
+// matrix, which makes the GEMM also the combine.
+enum GemmEpi { EPI_RAW = 0, EPI_GLU = 1, EPI_SCALE = 2, EPI_GLUBWD = 3, EPI_RAW_RED = 4,
+               EPI_SCALE_RED = 5 };
 enum Act { ACT_SILU = 0, ACT_GELU = 1, ACT_RELU = 2, ACT_SIGMOID = 3, ACT_TANH = 4 };
 
 // Status codes a kernel can leave in the status word (0 = fine).

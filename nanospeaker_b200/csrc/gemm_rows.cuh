@@ -14,8 +14,16 @@ constexpr int ROWS_THREADS_GATHER = ROWS_THREADS + (GATHER_WARPS - 1) * 32;
 // into shared memory by TMA one tile ahead (with per-thread global loads the epilogue waited for
 // them tile after tile: dHidden took 77 us with those loads, 50 us without).
 __host__ __device__ constexpr bool epi_loads_aux(int epi) { return epi == EPI_GLUBWD; }
+// The reducing epilogues hand their staged tiles to RED_WARPS more warps, which issue the atomic
+// adds: those stall on the L2's atomic throughput, and the epilogue warps would otherwise stand
+// still with them instead of draining the next accumulator.
+constexpr int RED_WARPS = 4;
+__host__ __device__ constexpr bool epi_reduces(int epi) {
+  return epi == EPI_RAW_RED || epi == EPI_SCALE_RED;
+}
 __host__ __device__ constexpr int rows_threads(int epi, bool gather) {
-  return (gather ? ROWS_THREADS_GATHER : ROWS_THREADS) + (epi_loads_aux(epi) ? 32 : 0);
+  return (gather ? ROWS_THREADS_GATHER : ROWS_THREADS) + (epi_loads_aux(epi) ? 32 : 0) +
+         (epi_reduces(epi) ? RED_WARPS * 32 : 0);
 }
 
 // Epilogues that leave through TMA stage the tile in shared memory one 64-column box (128 rows x
@@ -24,6 +32,10 @@ constexpr int OUT_BOX_BYTES = BM * 128;
 __host__ __device__ constexpr bool epi_uses_tma_store(int epi) {
   return epi == EPI_RAW || epi == EPI_SCALE;
 }
+// Epilogues that reduce into a token-major matrix stage the whole tile row by row (BN bf16 + 16
+// bytes of padding per row, so that the 32 rows a warp writes at once spread over all banks) in
+// OUT_BOXES buffers used in turn; the reducer warps read them back as whole rows.
+__host__ __device__ constexpr int red_row_bytes(int bn) { return bn * 2 + 16; }
 // OUT_BOXES = number of staging boxes. The stores are asynchronous: the epilogue warps only wait when a buffer
 // comes round again, so the boxes in flight are what keeps HBM writing while the warps already
 // work on the next tile. (With direct stores, and with two boxes, the time to write the output
@@ -34,7 +46,10 @@ struct RowsSmem {
   static constexpr int B_STAGE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int STAGING_OFFSET = STAGES * STAGE_BYTES;  // 1024-byte aligned
-  static constexpr int STAGING_BYTES = epi_uses_tma_store(EPI) ? OUT_BOXES * OUT_BOX_BYTES : 0;
+  static constexpr int RED_TILE_BYTES = (BM * red_row_bytes(BN) + 1023) / 1024 * 1024;
+  static constexpr int STAGING_BYTES = epi_uses_tma_store(EPI) ? OUT_BOXES * OUT_BOX_BYTES
+                                       : epi_reduces(EPI)      ? OUT_BOXES * RED_TILE_BYTES
+                                                               : 0;
   static constexpr int AUX_OFFSET = STAGING_OFFSET + STAGING_BYTES;  // 1024-byte aligned
   static constexpr int AUX_TILE_BYTES = BM * 2 * BN * 2;             // [128 x 2 BN] bf16
   static constexpr int BAR_OFFSET = AUX_OFFSET + (epi_loads_aux(EPI) ? 2 * AUX_TILE_BYTES : 0);
@@ -43,7 +58,8 @@ struct RowsSmem {
   static constexpr int MISC_OFFSET = BAR_OFFSET + 8 * N_BARS;      // tmem slot, abort flag
   static constexpr int PART_OFFSET = MISC_OFFSET + 16;             // float[128] dtw partials
   static constexpr int TOK_OFFSET = PART_OFFSET + 128 * 4;         // int[128] gathered row ids
-  static constexpr int TOTAL = TOK_OFFSET + 128 * 4;
+  static constexpr int RED_TOK_OFFSET = TOK_OFFSET + 128 * 4;      // int[OUT_BOXES][128] tokens of the staged rows
+  static constexpr int TOTAL = RED_TOK_OFFSET + (epi_reduces(EPI) ? OUT_BOXES * 128 * 4 : 0);
   static constexpr int DYNAMIC = TOTAL + 1024;  // slack for manual 1024-byte alignment
 };
 
@@ -219,8 +235,10 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar + b, 1);
       mbar_init(tempty_bar + b, EPI_WARPS);
-      mbar_init(afull_bar + b, 1);
-      mbar_init(aempty_bar + b, EPI_WARPS);
+      // (the reducing epilogues use this pair for their staging buffers: filled by the epilogue
+      // warps, drained by the reducer warps)
+      mbar_init(afull_bar + b, epi_reduces(EPI) ? EPI_WARPS : 1);
+      mbar_init(aempty_bar + b, epi_reduces(EPI) ? RED_WARPS : EPI_WARPS);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -413,6 +431,68 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
         umma_commit(tfull_bar + b);
       }
     }
+  } else if (epi_reduces(EPI) && warp >= 2 + EPI_WARPS) {
+    // ------------------------------------------------------------------------ reducers
+    // Staged tile -> token-major output: thread i takes the 16-byte pieces i, i + 128, ... of the
+    // tile in row-major order, so a warp's adds cover whole rows (full lines for the L2's atomic
+    // units); red.global is fire-and-forget, the waiting happens in the queues behind it.
+    if constexpr (epi_reduces(EPI)) {
+      static_assert(OUT_BOXES == 2, "two staging buffers (the barrier pairs are [2])");
+      constexpr int ROWB = red_row_bytes(BN);
+      int* tok_all = reinterpret_cast<int*>(smem + L::RED_TOK_OFFSET);
+      const uint64_t keep = l2_policy_evict_last();
+      int j = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++j) {
+        const TileCoord tc = decode_tile(p, t, m_tiles, BN, false);
+        const int b = j & 1;
+        if (!mbar_wait(afull_bar + b, (uint32_t(j) >> 1) & 1, p.status))
+          atomicExch(p.status, ST_WAIT_TIMEOUT);
+        const int ncols = min(BN, p.n_dim - tc.n0);   // a multiple of 32
+        const int ppr = ncols >> 3;                   // 16-byte pieces per row (<= 32)
+        const uint32_t stg = smem_u32(smem + L::STAGING_OFFSET + b * L::RED_TILE_BYTES);
+        const int* toks = tok_all + b * BM;
+        __nv_bfloat16* dst0 = p.out + tc.n0 + lane * 8;
+        // A warp takes every RED_WARPS-th row. The adds leave an SM through two independent
+        // paths, each good for about 16 bytes per clock: vector red instructions (load/store
+        // unit) and bulk reductions (copy engine). The rows are split between the two: of a
+        // warp's 32 rows the odd ones go as one bulk reduction each (lane l issues row l's), the
+        // even ones as red instructions, lane l piece l of the row, RED_UNROLL rows loaded before
+        // the first add is issued.
+        constexpr int RED_UNROLL = 8;
+        constexpr int STEP = 2 * RED_WARPS;   // distance between two rows of the same kind
+        static_assert(BM % (STEP * RED_UNROLL) == 0, "rows per reducer warp");
+        const int rw = warp - (2 + EPI_WARPS);
+        if (lane < BM / STEP) {
+          const int r = rw + RED_WARPS + lane * STEP;
+          const int tok = toks[r];
+          if (tok >= 0)
+            bulk_reduce_add_bf16(p.out + tc.n0 + int64_t(tok) * p.ld_out,
+                                 smem + L::STAGING_OFFSET + b * L::RED_TILE_BYTES + r * ROWB,
+                                 uint32_t(ncols) * 2u);
+        }
+        bulk_commit();
+#pragma unroll 1
+        for (int r0 = rw; r0 < BM; r0 += STEP * RED_UNROLL) {
+          uint32_t w[RED_UNROLL][4];
+          int tk[RED_UNROLL];
+#pragma unroll
+          for (int u = 0; u < RED_UNROLL; ++u) {
+            const int r = r0 + u * STEP;
+            tk[u] = lane < ppr ? toks[r] : -1;
+            ld_shared_v4(stg + r * ROWB + (lane < ppr ? lane : 0) * 16, w[u][0], w[u][1], w[u][2],
+                         w[u][3]);
+          }
+#pragma unroll
+          for (int u = 0; u < RED_UNROLL; ++u)
+            if (tk[u] >= 0)
+              red_add_bf16x8(dst0 + int64_t(tk[u]) * p.ld_out, w[u][0], w[u][1], w[u][2], w[u][3],
+                             keep);
+        }
+        bulk_wait_read<0>();   // the copy engine has read this thread's rows: the buffer may go back
+        __syncwarp();
+        if (lane == 0) mbar_arrive(aempty_bar + b);
+      }
+    }
   } else if (warp < 2 + EPI_WARPS) {
     // ---------------------------------------------------------------------- epilogue
     const int ew = warp - 2;
@@ -460,7 +540,7 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
       // (the tile's owner is looked up only when there is a bias: the epilogue has no other use
       // for it, and the load would sit at the head of every tile)
       [[maybe_unused]] const __nv_bfloat16* bias_row = nullptr;
-      if constexpr (EPI == EPI_GLU || EPI == EPI_SCALE) {
+      if constexpr (EPI == EPI_GLU || EPI == EPI_SCALE || EPI == EPI_SCALE_RED) {
         if (p.bias != nullptr) {
           const int grp = fixed ? tc.z : __ldg(p.expert_ids + tc.m_tile);
           if (grp < p.n_groups_b1) bias_row = p.bias + int64_t(grp) * p.n_dim;
@@ -521,6 +601,47 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
             bulk_commit();
           }
         }
+      } else if constexpr (EPI == EPI_RAW_RED || EPI == EPI_SCALE_RED) {
+        // The tile is staged row by row in shared memory (bf16, this row's weight and bias
+        // applied) with the rows' tokens beside it, and handed to the reducer warps, which add
+        // every row to row `token` of the token-major output (bf16 atomics performed in L2). Two
+        // staging buffers take turns.
+        constexpr int NB = BN / 64;
+        constexpr int ROWB = red_row_bytes(BN);
+        const int tok = fixed ? (row_ok ? int(grow) : -1)
+                              : (pair < p.n_pairs ? pair / p.top_k : -1);
+        if (j >= 2 && !mbar_wait(aempty_bar + b, ((uint32_t(j) >> 1) - 1) & 1, p.status))
+          atomicExch(p.status, ST_WAIT_TIMEOUT);
+        uint8_t* stg = smem + L::STAGING_OFFSET + b * L::RED_TILE_BYTES;
+        if (half == 0) reinterpret_cast<int*>(smem + L::RED_TOK_OFFSET)[b * BM + row] = tok;
+        const uint32_t my_row = smem_u32(stg) + row * ROWB + half * 64;
+        float v[2][32];
+        tmem_ld32(taddr + half * 32, v[0]);
+#pragma unroll
+        for (int jb = 0; jb < NB; ++jb) {
+          tmem_ld_wait();
+          if (jb + 1 < NB) tmem_ld32(taddr + (jb + 1) * 64 + half * 32, v[(jb + 1) & 1]);
+          float* cur = v[jb & 1];
+          if constexpr (EPI == EPI_SCALE_RED) {
+            if (bias_row != nullptr && tc.n0 + jb * 64 + half * 32 < p.n_dim)
+              add_bias32(cur, bias_row + tc.n0 + jb * 64 + half * 32);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) cur[i] *= w;
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t wd[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(cur[8 * i + 2 * k], cur[8 * i + 2 * k + 1]);
+              wd[k] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            st_shared_v4(my_row + jb * 128 + i * 16, wd[0], wd[1], wd[2], wd[3]);
+          }
+        }
+        fence_proxy_async();   // the copy engine reads the staged rows through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(afull_bar + b);   // (release: the staged rows are visible)
       } else {  // EPI_GLUBWD
         __nv_bfloat16* da1 = out_row;  // ld_out == 2 * BN
         __nv_bfloat16* hw = p.out2 + tc.z * p.out2_gstride + grow * BN;
@@ -565,6 +686,7 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
     if constexpr (TMA_OUT) {
       if (warp == 2 && lane == 0) bulk_wait_read<0>();
     }
+
   }
 
   tc_fence_before();

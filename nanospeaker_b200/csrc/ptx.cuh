@@ -120,6 +120,30 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* s
       "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// Eight bf16 at dst (global, 16-byte aligned) += the eight packed in w0..w3: one vector reduction,
+// performed as bf16 atomics in L2, no value returned.
+// `policy` (l2_policy_evict_last) asks L2 to keep the line: every output line is hit once per pair
+// of its token while the GEMM's operands stream through the cache in between.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void red_add_bf16x8(void* dst, uint32_t w0, uint32_t w1, uint32_t w2,
+                                               uint32_t w3, uint64_t policy) {
+  asm volatile("red.global.add.L2::cache_hint.noftz.v4.bf16x2 [%0], {%1,%2,%3,%4}, %5;" ::"l"(dst),
+               "r"(w0), "r"(w1), "r"(w2), "r"(w3), "l"(policy)
+               : "memory");
+}
+// Untiled bulk reduction: `bytes` of bf16 at src (shared memory) are added element-wise, as bf16
+// atomics performed in L2, to the bf16 values at dst (global). Both addresses 16-byte aligned, bytes
+// a multiple of 16. Completion is tracked per thread in bulk groups, like the tiled stores.
+__device__ __forceinline__ void bulk_reduce_add_bf16(void* dst, const void* src, uint32_t bytes) {
+  asm volatile(
+      "cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], %2;" ::"l"(dst),
+      "r"(smem_u32(src)), "r"(bytes)
+      : "memory");
+}
 __device__ __forceinline__ void bulk_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

@@ -23,7 +23,12 @@ class StackedMoEDecoder:
     it is overwritten by the next step with the same T). The first call for a given T captures the
     graph; later calls copy x into the graph's input and replay."""
 
-    def __init__(self, blocks: Sequence[MoEBlock]):
+    def __init__(self, blocks: Sequence[MoEBlock], combine: str = "store"):
+        # "store": per-pair rows summed in fp32 in pair order, so a replay reproduces the eager
+        # stack bit for bit and a token's routing further down the stack cannot flip from run to
+        # run; at decode sizes the separate combine launch costs next to nothing. "atomic" is the
+        # training default of the library (see moe_kernel.COMBINE_MODES).
+        self.combine = combine
         self.blocks: List[MoEBlock] = list(blocks)
         if not self.blocks:
             raise ValueError("need at least one block")
@@ -59,7 +64,8 @@ class StackedMoEDecoder:
         x = x.contiguous()
         for b in self.blocks:
             args = self._fast_args(b, x)
-            x = x + b(x) if args is None else MK.moe_block_inference(x, *args, residual=x)
+            x = x + b(x) if args is None else MK.moe_block_inference(x, *args, residual=x,
+                                                                      combine=b.combine_mode or self.combine)
         return x
 
     @torch.no_grad()

@@ -326,6 +326,42 @@ def down_gemm(hid, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair
     return y
 
 
+def down_gemm_acc(hid, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair_w,
+                  n_pairs: int, top_k: int, acc: torch.Tensor, w_extra=None, bias=None) -> torch.Tensor:
+    """The down GEMM fused with the combine: every live row of (hid x w_out[e]) * pair_w is added
+    (bf16 atomics) to row sorted_ids[row] // top_k of acc [T, D], which the caller has filled with
+    zeros or another summand. Fixed schedule: row r of every group goes to row r of acc."""
+    _need_cuda(hid, w_out, acc)
+    rows, k = hid.shape[-2:]
+    g, _, d = w_out.shape
+    assert acc.is_contiguous() and acc.shape[1] == d and acc.dtype == hid.dtype
+    xp, xn = _extra(w_extra)
+    _lib.check(_lib.load().moe_b200_down_gemm_acc(
+        hid.data_ptr(), rows, k, w_out.data_ptr(), g, xp, xn, d, _lib.ptr(expert_ids),
+        _lib.ptr(n_post_pad), n_fixed, _lib.ptr(sorted_ids), _lib.ptr(pair_w), n_pairs, top_k,
+        acc.data_ptr(), acc.shape[0], _lib.ptr(bias), status_word(hid.device).data_ptr(),
+        _stream(hid)), "moe_b200_down_gemm_acc")
+    _count(1 if rows else 0)
+    return acc
+
+
+def dx_gemm_acc(da1, w_in, expert_ids, n_post_pad, n_fixed: int, sorted_ids, n_pairs: int,
+                top_k: int, acc: torch.Tensor, w_extra=None) -> torch.Tensor:
+    """The dX GEMM fused with the combine: row `row` of da1 x w_in[e]^T is added to row
+    sorted_ids[row] // top_k of acc [T, D] (fixed schedule: row r of every group to row r)."""
+    _need_cuda(da1, w_in, acc)
+    rows, h2 = da1.shape[-2:]
+    g, d, _ = w_in.shape
+    assert acc.is_contiguous() and acc.shape[1] == d and acc.dtype == da1.dtype
+    xp, xn = _extra(w_extra)
+    _lib.check(_lib.load().moe_b200_dx_gemm_acc(
+        da1.data_ptr(), rows, h2 // 2, w_in.data_ptr(), g, xp, xn, d, _lib.ptr(expert_ids),
+        _lib.ptr(n_post_pad), n_fixed, _lib.ptr(sorted_ids), n_pairs, top_k, acc.data_ptr(),
+        acc.shape[0], status_word(da1.device).data_ptr(), _stream(da1)), "moe_b200_dx_gemm_acc")
+    _count(1 if rows else 0)
+    return acc
+
+
 def dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, pair_w,
                     n_pairs: int, a1, act: int, want_dtw: bool, gather_top_k: int = 0,
                     w_extra=None, token_rows=None, dtw_out=None):

@@ -65,6 +65,9 @@ class MoEBlock(nn.Module):
         self.activation, act_fn = resolve_activation(activation)
         self.glu = make_glu(act_fn, fused)
         self.kernel = kernel
+        # how the kernel path sums a token's per-pair rows: None = the library default
+        # (moe_kernel.get_combine_mode()), or "atomic" / "store" for this block
+        self.combine_mode = None
         # a registered name bound to its registered function, and known to the epilogues
         named = ACTIVATIONS.get(self.activation) is act_fn and self.activation in KERNEL_ACTIVATIONS
         self._kernel_act = self.activation if named else None
@@ -201,7 +204,7 @@ class MoEBlock(nn.Module):
             full = self.router.wants_probs()
             out, aux, counts = fused_moe_block(
                 x, self.router, self.W_in, self.W_out, self.W_sh_in, self.W_sh_out,
-                self._kernel_act, full)
+                self._kernel_act, full, combine=self.combine_mode)
             self.expert_counts = counts.detach()
             self.aux_loss = aux if full else torch.zeros((), device=x.device, dtype=x.dtype)
             return out.view(shape)
@@ -212,6 +215,7 @@ class MoEBlock(nn.Module):
             out, counts = fused_moe_forward(
                 x, self.W_in, self.W_out, topk_w, topk_idx, self.b_in, self.b_out,
                 self._kernel_act, w_sh_in=self.W_sh_in, w_sh_out=self.W_sh_out,
+                combine=self.combine_mode,
             )
             self._record(probs, counts, x)
             return out.view(shape)

@@ -24,6 +24,38 @@ from .kernels import ALIGN_M, KERNEL_ACTIVATIONS, l_cap as _l_cap  # noqa: F401 
 # dtypes the tcgen05 path computes in (fp32 accumulation inside).
 KERNEL_DTYPES = (torch.bfloat16,)
 
+# How a token's k (+ S) per-pair rows are summed, in the forward (out) and in the backward (dx):
+#   "atomic"  the down / dX GEMM adds every row straight into the token-major result (bf16 atomics
+#             in L2): no per-pair [l_cap, D] buffer is written or read back and there is no combine
+#             launch. The sum is taken in bf16 in arrival order, so results can differ in the last
+#             bf16 bit from run to run (the reference's eager path also sums in bf16,
+#             src/model/moe.py:407-413).
+#   "store"   the GEMM stores per-pair rows and a combine kernel sums them in fp32 in pair order:
+#             bitwise reproducible, what the reference's kernel path does
+#             (src/model/moe_kernel.py:26-30, 579-582).
+COMBINE_MODES = ("atomic", "store")
+_combine_mode = "atomic"
+
+
+def set_combine_mode(mode: str) -> None:
+    """Library-wide default for how per-pair rows are summed ("atomic" or "store")."""
+    global _combine_mode
+    if mode not in COMBINE_MODES:
+        raise ValueError(f"combine mode must be one of {COMBINE_MODES}, got {mode!r}")
+    _combine_mode = mode
+
+
+def get_combine_mode() -> str:
+    return _combine_mode
+
+
+def _atomic(mode: Optional[str]) -> bool:
+    mode = _combine_mode if mode is None else mode
+    if mode not in COMBINE_MODES:
+        raise ValueError(f"combine mode must be one of {COMBINE_MODES}, got {mode!r}")
+    return mode == "atomic"
+
+
 MAX_EXPERTS = 256  # per-expert state of the routing kernels lives on chip
 MAX_TOPK = 16
 MAX_SHARED = 8     # shared experts are dispatched as extra experts: E + S <= MAX_EXPERTS
@@ -153,6 +185,7 @@ def moe_experts(
     save_for_backward: bool,
     b_in: Optional[torch.Tensor] = None,
     b_out: Optional[torch.Tensor] = None,
+    atomic_combine: bool = False,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """out[t] = sum_j topk_w[t,j] * expert_{idx[t,j]}(x[t]) on pre-dispatched pairs.
 
@@ -190,6 +223,8 @@ def moe_experts(
         w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
     b_in = None if b_in is None else b_in.to(x.dtype).contiguous()
     b_out = None if b_out is None else b_out.to(x.dtype).contiguous()
+    # the accumulator of the atomic combine is cleared first thing, far ahead of the GEMM that adds to it
+    out = torch.zeros_like(x) if atomic_combine else None
 
     if save_for_backward:
         live, tok = _routed_rows(x, w_in, w_sh_in, pad_offsets, n_post_pad)
@@ -200,15 +235,20 @@ def moe_experts(
         xs, a1 = x.new_empty(0), x.new_empty(0)
         hid, _ = K.up_gemm(x, w_in, expert_ids, n_post_pad, 0, act, False,
                            gather=(sorted_ids, topk), w_extra=w_sh_in, bias=b_in)
-    y = K.down_gemm(hid, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m, w_extra=w_sh_out,
-                    bias=b_out)
-    out = K.combine(y, inv_ids, n, topk)
+    if atomic_combine:
+        out = K.down_gemm_acc(hid, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m, topk, out,
+                              w_extra=w_sh_out, bias=b_out)
+    else:
+        y = K.down_gemm(hid, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m, w_extra=w_sh_out,
+                        bias=b_out)
+        out = K.combine(y, inv_ids, n, topk)
     return out, xs, a1
 
 
 @moe_experts.register_fake
 def _(x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
-      n_post_pad, inv_ids, activation, save_for_backward, b_in=None, b_out=None):
+      n_post_pad, inv_ids, activation, save_for_backward, b_in=None, b_out=None,
+      atomic_combine=False):
     n, d = x.shape
     if n == 0 or not save_for_backward:
         return x.new_empty((n, d)), x.new_empty(0), x.new_empty(0)
@@ -249,6 +289,7 @@ def moe_experts_bwd(
     activation: str,
     b_out: Optional[torch.Tensor] = None,
     need_db_in: bool = False,
+    atomic_combine: bool = False,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
            torch.Tensor, torch.Tensor]:
     """(dx, dW_in, dW_out, dtopk_w, dW_sh_in, dW_sh_out, db_in, db_out); the shared-expert and bias
@@ -270,13 +311,17 @@ def moe_experts_bwd(
     topk = topk_w.shape[-1]
     m = n * topk
     tw = topk_w.reshape(-1).contiguous()
+    dx = torch.zeros_like(x) if atomic_combine else None
 
     live, tok = _routed_rows(grad_out, w_in, w_sh_in, pad_offsets, n_post_pad)
     douts = K.permute(grad_out, topk, sorted_ids, live)
     da1, hidw, dtw = K.dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m,
                                        a1, act, True, w_extra=w_sh_out, token_rows=tok)
-    ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
-    dx = K.combine(ydx, inv_ids, n, topk)
+    if atomic_combine:
+        K.dx_gemm_acc(da1, w_in, expert_ids, n_post_pad, 0, sorted_ids, m, topk, dx, w_extra=w_sh_in)
+    else:
+        ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
+        dx = K.combine(ydx, inv_ids, n, topk)
     g_in = K.wgrad(xs, da1, pad_offsets, e_n + s_n, n_extra=s_n,
                    token_rows=("a", x) if s_n else None)
     g_out = K.wgrad(hidw, douts, pad_offsets, e_n + s_n, n_extra=s_n,
@@ -312,7 +357,8 @@ def moe_experts_bwd(
 
 @moe_experts_bwd.register_fake
 def _(grad_out, x, xs, a1, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
-      pad_offsets, counts, n_post_pad, inv_ids, activation, b_out=None, need_db_in=False):
+      pad_offsets, counts, n_post_pad, inv_ids, activation, b_out=None, need_db_in=False,
+      atomic_combine=False):
     e_n = w_in.shape[0]
     return (torch.empty_like(x), torch.empty_like(w_in), torch.empty_like(w_out),
             torch.empty_like(topk_w),
@@ -324,8 +370,9 @@ def _(grad_out, x, xs, a1, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, e
 
 def _experts_setup(ctx, inputs, output):
     (x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
-     n_post_pad, inv_ids, activation, save_for_backward, b_in, b_out) = inputs
+     n_post_pad, inv_ids, activation, save_for_backward, b_in, b_out, atomic_combine) = inputs
     out, xs, a1 = output
+    ctx.atomic_combine = atomic_combine
     ctx.mark_non_differentiable(xs, a1)
     # without this autograd would hand the backward zero-filled gradients for the kept buffers
     ctx.set_materialize_grads(False)
@@ -354,10 +401,11 @@ def _experts_backward(ctx, grad_out, g_xs, g_a1):
         grad_out = torch.zeros_like(x)
     dx, dw_in, dw_out, dtw, dsi, dso, db_in, db_out = moe_experts_bwd(
         grad_out, x, xs, a1, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
-        pad_offsets, counts, n_post_pad, inv_ids, ctx.activation, b_out, ctx.has_b_in)
+        pad_offsets, counts, n_post_pad, inv_ids, ctx.activation, b_out, ctx.has_b_in,
+        ctx.atomic_combine)
     return (dx, dw_in, dw_out, dtw, dsi if ctx.has_shared else None,
             dso if ctx.has_shared else None, None, None, None, None, None, None, None, None,
-            db_in if ctx.has_b_in else None, db_out if ctx.has_b_out else None)
+            db_in if ctx.has_b_in else None, db_out if ctx.has_b_out else None, None)
 
 
 moe_experts.register_autograd(_experts_backward, setup_context=_experts_setup)
@@ -405,6 +453,7 @@ def moe_block(
     activation: str,
     save_for_backward: bool,
     residual: Optional[torch.Tensor] = None,
+    atomic_combine: bool = False,
 ) -> _T15:
     """The whole MoE block as one op: router GEMM, top-k, dispatch, experts (routed + shared),
     combine and the balance loss, with no PyTorch glue kernels in between
@@ -425,6 +474,9 @@ def moe_block(
         w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
     ld = _router_ld(e_n)
     ks = top_k + s_n
+    out = None
+    if atomic_combine:   # the accumulator the down GEMM adds into: zeros, or the residual
+        out = torch.zeros_like(x) if residual is None else residual.contiguous().clone()
 
     wp = K.copy_cols(router_w, ld).unsqueeze(0)   # [1, D, ld], zero pad columns
     logits = K.down_gemm(x, wp, None, None, 1, None, None, 0)[0]
@@ -439,8 +491,11 @@ def moe_block(
     else:
         xs, a1 = x.new_empty(0), x.new_empty(0)
         hid, _ = K.up_gemm(x, w_in, eids, npp, 0, act, False, gather=(sids, ks), w_extra=w_sh_in)
-    y = K.down_gemm(hid, w_out, eids, npp, 0, sids, tw, m, w_extra=w_sh_out)
-    out = K.combine(y, inv, n, ks, residual)   # + residual [T, D] in the same fp32 sum when given
+    if atomic_combine:
+        K.down_gemm_acc(hid, w_out, eids, npp, 0, sids, tw, m, ks, out, w_extra=w_sh_out)
+    else:
+        y = K.down_gemm(hid, w_out, eids, npp, 0, sids, tw, m, w_extra=w_sh_out)
+        out = K.combine(y, inv, n, ks, residual)   # + residual [T, D] in the same fp32 sum when given
     if full_softmax:
         aux = K.balance_loss(colsum, counts_all, e_n, n, aux_coef)
     else:
@@ -451,7 +506,7 @@ def moe_block(
 
 @moe_block.register_fake
 def _(x, router_w, logit_bias, w_in, w_out, w_sh_in, w_sh_out, top_k, normalize, full_softmax,
-      aux_coef, activation, save_for_backward, residual=None):
+      aux_coef, activation, save_for_backward, residual=None, atomic_combine=False):
     n, d = x.shape
     e_n = w_in.shape[0]
     s_n = 0 if w_sh_in is None else w_sh_in.shape[0]
@@ -493,9 +548,11 @@ def moe_block_bwd(
     full_softmax: bool,
     aux_coef: float,
     activation: str,
+    atomic_combine: bool = False,
 ) -> _T6:
     """[dx, d_router_w [D, E], dW_in, dW_out, dW_sh_in, dW_sh_out] of moe_block."""
     grad_out = grad_out.to(x.dtype).contiguous()
+    dx = torch.zeros_like(x) if atomic_combine else None   # cleared far ahead of the adds
     act = _act_id(activation)
     n, d = x.shape
     e_n = w_in.shape[0]
@@ -519,7 +576,10 @@ def moe_block_bwd(
     side_router.wait_stream(main)
     g_in = K.wgrad(xs, da1, pad_offsets, e_n + s_n, n_extra=s_n,
                    token_rows=("a", x) if s_n else None)
-    ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
+    if atomic_combine:
+        K.dx_gemm_acc(da1, w_in, expert_ids, n_post_pad, 0, sorted_ids, m, ks, dx, w_extra=w_sh_in)
+    else:
+        ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
     with torch.cuda.stream(side_out):
         g_out = K.wgrad(hidw, douts, pad_offsets, e_n + s_n, n_extra=s_n,
                         token_rows=("b", grad_out) if s_n else None)
@@ -530,21 +590,26 @@ def moe_block_bwd(
                                 normalize, full_softmax, d_aux, counts_all, aux_coef,
                                 logits.shape[1])
         d_router = K.copy_cols(K.wgrad(x, dl, None, 1)[0], e_n)   # pad columns dropped
-        dx_router = K.dx_gemm(dl, router_w_padded, None, None, 1)[0]
+        if atomic_combine:   # the router's share of dx joins the same accumulator
+            K.dx_gemm_acc(dl.unsqueeze(0), router_w_padded, None, None, 1, None, 0, 1, dx)
+        else:
+            dx_router = K.dx_gemm(dl, router_w_padded, None, None, 1)[0]
     main.wait_stream(side_out)
     main.wait_stream(side_router)
     if s_n:
         (dw_in, dw_sh_in), (dw_out, dw_sh_out) = g_in, g_out
     else:
         dw_in, dw_out, dw_sh_in, dw_sh_out = g_in, g_out, x.new_empty(0), x.new_empty(0)
-    dx = K.combine(ydx, inv_ids, n, ks, dx_router)
+    if not atomic_combine:
+        dx = K.combine(ydx, inv_ids, n, ks, dx_router)
     return dx, d_router, dw_in, dw_out, dw_sh_in, dw_sh_out
 
 
 @moe_block_bwd.register_fake
 def _(grad_out, grad_aux, x, logit_bias, w_in, w_out, w_sh_in, w_sh_out, xs, a1, logits, w_all,
       idx_all, sorted_ids, expert_ids, pad_offsets, counts_all, n_post_pad, inv_ids,
-      router_w_padded, top_k, normalize, full_softmax, aux_coef, activation):
+      router_w_padded, top_k, normalize, full_softmax, aux_coef, activation,
+      atomic_combine=False):
     return (torch.empty_like(x), x.new_empty((x.shape[1], w_in.shape[0])), torch.empty_like(w_in),
             torch.empty_like(w_out),
             torch.empty_like(w_sh_in) if w_sh_in is not None else x.new_empty(0),
@@ -553,8 +618,9 @@ def _(grad_out, grad_aux, x, logit_bias, w_in, w_out, w_sh_in, w_sh_out, xs, a1,
 
 def _block_setup(ctx, inputs, output):
     (x, router_w, logit_bias, w_in, w_out, w_sh_in, w_sh_out, top_k, normalize, full_softmax,
-     aux_coef, activation, save_for_backward, residual) = inputs
+     aux_coef, activation, save_for_backward, residual, atomic_combine) = inputs
     ctx.has_residual = residual is not None
+    ctx.atomic_combine = atomic_combine
     ctx.mark_non_differentiable(*output[2:])
     ctx.set_materialize_grads(False)
     if not save_for_backward:
@@ -583,17 +649,19 @@ def _block_backward(ctx, grad_out, grad_aux, *unused):
     if grad_out is None:
         grad_out = torch.zeros_like(x)
     dx, d_router, dw_in, dw_out, dsi, dso = moe_block_bwd(
-        grad_out, grad_aux, x, bias, w_in, w_out, w_sh_in, w_sh_out, *kept, *ctx.args)
+        grad_out, grad_aux, x, bias, w_in, w_out, w_sh_in, w_sh_out, *kept, *ctx.args,
+        ctx.atomic_combine)
     d_router = d_router.to(ctx.router_dtype)
     return (dx, d_router, None, dw_in, dw_out, dsi if ctx.has_shared else None,
             dso if ctx.has_shared else None, None, None, None, None, None, None,
-            grad_out if ctx.has_residual else None)
+            grad_out if ctx.has_residual else None, None)
 
 
 moe_block.register_autograd(_block_backward, setup_context=_block_setup)
 
 
-def fused_moe_block(x, router, w_in, w_out, w_sh_in, w_sh_out, activation, full_softmax):
+def fused_moe_block(x, router, w_in, w_out, w_sh_in, w_sh_out, activation, full_softmax,
+                    combine: Optional[str] = None):
     """(out, aux_loss fp32, counts int32 [E]) for a TopKRouter-like `router` (attributes W,
     logit_bias, top_k, normalize_weights, aux_loss_coef) -- the path MoEBlock.forward takes
     whenever no exploration noise has to be added to the logits."""
@@ -606,7 +674,8 @@ def fused_moe_block(x, router, w_in, w_out, w_sh_in, w_sh_out, activation, full_
         bias = bias.to(torch.float32).contiguous()
     res = moe_block(x, cast(router.W), bias, cast(w_in), cast(w_out), cast(w_sh_in),
                     cast(w_sh_out), router.top_k, bool(router.normalize_weights),
-                    bool(full_softmax), float(router.aux_loss_coef), activation, save)
+                    bool(full_softmax), float(router.aux_loss_coef), activation, save, None,
+                    _atomic(combine))
     return res[0], res[1], res[2]
 
 
@@ -619,7 +688,8 @@ def pad_router_weight(router_w: torch.Tensor, dtype: torch.dtype) -> torch.Tenso
 @torch.no_grad()
 def moe_block_inference(x, router_w_padded, logit_bias, w_in, w_out, w_sh_in, w_sh_out,
                         n_experts: int, top_k: int, normalize: bool, activation: str,
-                        residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        residual: Optional[torch.Tensor] = None,
+                        combine: Optional[str] = None) -> torch.Tensor:
     """Forward of the whole block for a caller that wants nothing but `out` (+ residual): the
     launches of moe_block's inference branch without its per-call extras (the padded copy of the
     router weight, the counts tensor, the zero balance loss). Six launches: logits GEMM, router
@@ -633,13 +703,17 @@ def moe_block_inference(x, router_w_padded, logit_bias, w_in, w_out, w_sh_in, w_
     w_all, _, _, sids, eids, _, _, npp, inv = K.router_dispatch(
         logits, logit_bias, n_experts, top_k, s_n, normalize, False)
     hid, _ = K.up_gemm(x, w_in, eids, npp, 0, act, False, gather=(sids, ks), w_extra=w_sh_in)
+    if _atomic(combine):
+        out = torch.zeros_like(x) if residual is None else residual.clone()
+        return K.down_gemm_acc(hid, w_out, eids, npp, 0, sids, w_all.reshape(-1), n * ks, ks, out,
+                               w_extra=w_sh_out)
     y = K.down_gemm(hid, w_out, eids, npp, 0, sids, w_all.reshape(-1), n * ks, w_extra=w_sh_out)
     return K.combine(y, inv, n, ks, residual)
 
 
 # ------------------------------------------------------------------------------- entry point
 def fused_moe_forward(x, w_in, w_out, topk_w, topk_idx, b_in, b_out, activation,
-                      w_sh_in=None, w_sh_out=None):
+                      w_sh_in=None, w_sh_out=None, combine: Optional[str] = None):
     """Dispatch + experts on the GPU; returns (out [N, d_model], counts [n_experts] int32).
 
     Same contract as src/model/moe_kernel.py:785-803, plus optional stacked shared-expert weights
@@ -663,5 +737,6 @@ def fused_moe_forward(x, w_in, w_out, topk_w, topk_idx, b_in, b_out, activation,
     tensors = (x, w_in, w_out, topk_w, w_sh_in, w_sh_out, b_in, b_out)
     save = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
     out, _, _ = moe_experts(x, cast(w_in), cast(w_out), topk_w, cast(w_sh_in), cast(w_sh_out), sids,
-                         eids, offs, counts, npp, inv, activation, save, cast(b_in), cast(b_out))
+                         eids, offs, counts, npp, inv, activation, save, cast(b_in), cast(b_out),
+                         _atomic(combine))
     return out, counts[: w_in.shape[0]]

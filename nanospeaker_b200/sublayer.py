@@ -26,12 +26,12 @@ class _FFNSublayerFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, gamma, eps, router_w, logit_bias, w_in, w_out, w_sh_in, w_sh_out, top_k,
-                normalize, full_softmax, aux_coef, activation):
+                normalize, full_softmax, aux_coef, activation, atomic_combine):
         cast = lambda t: None if t is None else t.to(x.dtype)
         h, rstd = K.rmsnorm(x, cast(gamma).contiguous(), eps)
         res = MK.moe_block(h, cast(router_w), logit_bias, cast(w_in), cast(w_out), cast(w_sh_in),
                            cast(w_sh_out), top_k, normalize, full_softmax, aux_coef, activation,
-                           True, x)
+                           True, x, atomic_combine)
         out, aux, counts = res[0], res[1], res[2]
         ctx.has_shared = w_sh_in is not None
         ctx.has_bias = logit_bias is not None
@@ -41,7 +41,7 @@ class _FFNSublayerFn(torch.autograd.Function):
         if ctx.has_bias:
             saved.append(logit_bias)
         ctx.save_for_backward(*saved)
-        ctx.args = (top_k, normalize, full_softmax, aux_coef, activation)
+        ctx.args = (top_k, normalize, full_softmax, aux_coef, activation, atomic_combine)
         ctx.mark_non_differentiable(counts)
         ctx.set_materialize_grads(False)
         return out, aux, counts
@@ -65,7 +65,8 @@ class _FFNSublayerFn(torch.autograd.Function):
         return (dx, dgamma.to(gamma.dtype), None, d_router.to(router_w.dtype), None,
                 dw_in.to(w_in.dtype), dw_out.to(w_out.dtype),
                 dsi.to(w_sh_in.dtype) if ctx.has_shared else None,
-                dso.to(w_sh_out.dtype) if ctx.has_shared else None, None, None, None, None, None)
+                dso.to(w_sh_out.dtype) if ctx.has_shared else None, None, None, None, None, None,
+                None)
 
 
 class MoEFFNSublayer(nn.Module):
@@ -95,7 +96,8 @@ class MoEFFNSublayer(nn.Module):
             out, aux, counts = _FFNSublayerFn.apply(
                 x2.contiguous(), self.norm_gamma, self.epsilon, f.router.W, bias, f.W_in, f.W_out,
                 f.W_sh_in, f.W_sh_out, f.router.top_k, bool(f.router.normalize_weights),
-                bool(full), float(f.router.aux_loss_coef), f._kernel_act)
+                bool(full), float(f.router.aux_loss_coef), f._kernel_act,
+                MK._atomic(f.combine_mode))
             f.expert_counts = counts.detach()
             f.aux_loss = aux if full else torch.zeros((), device=x.device, dtype=x.dtype)
             return out.view(shape), f.aux_loss

@@ -82,6 +82,21 @@ def test_arguments_are_validated_before_any_launch(lib):
     assert up(128, 128, 5, 0) == -1     # more fixed groups than weight matrices
     assert up(128, 128, 1, 2) == -1     # gathered A only on the routed schedule
     assert up(128, 128, 1, 0, 2) == -1  # a second weight stack only on the routed schedule
+    # the accumulating GEMMs: the token-major accumulator and the slot -> token map are checked too
+    dacc = lambda rows, fixed, sid, topk, acc, n_tok=4, n_pairs=8: lib.moe_b200_down_gemm_acc(
+        p, rows, 128, p, 4, null, 0, 64, p, p, fixed, sid, p, n_pairs, topk, acc, n_tok, null, p,
+        null)
+    assert dacc(128, 0, p, 2, null) == -2        # no accumulator
+    assert dacc(128, 0, null, 2, p) == -2        # routed schedule without sorted_ids
+    assert dacc(128, 0, p, 0, p) == -1           # top_k < 1
+    assert dacc(128, 0, p, 2, p, 4, 9) == -1     # more pairs than n_tokens * top_k
+    assert dacc(128, 1, null, 1, p, 100) == -1   # fixed schedule: more rows than tokens
+    assert dacc(100, 0, p, 2, p) == -1           # routed rows must be a multiple of 128
+    xacc = lambda sid, topk, acc: lib.moe_b200_dx_gemm_acc(
+        p, 128, 128, p, 4, null, 0, 64, p, p, 0, sid, 8, topk, acc, 4, p, null)
+    assert xacc(p, 2, null) == -2
+    assert xacc(null, 2, p) == -2
+    assert xacc(p, 0, p) == -1
     wg = lambda n_dim, ks, which, po, n_first=4: lib.moe_b200_wgrad(
         p, 0, 64, p, 0, n_dim, 128, po, 4, ks, p, 2, 8, which, p, n_first, null, p, 0, null, 0, 0, p,
         null)

@@ -280,3 +280,67 @@ def test_shared_experts_read_token_rows_in_place(T, E, S, k, D):
         for a, b in zip(ref_in + ref_out, got_in + got_out):
             assert torch.equal(a, b)
     K().check_status("cuda")
+
+
+@pytest.mark.parametrize("T,E,k,D,skew", CASES)
+def test_accumulating_down_and_dx_gemms_match_store_then_combine(T, E, k, D, skew):
+    """The GEMMs that add their rows straight into the token-major result (bf16 atomics) against
+    fp32 CPU math: out[t] = sum_j w * hid @ W_out (+ what the accumulator held), dx[t] = sum_j
+    da1 @ W_in^T; also against the store-then-reduce pair on the GPU, and with a per-expert bias."""
+    idx, (sids, eids, offs, counts, npp, inv), x, w_in, w_out, tw = _setup(T, E, k, D, skew=skew)
+    nl, M = int(npp), T * k
+    g = lambda t: t.cuda()
+    torch.manual_seed(3)
+    hid = (torch.randn(sids.numel(), 128) * 0.5).bfloat16()
+    s = sids[:nl].long()
+    live = s < M
+    hid[:nl][~live] = 0                                   # pad rows are zero rows
+    tok = (s // k).clamp(max=T - 1)
+    wrow = torch.where(live, tw.reshape(-1)[s.clamp(max=M - 1)].float(), torch.zeros(()))
+    bias = (torch.randn(E, D) * 0.1).bfloat16()
+    eid_row = eids.long().repeat_interleave(128)[:nl]
+    for b in (None, bias):
+        y = _per_expert(hid[:nl], w_out, offs)
+        if b is not None:
+            y = y + b.float()[eid_row]
+        y = y * wrow[:, None]
+        init = torch.randn(T, D).bfloat16()
+        want = init.float().index_add(0, tok[live], y[live])
+        acc = g(init).clone()
+        K().down_gemm_acc(g(hid), g(w_out), g(eids), g(npp), 0, g(sids), g(tw.reshape(-1)), M, k,
+                          acc, bias=None if b is None else g(b))
+        assert rel_l2(acc.cpu(), want) < TOL
+        ys = K().down_gemm(g(hid), g(w_out), g(eids), g(npp), 0, g(sids), g(tw.reshape(-1)), M,
+                           bias=None if b is None else g(b))
+        ref = K().combine(ys, g(inv), T, k, g(init))
+        assert rel_l2(acc, ref) < TOL
+    da1 = (torch.randn(sids.numel(), 256) * 0.5).bfloat16()
+    da1[:nl][~live] = 0
+    ydx = _per_expert(da1[:nl], w_in, offs, transpose=True)
+    want = torch.zeros(T, D).index_add(0, tok[live], ydx[live])
+    acc = torch.zeros(T, D, device="cuda", dtype=torch.bfloat16)
+    K().dx_gemm_acc(g(da1), g(w_in), g(eids), g(npp), 0, g(sids), M, k, acc)
+    assert rel_l2(acc.cpu(), want) < TOL
+    K().check_status("cuda")
+
+
+def test_accumulating_gemms_on_the_fixed_schedule_add_every_group_to_the_same_rows():
+    """Fixed schedule: row r of every group lands on row r of the accumulator (how the router's
+    share of dx joins the experts'); exact against the storing kernels for one group."""
+    torch.manual_seed(0)
+    T, D, S = 300, 576, 2
+    a = (torch.randn(S, T, 128) * 0.5).bfloat16().cuda()
+    w = (torch.randn(S, 128, D) * 0.1).bfloat16().cuda()
+    y = K().down_gemm(a, w, None, None, S, None, None, 0)            # [S, T, D]
+    acc = torch.zeros(T, D, device="cuda", dtype=torch.bfloat16)
+    K().down_gemm_acc(a, w, None, None, S, None, None, 0, 1, acc)
+    assert rel_l2(acc, y.float().sum(0)) < TOL
+    one = torch.zeros(T, D, device="cuda", dtype=torch.bfloat16)
+    K().down_gemm_acc(a[:1], w[:1], None, None, 1, None, None, 0, 1, one)
+    assert torch.equal(one, y[0])
+    wt = (torch.randn(1, D, 128) * 0.1).bfloat16().cuda()
+    ydx = K().dx_gemm(a[:1], wt, None, None, 1)
+    one.zero_()
+    K().dx_gemm_acc(a[:1], wt, None, None, 1, None, 0, 1, one)
+    assert torch.equal(one, ydx[0])
+    K().check_status("cuda")
