@@ -117,11 +117,19 @@ int moe_b200_balance_loss(const float* colsum, const int32_t* counts, int32_t n_
  *   n_post_pad  [1]          live padded length
  *   inv_ids     [n_pairs]    pair id -> slot
  * Unlike the reference's atomic scatter the order inside a run is STABLE (ascending pair id), so
- * sorted_ids with the sentinels removed equals a stable sort of the expert ids. */
+ * sorted_ids with the sentinels removed equals a stable sort of the expert ids.
+ * capacity = 0: dropless. capacity > 0 is the fixed-capacity schedule of the reference's padded
+ * path (MoEBlock._slots / _forward_padded, src/model/moe.py:225-283) on the same kernels: every
+ * expert below n_capped (the routed ones; shared experts dispatched as extra experts behind them
+ * are never limited) keeps the first `capacity` pairs of its run and drops the rest; a dropped pair gets no
+ * slot (inv_ids = -1, which moe_b200_combine reads as a zero row), the runs and n_post_pad are laid
+ * out by the kept counts, and counts still reports the routing decisions before the drop. A pair
+ * whose expert id is out of range also gets inv_ids = -1 (and sets the status word). */
 int moe_b200_dispatch(const int64_t* topk_idx, int64_t n_pairs, int32_t n_experts,
                       int32_t* sorted_ids, int32_t* expert_ids, int32_t* pad_offsets,
                       int32_t* counts, int32_t* n_post_pad, int32_t* inv_ids, void* scratch,
-                      size_t scratch_bytes, int32_t* status, void* stream);
+                      size_t scratch_bytes, int32_t capacity, int32_t n_capped, int32_t* status,
+                      void* stream);
 
 /* Router top-k and dispatch in two launches for the whole-block path: the router kernel
  * (moe_b200_router_fused's arithmetic and outputs) runs with one block per chunk of 128+ tokens and
@@ -144,9 +152,10 @@ int moe_b200_router_dispatch(const void* logits, int32_t ld, const float* bias, 
  * reference: its dispatch allocates through torch.) Meant for hosts that may not allocate device
  * memory at call time -- a process whose memory plan was frozen at start-up, or a foreign-function
  * caller that owns its input/output buffers but has no device allocator. The per-block histograms
- * live in a 256 KB __device__ array inside the library instead of a caller buffer, so:
- *   - n_pairs may not exceed moe_b200_dispatch_static_max_pairs(n_experts)
- *     (= floor(65536 / n_experts) * 4096; 3 530 752 pairs at 76 experts), else
+ * live in a 128 KB __device__ array inside the library instead of a caller buffer, so:
+ *   - the array holds 128 blocks x 256 experts, which is the most the dispatch ever uses (past
+ *     128 blocks it doubles the pairs per block instead), so the limit on n_pairs is the dispatch's
+ *     own 2^30 = moe_b200_dispatch_static_max_pairs(n_experts); beyond it the call returns
  *     MOE_B200_ERR_TOO_LARGE;
  *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress,
  *     with that device current); make that first call outside any stream capture;
@@ -172,12 +181,28 @@ int moe_b200_permute(const void* x, int64_t n_tokens, int32_t d_model, int32_t t
                      void* stream);
 
 /* Token-major combine: out[t, :] = sum_j y[inv_ids[t*top_k + j], :] (+ extra[t, :] + extra2[t, :])
- * accumulated in fp32. Replaces _reduce_kernel (src/model/moe_kernel.py:415-437) and
+ * accumulated in fp32; a negative inv_ids entry (a pair the dispatch dropped) counts as a zero row.
+ * Replaces _reduce_kernel (src/model/moe_kernel.py:415-437) and
  * out.index_add_ (src/model/moe.py:413); extra / extra2 (nullable, [n_tokens, d_model]) carry the
  * shared experts' rows (src/model/moe.py:416-417). */
 int moe_b200_combine(const void* y, const int32_t* inv_ids, int64_t n_tokens, int32_t top_k,
                      int32_t d_model, const void* extra, const void* extra2, void* out,
                      void* stream);
+
+/* Per-expert column sums of a slot-ordered buffer: out[e, :] += sum over the rows of run e of
+ * row_w * buf[row, :] (fp32 [n_groups, width]; the caller zeroes it first; one atomic add per
+ * 128-row tile and column). row_w = pair_w[sorted_ids[row]] when pair_w is given (pad rows weigh 0),
+ * else 1. alt / first_alt_group: the runs from first_alt_group on read row `slot - pad_offsets[run]`
+ * of the token-major matrix alt [alt_rows, width] instead (rows past alt_rows count as zero), as
+ * the GEMMs do for the shared experts. These are the bias gradients of the block:
+ * db_in = column sums of dA1, db_out = column sums of w * dOut -- the segment sums the reference
+ * takes with index_add_ (src/model/moe_kernel.py:723-737). width % 8 == 0. */
+int moe_b200_segment_colsum(const void* buf, int64_t rows, int32_t width,
+                            const int32_t* expert_ids, const int32_t* n_post_pad,
+                            const int32_t* pad_offsets, int32_t n_groups,
+                            const int32_t* sorted_ids, const void* pair_w, int64_t n_pairs,
+                            const void* alt, int64_t alt_rows, int32_t first_alt_group,
+                            float* out, void* stream);
 
 /* dst[r, c] = c < cols ? src[r, c] : 0 for 0 <= c < dst_ld; 16-bit elements, row strides src_ld /
  * dst_ld elements. Pads the router weight [d_model, n_experts] (src/model/router.py:51) to the
@@ -233,9 +258,9 @@ int moe_b200_rmsnorm_bwd(const void* dh, const void* x, const float* rstd, const
  * a_tokens instead of row `slot` of a, so their rows of a need not have been written at all (see
  * moe_b200_permute: pass pad_offsets + n_groups as its live-row count). Rows past n_tokens read as
  * zeros.
- * bias (may be NULL; routed schedule): b_in [n_groups, 2*d_hidden] in the activation dtype, added
- * to [g | u] before the GLU (src/model/moe_kernel.py:311-313); raw then holds the biased values.
- * The groups of the second weight stack have no bias. */
+ * bias (may be NULL; routed schedule): [n_groups + n_extra, 2*d_hidden] in the activation dtype --
+ * b_in followed by the second stack's b_sh_in (src/model/moe.py:155-156, 166-167) -- added to
+ * [g | u] before the GLU (src/model/moe_kernel.py:311-313); raw then holds the biased values. */
 int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w_in,
                      int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_hidden, const int32_t* expert_ids,
                      const int32_t* n_post_pad, int32_t n_fixed_groups,
@@ -248,8 +273,8 @@ int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w
  * (w_out [n_groups, k_dim, d_model]; weight 1 when pair_w is NULL). With fixed groups hid is
  * [S, rows, k_dim]. Replaces the forward use of _gemm2_kernel
  * (src/model/moe_kernel.py:339-402, 603-613). 
- * bias (may be NULL; routed schedule): b_out [n_groups, d_model], added before the weight scale
- * (src/model/moe_kernel.py:395-399); the groups of the second weight stack have none. */
+ * bias (may be NULL; routed schedule): [n_groups + n_extra, d_model], b_out followed by the second
+ * stack's b_sh_out, added before the weight scale (src/model/moe_kernel.py:395-399). */
 int moe_b200_down_gemm(const void* hid, int64_t rows, int32_t k_dim, const void* w_out,
                        int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_model, const int32_t* expert_ids,
                        const int32_t* n_post_pad, int32_t n_fixed_groups,

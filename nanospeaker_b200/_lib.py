@@ -36,8 +36,8 @@ SIGNATURES = {
         ctypes.c_int, [_c_vp, _c_vp, _c_i32, _c_i64, ctypes.c_float, _c_vp, _c_vp]),
     "moe_b200_dispatch": (
         ctypes.c_int,
-        [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_sz, _c_vp,
-         _c_vp]),
+        [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_sz, _c_i32,
+         _c_i32, _c_vp, _c_vp]),
     "moe_b200_dispatch_static_max_pairs": (_c_i64, [_c_i32]),
     "moe_b200_router_dispatch_scratch_bytes": (_c_sz, [_c_i64, _c_i32]),
     "moe_b200_router_dispatch": (
@@ -51,6 +51,10 @@ SIGNATURES = {
         ctypes.c_int, [_c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp, _c_i64, _c_vp, _c_vp]),
     "moe_b200_combine": (
         ctypes.c_int, [_c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp]),
+    "moe_b200_segment_colsum": (
+        ctypes.c_int,
+        [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_i32, _c_vp, _c_vp, _c_i64, _c_vp, _c_i64,
+         _c_i32, _c_vp, _c_vp]),
     "moe_b200_rmsnorm": (
         ctypes.c_int, [_c_vp, _c_vp, _c_i64, _c_i32, ctypes.c_float, _c_vp, _c_vp, _c_vp]),
     "moe_b200_rmsnorm_bwd": (

@@ -3,7 +3,7 @@
 
 extern "C" {
 
-int32_t moe_b200_abi_version(void) { return 1; }
+int32_t moe_b200_abi_version(void) { return 2; }
 
 const char* moe_b200_error_string(int32_t code) {
   switch (code) {

@@ -76,9 +76,9 @@ struct RowsArgs {
   const __nv_bfloat16* aux;    // GLUBWD: [gate | up] pre-activations [rows, 2H]
   int64_t aux_gstride;
   const __nv_bfloat16* pair_w; // SCALE / GLUBWD: topk_w flat [n_pairs] (null -> weight 1)
-  const __nv_bfloat16* bias;   // GLU / SCALE: per-expert bias [n_groups_b1 or all groups, n_dim] added to
-                               // the accumulator before the GLU / before the weight scale (null = none;
-                               // the groups of the second weight stack have no bias)
+  const __nv_bfloat16* bias;   // GLU / SCALE: per-expert bias [all groups of both weight stacks, n_dim]
+                               // added to the accumulator before the GLU / before the weight scale
+                               // (null = none)
   int32_t act;
   int32_t* status;
 };

@@ -536,14 +536,14 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
       const bool row_ok = !fixed || grow < p.rows_host;
       __nv_bfloat16* out_row = p.out + tc.z * p.out_gstride + grow * p.ld_out;
 
-      // this tile's bias row: only the groups of the first weight stack have one
+      // this tile's bias row
       // (the tile's owner is looked up only when there is a bias: the epilogue has no other use
       // for it, and the load would sit at the head of every tile)
       [[maybe_unused]] const __nv_bfloat16* bias_row = nullptr;
       if constexpr (EPI == EPI_GLU || EPI == EPI_SCALE || EPI == EPI_SCALE_RED) {
         if (p.bias != nullptr) {
           const int grp = fixed ? tc.z : __ldg(p.expert_ids + tc.m_tile);
-          if (grp < p.n_groups_b1) bias_row = p.bias + int64_t(grp) * p.n_dim;
+          bias_row = p.bias + int64_t(grp) * p.n_dim;   // one row per group of both weight stacks
         }
       }
       if constexpr (EPI == EPI_GLU) {

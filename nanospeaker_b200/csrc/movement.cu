@@ -131,15 +131,16 @@ __global__ void __launch_bounds__(256)
       uint4 rows[TOPK > 0 ? TOPK : 1];
 #pragma unroll
       for (int j = 0; j < TOPK; ++j) {
-        const int32_t slot = __ldg(inv_ids + t * TOPK + j);
-        rows[j] = ld_stream(y + int64_t(slot) * chunks_per_row + c);
+        const int32_t slot = __ldg(inv_ids + t * TOPK + j);   // < 0: the pair has no row (dropped)
+        rows[j] = slot >= 0 ? ld_stream(y + int64_t(slot) * chunks_per_row + c)
+                            : make_uint4(0u, 0u, 0u, 0u);
       }
 #pragma unroll
       for (int j = 0; j < TOPK; ++j) acc_bf16x8(acc, rows[j]);
     } else {
       for (int j = 0; j < top_k; ++j) {
         const int32_t slot = __ldg(inv_ids + t * top_k + j);
-        acc_bf16x8(acc, ld_stream(y + int64_t(slot) * chunks_per_row + c));
+        if (slot >= 0) acc_bf16x8(acc, ld_stream(y + int64_t(slot) * chunks_per_row + c));
       }
     }
     if (extra != nullptr) acc_bf16x8(acc, ld_stream(extra + i));
@@ -151,6 +152,68 @@ __global__ void __launch_bounds__(256)
       w[q] = *reinterpret_cast<const uint32_t*>(&h);
     }
     out[i] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// out[group of tile, c] += sum over the tile's 128 rows of w(row) * buf[row, c]. One block per
+// (tile, 256-column chunk); thread = one 8-column piece of one of 8 row phases; the phases are
+// folded through shared memory, then one fp32 atomic per column.
+__global__ void __launch_bounds__(256)
+    segment_colsum_kernel(const uint4* __restrict__ buf, int32_t pieces_per_row,
+                          const int32_t* __restrict__ expert_ids,
+                          const int32_t* __restrict__ n_post_pad,
+                          const int32_t* __restrict__ pad_offsets,
+                          const int32_t* __restrict__ sorted_ids,
+                          const __nv_bfloat16* __restrict__ pair_w, int32_t n_pairs,
+                          const uint4* __restrict__ alt, int64_t alt_rows, int32_t first_alt_group,
+                          float* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
+  const int tile = blockIdx.x;
+  if (int64_t(tile) * 128 >= __ldg(n_post_pad)) return;
+  const int group = __ldg(expert_ids + tile);
+  const int piece = blockIdx.y * 32 + (threadIdx.x & 31);   // 16-byte piece (8 columns) of the row
+  const int phase = threadIdx.x >> 5;                        // rows phase, phase + 8, ...
+  __shared__ float part[8][32][8];
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const bool from_alt = alt != nullptr && group >= first_alt_group;
+  const int64_t run0 = from_alt ? __ldg(pad_offsets + group) : 0;
+  if (piece < pieces_per_row) {
+    for (int r = phase; r < 128; r += 8) {
+      const int64_t slot = int64_t(tile) * 128 + r;
+      float w = 1.f;
+      if (pair_w != nullptr) {
+        const int32_t pr = __ldg(sorted_ids + slot);
+        w = pr < n_pairs ? __bfloat162float(__ldg(pair_w + pr)) : 0.f;
+      }
+      uint4 v;
+      if (from_alt) {
+        const int64_t tr = slot - run0;
+        if (tr >= alt_rows) continue;
+        v = ld_stream(alt + tr * pieces_per_row + piece);
+      } else {
+        v = ld_stream(buf + slot * pieces_per_row + piece);
+      }
+      const uint32_t wd[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wd[i]));
+        acc[2 * i] += w * f.x;
+        acc[2 * i + 1] += w * f.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) part[phase][threadIdx.x & 31][i] = acc[i];
+  __syncthreads();
+  // thread t: column t of the block's 256
+  const int c = threadIdx.x;
+  const int col = blockIdx.y * 256 + c;
+  if (col < pieces_per_row * 8) {
+    float sum = 0.f;
+#pragma unroll
+    for (int ph = 0; ph < 8; ++ph) sum += part[ph][c >> 3][c & 7];
+    atomicAdd(out + int64_t(group) * pieces_per_row * 8 + col, sum);
   }
 }
 
@@ -234,6 +297,29 @@ int moe_b200_combine(const void* y, const int32_t* inv_ids, int64_t n_tokens, in
     default: LAUNCH(0); break;
   }
 #undef LAUNCH
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+int moe_b200_segment_colsum(const void* buf, int64_t rows, int32_t width,
+                            const int32_t* expert_ids, const int32_t* n_post_pad,
+                            const int32_t* pad_offsets, int32_t n_groups,
+                            const int32_t* sorted_ids, const void* pair_w, int64_t n_pairs,
+                            const void* alt, int64_t alt_rows, int32_t first_alt_group,
+                            float* out, void* stream) {
+  if (rows < 0 || rows % 128 != 0 || width < 8 || width % 8 != 0 || n_groups < 1 || n_pairs < 0 ||
+      n_pairs > (int64_t(1) << 30))
+    return MOE_B200_ERR_SHAPE;
+  if (rows == 0) return MOE_B200_OK;
+  if (!buf || !expert_ids || !n_post_pad || !out) return MOE_B200_ERR_NULL;
+  if (pair_w && !sorted_ids) return MOE_B200_ERR_NULL;
+  if (alt && (!pad_offsets || alt_rows < 1 || first_alt_group < 0)) return MOE_B200_ERR_SHAPE;
+  if (!aligned16(buf) || !aligned16(alt)) return MOE_B200_ERR_ALIGN;
+  const int32_t ppr = width / 8;
+  launch_pdl(segment_colsum_kernel, dim3(unsigned(rows / 128), unsigned((ppr + 31) / 32)),
+             dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const uint4*>(buf), ppr,
+             expert_ids, n_post_pad, pad_offsets, sorted_ids,
+             static_cast<const __nv_bfloat16*>(pair_w), int32_t(n_pairs),
+             static_cast<const uint4*>(alt), alt_rows, first_alt_group, out);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 

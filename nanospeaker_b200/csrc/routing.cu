@@ -306,9 +306,15 @@ __global__ void __launch_bounds__(DISPATCH_THREADS)
                             int32_t* __restrict__ counts, int32_t* __restrict__ pad_offsets,
                             int32_t* __restrict__ n_post_pad, int32_t* __restrict__ expert_ids,
                             int64_t n_tiles_cap, int32_t* __restrict__ sorted_ids,
-                            int32_t* __restrict__ inv_ids) {
+                            int32_t* __restrict__ inv_ids, int32_t capacity, int32_t n_capped) {
   pdl_trigger();
   pdl_wait();
+  // capacity > 0: an expert keeps the first `capacity` pairs of its run (lowest pair ids) and drops
+  // the rest: a dropped pair gets no slot (inv_ids = -1) and the runs are laid out by the kept
+  // counts, while counts[] still reports the routing decisions. Only experts below n_capped are
+  // limited (the always-on shared experts dispatched as extra experts behind them are not).
+  const int32_t cap_all = capacity > 0 ? capacity : INT32_MAX;
+  auto cap_of = [&](int e) { return e < n_capped ? cap_all : INT32_MAX; };
   __shared__ int32_t total[MAX_EXPERTS];
   __shared__ int32_t before[MAX_EXPERTS];
   __shared__ int32_t off[MAX_EXPERTS + 1];
@@ -361,7 +367,7 @@ __global__ void __launch_bounds__(DISPATCH_THREADS)
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
       const int e = lane * PER + i;
-      pad[i] = e < n_experts ? (total[e] + ALIGN_M - 1) / ALIGN_M * ALIGN_M : 0;
+      pad[i] = e < n_experts ? (min(total[e], cap_of(e)) + ALIGN_M - 1) / ALIGN_M * ALIGN_M : 0;
       mine += pad[i];
     }
     int32_t incl = mine;
@@ -428,9 +434,9 @@ __global__ void __launch_bounds__(DISPATCH_THREADS)
       if (ev[u] >= 0) atomicAdd(&cursor[warp][ev[u]], 1);
   }
   __syncthreads();
-  // exclusive prefix over warps, seeded with the run start and the earlier blocks' share
+  // exclusive prefix over warps (ranks inside the expert's run), seeded with the earlier blocks' share
   for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
-    int32_t run = off[e] + before[e];
+    int32_t run = before[e];
     for (int w = 0; w < DISPATCH_WARPS; ++w) {
       const int32_t c = cursor[w][e];
       cursor[w][e] = run;
@@ -448,10 +454,16 @@ __global__ void __launch_bounds__(DISPATCH_THREADS)
       const int32_t e = ev[u];
       const unsigned peers = __match_any_sync(0xffffffffu, e);
       if (e >= 0) {
-        const int rank = __popc(peers & ((1u << lane) - 1u));
-        const int32_t dst = cursor[warp][e] + rank;
-        sorted_ids[dst] = int32_t(pidx);
-        inv_ids[pidx] = dst;
+        const int32_t rank = cursor[warp][e] + __popc(peers & ((1u << lane) - 1u));
+        if (rank < cap_of(e)) {
+          const int32_t dst = off[e] + rank;
+          sorted_ids[dst] = int32_t(pidx);
+          inv_ids[pidx] = dst;
+        } else {
+          inv_ids[pidx] = -1;   // over capacity: dropped
+        }
+      } else if (pidx < n_pairs && pidx < wend) {
+        inv_ids[pidx] = -1;     // expert id out of range (status word already set): no slot
       }
       __syncwarp();
       if (e >= 0 && lane == 31 - __clz(peers)) cursor[warp][e] += __popc(peers);
@@ -464,7 +476,8 @@ __global__ void __launch_bounds__(DISPATCH_THREADS)
 static int launch_dispatch(const int64_t* topk_idx, int64_t n_pairs, int32_t n_experts,
                            int32_t* sorted_ids, int32_t* expert_ids, int32_t* pad_offsets,
                            int32_t* counts, int32_t* n_post_pad, int32_t* inv_ids,
-                           int32_t* block_hist, int32_t* status, cudaStream_t st) {
+                           int32_t* block_hist, int32_t* status, cudaStream_t st,
+                           int32_t capacity = 0, int32_t n_capped = 0) {
   const int64_t l_cap = moe_b200_l_cap(n_pairs, n_experts);
   const int chunk = int(dispatch_chunk(n_pairs));
   const int blocks = int((n_pairs + chunk - 1) / chunk);
@@ -473,7 +486,7 @@ static int launch_dispatch(const int64_t* topk_idx, int64_t n_pairs, int32_t n_e
                n_experts, chunk, block_hist, sorted_ids, l_cap, status);
   launch_pdl(dispatch_scatter_kernel, dim3(blocks > 0 ? blocks : 1), dim3(DISPATCH_THREADS), 0, st,
              topk_idx, n_pairs, n_experts, chunk, blocks, block_hist, counts, pad_offsets,
-             n_post_pad, expert_ids, l_cap / ALIGN_M, sorted_ids, inv_ids);
+             n_post_pad, expert_ids, l_cap / ALIGN_M, sorted_ids, inv_ids, capacity, n_capped);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
@@ -548,16 +561,18 @@ int moe_b200_router_topk_bwd(const float* logits, const int64_t* topk_idx, const
 int moe_b200_dispatch(const int64_t* topk_idx, int64_t n_pairs, int32_t n_experts,
                       int32_t* sorted_ids, int32_t* expert_ids, int32_t* pad_offsets,
                       int32_t* counts, int32_t* n_post_pad, int32_t* inv_ids, void* scratch,
-                      size_t scratch_bytes, int32_t* status, void* stream) {
-  if (n_experts < 1 || n_experts > MAX_EXPERTS || n_pairs < 0 || n_pairs > (int64_t(1) << 30))
+                      size_t scratch_bytes, int32_t capacity, int32_t n_capped, int32_t* status,
+                      void* stream) {
+  if (n_experts < 1 || n_experts > MAX_EXPERTS || n_pairs < 0 || n_pairs > (int64_t(1) << 30) ||
+      capacity < 0 || n_capped < 0 || n_capped > n_experts)
     return MOE_B200_ERR_SHAPE;
-  if (!sorted_ids && n_pairs) return MOE_B200_ERR_NULL;
+  if (n_pairs && (!sorted_ids || !topk_idx || !inv_ids)) return MOE_B200_ERR_NULL;
   if (!pad_offsets || !counts || !n_post_pad || !status) return MOE_B200_ERR_NULL;
   if (scratch_bytes < moe_b200_dispatch_scratch_bytes(n_pairs, n_experts) || !scratch)
     return MOE_B200_ERR_SCRATCH;
   return launch_dispatch(topk_idx, n_pairs, n_experts, sorted_ids, expert_ids, pad_offsets, counts,
                          n_post_pad, inv_ids, static_cast<int32_t*>(scratch), status,
-                         static_cast<cudaStream_t>(stream));
+                         static_cast<cudaStream_t>(stream), capacity, n_capped);
 }
 
 }  // extern "C"
@@ -613,7 +628,7 @@ int moe_b200_router_dispatch(const void* logits, int32_t ld, const float* bias, 
   launch_pdl(dispatch_scatter_kernel, dim3(blocks), dim3(DISPATCH_THREADS), 0, st,
              static_cast<const int64_t*>(idx_all), n_pairs, int(n_all), tpb * kS, blocks,
              static_cast<const int32_t*>(block_hist), counts, pad_offsets, n_post_pad, expert_ids,
-             l_cap / ALIGN_M, sorted_ids, inv_ids);
+             l_cap / ALIGN_M, sorted_ids, inv_ids, 0, 0);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
@@ -625,8 +640,11 @@ int moe_b200_router_dispatch(const void* logits, int32_t ld, const float* bias, 
 // synchronise the device and fragment the pool), or a thin foreign-function caller that owns
 // pointers for its inputs and outputs but has no device allocator to ask for one more buffer.
 // For them the per-block histograms of the dispatch live in this fixed array instead. Every GPU
-// that loads the library carries it (256 KB) until the process exits.
-constexpr int STATIC_SCRATCH_INTS = 65536;  // blocks * n_experts must fit: 256 KB of int32
+// that loads the library carries it (128 KB) until the process exits. The dispatch never uses more
+// than DISPATCH_MAX_BLOCKS blocks (the chunk a block covers doubles instead) and never more than
+// MAX_EXPERTS experts, so the array covers every input the dispatch itself accepts.
+constexpr int STATIC_SCRATCH_INTS = DISPATCH_MAX_BLOCKS * MAX_EXPERTS;
+static_assert(STATIC_SCRATCH_INTS * sizeof(int32_t) == 128 * 1024, "128 KB of int32");
 static __device__ __align__(256) int32_t g_dispatch_scratch[STATIC_SCRATCH_INTS];
 
 namespace {
@@ -655,7 +673,7 @@ extern "C" {
 
 int64_t moe_b200_dispatch_static_max_pairs(int32_t n_experts) {
   if (n_experts < 1 || n_experts > MAX_EXPERTS) return 0;
-  return int64_t(STATIC_SCRATCH_INTS / n_experts) * 4096;
+  return int64_t(1) << 30;   // the dispatch's own limit: the array is never the tighter one
 }
 
 int moe_b200_dispatch_static(const int64_t* topk_idx, int64_t n_pairs, int32_t n_experts,
@@ -663,8 +681,10 @@ int moe_b200_dispatch_static(const int64_t* topk_idx, int64_t n_pairs, int32_t n
                              int32_t* counts, int32_t* n_post_pad, int32_t* inv_ids,
                              int32_t* status, void* stream) {
   if (n_experts < 1 || n_experts > MAX_EXPERTS || n_pairs < 0) return MOE_B200_ERR_SHAPE;
-  if (n_pairs > moe_b200_dispatch_static_max_pairs(n_experts)) return MOE_B200_ERR_TOO_LARGE;
-  if (!sorted_ids && n_pairs) return MOE_B200_ERR_NULL;
+  if (n_pairs > moe_b200_dispatch_static_max_pairs(n_experts) ||
+      moe_b200_dispatch_scratch_bytes(n_pairs, n_experts) > sizeof(int32_t) * STATIC_SCRATCH_INTS)
+    return MOE_B200_ERR_TOO_LARGE;
+  if (n_pairs && (!sorted_ids || !topk_idx || !inv_ids)) return MOE_B200_ERR_NULL;
   if (!pad_offsets || !counts || !n_post_pad || !status) return MOE_B200_ERR_NULL;
   int32_t* block_hist = nullptr;
   const int rc = static_scratch_for_current_device(&block_hist);

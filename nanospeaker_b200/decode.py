@@ -41,7 +41,7 @@ class StackedMoEDecoder:
         """Per-block constants of the kernel path (weights are fixed while decoding): the padded
         router weight and the weights in x.dtype, built on first use. None when the block's
         kernels decline this input (then the block's own forward runs)."""
-        if not b._use_kernel(x):
+        if not b._whole_block_ok(x):      # biases, a capacity, ...: the block's own forward
             return None
         key = (id(b), x.dtype, x.device)
         if key not in self._consts:

@@ -175,8 +175,10 @@ def balance_loss(colsum, counts, n_experts: int, n_tokens: int, aux_coef: float)
     return aux
 
 
-def dispatch(topk_idx: torch.Tensor, n_experts: int):
-    """int64 topk_idx [T, k] -> (sorted_ids, expert_ids, pad_offsets, counts, n_post_pad, inv_ids)."""
+def dispatch(topk_idx: torch.Tensor, n_experts: int, capacity: int = 0, n_capped: int = -1):
+    """int64 topk_idx [T, k] -> (sorted_ids, expert_ids, pad_offsets, counts, n_post_pad, inv_ids).
+    capacity > 0: every expert below n_capped (default: all) keeps the first `capacity` pairs of its
+    run; dropped pairs get inv_ids = -1 and no slot, counts still reports the routing decisions."""
     _need_cuda(topk_idx)
     flat = topk_idx.reshape(-1).contiguous()
     if flat.dtype != torch.int64:
@@ -195,8 +197,9 @@ def dispatch(topk_idx: torch.Tensor, n_experts: int):
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     _lib.check(lib.moe_b200_dispatch(
         flat.data_ptr(), m, n_experts, sids.data_ptr(), eids.data_ptr(), offs.data_ptr(),
-        counts.data_ptr(), npp.data_ptr(), inv.data_ptr(), scratch.data_ptr(), nbytes,
-        status_word(dev).data_ptr(), _stream(flat)), "moe_b200_dispatch")
+        counts.data_ptr(), npp.data_ptr(), inv.data_ptr(), scratch.data_ptr(), nbytes, capacity,
+        n_experts if n_capped < 0 else n_capped, status_word(dev).data_ptr(), _stream(flat)),
+        "moe_b200_dispatch")
     _count(3 if m else 1)
     return sids, eids, offs, counts, npp, inv
 
@@ -225,6 +228,25 @@ def combine(y: torch.Tensor, inv_ids: torch.Tensor, n_tokens: int, top_k: int,
         y.data_ptr(), inv_ids.data_ptr(), n_tokens, top_k, d, _lib.ptr(extra), _lib.ptr(extra2),
         out.data_ptr(), _stream(y)), "moe_b200_combine")
     _count(1 if n_tokens else 0)
+    return out
+
+
+def segment_colsum(buf, expert_ids, n_post_pad, n_groups: int, sorted_ids=None, pair_w=None,
+                   n_pairs: int = 0, token_rows=None) -> torch.Tensor:
+    """fp32 [n_groups, width]: per expert the column sums of its run's rows of the slot-ordered
+    buf [rows, width], each row weighted by pair_w[sorted_ids[row]] when pair_w is given.
+    token_rows=(matrix, pad_offsets, first_group): the runs from first_group on read their rows
+    from the token-major matrix (row = slot - start of the run) instead of from buf."""
+    _need_cuda(buf)
+    rows, width = buf.shape
+    out = torch.zeros((n_groups, width), dtype=torch.float32, device=buf.device)
+    alt, offs, first = token_rows if token_rows is not None else (None, None, 0)
+    _lib.check(_lib.load().moe_b200_segment_colsum(
+        buf.data_ptr(), rows, width, expert_ids.data_ptr(), n_post_pad.data_ptr(), _lib.ptr(offs),
+        n_groups, _lib.ptr(sorted_ids), _lib.ptr(pair_w), n_pairs, _lib.ptr(alt),
+        alt.shape[0] if alt is not None else 0, first, out.data_ptr(), _stream(buf)),
+        "moe_b200_segment_colsum")
+    _count(1 if rows else 0)
     return out
 
 

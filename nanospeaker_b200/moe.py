@@ -7,14 +7,15 @@ the reference, so its callers (Block in src/model/nanospeaker.py:153-169, moe_he
 src/train/metrics.py:84-97) and its checkpoints work unchanged.
 
 Paths, in the order `forward` tries them:
-  1. kernel    CUDA + bf16 + a named activation + no capacity cap + shapes the tiles
-               cover: router top-k, dispatch, permute, grouped GEMMs, combine and the shared
-               experts all run as the `moe_b200` ops. No host sync. A missing or failing library
-               raises; nothing is silently rerouted.
-  2. padded    a capacity_factor is set: fixed-capacity batched GEMM in torch
-               (src/model/moe.py:225-283); not a dropless path and not accelerated here.
-  3. eager     the ragged per-expert loop in torch (src/model/moe.py:377-418) for everything the
-               kernels decline (CPU, fp32/fp64, custom activations).
+  1. kernel    CUDA + bf16 + a named activation + shapes the tiles cover: router top-k, dispatch,
+               permute, grouped GEMMs, combine and the shared experts all run as the `moe_b200`
+               ops (one whole-block op when there are no biases, no exploration noise and no
+               capacity; router + dispatch + experts ops otherwise). No host sync. A missing or
+               failing library raises; nothing is silently rerouted. An explicit capacity_factor
+               (the reference's padded path, src/model/moe.py:225-283) runs on the same kernels:
+               the dispatch drops the pairs over capacity instead of padding a batch.
+  2. torch     the per-expert loop in plain torch (src/model/moe.py:377-418) for everything the
+               kernels decline (CPU, fp32/fp64, custom activations), with or without a capacity.
 """
 import math
 
@@ -112,8 +113,19 @@ class MoEBlock(nn.Module):
         return None if self._kernel_ready() else AUTO_CAPACITY
 
     def _use_kernel(self, x: torch.Tensor) -> bool:
+        """The dropless kernel path (the gate of src/model/moe.py:331-343)."""
         return (self._kernel_config_ok() and self.capacity_factor is None
                 and kernel_supported(x))
+
+    def _kernels_take(self, x: torch.Tensor) -> bool:
+        """Any kernel path: dropless, or an explicit capacity as a variant of the dispatch."""
+        return self._kernel_config_ok() and kernel_supported(x)
+
+    def _whole_block_ok(self, x: torch.Tensor) -> bool:
+        """Can `forward` hand x to the single whole-block op? It has no bias operands, draws no
+        exploration noise and knows no capacity, so those cases take router + fused_moe_forward."""
+        return (self._use_kernel(x) and self.b_in is None and self.b_sh_in is None
+                and not (self.training and self.router.noise_std))
 
     # ---------------------------------------------------------------------------- bookkeeping
     def _record(self, probs, counts, x):
@@ -124,71 +136,62 @@ class MoEBlock(nn.Module):
             self.aux_loss = torch.zeros((), device=x.device, dtype=x.dtype)
 
     def _plan(self, topk_idx: torch.Tensor):
-        """Stable sort of the flat expert ids: (experts, order, token_idx, counts), all int64
-        (src/model/moe.py:208-223). `order` is the canonical permutation the CUDA dispatch also
-        produces."""
-        experts, order = topk_idx.reshape(-1).sort(stable=True)
-        token_idx = order.div(self.top_k, rounding_mode="floor")
-        counts = torch.searchsorted(experts, self.edges).diff()
-        return experts, order, token_idx, counts
+        """(experts, order, token_idx, counts), all int64: the flat pair ids `order` sorted by
+        expert with ties in ascending pair id, the expert and the token of each sorted pair, and
+        the per-expert histogram -- the canonical permutation of src/model/moe.py:208-223, which
+        the CUDA dispatch reproduces."""
+        flat = topk_idx.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        counts = torch.zeros(self.n_experts, dtype=torch.long, device=flat.device)
+        counts.scatter_add_(0, flat, torch.ones_like(flat))
+        return flat[order], order, order // self.top_k, counts
+
+    def _capacity(self, n_tokens: int) -> int:
+        """Pairs an expert may keep: capacity_factor x the fair share of the n_tokens * top_k
+        pairs, at least 1 and at most all of them (src/model/moe.py:225-231)."""
+        pairs = n_tokens * self.top_k
+        return min(max(math.ceil(self.capacity_factor * pairs / self.n_experts), 1), pairs)
 
     # ------------------------------------------------------------------------ torch paths
-    def _expert(self, e, x, w, wts):
-        w_in, w_out, b_in, b_out = wts
-        h = x @ w_in[e]
+    def _mlp(self, x, w_in, b_in, w_out, b_out):
+        """One GLU expert on the rows of x."""
+        h = x @ w_in
         if b_in is not None:
-            h = h + b_in[e]
+            h = h + b_in
         gate, up = h.chunk(2, dim=-1)
-        y = self.glu(gate, up) @ w_out[e]
-        if b_out is not None:
-            y = y + b_out[e]
-        return y * w[:, None]
+        y = self.glu(gate, up) @ w_out
+        return y if b_out is None else y + b_out
 
     def _shared(self, x):
+        """Sum of the always-on experts on every token (src/model/moe.py:310-329)."""
         total = None
         for s in range(self.n_shared):
-            h = x @ self.W_sh_in[s]
-            if self.b_sh_in is not None:
-                h = h + self.b_sh_in[s]
-            gate, up = h.chunk(2, dim=-1)
-            y = self.glu(gate, up) @ self.W_sh_out[s]
-            if self.b_sh_out is not None:
-                y = y + self.b_sh_out[s]
+            y = self._mlp(x, self.W_sh_in[s], None if self.b_sh_in is None else self.b_sh_in[s],
+                          self.W_sh_out[s], None if self.b_sh_out is None else self.b_sh_out[s])
             total = y if total is None else total + y
         return total
 
-    def _capacity(self, n_tokens: int) -> int:
-        fair = n_tokens * self.top_k / self.n_experts
-        return max(1, min(math.ceil(self.capacity_factor * fair), n_tokens * self.top_k))
-
-    def _slots(self, experts, counts, cap: int):
-        starts = counts.cumsum(0) - counts
-        rank = torch.arange(experts.numel(), device=experts.device) - starts[experts]
-        keep = rank < cap
-        return torch.where(keep, experts * cap + rank, self.n_experts * cap), keep
-
-    def _forward_padded(self, x, experts, order, token_idx, counts, topk_w, shape):
-        n = x.shape[0]
-        cap = self._capacity(n)
-        slot, keep = self._slots(experts, counts, cap)
-        self.dropped = (~keep).sum().detach()
-        buf = x.new_zeros(self.n_experts * cap + 1, self.d_model)
-        buf.index_copy_(0, slot, x.index_select(0, token_idx))
-        buf = buf[: self.n_experts * cap].view(self.n_experts, cap, self.d_model)
-        h = buf @ self.W_in
-        if self.b_in is not None:
-            h = h + self.b_in[:, None, :]
-        gate, up = h.chunk(2, dim=-1)
-        y = self.glu(gate, up) @ self.W_out
-        if self.b_out is not None:
-            y = y + self.b_out[:, None, :]
-        y = torch.cat((y.reshape(-1, self.d_model), y.new_zeros(1, self.d_model)))
-        w = topk_w.reshape(-1).index_select(0, order)
+    def _torch_experts(self, x, topk_w, topk_idx, cap: int):
+        """The routed experts in plain torch, for what the kernels decline (CPU tensors, fp32 /
+        fp64, unnamed activations): expert by expert over the sorted pairs, each expert's rows
+        gathered, run through its GLU MLP, scaled by the router weight and added to their tokens
+        (the arithmetic of src/model/moe.py:285-308, 396-413). With a capacity only the first
+        `cap` pairs of a run are visited; the rest are dropped (src/model/moe.py:233-283)."""
+        _, order, token_idx, counts = self._plan(topk_idx)
+        pair_w = topk_w.reshape(-1)[order]
+        kept = counts.clamp(max=cap) if cap else counts
+        if cap:
+            self.dropped = (counts - kept).sum().detach()
+        starts = (counts.cumsum(0) - counts).tolist()      # the one host sync of this path
         out = torch.zeros_like(x)
-        out.index_add_(0, token_idx, y.index_select(0, slot) * w[:, None])
-        if self.n_shared:
-            out = out + self._shared(x)
-        return out.view(shape)
+        for e, (lo, n) in enumerate(zip(starts, kept.tolist())):
+            if n == 0:
+                continue
+            rows = token_idx[lo:lo + n]
+            y = self._mlp(x[rows], self.W_in[e], None if self.b_in is None else self.b_in[e],
+                          self.W_out[e], None if self.b_out is None else self.b_out[e])
+            out.index_add_(0, rows, y * pair_w[lo:lo + n, None])
+        return out, counts
 
     # ------------------------------------------------------------------------------ forward
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -198,8 +201,7 @@ class MoEBlock(nn.Module):
         x = x.reshape(-1, self.d_model)
         if x.shape[0] == 0:
             return x.clone().view(shape)
-        if (self._use_kernel(x) and self.b_in is None
-                and not (self.training and self.router.noise_std)):
+        if self._whole_block_ok(x):
             # whole block as one op: router GEMM, top-k, dispatch, experts, combine, balance loss
             full = self.router.wants_probs()
             out, aux, counts = fused_moe_block(
@@ -210,39 +212,31 @@ class MoEBlock(nn.Module):
             return out.view(shape)
 
         topk_w, topk_idx, probs = self.router(x)
+        cap = self._capacity(x.shape[0]) if self.capacity_factor is not None else 0
 
-        if self._use_kernel(x):
+        if self._kernels_take(x):
+            # biases, exploration noise (drawn by the router above) or a capacity: the same kernels
+            # behind the router, the capacity as a variant of the dispatch schedule
             out, counts = fused_moe_forward(
                 x, self.W_in, self.W_out, topk_w, topk_idx, self.b_in, self.b_out,
                 self._kernel_act, w_sh_in=self.W_sh_in, w_sh_out=self.W_sh_out,
-                combine=self.combine_mode,
-            )
+                combine=self.combine_mode, b_sh_in=self.b_sh_in, b_sh_out=self.b_sh_out,
+                capacity=cap)
             self._record(probs, counts, x)
+            if cap:
+                self.dropped = (counts - cap).clamp(min=0).sum().detach().long()
             return out.view(shape)
 
-        experts, order, token_idx, counts = self._plan(topk_idx)
+        out, counts = self._torch_experts(x, topk_w, topk_idx, cap)
         self._record(probs, counts, x)
-        if self.capacity_factor is not None:
-            return self._forward_padded(x, experts, order, token_idx, counts, topk_w, shape)
-
-        sizes = counts.tolist()
-        xs = x.index_select(0, token_idx).split(sizes)
-        ws = topk_w.reshape(-1).index_select(0, order).split(sizes)
-        rows = token_idx.split(sizes)
-        wts = (self.W_in.unbind(0), self.W_out.unbind(0),
-               None if self.b_in is None else self.b_in.unbind(0),
-               None if self.b_out is None else self.b_out.unbind(0))
-        out = torch.zeros_like(x)
-        for e in range(self.n_experts):
-            if sizes[e]:
-                out.index_add_(0, rows[e], self._expert(e, xs[e], ws[e], wts))
         if self.n_shared:
             out = out + self._shared(x)
         return out.view(shape)
 
     def dense_forward(self, x: torch.Tensor) -> torch.Tensor:
-        """Every expert on every token, mixed by a dense [N, E] gate matrix: the shape-static
-        cross-check of `forward` (src/model/moe.py:420-474). Same side effects as `forward`."""
+        """Every expert on every token, mixed by a dense [N, E] gate matrix that is zero off the
+        selected (and, under a capacity, kept) pairs: the shape-static cross-check of `forward`
+        (src/model/moe.py:420-474). Same side effects as `forward`."""
         if x.shape[-1] != self.d_model:
             raise ValueError(f"expected last dim {self.d_model}, got {tuple(x.shape)}.")
         shape = x.shape
@@ -251,20 +245,18 @@ class MoEBlock(nn.Module):
         experts, order, _, counts = self._plan(topk_idx)
         self._record(probs, counts, x)
         if self.capacity_factor is not None and x.shape[0]:
-            _, keep = self._slots(experts, counts, self._capacity(x.shape[0]))
-            kept = torch.empty_like(keep).index_copy_(0, order, keep)
-            self.dropped = (~keep).sum().detach()
+            cap = self._capacity(x.shape[0])
+            pos = torch.arange(order.numel(), device=x.device) - (counts.cumsum(0) - counts)[experts]
+            kept = torch.zeros_like(order, dtype=torch.bool).scatter_(0, order, pos < cap)
+            self.dropped = (~kept).sum().detach()
             topk_w = topk_w * kept.view_as(topk_w)
         gates = torch.zeros(x.shape[0], self.n_experts, dtype=x.dtype, device=x.device)
         gates.scatter_(1, topk_idx, topk_w)
-        h = x @ self.W_in
-        if self.b_in is not None:
-            h = h + self.b_in[:, None, :]
-        gate, up = h.chunk(2, dim=-1)
-        y = self.glu(gate, up) @ self.W_out
-        if self.b_out is not None:
-            y = y + self.b_out[:, None, :]
-        out = torch.einsum("enf,ne->nf", y, gates)
+        out = torch.zeros_like(x)
+        for e in range(self.n_experts):
+            y = self._mlp(x, self.W_in[e], None if self.b_in is None else self.b_in[e],
+                          self.W_out[e], None if self.b_out is None else self.b_out[e])
+            out = out + gates[:, e:e + 1] * y
         if self.n_shared:
             out = out + self._shared(x)
         return out.view(shape)

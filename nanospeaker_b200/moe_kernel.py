@@ -128,17 +128,22 @@ router_topk.register_autograd(_router_backward, setup_context=_router_setup)
 
 # ---------------------------------------------------------------------------------- dispatch
 @torch.library.custom_op("moe_b200::moe_dispatch", mutates_args=())
-def moe_dispatch(topk_idx: torch.Tensor, n_experts: int) -> Tuple[
+def moe_dispatch(topk_idx: torch.Tensor, n_experts: int, capacity: int = 0,
+                 n_capped: int = -1) -> Tuple[
     torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor
 ]:
     """(sorted_ids [l_cap], expert_ids [l_cap/128], pad_offsets [E+1], counts [E], n_post_pad [1],
     inv_ids [M]) as int32 -- the tuple of src/model/moe_kernel.py:180-209, with one stronger
-    guarantee: inside a run, pairs are in ascending pair id (a stable sort by expert)."""
-    return K.dispatch(topk_idx, n_experts)
+    guarantee: inside a run, pairs are in ascending pair id (a stable sort by expert).
+
+    capacity > 0 turns the plan into the fixed-capacity schedule (src/model/moe.py:225-283): the
+    experts below n_capped (default: all) keep the first `capacity` pairs of their runs, the other
+    pairs get no slot (inv_ids = -1); counts still holds the routing decisions."""
+    return K.dispatch(topk_idx, n_experts, capacity, n_capped)
 
 
 @moe_dispatch.register_fake
-def _(topk_idx, n_experts):
+def _(topk_idx, n_experts, capacity=0, n_capped=-1):
     m = topk_idx.numel()
     cap = _l_cap(m, n_experts)
     mk = lambda n: topk_idx.new_empty((n,), dtype=torch.int32)
@@ -186,11 +191,16 @@ def moe_experts(
     b_in: Optional[torch.Tensor] = None,
     b_out: Optional[torch.Tensor] = None,
     atomic_combine: bool = False,
+    b_sh_in: Optional[torch.Tensor] = None,
+    b_sh_out: Optional[torch.Tensor] = None,
+    has_dropped: bool = False,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """out[t] = sum_j topk_w[t,j] * expert_{idx[t,j]}(x[t]) on pre-dispatched pairs.
 
-    Optional per-expert biases of the routed experts, b_in [E, 2H] and b_out [E, D], are added in
-    the GEMM epilogues (before the GLU / before the weight scale, src/model/moe.py:295-305).
+    Optional per-expert biases, b_in [E, 2H] / b_out [E, D] of the routed experts and b_sh_in
+    [S, 2H] / b_sh_out [S, D] of the shared ones, are added in the GEMM epilogues (before the GLU /
+    before the weight scale, src/model/moe.py:295-305, 317-326). has_dropped: the plan was built
+    with a capacity, so some pairs may have no slot (their d topk_w is then zero).
 
     up/gate GEMM with the GLU fused -> down GEMM with fused router weight -> token-major fp32
     combine. All tensors share x's dtype (the wrapper casts). Two ways to feed the up GEMM:
@@ -221,8 +231,7 @@ def moe_experts(
     tw = topk_w.reshape(-1).contiguous()
     if w_sh_in is not None:
         w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
-    b_in = None if b_in is None else b_in.to(x.dtype).contiguous()
-    b_out = None if b_out is None else b_out.to(x.dtype).contiguous()
+    b_in, b_out = _all_bias(b_in, b_sh_in, w_in, w_sh_in, 2), _all_bias(b_out, b_sh_out, w_out, w_sh_out, 2)
     # the accumulator of the atomic combine is cleared first thing, far ahead of the GEMM that adds to it
     out = torch.zeros_like(x) if atomic_combine else None
 
@@ -248,12 +257,24 @@ def moe_experts(
 @moe_experts.register_fake
 def _(x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
       n_post_pad, inv_ids, activation, save_for_backward, b_in=None, b_out=None,
-      atomic_combine=False):
+      atomic_combine=False, b_sh_in=None, b_sh_out=None, has_dropped=False):
     n, d = x.shape
     if n == 0 or not save_for_backward:
         return x.new_empty((n, d)), x.new_empty(0), x.new_empty(0)
     cap = sorted_ids.shape[0]
     return x.new_empty(x.shape), x.new_empty((cap, d)), x.new_empty((cap, w_in.shape[2]))
+
+
+def _all_bias(b, b_sh, w, w_sh, dim):
+    """One bias row per group of both weight stacks ([E + S, width] in w's dtype), as the GEMM
+    epilogues index them; None when neither stack has a bias."""
+    if b is None and b_sh is None:
+        return None
+    e_n, s_n, width = w.shape[0], 0 if w_sh is None else w_sh.shape[0], w.shape[dim]
+    rows = [b if b is not None else w.new_zeros((e_n, width))]
+    if s_n:
+        rows.append(b_sh if b_sh is not None else w.new_zeros((s_n, width)))
+    return torch.cat([r.to(w.dtype) for r in rows], 0).contiguous()
 
 
 def _routed_rows(src, w_in, w_sh_in, pad_offsets, n_post_pad):
@@ -290,14 +311,17 @@ def moe_experts_bwd(
     b_out: Optional[torch.Tensor] = None,
     need_db_in: bool = False,
     atomic_combine: bool = False,
+    need_db_out: bool = False,
+    has_dropped: bool = False,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor,
            torch.Tensor, torch.Tensor]:
-    """(dx, dW_in, dW_out, dtopk_w, dW_sh_in, dW_sh_out, db_in, db_out); the shared-expert and bias
-    gradients are empty when the forward had none. The kept pre-activations a1 already include
-    b_in, so only b_out's value enters the backward (through dtopk_w); the bias gradients are
-    segment sums over each expert's run, done with sync-free torch ops as the reference does
-    (src/model/moe_kernel.py:723-737). xs (x in slot order) and a1 (pre-activations) are what the forward kept; grad_out is
-    permuted once and feeds both the dHidden GEMM and the dW_out GEMM."""
+    """(dx, dW_in, dW_out, dtopk_w, dW_sh_in, dW_sh_out, db_in_all, db_out_all); the shared-expert
+    and bias gradients are empty when the forward had none. The bias gradients cover the groups of
+    both weight stacks ([E + S, width]: routed experts first). The kept pre-activations a1 already
+    include b_in, so only b_out's value ([E, D], routed experts) enters the backward, through
+    dtopk_w. xs (x in slot order) and a1 are what the forward kept; grad_out is permuted once and
+    feeds both the dHidden GEMM and the dW_out GEMM. The bias gradients are segment sums over each
+    expert's run (src/model/moe_kernel.py:723-737), here one column-sum kernel each."""
     grad_out = grad_out.to(x.dtype).contiguous()
     x, w_in, w_out = x.contiguous(), w_in.contiguous(), w_out.contiguous()
     _check_inputs(x, w_in, w_out, w_sh_in)
@@ -312,11 +336,14 @@ def moe_experts_bwd(
     m = n * topk
     tw = topk_w.reshape(-1).contiguous()
     dx = torch.zeros_like(x) if atomic_combine else None
+    # pairs without a slot (dropped by a capacity) are never visited by the dHidden epilogue
+    dtw_buf = torch.zeros(m, dtype=x.dtype, device=x.device) if has_dropped else None
 
     live, tok = _routed_rows(grad_out, w_in, w_sh_in, pad_offsets, n_post_pad)
     douts = K.permute(grad_out, topk, sorted_ids, live)
     da1, hidw, dtw = K.dhidden_glu_bwd(douts, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m,
-                                       a1, act, True, w_extra=w_sh_out, token_rows=tok)
+                                       a1, act, True, w_extra=w_sh_out, token_rows=tok,
+                                       dtw_out=dtw_buf)
     if atomic_combine:
         K.dx_gemm_acc(da1, w_in, expert_ids, n_post_pad, 0, sorted_ids, m, topk, dx, w_extra=w_sh_in)
     else:
@@ -332,47 +359,46 @@ def moe_experts_bwd(
         dw_in, dw_out, dw_sh_in, dw_sh_out = g_in, g_out, x.new_empty(0), x.new_empty(0)
     dtw = dtw.view_as(topk_w)
     db_in, db_out = x.new_empty(0), x.new_empty(0)
-    if need_db_in:
-        # column sums of dA1 over each expert's run: per 128-row tile first (the tiles past the live
-        # length hold whatever the allocator left there and are masked out), then per expert
-        tiles = da1.shape[0] // ALIGN_M
-        sums = da1.view(tiles, ALIGN_M, -1).sum(1, dtype=torch.float32)
-        live_tile = (torch.arange(tiles, device=x.device) * ALIGN_M < n_post_pad).unsqueeze(1)
-        sums = torch.where(live_tile, sums, torch.zeros((), device=x.device))
-        db_in = torch.zeros((e_n + s_n, da1.shape[1]), dtype=torch.float32, device=x.device) \
-            .index_add_(0, expert_ids.long(), sums)[:e_n].to(x.dtype)
+    if need_db_in:      # db_in[e] = column sums of dA1 over e's run
+        db_in = K.segment_colsum(da1, expert_ids, n_post_pad, e_n + s_n).to(x.dtype)
+    if need_db_out:     # db_out[e] = sum over e's pairs of w * dOut[t]
+        db_out = K.segment_colsum(
+            douts, expert_ids, n_post_pad, e_n + s_n, sorted_ids, tw, m,
+            token_rows=(grad_out, pad_offsets, e_n) if s_n else None).to(x.dtype)
     if b_out is not None:
-        # y_pair = (hid W_out + b_out[e]) * w: dtopk_w gains <dOut[t], b_out[e]>, and
-        # db_out[e] = sum over e's pairs of w * dOut[t]
-        e_of_pair = expert_ids.long()[inv_ids.long() // ALIGN_M].view(n, topk)
-        gb = grad_out.float() @ b_out.float().t()                       # [T, E]
-        if s_n:
-            gb = torch.cat([gb, gb.new_zeros((n, s_n))], 1)             # shared experts: no bias
-        dtw = (dtw.float() + gb.gather(1, e_of_pair)).to(topk_w.dtype)
-        gates = torch.zeros((n, e_n + s_n), dtype=torch.float32, device=x.device) \
-            .scatter_add_(1, e_of_pair, topk_w.float())
-        db_out = (gates[:, :e_n].t() @ grad_out.float()).to(x.dtype)
+        # y_pair = (hid W_out + b_out[e]) * w: dtopk_w gains <dOut[t], b_out[e]>. One row GEMM
+        # dOut @ b_out^T -> [T, E (padded)], then each pair picks its expert's column.
+        ld = _router_ld(e_n)
+        bt = K.copy_cols(b_out.to(x.dtype).t().contiguous(), ld).unsqueeze(0)      # [1, D, ld]
+        gb = K.down_gemm(grad_out, bt, None, None, 1, None, None, 0)[0]             # [T, ld]
+        slot = inv_ids.long().view(n, topk)
+        e_of_pair = expert_ids.long()[slot.clamp(min=0) // ALIGN_M]
+        routed = (e_of_pair < e_n) & (slot >= 0)       # shared experts' d topk_w is not used
+        pick = gb.gather(1, e_of_pair.clamp(max=e_n - 1)).float()
+        dtw = (dtw.float() + torch.where(routed, pick, torch.zeros((), device=x.device))) \
+            .to(topk_w.dtype)
     return dx, dw_in, dw_out, dtw, dw_sh_in, dw_sh_out, db_in, db_out
 
 
 @moe_experts_bwd.register_fake
 def _(grad_out, x, xs, a1, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
       pad_offsets, counts, n_post_pad, inv_ids, activation, b_out=None, need_db_in=False,
-      atomic_combine=False):
-    e_n = w_in.shape[0]
+      atomic_combine=False, need_db_out=False, has_dropped=False):
+    g_n = w_in.shape[0] + (0 if w_sh_in is None else w_sh_in.shape[0])
     return (torch.empty_like(x), torch.empty_like(w_in), torch.empty_like(w_out),
             torch.empty_like(topk_w),
             torch.empty_like(w_sh_in) if w_sh_in is not None else x.new_empty(0),
             torch.empty_like(w_sh_out) if w_sh_out is not None else x.new_empty(0),
-            x.new_empty((e_n, w_in.shape[2])) if need_db_in else x.new_empty(0),
-            x.new_empty((e_n, x.shape[1])) if b_out is not None else x.new_empty(0))
+            x.new_empty((g_n, w_in.shape[2])) if need_db_in else x.new_empty(0),
+            x.new_empty((g_n, x.shape[1])) if need_db_out else x.new_empty(0))
 
 
 def _experts_setup(ctx, inputs, output):
     (x, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids, pad_offsets, counts,
-     n_post_pad, inv_ids, activation, save_for_backward, b_in, b_out, atomic_combine) = inputs
+     n_post_pad, inv_ids, activation, save_for_backward, b_in, b_out, atomic_combine, b_sh_in,
+     b_sh_out, has_dropped) = inputs
     out, xs, a1 = output
-    ctx.atomic_combine = atomic_combine
+    ctx.atomic_combine, ctx.has_dropped = atomic_combine, has_dropped
     ctx.mark_non_differentiable(xs, a1)
     # without this autograd would hand the backward zero-filled gradients for the kept buffers
     ctx.set_materialize_grads(False)
@@ -384,9 +410,10 @@ def _experts_setup(ctx, inputs, output):
     ctx.has_shared = w_sh_in is not None
     if ctx.has_shared:
         saved += [w_sh_in, w_sh_out]
-    # b_in's value is not needed again (a1 was kept with it inside), b_out's is (for dtopk_w)
-    ctx.has_b_in, ctx.has_b_out = b_in is not None, b_out is not None
-    if ctx.has_b_out:
+    # the values of b_in / b_sh_* are not needed again (a1 was kept with b_in inside, the shared
+    # experts' router weight is a constant), b_out's is (for dtopk_w)
+    ctx.has_b = (b_in is not None, b_out is not None, b_sh_in is not None, b_sh_out is not None)
+    if b_out is not None:
         saved.append(b_out)
     ctx.save_for_backward(*saved)
     ctx.activation = activation
@@ -396,16 +423,19 @@ def _experts_backward(ctx, grad_out, g_xs, g_a1):
     (x, xs, a1, w_in, w_out, topk_w, sorted_ids, expert_ids, pad_offsets, counts, n_post_pad,
      inv_ids, *rest) = ctx.saved_tensors
     w_sh_in, w_sh_out = (rest[0], rest[1]) if ctx.has_shared else (None, None)
-    b_out = rest[-1] if ctx.has_b_out else None
+    has_b_in, has_b_out, has_b_sh_in, has_b_sh_out = ctx.has_b
+    b_out = rest[-1] if has_b_out else None
     if grad_out is None:
         grad_out = torch.zeros_like(x)
     dx, dw_in, dw_out, dtw, dsi, dso, db_in, db_out = moe_experts_bwd(
         grad_out, x, xs, a1, w_in, w_out, topk_w, w_sh_in, w_sh_out, sorted_ids, expert_ids,
-        pad_offsets, counts, n_post_pad, inv_ids, ctx.activation, b_out, ctx.has_b_in,
-        ctx.atomic_combine)
+        pad_offsets, counts, n_post_pad, inv_ids, ctx.activation, b_out,
+        has_b_in or has_b_sh_in, ctx.atomic_combine, has_b_out or has_b_sh_out, ctx.has_dropped)
+    e_n = w_in.shape[0]
     return (dx, dw_in, dw_out, dtw, dsi if ctx.has_shared else None,
             dso if ctx.has_shared else None, None, None, None, None, None, None, None, None,
-            db_in if ctx.has_b_in else None, db_out if ctx.has_b_out else None, None)
+            db_in[:e_n] if has_b_in else None, db_out[:e_n] if has_b_out else None, None,
+            db_in[e_n:] if has_b_sh_in else None, db_out[e_n:] if has_b_sh_out else None, None)
 
 
 moe_experts.register_autograd(_experts_backward, setup_context=_experts_setup)
@@ -713,11 +743,15 @@ def moe_block_inference(x, router_w_padded, logit_bias, w_in, w_out, w_sh_in, w_
 
 # ------------------------------------------------------------------------------- entry point
 def fused_moe_forward(x, w_in, w_out, topk_w, topk_idx, b_in, b_out, activation,
-                      w_sh_in=None, w_sh_out=None, combine: Optional[str] = None):
+                      w_sh_in=None, w_sh_out=None, combine: Optional[str] = None,
+                      b_sh_in=None, b_sh_out=None, capacity: int = 0):
     """Dispatch + experts on the GPU; returns (out [N, d_model], counts [n_experts] int32).
 
     Same contract as src/model/moe_kernel.py:785-803, plus optional stacked shared-expert weights
-    (`w_sh_in [S, D, 2H]`, `w_sh_out [S, H, D]`) whose outputs are then included in `out`.
+    (`w_sh_in [S, D, 2H]`, `w_sh_out [S, H, D]`, biases `b_sh_in [S, 2H]`, `b_sh_out [S, D]`) whose
+    outputs are then included in `out`, and an optional per-expert `capacity` (> 0: every routed
+    expert keeps the first `capacity` pairs of its run, the padded path's rule,
+    src/model/moe.py:225-283; counts still reports the routing decisions).
     Parameters are cast to x.dtype here (what autocast would do); gradients flow back through
     the cast. Per-expert biases b_in [E, 2H] / b_out [E, D] (either may be None) are applied in
     the GEMM epilogues and get gradients.
@@ -732,11 +766,12 @@ def fused_moe_forward(x, w_in, w_out, topk_w, topk_idx, b_in, b_out, activation,
         topk_idx = torch.cat([topk_idx, ids.expand(t, s_n)], dim=1)
         topk_w = torch.cat([topk_w, topk_w.new_ones((t, s_n))], dim=1)
         n_experts += s_n
-    sids, eids, offs, counts, npp, inv = moe_dispatch(topk_idx, n_experts)
+    sids, eids, offs, counts, npp, inv = moe_dispatch(topk_idx, n_experts, int(capacity),
+                                                      w_in.shape[0])
     cast = lambda t: None if t is None else t.to(x.dtype)
-    tensors = (x, w_in, w_out, topk_w, w_sh_in, w_sh_out, b_in, b_out)
+    tensors = (x, w_in, w_out, topk_w, w_sh_in, w_sh_out, b_in, b_out, b_sh_in, b_sh_out)
     save = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
     out, _, _ = moe_experts(x, cast(w_in), cast(w_out), topk_w, cast(w_sh_in), cast(w_sh_out), sids,
-                         eids, offs, counts, npp, inv, activation, save, cast(b_in), cast(b_out),
-                         _atomic(combine))
+                            eids, offs, counts, npp, inv, activation, save, cast(b_in), cast(b_out),
+                            _atomic(combine), cast(b_sh_in), cast(b_sh_out), capacity > 0)
     return out, counts[: w_in.shape[0]]

@@ -147,19 +147,25 @@ def dispatch(topk_idx: torch.Tensor, n_experts: int):
 
 
 # ---------------------------------------------------------------------------------- experts
-def shared_forward(x, w_sh_in, w_sh_out, act="silu"):
-    """Always-on experts, weight 1, summed (src/model/moe.py:310-329)."""
+def shared_forward(x, w_sh_in, w_sh_out, act="silu", b_sh_in=None, b_sh_out=None):
+    """Always-on experts, weight 1, summed, with their optional biases
+    (src/model/moe.py:310-329)."""
     fn = ACTS[act]
     total = None
     for s in range(w_sh_in.shape[0]):
-        gate, up = (x @ w_sh_in[s]).chunk(2, dim=-1)
+        h = x @ w_sh_in[s]
+        if b_sh_in is not None:
+            h = h + b_sh_in[s]
+        gate, up = h.chunk(2, dim=-1)
         y = (fn(gate) * up) @ w_sh_out[s]
+        if b_sh_out is not None:
+            y = y + b_sh_out[s]
         total = y if total is None else total + y
     return total
 
 
 def experts_forward(x, w_in, w_out, topk_w, topk_idx, act="silu", w_sh_in=None, w_sh_out=None,
-                    b_in=None, b_out=None):
+                    b_in=None, b_out=None, b_sh_in=None, b_sh_out=None):
     """Eager ragged dispatch (src/model/moe.py:377-418): gather per expert, two matmuls with the GLU
     between, scale by the router weight, index_add_ into the output, then the shared experts.
     Optional per-expert biases b_in [E, 2H] / b_out [E, D] as in src/model/moe.py:295-305 (added
@@ -185,8 +191,23 @@ def experts_forward(x, w_in, w_out, topk_w, topk_idx, act="silu", w_sh_in=None, 
             y = y + b_out[e]
         out = out.index_add(0, rows[e], y * ws[e][:, None])
     if w_sh_in is not None:
-        out = out + shared_forward(x, w_sh_in, w_sh_out, act)
+        out = out + shared_forward(x, w_sh_in, w_sh_out, act, b_sh_in, b_sh_out)
     return out
+
+
+def seeded_block_weights(seed, d_model, n_experts, d_hidden, n_shared, dtype=torch.bfloat16):
+    """Weights of a block drawn from one CPU generator in a fixed order (router W ~ N(0, 0.02),
+    expert weights ~ N(0, 1/sqrt(fan_in))), rounded once to dtype: what lets a golden file for
+    nanoSpeaker's real block shape (34 MB of weights) hold only the seed."""
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *shape: torch.randn(*shape, generator=g)
+    w = {"router_W": rn(d_model, n_experts) * 0.02,
+         "W_in": rn(n_experts, d_model, 2 * d_hidden) * d_model ** -0.5,
+         "W_out": rn(n_experts, d_hidden, d_model) * d_hidden ** -0.5}
+    if n_shared:
+        w["W_sh_in"] = rn(n_shared, d_model, 2 * d_hidden) * d_model ** -0.5
+        w["W_sh_out"] = rn(n_shared, d_hidden, d_model) * d_hidden ** -0.5
+    return {k: v.to(dtype) for k, v in w.items()}
 
 
 def dense_forward(x, w_in, w_out, topk_w, topk_idx, act="silu", w_sh_in=None, w_sh_out=None):

@@ -1,7 +1,7 @@
 """Generate the golden vectors in this directory by running the UNMODIFIED reference.
 
 Usage (needs a checkout of Osmansiddiquer/nanospeaker):
-    python tests/golden/make_golden.py /path/to/nanospeaker [--sublayer-only | --bias-only]
+    python tests/golden/make_golden.py /path/to/nanospeaker [--sublayer-only | --bias-only | --real-only]
 
 Each .npz holds the inputs and everything the reference's pure-PyTorch MoE path
 (MoEBlock(..., fused=False, kernel=False, capacity_factor=None) on CPU) computes from them:
@@ -44,6 +44,9 @@ def block_case(MoEBlock, name, *, d_model, n_experts, d_ff, top_k, n_shared, tok
         with torch.no_grad():
             m.b_in.copy_(torch.randn_like(m.b_in) * 0.5)
             m.b_out.copy_(torch.randn_like(m.b_out) * 0.5)
+            if n_shared:
+                m.b_sh_in.copy_(torch.randn_like(m.b_sh_in) * 0.5)
+                m.b_sh_out.copy_(torch.randn_like(m.b_sh_out) * 0.5)
     m = m.to(dtype)
     x = x.to(dtype).requires_grad_(train)
     m.train(train)
@@ -59,6 +62,9 @@ def block_case(MoEBlock, name, *, d_model, n_experts, d_ff, top_k, n_shared, tok
     if bias:
         put(s, "b_in", m.b_in)
         put(s, "b_out", m.b_out)
+        if n_shared:
+            put(s, "b_sh_in", m.b_sh_in)
+            put(s, "b_sh_out", m.b_sh_out)
     s["meta"] = np.array([d_model, n_experts, d_ff, top_k, n_shared, tokens, int(train),
                           int(normalize)], dtype=np.int64)
     s["activation"] = np.array(activation)
@@ -95,6 +101,9 @@ def block_case(MoEBlock, name, *, d_model, n_experts, d_ff, top_k, n_shared, tok
         if bias:
             put(s, "grad_b_in", m.b_in.grad)
             put(s, "grad_b_out", m.b_out.grad)
+            if n_shared:
+                put(s, "grad_b_sh_in", m.b_sh_in.grad)
+                put(s, "grad_b_sh_out", m.b_sh_out.grad)
     np.savez_compressed(os.path.join(HERE, name + ".npz"), **s)
     print(name, {k: v.shape for k, v in s.items() if hasattr(v, "shape") and v.ndim})
 
@@ -145,6 +154,62 @@ def sublayer_case(MoEBlock, RMSNorm, name, *, d_model, n_experts, d_ff, top_k, n
     print(name, tuple(out.shape))
 
 
+# every REAL_STRIDE-th element of the big weight gradients goes into the real-shape golden
+REAL_STRIDE = 61
+
+
+def real_shape_case(MoEBlock, name, *, tokens, seed):
+    """nanoSpeaker's own block shape (d_model 576, 76 routed + 2 shared experts, d_expert 128,
+    top-6), bf16, training mode: forward, balance loss and all gradients of
+    out^2.mean() + aux_loss. The 34 MB of weights are not stored: they come from
+    oracle.moe_oracle.seeded_block_weights(seed, ...), and the two big weight gradients are stored
+    as every REAL_STRIDE-th element plus per-expert norms. bf16-derived logits tie now and then,
+    and torch.topk's choice among equal logits is unspecified: the seed is one for which every
+    token's selected SET is the same under any tie rule (checked by tests/test_oracle.py), so the
+    output and the gradients do not depend on the rule."""
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from oracle.moe_oracle import seeded_block_weights
+    D, E, k, S, d_ff, H = 576, 76, 6, 2, 192, 128
+    w = seeded_block_weights(seed, D, E, H, S)
+    m = MoEBlock(D, E, d_ff=d_ff, top_k=k, n_shared=S, capacity_factor=None, fused=False,
+                 kernel=False).to(torch.bfloat16)
+    with torch.no_grad():
+        m.router.W.copy_(w["router_W"])
+        for key in ("W_in", "W_out", "W_sh_in", "W_sh_out"):
+            getattr(m, key).copy_(w[key])
+    x = torch.randn(tokens, D, generator=torch.Generator().manual_seed(seed + 1)).bfloat16()
+    x.requires_grad_(True)
+    m.train()
+    s = {}
+    put(s, "x", x)
+    s["meta"] = np.array([D, E, d_ff, k, S, tokens, seed, REAL_STRIDE], dtype=np.int64)
+    # exact (integer) fingerprint of the drawn weights: the sum of their bf16 bit patterns
+    s["weights_fingerprint"] = np.array(
+        [int(w[key].view(torch.int16).long().sum())
+         for key in ("router_W", "W_in", "W_out", "W_sh_in", "W_sh_out")], dtype=np.int64)
+    put(s, "logits", (x.detach() @ m.router.W.detach()).float())
+    topk_w, topk_idx, _ = m.router(x.detach())
+    _, order, _, counts = m._plan(topk_idx)
+    put(s, "topk_idx", topk_idx)
+    put(s, "topk_w", topk_w)
+    put(s, "plan_order", order)
+    put(s, "plan_counts", counts)
+    out = m(x)
+    put(s, "out", out)
+    put(s, "aux_loss", m.aux_loss.float())
+    (out.float().square().mean() + m.aux_loss).backward()
+    put(s, "grad_x", x.grad)
+    put(s, "grad_router_W", m.router.W.grad)
+    put(s, "grad_W_sh_in", m.W_sh_in.grad)
+    put(s, "grad_W_sh_out", m.W_sh_out.grad)
+    for key in ("W_in", "W_out"):
+        grad = getattr(m, key).grad
+        put(s, f"grad_{key}_strided", grad.reshape(-1)[::REAL_STRIDE])
+        put(s, f"grad_{key}_norms", grad.float().flatten(1).norm(dim=1))
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **s)
+    print(name, tuple(out.shape))
+
+
 def routing_case(MoEBlock, name, *, tokens, n_experts, top_k, seed, bf16_logits):
     """Routing only at nanoSpeaker's width: logits -> torch.topk -> stable-sort plan."""
     torch.manual_seed(seed)
@@ -169,6 +234,9 @@ def main():
     from src.model.moe import MoEBlock  # the reference, unmodified
     from src.model.ln import RMSNorm
 
+    if "--real-only" in sys.argv:
+        real_shape_case(MoEBlock, "block_real_shape_bf16_train", tokens=256, seed=27)
+        return
     sub = dict(d_model=64, n_experts=4, d_ff=192, top_k=2, n_shared=1, tokens=80)
     sublayer_case(MoEBlock, RMSNorm, "sublayer_fp32_train", dtype=torch.float32, seed=7, **sub)
     sublayer_case(MoEBlock, RMSNorm, "sublayer_bf16_train", dtype=torch.bfloat16, seed=8, **sub)
@@ -192,6 +260,7 @@ def main():
                  bf16_logits=False)
     routing_case(MoEBlock, "routing_e76_k6_bf16", tokens=512, n_experts=76, top_k=6, seed=6,
                  bf16_logits=True)
+    real_shape_case(MoEBlock, "block_real_shape_bf16_train", tokens=256, seed=27)
 
 
 if __name__ == "__main__":

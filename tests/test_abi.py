@@ -34,7 +34,7 @@ def test_header_and_binding_agree(lib):
 
 def test_abi_version_and_error_strings(lib):
     from nanospeaker_b200 import _lib
-    assert lib.moe_b200_abi_version() == 1
+    assert lib.moe_b200_abi_version() == 2
     assert _lib.error_string(0) == "ok"
     for code in range(-7, 0):
         assert _lib.error_string(code) not in ("ok", "unknown moe_b200 error code")
@@ -65,8 +65,17 @@ def test_arguments_are_validated_before_any_launch(lib):
     assert lib.moe_b200_router_topk(null, 4, 8, 9, 1, 0, null, null, null, null) == -1    # k > E
     assert lib.moe_b200_router_topk(null, 4, 8, 2, 1, 0, null, null, null, null) == -2    # NULL
     assert lib.moe_b200_router_topk(null, 0, 8, 2, 1, 0, null, null, null, null) == 0     # empty
-    assert lib.moe_b200_dispatch(null, 10, 8, null, null, null, null, null, null, null, 0, null,
+    assert lib.moe_b200_dispatch(null, 10, 8, null, null, null, null, null, null, null, 0, 0, 0, null,
                                  null) == -2
+    buf0 = ctypes.create_string_buffer(64)
+    q = ctypes.c_void_p(ctypes.addressof(buf0))
+    # every pointer the kernels would dereference is checked: topk_idx and inv_ids too
+    assert lib.moe_b200_dispatch(null, 10, 8, q, q, q, q, q, q, q, 1 << 20, 0, 0, q, null) == -2
+    assert lib.moe_b200_dispatch(q, 10, 8, q, q, q, q, q, null, q, 1 << 20, 0, 0, q, null) == -2
+    assert lib.moe_b200_dispatch(q, 10, 8, q, q, q, q, q, q, q, 1 << 20, -1, 0, q, null) == -1  # capacity < 0
+    assert lib.moe_b200_dispatch(q, 10, 8, q, q, q, q, q, q, q, 1 << 20, 4, 9, q, null) == -1   # n_capped > E
+    assert lib.moe_b200_dispatch_static(null, 10, 8, q, q, q, q, q, q, q, null) == -2
+    assert lib.moe_b200_dispatch_static(q, 10, 8, q, q, q, q, q, null, q, null) == -2
     assert lib.moe_b200_permute(null, 4, 100, 2, null, null, 128, null, null) == -1       # D % 8
     assert lib.moe_b200_permute(null, 4, 64, 2, null, null, 128, null, null) == -2
     assert lib.moe_b200_combine(null, null, 4, 2, 64, null, null, null, null) == -2

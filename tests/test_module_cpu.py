@@ -40,7 +40,10 @@ def test_matches_reference_golden_on_cpu():
     (out.float().square().mean() + m.aux_loss).backward()
     assert torch.equal(out, g["out"])
     assert torch.equal(m.expert_counts, g["plan_counts"])
-    assert torch.equal(x.grad, g["grad_x"]) and torch.equal(m.W_in.grad, g["grad_W_in"])
+    # (the gradient's k contributions per token are summed in this module's own order: equal to
+    # fp32 rounding, not bit for bit; the oracle is what is pinned bitwise)
+    assert rel_l2(x.grad, g["grad_x"]) < 1e-6 and rel_l2(m.W_in.grad, g["grad_W_in"]) < 1e-6
+    assert rel_l2(m.router.W.grad, g["grad_router_W"]) < 1e-5
     experts, order, token_idx, counts = m._plan(g["topk_idx"])
     assert torch.equal(order, g["plan_order"]) and torch.equal(token_idx, g["plan_token_idx"])
 

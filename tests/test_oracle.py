@@ -9,8 +9,8 @@ import torch
 from conftest import load_golden, rel_l2
 from oracle import moe_oracle as O
 
-# checkout of the reference project, where one exists (live cross-checks are skipped otherwise)
-REF = os.environ.get("NANOSPEAKER_REF") or os.path.join(os.sep, "root", "reference")
+# checkout of the reference project, where one is named (live cross-checks are skipped otherwise)
+REF = os.environ.get("NANOSPEAKER_REF", "")
 BLOCK_CASES = ["block_fp32_eval", "block_fp32_train", "block_bf16_train", "block_bf16_eval_gelu"]
 
 
@@ -195,11 +195,60 @@ def test_expert_biases_match_golden(case):
     routing: the reference's output, and through autograd its bias and weight gradients."""
     g = load_golden(case)
     leaf = lambda k: g[k].clone().requires_grad_(True)
-    p = {k: leaf(k) for k in ("x", "W_in", "W_out", "W_sh_in", "W_sh_out", "b_in", "b_out")}
+    names = ("x", "W_in", "W_out", "W_sh_in", "W_sh_out", "b_in", "b_out", "b_sh_in", "b_sh_out")
+    p = {k: leaf(k) for k in names}
+    assert float(g["b_sh_in"].abs().sum()) > 0 and float(g["b_sh_out"].abs().sum()) > 0
     out = O.experts_forward(p["x"], p["W_in"], p["W_out"], g["topk_w"], g["topk_idx"], "silu",
-                            p["W_sh_in"], p["W_sh_out"], p["b_in"], p["b_out"])
+                            p["W_sh_in"], p["W_sh_out"], p["b_in"], p["b_out"], p["b_sh_in"],
+                            p["b_sh_out"])
     fp32 = g["x"].dtype == torch.float32
     assert rel_l2(out, g["out"]) < (1e-6 if fp32 else 1e-2)
     out.float().square().mean().backward()       # the balance loss does not reach these gradients
-    for k in ("W_in", "W_out", "W_sh_in", "W_sh_out", "b_in", "b_out"):
+    for k in names[1:]:
         assert rel_l2(p[k].grad, g["grad_" + k]) < (1e-5 if fp32 else 2e-2), k
+
+
+def real_shape_oracle(g):
+    """The oracle block at nanoSpeaker's real shape with the weights the real-shape golden was
+    generated from (they are re-drawn from the stored seed; the fingerprint says whether this
+    torch build draws the same numbers)."""
+    D, E, d_ff, k, S, tokens, seed, stride = g["meta"].tolist()
+    w = O.seeded_block_weights(seed, D, E, 2 * d_ff // 3, S)
+    fp = torch.tensor([int(w[key].view(torch.int16).long().sum()) for key in
+                       ("router_W", "W_in", "W_out", "W_sh_in", "W_sh_out")], dtype=torch.int64)
+    if not torch.equal(fp, g["weights_fingerprint"]):
+        pytest.skip("this torch build draws other random numbers than the golden's generator")
+    o = O.OracleBlock(D, E, d_ff, k, S).to(torch.bfloat16)
+    with torch.no_grad():
+        o.router_W.copy_(w["router_W"])
+        for key in ("W_in", "W_out", "W_sh_in", "W_sh_out"):
+            getattr(o, key).copy_(w[key])
+    return o.train(), w, stride
+
+
+def test_oracle_matches_the_reference_at_nanospeakers_real_shape():
+    """d_model 576, 76 + 2 experts, top-6, bf16, training mode, 256 tokens: the reference's output,
+    balance loss and gradients (golden generated by the unmodified reference), bit for bit."""
+    g = load_golden("block_real_shape_bf16_train")
+    o, _, stride = real_shape_oracle(g)
+    x = g["x"].clone().requires_grad_(True)
+    logits, w, idx, probs = o.route(x)
+    assert torch.equal(logits.detach(), g["logits"]) and torch.equal(idx, g["topk_idx"])
+    assert torch.equal(w.detach(), g["topk_w"])
+    # every token's selected set is the same under the canonical tie rule: results cannot depend
+    # on how ties are broken
+    canon = O.canonical_topk(logits.detach(), o.top_k)
+    assert torch.equal(canon.sort(1).values, idx.sort(1).values)
+    out = o(x)
+    assert torch.equal(out.detach(), g["out"])
+    assert torch.equal(o.expert_counts, g["plan_counts"])
+    assert float(o.aux_loss) == float(g["aux_loss"])
+    (out.float().square().mean() + o.aux_loss).backward()
+    assert torch.equal(x.grad, g["grad_x"])
+    assert torch.equal(o.router_W.grad, g["grad_router_W"])
+    assert torch.equal(o.W_sh_in.grad, g["grad_W_sh_in"])
+    assert torch.equal(o.W_sh_out.grad, g["grad_W_sh_out"])
+    for key in ("W_in", "W_out"):
+        grad = getattr(o, key).grad
+        assert torch.equal(grad.reshape(-1)[::stride], g[f"grad_{key}_strided"]), key
+        assert torch.allclose(grad.float().flatten(1).norm(dim=1), g[f"grad_{key}_norms"])

@@ -58,8 +58,12 @@ def test_static_dispatch_matches_regular_dispatch_twice_in_a_row():
 def test_static_dispatch_rejects_sizes_beyond_its_scratch():
     from nanospeaker_b200 import _lib
     lib = _lib.load()
-    assert lib.moe_b200_dispatch_static_max_pairs(76) == (65536 // 76) * 4096
+    # the array holds 128 blocks x 256 experts, the most the dispatch ever uses, so the limit is
+    # the dispatch's own cap on the pair count
+    assert lib.moe_b200_dispatch_static_max_pairs(76) == 1 << 30
+    assert lib.moe_b200_dispatch_static_max_pairs(256) == 1 << 30
     assert lib.moe_b200_dispatch_static_max_pairs(0) == 0
+    assert lib.moe_b200_dispatch_scratch_bytes(1 << 30, 256) <= 128 * 1024
     too_many = lib.moe_b200_dispatch_static_max_pairs(256) + 1
     buf = torch.zeros(16, dtype=torch.int32, device="cuda")
     p = buf.data_ptr()
