@@ -51,6 +51,7 @@ METRIC = "MoE-block tokens/s (fwd+bwd)"
 # profiles/ncu_dW_in_dHidden_permute_T16384.md.
 NCU_TRAFFIC_BYTES = {"permute (routed rows; shared experts read x in place)": 82.0e6,
                      "wgrad_in (gemm + reduce)": 227.8e6, "dhidden+glu_bwd": 283.7e6}
+# (filled from the ncu summaries under profiles/; a kernel without a capture reports null)
 
 FLOP_PER_TOKEN_FWD_BWD = 10_879_488   # 3 * (routed up 1 769 472 + down 884 736 + shared 884 736 + router 87 552)
 
@@ -179,7 +180,10 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args.gpus, tokens),
+        "config": dict(workload_config(args.gpus, tokens),
+                       reference_scope="the CPU arm runs on rank 0's host cores only and its "
+                                       "tokens/s does not depend on n_gpus: at n_gpus > 1 the "
+                                       "ratio compares N GPUs with ONE host, not like for like"),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0,
@@ -269,6 +273,7 @@ def build_stages(m, x):
         hid0, a1 = K.up_gemm(xs[0], m.W_in, eids, npp, 0, 0, True, w_extra=m.W_sh_in)
         hid = copies(hid0)
         y = copies(K.down_gemm(hid[0], m.W_out, eids, npp, 0, sids, tw, M, w_extra=m.W_sh_out))
+        acc = [torch.zeros_like(x) for _ in range(3)]
         da1 = copies(K.dhidden_glu_bwd(xs[0], m.W_out, eids, npp, 0, sids, tw, M, a1, 0, True,
                                        w_extra=m.W_sh_out)[0])
         from nanospeaker_b200.moe_kernel import _router_ld
@@ -312,10 +317,18 @@ def build_stages(m, x):
             ("up_gemm+glu (gathered rows, inference)", TF, 2.0 * M * D * 2 * H, 0,
              lambda i: K.up_gemm(xr[i % 3], m.W_in, eids, npp, 0, 0, False, gather=gather,
                                  w_extra=m.W_sh_in)),
-            ("down_gemm+scale", TF, 2.0 * M * H * D, 1,
+            # the step's default: the down / dX GEMMs add their rows straight into the token-major
+            # result (bf16 atomics in L2); the accumulator is cleared by a fill first
+            ("down_gemm+scale+combine (atomic adds into out)", TF, 2.0 * M * H * D, 1,
+             lambda i: K.down_gemm_acc(hid[i % 3], m.W_out, eids, npp, 0, sids, tw, M, ka,
+                                       acc[i % 3], w_extra=m.W_sh_out)),
+            ("accumulator fill (out / dx zeroed before the atomic adds)", GE, T * D * 2, 2,
+             lambda i: acc[i % 3].zero_()),
+            # the store-then-reduce alternative (combine mode "store"): not part of the default step
+            ("down_gemm+scale (stores per-pair rows)", TF, 2.0 * M * H * D, 0,
              lambda i: K.down_gemm(hid[i % 3], m.W_out, eids, npp, 0, sids, tw, M,
                                    w_extra=m.W_sh_out)),
-            ("combine", GE, M * D * 2 + M * 4 + T * D * 2, 2,
+            ("combine (store mode)", GE, M * D * 2 + M * 4 + T * D * 2, 0,
              lambda i: K.combine(y[i % 3], inv, T, ka)),
             ("balance_loss", GE, E * 8, 1, lambda i: K.balance_loss(colsum, counts, E, T, 1e-2)),
             ("dhidden+glu_bwd", TF, 2.0 * M * D * H, 1,
@@ -325,7 +338,10 @@ def build_stages(m, x):
             ("dhidden+glu_bwd (gathered rows)", TF, 2.0 * M * D * H, 0,
              lambda i: K.dhidden_glu_bwd(xr[i % 3], m.W_out, eids, npp, 0, sids, tw, M, a1, 0,
                                          True, gather_top_k=ka, w_extra=m.W_sh_out)),
-            ("dx_gemm", TF, 2.0 * M * 2 * H * D, 1,
+            ("dx_gemm+combine (atomic adds into dx)", TF, 2.0 * M * 2 * H * D, 1,
+             lambda i: K.dx_gemm_acc(da1[i % 3], m.W_in, eids, npp, 0, sids, M, ka, acc[i % 3],
+                                     w_extra=m.W_sh_in)),
+            ("dx_gemm (stores per-pair rows)", TF, 2.0 * M * 2 * H * D, 0,
              lambda i: K.dx_gemm(da1[i % 3], m.W_in, eids, npp, 0, w_extra=m.W_sh_in)),
             ("wgrad_in (gemm + reduce)", TF, 2.0 * M * D * 2 * H, 1,
              lambda i: K.wgrad(xs[i % 3], da1[i % 3], offs, Ea, n_extra=S,
@@ -346,8 +362,9 @@ def build_stages(m, x):
                                           d_aux, counts, 1e-2, ld)),
             ("router wgrad x^T@dl (gemm + reduce)", TF, 2.0 * T * D * E, 1,
              lambda i: K.wgrad(xr[i % 3], dl[i % 3], None, 1)),
-            ("router dx dl@W^T", TF, 2.0 * T * D * E, 1,
-             lambda i: K.dx_gemm(dl[i % 3], wp, None, None, 1)),
+            ("router dx dl@W^T (atomic adds into dx)", TF, 2.0 * T * D * E, 1,
+             lambda i: K.dx_gemm_acc(dl[i % 3].unsqueeze(0), wp, None, None, 1, None, 0, 1,
+                                     acc[i % 3])),
         ]
     return stages
 
@@ -363,9 +380,12 @@ def gemm_stage_bytes(T, ld):
         "router GEMM": T * D * 2 + D * ld * 2 + T * ld * 2,
         "up_gemm+glu (+a1 saved)": M * D * 2 + w_in + M * 3 * H * 2,
         "up_gemm+glu (gathered rows, inference)": T * D * 2 + w_in + M * H * 2,
-        "down_gemm+scale": M * H * 2 + w_out + M * D * 2,
+        "down_gemm+scale (stores": M * H * 2 + w_out + M * D * 2,
+        # atomic variants: no per-pair rows; the token-major result is read and written once in HBM
+        "down_gemm+scale+combine": M * H * 2 + w_out + 2 * T * D * 2,
+        "dx_gemm+combine": M * 2 * H * 2 + w_in + 2 * T * D * 2,
         "dhidden+glu_bwd": M * D * 2 + M * 2 * H * 2 + w_out + M * 3 * H * 2 + M * 2,
-        "dx_gemm": M * 2 * H * 2 + w_in + M * D * 2,
+        "dx_gemm (stores": M * 2 * H * 2 + w_in + M * D * 2,
         "wgrad_in (gemm + reduce)": M * D * 2 + M * 2 * H * 2 + w_in,
         "wgrad_out (gemm + reduce)": M * H * 2 + M * D * 2 + w_out,
     }
@@ -635,23 +655,20 @@ def run_ours(args):
                                 "achieved": top["achieved"], "peak": top["peak"],
                                 "unit": top["unit"], "frac": top["frac"],
                                 "traffic": NCU_TRAFFIC_BYTES.get(top["kernel"]),
-                                "peak_source": pk["source"] + " (burst: kernel timed alone)"}
+                                "peak_source": pk["source"] + " (burst: kernel timed alone)",
+                                "algorithmic_work": "flop (or bytes) per token of the stage x "
+                                                    f"{TOKENS} tokens, pad rows and recompute not counted"}
             if "hbm_frac" in top:
-                # A GEMM stage: report the roof that binds it. Its flop per compulsory HBM byte
-                # against the ridge of the measured peaks decides; every GEMM of this block is
-                # below the ridge (~250 flop/B), so the byte floor binds and the tensor figures
-                # ride along.
+                # A GEMM stage is reported against the tensor roof. Next to it, as extra keys, the
+                # stage's time against the HBM bytes THIS DESIGN moves for it (operands read once,
+                # outputs written once, materialised intermediates included): that byte count is
+                # the design's, not algorithmic work.
                 work_flop = top["achieved"] * 1e12 * top["us"] * 1e-6
-                ridge = pk["bf16_tflops"] * 1e12 / (pk["hbm_gbs"] * 1e9)
-                line["roofline"].update({"tensor_tflops": top["achieved"],
-                                         "tensor_frac": top["frac"],
-                                         "flop_per_hbm_byte": round(work_flop / top["hbm_bytes"], 1),
-                                         "ridge_flop_per_byte": round(ridge, 1)})
-                if work_flop / top["hbm_bytes"] < ridge:
-                    line["roofline"].update({"bound": "hbm", "achieved": top["hbm_gbs"],
-                                             "peak": pk["hbm_gbs"], "unit": "GB/s",
-                                             "frac": top["hbm_frac"],
-                                             "algorithmic_bytes": top["hbm_bytes"]})
+                line["roofline"].update({
+                    "design_hbm_bytes": top["hbm_bytes"], "design_hbm_gbs": top["hbm_gbs"],
+                    "design_hbm_frac": top["hbm_frac"],
+                    "flop_per_design_hbm_byte": round(work_flop / top["hbm_bytes"], 1),
+                    "ridge_flop_per_byte": round(pk["bf16_tflops"] * 1e12 / (pk["hbm_gbs"] * 1e9), 1)})
             line["stages"] = stages
     if world > 1:
         dist.barrier()
@@ -794,12 +811,18 @@ def run_ep_workload(args):
             "cuda_graph": use_graph, "phases": phases}), flush=True)
     dist.barrier()
     torch.cuda.synchronize()
+    # Captured graphs that contain collectives keep references into the communicator: tearing the
+    # process group down while they are alive did not return. Drop the graphs (and the exchange
+    # buffers they point into) first, then tear down.
+    run = None
     if use_graph:
-        # Graphs that captured collectives are still alive: tearing the process group down under
-        # them did not return (both ranks sat in destroy_process_group until the launcher's
-        # timeout). The results are out and every rank has passed the barrier: leave directly.
-        sys.stdout.flush()
-        os._exit(0)
+        graphs.clear()
+    if push:
+        del grp
+    import gc
+    gc.collect()
+    torch.cuda.synchronize()
+    dist.barrier()
     dist.destroy_process_group()
 
 

@@ -8,7 +8,6 @@
 
 #include <cuda_runtime.h>
 
-#include <cstdlib>
 #include <utility>
 
 namespace moe {
@@ -28,14 +27,17 @@ static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 blo
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  // MOE_B200_NO_PDL=1 in the environment launches every kernel fully serialised (a debugging aid:
-  // the kernels' pdl_wait() is then a no-op)
-  static const bool no_pdl = std::getenv("MOE_B200_NO_PDL") != nullptr;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = no_pdl ? 0 : 1;
+  // A debug build (-DMOE_B200_DEBUG_NO_PDL) launches every kernel fully serialised; the kernels'
+  // pdl_wait() is then a no-op.
+#ifdef MOE_B200_DEBUG_NO_PDL
+  cfg.numAttrs = 0;
+#else
+  cfg.numAttrs = 1;
+#endif
   return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
 }
 

@@ -14,8 +14,6 @@ stays in a 1-element device tensor that the kernels read.
 """
 from typing import List, Optional, Tuple
 
-import os
-
 import torch
 
 from . import kernels as K
@@ -447,6 +445,8 @@ _T6 = Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor
 
 
 _SIDE_STREAMS = {}
+# Debugging aid, off in normal use: True keeps every launch of the backward on the caller's stream.
+_DEBUG_ONE_STREAM = False
 
 
 def _side_streams(device: torch.device):
@@ -600,7 +600,7 @@ def moe_block_bwd(
     # tail of one persistent GEMM (SMs that ran out of tiles) is filled by the next one's CTAs.
     main = torch.cuda.current_stream(x.device)
     side_out, side_router = _side_streams(x.device)
-    if os.environ.get("MOE_B200_ONE_STREAM"):      # debugging aid: everything on the caller's stream
+    if _DEBUG_ONE_STREAM:
         side_out = side_router = main
     side_out.wait_stream(main)
     side_router.wait_stream(main)

@@ -65,6 +65,43 @@ def test_loopback_ranks_match_the_single_gpu_block(world, tokens):
     kernels.check_status("cuda")
 
 
+def _report_and_leave(q, rank, text):
+    """A failed rank hands its error to the parent and leaves at once, without tearing the process
+    group down: its peer may be inside a collective that this rank will never join, and the hard
+    exit is what lets that collective end with an error instead of waiting."""
+    import os
+    q.put((rank, text))
+    q.close()
+    q.join_thread()
+    os._exit(1)
+
+
+def _collect(procs, q, world):
+    """Results of all ranks, or an assertion; whatever happens, no worker is left behind holding a
+    GPU (a rank stuck in a collective is terminated, then killed)."""
+    import queue
+    got = {}
+    try:
+        for _ in range(world):
+            try:
+                item = q.get(timeout=300)
+            except queue.Empty:
+                raise AssertionError("a rank did not report within 300 s")
+            assert len(item) == 5, item
+            got[item[0]] = item[1:]
+        for p in procs:
+            p.join(timeout=60)
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=10)
+    return got
+
+
 def _nccl_worker(rank, world, port, tokens, q):
     try:
         import os
@@ -72,8 +109,10 @@ def _nccl_worker(rank, world, port, tokens, q):
         from nanospeaker_b200 import expert_parallel as EP
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
         torch.cuda.set_device(rank)
+        import datetime
         dist.init_process_group("nccl", rank=rank, world_size=world,
-                                device_id=torch.device("cuda", rank))
+                                device_id=torch.device("cuda", rank),
+                                timeout=datetime.timedelta(seconds=120))
         m = _block(seed=5)
         E = m.router.n_experts
         g = torch.Generator().manual_seed(11)
@@ -93,7 +132,7 @@ def _nccl_worker(rank, world, port, tokens, q):
         dist.barrier()
         dist.destroy_process_group()
     except Exception as exc:  # surface the failure instead of hanging the parent
-        q.put((rank, repr(exc)))
+        _report_and_leave(q, rank, repr(exc))
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
@@ -110,13 +149,7 @@ def test_two_gpus_over_nccl_match_the_single_gpu_block():
     procs = [ctx.Process(target=_nccl_worker, args=(r, world, port, tokens, q)) for r in range(world)]
     for p in procs:
         p.start()
-    got = {}
-    for _ in range(world):
-        item = q.get(timeout=300)
-        assert len(item) == 5, item
-        got[item[0]] = item[1:]
-    for p in procs:
-        p.join(timeout=60)
+    got = _collect(procs, q, world)
     m = _block(seed=5)
     g = torch.Generator().manual_seed(11)
     x_all = torch.randn(world * tokens, 576, generator=g).bfloat16()
@@ -186,7 +219,9 @@ def _push_worker(rank, world, port, tokens, q):
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
         torch.cuda.set_device(rank)
         dev = torch.device("cuda", rank)
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                                timeout=datetime.timedelta(seconds=120))
         m = _block(seed=5)
         E = m.router.n_experts
         g = torch.Generator().manual_seed(11)
@@ -214,7 +249,7 @@ def _push_worker(rank, world, port, tokens, q):
         dist.destroy_process_group()
     except Exception as exc:  # surface the failure instead of hanging the parent
         import traceback
-        q.put((rank, repr(exc) + traceback.format_exc()))
+        _report_and_leave(q, rank, repr(exc) + traceback.format_exc())
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
@@ -233,13 +268,7 @@ def test_two_gpus_over_peer_memory_match_the_single_gpu_block():
     procs = [ctx.Process(target=_push_worker, args=(r, world, port, tokens, q)) for r in range(world)]
     for p in procs:
         p.start()
-    got = {}
-    for _ in range(world):
-        item = q.get(timeout=300)
-        assert len(item) == 5, item
-        got[item[0]] = item[1:]
-    for p in procs:
-        p.join(timeout=60)
+    got = _collect(procs, q, world)
     m = _block(seed=5)
     g = torch.Generator().manual_seed(11)
     x_all = torch.randn(world * tokens, 576, generator=g).bfloat16()
