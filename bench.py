@@ -340,7 +340,7 @@ def build_stages(m, x):
                                          True, gather_top_k=ka, w_extra=m.W_sh_out)),
             ("dx_gemm+combine (atomic adds into dx)", TF, 2.0 * M * 2 * H * D, 1,
              lambda i: K.dx_gemm_acc(da1[i % 3], m.W_in, eids, npp, 0, sids, M, ka, acc[i % 3],
-                                     w_extra=m.W_sh_in)),
+                                     w_extra=m.W_sh_in, pad_offsets=offs)),
             ("dx_gemm (stores per-pair rows)", TF, 2.0 * M * 2 * H * D, 0,
              lambda i: K.dx_gemm(da1[i % 3], m.W_in, eids, npp, 0, w_extra=m.W_sh_in)),
             ("wgrad_in (gemm + reduce)", TF, 2.0 * M * D * 2 * H, 1,

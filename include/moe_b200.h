@@ -326,13 +326,16 @@ int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void
 /* The dX GEMM fused with the combine: row `row` of da1 @ w_in[e]^T is added to row
  * sorted_ids[row] / top_k of acc [n_tokens, d_model] (bf16, filled by the caller), as
  * moe_b200_down_gemm_acc does for the forward. Replaces the dX use of _gemm2_kernel together with
- * the _reduce_kernel pass behind it (src/model/moe_kernel.py:696-710). */
+ * the _reduce_kernel pass behind it (src/model/moe_kernel.py:696-710). pad_offsets (may be NULL;
+ * routed schedule): the dispatch's run starts [n_groups + n_extra + 1]; with them the kernel runs
+ * on CTA pairs that share each weight tile (half the weight traffic per SM), without them on
+ * single CTAs. */
 int moe_b200_dx_gemm_acc(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,
                          int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_model,
                          const int32_t* expert_ids, const int32_t* n_post_pad,
                          int32_t n_fixed_groups, const int32_t* sorted_ids, int64_t n_pairs,
-                         int32_t top_k, void* acc, int64_t n_tokens, int32_t* status,
-                         void* stream);
+                         int32_t top_k, void* acc, int64_t n_tokens, const int32_t* pad_offsets,
+                         int32_t* status, void* stream);
 
 /* Bytes of fp32 scratch moe_b200_wgrad needs for its partial tiles (contents arbitrary).
  * routed != 0: the pad_offsets schedule over `rows` = l_cap rows. ks_rows as for moe_b200_wgrad. */

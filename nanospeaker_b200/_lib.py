@@ -76,7 +76,7 @@ SIGNATURES = {
     "moe_b200_dx_gemm_acc": (
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,
-         _c_i64, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp]),
+         _c_i64, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp]),
     "moe_b200_dhidden_glu_bwd": (
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,

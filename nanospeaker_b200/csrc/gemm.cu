@@ -13,6 +13,13 @@
 
 #include "../../include/moe_b200.h"
 
+#ifndef MOE_PAIR_UP_STAGES
+#define MOE_PAIR_UP_STAGES 6
+#endif
+#ifndef MOE_PAIR_DX_STAGES
+#define MOE_PAIR_DX_STAGES 4
+#endif
+
 namespace moe {
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -128,6 +135,49 @@ static int launch_rows(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
                                      size_t(smem), st, tmA, tmA2 ? *tmA2 : tmA, tmB, tmB2, tmOut,
                                      args);
   return err == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+// CTA-pair launch (rows_gemm2_kernel): as many clusters of two as can be resident at once (a
+// 148-SM part need not fit 74 of them: SMs pair up inside their processing cluster), fewer when
+// the unit list is shorter.
+template <int BN, int STAGES, bool B_MN, int EPI>
+static int launch_rows2(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUtensorMap& tmB,
+                        const CUtensorMap& tmB2, const CUtensorMap& tmOut, const RowsArgs& args,
+                        int64_t max_units, cudaStream_t st) {
+  auto kern = rows_gemm2_kernel<BN, STAGES, B_MN, EPI>;
+  constexpr int smem = Rows2Smem<BN, STAGES, EPI>::DYNAMIC;
+  static_assert(smem <= 232448, "shared memory of a row GEMM exceeds the 227 KB per-CTA limit");
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  static int max_clusters = 0;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (attr_err != cudaSuccess) return;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(sm_count() / 2 * 2));
+    cfg.blockDim = dim3(rows_threads(EPI, false));
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    attr_err = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
+  });
+  if (attr_err != cudaSuccess || max_clusters < 1) return MOE_B200_ERR_CUDA;
+  int64_t clusters = std::min<int64_t>(max_clusters, sm_count() / 2);
+  if (max_units < clusters) clusters = max_units;
+  const cudaError_t err = launch_pdl_pairs(kern, dim3(unsigned(2 * clusters)),
+                                           dim3(rows_threads(EPI, false)), size_t(smem), st, tmA,
+                                           tmA2, tmB, tmB2, tmOut, args);
+  return err == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+// Upper bound on the pair units of a routed launch: every run may end in a half-empty pair.
+static int64_t max_pair_units(int64_t rows, int n_groups_total, int n_chunks) {
+  return ((rows / BM + n_groups_total + 1) / 2) * n_chunks;
 }
 
 template <int BN, int STAGES, int GATHER>
@@ -273,6 +323,22 @@ int moe_b200_up_gemm(const void* a, int64_t rows, int32_t d_model, const void* w
   if (rc2 != MOE_B200_OK) return rc2;
   if (gather_top_k > 0)
     return launch_rows<256, 4, true, EPI_GLU, true>(tmA, tmB, tmB2, tmB, g, tiles, st);
+#ifndef MOE_NO_PAIR_UP
+  // Routed schedule with the run table at hand: CTA pairs, each CTA loading half of the expert's
+  // weight tile (the 4-D weight maps then bring 2 of the 4 64-column boxes per copy).
+  if (n_fixed_groups == 0 && pad_offsets != nullptr && fused) {
+    int32_t f2 = 0;
+    CUtensorMap hB, hB2;
+    if (!map_weight_mnmajor(&hB, w_in, n_groups, d_model, 2 * d_hidden, 2, &f2)) return MOE_B200_ERR_TMA;
+    hB2 = hB;
+    if (n_extra > 0 && !map_weight_mnmajor(&hB2, w_extra, n_extra, d_model, 2 * d_hidden, 2, &f2))
+      return MOE_B200_ERR_TMA;
+    g.a2_offsets = pad_offsets;
+    g.n_groups_total = n_groups + n_extra;
+    return launch_rows2<256, MOE_PAIR_UP_STAGES, true, EPI_GLU>(
+        tmA, tmA2, hB, hB2, hB, g, max_pair_units(rows, n_groups + n_extra, 1), st);
+  }
+#endif
   return launch_rows<256, 4, true, EPI_GLU>(tmA, tmB, tmB2, tmB, g, tiles, st, &tmA2);
 }
 
@@ -486,8 +552,8 @@ int moe_b200_dx_gemm_acc(const void* da1, int64_t rows, int32_t d_hidden, const 
                          int32_t n_groups, const void* w_extra, int32_t n_extra, int32_t d_model,
                          const int32_t* expert_ids, const int32_t* n_post_pad,
                          int32_t n_fixed_groups, const int32_t* sorted_ids, int64_t n_pairs,
-                         int32_t top_k, void* acc, int64_t n_tokens, int32_t* status,
-                         void* stream) {
+                         int32_t top_k, void* acc, int64_t n_tokens, const int32_t* pad_offsets,
+                         int32_t* status, void* stream) {
   CHECK_SCHED();
   if (d_hidden % 4 != 0 || d_hidden < 32 || d_model % 32 != 0) return MOE_B200_ERR_UNSUPPORTED;
   if (!da1 || !w_in) return MOE_B200_ERR_NULL;
@@ -514,6 +580,22 @@ int moe_b200_dx_gemm_acc(const void* da1, int64_t rows, int32_t d_hidden, const 
   g.out = static_cast<__nv_bfloat16*>(acc);
   g.ld_out = d_model;
   g.n_groups_b1 = n_extra > 0 ? n_groups : INT32_MAX;
+#ifndef MOE_NO_PAIR_DX
+  // Routed schedule with the run table at hand: CTA pairs, each CTA loading 96 of the 192 weight
+  // rows of the tile.
+  if (n_fixed_groups == 0 && pad_offsets != nullptr) {
+    CUtensorMap hB, hB2;
+    if (!map_weight_kmajor(&hB, w_in, n_groups, d_model, 2 * d_hidden, 96)) return MOE_B200_ERR_TMA;
+    hB2 = hB;
+    if (n_extra > 0 && !map_weight_kmajor(&hB2, w_extra, n_extra, d_model, 2 * d_hidden, 96))
+      return MOE_B200_ERR_TMA;
+    g.a2_offsets = pad_offsets;
+    g.n_groups_total = n_groups + n_extra;
+    return launch_rows2<192, MOE_PAIR_DX_STAGES, false, EPI_RAW_RED>(
+        tmA, tmA, hB, hB2, hB, g, max_pair_units(rows, n_groups + n_extra, g.n_chunks),
+        static_cast<cudaStream_t>(stream));
+  }
+#endif
   return launch_rows<192, MOE_RED_DX_STAGES, false, EPI_RAW_RED, false, MOE_RED_DX_BUFS>(
       tmA, tmB, tmB2, tmB, g, max_tiles(rows, g.n_chunks, n_fixed_groups),
       static_cast<cudaStream_t>(stream));

@@ -58,6 +58,7 @@ struct RowsArgs {
   int32_t num_k;               // K / 64 (rounded up; the tail reads as zeros)
   int32_t n_dim;               // valid accumulator columns over all N chunks
   int32_t n_chunks;            // ceil(n_dim / BN)
+  int32_t n_groups_total;      // CTA-pair kernels: number of runs in a2_offsets (both weight stacks)
   int32_t n_groups_b1;         // groups [0, n_groups_b1) read the first B stack, the rest the second
   int32_t a2_first_group;      // routed schedule: groups from here on read their A rows from the
                                // token-major second A map (row = slot - a2_offsets[group]);
@@ -217,4 +218,5 @@ __device__ __forceinline__ void issue_stage_mmas(uint32_t sA, uint32_t sB, uint3
 }  // namespace moe
 
 #include "gemm_rows.cuh"
+#include "gemm_rows2.cuh"
 #include "gemm_wgrad.cuh"

@@ -41,4 +41,29 @@ static inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 blo
   return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
 }
 
+// The same launch for kernels that run as clusters of two CTAs (grid.x a multiple of 2).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl_pairs(void (*kern)(KArgs...), dim3 grid, dim3 block,
+                                           size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+#ifdef MOE_B200_DEBUG_NO_PDL
+  cfg.numAttrs = 1;
+#else
+  cfg.numAttrs = 2;
+#endif
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
 }  // namespace moe

@@ -301,7 +301,7 @@ def copy_cols(src: torch.Tensor, dst_ld: int) -> torch.Tensor:
 
 
 def up_gemm(a, w_in, expert_ids, n_post_pad, n_fixed: int, act: int, want_raw: bool,
-            gather=None, w_extra=None, token_rows=None, bias=None):
+            gather=None, w_extra=None, token_rows=None, bias=None, pad_offsets=None):
     """a x w_in [G, D, 2H] -> (act(g)*u [rows, H], raw [g|u] [rows, 2H] | None).
     a is slot-ordered [rows, D]; or, with gather=(sorted_ids, top_k), the token-major x [T, D] whose
     rows the kernel gathers itself (rows = len(sorted_ids)). n_fixed = S > 0 applies weight
@@ -309,9 +309,11 @@ def up_gemm(a, w_in, expert_ids, n_post_pad, n_fixed: int, act: int, want_raw: b
     weight stack for expert ids >= G (the shared experts on the routed schedule).
     token_rows=(x, pad_offsets): the experts of the second stack read their rows from the token-major
     x [T, D] (row = slot - start of the expert's run) instead of from a, whose rows in those runs
-    need not have been written."""
+    need not have been written.
+    pad_offsets (the dispatch's run starts; implied by token_rows): lets the routed schedule run on
+    CTA pairs that share each weight tile."""
     _need_cuda(a, w_in)
-    tok, offs = token_rows if token_rows is not None else (None, None)
+    tok, offs = token_rows if token_rows is not None else (None, pad_offsets)
     d = a.shape[1]
     xp, xn = _extra(w_extra)
     sids, top_k = gather if gather is not None else (None, 0)
@@ -368,9 +370,10 @@ def down_gemm_acc(hid, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, 
 
 
 def dx_gemm_acc(da1, w_in, expert_ids, n_post_pad, n_fixed: int, sorted_ids, n_pairs: int,
-                top_k: int, acc: torch.Tensor, w_extra=None) -> torch.Tensor:
+                top_k: int, acc: torch.Tensor, w_extra=None, pad_offsets=None) -> torch.Tensor:
     """The dX GEMM fused with the combine: row `row` of da1 x w_in[e]^T is added to row
-    sorted_ids[row] // top_k of acc [T, D] (fixed schedule: row r of every group to row r)."""
+    sorted_ids[row] // top_k of acc [T, D] (fixed schedule: row r of every group to row r).
+    pad_offsets (the dispatch's run starts): lets the routed schedule run on CTA pairs."""
     _need_cuda(da1, w_in, acc)
     rows, h2 = da1.shape[-2:]
     g, d, _ = w_in.shape
@@ -379,7 +382,8 @@ def dx_gemm_acc(da1, w_in, expert_ids, n_post_pad, n_fixed: int, sorted_ids, n_p
     _lib.check(_lib.load().moe_b200_dx_gemm_acc(
         da1.data_ptr(), rows, h2 // 2, w_in.data_ptr(), g, xp, xn, d, _lib.ptr(expert_ids),
         _lib.ptr(n_post_pad), n_fixed, _lib.ptr(sorted_ids), n_pairs, top_k, acc.data_ptr(),
-        acc.shape[0], status_word(da1.device).data_ptr(), _stream(da1)), "moe_b200_dx_gemm_acc")
+        acc.shape[0], _lib.ptr(pad_offsets), status_word(da1.device).data_ptr(), _stream(da1)),
+        "moe_b200_dx_gemm_acc")
     _count(1 if rows else 0)
     return acc
 

@@ -237,7 +237,7 @@ def moe_experts(
         live, tok = _routed_rows(x, w_in, w_sh_in, pad_offsets, n_post_pad)
         xs = K.permute(x, topk, sorted_ids, live)
         hid, a1 = K.up_gemm(xs, w_in, expert_ids, n_post_pad, 0, act, True, w_extra=w_sh_in,
-                            token_rows=tok, bias=b_in)
+                            token_rows=tok, bias=b_in, pad_offsets=pad_offsets)
     else:
         xs, a1 = x.new_empty(0), x.new_empty(0)
         hid, _ = K.up_gemm(x, w_in, expert_ids, n_post_pad, 0, act, False,
@@ -343,7 +343,8 @@ def moe_experts_bwd(
                                        a1, act, True, w_extra=w_sh_out, token_rows=tok,
                                        dtw_out=dtw_buf)
     if atomic_combine:
-        K.dx_gemm_acc(da1, w_in, expert_ids, n_post_pad, 0, sorted_ids, m, topk, dx, w_extra=w_sh_in)
+        K.dx_gemm_acc(da1, w_in, expert_ids, n_post_pad, 0, sorted_ids, m, topk, dx,
+                      w_extra=w_sh_in, pad_offsets=pad_offsets)
     else:
         ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
         dx = K.combine(ydx, inv_ids, n, topk)
@@ -517,7 +518,8 @@ def moe_block(
     if save_for_backward:
         live, tok = _routed_rows(x, w_in, w_sh_in, offs, npp)
         xs = K.permute(x, ks, sids, live)
-        hid, a1 = K.up_gemm(xs, w_in, eids, npp, 0, act, True, w_extra=w_sh_in, token_rows=tok)
+        hid, a1 = K.up_gemm(xs, w_in, eids, npp, 0, act, True, w_extra=w_sh_in, token_rows=tok,
+                            pad_offsets=offs)
     else:
         xs, a1 = x.new_empty(0), x.new_empty(0)
         hid, _ = K.up_gemm(x, w_in, eids, npp, 0, act, False, gather=(sids, ks), w_extra=w_sh_in)
@@ -607,7 +609,8 @@ def moe_block_bwd(
     g_in = K.wgrad(xs, da1, pad_offsets, e_n + s_n, n_extra=s_n,
                    token_rows=("a", x) if s_n else None)
     if atomic_combine:
-        K.dx_gemm_acc(da1, w_in, expert_ids, n_post_pad, 0, sorted_ids, m, ks, dx, w_extra=w_sh_in)
+        K.dx_gemm_acc(da1, w_in, expert_ids, n_post_pad, 0, sorted_ids, m, ks, dx,
+                      w_extra=w_sh_in, pad_offsets=pad_offsets)
     else:
         ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
     with torch.cuda.stream(side_out):

@@ -102,7 +102,7 @@ def test_arguments_are_validated_before_any_launch(lib):
     assert dacc(128, 1, null, 1, p, 100) == -1   # fixed schedule: more rows than tokens
     assert dacc(100, 0, p, 2, p) == -1           # routed rows must be a multiple of 128
     xacc = lambda sid, topk, acc: lib.moe_b200_dx_gemm_acc(
-        p, 128, 128, p, 4, null, 0, 64, p, p, 0, sid, 8, topk, acc, 4, p, null)
+        p, 128, 128, p, 4, null, 0, 64, p, p, 0, sid, 8, topk, acc, 4, null, p, null)
     assert xacc(p, 2, null) == -2
     assert xacc(null, 2, p) == -2
     assert xacc(p, 0, p) == -1
