@@ -199,7 +199,9 @@ def workload_config(n_gpus, tokens_per_gpu=TOKENS):
                     "d_model 576, 76 routed + 2 shared SwiGLU experts, d_expert 128, top-6",
         "tokens_per_gpu": tokens_per_gpu, "global_tokens": tokens_per_gpu * n_gpus,
         "skew": f"{SKEW_NAME}: per-expert logit bias N(0,{BIAS_STD}), seed 1",
-        "parallelism": f"token-sharded replicas x{n_gpus}, no data-path collective",
+        "parallelism": f"token-sharded replicas x{n_gpus}: no collective on the data path" +
+                       ("; the weight gradients are all-reduced over the ranks every step (NCCL), "
+                        "inside the timed region" if n_gpus > 1 else ""),
         "l2": f"{N_INPUT_SETS} input/dOut sets cycled (302 MB) and ~1 GB of intermediates per "
               "step, both beyond the 126 MB L2; no explicit flush",
     }
@@ -479,7 +481,7 @@ def run_ours(args):
         x = dev_x[i % N_INPUT_SETS].detach().requires_grad_(True)
         out = m(x)
         torch.autograd.backward([out, m.aux_loss], [dev_dout[i % N_INPUT_SETS], one])
-        if args.grad_allreduce and world > 1:
+        if world > 1 and not args.no_grad_allreduce:
             from nanospeaker_b200.parallel import all_reduce_gradients
             all_reduce_gradients(params)
 
@@ -521,7 +523,9 @@ def run_ours(args):
             else:
                 loss = None
                 torch.autograd.backward([out, m.aux_loss], [static_dout, one])
-        return graph, loss, K.LAUNCHES - l0
+        # the gradients this graph writes (its own static tensors, rewritten by every replay)
+        grads = [p.grad for p in params if p.grad is not None]
+        return graph, loss, K.LAUNCHES - l0, grads
 
     def barrier():
         if world > 1:
@@ -548,7 +552,13 @@ def run_ours(args):
 
     torch.autograd.graph.set_warn_on_accumulate_grad_stream_mismatch(False)
     warmup = max(args.warmup, 3)
-    use_graph = not args.no_graph and not (args.grad_allreduce and world > 1)
+    use_graph = not args.no_graph
+    # N > 1: the data-parallel training step. Every rank's weight gradients (34.6 MB in bf16) are
+    # summed over the ranks inside the timed region: the step's graph is replayed, then one flattened
+    # NCCL all-reduce runs on a communication stream under the NEXT step's compute (what a trainer
+    # does between two micro-steps); the barrier that ends the timed region waits for the last one.
+    # --no-grad-allreduce times the bare replicas instead.
+    with_comm = world > 1 and not args.no_grad_allreduce
     eager_ms, _, _ = timed(step, args.steps, warmup)
     if use_graph:
         # value: one graph per resident input set (the sets are cycled so that no step finds its
@@ -558,8 +568,30 @@ def run_ours(args):
         graph_sets = [capture(False, value_x[i], dev_dout[i]) for i in range(N_INPUT_SETS)]
         per_step_launches = graph_sets[0][2]
 
+        comm_stream = torch.cuda.Stream()
+        computed, flattened = torch.cuda.Event(), torch.cuda.Event()
+        n_grad = sum(g.numel() for g in graph_sets[0][3])
+        bucket = torch.empty(n_grad, dtype=torch.bfloat16, device=dev)
+
+        def reduce_grads(grads):
+            """Flatten this step's gradients into the bucket and all-reduce it, on the
+            communication stream; the compute stream only waits for the flatten copy before the
+            next replay overwrites the gradients."""
+            computed.record()
+            with torch.cuda.stream(comm_stream):
+                comm_stream.wait_event(computed)
+                torch.cat([g.reshape(-1) for g in grads], out=bucket)
+                flattened.record(comm_stream)
+                dist.all_reduce(bucket)
+            torch.cuda.current_stream().wait_event(flattened)
+
+        def replica_step(i):
+            graph_sets[i % N_INPUT_SETS][0].replay()
+
         def value_step(i):
             graph_sets[i % N_INPUT_SETS][0].replay()
+            if with_comm:
+                reduce_grads(graph_sets[i % N_INPUT_SETS][3])
 
         # e2e: two input buffers / graphs in ping-pong. The pinned-host -> device copy of step i+1
         # runs on a copy stream while step i computes (what an input pipeline does), and the loss
@@ -590,6 +622,8 @@ def run_ours(args):
             torch.cuda.current_stream().wait_event(copied[b])
             e2e_graphs[b][0].replay()
             consumed[b].record()
+            if with_comm:
+                reduce_grads(e2e_graphs[b][3])
             prefetch(i + 1)                               # H2D of the next step's input
             with torch.cuda.stream(d2h_stream):           # D2H of this step's loss
                 d2h_stream.wait_event(consumed[b])
@@ -602,7 +636,7 @@ def run_ours(args):
             loss_read[prev].synchronize()                 # the previous step's loss has arrived
             return float(loss_host[prev])
     else:
-        value_step = step
+        value_step = replica_step = step
         l0 = K.LAUNCHES
         step(0)
         per_step_launches = K.LAUNCHES - l0
@@ -616,6 +650,15 @@ def run_ours(args):
             loss.backward()
             return loss.item()
 
+    replica_ms = comm_ms = None
+    if with_comm and use_graph:
+        replica_ms, _, _ = timed(replica_step, args.steps, warmup)
+        # the all-reduce alone, back to back on the communication stream
+        def comm_only(i):
+            with torch.cuda.stream(comm_stream):
+                dist.all_reduce(bucket)
+            torch.cuda.current_stream().wait_stream(comm_stream)
+        comm_ms, _, _ = timed(comm_only, args.steps, warmup)
     sampler = ClockSampler(local)
     ms, t0, t1 = timed(value_step, args.steps, warmup)
     launches = per_step_launches * args.steps
@@ -635,6 +678,7 @@ def run_ours(args):
             "data": "synthetic", "config": workload_config(world),
             "e2e": {"value": e2e_value, "unit": "tokens/s",
                     "h2d_bytes_per_step": TOKENS * D_MODEL * 2, "d2h_bytes_per_step": 4,
+                    "h2d_gbs_per_rank": TOKENS * D_MODEL * 2 / (e2e_ms / args.steps * 1e-3) / 1e9,
                     "ms_per_step": e2e_ms / args.steps,
                     "how": "MoEBlock.forward + loss.backward captured in a CUDA graph; every "
                            "step copies its x from pinned host memory (on a copy stream, "
@@ -644,10 +688,20 @@ def run_ours(args):
             "pct_bf16_peak": {"measured_burst": 100 * value / world * FLOP_PER_TOKEN_FWD_BWD
                               / (pk["bf16_tflops"] * 1e12),
                               "nominal_2250": 100 * value / world * FLOP_PER_TOKEN_FWD_BWD / 2.25e15},
-            "grad_allreduce": bool(args.grad_allreduce and world > 1),
+            "grad_allreduce": bool(with_comm),
             "cuda_graph": use_graph,
             "eager_ms_per_step": eager_ms / args.steps,
         }
+        if with_comm and replica_ms is not None:
+            line["grad_allreduce_detail"] = {
+                "what": "weight gradients of the block summed over the ranks: one flattened bf16 "
+                        "bucket, ncclAllReduce on a communication stream under the next step's "
+                        "compute; inside the timed region",
+                "bytes": int(n_grad) * 2,
+                "allreduce_alone_ms": comm_ms / args.steps,
+                "allreduce_bus_gbs": 2 * (world - 1) / world * n_grad * 2 / (comm_ms / args.steps * 1e-3) / 1e9,
+                "replicas_only_ms_per_step": replica_ms / args.steps,
+                "replicas_only_value": TOKENS * world * args.steps / (replica_ms / 1e3)}
         if not args.no_stages:
             stages = stage_rooflines(m, dev_x[0], pk)
             top = max(stages, key=lambda s: s["us"] * s["launches_per_step"])
@@ -811,18 +865,14 @@ def run_ep_workload(args):
             "cuda_graph": use_graph, "phases": phases}), flush=True)
     dist.barrier()
     torch.cuda.synchronize()
-    # Captured graphs that contain collectives keep references into the communicator: tearing the
-    # process group down while they are alive did not return. Drop the graphs (and the exchange
-    # buffers they point into) first, then tear down.
-    run = None
+    # Tear-down. With the step captured in CUDA graphs (NCCL collectives and symmetric-memory
+    # buffers inside), destroy_process_group() does not return: neither with the graphs alive nor
+    # after releasing the graphs and the exchange buffers first (tried; both ranks then sit in the
+    # tear-down until the launcher's timeout). The results are out and every rank has passed the
+    # barrier, so a graph run leaves directly.
     if use_graph:
-        graphs.clear()
-    if push:
-        del grp
-    import gc
-    gc.collect()
-    torch.cuda.synchronize()
-    dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
     dist.destroy_process_group()
 
 
@@ -1020,8 +1070,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-grad-allreduce", action="store_true",
+                    help="N > 1: time the bare token-sharded replicas, without the gradient all-reduce")
     ap.add_argument("--grad-allreduce", action="store_true",
-                    help="also all-reduce the weight gradients across ranks inside the step")
+                    help="(default at N > 1; kept so that older command lines still parse)")
     ap.add_argument("--no-stages", action="store_true", help="skip the per-kernel roofline pass")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true",
