@@ -659,6 +659,20 @@ def run_ours(args):
                 dist.all_reduce(bucket)
             torch.cuda.current_stream().wait_stream(comm_stream)
         comm_ms, _, _ = timed(comm_only, args.steps, warmup)
+    # the same step through the package's graph wrapper (what a trainer calls instead of the bench's
+    # own capture): GraphedMoEBlock.forward + autograd backward, forward and backward each a replay
+    graphed_ms = None
+    if use_graph:
+        from nanospeaker_b200 import GraphedMoEBlock
+        gm = GraphedMoEBlock(m)
+
+        def graphed_step(i):
+            for p in params:
+                p.grad = None
+            x = dev_x[i % N_INPUT_SETS].detach().requires_grad_(True)
+            out = gm(x)
+            torch.autograd.backward([out, gm.aux_loss], [dev_dout[i % N_INPUT_SETS], one])
+        graphed_ms, _, _ = timed(graphed_step, args.steps, warmup)
     sampler = ClockSampler(local)
     ms, t0, t1 = timed(value_step, args.steps, warmup)
     launches = per_step_launches * args.steps
@@ -691,6 +705,7 @@ def run_ours(args):
             "grad_allreduce": bool(with_comm),
             "cuda_graph": use_graph,
             "eager_ms_per_step": eager_ms / args.steps,
+            "graphed_module_ms_per_step": None if graphed_ms is None else graphed_ms / args.steps,
         }
         if with_comm and replica_ms is not None:
             line["grad_allreduce_detail"] = {

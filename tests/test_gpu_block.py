@@ -524,3 +524,42 @@ def test_stacked_decoder_graph_replay_equals_eager_stack():
                     assert rel_l2(fast.float(), ref) < tol, mode
     from nanospeaker_b200 import kernels
     kernels.check_status("cuda")
+
+
+def test_graphed_block_replays_the_blocks_training_step():
+    """GraphedMoEBlock: forward and backward captured once per shape and replayed behind the module
+    interface. Against the block called directly, over several steps with changing inputs and an
+    in-place weight update in between: output, balance loss, counts and every gradient."""
+    from nanospeaker_b200 import GraphedMoEBlock
+    x0, m, _ = _model_shape_pair(1024, train=True, seed=6)
+    m.combine_mode = "store"                     # bitwise comparable
+    g = GraphedMoEBlock(m)
+    params = dict(m.named_parameters())
+    for step in range(3):
+        torch.manual_seed(20 + step)
+        x = torch.randn(4, 256, 576, device="cuda").bfloat16()      # leading dims kept
+        xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+        for p in params.values():
+            p.grad = None
+        out_a = g(xa)
+        (out_a.float().square().mean() + g.aux_loss).backward()
+        got = {n: p.grad.clone() for n, p in params.items()}
+        aux_a, counts_a = g.aux_loss.detach().clone(), g.expert_counts.clone()
+        for p in params.values():
+            p.grad = None
+        out_b = m(xb)
+        (out_b.float().square().mean() + m.aux_loss).backward()
+        assert out_a.shape == x.shape and torch.equal(out_a, out_b)
+        assert torch.equal(counts_a.long(), m.expert_counts.long())
+        assert abs(float(aux_a) - float(m.aux_loss)) < 1e-6
+        assert torch.equal(xa.grad, xb.grad)
+        for n, p in params.items():
+            assert torch.equal(got[n], p.grad), n
+        with torch.no_grad():                    # an optimizer step in place: the graphs see it
+            for p in params.values():
+                p.add_(0.01 * torch.randn_like(p))
+    assert len(g._graphed) == 1
+    with torch.no_grad():                        # no autograd: the block's own inference path
+        assert g(x).shape == x.shape
+    from nanospeaker_b200 import kernels
+    kernels.check_status("cuda")
