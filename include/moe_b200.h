@@ -86,8 +86,12 @@ int moe_b200_router_topk_bwd(const float* logits, const int64_t* topk_idx, const
  * int64) whose last n_shared columns are the shared experts as (expert n_experts + s, weight 1)
  * pairs, and -- when full_softmax != 0 and colsum != NULL -- ADDING sum_t softmax(l_t)[e] into
  * colsum[e] (fp32 [n_experts], zero it first), the only statistic balance_loss needs
- * (src/model/router.py:100-111). No [T, E] fp32 tensor is written. */
-int moe_b200_router_fused(const void* logits, int32_t ld, const float* bias, int64_t n_tokens,
+ * (src/model/router.py:100-111). No [T, E] fp32 tensor is written.
+ * noise (may be NULL): fp32 [n_tokens, n_experts], added to the logits like the bias -- the
+ * exploration noise of a training step (src/model/router.py:76-77), drawn by the caller so that the
+ * random stream stays outside the kernels. */
+int moe_b200_router_fused(const void* logits, int32_t ld, const float* bias, const float* noise,
+                          int64_t n_tokens,
                           int32_t n_experts, int32_t top_k, int32_t n_shared, int32_t normalize,
                           int32_t full_softmax, void* w_all, int64_t* idx_all, float* colsum,
                           void* stream);
@@ -97,7 +101,7 @@ int moe_b200_router_fused(const void* logits, int32_t ld, const float* bias, int
  * balance loss's gradient d_aux[0] * aux_coef * n_experts / n_tokens * counts[e] / sum(counts)
  * on every probability of expert e (counts int32 [n_experts] from the dispatch). */
 int moe_b200_router_fused_bwd(const void* logits, int32_t ld, const float* bias,
-                              const int64_t* idx_all, const void* dw_all, int64_t n_tokens,
+                              const float* noise, const int64_t* idx_all, const void* dw_all, int64_t n_tokens,
                               int32_t n_experts, int32_t top_k, int32_t n_shared,
                               int32_t normalize, int32_t full_softmax, const float* d_aux,
                               const int32_t* counts, float aux_coef, void* d_logits,
@@ -140,7 +144,8 @@ int moe_b200_dispatch(const int64_t* topk_idx, int64_t n_pairs, int32_t n_expert
  * n_experts + n_shared) bytes. Replaces TopKRouter.forward's selection (src/model/router.py:79-97)
  * followed by moe_dispatch (src/model/moe_kernel.py:180-218). */
 size_t moe_b200_router_dispatch_scratch_bytes(int64_t n_tokens, int32_t n_experts_total);
-int moe_b200_router_dispatch(const void* logits, int32_t ld, const float* bias, int64_t n_tokens,
+int moe_b200_router_dispatch(const void* logits, int32_t ld, const float* bias,
+                             const float* noise, int64_t n_tokens,
                              int32_t n_experts, int32_t top_k, int32_t n_shared,
                              int32_t normalize, int32_t full_softmax, void* w_all,
                              int64_t* idx_all, float* colsum, int32_t* sorted_ids,

@@ -26,11 +26,11 @@ SIGNATURES = {
         [_c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp]),
     "moe_b200_router_fused": (
         ctypes.c_int,
-        [_c_vp, _c_i32, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp,
+        [_c_vp, _c_i32, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp,
          _c_vp]),
     "moe_b200_router_fused_bwd": (
         ctypes.c_int,
-        [_c_vp, _c_i32, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp,
+        [_c_vp, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp,
          _c_vp, ctypes.c_float, _c_vp, _c_i32, _c_vp]),
     "moe_b200_balance_loss": (
         ctypes.c_int, [_c_vp, _c_vp, _c_i32, _c_i64, ctypes.c_float, _c_vp, _c_vp]),
@@ -42,7 +42,7 @@ SIGNATURES = {
     "moe_b200_router_dispatch_scratch_bytes": (_c_sz, [_c_i64, _c_i32]),
     "moe_b200_router_dispatch": (
         ctypes.c_int,
-        [_c_vp, _c_i32, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp,
+        [_c_vp, _c_i32, _c_vp, _c_vp, _c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32, _c_vp, _c_vp, _c_vp,
          _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_sz, _c_vp, _c_vp]),
     "moe_b200_dispatch_static": (
         ctypes.c_int,

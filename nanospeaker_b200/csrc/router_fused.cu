@@ -26,7 +26,7 @@ constexpr int RF_WARPS = 8;
 template <int NSLOT, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
     router_fused_kernel(const __nv_bfloat16* __restrict__ logits, int ld,
-                        const float* __restrict__ bias, int64_t n_tokens, int n_experts, int top_k,
+                        const float* __restrict__ bias, const float* __restrict__ noise, int64_t n_tokens, int n_experts, int top_k,
                         int n_shared, int normalize, int full_softmax,
                         __nv_bfloat16* __restrict__ w_all, int64_t* __restrict__ idx_all,
                         float* __restrict__ colsum, int tokens_per_block,
@@ -67,7 +67,9 @@ __global__ void __launch_bounds__(WARPS * 32)
     for (int i = 0; i < NSLOT; ++i) {
       const int e = i * 32 + lane;
       const bool in = e < n_experts;
-      v[i] = in ? __bfloat162float(row[e]) + b[i] : -CUDART_INF_F;
+      v[i] = in ? __bfloat162float(row[e]) + b[i] +
+                      (noise != nullptr ? __ldg(noise + t * n_experts + e) : 0.f)
+                : -CUDART_INF_F;
       const uint32_t fk = float_key(v[i]);
       key[i] = in ? (fk == 0u ? 1u : fk) : 0u;
       mx = fmaxf(mx, v[i]);
@@ -192,7 +194,7 @@ __device__ __forceinline__ float key_float(uint32_t k) {   // inverse of float_k
 template <int EPL, bool COLSUM>
 __global__ void __launch_bounds__(RF4_THREADS)
     router_fused4_kernel(const __nv_bfloat16* __restrict__ logits, int ld,
-                         const float* __restrict__ bias, int64_t n_tokens, int n_experts, int top_k,
+                         const float* __restrict__ bias, const float* __restrict__ noise, int64_t n_tokens, int n_experts, int top_k,
                          int n_shared, int normalize, int full_softmax,
                          __nv_bfloat16* __restrict__ w_all, int64_t* __restrict__ idx_all,
                          float* __restrict__ colsum, int tokens_per_block,
@@ -244,8 +246,12 @@ __global__ void __launch_bounds__(RF4_THREADS)
         for (int h = 0; h < 4; ++h) {
           const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[h]));
           const int i = c * 8 + 2 * h;
-          const float v0 = (e0 + i < n_experts) ? f.x + b[i] : -CUDART_INF_F;
-          const float v1 = (e0 + i + 1 < n_experts) ? f.y + b[i + 1] : -CUDART_INF_F;
+          float v0 = (e0 + i < n_experts) ? f.x + b[i] : -CUDART_INF_F;
+          float v1 = (e0 + i + 1 < n_experts) ? f.y + b[i + 1] : -CUDART_INF_F;
+          if (noise != nullptr) {   // exploration noise, one value per (token, expert)
+            if (e0 + i < n_experts) v0 += __ldg(noise + tc * n_experts + e0 + i);
+            if (e0 + i + 1 < n_experts) v1 += __ldg(noise + tc * n_experts + e0 + i + 1);
+          }
           key[i] = __float_as_uint(v0);
           key[i + 1] = __float_as_uint(v1);
           mx = fmaxf(mx, fmaxf(v0, v1));
@@ -406,7 +412,7 @@ static void launch_rf4(int epl, bool want_colsum, unsigned grid, cudaStream_t st
 template <int NSLOT>
 __global__ void __launch_bounds__(RF_WARPS * 32)
     router_fused_bwd_kernel(const __nv_bfloat16* __restrict__ logits, int ld,
-                            const float* __restrict__ bias, const int64_t* __restrict__ idx_all,
+                            const float* __restrict__ bias, const float* __restrict__ noise, const int64_t* __restrict__ idx_all,
                             const __nv_bfloat16* __restrict__ dw_all, int64_t n_tokens,
                             int n_experts, int top_k, int n_shared, int normalize,
                             int full_softmax, const float* __restrict__ d_aux,
@@ -421,12 +427,24 @@ __global__ void __launch_bounds__(RF_WARPS * 32)
   float b[NSLOT], dcs[NSLOT];
   {
     const float g = (d_aux != nullptr && full_softmax) ? *d_aux : 0.f;
-    const float denom_c = float(n_tokens) * float(top_k);
+    // the loss weighs expert e by counts[e] / sum(counts): the sum is taken here rather than
+    // assumed to be n_tokens * top_k, so that counts summed over several ranks (a global balance
+    // loss) give the exact gradient too
+    float c[NSLOT], tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NSLOT; ++i) {
+      const int e = i * 32 + lane;
+      c[i] = (g != 0.f && e < n_experts) ? float(counts[e]) : 0.f;
+      tot += c[i];
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    const float denom_c = fmaxf(tot, 1.f);
 #pragma unroll
     for (int i = 0; i < NSLOT; ++i) {
       const int e = i * 32 + lane;
       b[i] = (bias != nullptr && e < n_experts) ? bias[e] : 0.f;
-      dcs[i] = (e < n_experts && g != 0.f) ? g * aux_scale_T * float(counts[e]) / denom_c : 0.f;
+      dcs[i] = (e < n_experts && g != 0.f) ? g * aux_scale_T * c[i] / denom_c : 0.f;
     }
   }
 
@@ -439,7 +457,9 @@ __global__ void __launch_bounds__(RF_WARPS * 32)
 #pragma unroll
     for (int i = 0; i < NSLOT; ++i) {
       const int e = i * 32 + lane;
-      v[i] = e < n_experts ? __bfloat162float(row[e]) + b[i] : -CUDART_INF_F;
+      v[i] = e < n_experts ? __bfloat162float(row[e]) + b[i] +
+                                 (noise != nullptr ? __ldg(noise + t * n_experts + e) : 0.f)
+                           : -CUDART_INF_F;
       mx = fmaxf(mx, v[i]);
       dp[i] = dcs[i];
     }
@@ -574,20 +594,21 @@ static unsigned rf_grid(int64_t n_tokens, int blocks_per_sm = 16) {
 constexpr int RF_CHUNK_WARPS = 32;
 
 int launch_router_fused_chunked(const __nv_bfloat16* logits, int ld, const float* bias,
-                                int64_t n_tokens, int n_experts, int top_k, int n_shared,
+                                const float* noise, int64_t n_tokens, int n_experts, int top_k, int n_shared,
                                 int normalize, int full_softmax, __nv_bfloat16* w_all,
                                 int64_t* idx_all, float* colsum, int tokens_per_block, int n_blocks,
                                 int32_t* block_hist, int32_t* sorted_ids, int64_t l_cap,
                                 cudaStream_t st) {
   if (const int epl = rf4_experts_per_lane(logits, ld, n_experts, top_k)) {
     launch_rf4(epl, full_softmax && colsum != nullptr, unsigned(n_blocks), st, logits, ld, bias,
-               n_tokens, n_experts, top_k, n_shared, normalize, full_softmax, w_all, idx_all, colsum,
+               noise, n_tokens, n_experts, top_k, n_shared, normalize, full_softmax, w_all, idx_all, colsum,
                tokens_per_block, block_hist, sorted_ids, l_cap);
     return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
   }
 #define LAUNCH(NS)                                                                              \
   launch_pdl(router_fused_kernel<NS, RF_CHUNK_WARPS>, dim3(n_blocks), dim3(RF_CHUNK_WARPS * 32), 0, \
-             st, logits, ld, bias, n_tokens, n_experts, top_k, n_shared, normalize, full_softmax,   \
+             st, logits, ld, bias, noise, n_tokens, n_experts, top_k, n_shared, normalize,          \
+             full_softmax,                                                                          \
              w_all, idx_all, colsum, tokens_per_block, block_hist, sorted_ids, l_cap)
   const int nslot = (n_experts + 31) / 32;
   if (nslot <= 1) LAUNCH(1);
@@ -605,7 +626,8 @@ using namespace moe;
 
 extern "C" {
 
-int moe_b200_router_fused(const void* logits, int32_t ld, const float* bias, int64_t n_tokens,
+int moe_b200_router_fused(const void* logits, int32_t ld, const float* bias, const float* noise,
+                          int64_t n_tokens,
                           int32_t n_experts, int32_t top_k, int32_t n_shared, int32_t normalize,
                           int32_t full_softmax, void* w_all, int64_t* idx_all, float* colsum,
                           void* stream) {
@@ -623,14 +645,16 @@ int moe_b200_router_fused(const void* logits, int32_t ld, const float* bias, int
   if (const int epl = rf4_experts_per_lane(logits, ld, n_experts, top_k)) {
     int64_t blocks = (n_tokens + RF4_TOKENS - 1) / RF4_TOKENS;
     if (blocks > 148 * 2) blocks = 148 * 2;
-    launch_rf4(epl, full_softmax && colsum != nullptr, unsigned(blocks), st, lg, ld, bias, n_tokens,
+    launch_rf4(epl, full_softmax && colsum != nullptr, unsigned(blocks), st, lg, ld, bias, noise,
+               n_tokens,
                n_experts, top_k, n_shared, normalize, full_softmax, w, idx_all, colsum, 0,
                static_cast<int32_t*>(nullptr), static_cast<int32_t*>(nullptr), int64_t(0));
     return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
   }
 #define LAUNCH(NS)                                                                          \
   launch_pdl(router_fused_kernel<NS, RF_WARPS>, dim3(grid), dim3(RF_WARPS * 32), 0, st, lg, ld,    \
-             bias, n_tokens, n_experts, top_k, n_shared, normalize, full_softmax, w, idx_all,      \
+             bias, noise, n_tokens, n_experts, top_k, n_shared, normalize, full_softmax, w,        \
+             idx_all,                                                                               \
              colsum, 0, static_cast<int32_t*>(nullptr), static_cast<int32_t*>(nullptr), int64_t(0))
   const int nslot = (n_experts + 31) / 32;
   if (nslot <= 1) LAUNCH(1);
@@ -643,7 +667,7 @@ int moe_b200_router_fused(const void* logits, int32_t ld, const float* bias, int
 }
 
 int moe_b200_router_fused_bwd(const void* logits, int32_t ld, const float* bias,
-                              const int64_t* idx_all, const void* dw_all, int64_t n_tokens,
+                              const float* noise, const int64_t* idx_all, const void* dw_all, int64_t n_tokens,
                               int32_t n_experts, int32_t top_k, int32_t n_shared,
                               int32_t normalize, int32_t full_softmax, const float* d_aux,
                               const int32_t* counts, float aux_coef, void* d_logits,
@@ -662,7 +686,8 @@ int moe_b200_router_fused_bwd(const void* logits, int32_t ld, const float* bias,
   __nv_bfloat16* out = static_cast<__nv_bfloat16*>(d_logits);
 #define LAUNCH(NS)                                                                               \
   launch_pdl(router_fused_bwd_kernel<NS>, dim3(grid), dim3(RF_WARPS * 32), 0, st,                                     \
-      lg, ld, bias, idx_all, dw, n_tokens, n_experts, top_k, n_shared, normalize, full_softmax,   \
+      lg, ld, bias, noise, idx_all, dw, n_tokens, n_experts, top_k, n_shared, normalize,          \
+      full_softmax,                                                                                \
       d_aux, counts, scale, out, ld_out)
   const int nslot = (n_experts + 31) / 32;
   if (nslot <= 1) LAUNCH(1);

@@ -596,7 +596,8 @@ size_t moe_b200_router_dispatch_scratch_bytes(int64_t n_tokens, int32_t n_expert
   return size_t(blocks > 0 ? blocks : 1) * size_t(n_experts_total) * sizeof(int32_t);
 }
 
-int moe_b200_router_dispatch(const void* logits, int32_t ld, const float* bias, int64_t n_tokens,
+int moe_b200_router_dispatch(const void* logits, int32_t ld, const float* bias,
+                             const float* noise, int64_t n_tokens,
                              int32_t n_experts, int32_t top_k, int32_t n_shared,
                              int32_t normalize, int32_t full_softmax, void* w_all,
                              int64_t* idx_all, float* colsum, int32_t* sorted_ids,
@@ -621,7 +622,8 @@ int moe_b200_router_dispatch(const void* logits, int32_t ld, const float* bias, 
   int32_t* block_hist = static_cast<int32_t*>(scratch);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int rc = launch_router_fused_chunked(
-      static_cast<const __nv_bfloat16*>(logits), ld, bias, n_tokens, n_experts, top_k, n_shared,
+      static_cast<const __nv_bfloat16*>(logits), ld, bias, noise, n_tokens, n_experts, top_k,
+      n_shared,
       normalize, full_softmax, static_cast<__nv_bfloat16*>(w_all), idx_all, colsum, tpb, blocks,
       block_hist, sorted_ids, l_cap, st);
   if (rc != MOE_B200_OK) return rc;

@@ -26,6 +26,7 @@ namespace moe {
 // that also leaves the dispatch's per-block histograms and the sentinel fill. Returns an error code
 // of include/moe_b200.h.
 int launch_router_fused_chunked(const __nv_bfloat16* logits, int ld, const float* bias,
+                                const float* noise,
                                 int64_t n_tokens, int n_experts, int top_k, int n_shared,
                                 int normalize, int full_softmax, __nv_bfloat16* w_all,
                                 int64_t* idx_all, float* colsum, int tokens_per_block, int n_blocks,

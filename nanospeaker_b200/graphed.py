@@ -83,7 +83,8 @@ class GraphedMoEBlock(nn.Module):
         # (without autograd there is no backward to pair the forward with: the block's own
         # inference path is the lighter one then, and nanospeaker_b200.decode graphs it)
         if (not x.is_cuda or x2.shape[0] == 0 or x.shape[-1] != b.d_model
-                or not torch.is_grad_enabled() or not b._whole_block_ok(x2)):
+                or not torch.is_grad_enabled() or not b._whole_block_ok(x2)
+                or (b.training and b.router.noise_std)):   # noise: fresh random numbers every call
             return b(x)
         out, aux, counts = self._callable_for(x)(x)
         full = b.router.wants_probs()

@@ -98,7 +98,7 @@ def router_topk_bwd(logits, topk_idx, d_topk_w, d_probs, normalize: bool,
 
 
 def router_fused(logits, bias, n_experts: int, top_k: int, n_shared: int, normalize: bool,
-                 full_softmax: bool):
+                 full_softmax: bool, noise=None):
     """bf16 logits [T, ld] (+ fp32 bias [E]) -> (w_all bf16 [T, k+S], idx_all int64 [T, k+S],
     colsum fp32 [E] or None). The last S columns are the shared experts (id E+s, weight 1)."""
     _need_cuda(logits)
@@ -109,15 +109,24 @@ def router_fused(logits, bias, n_experts: int, top_k: int, n_shared: int, normal
     colsum = (torch.zeros(n_experts, dtype=torch.float32, device=logits.device)
               if full_softmax else None)
     _lib.check(_lib.load().moe_b200_router_fused(
-        logits.data_ptr(), ld, _lib.ptr(bias), t, n_experts, top_k, n_shared, int(normalize),
-        int(full_softmax), w_all.data_ptr(), idx_all.data_ptr(), _lib.ptr(colsum),
-        _stream(logits)), "moe_b200_router_fused")
+        logits.data_ptr(), ld, _lib.ptr(bias), _lib.ptr(_noise(noise, t, n_experts)), t, n_experts,
+        top_k, n_shared, int(normalize), int(full_softmax), w_all.data_ptr(), idx_all.data_ptr(),
+        _lib.ptr(colsum), _stream(logits)), "moe_b200_router_fused")
     _count(1 if t else 0)
     return w_all, idx_all, colsum
 
 
+def _noise(noise, n_tokens: int, n_experts: int):
+    """Exploration noise as the kernels read it: fp32 [n_tokens, n_experts], contiguous."""
+    if noise is None:
+        return None
+    assert tuple(noise.shape) == (n_tokens, n_experts) and noise.dtype == torch.float32
+    assert noise.is_contiguous()
+    return noise
+
+
 def router_dispatch(logits, bias, n_experts: int, top_k: int, n_shared: int, normalize: bool,
-                    full_softmax: bool):
+                    full_softmax: bool, noise=None):
     """router_fused + dispatch in two launches (the router kernel leaves the dispatch's per-block
     histograms): -> (w_all, idx_all, colsum | None, sorted_ids, expert_ids, pad_offsets, counts,
     n_post_pad, inv_ids) with counts / pad_offsets over the n_experts + n_shared experts."""
@@ -140,7 +149,8 @@ def router_dispatch(logits, bias, n_experts: int, top_k: int, n_shared: int, nor
     nbytes = lib.moe_b200_router_dispatch_scratch_bytes(t, n_all)
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     _lib.check(lib.moe_b200_router_dispatch(
-        logits.data_ptr(), ld, _lib.ptr(bias), t, n_experts, top_k, n_shared, int(normalize),
+        logits.data_ptr(), ld, _lib.ptr(bias), _lib.ptr(_noise(noise, t, n_experts)), t, n_experts,
+        top_k, n_shared, int(normalize),
         int(full_softmax), w_all.data_ptr(), idx_all.data_ptr(), _lib.ptr(colsum), sids.data_ptr(),
         eids.data_ptr(), offs.data_ptr(), counts.data_ptr(), npp.data_ptr(), inv.data_ptr(),
         scratch.data_ptr(), nbytes, status_word(dev).data_ptr(), _stream(logits)),
@@ -151,13 +161,14 @@ def router_dispatch(logits, bias, n_experts: int, top_k: int, n_shared: int, nor
 
 def router_fused_bwd(logits, bias, idx_all, dw_all, n_experts: int, top_k: int, n_shared: int,
                      normalize: bool, full_softmax: bool, d_aux, counts, aux_coef: float,
-                     ld_out: int) -> torch.Tensor:
+                     ld_out: int, noise=None) -> torch.Tensor:
     """-> d(logits) bf16 [T, ld_out], zero in the pad columns."""
     _need_cuda(logits, idx_all, dw_all)
     t, ld = logits.shape
     out = torch.empty((t, ld_out), dtype=logits.dtype, device=logits.device)
     _lib.check(_lib.load().moe_b200_router_fused_bwd(
-        logits.data_ptr(), ld, _lib.ptr(bias), idx_all.data_ptr(), dw_all.data_ptr(), t,
+        logits.data_ptr(), ld, _lib.ptr(bias), _lib.ptr(_noise(noise, t, n_experts)),
+        idx_all.data_ptr(), dw_all.data_ptr(), t,
         n_experts, top_k, n_shared, int(normalize), int(full_softmax), _lib.ptr(d_aux),
         _lib.ptr(counts), float(aux_coef), out.data_ptr(), ld_out, _stream(logits)),
         "moe_b200_router_fused_bwd")

@@ -9,8 +9,8 @@ src/train/metrics.py:84-97) and its checkpoints work unchanged.
 Paths, in the order `forward` tries them:
   1. kernel    CUDA + bf16 + a named activation + shapes the tiles cover: router top-k, dispatch,
                permute, grouped GEMMs, combine and the shared experts all run as the `moe_b200`
-               ops (one whole-block op when there are no biases, no exploration noise and no
-               capacity; router + dispatch + experts ops otherwise). No host sync. A missing or
+               ops (one whole-block op when there are no biases and no capacity; router +
+               dispatch + experts ops otherwise). No host sync. A missing or
                failing library raises; nothing is silently rerouted. An explicit capacity_factor
                (the reference's padded path, src/model/moe.py:225-283) runs on the same kernels:
                the dispatch drops the pairs over capacity instead of padding a batch.
@@ -122,10 +122,9 @@ class MoEBlock(nn.Module):
         return self._kernel_config_ok() and kernel_supported(x)
 
     def _whole_block_ok(self, x: torch.Tensor) -> bool:
-        """Can `forward` hand x to the single whole-block op? It has no bias operands, draws no
-        exploration noise and knows no capacity, so those cases take router + fused_moe_forward."""
-        return (self._use_kernel(x) and self.b_in is None and self.b_sh_in is None
-                and not (self.training and self.router.noise_std))
+        """Can `forward` hand x to the single whole-block op? It has no bias operands and knows no
+        capacity, so those cases take router + fused_moe_forward."""
+        return self._use_kernel(x) and self.b_in is None and self.b_sh_in is None
 
     # ---------------------------------------------------------------------------- bookkeeping
     def _record(self, probs, counts, x):
@@ -204,9 +203,15 @@ class MoEBlock(nn.Module):
         if self._whole_block_ok(x):
             # whole block as one op: router GEMM, top-k, dispatch, experts, combine, balance loss
             full = self.router.wants_probs()
+            noise = None
+            if self.training and self.router.noise_std:
+                # exploration noise on the logits (src/model/router.py:76-77), drawn here so that
+                # the op stays a pure function of its inputs
+                noise = torch.randn(x.shape[0], self.n_experts, device=x.device,
+                                    dtype=torch.float32) * self.router.noise_std
             out, aux, counts = fused_moe_block(
                 x, self.router, self.W_in, self.W_out, self.W_sh_in, self.W_sh_out,
-                self._kernel_act, full, combine=self.combine_mode)
+                self._kernel_act, full, combine=self.combine_mode, noise=noise)
             self.expert_counts = counts.detach()
             self.aux_loss = aux if full else torch.zeros((), device=x.device, dtype=x.dtype)
             return out.view(shape)
@@ -215,8 +220,8 @@ class MoEBlock(nn.Module):
         cap = self._capacity(x.shape[0]) if self.capacity_factor is not None else 0
 
         if self._kernels_take(x):
-            # biases, exploration noise (drawn by the router above) or a capacity: the same kernels
-            # behind the router, the capacity as a variant of the dispatch schedule
+            # biases or a capacity: the same kernels behind the router, the capacity as a variant of
+            # the dispatch schedule
             out, counts = fused_moe_forward(
                 x, self.W_in, self.W_out, topk_w, topk_idx, self.b_in, self.b_out,
                 self._kernel_act, w_sh_in=self.W_sh_in, w_sh_out=self.W_sh_out,

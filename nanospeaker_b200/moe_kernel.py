@@ -54,6 +54,24 @@ def _atomic(mode: Optional[str]) -> bool:
     return mode == "atomic"
 
 
+# Balance loss over more than one rank's tokens. With tokens sharded over ranks every rank's own
+# loss uses its shard's routing counts (what the reference computes per process); for the loss of the
+# WHOLE batch the counts have to be summed over the ranks first. _aux_reduce, when set, is called
+# inside the whole-block op on a copy of the routed experts' counts (int32 [E], in place, e.g.
+# torch.distributed.all_reduce): the op then weighs its probability sums by the global counts, and
+# fused_moe_block scales the result by T_local / T_global, so that every rank holds ITS SHARE of the
+# global loss -- the shares sum to the global loss, and so do their gradients when the ranks'
+# gradients are summed. nanospeaker_b200.parallel.enable_global_balance_loss sets it.
+_aux_reduce = None
+
+
+def set_aux_reduce(fn) -> None:
+    """fn(counts int32 [E]) -> None reduces the counts over the ranks in place; None switches the
+    global balance loss off."""
+    global _aux_reduce
+    _aux_reduce = fn
+
+
 MAX_EXPERTS = 256  # per-expert state of the routing kernels lives on chip
 MAX_TOPK = 16
 MAX_SHARED = 8     # shared experts are dispatched as extra experts: E + S <= MAX_EXPERTS
@@ -485,6 +503,8 @@ def moe_block(
     save_for_backward: bool,
     residual: Optional[torch.Tensor] = None,
     atomic_combine: bool = False,
+    noise: Optional[torch.Tensor] = None,
+    global_aux: bool = False,
 ) -> _T15:
     """The whole MoE block as one op: router GEMM, top-k, dispatch, experts (routed + shared),
     combine and the balance loss, with no PyTorch glue kernels in between
@@ -494,6 +514,9 @@ def moe_block(
     logits, w_all, idx_all, sorted_ids, expert_ids, pad_offsets, counts_all, n_post_pad, inv_ids,
     router_w_padded]. The router GEMM runs on the same tcgen05 kernels as the experts against a
     copy of router_w zero-padded to a multiple of 64 columns, so the logits are [T, ld] bf16.
+    noise: optional fp32 [T, E] added to the logits before the selection -- the exploration noise of
+    a training step (src/model/router.py:76-77), drawn by the caller: the random stream stays
+    outside the op, so a reentrant checkpoint replays it like any other input.
     """
     x, w_in, w_out = x.contiguous(), w_in.contiguous(), w_out.contiguous()
     _check_inputs(x, w_in, w_out, w_sh_in)
@@ -511,8 +534,10 @@ def moe_block(
 
     wp = K.copy_cols(router_w, ld).unsqueeze(0)   # [1, D, ld], zero pad columns
     logits = K.down_gemm(x, wp, None, None, 1, None, None, 0)[0]
+    if noise is not None:
+        noise = noise.to(torch.float32).contiguous()
     w_all, idx_all, colsum, sids, eids, offs, counts_all, npp, inv = K.router_dispatch(
-        logits, logit_bias, e_n, top_k, s_n, normalize, full_softmax)
+        logits, logit_bias, e_n, top_k, s_n, normalize, full_softmax, noise)
     tw = w_all.reshape(-1)
     m = n * ks
     if save_for_backward:
@@ -528,17 +553,24 @@ def moe_block(
     else:
         y = K.down_gemm(hid, w_out, eids, npp, 0, sids, tw, m, w_extra=w_sh_out)
         out = K.combine(y, inv, n, ks, residual)   # + residual [T, D] in the same fp32 sum when given
+    counts = counts_all[:e_n].clone()
     if full_softmax:
+        if global_aux and _aux_reduce is not None:
+            # the loss (and, in the backward, its gradient) weighs the experts by the counts of all
+            # ranks; the plan tensors keep the local ones
+            counts_all = counts_all.clone()
+            _aux_reduce(counts_all[:e_n])
         aux = K.balance_loss(colsum, counts_all, e_n, n, aux_coef)
     else:
         aux = torch.zeros((), dtype=torch.float32, device=x.device)
-    return (out, aux, counts_all[:e_n].clone(), xs, a1, logits, w_all, idx_all, sids, eids, offs,
+    return (out, aux, counts, xs, a1, logits, w_all, idx_all, sids, eids, offs,
             counts_all, npp, inv, wp)
 
 
 @moe_block.register_fake
 def _(x, router_w, logit_bias, w_in, w_out, w_sh_in, w_sh_out, top_k, normalize, full_softmax,
-      aux_coef, activation, save_for_backward, residual=None, atomic_combine=False):
+      aux_coef, activation, save_for_backward, residual=None, atomic_combine=False, noise=None,
+      global_aux=False):
     n, d = x.shape
     e_n = w_in.shape[0]
     s_n = 0 if w_sh_in is None else w_sh_in.shape[0]
@@ -581,6 +613,7 @@ def moe_block_bwd(
     aux_coef: float,
     activation: str,
     atomic_combine: bool = False,
+    noise: Optional[torch.Tensor] = None,
 ) -> _T6:
     """[dx, d_router_w [D, E], dW_in, dW_out, dW_sh_in, dW_sh_out] of moe_block."""
     grad_out = grad_out.to(x.dtype).contiguous()
@@ -621,7 +654,7 @@ def moe_block_bwd(
         d_aux = None if grad_aux is None else grad_aux.to(torch.float32).reshape(1)
         dl = K.router_fused_bwd(logits, logit_bias, idx_all, dtw.view(n, ks), e_n, top_k, s_n,
                                 normalize, full_softmax, d_aux, counts_all, aux_coef,
-                                logits.shape[1])
+                                logits.shape[1], noise)
         d_router = K.copy_cols(K.wgrad(x, dl, None, 1)[0], e_n)   # pad columns dropped
         if atomic_combine:   # the router's share of dx joins the same accumulator
             K.dx_gemm_acc(dl.unsqueeze(0), router_w_padded, None, None, 1, None, 0, 1, dx)
@@ -642,7 +675,7 @@ def moe_block_bwd(
 def _(grad_out, grad_aux, x, logit_bias, w_in, w_out, w_sh_in, w_sh_out, xs, a1, logits, w_all,
       idx_all, sorted_ids, expert_ids, pad_offsets, counts_all, n_post_pad, inv_ids,
       router_w_padded, top_k, normalize, full_softmax, aux_coef, activation,
-      atomic_combine=False):
+      atomic_combine=False, noise=None):
     return (torch.empty_like(x), x.new_empty((x.shape[1], w_in.shape[0])), torch.empty_like(w_in),
             torch.empty_like(w_out),
             torch.empty_like(w_sh_in) if w_sh_in is not None else x.new_empty(0),
@@ -651,8 +684,9 @@ def _(grad_out, grad_aux, x, logit_bias, w_in, w_out, w_sh_in, w_sh_out, xs, a1,
 
 def _block_setup(ctx, inputs, output):
     (x, router_w, logit_bias, w_in, w_out, w_sh_in, w_sh_out, top_k, normalize, full_softmax,
-     aux_coef, activation, save_for_backward, residual, atomic_combine) = inputs
+     aux_coef, activation, save_for_backward, residual, atomic_combine, noise, global_aux) = inputs
     ctx.has_residual = residual is not None
+    ctx.has_noise = noise is not None
     ctx.atomic_combine = atomic_combine
     ctx.mark_non_differentiable(*output[2:])
     ctx.set_materialize_grads(False)
@@ -666,6 +700,8 @@ def _block_setup(ctx, inputs, output):
         saved += [w_sh_in, w_sh_out]
     if ctx.has_bias:
         saved.append(logit_bias)
+    if ctx.has_noise:
+        saved.append(noise)
     ctx.save_for_backward(*saved)
     ctx.n_experts = w_in.shape[0]
     ctx.router_dtype = router_w.dtype
@@ -678,23 +714,24 @@ def _block_backward(ctx, grad_out, grad_aux, *unused):
     kept = saved[3:15]
     rest = saved[15:]
     w_sh_in, w_sh_out = (rest[0], rest[1]) if ctx.has_shared else (None, None)
+    noise = rest.pop() if ctx.has_noise else None
     bias = rest[-1] if ctx.has_bias else None
     if grad_out is None:
         grad_out = torch.zeros_like(x)
     dx, d_router, dw_in, dw_out, dsi, dso = moe_block_bwd(
         grad_out, grad_aux, x, bias, w_in, w_out, w_sh_in, w_sh_out, *kept, *ctx.args,
-        ctx.atomic_combine)
+        ctx.atomic_combine, noise)
     d_router = d_router.to(ctx.router_dtype)
     return (dx, d_router, None, dw_in, dw_out, dsi if ctx.has_shared else None,
             dso if ctx.has_shared else None, None, None, None, None, None, None,
-            grad_out if ctx.has_residual else None, None)
+            grad_out if ctx.has_residual else None, None, None, None)
 
 
 moe_block.register_autograd(_block_backward, setup_context=_block_setup)
 
 
 def fused_moe_block(x, router, w_in, w_out, w_sh_in, w_sh_out, activation, full_softmax,
-                    combine: Optional[str] = None):
+                    combine: Optional[str] = None, noise: Optional[torch.Tensor] = None):
     """(out, aux_loss fp32, counts int32 [E]) for a TopKRouter-like `router` (attributes W,
     logit_bias, top_k, normalize_weights, aux_loss_coef) -- the path MoEBlock.forward takes
     whenever no exploration noise has to be added to the logits."""
@@ -708,8 +745,14 @@ def fused_moe_block(x, router, w_in, w_out, w_sh_in, w_sh_out, activation, full_
     res = moe_block(x, cast(router.W), bias, cast(w_in), cast(w_out), cast(w_sh_in),
                     cast(w_sh_out), router.top_k, bool(router.normalize_weights),
                     bool(full_softmax), float(router.aux_loss_coef), activation, save, None,
-                    _atomic(combine))
-    return res[0], res[1], res[2]
+                    _atomic(combine), noise, _aux_reduce is not None)
+    aux = res[1]
+    if full_softmax and _aux_reduce is not None:
+        # this rank's share of the global loss: T_local / T_global, with T_global read off the
+        # reduced counts (sum = T_global * top_k) on the device
+        total = res[11][: w_in.shape[0]].sum().clamp(min=1).to(torch.float32)
+        aux = aux * (float(x.shape[0] * router.top_k) / total)
+    return res[0], aux, res[2]
 
 
 def pad_router_weight(router_w: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:

@@ -59,3 +59,23 @@ def all_reduce_counts(counts: torch.Tensor, group=None) -> torch.Tensor:
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(total, op=dist.ReduceOp.SUM, group=group)
     return total
+
+
+def enable_global_balance_loss(group=None) -> None:
+    """From now on the kernel path's balance loss is that of the WHOLE batch over `group`'s ranks
+    (the routing counts are all-reduced inside the block's op, 4 bytes per expert): every rank's
+    `aux_loss` is its share, the shares sum to the global loss, and so do the gradients once the
+    ranks' gradients are summed. Without this call (the default) each rank's loss is that of its
+    own shard, which is what the reference computes in every process."""
+    from . import moe_kernel as MK
+
+    def reduce(counts: torch.Tensor) -> None:
+        if dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(counts, op=dist.ReduceOp.SUM, group=group)
+
+    MK.set_aux_reduce(reduce)
+
+
+def disable_global_balance_loss() -> None:
+    from . import moe_kernel as MK
+    MK.set_aux_reduce(None)

@@ -81,8 +81,9 @@ class MoEFFNSublayer(nn.Module):
 
     def _fused_ok(self, x: torch.Tensor) -> bool:
         f = self.ffn
-        # (the whole-block op has no bias operands and draws no exploration noise)
-        return f._whole_block_ok(x) and f.d_model % 8 == 0 and f.d_model <= 2048
+        # (the whole-block op has no bias operands; exploration noise goes through the block itself)
+        return (f._whole_block_ok(x) and not (f.training and f.router.noise_std)
+                and f.d_model % 8 == 0 and f.d_model <= 2048)
 
     def forward(self, x: torch.Tensor):
         shape = x.shape

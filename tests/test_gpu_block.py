@@ -563,3 +563,81 @@ def test_graphed_block_replays_the_blocks_training_step():
         assert g(x).shape == x.shape
     from nanospeaker_b200 import kernels
     kernels.check_status("cuda")
+
+
+def test_exploration_noise_runs_inside_the_whole_block_op():
+    """Training with router.noise_std > 0 (the opening stretch of the reference's run,
+    src/model/router.py:76-77, src/train/train.py:298-300) stays on the whole-block op: the noise is
+    drawn in torch and handed to the op, which adds it to the logits in the router kernel and again
+    in the router's backward. Against the oracle routed on identical noisy logits: output, balance
+    loss, counts and all six gradients; a second call draws fresh noise."""
+    T = 2048
+    x, m, o = _model_shape_pair(T, train=True, seed=8)
+    m.router.noise_std = 0.5
+    xc = x.cuda().requires_grad_(True)
+    torch.manual_seed(77)
+    out = m(xc)
+    assert m._whole_block_ok(xc)
+    (out.float().square().mean() + m.aux_loss).backward()
+    torch.manual_seed(77)                     # the same draw the module made
+    noise = torch.randn(T, 76, device="cuda", dtype=torch.float32) * 0.5
+    o.logits_override = (_block_logits(m, xc.detach()) + noise).cpu()
+    xo = x.clone().requires_grad_(True)
+    ref = o(xo)
+    (ref.float().square().mean() + o.aux_loss).backward()
+    assert torch.equal(m.expert_counts.cpu().long(), o.expert_counts)
+    noiseless = O.canonical_topk(_block_logits(m, xc.detach()).cpu(), 6)
+    assert not torch.equal(torch.bincount(noiseless.reshape(-1), minlength=76), o.expert_counts)
+    assert rel_l2(out.detach().cpu(), ref.detach()) < TOL
+    assert abs(float(m.aux_loss) - float(o.aux_loss)) < 1e-4
+    for name, a, b in [("dx", xc.grad, xo.grad), ("dW_in", m.W_in.grad, o.W_in.grad),
+                       ("dW_out", m.W_out.grad, o.W_out.grad),
+                       ("dW_sh_in", m.W_sh_in.grad, o.W_sh_in.grad),
+                       ("dW_sh_out", m.W_sh_out.grad, o.W_sh_out.grad),
+                       ("d_router", m.router.W.grad, o.router_W.grad)]:
+        assert rel_l2(a.cpu(), b) < (2e-2 if name == "d_router" else TOL), name
+    with torch.no_grad():
+        counts = m.expert_counts.clone()
+        m(xc)
+        assert not torch.equal(counts, m.expert_counts)      # fresh noise, other routing
+        m.eval()                                             # no noise outside training
+        a, b = m(xc), m(xc)
+        assert rel_l2(a, b) < ATOMIC_TOL
+    from nanospeaker_b200 import kernels
+    kernels.check_status("cuda")
+
+
+def test_global_balance_loss_shares_sum_to_the_loss_of_the_whole_batch():
+    """Tokens sharded over two ranks (run one after the other on this GPU; the count exchange is a
+    hook that adds the other rank's counts): each rank's aux_loss is its share of the balance loss
+    of the concatenated batch, and its gradient with respect to the rank's own tokens is the
+    oracle's gradient of that global loss."""
+    from nanospeaker_b200 import moe_kernel as MK
+    T = 1024
+    x, m, o = _model_shape_pair(2 * T, train=True, seed=12)
+    shards = [x[:T].cuda(), x[T:].cuda()]
+    try:
+        local = []
+        for xs in shards:                       # pass 1: every rank's own counts
+            with torch.no_grad():
+                m(xs)
+            local.append(m.expert_counts.clone())
+        shares, grads = [], []
+        for r, xs in enumerate(shards):         # pass 2: with the exchange
+            other = local[1 - r]
+            MK.set_aux_reduce(lambda c, other=other: c.add_(other.to(c.dtype)))
+            xr = xs.clone().requires_grad_(True)
+            m(xr)
+            shares.append(m.aux_loss.detach().float().cpu())
+            m.aux_loss.backward()
+            grads.append(xr.grad.float().cpu())
+    finally:
+        MK.set_aux_reduce(None)
+    logits = torch.cat([_block_logits(m, s) for s in shards]).cpu()
+    o.logits_override = logits
+    xo = x.clone().requires_grad_(True)
+    o(xo)
+    o.aux_loss.backward()
+    assert torch.equal((local[0] + local[1]).cpu().long(), o.expert_counts)
+    assert abs(float(shares[0] + shares[1]) - float(o.aux_loss)) < 1e-5
+    assert rel_l2(torch.cat(grads), xo.grad.float()) < 2e-2
