@@ -995,6 +995,42 @@ def run_side_workload(args):
         return e0.elapsed_time(e1) / steps
 
     g = torch.Generator().manual_seed(100)
+    if args.workload == "muon":
+        # Muon's Newton-Schulz on the block's stacked weight gradients (the next consumer of dW_in
+        # / dW_out, src/train/optim.py:27-40): 78 x [576, 256] and 78 x [128, 576], 5 iterations
+        # each, replayed from a CUDA graph; next to it the same iteration as torch batched matmuls.
+        from nanospeaker_b200.muon import _ns_torch, newton_schulz5
+        E = N_EXPERTS + N_SHARED
+        grads = [(torch.randn(E, D_MODEL, 2 * D_HIDDEN, generator=g) * 0.02).bfloat16().to(dev),
+                 (torch.randn(E, D_HIDDEN, D_MODEL, generator=g) * 0.02).bfloat16().to(dev)]
+
+        def graphed(fn):
+            for _ in range(2):
+                [fn(t) for t in grads]
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                outs = [fn(t) for t in grads]
+            return gr, outs
+        l0 = K.LAUNCHES
+        g_k, _ = graphed(lambda t: newton_schulz5(t))
+        launches = (K.LAUNCHES - l0) // 3
+        g_t, _ = graphed(lambda t: _ns_torch(t, 5, 1e-7))
+        ms = time_loop(lambda i: g_k.replay())
+        ms_torch = time_loop(lambda i: g_t.replay())
+        K.check_status(dev)
+        flop = 0
+        for r_, c_ in ((2 * D_HIDDEN, D_MODEL), (D_HIDDEN, D_MODEL)):     # small side, large side
+            flop += E * 5 * (2 * r_ * r_ * c_ * 2 + 2 * r_ ** 3)
+        print(json.dumps({
+            "metric": "Muon Newton-Schulz on the block's stacked expert gradients (5 iterations)",
+            "value": ms, "unit": "ms", "higher_is_better": False, "n_gpus": 1, "steps": steps,
+            "warmup": warmup, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{E} x [576, 256] and {E} x [128, 576] bf16 gradients, "
+                                   "X <- aX + (bA + cAA)X five times each, CUDA graph replay"},
+            "gpu_launches_per_step": launches, "tflops": flop / (ms * 1e-3) / 1e12,
+            "torch_bmm_ms": ms_torch}), flush=True)
+        return
     if args.workload == "sublayer":
         from nanospeaker_b200.sublayer import MoEFFNSublayer
         T = TOKENS
@@ -1098,7 +1134,7 @@ def main():
     ap.add_argument("--ep-tokens", type=int, default=16384,
                     help="ep-loopback workload: tokens per virtual rank")
     ap.add_argument("--workload", default="train",
-                    choices=["train", "decode", "prefill", "sublayer", "ep", "ep-loopback"],
+                    choices=["train", "decode", "prefill", "sublayer", "muon", "ep", "ep-loopback"],
                     help="train = the headline (forward + backward, T=16384); decode / prefill = "
                          "the forward-only workloads of the block's other callers; sublayer = "
                          "x + ffn(rmsnorm(x)) forward + backward at T=16384, fused node against "

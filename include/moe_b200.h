@@ -209,6 +209,20 @@ int moe_b200_segment_colsum(const void* buf, int64_t rows, int32_t width,
                             const void* alt, int64_t alt_rows, int32_t first_alt_group,
                             float* out, void* stream);
 
+/* Two element-wise helpers of the batched Newton-Schulz iteration that Muon runs on the stacked
+ * expert weights (zeropower_via_newtonschulz5, src/train/optim.py:27-40); its matrix products run on
+ * the grouped GEMM entry points above with the fixed schedule.
+ *   moe_b200_group_sumsq: sumsq[g] += sum of squares of x[g, :] (x [groups, per_group] bf16, per_group
+ *     a multiple of 8; sumsq fp32 [groups], zeroed by the caller) -- the Frobenius norms of
+ *     `X / (X.norm(dim=(-2, -1)) + eps)`.
+ *   moe_b200_axpby: out = alpha * s_g * x + beta * y in fp32, rounded once to bf16, with
+ *     s_g = 1 / (sqrt(sumsq[g]) + eps) when sumsq is given and 1 otherwise; y may be NULL. Covers the
+ *     normalisation, `b * A + c * (A @ A)` and `a * X + (...) @ X`. */
+int moe_b200_group_sumsq(const void* x, int32_t groups, int64_t per_group, float* sumsq,
+                         void* stream);
+int moe_b200_axpby(const void* x, const void* y, void* out, int32_t groups, int64_t per_group,
+                   float alpha, float beta, const float* sumsq, float eps, void* stream);
+
 /* dst[r, c] = c < cols ? src[r, c] : 0 for 0 <= c < dst_ld; 16-bit elements, row strides src_ld /
  * dst_ld elements. Pads the router weight [d_model, n_experts] (src/model/router.py:51) to the
  * 64-column multiple the GEMM kernels' tensor maps need, and strips the pad columns from its

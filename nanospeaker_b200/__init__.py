@@ -8,12 +8,13 @@ from .moe_kernel import (ALIGN_M, KERNEL_ACTIVATIONS, KERNEL_DTYPES, fused_moe_f
                          shapes_supported)
 from .expert_parallel import ep_block_forward, expert_partition
 from .graphed import GraphedMoEBlock
+from .muon import Muon, newton_schulz5
 from .router import TopKRouter
 from .sublayer import MoEFFNSublayer
 from .utils import ACTIVATIONS, resolve_activation
 
 __all__ = [
-    "MoEBlock", "GraphedMoEBlock", "MoEFFNSublayer", "TopKRouter", "AUTO_CAPACITY", "ALIGN_M", "KERNEL_ACTIVATIONS", "KERNEL_DTYPES",
+    "MoEBlock", "GraphedMoEBlock", "Muon", "newton_schulz5", "MoEFFNSublayer", "TopKRouter", "AUTO_CAPACITY", "ALIGN_M", "KERNEL_ACTIVATIONS", "KERNEL_DTYPES",
     "fused_moe_forward", "kernel_supported", "shapes_supported", "moe_dispatch", "moe_experts",
     "router_topk", "ep_block_forward", "expert_partition", "glu_hidden_dim", "make_glu", "ACTIVATIONS", "resolve_activation",
 ]

@@ -55,6 +55,11 @@ SIGNATURES = {
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_i32, _c_vp, _c_vp, _c_i64, _c_vp, _c_i64,
          _c_i32, _c_vp, _c_vp]),
+    "moe_b200_group_sumsq": (ctypes.c_int, [_c_vp, _c_i32, _c_i64, _c_vp, _c_vp]),
+    "moe_b200_axpby": (
+        ctypes.c_int,
+        [_c_vp, _c_vp, _c_vp, _c_i32, _c_i64, ctypes.c_float, ctypes.c_float, _c_vp,
+         ctypes.c_float, _c_vp]),
     "moe_b200_rmsnorm": (
         ctypes.c_int, [_c_vp, _c_vp, _c_i64, _c_i32, ctypes.c_float, _c_vp, _c_vp, _c_vp]),
     "moe_b200_rmsnorm_bwd": (

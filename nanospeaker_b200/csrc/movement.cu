@@ -217,6 +217,66 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// sumsq[g] += sum of squares of group g's elements (fp32; the caller zeroes it). x [groups, per_group]
+// bf16, per_group a multiple of 8. One block-level reduction and one atomic per block.
+__global__ void __launch_bounds__(256)
+    group_sumsq_kernel(const uint4* __restrict__ x, int64_t pieces_per_group,
+                       float* __restrict__ sumsq) {
+  pdl_trigger();
+  pdl_wait();
+  const int g = blockIdx.y;
+  const uint4* base = x + int64_t(g) * pieces_per_group;
+  float acc = 0.f;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < pieces_per_group;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    const uint4 v = ld_stream(base + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]));
+      acc += f.x * f.x + f.y * f.y;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  __shared__ float part[8];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += part[i];
+    atomicAdd(sumsq + g, t);
+  }
+}
+
+// out = alpha * s_g * x + beta * y, element-wise in fp32, one rounding to bf16. s_g = 1 / (sqrt(
+// sumsq[g]) + eps) when sumsq is given (the Frobenius normalisation of group g), else 1; y may be null.
+__global__ void __launch_bounds__(256)
+    axpby_kernel(const uint4* __restrict__ x, const uint4* __restrict__ y, uint4* __restrict__ out,
+                 int64_t pieces_per_group, int64_t total, float alpha, float beta,
+                 const float* __restrict__ sumsq, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    float a = alpha;
+    if (sumsq != nullptr) a *= 1.f / (sqrtf(__ldg(sumsq + i / pieces_per_group)) + eps);
+    const uint4 vx = ld_stream(x + i);
+    uint4 vy = make_uint4(0u, 0u, 0u, 0u);
+    if (y != nullptr) vy = ld_stream(y + i);
+    const uint32_t wx[4] = {vx.x, vx.y, vx.z, vx.w}, wy[4] = {vy.x, vy.y, vy.z, vy.w};
+    uint32_t wo[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 fx = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wx[k]));
+      const float2 fy = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wy[k]));
+      const __nv_bfloat162 h = __floats2bfloat162_rn(a * fx.x + beta * fy.x, a * fx.y + beta * fy.y);
+      wo[k] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    out[i] = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+  }
+}
+
 // dst[r, c] = c < cols ? src[r, c] : 0 for c < dst_ld: pads a matrix's rows to a TMA-friendly
 // stride (the router weight [D, E] -> [D, ld]) or drops the pad columns again.
 __global__ void __launch_bounds__(256)
@@ -320,6 +380,34 @@ int moe_b200_segment_colsum(const void* buf, int64_t rows, int32_t width,
              expert_ids, n_post_pad, pad_offsets, sorted_ids,
              static_cast<const __nv_bfloat16*>(pair_w), int32_t(n_pairs),
              static_cast<const uint4*>(alt), alt_rows, first_alt_group, out);
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+int moe_b200_group_sumsq(const void* x, int32_t groups, int64_t per_group, float* sumsq,
+                         void* stream) {
+  if (groups < 1 || groups > 65535 || per_group < 8 || per_group % 8 != 0) return MOE_B200_ERR_SHAPE;
+  if (!x || !sumsq) return MOE_B200_ERR_NULL;
+  if (!aligned16(x)) return MOE_B200_ERR_ALIGN;
+  const int64_t ppg = per_group / 8;
+  int64_t bx = (ppg + 255) / 256;
+  const int64_t cap = (148 * 8 + groups - 1) / groups;
+  if (bx > cap) bx = cap;
+  launch_pdl(group_sumsq_kernel, dim3(unsigned(bx), unsigned(groups)), dim3(256), 0,
+             static_cast<cudaStream_t>(stream), static_cast<const uint4*>(x), ppg, sumsq);
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+int moe_b200_axpby(const void* x, const void* y, void* out, int32_t groups, int64_t per_group,
+                   float alpha, float beta, const float* sumsq, float eps, void* stream) {
+  if (groups < 1 || per_group < 8 || per_group % 8 != 0) return MOE_B200_ERR_SHAPE;
+  if (!x || !out) return MOE_B200_ERR_NULL;
+  if (!aligned16(x) || !aligned16(y) || !aligned16(out)) return MOE_B200_ERR_ALIGN;
+  const int64_t ppg = per_group / 8, total = ppg * groups;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  launch_pdl(axpby_kernel, dim3(unsigned(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+             static_cast<const uint4*>(x), static_cast<const uint4*>(y), static_cast<uint4*>(out),
+             ppg, total, alpha, beta, sumsq, eps);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 

@@ -261,6 +261,30 @@ def segment_colsum(buf, expert_ids, n_post_pad, n_groups: int, sorted_ids=None, 
     return out
 
 
+def group_sumsq(x: torch.Tensor) -> torch.Tensor:
+    """fp32 [G]: sum of squares of every x[g] (x [G, ...] bf16, contiguous)."""
+    _need_cuda(x)
+    g = x.shape[0]
+    out = torch.zeros(g, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().moe_b200_group_sumsq(x.data_ptr(), g, x[0].numel(), out.data_ptr(),
+                                                _stream(x)), "moe_b200_group_sumsq")
+    _count(1)
+    return out
+
+
+def axpby(x: torch.Tensor, alpha: float, y=None, beta: float = 0.0, sumsq=None, eps: float = 0.0,
+          out=None) -> torch.Tensor:
+    """alpha * s_g * x + beta * y (fp32 arithmetic, bf16 result), s_g = 1 / (sqrt(sumsq[g]) + eps)
+    per leading-dim group when sumsq is given."""
+    _need_cuda(x, y)
+    out = torch.empty_like(x) if out is None else out
+    _lib.check(_lib.load().moe_b200_axpby(
+        x.data_ptr(), _lib.ptr(y), out.data_ptr(), x.shape[0], x[0].numel(), float(alpha),
+        float(beta), _lib.ptr(sumsq), float(eps), _stream(x)), "moe_b200_axpby")
+    _count(1)
+    return out
+
+
 def _stack(n_fixed: int, rows: int, width: int, like: torch.Tensor) -> torch.Tensor:
     shape = (rows, width) if n_fixed == 0 else (n_fixed, rows, width)
     return torch.empty(shape, dtype=like.dtype, device=like.device)

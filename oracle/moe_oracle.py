@@ -408,3 +408,51 @@ def ep_plan(cnt_all, bounds, rank: int, cap_tiles: int):
                  // ALIGN_M] = e - lo
     return (owner_of, (start + before).astype(np.int32), own_offs, tot[lo:hi].astype(np.int32),
             int(live), own_eids)
+
+
+# ------------------------------------------------------------------- Muon's Newton-Schulz
+def newton_schulz5(G: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.Tensor:
+    """zeropower_via_newtonschulz5 (src/train/optim.py:27-40) restated: the quintic Newton-Schulz
+    iteration X <- a X + (b A + c A A) X with A = X X^T on X = G / (|G|_F + eps), in bf16, the
+    smaller dimension leading (tall matrices are transposed on the way in and out). Batched over
+    leading dimensions."""
+    a, b, c = 3.4445, -4.7750, 2.0315
+    X = G.to(torch.bfloat16)
+    tall = X.shape[-2] > X.shape[-1]
+    if tall:
+        X = X.transpose(-2, -1)
+    X = X / (X.norm(dim=(-2, -1), keepdim=True) + eps)
+    for _ in range(steps):
+        A = X @ X.transpose(-2, -1)
+        X = a * X + (b * A + c * (A @ A)) @ X
+    return X.transpose(-2, -1) if tall else X
+
+
+def muon_step(p, grad, buf, lr=0.02, momentum=0.95, weight_decay=0.1, ns_steps=5):
+    """One Muon update of parameter p in place (src/train/optim.py:75-100): bf16 momentum buffer
+    `buf` lerped towards the gradient, Nesterov direction orthogonalised, aspect-ratio scale,
+    decoupled weight decay. Returns the applied delta."""
+    g = grad.to(buf.dtype)
+    buf.lerp_(g, 1 - momentum)
+    update = newton_schulz5(g.lerp(buf, momentum), ns_steps)
+    scale = max(1.0, p.shape[-2] / p.shape[-1]) ** 0.5
+    delta = update.to(p.dtype) * (-lr * scale)
+    p.mul_(1 - lr * weight_decay)
+    p.add_(delta)
+    return delta
+
+
+MUON_SHAPES = (("in", (1, 576, 256)), ("out", (1, 128, 576)))
+
+
+def seeded_muon_inputs(seed=21):
+    """The inputs of the Muon golden, re-drawn from the seed: per shape a gradient for the bare
+    Newton-Schulz call (g_*), a weight (w_*) and two optimizer-step gradients (grad_*_0/1)."""
+    gen = torch.Generator().manual_seed(seed)
+    out = {}
+    for tag, shape in MUON_SHAPES:
+        out[f"g_{tag}"] = (torch.randn(*shape, generator=gen) * 0.02).bfloat16()
+        out[f"w_{tag}"] = (torch.randn(*shape, generator=gen) * 0.05).bfloat16()
+        for step in range(2):
+            out[f"grad_{tag}_{step}"] = (torch.randn(*shape, generator=gen) * 0.02).bfloat16()
+    return out

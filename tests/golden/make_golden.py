@@ -1,7 +1,7 @@
 """Generate the golden vectors in this directory by running the UNMODIFIED reference.
 
 Usage (needs a checkout of Osmansiddiquer/nanospeaker):
-    python tests/golden/make_golden.py /path/to/nanospeaker [--sublayer-only | --bias-only | --real-only]
+    python tests/golden/make_golden.py /path/to/nanospeaker [--sublayer-only | --bias-only | --real-only | --muon-only]
 
 Each .npz holds the inputs and everything the reference's pure-PyTorch MoE path
 (MoEBlock(..., fused=False, kernel=False, capacity_factor=None) on CPU) computes from them:
@@ -210,6 +210,33 @@ def real_shape_case(MoEBlock, name, *, tokens, seed):
     print(name, tuple(out.shape))
 
 
+MUON_STRIDE = 7
+
+
+def muon_case(name):
+    """Muon's Newton-Schulz and two optimizer steps of the reference (src/train/optim.py) on
+    gradients shaped like one expert of the block's stacked weights: W_in-like [1, 576, 256] (tall:
+    taken transposed) and W_out-like [1, 128, 576] (wide). Inputs come from
+    oracle.moe_oracle.seeded_muon_inputs(seed); stored
+    are the orthogonalised gradients and every MUON_STRIDE-th element of the weights after the steps."""
+    from src.train.optim import Muon, zeropower_via_newtonschulz5
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from oracle.moe_oracle import MUON_SHAPES, seeded_muon_inputs
+    t = seeded_muon_inputs()
+    s = {"fingerprint": np.array([int(v.view(torch.int16).long().sum()) for v in t.values()],
+                                 dtype=np.int64)}
+    for tag, _ in MUON_SHAPES:
+        put(s, f"ns_{tag}", zeropower_via_newtonschulz5(t[f"g_{tag}"]))
+        w = torch.nn.Parameter(t[f"w_{tag}"].clone())
+        opt = Muon([w], lr=0.02, momentum=0.95, weight_decay=0.1, ns_steps=5)
+        for step in range(2):
+            w.grad = t[f"grad_{tag}_{step}"].clone()
+            opt.step()
+        put(s, f"w_{tag}_after", w.reshape(-1)[::MUON_STRIDE])
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **s)
+    print(name, sorted(s))
+
+
 def routing_case(MoEBlock, name, *, tokens, n_experts, top_k, seed, bf16_logits):
     """Routing only at nanoSpeaker's width: logits -> torch.topk -> stable-sort plan."""
     torch.manual_seed(seed)
@@ -234,6 +261,9 @@ def main():
     from src.model.moe import MoEBlock  # the reference, unmodified
     from src.model.ln import RMSNorm
 
+    if "--muon-only" in sys.argv:
+        muon_case("muon_newton_schulz")
+        return
     if "--real-only" in sys.argv:
         real_shape_case(MoEBlock, "block_real_shape_bf16_train", tokens=256, seed=27)
         return
@@ -261,6 +291,7 @@ def main():
     routing_case(MoEBlock, "routing_e76_k6_bf16", tokens=512, n_experts=76, top_k=6, seed=6,
                  bf16_logits=True)
     real_shape_case(MoEBlock, "block_real_shape_bf16_train", tokens=256, seed=27)
+    muon_case("muon_newton_schulz")
 
 
 if __name__ == "__main__":

@@ -252,3 +252,27 @@ def test_oracle_matches_the_reference_at_nanospeakers_real_shape():
         grad = getattr(o, key).grad
         assert torch.equal(grad.reshape(-1)[::stride], g[f"grad_{key}_strided"]), key
         assert torch.allclose(grad.float().flatten(1).norm(dim=1), g[f"grad_{key}_norms"])
+
+
+def _muon_golden():
+    g = load_golden("muon_newton_schulz")
+    t = O.seeded_muon_inputs()
+    fp = torch.tensor([int(v.view(torch.int16).long().sum()) for v in t.values()], dtype=torch.int64)
+    if not torch.equal(fp, g["fingerprint"]):
+        pytest.skip("this torch build draws other random numbers than the golden's generator")
+    return g, t
+
+
+def test_newton_schulz_and_muon_step_match_the_reference():
+    """oracle.newton_schulz5 / muon_step against the reference's zeropower_via_newtonschulz5 and two
+    steps of its Muon optimizer (golden from src/train/optim.py), bit for bit."""
+    g, t = _muon_golden()
+    for tag, _ in O.MUON_SHAPES:
+        assert torch.equal(O.newton_schulz5(t[f"g_{tag}"]), g[f"ns_{tag}"]), tag
+        w, buf = t[f"w_{tag}"].clone(), torch.zeros_like(t[f"w_{tag}"])
+        for step in range(2):
+            O.muon_step(w, t[f"grad_{tag}_{step}"], buf)
+        assert torch.equal(w.reshape(-1)[::7], g[f"w_{tag}_after"]), tag
+        # the orthogonal factor: singular values pulled towards 1
+        sv = torch.linalg.svdvals(g[f"ns_{tag}"][0].float())
+        assert 0.6 < float(sv.min()) and float(sv.max()) < 1.3
