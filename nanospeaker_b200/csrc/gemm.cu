@@ -13,6 +13,16 @@
 
 #include "../../include/moe_b200.h"
 
+// dHidden: ring stages / pre-activation buffers (32 KB / 64 KB each)
+#ifndef MOE_DH_STAGES
+#define MOE_DH_STAGES 4
+#endif
+#ifndef MOE_DH_AUX_BUFS
+#define MOE_DH_AUX_BUFS 1
+#endif
+#ifndef MOE_PAIR_WGRAD_STAGES
+#define MOE_PAIR_WGRAD_STAGES 6   // 32 KB per stage and CTA
+#endif
 #ifndef MOE_PAIR_UP_STAGES
 #define MOE_PAIR_UP_STAGES 6
 #endif
@@ -198,6 +208,43 @@ static int launch_wgrad_g(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   const cudaError_t err =
       launch_pdl(kern, dim3(grid), dim3(threads), size_t(smem), st, tmA, tmB, tmAlt, args, tiles_x,
                  tiles_y);
+  return err == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+// The weight gradient on CTA pairs (gemm_wgrad2.cuh): clusters of two, one per SM pair.
+template <int BN, int STAGES>
+static int launch_wgrad2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmAlt,
+                         const WgradArgs& args, int tiles_x, int tiles_y, int64_t max_items,
+                         cudaStream_t st) {
+  auto kern = wgrad_gemm2_kernel<BN, STAGES>;
+  constexpr int smem = Wgrad2Smem<BN, STAGES>::DYNAMIC;
+  static_assert(smem <= 232448, "shared memory of the pair weight gradient exceeds the CTA limit");
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  static int max_clusters = 0;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (attr_err != cudaSuccess) return;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(sm_count() / 2 * 2));
+    cfg.blockDim = dim3(WGRAD_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    attr_err = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
+  });
+  if (attr_err != cudaSuccess || max_clusters < 1) return MOE_B200_ERR_CUDA;
+  const int64_t units = max_items * ((tiles_x + 1) / 2) * tiles_y;
+  int64_t clusters = std::min<int64_t>(max_clusters, sm_count() / 2);
+  if (units < clusters) clusters = units;
+  const cudaError_t err =
+      launch_pdl_pairs(kern, dim3(unsigned(2 * clusters)), dim3(WGRAD_THREADS), size_t(smem), st,
+                       tmA, tmB, tmAlt, args, tiles_x, tiles_y);
   return err == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
@@ -443,7 +490,8 @@ int moe_b200_dhidden_glu_bwd(const void* douts, int64_t rows, int32_t d_model, c
   if (rc2 != MOE_B200_OK) return rc2;
   if (gather_top_k > 0)
     return launch_rows<128, 3, false, EPI_GLUBWD, true>(tmA, tmB, tmB2, tmAux, g, tiles, st);
-  return launch_rows<128, 3, false, EPI_GLUBWD>(tmA, tmB, tmB2, tmAux, g, tiles, st, &tmA2);
+  return launch_rows<128, MOE_DH_STAGES, false, EPI_GLUBWD, false, MOE_DH_AUX_BUFS>(
+      tmA, tmB, tmB2, tmAux, g, tiles, st, &tmA2);
 }
 
 int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,
@@ -670,7 +718,12 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   // rows == 0 still launches: every C[e] must be written (with zeros)
   const int64_t map_rows = rows > 0 ? rows : 1;
   // a gathered operand is token-major and copied with cp.async: it gets the other one's map
-  const int bn_boxes = n_dim % 256 == 0 ? 4 : 3;
+  // CTA pairs: plain operands, 256-column tiles, at least two 128-row tiles of C; each CTA of a
+  // pair loads half of the B tile, so B's map has 128-column boxes
+  static const bool no_pair_wgrad = getenv("MOE_NO_PAIR_WGRAD") != nullptr;
+  bool pairs = !no_pair_wgrad && gather_which == 0 && n_dim % 256 == 0 && m_dim > BM &&
+               m_dim % 64 == 0;
+  const int bn_boxes = n_dim % 256 == 0 ? (pairs ? 2 : 4) : 3;
   int32_t a_fused = 0, b_fused = 0;
   if (gather_which != 1 &&
       !map_rows_mnmajor(&tmA, a, a_grouped ? n_groups : 1, map_rows, m_dim, BM / 64, &a_fused))
@@ -691,6 +744,16 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
                           alt_which == 1 ? BM / 64 : bn_boxes, &alt_fused))
       return MOE_B200_ERR_TMA;
     if (alt_fused != (alt_which == 1 ? a_fused : b_fused)) return MOE_B200_ERR_TMA;
+  }
+  if (pairs && !(a_fused && b_fused)) {   // the pair kernel takes 4-D maps only: remake B's
+    pairs = false;
+    if (!map_rows_mnmajor(&tmB, b, b_grouped ? n_groups : 1, map_rows, n_dim, 4, &b_fused))
+      return MOE_B200_ERR_TMA;
+    if (alt && alt_which == 2) {
+      int32_t alt_fused = 0;
+      if (!map_rows_mnmajor(&tmAlt, alt, 1, alt_rows, n_dim, 4, &alt_fused) || alt_fused != b_fused)
+        return MOE_B200_ERR_TMA;
+    }
   }
   WgradArgs g{};
   g.alt_which = alt ? alt_which : 0;
@@ -727,7 +790,9 @@ int moe_b200_wgrad(const void* a, int32_t a_grouped, int32_t m_dim, const void* 
   int rc;
   if (n_dim % 256 == 0) {
     const unsigned ty = unsigned(n_dim / 256);
-    rc = launch_wgrad<256, 4>(tmA, tmB, tmAlt, g, int(tx), int(ty), items, st);
+    rc = pairs ? launch_wgrad2<256, MOE_PAIR_WGRAD_STAGES>(tmA, tmB, tmAlt, g, int(tx), int(ty),
+                                                           items, st)
+               : launch_wgrad<256, 4>(tmA, tmB, tmAlt, g, int(tx), int(ty), items, st);
     if (rc == MOE_B200_OK && may_split)
       launch_pdl(wgrad_reduce_kernel<256>, dim3(tx * ty * WGRAD_REDUCE_SPLIT, gy), dim3(256), 0, st,
                  g, int(tx), int(ty));

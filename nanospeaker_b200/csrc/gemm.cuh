@@ -220,3 +220,4 @@ __device__ __forceinline__ void issue_stage_mmas(uint32_t sA, uint32_t sB, uint3
 #include "gemm_rows.cuh"
 #include "gemm_rows2.cuh"
 #include "gemm_wgrad.cuh"
+#include "gemm_wgrad2.cuh"

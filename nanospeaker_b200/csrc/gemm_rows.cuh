@@ -52,7 +52,9 @@ struct RowsSmem {
                                                                : 0;
   static constexpr int AUX_OFFSET = STAGING_OFFSET + STAGING_BYTES;  // 1024-byte aligned
   static constexpr int AUX_TILE_BYTES = BM * 2 * BN * 2;             // [128 x 2 BN] bf16
-  static constexpr int BAR_OFFSET = AUX_OFFSET + (epi_loads_aux(EPI) ? 2 * AUX_TILE_BYTES : 0);
+  // (for the aux-loading epilogue OUT_BOXES is the number of pre-activation buffers, 1 or 2)
+  static constexpr int AUX_BUFS = OUT_BOXES >= 2 ? 2 : 1;
+  static constexpr int BAR_OFFSET = AUX_OFFSET + (epi_loads_aux(EPI) ? AUX_BUFS * AUX_TILE_BYTES : 0);
   // full, empty, tmem_full[2], tmem_empty[2], aux_full[2], aux_empty[2]
   static constexpr int N_BARS = 2 * STAGES + 8;
   static constexpr int MISC_OFFSET = BAR_OFFSET + 8 * N_BARS;      // tmem slot, abort flag
@@ -258,8 +260,8 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
       int j = 0;
       for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x, ++j) {
         const TileCoord tc = decode_tile(p, t, m_tiles, BN);
-        const int b = j & 1;
-        const uint32_t use = uint32_t(j) >> 1;
+        const int b = j % L::AUX_BUFS;
+        const uint32_t use = uint32_t(j) / L::AUX_BUFS;
         if (use > 0 && !mbar_wait(aempty_bar + b, (use - 1) & 1, p.status)) {
           *abort_flag = 1;
           atomicExch(p.status, ST_WAIT_TIMEOUT);
@@ -646,9 +648,10 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
         __nv_bfloat16* da1 = out_row;  // ld_out == 2 * BN
         __nv_bfloat16* hw = p.out2 + tc.z * p.out2_gstride + grow * BN;
         // this tile's pre-activations were brought in by the aux warp
-        if (!mbar_wait(afull_bar + b, (uint32_t(j) >> 1) & 1, p.status))
+        const int ab = j % L::AUX_BUFS;
+        if (!mbar_wait(afull_bar + ab, (uint32_t(j) / L::AUX_BUFS) & 1, p.status))
           atomicExch(p.status, ST_WAIT_TIMEOUT);
-        const uint32_t a1_tile = smem_u32(smem + L::AUX_OFFSET + b * L::AUX_TILE_BYTES);
+        const uint32_t a1_tile = smem_u32(smem + L::AUX_OFFSET + ab * L::AUX_TILE_BYTES);
         float part;
         switch (p.act) {
           case ACT_SILU: part = epilogue_glubwd<ACT_SILU, BN>(taddr, c_lo, c_hi, row_ok, w, a1_tile, row, da1, hw); break;
@@ -658,7 +661,7 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
           default: part = epilogue_glubwd<ACT_TANH, BN>(taddr, c_lo, c_hi, row_ok, w, a1_tile, row, da1, hw); break;
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(aempty_bar + b);  // this warp is done with the tile's buffer
+        if (lane == 0) mbar_arrive(aempty_bar + ab);  // this warp is done with the tile's buffer
         // <G, hidden> of a row is split over the two column halves: fold half 1 into half 0
         // Barrier 1 hands half 1's partials to half 0, barrier 2 hands the buffer back; each half
         // only ever waits for the other one's previous step.
