@@ -319,13 +319,15 @@ def build_stages(m, x):
             ("up_gemm+glu (gathered rows, inference)", TF, 2.0 * M * D * 2 * H, 0,
              lambda i: K.up_gemm(xr[i % 3], m.W_in, eids, npp, 0, 0, False, gather=gather,
                                  w_extra=m.W_sh_in)),
-            # the step's default: the down / dX GEMMs add their rows straight into the token-major
-            # result (bf16 atomics in L2); the accumulator is cleared by a fill first
-            ("down_gemm+scale+combine (atomic adds into out)", TF, 2.0 * M * H * D, 1,
-             lambda i: K.down_gemm_acc(hid[i % 3], m.W_out, eids, npp, 0, sids, tw, M, ka,
-                                       acc[i % 3], w_extra=m.W_sh_out)),
-            ("accumulator fill (out / dx zeroed before the atomic adds)", GE, T * D * 2, 2,
-             lambda i: acc[i % 3].zero_()),
+            # the step's default: the shared experts' rows (token-ordered, weight 1) are summed by a
+            # plain-store GEMM that gives the token-major result its first value; the routed
+            # experts' rows are then added to it in the down / dX GEMMs' epilogues (bf16 atomics in L2)
+            ("down_gemm shared experts (stores; first value of out)", TF, 2.0 * T * S * H * D, 1,
+             lambda i: K.down_gemm_sum(hid[i % 3], m.W_sh_out, offs[E:], T, out=acc[i % 3])),
+            ("down_gemm+scale+combine (routed rows, atomic adds into out)", TF,
+             2.0 * T * k * H * D, 1,
+             lambda i: K.down_gemm_acc(hid[i % 3], m.W_out, eids, offs[E:E + 1], 0, sids, tw, M, ka,
+                                       acc[i % 3])),
             # the store-then-reduce alternative (combine mode "store"): not part of the default step
             ("down_gemm+scale (stores per-pair rows)", TF, 2.0 * M * H * D, 0,
              lambda i: K.down_gemm(hid[i % 3], m.W_out, eids, npp, 0, sids, tw, M,
@@ -340,9 +342,11 @@ def build_stages(m, x):
             ("dhidden+glu_bwd (gathered rows)", TF, 2.0 * M * D * H, 0,
              lambda i: K.dhidden_glu_bwd(xr[i % 3], m.W_out, eids, npp, 0, sids, tw, M, a1, 0,
                                          True, gather_top_k=ka, w_extra=m.W_sh_out)),
-            ("dx_gemm+combine (atomic adds into dx)", TF, 2.0 * M * 2 * H * D, 1,
-             lambda i: K.dx_gemm_acc(da1[i % 3], m.W_in, eids, npp, 0, sids, M, ka, acc[i % 3],
-                                     w_extra=m.W_sh_in, pad_offsets=offs)),
+            ("dx_gemm shared experts (stores; first value of dx)", TF, 2.0 * T * S * 2 * H * D, 1,
+             lambda i: K.dx_gemm_sum(da1[i % 3], m.W_sh_in, offs[E:], T, out=acc[i % 3])),
+            ("dx_gemm+combine (routed rows, atomic adds into dx)", TF, 2.0 * T * k * 2 * H * D, 1,
+             lambda i: K.dx_gemm_acc(da1[i % 3], m.W_in, eids, offs[E:E + 1], 0, sids, M, ka,
+                                     acc[i % 3], pad_offsets=offs[:E + 1])),
             ("dx_gemm (stores per-pair rows)", TF, 2.0 * M * 2 * H * D, 0,
              lambda i: K.dx_gemm(da1[i % 3], m.W_in, eids, npp, 0, w_extra=m.W_sh_in)),
             ("wgrad_in (gemm + reduce)", TF, 2.0 * M * D * 2 * H, 1,
@@ -384,8 +388,10 @@ def gemm_stage_bytes(T, ld):
         "up_gemm+glu (gathered rows, inference)": T * D * 2 + w_in + M * H * 2,
         "down_gemm+scale (stores": M * H * 2 + w_out + M * D * 2,
         # atomic variants: no per-pair rows; the token-major result is read and written once in HBM
-        "down_gemm+scale+combine": M * H * 2 + w_out + 2 * T * D * 2,
-        "dx_gemm+combine": M * 2 * H * 2 + w_in + 2 * T * D * 2,
+        "down_gemm+scale+combine": T * k * H * 2 + N_EXPERTS * H * D * 2 + 2 * T * D * 2,
+        "dx_gemm+combine": T * k * 2 * H * 2 + N_EXPERTS * D * 2 * H * 2 + 2 * T * D * 2,
+        "down_gemm shared experts": T * S * H * 2 + S * H * D * 2 + T * D * 2,
+        "dx_gemm shared experts": T * S * 2 * H * 2 + S * D * 2 * H * 2 + T * D * 2,
         "dhidden+glu_bwd": M * D * 2 + M * 2 * H * 2 + w_out + M * 3 * H * 2 + M * 2,
         "dx_gemm (stores": M * 2 * H * 2 + w_in + M * D * 2,
         "wgrad_in (gemm + reduce)": M * D * 2 + M * 2 * H * 2 + w_in,

@@ -356,6 +356,23 @@ int moe_b200_dx_gemm_acc(const void* da1, int64_t rows, int32_t d_hidden, const 
                          int32_t top_k, void* acc, int64_t n_tokens, const int32_t* pad_offsets,
                          int32_t* status, void* stream);
 
+/* Group-summed row GEMMs with plain stores: out[t] = sum over g < n_sum of
+ *   hid[run_offsets[g] + t] @ w_out[g]            (moe_b200_down_gemm_sum, k_dim = d_hidden)
+ *   da1[run_offsets[g] + t] @ w_in[g]^T           (moe_b200_dx_gemm_sum)
+ * for t < n_tokens. run_offsets [n_sum] int32 on the device: where each group's token-ordered run
+ * starts in the slot-ordered buffer of `rows` rows (for the shared experts: pad_offsets + n_experts).
+ * They write the shared experts' share of the block's output (router weight 1) and of dX straight
+ * into the token-major accumulators, which then need no zero fill, and leave only the routed
+ * experts' rows to the atomic adds of moe_b200_down_gemm_acc / moe_b200_dx_gemm_acc (called with
+ * n_post_pad = the start of the first shared run, n_extra = 0). The shared branch of the reference
+ * is src/model/moe.py:310-329, added at :414-416. */
+int moe_b200_down_gemm_sum(const void* hid, int64_t rows, int32_t k_dim, const void* w_out,
+                           int32_t n_sum, int32_t d_model, const int32_t* run_offsets,
+                           int64_t n_tokens, void* out, int32_t* status, void* stream);
+int moe_b200_dx_gemm_sum(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,
+                         int32_t n_sum, int32_t d_model, const int32_t* run_offsets,
+                         int64_t n_tokens, void* out, int32_t* status, void* stream);
+
 /* Bytes of fp32 scratch moe_b200_wgrad needs for its partial tiles (contents arbitrary).
  * routed != 0: the pad_offsets schedule over `rows` = l_cap rows. ks_rows as for moe_b200_wgrad. */
 int moe_b200_wgrad_scratch_bytes(int32_t m_dim, int32_t n_dim, int64_t rows, int32_t n_groups,

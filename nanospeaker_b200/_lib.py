@@ -78,6 +78,12 @@ SIGNATURES = {
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,
          _c_vp, _c_i64, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp]),
+    "moe_b200_down_gemm_sum": (
+        ctypes.c_int,
+        [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp]),
+    "moe_b200_dx_gemm_sum": (
+        ctypes.c_int,
+        [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_i64, _c_vp, _c_vp, _c_vp]),
     "moe_b200_dx_gemm_acc": (
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_i32, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32, _c_vp,

@@ -525,6 +525,69 @@ int moe_b200_dx_gemm(const void* da1, int64_t rows, int32_t d_hidden, const void
       tmA, tmB, tmB2, tmOut, g, max_tiles(rows, g.n_chunks, n_fixed_groups), static_cast<cudaStream_t>(stream));
 }
 
+// The group-summed row GEMMs: out[t] = sum_g A[run_offsets[g] + t] @ B_g, plain stores. They give
+// the token-major accumulators of the atomic combine their initial value -- the shared experts'
+// contribution, whose rows are in token order -- so that no fill pass is needed and only the routed
+// experts' rows go through the L2's atomic units.
+static int sum_checks(const void* a, const void* w, const void* out, const int32_t* run_offsets,
+                      int64_t rows, int32_t n_sum, int64_t n_tokens, const int32_t* status) {
+  if (rows < 1 || n_sum < 1 || n_tokens < 1 || rows > (int64_t(1) << 30) || n_tokens > rows)
+    return MOE_B200_ERR_SHAPE;
+  if (!a || !w || !out || !run_offsets || !status) return MOE_B200_ERR_NULL;
+  if (!aligned16(a) || !aligned16(w) || !aligned16(out)) return MOE_B200_ERR_ALIGN;
+  return MOE_B200_OK;
+}
+
+int moe_b200_down_gemm_sum(const void* hid, int64_t rows, int32_t k_dim, const void* w_out,
+                           int32_t n_sum, int32_t d_model, const int32_t* run_offsets,
+                           int64_t n_tokens, void* out, int32_t* status, void* stream) {
+  const int rc = sum_checks(hid, w_out, out, run_offsets, rows, n_sum, n_tokens, status);
+  if (rc != MOE_B200_OK) return rc;
+  if (k_dim % 8 != 0 || k_dim < 64 || d_model % 32 != 0) return MOE_B200_ERR_UNSUPPORTED;
+  CUtensorMap tmA, tmB, tmOut;
+  int32_t fused = 0;
+  if (!map_rows_kmajor(&tmA, hid, 1, rows, k_dim) ||
+      !map_weight_mnmajor(&tmB, w_out, n_sum, k_dim, d_model, 3, &fused) ||
+      !map_rows_kmajor(&tmOut, out, 1, n_tokens, d_model))
+    return MOE_B200_ERR_TMA;
+  RowsArgs g = base_args(nullptr, nullptr, 1, n_tokens, status);
+  g.sum_groups = n_sum;
+  g.sum_offsets = run_offsets;
+  g.num_k = (k_dim + BK - 1) / BK;
+  g.n_dim = d_model;
+  g.n_chunks = (d_model + 191) / 192;
+  g.b_fused = fused;
+  g.out = static_cast<__nv_bfloat16*>(out);
+  g.ld_out = d_model;
+  g.n_groups_b1 = INT32_MAX;
+  return launch_rows<192, 4, true, EPI_SCALE, false, 4>(
+      tmA, tmB, tmB, tmOut, g, max_tiles(n_tokens, g.n_chunks, 1), static_cast<cudaStream_t>(stream));
+}
+
+int moe_b200_dx_gemm_sum(const void* da1, int64_t rows, int32_t d_hidden, const void* w_in,
+                         int32_t n_sum, int32_t d_model, const int32_t* run_offsets,
+                         int64_t n_tokens, void* out, int32_t* status, void* stream) {
+  const int rc = sum_checks(da1, w_in, out, run_offsets, rows, n_sum, n_tokens, status);
+  if (rc != MOE_B200_OK) return rc;
+  if (d_hidden % 4 != 0 || d_hidden < 32 || d_model % 32 != 0) return MOE_B200_ERR_UNSUPPORTED;
+  CUtensorMap tmA, tmB, tmOut;
+  if (!map_rows_kmajor(&tmA, da1, 1, rows, 2 * d_hidden) ||
+      !map_weight_kmajor(&tmB, w_in, n_sum, d_model, 2 * d_hidden, 192) ||
+      !map_rows_kmajor(&tmOut, out, 1, n_tokens, d_model))
+    return MOE_B200_ERR_TMA;
+  RowsArgs g = base_args(nullptr, nullptr, 1, n_tokens, status);
+  g.sum_groups = n_sum;
+  g.sum_offsets = run_offsets;
+  g.num_k = (2 * d_hidden + BK - 1) / BK;
+  g.n_dim = d_model;
+  g.n_chunks = (d_model + 191) / 192;
+  g.out = static_cast<__nv_bfloat16*>(out);
+  g.ld_out = d_model;
+  g.n_groups_b1 = INT32_MAX;
+  return launch_rows<192, 4, false, EPI_RAW, false, 3>(
+      tmA, tmB, tmB, tmOut, g, max_tiles(n_tokens, g.n_chunks, 1), static_cast<cudaStream_t>(stream));
+}
+
 // Ring stages / staging buffers of the two accumulating row GEMMs (shared memory per CTA: stages x
 // 40 KB + buffers x 50 KB at 192-column tiles).
 #ifndef MOE_RED_DOWN_STAGES

@@ -64,6 +64,13 @@ struct RowsArgs {
                                // token-major second A map (row = slot - a2_offsets[group]);
                                // INT32_MAX = every group reads the slot-ordered buffer
   const int32_t* a2_offsets;   // [G + 1] run starts (pad_offsets), used with a2_first_group
+  // group-summed fixed schedule (sum_groups > 0, n_fixed_groups == 1): ONE output row block per 128
+  // token rows, accumulated over sum_groups groups -- C = sum_g A_g @ B_g with A_g = rows
+  // [sum_offsets[g], sum_offsets[g] + rows_host) of the slot-ordered buffer (device offsets: the
+  // dispatch's run starts) and B_g = group g of the weight stack. The k loop simply runs over
+  // sum_groups * num_k stages.
+  int32_t sum_groups;
+  const int32_t* sum_offsets;
   int32_t b_fused;             // MN-major B: the maps are 4-D (64 n, k, n / 64, group) and one copy
                                // brings all BN / 64 boxes of a stage (a TMA instruction costs the
                                // issuing thread about as much as a whole stage of MMAs)

@@ -369,7 +369,8 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
         const bool a_alt = tc.group >= p.a2_first_group;
         group_next = tile_group(p, t + gridDim.x, m_tiles, total_tiles);
         start_next = run_start_of(group_next);
-        for (int kt = 0; kt < p.num_k; ++kt, ++it) {
+        const int k_total = p.sum_groups > 0 ? p.sum_groups * p.num_k : p.num_k;
+        for (int kt = 0; kt < k_total; ++kt, ++it) {
           const int s = it % STAGES;
           const uint32_t use = it / STAGES;
           if (use > 0 && !mbar_wait(empty_bar + s, (use - 1) & 1, p.status)) {
@@ -380,15 +381,20 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
           uint8_t* sA = smem + s * L::STAGE_BYTES;
           uint8_t* sB = sA + A_STAGE_BYTES;
           mbar_expect_tx(full_bar + s, L::STAGE_BYTES);
-          const int k0 = kt * BK;
-          if (a_alt)
+          const int g_sum = p.sum_groups > 0 ? kt / p.num_k : 0;
+          const int k0 = (kt - g_sum * p.num_k) * BK;
+          if (p.sum_groups > 0)
+            tma_load_3d(sA, &tmA, full_bar + s, k0,
+                        tc.m_tile * BM + __ldg(p.sum_offsets + g_sum), 0);
+          else if (a_alt)
             tma_load_3d(sA, &tmA2, full_bar + s, k0, tc.m_tile * BM - a_start, 0);
           else
             tma_load_3d(sA, &tmA, full_bar + s, k0, tc.m_tile * BM, p.a_grouped ? tc.z : 0);
           // the tile's expert lives in the first weight stack or (shared experts) the second
           const bool first = tc.group < p.n_groups_b1;
           const CUtensorMap* mb = first ? &tmB : &tmB2;
-          const int gb = first ? tc.group : tc.group - p.n_groups_b1;
+          const int gb = p.sum_groups > 0 ? g_sum
+                                          : first ? tc.group : tc.group - p.n_groups_b1;
           if constexpr (B_MN) {
             if (p.b_fused) {
               tma_load_4d(sB, mb, full_bar + s, 0, k0, tc.n0 / 64, gb);
@@ -418,7 +424,8 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + b * TMEM_BUF;
-        for (int kt = 0; kt < p.num_k; ++kt, ++it) {
+        const int k_total = p.sum_groups > 0 ? p.sum_groups * p.num_k : p.num_k;
+        for (int kt = 0; kt < k_total; ++kt, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(full_bar + s, (it / STAGES) & 1, p.status)) {
             *abort_flag = 1;

@@ -404,6 +404,39 @@ def down_gemm_acc(hid, w_out, expert_ids, n_post_pad, n_fixed: int, sorted_ids, 
     return acc
 
 
+def down_gemm_sum(hid, w_out, run_offsets, n_tokens: int, out=None) -> torch.Tensor:
+    """out [T, D] = sum_g hid[run_offsets[g] + t] @ w_out[g] (plain stores): the shared experts'
+    share of the block's output, written as the initial value of the atomic combine's accumulator.
+    run_offsets: int32 device tensor [S], the starts of the groups' token-ordered runs in hid."""
+    _need_cuda(hid, w_out)
+    rows, k = hid.shape
+    g, _, d = w_out.shape
+    if out is None:
+        out = torch.empty((n_tokens, d), dtype=hid.dtype, device=hid.device)
+    assert run_offsets.dtype == torch.int32 and run_offsets.numel() >= g and out.is_contiguous()
+    _lib.check(_lib.load().moe_b200_down_gemm_sum(
+        hid.data_ptr(), rows, k, w_out.data_ptr(), g, d, run_offsets.data_ptr(), n_tokens,
+        out.data_ptr(), status_word(hid.device).data_ptr(), _stream(hid)), "moe_b200_down_gemm_sum")
+    _count(1)
+    return out
+
+
+def dx_gemm_sum(da1, w_in, run_offsets, n_tokens: int, out=None) -> torch.Tensor:
+    """out [T, D] = sum_g da1[run_offsets[g] + t] @ w_in[g]^T (plain stores): the shared experts'
+    share of dX as the initial value of the accumulator dx_gemm_acc adds the routed rows to."""
+    _need_cuda(da1, w_in)
+    rows, h2 = da1.shape
+    g, d, _ = w_in.shape
+    if out is None:
+        out = torch.empty((n_tokens, d), dtype=da1.dtype, device=da1.device)
+    assert run_offsets.dtype == torch.int32 and run_offsets.numel() >= g and out.is_contiguous()
+    _lib.check(_lib.load().moe_b200_dx_gemm_sum(
+        da1.data_ptr(), rows, h2 // 2, w_in.data_ptr(), g, d, run_offsets.data_ptr(), n_tokens,
+        out.data_ptr(), status_word(da1.device).data_ptr(), _stream(da1)), "moe_b200_dx_gemm_sum")
+    _count(1)
+    return out
+
+
 def dx_gemm_acc(da1, w_in, expert_ids, n_post_pad, n_fixed: int, sorted_ids, n_pairs: int,
                 top_k: int, acc: torch.Tensor, w_extra=None, pad_offsets=None) -> torch.Tensor:
     """The dX GEMM fused with the combine: row `row` of da1 x w_in[e]^T is added to row

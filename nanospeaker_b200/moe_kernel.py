@@ -188,6 +188,51 @@ def _check_inputs(x, w_in, w_out, w_sh_in):
             f"n_experts={w_in.shape[0]}, n_shared={n_shared}")
 
 
+def _down_combine_atomic(hid, w_out, w_sh_out, expert_ids, n_post_pad, pad_offsets, sorted_ids, tw,
+                         m, topk, x, b_out, out):
+    """The down GEMM with the atomic combine. `out` given (a residual, or zeros when there are
+    biases): every row, shared experts included, is added to it. Otherwise the shared experts'
+    rows -- token-ordered, weight 1 -- are summed by one plain-store GEMM that gives the accumulator
+    its initial value (no fill pass, a quarter fewer atomic adds at S = 2, k = 6), and only the
+    routed experts' rows are added."""
+    if out is None and w_sh_out is not None and b_out is None:
+        e_n = w_out.shape[0]
+        out = K.down_gemm_sum(hid, w_sh_out, pad_offsets[e_n:], x.shape[0])
+        return K.down_gemm_acc(hid, w_out, expert_ids, pad_offsets[e_n:e_n + 1], 0, sorted_ids, tw,
+                               m, topk, out)
+    if out is None:
+        out = torch.zeros_like(x)
+    return K.down_gemm_acc(hid, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m, topk, out,
+                           w_extra=w_sh_out, bias=b_out)
+
+
+def _dx_first_value(da1, w_sh_in, pad_offsets, e_n, x):
+    """dX's accumulator with its first value: the shared experts' share by one plain-store GEMM
+    (see _down_combine_atomic), zeros without shared experts."""
+    if w_sh_in is not None:
+        return K.dx_gemm_sum(da1, w_sh_in, pad_offsets[e_n:], x.shape[0])
+    return torch.zeros_like(x)
+
+
+def _dx_add_routed(da1, w_in, shared_done, expert_ids, n_post_pad, pad_offsets, sorted_ids, m, topk,
+                   dx):
+    """The routed experts' rows of dX added to dx (atomic combine in the GEMM's epilogue)."""
+    e_n = w_in.shape[0]
+    if shared_done:   # the tile list ends where the first shared run starts
+        return K.dx_gemm_acc(da1, w_in, expert_ids, pad_offsets[e_n:e_n + 1], 0, sorted_ids, m,
+                             topk, dx, pad_offsets=pad_offsets[:e_n + 1])
+    return K.dx_gemm_acc(da1, w_in, expert_ids, n_post_pad, 0, sorted_ids, m, topk, dx,
+                         pad_offsets=pad_offsets)
+
+
+def _dx_combine_atomic(da1, w_in, w_sh_in, expert_ids, n_post_pad, pad_offsets, sorted_ids, m,
+                       topk, x):
+    """dX with the atomic combine: first value, then the routed rows."""
+    dx = _dx_first_value(da1, w_sh_in, pad_offsets, w_in.shape[0], x)
+    return _dx_add_routed(da1, w_in, w_sh_in is not None, expert_ids, n_post_pad, pad_offsets,
+                          sorted_ids, m, topk, dx)
+
+
 @torch.library.custom_op("moe_b200::moe_experts", mutates_args=())
 def moe_experts(
     x: torch.Tensor,
@@ -248,9 +293,6 @@ def moe_experts(
     if w_sh_in is not None:
         w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
     b_in, b_out = _all_bias(b_in, b_sh_in, w_in, w_sh_in, 2), _all_bias(b_out, b_sh_out, w_out, w_sh_out, 2)
-    # the accumulator of the atomic combine is cleared first thing, far ahead of the GEMM that adds to it
-    out = torch.zeros_like(x) if atomic_combine else None
-
     if save_for_backward:
         live, tok = _routed_rows(x, w_in, w_sh_in, pad_offsets, n_post_pad)
         xs = K.permute(x, topk, sorted_ids, live)
@@ -261,8 +303,8 @@ def moe_experts(
         hid, _ = K.up_gemm(x, w_in, expert_ids, n_post_pad, 0, act, False,
                            gather=(sorted_ids, topk), w_extra=w_sh_in, bias=b_in)
     if atomic_combine:
-        out = K.down_gemm_acc(hid, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m, topk, out,
-                              w_extra=w_sh_out, bias=b_out)
+        out = _down_combine_atomic(hid, w_out, w_sh_out, expert_ids, n_post_pad, pad_offsets,
+                                   sorted_ids, tw, m, topk, x, b_out, None)
     else:
         y = K.down_gemm(hid, w_out, expert_ids, n_post_pad, 0, sorted_ids, tw, m, w_extra=w_sh_out,
                         bias=b_out)
@@ -351,7 +393,6 @@ def moe_experts_bwd(
     topk = topk_w.shape[-1]
     m = n * topk
     tw = topk_w.reshape(-1).contiguous()
-    dx = torch.zeros_like(x) if atomic_combine else None
     # pairs without a slot (dropped by a capacity) are never visited by the dHidden epilogue
     dtw_buf = torch.zeros(m, dtype=x.dtype, device=x.device) if has_dropped else None
 
@@ -361,8 +402,8 @@ def moe_experts_bwd(
                                        a1, act, True, w_extra=w_sh_out, token_rows=tok,
                                        dtw_out=dtw_buf)
     if atomic_combine:
-        K.dx_gemm_acc(da1, w_in, expert_ids, n_post_pad, 0, sorted_ids, m, topk, dx,
-                      w_extra=w_sh_in, pad_offsets=pad_offsets)
+        dx = _dx_combine_atomic(da1, w_in, w_sh_in, expert_ids, n_post_pad, pad_offsets,
+                                sorted_ids, m, topk, x)
     else:
         ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
         dx = K.combine(ydx, inv_ids, n, topk)
@@ -529,8 +570,8 @@ def moe_block(
     ld = _router_ld(e_n)
     ks = top_k + s_n
     out = None
-    if atomic_combine:   # the accumulator the down GEMM adds into: zeros, or the residual
-        out = torch.zeros_like(x) if residual is None else residual.contiguous().clone()
+    if atomic_combine and residual is not None:   # the residual is the accumulator's initial value
+        out = residual.contiguous().clone()
 
     wp = K.copy_cols(router_w, ld).unsqueeze(0)   # [1, D, ld], zero pad columns
     logits = K.down_gemm(x, wp, None, None, 1, None, None, 0)[0]
@@ -549,7 +590,8 @@ def moe_block(
         xs, a1 = x.new_empty(0), x.new_empty(0)
         hid, _ = K.up_gemm(x, w_in, eids, npp, 0, act, False, gather=(sids, ks), w_extra=w_sh_in)
     if atomic_combine:
-        K.down_gemm_acc(hid, w_out, eids, npp, 0, sids, tw, m, ks, out, w_extra=w_sh_out)
+        out = _down_combine_atomic(hid, w_out, w_sh_out, eids, npp, offs, sids, tw, m, ks, x, None,
+                                   out)
     else:
         y = K.down_gemm(hid, w_out, eids, npp, 0, sids, tw, m, w_extra=w_sh_out)
         out = K.combine(y, inv, n, ks, residual)   # + residual [T, D] in the same fp32 sum when given
@@ -617,7 +659,7 @@ def moe_block_bwd(
 ) -> _T6:
     """[dx, d_router_w [D, E], dW_in, dW_out, dW_sh_in, dW_sh_out] of moe_block."""
     grad_out = grad_out.to(x.dtype).contiguous()
-    dx = torch.zeros_like(x) if atomic_combine else None   # cleared far ahead of the adds
+    dx = None
     act = _act_id(activation)
     n, d = x.shape
     e_n = w_in.shape[0]
@@ -639,11 +681,17 @@ def moe_block_bwd(
         side_out = side_router = main
     side_out.wait_stream(main)
     side_router.wait_stream(main)
+    if atomic_combine:
+        # dx gets its first value by plain stores (the shared experts' share, or zeros); the
+        # router's share on the third stream is added once that has happened
+        dx = _dx_first_value(da1, w_sh_in, pad_offsets, e_n, x)
+        dx_ready = torch.cuda.Event()
+        dx_ready.record(main)
     g_in = K.wgrad(xs, da1, pad_offsets, e_n + s_n, n_extra=s_n,
                    token_rows=("a", x) if s_n else None)
     if atomic_combine:
-        K.dx_gemm_acc(da1, w_in, expert_ids, n_post_pad, 0, sorted_ids, m, ks, dx,
-                      w_extra=w_sh_in, pad_offsets=pad_offsets)
+        _dx_add_routed(da1, w_in, w_sh_in is not None, expert_ids, n_post_pad, pad_offsets,
+                       sorted_ids, m, ks, dx)
     else:
         ydx = K.dx_gemm(da1, w_in, expert_ids, n_post_pad, 0, w_extra=w_sh_in)
     with torch.cuda.stream(side_out):
@@ -657,6 +705,7 @@ def moe_block_bwd(
                                 logits.shape[1], noise)
         d_router = K.copy_cols(K.wgrad(x, dl, None, 1)[0], e_n)   # pad columns dropped
         if atomic_combine:   # the router's share of dx joins the same accumulator
+            side_router.wait_event(dx_ready)
             K.dx_gemm_acc(dl.unsqueeze(0), router_w_padded, None, None, 1, None, 0, 1, dx)
         else:
             dx_router = K.dx_gemm(dl, router_w_padded, None, None, 1)[0]

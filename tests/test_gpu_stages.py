@@ -197,6 +197,37 @@ def test_shared_expert_schedule_on_unpermuted_tokens(T):
     K().check_status("cuda")
 
 
+@pytest.mark.parametrize("T,S", [(1, 1), (127, 2), (300, 2), (1000, 3), (2048, 2)])
+def test_group_summed_gemms_store_the_shared_experts_share(T, S):
+    """out[t] = sum_g A[offsets[g] + t] @ B_g with plain stores: the shared experts' share of the
+    block's output and of dX, read from token-ordered runs at device-side offsets (runs padded to
+    128 rows, neighbours holding other data), any token count; and it composes with the routed
+    experts' atomic adds that follow it on the same buffer."""
+    D, H = 576, 128
+    torch.manual_seed(T + S)
+    run = (T + 127) // 128 * 128
+    first = 256                                  # rows of other runs in front
+    rows = first + S * run + 128
+    hid = torch.randn(rows, H).bfloat16()
+    da1 = (torch.randn(rows, 2 * H) * 0.1).bfloat16()
+    wso = (torch.randn(S, H, D) * H ** -0.5).bfloat16()
+    wsi = (torch.randn(S, D, 2 * H) * D ** -0.5).bfloat16()
+    offs = torch.tensor([first + g * run for g in range(S)], dtype=torch.int32)
+    g = lambda t: t.cuda()
+    y = K().down_gemm_sum(g(hid), g(wso), g(offs), T)
+    dx = K().dx_gemm_sum(g(da1), g(wsi), g(offs), T)
+    assert y.shape == (T, D) and dx.shape == (T, D)
+    y_ref = sum(hid[int(o):int(o) + T].float() @ wso[i].float() for i, o in enumerate(offs))
+    dx_ref = sum(da1[int(o):int(o) + T].float() @ wsi[i].float().t() for i, o in enumerate(offs))
+    assert rel_l2(y.cpu(), y_ref) < TOL
+    assert rel_l2(dx.cpu(), dx_ref) < TOL
+    # a caller-provided buffer is overwritten, not added to
+    buf = torch.full((T, D), 7.0, dtype=torch.bfloat16, device="cuda")
+    K().down_gemm_sum(g(hid), g(wso), g(offs), T, out=buf)
+    assert torch.equal(buf, y)
+    K().check_status("cuda")
+
+
 def test_wgrad_split_k_is_deterministic_and_chunk_size_independent():
     """A hot expert (thousands of rows) is split over many CTAs; the partials are summed in chunk
     order, so two runs agree bit for bit and chunk sizes only move fp32 rounding."""
