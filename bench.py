@@ -760,6 +760,108 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def ep_phase_times(grp, m, x, gout, w_in, w_out, dev, world, dist, reps=5):
+    """Where the peer-memory step's time goes on every rank: each phase of the step (the calls
+    between two phase boundaries) is captured in a CUDA graph of its own and the graphs are replayed
+    in order with a CUDA event between them, so the figures are device time, not the eager launch
+    time of eight Python processes on one host. Pushes and pulls are NVLink phases, owner phases are
+    GEMMs, a boundary's time is the wait for the slowest rank. Returns per-rank milliseconds per
+    phase and the rows each rank owns."""
+    me = grp.me
+    cast = lambda t: t.detach().to(x.dtype).contiguous()
+    bias = m.router.logit_bias
+    bias = None if bias is None else bias.to(torch.float32).contiguous()
+    w_sh_in, w_sh_out = cast(m.W_sh_in), cast(m.W_sh_out)
+    wi, wo = cast(w_in), cast(w_out)
+    keep = {}
+
+    def route():
+        keep["cnt"] = grp.gather_counts(me.f1_route(x.detach(), m.router.W.detach(), bias,
+                                                    bool(m.router.normalize_weights), False))
+        me.f3_shared(w_sh_in, w_sh_out, "silu", True)
+        torch.cuda.current_stream().wait_stream(me.side)   # a graph must join what it forks
+
+    def push_dout():
+        me.b1_push(gout)
+        torch.cuda.current_stream().wait_stream(me.side)
+
+    def pull_y():      # (the pulls join the side stream: bring it into this graph first)
+        me.side.wait_stream(torch.cuda.current_stream())
+        keep["out"] = me.f4_pull(0.0)
+
+    def pull_dx():
+        me.side.wait_stream(torch.cuda.current_stream())
+        keep["dx"] = me.b3_pull(None)
+
+    seq = [("route + counts all-gather", route),
+           ("push x", lambda: me.f2_push(keep["cnt"])),
+           ("boundary 1", grp.boundary),
+           ("owner fwd", lambda: me.f3_experts(wi, wo, w_sh_in, w_sh_out, "silu", True)),
+           ("boundary 2", grp.boundary),
+           ("pull y", pull_y),
+           ("push dOut", push_dout),
+           ("boundary 3", grp.boundary),
+           ("owner bwd", me.b2_experts),
+           ("boundary 4", grp.boundary),
+           ("pull dX + router bwd", pull_dx)]
+    graphs = []
+    for name, fn in seq:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()                                  # warm-up outside capture
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        graphs.append(g)
+    dist.barrier()
+    torch.cuda.synchronize()
+    total = [0.0] * len(seq)
+    for it in range(reps + 1):
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(seq) + 1)]
+        for i, g in enumerate(graphs):
+            evs[i].record()
+            g.replay()
+        evs[-1].record()
+        torch.cuda.synchronize()
+        if it > 0:
+            for i in range(len(seq)):
+                total[i] += evs[i].elapsed_time(evs[i + 1]) / reps
+    local = torch.tensor(total + [float(me.own_npp.item())], device=dev)
+    every = [torch.empty_like(local) for _ in range(world)]
+    dist.all_gather(every, local)
+    table = torch.stack(every).cpu()
+    return {"per_rank_ms": {n: [round(float(v), 3) for v in table[:, i]]
+                            for i, (n, _) in enumerate(seq)},
+            "rows_owned_per_rank": [int(v) for v in table[:, -1]],
+            "method": "one CUDA graph per phase, CUDA events between the replays; the shared "
+                      "experts' forward / backward (side stream in the real step, under the push "
+                      "and the boundary) are joined inside 'route' / 'push dOut' here"}
+
+
+def ep_nvlink_roofline(phases, T, world):
+    """The push / pull phases against the NVLink roof: bytes that cross the links per rank and
+    direction (a row per routed pair whose owner is another rank: the (world - 1) / world share
+    under uniform routing; a pushed row carries its slot id and router weight) over the slowest
+    rank's phase time, against the measured peer-copy bandwidth of this pool (770 GB/s per
+    direction, nominal 900)."""
+    if not phases:
+        return None
+    remote = T * TOP_K * (world - 1) / world
+    row = D_MODEL * 2
+    out = {"bound": "nvlink", "peak": 770.0, "unit": "GB/s per direction per GPU",
+           "peak_source": "measured peer copy on this pool (nominal 900)"}
+    for key, name, extra in (("push_x", "push x", 6), ("pull_y", "pull y", 0),
+                             ("push_dout", "push dOut", 0), ("pull_dx", "pull dX + router bwd", 0)):
+        ms = max(phases["per_rank_ms"][name])
+        out[key] = {"bytes_per_rank": int(remote * (row + extra)), "ms": ms,
+                    "achieved": round(remote * (row + extra) / (ms * 1e-3) / 1e9, 1),
+                    "frac": round(remote * (row + extra) / (ms * 1e-3) / 1e9 / 770.0, 3)}
+    return out
+
+
 def run_ep_workload(args):
     """BASELINE config 5: expert-parallel forward + backward. 76 routed experts partitioned over the
     ranks, shared experts and router replicated, T=65536 tokens per GPU, uniform or hot-spot routing (--routing). One rank
@@ -856,22 +958,7 @@ def run_ep_workload(args):
     K.check_status(dev)
     phases = None
     if push:
-        # a few more steps with an event at every phase start: where the step's time goes on each
-        # rank (pushes and pulls = NVLink, owner phases = GEMMs, waits = the other ranks), and how
-        # many rows each rank owns
-        grp.timing = True
-        for i in range(3):
-            step(i)
-        mine = grp.phase_times()
-        names = list(mine)
-        local = torch.tensor([mine[n] for n in names] + [float(grp.me.own_npp.item())], device=dev)
-        every = [torch.empty_like(local) for _ in range(world)]
-        dist.all_gather(every, local)
-        grp.timing = False
-        table = torch.stack(every).cpu()
-        phases = {"per_rank_ms": {n: [round(float(v), 3) for v in table[:, i]]
-                                  for i, n in enumerate(names)},
-                  "rows_owned_per_rank": [int(v) for v in table[:, -1]]}
+        phases = ep_phase_times(grp, m, xs[0], gout, w_in, w_out, dev, world, dist)
     if rank == 0:
         print(json.dumps({
             "metric": "MoE-block tokens/s (fwd+bwd, expert parallel)",
@@ -883,7 +970,8 @@ def run_ep_workload(args):
                                    + ("rows pushed into / pulled from the owners' buffers "
                                       "through peer pointers (symmetric memory)" if push else
                                       "dispatch / combine by NCCL all-to-all")},
-            "cuda_graph": use_graph, "phases": phases}), flush=True)
+            "cuda_graph": use_graph, "phases": phases,
+            "roofline": ep_nvlink_roofline(phases, T, world)}), flush=True)
     dist.barrier()
     torch.cuda.synchronize()
     # Tear-down. With the step captured in CUDA graphs (NCCL collectives and symmetric-memory
