@@ -47,10 +47,10 @@ N_INPUT_SETS = 8         # x / dOut pairs cycled through so successive steps do 
 METRIC = "MoE-block tokens/s (fwd+bwd)"
 
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels that have
-# been captured with `ncu --set full` on this workload; see
+# been captured with ncu on this workload; see profiles/ncu_block_kernels_T16384.md and
 # profiles/ncu_dW_in_dHidden_permute_T16384.md.
 NCU_TRAFFIC_BYTES = {"permute (routed rows; shared experts read x in place)": 82.0e6,
-                     "wgrad_in (gemm + reduce)": 227.8e6, "dhidden+glu_bwd": 283.7e6}
+                     "wgrad_in (gemm + reduce)": 243.2e6, "dhidden+glu_bwd": 285.7e6}
 # (filled from the ncu summaries under profiles/; a kernel without a capture reports null)
 
 FLOP_PER_TOKEN_FWD_BWD = 10_879_488   # 3 * (routed up 1 769 472 + down 884 736 + shared 884 736 + router 87 552)
