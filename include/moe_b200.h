@@ -142,7 +142,8 @@ int moe_b200_dispatch(const int64_t* topk_idx, int64_t n_pairs, int32_t n_expert
  * experts (outputs as moe_b200_dispatch; l_cap = moe_b200_l_cap(n_tokens * (top_k + n_shared),
  * n_experts + n_shared)). scratch: moe_b200_router_dispatch_scratch_bytes(n_tokens,
  * n_experts + n_shared) bytes. Replaces TopKRouter.forward's selection (src/model/router.py:79-97)
- * followed by moe_dispatch (src/model/moe_kernel.py:180-218). */
+ * followed by moe_dispatch (src/model/moe_kernel.py:180-218). 
+ * A batch of at most 128 tokens (one block) is routed, planned and scattered by a single launch. */
 size_t moe_b200_router_dispatch_scratch_bytes(int64_t n_tokens, int32_t n_experts_total);
 int moe_b200_router_dispatch(const void* logits, int32_t ld, const float* bias,
                              const float* noise, int64_t n_tokens,

@@ -11,6 +11,7 @@
 #include "../../include/moe_b200.h"
 #include "pdl.cuh"
 #include "routing.cuh"
+#include "dispatch_scatter.cuh"
 
 namespace moe {
 
@@ -199,10 +200,11 @@ __global__ void __launch_bounds__(RF4_THREADS)
                          __nv_bfloat16* __restrict__ w_all, int64_t* __restrict__ idx_all,
                          float* __restrict__ colsum, int tokens_per_block,
                          int32_t* __restrict__ block_hist, int32_t* __restrict__ sorted_ids,
-                         int64_t l_cap) {
+                         int64_t l_cap, const ScatterArgs sc) {
   pdl_trigger();
   pdl_wait();
   static_assert(EPL % 8 == 0, "a lane loads its experts as 16-byte pieces");
+  static_assert(RF4_THREADS == DISPATCH_THREADS, "the scatter pass runs on this kernel's block");
   __shared__ float cs[RF4_THREADS / 32][4 * EPL];
   __shared__ int32_t hist[MAX_EXPERTS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -383,6 +385,14 @@ __global__ void __launch_bounds__(RF4_THREADS)
     const int64_t lo = per * blockIdx.x;
     const int64_t hi = lo + per < l_cap ? lo + per : l_cap;
     for (int64_t sl = lo + threadIdx.x; sl < hi; sl += blockDim.x) sorted_ids[sl] = int32_t(n_pairs);
+    if (sc.counts != nullptr) {
+      // one block holds the whole input: plan and scatter here instead of in a second launch (what
+      // this block wrote above is read back through L2 after the barrier)
+      __syncthreads();
+      dispatch_scatter_body<true>(idx_all, n_pairs, n_experts + n_shared, tokens_per_block * kS, 1,
+                                  block_hist, sc.counts, sc.pad_offsets, sc.n_post_pad,
+                                  sc.expert_ids, sc.n_tiles_cap, sorted_ids, sc.inv_ids, 0, 0, 0, 1);
+    }
   }
 }
 
@@ -598,11 +608,17 @@ int launch_router_fused_chunked(const __nv_bfloat16* logits, int ld, const float
                                 int normalize, int full_softmax, __nv_bfloat16* w_all,
                                 int64_t* idx_all, float* colsum, int tokens_per_block, int n_blocks,
                                 int32_t* block_hist, int32_t* sorted_ids, int64_t l_cap,
-                                cudaStream_t st) {
+                                cudaStream_t st, const ScatterArgs* sc, bool* did_scatter) {
+  if (did_scatter) *did_scatter = false;
   if (const int epl = rf4_experts_per_lane(logits, ld, n_experts, top_k)) {
+    ScatterArgs fuse{};
+    if (sc != nullptr && n_blocks == 1) {
+      fuse = *sc;
+      if (did_scatter) *did_scatter = true;
+    }
     launch_rf4(epl, full_softmax && colsum != nullptr, unsigned(n_blocks), st, logits, ld, bias,
                noise, n_tokens, n_experts, top_k, n_shared, normalize, full_softmax, w_all, idx_all, colsum,
-               tokens_per_block, block_hist, sorted_ids, l_cap);
+               tokens_per_block, block_hist, sorted_ids, l_cap, fuse);
     return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
   }
 #define LAUNCH(NS)                                                                              \
@@ -648,7 +664,8 @@ int moe_b200_router_fused(const void* logits, int32_t ld, const float* bias, con
     launch_rf4(epl, full_softmax && colsum != nullptr, unsigned(blocks), st, lg, ld, bias, noise,
                n_tokens,
                n_experts, top_k, n_shared, normalize, full_softmax, w, idx_all, colsum, 0,
-               static_cast<int32_t*>(nullptr), static_cast<int32_t*>(nullptr), int64_t(0));
+               static_cast<int32_t*>(nullptr), static_cast<int32_t*>(nullptr), int64_t(0),
+               ScatterArgs{});
     return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
   }
 #define LAUNCH(NS)                                                                          \

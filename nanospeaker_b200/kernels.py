@@ -128,7 +128,7 @@ def _noise(noise, n_tokens: int, n_experts: int):
 def router_dispatch(logits, bias, n_experts: int, top_k: int, n_shared: int, normalize: bool,
                     full_softmax: bool, noise=None):
     """router_fused + dispatch in two launches (the router kernel leaves the dispatch's per-block
-    histograms): -> (w_all, idx_all, colsum | None, sorted_ids, expert_ids, pad_offsets, counts,
+    histograms; one launch when the batch fits one block of 128 tokens): -> (w_all, idx_all, colsum | None, sorted_ids, expert_ids, pad_offsets, counts,
     n_post_pad, inv_ids) with counts / pad_offsets over the n_experts + n_shared experts."""
     _need_cuda(logits)
     t, ld = logits.shape
@@ -155,7 +155,10 @@ def router_dispatch(logits, bias, n_experts: int, top_k: int, n_shared: int, nor
         eids.data_ptr(), offs.data_ptr(), counts.data_ptr(), npp.data_ptr(), inv.data_ptr(),
         scratch.data_ptr(), nbytes, status_word(dev).data_ptr(), _stream(logits)),
         "moe_b200_router_dispatch")
-    _count(2)
+    # up to 128 tokens of a shape the four-lanes-per-token kernel takes: one launch does both passes
+    one = (t <= 128 and top_k <= 8 and n_experts <= 96 and ld % 8 == 0
+           and ld >= (64 if n_experts <= 64 else 96))
+    _count(1 if one else 2)
     return w_all, idx_all, colsum, sids, eids, offs, counts, npp, inv
 
 
