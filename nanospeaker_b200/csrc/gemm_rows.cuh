@@ -190,19 +190,15 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
                      const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmB2,
                      const __grid_constant__ CUtensorMap tmOut, const RowsArgs p) {
+  // The prologue below (barriers, TMEM, descriptor prefetch) touches nothing an earlier kernel
+  // wrote, so it runs BEFORE the wait for the preceding kernels: under programmatic dependent launch
+  // this CTA is resident while the previous grid's last CTAs still work.
   pdl_trigger();
-  pdl_wait();
   using L = RowsSmem<BN, STAGES, EPI, OUT_BOXES>;
   constexpr bool TMA_OUT = epi_uses_tma_store(EPI);
   static_assert(BN % 64 == 0 && BN <= 256, "BN must be a multiple of 64 up to 256");
   constexpr uint32_t TMEM_BUF = BN <= 128 ? 128 : 256;  // columns per accumulator buffer
   constexpr uint32_t TMEM_COLS = 2 * TMEM_BUF;
-
-  // ------------------------------------------------------------ tile list (before any barrier)
-  const int live = p.n_fixed_groups > 0 ? p.rows_host : __ldg(p.n_post_pad);
-  const int m_tiles = (live + BM - 1) / BM;
-  const int total_tiles = m_tiles * p.n_chunks * (p.n_fixed_groups > 0 ? p.n_fixed_groups : 1);
-  if (int(blockIdx.x) >= total_tiles) return;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -253,6 +249,14 @@ __global__ void __launch_bounds__(rows_threads(EPI, GATHER_A), 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+
+  // ------------------------------------------------------------ tile list
+  // (every thread waits for the preceding kernels itself before its first read of their data; a
+  // CTA beyond the end of the list runs no loop iteration and only gives its TMEM back)
+  pdl_wait();
+  const int live = p.n_fixed_groups > 0 ? p.rows_host : __ldg(p.n_post_pad);
+  const int m_tiles = (live + BM - 1) / BM;
+  const int total_tiles = m_tiles * p.n_chunks * (p.n_fixed_groups > 0 ? p.n_fixed_groups : 1);
 
   if (AUX_IN && warp == AUX_WARP) {
     // ------------------------------------------------ pre-activation tiles for the epilogue

@@ -108,8 +108,8 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
                       const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmAlt, const WgradArgs p, int tiles_x,
                       int tiles_y) {
-  pdl_trigger();
-  pdl_wait();
+  pdl_trigger();   // (the wait for the preceding kernels comes after the part of the prologue
+                   // that reads nothing of theirs: barriers and TMEM)
   using L = WgradSmem<BN, STAGES>;
   constexpr uint32_t TMEM_BUF = BN <= 128 ? 128 : 256;
   constexpr uint32_t TMEM_COLS = 2 * TMEM_BUF;
@@ -132,6 +132,7 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
   const int lane = threadIdx.x & 31;
 
   if (warp == 2) {
+    pdl_wait();   // the run table is the dispatch's
     wgrad_build_table(p, lane, first_item, run_start);
     // the reduction pass reads the item counts from global memory instead of rebuilding them
     if (blockIdx.x == 0) {
@@ -162,6 +163,7 @@ __global__ void __launch_bounds__(GATHER ? WGRAD_THREADS_GATHER : WGRAD_THREADS,
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();      // every thread, before its first read of an earlier kernel's data
   const uint32_t tmem_base = *tmem_slot;
   const int tiles_xy = tiles_x * tiles_y;
   const int n_items = first_item[p.n_groups];
