@@ -463,6 +463,61 @@ int moe_b200_ep_pull_vec(const void* const* v, int32_t n_ranks, const int32_t* p
                          const int32_t* pair_row, int64_t n_tokens, int32_t k_all, int32_t top_k,
                          void* out, void* stream);
 
+/* ---- The whole block in one host call per direction -------------------------------------------
+ * moe_b200_block_fwd / moe_b200_block_bwd issue the complete stage sequence of a training step of
+ * MoEBlock.forward (src/model/moe.py:345-418, router.py:56-111) and of its backward from C++: a
+ * host that pays per call into this library (ctypes from Python: ~22 calls, ~1 ms per step at
+ * T = 16384, more than the GPU needs) makes two. Training form: the permuted rows xs, the
+ * pre-activations a1, the bf16 logits and the routing plan are kept for the backward; combine in
+ * the GEMM epilogues (atomic); no residual, no per-expert biases (use the stage entry points for
+ * those). Tensors: x [T, D], router_w [D, E], w_in [E, D, 2H], w_out [E, H, D], w_sh_* likewise
+ * with n_shared groups (NULL when n_shared == 0), all bf16 and contiguous; logit_bias [E] and
+ * noise [T, E] fp32 or NULL. With ld = E rounded up to 64, kS = top_k + n_shared, M = T * kS and
+ * L = moe_b200_l_cap(M, E + n_shared) the caller provides out [T, D], aux (1 float), counts [E],
+ * xs [L, D], a1 [L, 2H], logits [T, ld], w_all [T, kS] bf16, idx_all [T, kS] int64,
+ * sorted_ids [L], expert_ids [L / 128], pad_offsets [E + n_shared + 1], counts_all [E + n_shared],
+ * n_post_pad [1], inv_ids [M], router_w_padded [D, ld], and scratch of
+ * moe_b200_block_fwd_scratch_bytes(...) bytes (contents arbitrary). n_launches (host, may be NULL)
+ * receives the number of kernel launches made. */
+size_t moe_b200_block_fwd_scratch_bytes(int64_t n_tokens, int32_t d_model, int32_t d_hidden,
+                                        int32_t n_experts, int32_t n_shared, int32_t top_k);
+int moe_b200_block_fwd(const void* x, int64_t n_tokens, int32_t d_model, const void* router_w,
+                       const float* logit_bias, const float* noise, const void* w_in,
+                       const void* w_out, int32_t n_experts, int32_t d_hidden,
+                       const void* w_sh_in, const void* w_sh_out, int32_t n_shared,
+                       int32_t top_k, int32_t normalize, int32_t full_softmax, float aux_coef,
+                       int32_t activation, void* out, float* aux, int32_t* counts, void* xs,
+                       void* a1, void* logits, void* w_all, int64_t* idx_all,
+                       int32_t* sorted_ids, int32_t* expert_ids, int32_t* pad_offsets,
+                       int32_t* counts_all, int32_t* n_post_pad, int32_t* inv_ids,
+                       void* router_w_padded, void* scratch, size_t scratch_bytes,
+                       int32_t* n_launches, int32_t* status, void* stream);
+
+/* The backward of moe_b200_block_fwd: grad_out [T, D] bf16, grad_aux (1 float on the device, or
+ * NULL), the forward's inputs and kept tensors -> dx [T, D], d_router [D, E], dw_in, dw_out,
+ * dw_sh_in, dw_sh_out (shapes of the weights; the last two NULL when n_shared == 0). After the
+ * dHidden kernel the work splits into three independent branches (dW_in + dX; dW_out; the
+ * router's backward); side_stream_a / side_stream_b (cudaStream_t, may be NULL) take the second
+ * and third, forked from and joined back into `stream` with events, so the call is capturable in
+ * a CUDA graph and the caller only ever sees `stream`. scratch:
+ * moe_b200_block_bwd_scratch_bytes(...) bytes. */
+size_t moe_b200_block_bwd_scratch_bytes(int64_t n_tokens, int32_t d_model, int32_t d_hidden,
+                                        int32_t n_experts, int32_t n_shared, int32_t top_k);
+int moe_b200_block_bwd(const void* grad_out, const float* grad_aux, const void* x,
+                       int64_t n_tokens, int32_t d_model, const float* logit_bias,
+                       const float* noise, const void* w_in, const void* w_out,
+                       int32_t n_experts, int32_t d_hidden, const void* w_sh_in,
+                       const void* w_sh_out, int32_t n_shared, int32_t top_k, int32_t normalize,
+                       int32_t full_softmax, float aux_coef, int32_t activation, const void* xs,
+                       const void* a1, const void* logits, const void* w_all,
+                       const int64_t* idx_all, const int32_t* sorted_ids,
+                       const int32_t* expert_ids, const int32_t* pad_offsets,
+                       const int32_t* counts_all, const int32_t* n_post_pad,
+                       const void* router_w_padded, void* dx, void* d_router, void* dw_in,
+                       void* dw_out, void* dw_sh_in, void* dw_sh_out, void* scratch,
+                       size_t scratch_bytes, void* side_stream_a, void* side_stream_b,
+                       int32_t* n_launches, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

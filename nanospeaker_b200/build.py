@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmoe_b200.so")
-SOURCES = ["api.cu", "routing.cu", "router_fused.cu", "movement.cu", "norm.cu", "gemm.cu", "ep.cu"]
+SOURCES = ["api.cu", "routing.cu", "router_fused.cu", "movement.cu", "norm.cu", "gemm.cu", "ep.cu", "block.cu"]
 HEADERS = ["ptx.cuh", "pdl.cuh", "gemm.cuh", "gemm_rows.cuh", "gemm_rows2.cuh", "gemm_wgrad2.cuh", "gemm_wgrad.cuh", "routing.cuh", "dispatch_scatter.cuh", os.path.join("..", "..", "include", "moe_b200.h")]
 
 

@@ -545,6 +545,83 @@ def wgrad(a, b, pad_offsets, n_groups: int, ks_rows: int = 0, a_grouped: bool = 
     return (dw, dw_extra) if n_extra else dw
 
 
+# ---------------------------------------------------------------- the whole block in one call
+def block_fwd(x, router_w, logit_bias, noise, w_in, w_out, w_sh_in, w_sh_out, top_k: int,
+              normalize: bool, full_softmax: bool, aux_coef: float, act: int, ld: int):
+    """moe_b200_block_fwd: the training forward of the whole block issued by one C call. Returns
+    (out, aux, counts, xs, a1, logits, w_all, idx_all, sorted_ids, expert_ids, pad_offsets,
+    counts_all, n_post_pad, inv_ids, router_w_padded [1, D, ld])."""
+    import ctypes
+    _need_cuda(x, w_in, w_out)
+    t, d = x.shape
+    e_n, _, h2 = w_in.shape
+    s_n = 0 if w_sh_in is None else w_sh_in.shape[0]
+    ks, n_all = top_k + s_n, e_n + s_n
+    cap = l_cap(t * ks, n_all)
+    dev, i32 = x.device, torch.int32
+    new = lambda shape, dtype=x.dtype: torch.empty(shape, dtype=dtype, device=dev)
+    out, aux, counts = new((t, d)), new((), torch.float32), new((e_n,), i32)
+    xs, a1, logits = new((cap, d)), new((cap, h2)), new((t, ld))
+    w_all, idx_all = new((t, ks)), new((t, ks), torch.int64)
+    sids, eids, offs = new((cap,), i32), new((cap // ALIGN_M,), i32), new((n_all + 1,), i32)
+    counts_all, npp, inv = new((n_all,), i32), new((1,), i32), new((t * ks,), i32)
+    wp = new((1, d, ld))
+    lib = _lib.load()
+    nbytes = lib.moe_b200_block_fwd_scratch_bytes(t, d, h2 // 2, e_n, s_n, top_k)
+    scratch = new((nbytes,), torch.uint8)
+    n_l = ctypes.c_int32(0)
+    _lib.check(lib.moe_b200_block_fwd(
+        x.data_ptr(), t, d, router_w.data_ptr(), _lib.ptr(logit_bias),
+        _lib.ptr(_noise(noise, t, e_n)), w_in.data_ptr(), w_out.data_ptr(), e_n, h2 // 2,
+        _lib.ptr(w_sh_in), _lib.ptr(w_sh_out), s_n, top_k, int(normalize), int(full_softmax),
+        float(aux_coef), act, out.data_ptr(), aux.data_ptr(), counts.data_ptr(), xs.data_ptr(),
+        a1.data_ptr(), logits.data_ptr(), w_all.data_ptr(), idx_all.data_ptr(), sids.data_ptr(),
+        eids.data_ptr(), offs.data_ptr(), counts_all.data_ptr(), npp.data_ptr(), inv.data_ptr(),
+        wp.data_ptr(), scratch.data_ptr(), nbytes, ctypes.byref(n_l),
+        status_word(dev).data_ptr(), _stream(x)), "moe_b200_block_fwd")
+    _count(n_l.value)
+    return (out, aux, counts, xs, a1, logits, w_all, idx_all, sids, eids, offs, counts_all, npp,
+            inv, wp)
+
+
+def block_bwd(grad_out, grad_aux, x, logit_bias, noise, w_in, w_out, w_sh_in, w_sh_out, xs, a1,
+              logits, w_all, idx_all, sids, eids, offs, counts_all, npp, wp, top_k: int,
+              normalize: bool, full_softmax: bool, aux_coef: float, act: int, side_streams):
+    """moe_b200_block_bwd: the whole backward issued by one C call (three streams inside).
+    Returns (dx, d_router [D, E], dw_in, dw_out, dw_sh_in | None, dw_sh_out | None)."""
+    import ctypes
+    _need_cuda(grad_out, x)
+    t, d = x.shape
+    e_n, _, h2 = w_in.shape
+    s_n = 0 if w_sh_in is None else w_sh_in.shape[0]
+    dev = x.device
+    new = lambda shape, dtype=x.dtype: torch.empty(shape, dtype=dtype, device=dev)
+    dx, d_router = new((t, d)), new((d, e_n))
+    dw_in, dw_out = torch.empty_like(w_in), torch.empty_like(w_out)
+    dw_sh_in = torch.empty_like(w_sh_in) if s_n else None
+    dw_sh_out = torch.empty_like(w_sh_out) if s_n else None
+    lib = _lib.load()
+    nbytes = lib.moe_b200_block_bwd_scratch_bytes(t, d, h2 // 2, e_n, s_n, top_k)
+    scratch = new((nbytes,), torch.uint8)
+    sa, sb = side_streams if side_streams is not None else (None, None)
+    # (buffers of this stream are used on the side streams too: the call joins them back into
+    # this stream before it returns, so whatever reuses the memory later is ordered after them)
+    n_l = ctypes.c_int32(0)
+    _lib.check(lib.moe_b200_block_bwd(
+        grad_out.data_ptr(), _lib.ptr(grad_aux), x.data_ptr(), t, d, _lib.ptr(logit_bias),
+        _lib.ptr(_noise(noise, t, e_n)), w_in.data_ptr(), w_out.data_ptr(), e_n, h2 // 2,
+        _lib.ptr(w_sh_in), _lib.ptr(w_sh_out), s_n, top_k, int(normalize), int(full_softmax),
+        float(aux_coef), act, xs.data_ptr(), a1.data_ptr(), logits.data_ptr(), w_all.data_ptr(),
+        idx_all.data_ptr(), sids.data_ptr(), eids.data_ptr(), offs.data_ptr(),
+        counts_all.data_ptr(), npp.data_ptr(), wp.data_ptr(), dx.data_ptr(), d_router.data_ptr(),
+        dw_in.data_ptr(), dw_out.data_ptr(), _lib.ptr(dw_sh_in), _lib.ptr(dw_sh_out),
+        scratch.data_ptr(), nbytes, sa.cuda_stream if sa is not None else None,
+        sb.cuda_stream if sb is not None else None, ctypes.byref(n_l),
+        status_word(dev).data_ptr(), _stream(x)), "moe_b200_block_bwd")
+    _count(n_l.value)
+    return dx, d_router, dw_in, dw_out, dw_sh_in, dw_sh_out
+
+
 # ---------------------------------------------------------------- expert parallelism, peer memory
 def _ptr_array(ptrs):
     import ctypes

@@ -507,6 +507,10 @@ _T6 = Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor
 _SIDE_STREAMS = {}
 # Debugging aid, off in normal use: True keeps every launch of the backward on the caller's stream.
 _DEBUG_ONE_STREAM = False
+# The whole-block op's common training form (atomic combine, no residual) is issued by ONE call into
+# the library per direction (moe_b200_block_fwd / _bwd) instead of ~22 calls from Python; False
+# keeps the stage-by-stage sequence below, which is the same launches.
+_ONE_CALL = True
 
 
 def _side_streams(device: torch.device):
@@ -569,6 +573,13 @@ def moe_block(
         w_sh_in, w_sh_out = w_sh_in.contiguous(), w_sh_out.contiguous()
     ld = _router_ld(e_n)
     ks = top_k + s_n
+    if (_ONE_CALL and atomic_combine and save_for_backward and residual is None
+            and not (global_aux and _aux_reduce is not None)):
+        # the common training form: the whole sequence below issued by one call into the library
+        if noise is not None:
+            noise = noise.to(torch.float32).contiguous()
+        return K.block_fwd(x, router_w.contiguous(), logit_bias, noise, w_in, w_out, w_sh_in,
+                           w_sh_out, top_k, normalize, full_softmax, aux_coef, act, ld)
     out = None
     if atomic_combine and residual is not None:   # the residual is the accumulator's initial value
         out = residual.contiguous().clone()
@@ -667,6 +678,16 @@ def moe_block_bwd(
     ks = top_k + s_n
     m = n * ks
     tw = w_all.reshape(-1)
+    if _ONE_CALL and atomic_combine:
+        d_aux = None if grad_aux is None else grad_aux.to(torch.float32).reshape(1)
+        side = None if _DEBUG_ONE_STREAM else _side_streams(x.device)
+        dx, d_router, dw_in, dw_out, dw_sh_in, dw_sh_out = K.block_bwd(
+            grad_out, d_aux, x, logit_bias, noise, w_in, w_out, w_sh_in, w_sh_out, xs, a1, logits,
+            w_all, idx_all, sorted_ids, expert_ids, pad_offsets, counts_all, n_post_pad,
+            router_w_padded, top_k, normalize, full_softmax, aux_coef, act, side)
+        if not s_n:
+            dw_sh_in, dw_sh_out = x.new_empty(0), x.new_empty(0)
+        return dx, d_router, dw_in, dw_out, dw_sh_in, dw_sh_out
 
     live, tok = _routed_rows(grad_out, w_in, w_sh_in, pad_offsets, n_post_pad)
     douts = K.permute(grad_out, ks, sorted_ids, live)
@@ -779,6 +800,47 @@ def _block_backward(ctx, grad_out, grad_aux, *unused):
 moe_block.register_autograd(_block_backward, setup_context=_block_setup)
 
 
+class _BlockFn(torch.autograd.Function):
+    """The same forward / backward as the registered op `moe_b200::moe_block`, as a plain autograd
+    node. Eager training calls go through this: a Python-registered torch.library op costs the
+    host ~100 us per call in dispatcher and schema work (twice per step), which at T = 16384 is a
+    quarter of what the GPU needs for the whole step. The registered ops remain what
+    torch.compile, fake tensors and opcheck see."""
+
+    @staticmethod
+    def forward(ctx, *inputs):
+        output = moe_block._init_fn(*inputs)
+        _block_setup(ctx, inputs, output)
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_out, grad_aux, *unused):
+        saved = list(ctx.saved_tensors)
+        x, w_in, w_out = saved[:3]
+        kept = saved[3:15]
+        rest = saved[15:]
+        w_sh_in, w_sh_out = (rest[0], rest[1]) if ctx.has_shared else (None, None)
+        noise = rest.pop() if ctx.has_noise else None
+        bias = rest[-1] if ctx.has_bias else None
+        if grad_out is None:
+            grad_out = torch.zeros_like(x)
+        dx, d_router, dw_in, dw_out, dsi, dso = moe_block_bwd._init_fn(
+            grad_out, grad_aux, x, bias, w_in, w_out, w_sh_in, w_sh_out, *kept, *ctx.args,
+            ctx.atomic_combine, noise)
+        d_router = d_router.to(ctx.router_dtype)
+        return (dx, d_router, None, dw_in, dw_out, dsi if ctx.has_shared else None,
+                dso if ctx.has_shared else None, None, None, None, None, None, None,
+                grad_out if ctx.has_residual else None, None, None, None)
+
+
+def _call_block(*args):
+    """moe_block through the light autograd node when a gradient is being recorded in plain eager
+    mode, through the registered op otherwise (no grad, tracing, compiling)."""
+    if args[12] and not torch.compiler.is_compiling():     # args[12] = save_for_backward
+        return _BlockFn.apply(*args)
+    return moe_block(*args)
+
+
 def fused_moe_block(x, router, w_in, w_out, w_sh_in, w_sh_out, activation, full_softmax,
                     combine: Optional[str] = None, noise: Optional[torch.Tensor] = None):
     """(out, aux_loss fp32, counts int32 [E]) for a TopKRouter-like `router` (attributes W,
@@ -791,10 +853,10 @@ def fused_moe_block(x, router, w_in, w_out, w_sh_in, w_sh_out, activation, full_
     bias = router.logit_bias
     if bias is not None:
         bias = bias.to(torch.float32).contiguous()
-    res = moe_block(x, cast(router.W), bias, cast(w_in), cast(w_out), cast(w_sh_in),
-                    cast(w_sh_out), router.top_k, bool(router.normalize_weights),
-                    bool(full_softmax), float(router.aux_loss_coef), activation, save, None,
-                    _atomic(combine), noise, _aux_reduce is not None)
+    res = _call_block(x, cast(router.W), bias, cast(w_in), cast(w_out), cast(w_sh_in),
+                      cast(w_sh_out), router.top_k, bool(router.normalize_weights),
+                      bool(full_softmax), float(router.aux_loss_coef), activation, save, None,
+                      _atomic(combine), noise, _aux_reduce is not None)
     aux = res[1]
     if full_softmax and _aux_reduce is not None:
         # this rank's share of the global loss: T_local / T_global, with T_global read off the

@@ -146,3 +146,28 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="no non-CUDA implementation"):
         _lib.load()
+
+
+def test_block_entry_points_validate_and_size_their_scratch(lib):
+    """moe_b200_block_fwd / _bwd: scratch sizes grow with the token count, bad shapes and NULL
+    pointers are refused before anything is launched."""
+    f = lib.moe_b200_block_fwd_scratch_bytes
+    b = lib.moe_b200_block_bwd_scratch_bytes
+    assert f(0, 576, 128, 76, 2, 6) == 0 and b(16, 576, 128, 76, 2, 77) == 0      # bad shapes
+    small, big = f(256, 576, 128, 76, 2, 6), f(16384, 576, 128, 76, 2, 6)
+    assert 0 < small < big
+    # hidden rows of every slot + the dispatch's histograms + the column sums
+    cap = O.l_cap(16384 * 8, 78)
+    assert cap * 128 * 2 <= big <= cap * 128 * 2 + (1 << 20)
+    assert b(16384, 576, 128, 76, 2, 6) > cap * (576 + 256 + 128) * 2
+    null = ctypes.c_void_p(0)
+    one = ctypes.c_void_p(256)      # never dereferenced: validation comes first
+    n_l = ctypes.c_int32(0)
+    fwd = lambda x, scratch, nbytes, top_k=6: lib.moe_b200_block_fwd(
+        x, 256, 576, one, null, null, one, one, 76, 128, one, one, 2, top_k, 1, 1, 0.01, 0,
+        one, one, one, one, one, one, one, one, one, one, one, one, one, one, one, scratch, nbytes,
+        ctypes.byref(n_l), one, null)
+    assert fwd(null, one, small) == -2           # MOE_B200_ERR_NULL
+    assert fwd(one, null, small) == -2
+    assert fwd(one, one, small - 1) == -4        # MOE_B200_ERR_SCRATCH
+    assert fwd(one, one, small, top_k=0) == -1   # MOE_B200_ERR_SHAPE

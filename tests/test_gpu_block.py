@@ -607,6 +607,72 @@ def test_exploration_noise_runs_inside_the_whole_block_op():
     kernels.check_status("cuda")
 
 
+@pytest.mark.parametrize("n_shared,noise_std,T", [(2, 0.0, 2048), (0, 0.0, 1000), (2, 0.5, 300)])
+def test_one_call_per_direction_equals_the_stage_sequence(n_shared, noise_std, T):
+    """The whole-block op's training form is issued by one call into the library per direction
+    (moe_b200_block_fwd / moe_b200_block_bwd, host code over the same stage entry points, three
+    streams inside the backward). Against the stage-by-stage sequence from Python on the same
+    inputs: the routing plan bit-equal, everything numeric within the atomic combine's ordering
+    noise; with and without shared experts, with exploration noise, T off the tile grid; through
+    the registered op as well as the autograd node eager calls use."""
+    from nanospeaker_b200 import MoEBlock, moe_kernel as MK, kernels
+    torch.manual_seed(31 + T)
+    m = MoEBlock(576, 76, d_ff=192, top_k=6, n_shared=n_shared, capacity_factor=None)
+    with torch.no_grad():
+        m.router.W.copy_(torch.randn(576, 76) * 0.02)
+        for p_ in (m.W_in, m.W_out) + ((m.W_sh_in, m.W_sh_out) if n_shared else ()):
+            p_.copy_(torch.randn_like(p_) * p_.shape[1] ** -0.5)
+    m = m.to(torch.bfloat16).cuda().train()
+    m.router.noise_std = noise_std
+    m.router.logit_bias = torch.randn(76, device="cuda") * 0.27
+    x = torch.randn(T, 576, device="cuda").bfloat16()
+    assert MK._ONE_CALL
+    res = {}
+    try:
+        for mode in (True, False):
+            MK._ONE_CALL = mode
+            xc = x.clone().requires_grad_(True)
+            for p in m.parameters():
+                p.grad = None
+            torch.manual_seed(5)                          # the same exploration noise in both runs
+            out = m(xc)
+            (out.float().square().mean() + m.aux_loss).backward()
+            res[mode] = dict(out=out.detach(), aux=m.aux_loss.detach().clone(),
+                             counts=m.expert_counts.clone(), dx=xc.grad,
+                             **{n: p.grad.clone() for n, p in m.named_parameters()
+                                if p.grad is not None})
+    finally:
+        MK._ONE_CALL = True
+    a, b = res[True], res[False]
+    assert a.keys() == b.keys() and "router.W" in a and ("W_sh_in" in a) == bool(n_shared)
+    assert torch.equal(a["counts"], b["counts"])
+    assert abs(float(a["aux"]) - float(b["aux"])) < 1e-5
+    for k in a:
+        if k not in ("counts", "aux"):
+            assert rel_l2(a[k], b[k]) < ATOMIC_TOL, k
+    # the registered op takes the same path: plan tensors bit-equal with the stage sequence
+    cast = lambda t: None if t is None else t.detach()
+    args = (x, cast(m.router.W), m.router.logit_bias.float().contiguous(), cast(m.W_in),
+            cast(m.W_out), cast(m.W_sh_in), cast(m.W_sh_out), 6, True, True, 0.01, "silu", True,
+            None, True, None, False)
+    with torch.no_grad():
+        one = torch.ops.moe_b200.moe_block(*args)
+        MK._ONE_CALL = False
+        try:
+            seq = torch.ops.moe_b200.moe_block(*args)
+        finally:
+            MK._ONE_CALL = True
+    live = int(one[12].item())
+    assert live == int(seq[12].item())
+    for i in (2, 10, 11, 13):                              # counts, offsets, counts_all, inv_ids
+        assert torch.equal(one[i], seq[i]), i
+    assert torch.equal(one[8][:live], seq[8][:live])       # sorted_ids
+    assert torch.equal(one[9][: live // 128], seq[9][: live // 128])
+    assert torch.equal(one[5], seq[5]) and torch.equal(one[6], seq[6])   # logits, weights
+    assert rel_l2(one[0], seq[0]) < ATOMIC_TOL
+    kernels.check_status("cuda")
+
+
 def test_global_balance_loss_shares_sum_to_the_loss_of_the_whole_batch():
     """Tokens sharded over two ranks (run one after the other on this GPU; the count exchange is a
     hook that adds the other rank's counts): each rank's aux_loss is its share of the balance loss
