@@ -493,6 +493,23 @@ int moe_b200_block_fwd(const void* x, int64_t n_tokens, int32_t d_model, const v
                        void* router_w_padded, void* scratch, size_t scratch_bytes,
                        int32_t* n_launches, int32_t* status, void* stream);
 
+/* The inference forward of the whole block in one call: out [T, D] = block(x) (+ residual [T, D]
+ * when given), nothing kept. router_w_padded [D, ld] is the router weight zero-padded to ld = E
+ * rounded up to 64 columns (moe_b200_copy_cols, built once per weight); the up/gate GEMM gathers
+ * the token rows itself; atomic_combine != 0 adds the rows in the down GEMM's epilogue (bf16
+ * atomics), 0 is the deterministic store-then-reduce combine. The caller of the decode loop
+ * (src/model/nanospeaker.py:254-269) makes this one call per layer. */
+size_t moe_b200_block_infer_scratch_bytes(int64_t n_tokens, int32_t d_model, int32_t d_hidden,
+                                          int32_t n_experts, int32_t n_shared, int32_t top_k);
+int moe_b200_block_infer(const void* x, int64_t n_tokens, int32_t d_model,
+                         const void* router_w_padded, const float* logit_bias, const void* w_in,
+                         const void* w_out, int32_t n_experts, int32_t d_hidden,
+                         const void* w_sh_in, const void* w_sh_out, int32_t n_shared,
+                         int32_t top_k, int32_t normalize, int32_t activation,
+                         const void* residual, int32_t atomic_combine, void* out, void* scratch,
+                         size_t scratch_bytes, int32_t* n_launches, int32_t* status,
+                         void* stream);
+
 /* The backward of moe_b200_block_fwd: grad_out [T, D] bf16, grad_aux (1 float on the device, or
  * NULL), the forward's inputs and kept tensors -> dx [T, D], d_router [D, E], dw_in, dw_out,
  * dw_sh_in, dw_sh_out (shapes of the weights; the last two NULL when n_shared == 0). After the

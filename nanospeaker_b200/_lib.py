@@ -102,6 +102,12 @@ SIGNATURES = {
         [_c_i32, _c_i32, _c_i64, _c_i32, _c_i32, _c_i32, ctypes.POINTER(_c_sz)]),
     "moe_b200_block_fwd_scratch_bytes": (_c_sz, [_c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32]),
     "moe_b200_block_bwd_scratch_bytes": (_c_sz, [_c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32]),
+    "moe_b200_block_infer_scratch_bytes": (_c_sz, [_c_i64, _c_i32, _c_i32, _c_i32, _c_i32, _c_i32]),
+    "moe_b200_block_infer": (
+        ctypes.c_int,
+        [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp, _c_i32,
+         _c_i32, _c_i32, _c_i32, _c_vp, _c_i32, _c_vp, _c_vp, _c_sz, ctypes.POINTER(_c_i32), _c_vp,
+         _c_vp]),
     "moe_b200_block_fwd": (
         ctypes.c_int,
         [_c_vp, _c_i64, _c_i32, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_i32, _c_i32, _c_vp, _c_vp,

@@ -87,6 +87,34 @@ FwdScratch carve_fwd(void* p, int64_t n_tokens, int32_t d_hidden, int32_t n_expe
   return f;
 }
 
+struct InferScratch {
+  void *logits, *w_all, *hid, *y, *block_hist;
+  int64_t* idx_all;
+  int32_t *sorted_ids, *expert_ids, *pad_offsets, *counts, *n_post_pad, *inv_ids;
+  size_t block_hist_bytes, total;
+};
+InferScratch carve_infer(void* p, int64_t n_tokens, int32_t d_model, int32_t d_hidden,
+                         int32_t n_experts, int32_t n_shared, int32_t top_k) {
+  const Sizes z = sizes(n_tokens, n_experts, n_shared, top_k);
+  Carver c(p);
+  InferScratch f;
+  f.logits = c.take(size_t(n_tokens) * z.ld * 2);
+  f.w_all = c.take(size_t(z.m) * 2);
+  f.idx_all = static_cast<int64_t*>(c.take(size_t(z.m) * 8));
+  f.sorted_ids = static_cast<int32_t*>(c.take(size_t(z.l_cap) * 4));
+  f.expert_ids = static_cast<int32_t*>(c.take(size_t(z.l_cap / 128 + 1) * 4));
+  f.pad_offsets = static_cast<int32_t*>(c.take(size_t(z.n_all + 1) * 4));
+  f.counts = static_cast<int32_t*>(c.take(size_t(z.n_all) * 4));
+  f.n_post_pad = static_cast<int32_t*>(c.take(4));
+  f.inv_ids = static_cast<int32_t*>(c.take(size_t(z.m) * 4));
+  f.block_hist_bytes = moe_b200_router_dispatch_scratch_bytes(n_tokens, z.n_all);
+  f.block_hist = c.take(f.block_hist_bytes);
+  f.hid = c.take(size_t(z.l_cap) * d_hidden * 2);
+  f.y = c.take(size_t(z.l_cap) * d_model * 2);
+  f.total = c.used;
+  return f;
+}
+
 struct BwdScratch {
   void *douts, *da1, *hidw, *dtw, *dl, *d_router_padded, *part_in, *part_out, *part_r;
   size_t part_in_bytes, part_out_bytes, part_r_bytes, total;
@@ -136,6 +164,56 @@ size_t moe_b200_block_fwd_scratch_bytes(int64_t n_tokens, int32_t d_model, int32
                                         int32_t n_experts, int32_t n_shared, int32_t top_k) {
   if (bad_shape(n_tokens, d_model, d_hidden, n_experts, n_shared, top_k)) return 0;
   return carve_fwd(nullptr, n_tokens, d_hidden, n_experts, n_shared, top_k).total;
+}
+
+size_t moe_b200_block_infer_scratch_bytes(int64_t n_tokens, int32_t d_model, int32_t d_hidden,
+                                          int32_t n_experts, int32_t n_shared, int32_t top_k) {
+  if (bad_shape(n_tokens, d_model, d_hidden, n_experts, n_shared, top_k)) return 0;
+  return carve_infer(nullptr, n_tokens, d_model, d_hidden, n_experts, n_shared, top_k).total;
+}
+
+int moe_b200_block_infer(const void* x, int64_t n_tokens, int32_t d_model,
+                         const void* router_w_padded, const float* logit_bias, const void* w_in,
+                         const void* w_out, int32_t n_experts, int32_t d_hidden,
+                         const void* w_sh_in, const void* w_sh_out, int32_t n_shared,
+                         int32_t top_k, int32_t normalize, int32_t activation,
+                         const void* residual, int32_t atomic_combine, void* out, void* scratch,
+                         size_t scratch_bytes, int32_t* n_launches, int32_t* status,
+                         void* stream) {
+  if (bad_shape(n_tokens, d_model, d_hidden, n_experts, n_shared, top_k)) return MOE_B200_ERR_SHAPE;
+  if (!x || !router_w_padded || !w_in || !w_out || !out || !scratch || !status)
+    return MOE_B200_ERR_NULL;
+  if (n_shared > 0 && (!w_sh_in || !w_sh_out)) return MOE_B200_ERR_NULL;
+  const InferScratch f = carve_infer(scratch, n_tokens, d_model, d_hidden, n_experts, n_shared, top_k);
+  if (scratch_bytes < f.total) return MOE_B200_ERR_SCRATCH;
+  const Sizes z = sizes(n_tokens, n_experts, n_shared, top_k);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int launched = 0;
+  STEP(moe_b200_down_gemm(x, n_tokens, d_model, router_w_padded, 1, nullptr, 0, z.ld, nullptr,
+                          nullptr, 1, nullptr, nullptr, 0, f.logits, nullptr, status, stream));
+  STEP(moe_b200_router_dispatch(f.logits, z.ld, logit_bias, nullptr, n_tokens, n_experts, top_k,
+                                n_shared, normalize, 0, f.w_all, f.idx_all, nullptr, f.sorted_ids,
+                                f.expert_ids, f.pad_offsets, f.counts, f.n_post_pad, f.inv_ids,
+                                f.block_hist, f.block_hist_bytes, status, stream));
+  if (n_tokens > 128) ++launched;   // the dispatch's scatter pass is a launch of its own
+  // up/gate GEMM gathering the token rows itself (no permuted copy), then down GEMM + combine
+  STEP(moe_b200_up_gemm(x, z.l_cap, d_model, w_in, n_experts, w_sh_in, n_shared, d_hidden,
+                        f.expert_ids, f.n_post_pad, 0, f.sorted_ids, z.ks, z.m, activation, f.hid,
+                        nullptr, nullptr, 0, nullptr, nullptr, status, stream));
+  if (atomic_combine) {
+    if (residual) STEP(copy_words(residual, out, n_tokens * d_model / 2, st));
+    else STEP(zero_words(out, n_tokens * d_model / 2, st));
+    STEP(moe_b200_down_gemm_acc(f.hid, z.l_cap, d_hidden, w_out, n_experts, w_sh_out, n_shared,
+                                d_model, f.expert_ids, f.n_post_pad, 0, f.sorted_ids, f.w_all,
+                                z.m, z.ks, out, n_tokens, nullptr, status, stream));
+  } else {
+    STEP(moe_b200_down_gemm(f.hid, z.l_cap, d_hidden, w_out, n_experts, w_sh_out, n_shared,
+                            d_model, f.expert_ids, f.n_post_pad, 0, f.sorted_ids, f.w_all, z.m,
+                            f.y, nullptr, status, stream));
+    STEP(moe_b200_combine(f.y, f.inv_ids, n_tokens, z.ks, d_model, residual, nullptr, out, stream));
+  }
+  if (n_launches) *n_launches = launched;
+  return MOE_B200_OK;
 }
 
 size_t moe_b200_block_bwd_scratch_bytes(int64_t n_tokens, int32_t d_model, int32_t d_hidden,

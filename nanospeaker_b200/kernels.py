@@ -584,6 +584,29 @@ def block_fwd(x, router_w, logit_bias, noise, w_in, w_out, w_sh_in, w_sh_out, to
             inv, wp)
 
 
+def block_infer(x, router_w_padded, logit_bias, w_in, w_out, w_sh_in, w_sh_out, top_k: int,
+                normalize: bool, act: int, residual, atomic: bool) -> torch.Tensor:
+    """moe_b200_block_infer: the inference forward of the whole block (+ residual) by one C call."""
+    import ctypes
+    _need_cuda(x, w_in, w_out)
+    t, d = x.shape
+    e_n, _, h2 = w_in.shape
+    s_n = 0 if w_sh_in is None else w_sh_in.shape[0]
+    out = torch.empty_like(x)
+    lib = _lib.load()
+    nbytes = lib.moe_b200_block_infer_scratch_bytes(t, d, h2 // 2, e_n, s_n, top_k)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    n_l = ctypes.c_int32(0)
+    _lib.check(lib.moe_b200_block_infer(
+        x.data_ptr(), t, d, router_w_padded.data_ptr(), _lib.ptr(logit_bias), w_in.data_ptr(),
+        w_out.data_ptr(), e_n, h2 // 2, _lib.ptr(w_sh_in), _lib.ptr(w_sh_out), s_n, top_k,
+        int(normalize), act, _lib.ptr(residual), int(atomic), out.data_ptr(), scratch.data_ptr(),
+        nbytes, ctypes.byref(n_l), status_word(x.device).data_ptr(), _stream(x)),
+        "moe_b200_block_infer")
+    _count(n_l.value)
+    return out
+
+
 def block_bwd(grad_out, grad_aux, x, logit_bias, noise, w_in, w_out, w_sh_in, w_sh_out, xs, a1,
               logits, w_all, idx_all, sids, eids, offs, counts_all, npp, wp, top_k: int,
               normalize: bool, full_softmax: bool, aux_coef: float, act: int, side_streams):

@@ -879,13 +879,17 @@ def moe_block_inference(x, router_w_padded, logit_bias, w_in, w_out, w_sh_in, w_
                         combine: Optional[str] = None) -> torch.Tensor:
     """Forward of the whole block for a caller that wants nothing but `out` (+ residual): the
     launches of moe_block's inference branch without its per-call extras (the padded copy of the
-    router weight, the counts tensor, the zero balance loss). Six launches: logits GEMM, router
-    top-k, dispatch, up/gate GEMM on gathered rows, down GEMM, combine (the residual rides in its
-    fp32 sum). x [T, D] bf16 contiguous; weights already in x.dtype."""
+    router weight, the counts tensor, the zero balance loss). Logits GEMM, router top-k + dispatch
+    (one launch up to 128 tokens, else two), up/gate GEMM on gathered rows, down GEMM, combine (the
+    residual rides in its fp32 sum); issued by one call into the library (moe_b200_block_infer). x [T, D] bf16 contiguous; weights already in x.dtype."""
     act = _act_id(activation)
     n, _ = x.shape
     s_n = 0 if w_sh_in is None else w_sh_in.shape[0]
     ks = top_k + s_n
+    if _ONE_CALL and n > 0:
+        return K.block_infer(x, router_w_padded, logit_bias, w_in, w_out, w_sh_in, w_sh_out, top_k,
+                             normalize, act, None if residual is None else residual.contiguous(),
+                             _atomic(combine))
     logits = K.down_gemm(x, router_w_padded, None, None, 1, None, None, 0)[0]
     w_all, _, _, sids, eids, _, _, npp, inv = K.router_dispatch(
         logits, logit_bias, n_experts, top_k, s_n, normalize, False)

@@ -673,6 +673,30 @@ def test_one_call_per_direction_equals_the_stage_sequence(n_shared, noise_std, T
     kernels.check_status("cuda")
 
 
+@pytest.mark.parametrize("T", [1, 64, 129, 2048])
+def test_one_call_inference_block_equals_the_stage_sequence(T):
+    """moe_b200_block_infer (one call per layer of a decode stack) against the same launches issued
+    one by one: bit-identical with the deterministic combine, residual included."""
+    from nanospeaker_b200 import moe_kernel as MK, kernels
+    x, m, _ = _model_shape_pair(T, train=False, seed=T)
+    xc = x.cuda()
+    wp = MK.pad_router_weight(m.router.W.detach(), xc.dtype)
+    args = (wp, None, m.W_in.detach(), m.W_out.detach(), m.W_sh_in.detach(), m.W_sh_out.detach(),
+            76, 6, True, "silu")
+    assert MK._ONE_CALL
+    one = MK.moe_block_inference(xc, *args, residual=xc, combine="store")
+    one_atomic = MK.moe_block_inference(xc, *args, residual=None, combine="atomic")
+    MK._ONE_CALL = False
+    try:
+        seq = MK.moe_block_inference(xc, *args, residual=xc, combine="store")
+        seq_plain = MK.moe_block_inference(xc, *args, residual=None, combine="store")
+    finally:
+        MK._ONE_CALL = True
+    assert torch.equal(one, seq)
+    assert rel_l2(one_atomic, seq_plain) < ATOMIC_TOL
+    kernels.check_status("cuda")
+
+
 def test_global_balance_loss_shares_sum_to_the_loss_of_the_whole_batch():
     """Tokens sharded over two ranks (run one after the other on this GPU; the count exchange is a
     hook that adds the other rank's counts): each rank's aux_loss is its share of the balance loss
