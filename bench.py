@@ -1185,9 +1185,14 @@ def run_side_workload(args):
         launches = K.LAUNCHES - l0
         eager_ms = time_loop(lambda i: stack.eager(xs[i % 8]))
         ms = time_loop(lambda i: stack.step(xs[i % 8]))
+        # the same stack with the combine in the down GEMM's epilogue (one launch fewer per block;
+        # bf16 atomics, so not bit-reproducible from run to run: not the decoder's default)
+        stack_atomic = StackedMoEDecoder(stack.blocks, combine="atomic")
+        ms_atomic = time_loop(lambda i: stack_atomic.step(xs[i % 8]))
         line = {"metric": "MoE decode stack latency (20 blocks, forward)", "value": ms,
                 "unit": "ms", "higher_is_better": False, "tokens_per_s": T / (ms / 1e3),
                 "eager_ms": eager_ms, "gpu_launches_per_step": launches,
+                "atomic_combine_ms": ms_atomic,
                 "config": {"workload": "BASELINE config 3: 20 stacked MoE blocks (independent "
                                        "weights), T=64 tokens, bf16, forward, one CUDA graph"}}
     else:
