@@ -629,8 +629,9 @@ def test_one_call_per_direction_equals_the_stage_sequence(n_shared, noise_std, T
     assert MK._ONE_CALL
     res = {}
     try:
-        for mode in (True, False):
-            MK._ONE_CALL = mode
+        for mode in (True, False, "one stream"):
+            MK._ONE_CALL = bool(mode)
+            MK._DEBUG_ONE_STREAM = mode == "one stream"   # the backward's branches in line
             xc = x.clone().requires_grad_(True)
             for p in m.parameters():
                 p.grad = None
@@ -642,7 +643,10 @@ def test_one_call_per_direction_equals_the_stage_sequence(n_shared, noise_std, T
                              **{n: p.grad.clone() for n, p in m.named_parameters()
                                 if p.grad is not None})
     finally:
-        MK._ONE_CALL = True
+        MK._ONE_CALL, MK._DEBUG_ONE_STREAM = True, False
+    for k_ in res[True]:
+        if k_ not in ("counts", "aux"):
+            assert rel_l2(res["one stream"][k_], res[True][k_]) < ATOMIC_TOL, k_
     a, b = res[True], res[False]
     assert a.keys() == b.keys() and "router.W" in a and ("W_sh_in" in a) == bool(n_shared)
     assert torch.equal(a["counts"], b["counts"])
