@@ -200,7 +200,7 @@ def workload_config(n_gpus, tokens_per_gpu=TOKENS):
         "tokens_per_gpu": tokens_per_gpu, "global_tokens": tokens_per_gpu * n_gpus,
         "skew": f"{SKEW_NAME}: per-expert logit bias N(0,{BIAS_STD}), seed 1",
         "parallelism": f"token-sharded replicas x{n_gpus}: no collective on the data path" +
-                       ("; the weight gradients are all-reduced over the ranks every step (NCCL), "
+                       ("; the weight gradients are all-reduced over the ranks every step, "
                         "inside the timed region" if n_gpus > 1 else ""),
         "l2": f"{N_INPUT_SETS} input/dOut sets cycled (302 MB) and ~1 GB of intermediates per "
               "step, both beyond the 126 MB L2; no explicit flush",
@@ -560,10 +560,11 @@ def run_ours(args):
     warmup = max(args.warmup, 3)
     use_graph = not args.no_graph
     # N > 1: the data-parallel training step. Every rank's weight gradients (34.6 MB in bf16) are
-    # summed over the ranks inside the timed region: the step's graph is replayed, then one flattened
-    # NCCL all-reduce runs on a communication stream under the NEXT step's compute (what a trainer
-    # does between two micro-steps); the barrier that ends the timed region waits for the last one.
-    # --no-grad-allreduce times the bare replicas instead.
+    # summed over the ranks inside the timed region: the step's graph is replayed, then the flattened
+    # bucket is all-reduced on a communication stream under the NEXT step's compute (what a trainer
+    # does between two micro-steps) -- by device-to-device copies through peer memory
+    # (--grad-allreduce-impl peer, the default) or by NCCL; the barrier that ends the timed region
+    # waits for the last one. --no-grad-allreduce times the bare replicas instead.
     with_comm = world > 1 and not args.no_grad_allreduce
     eager_ms, _, _ = timed(step, args.steps, warmup)
     if use_graph:
@@ -575,29 +576,52 @@ def run_ours(args):
         per_step_launches = graph_sets[0][2]
 
         comm_stream = torch.cuda.Stream()
-        computed, flattened = torch.cuda.Event(), torch.cuda.Event()
+        computed = torch.cuda.Event()
+        flattened = {}    # per graph / gradient-buffer set: its last flatten copy
         n_grad = sum(g.numel() for g in graph_sets[0][3])
         bucket = torch.empty(n_grad, dtype=torch.bfloat16, device=dev)
+        peer_ar = None
+        if with_comm and args.grad_allreduce_impl == "peer":
+            # the sum through peer memory and the copy engines (parallel.PeerGradAllReduce): no
+            # collective kernel sits on SMs the persistent GEMMs want; NCCL if it cannot be set up
+            try:
+                from nanospeaker_b200.parallel import PeerGradAllReduce
+                peer_ar = PeerGradAllReduce(n_grad, dev)
+            except Exception as exc:       # symmetric memory unavailable on this box
+                if rank == 0:
+                    print(f"peer-memory all-reduce unavailable ({exc}); using NCCL", file=sys.stderr)
 
-        def reduce_grads(grads):
+        def reduce_grads(grads, key):
             """Flatten this step's gradients into the bucket and all-reduce it, on the
-            communication stream; the compute stream only waits for the flatten copy before the
-            next replay overwrites the gradients."""
+            communication stream. Every graph owns its gradient buffers, so the compute stream
+            does not wait here: a graph waits for ITS last flatten copy before it is replayed
+            again (`before_replay`), several steps later."""
             computed.record()
             with torch.cuda.stream(comm_stream):
                 comm_stream.wait_event(computed)
-                torch.cat([g.reshape(-1) for g in grads], out=bucket)
-                flattened.record(comm_stream)
-                dist.all_reduce(bucket)
-            torch.cuda.current_stream().wait_event(flattened)
+                if peer_ar is not None:
+                    peer_ar.fill(grads)
+                else:
+                    torch.cat([g.reshape(-1) for g in grads], out=bucket)
+                flattened.setdefault(key, torch.cuda.Event()).record(comm_stream)
+                if peer_ar is not None:
+                    peer_ar()
+                else:
+                    dist.all_reduce(bucket)
+
+        def before_replay(key):
+            if key in flattened:
+                torch.cuda.current_stream().wait_event(flattened[key])
 
         def replica_step(i):
             graph_sets[i % N_INPUT_SETS][0].replay()
 
         def value_step(i):
+            if with_comm:
+                before_replay(("value", i % N_INPUT_SETS))
             graph_sets[i % N_INPUT_SETS][0].replay()
             if with_comm:
-                reduce_grads(graph_sets[i % N_INPUT_SETS][3])
+                reduce_grads(graph_sets[i % N_INPUT_SETS][3], ("value", i % N_INPUT_SETS))
 
         # e2e: two input buffers / graphs in ping-pong. The pinned-host -> device copy of step i+1
         # runs on a copy stream while step i computes (what an input pipeline does), and the loss
@@ -626,10 +650,12 @@ def run_ours(args):
                 prefetch(i)
                 state["pending"] = None
             torch.cuda.current_stream().wait_event(copied[b])
+            if with_comm:
+                before_replay(("e2e", b))
             e2e_graphs[b][0].replay()
             consumed[b].record()
             if with_comm:
-                reduce_grads(e2e_graphs[b][3])
+                reduce_grads(e2e_graphs[b][3], ("e2e", b))
             prefetch(i + 1)                               # H2D of the next step's input
             with torch.cuda.stream(d2h_stream):           # D2H of this step's loss
                 d2h_stream.wait_event(consumed[b])
@@ -662,7 +688,10 @@ def run_ours(args):
         # the all-reduce alone, back to back on the communication stream
         def comm_only(i):
             with torch.cuda.stream(comm_stream):
-                dist.all_reduce(bucket)
+                if peer_ar is not None:
+                    peer_ar()
+                else:
+                    dist.all_reduce(bucket)
             torch.cuda.current_stream().wait_stream(comm_stream)
         comm_ms, _, _ = timed(comm_only, args.steps, warmup)
     # the same step through the package's graph wrapper (what a trainer calls instead of the bench's
@@ -716,8 +745,12 @@ def run_ours(args):
         if with_comm and replica_ms is not None:
             line["grad_allreduce_detail"] = {
                 "what": "weight gradients of the block summed over the ranks: one flattened bf16 "
-                        "bucket, ncclAllReduce on a communication stream under the next step's "
-                        "compute; inside the timed region",
+                        "bucket, " + ("reduce-scatter + all-gather by device-to-device copies "
+                                      "through peer memory (copy engines) with a local fp32 sum"
+                                      if peer_ar is not None else "ncclAllReduce")
+                        + " on a communication stream under the next step's compute; inside the "
+                          "timed region",
+                "how": "peer" if peer_ar is not None else "nccl",
                 "bytes": int(n_grad) * 2,
                 "allreduce_alone_ms": comm_ms / args.steps,
                 "allreduce_bus_gbs": 2 * (world - 1) / world * n_grad * 2 / (comm_ms / args.steps * 1e-3) / 1e9,
@@ -1221,6 +1254,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--grad-allreduce-impl", default="peer", choices=["nccl", "peer"],
+                    help="N > 1: how the weight gradients are summed over the ranks: device-to-"
+                         "device copies through peer memory (parallel.PeerGradAllReduce; NCCL if "
+                         "symmetric memory cannot be set up), or an NCCL all-reduce")
     ap.add_argument("--no-grad-allreduce", action="store_true",
                     help="N > 1: time the bare token-sharded replicas, without the gradient all-reduce")
     ap.add_argument("--grad-allreduce", action="store_true",

@@ -347,3 +347,59 @@ def test_push_pull_ranks_without_shared_experts():
         assert rel_l2(grads[r][3], m.W_out.grad[lo:hi].float()) < TOL
     assert rel_l2(sum(g[1].float() for g in grads), m.router.W.grad.float()) < 2e-2
     kernels.check_status("cuda")
+
+
+def _peer_allreduce_worker(rank, world, port, q):
+    try:
+        import os
+        import datetime
+        import torch.distributed as dist
+        from nanospeaker_b200.parallel import PeerGradAllReduce
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                                timeout=datetime.timedelta(seconds=120))
+        numel = 1_000_003                      # not a multiple of anything: padded chunks
+        ar = PeerGradAllReduce(numel, dev)
+        worst = 0.0
+        for it in range(4):                    # both buffer parities, twice
+            g = torch.Generator(device="cpu").manual_seed(100 * it + rank)
+            grads = [torch.randn(1000, 777, generator=g).bfloat16().to(dev),
+                     torch.randn(numel - 777000, generator=g).bfloat16().to(dev)]
+            ar.fill(grads)
+            want = ar.bucket[:numel].clone()
+            dist.all_reduce(want)
+            got = ar()
+            torch.cuda.synchronize()
+            worst = max(worst, float((got.float() - want.float()).abs().max()))
+        q.put((rank, worst, int(got.numel()), 0, 0))
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)       # (symmetric-memory buffers: leave without tearing the group down)
+    except Exception as exc:
+        _report_and_leave(q, rank, repr(exc))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpus_peer_memory_gradient_allreduce_equals_nccl():
+    """parallel.PeerGradAllReduce (reduce-scatter + all-gather by device-to-device copies through
+    peer memory, local fp32 sum in rank order) against ncclAllReduce on the same bf16 bucket: at
+    two ranks both round one fp32 sum per element, so the results are bit-equal."""
+    import socket
+    import torch.multiprocessing as mp
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_peer_allreduce_worker, args=(r, world, port, q))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    got = _collect(procs, q, world)
+    for r in range(world):
+        worst, numel = got[r][0], got[r][1]
+        assert numel == 1_000_003
+        assert worst == 0.0, f"rank {r}: max abs diff {worst}"
