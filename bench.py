@@ -567,9 +567,9 @@ def run_ours(args):
     # N > 1: the data-parallel training step. Every rank's weight gradients (34.6 MB in bf16) are
     # summed over the ranks inside the timed region: the step's graph is replayed, then the flattened
     # bucket is all-reduced on a communication stream under the NEXT step's compute (what a trainer
-    # does between two micro-steps) -- by device-to-device copies through peer memory
-    # (--grad-allreduce-impl peer, the default) or by NCCL; the barrier that ends the timed region
-    # waits for the last one. --no-grad-allreduce times the bare replicas instead.
+    # does between two micro-steps) -- by device-to-device copies through peer memory (up to 4
+    # ranks) or by NCCL (--grad-allreduce-impl); the barrier that ends the timed region waits for
+    # the last one. --no-grad-allreduce times the bare replicas instead.
     with_comm = world > 1 and not args.no_grad_allreduce
     eager_ms, _, _ = timed(step, args.steps, warmup)
     if use_graph:
@@ -586,7 +586,10 @@ def run_ours(args):
         n_grad = sum(g.numel() for g in graph_sets[0][3])
         bucket = torch.empty(n_grad, dtype=torch.bfloat16, device=dev)
         peer_ar = None
-        if with_comm and args.grad_allreduce_impl == "peer":
+        impl = args.grad_allreduce_impl
+        if impl == "auto":
+            impl = "peer" if world <= 4 else "nccl"
+        if with_comm and impl == "peer":
             # the sum through peer memory and the copy engines (parallel.PeerGradAllReduce): no
             # collective kernel sits on SMs the persistent GEMMs want; NCCL if it cannot be set up
             try:
@@ -1259,10 +1262,12 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--grad-allreduce-impl", default="peer", choices=["nccl", "peer"],
+    ap.add_argument("--grad-allreduce-impl", default="auto", choices=["auto", "nccl", "peer"],
                     help="N > 1: how the weight gradients are summed over the ranks: device-to-"
                          "device copies through peer memory (parallel.PeerGradAllReduce; NCCL if "
-                         "symmetric memory cannot be set up), or an NCCL all-reduce")
+                         "symmetric memory cannot be set up), or an NCCL all-reduce. auto: peer "
+                         "up to 4 ranks, NCCL beyond (measured: at 8 ranks NCCL's in-switch "
+                         "reduction takes 0.17 ms alone, the 14 copies per rank 0.44 ms)")
     ap.add_argument("--compute-priority", type=int, default=0,
                     help="1: capture the step on a high-priority stream")
     ap.add_argument("--no-grad-allreduce", action="store_true",
