@@ -497,8 +497,6 @@ def run_ours(args):
     static_x = dev_x[0].clone().requires_grad_(True)
     static_dout = dev_dout[0].clone()
 
-    capture_stream = torch.cuda.Stream(priority=-1) if args.compute_priority else torch.cuda.Stream()
-
     def capture(with_loss, static_x=static_x, static_dout=static_dout):
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -523,10 +521,7 @@ def run_ours(args):
         static_x.grad = None
         graph = torch.cuda.CUDAGraph()
         l0 = K.LAUNCHES
-        # captured on a high-priority stream: the step's kernel nodes keep that priority, so the
-        # gradient all-reduce's kernels on the (default-priority) communication stream only get the
-        # SMs the step's persistent GEMMs leave free
-        with torch.cuda.graph(graph, stream=capture_stream):
+        with torch.cuda.graph(graph):
             out = m(static_x)
             if with_loss:
                 loss = mean_loss(out) + m.aux_loss
@@ -1268,8 +1263,6 @@ def main():
                          "symmetric memory cannot be set up), or an NCCL all-reduce. auto: peer "
                          "up to 4 ranks, NCCL beyond (measured: at 8 ranks NCCL's in-switch "
                          "reduction takes 0.17 ms alone, the 14 copies per rank 0.44 ms)")
-    ap.add_argument("--compute-priority", type=int, default=0,
-                    help="1: capture the step on a high-priority stream")
     ap.add_argument("--no-grad-allreduce", action="store_true",
                     help="N > 1: time the bare token-sharded replicas, without the gradient all-reduce")
     ap.add_argument("--grad-allreduce", action="store_true",
