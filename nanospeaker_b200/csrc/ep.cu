@@ -161,7 +161,19 @@ __global__ void __launch_bounds__(256)
     const int64_t row = __ldg(pair_row + pair);
     const Chunk16* from = src + int64_t(pair / k_all) * chunks_per_row;
     Chunk16* to = static_cast<Chunk16*>(rows.p[r]) + row * chunks_per_row;
-    for (int c = lane; c < chunks_per_row; c += 32) to[c] = from[c];
+    // a lane's loads of the row are all issued before its first (remote) store: written as one
+    // load-store pair per iteration they ran one after the other, each behind the store before it
+    // (push x 0.47 -> 0.45 ms on two GPUs; 32-byte pieces on top of that changed nothing)
+    constexpr int INFLIGHT = 4;
+    for (int c0 = lane; c0 < chunks_per_row; c0 += 32 * INFLIGHT) {
+      Chunk16 v[INFLIGHT];
+#pragma unroll
+      for (int u = 0; u < INFLIGHT; ++u)
+        if (c0 + 32 * u < chunks_per_row) v[u] = from[c0 + 32 * u];
+#pragma unroll
+      for (int u = 0; u < INFLIGHT; ++u)
+        if (c0 + 32 * u < chunks_per_row) to[c0 + 32 * u] = v[u];
+    }
     if (lane == 0 && sid.p[r] != nullptr) static_cast<int32_t*>(sid.p[r])[row] = int32_t(row);
     if (lane == 1 && pw.p[r] != nullptr) static_cast<__nv_bfloat16*>(pw.p[r])[row] = w_all[pair];
   }
