@@ -3,38 +3,111 @@
 // down GEMM with the atomic combine, balance loss; and the backward with its three independent
 // branches on three streams) issued from C++, for hosts that pay per call into this library -- a
 // Python caller's ~22 ctypes calls per step cost it more than the GPU needs for the work.
-// Everything here is host code over the other entry points of include/moe_b200.h, plus two
-// trivial kernels (zero / copy a few words): memset and device-to-device copy nodes go to a copy
-// engine, where they queue behind a caller's large host-to-device copy in flight (the end-to-end
-// step lost 13 us to that). Training form only: pre-activations and permuted rows are kept,
+// Everything here is host code over the other entry points of include/moe_b200.h, plus four
+// trivial kernels: zero / copy a few words (memset and device-to-device copy nodes go to a copy
+// engine, where they queue behind a caller's large host-to-device copy in flight: the end-to-end
+// step lost 13 us to that), and the forward's first and last launch, which fold what would
+// otherwise be small launches of their own on the critical path (pad the router weight + clear
+// the column sums; counts for the caller + balance loss). All of them wait for their
+// predecessors programmatically like the library's other kernels, so none of them breaks the
+// chain of early launches. Training form only: pre-activations and permuted rows are kept,
 // combine mode "atomic", no residual, no per-expert biases.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include "../../include/moe_b200.h"
+#include "pdl.cuh"
 
 namespace {
 
 __global__ void zero_words_kernel(uint32_t* dst, int64_t n) {
+  moe::pdl_trigger();
+  moe::pdl_wait();
   for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < n;
        i += int64_t(gridDim.x) * blockDim.x)
     dst[i] = 0u;
 }
 __global__ void copy_words_kernel(const uint32_t* src, uint32_t* dst, int64_t n) {
+  moe::pdl_trigger();
+  moe::pdl_wait();
   for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < n;
        i += int64_t(gridDim.x) * blockDim.x)
     dst[i] = src[i];
 }
 inline int zero_words(void* dst, int64_t n_words, cudaStream_t st) {
   const int64_t blocks = (n_words + 255) / 256;
-  zero_words_kernel<<<unsigned(blocks < 592 ? blocks : 592), 256, 0, st>>>(
-      static_cast<uint32_t*>(dst), n_words);
+  moe::launch_pdl(zero_words_kernel, dim3(unsigned(blocks < 592 ? blocks : 592)), dim3(256), 0, st,
+                  static_cast<uint32_t*>(dst), n_words);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 inline int copy_words(const void* src, void* dst, int64_t n_words, cudaStream_t st) {
   const int64_t blocks = (n_words + 255) / 256;
-  copy_words_kernel<<<unsigned(blocks < 592 ? blocks : 592), 256, 0, st>>>(
-      static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), n_words);
+  moe::launch_pdl(copy_words_kernel, dim3(unsigned(blocks < 592 ? blocks : 592)), dim3(256), 0, st,
+                  static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), n_words);
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+// The forward's first launch: the router weight [D, E] zero-padded to [D, ld] (what
+// moe_b200_copy_cols does) and, in the same launch, the column sums of the balance loss cleared.
+__global__ void __launch_bounds__(256)
+    pad_router_kernel(const uint16_t* __restrict__ src, int64_t rows, int32_t cols,
+                      uint16_t* __restrict__ dst, int32_t dst_ld, float* __restrict__ colsum) {
+  moe::pdl_trigger();
+  moe::pdl_wait();
+  const int64_t first = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (colsum != nullptr && first < cols) colsum[first] = 0.f;
+  const int64_t total = rows * dst_ld;
+  for (int64_t i = first; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t r = i / dst_ld;
+    const int32_t c = int32_t(i - r * dst_ld);
+    dst[i] = c < cols ? src[r * cols + c] : uint16_t(0);
+  }
+}
+inline int pad_router(const void* src, int64_t rows, int32_t cols, void* dst, int32_t dst_ld,
+                      float* colsum, cudaStream_t st) {
+  int64_t blocks = (rows * dst_ld + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks * 256 < cols) return MOE_B200_ERR_SHAPE;   // (the clearing threads are the first `cols`)
+  moe::launch_pdl(pad_router_kernel, dim3(unsigned(blocks)), dim3(256), 0, st,
+                  static_cast<const uint16_t*>(src), rows, cols, static_cast<uint16_t*>(dst),
+                  dst_ld, colsum);
+  return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
+}
+
+// The forward's last launch: the routed experts' counts for the caller and the balance loss
+// aux = coef * E * sum_e (counts[e] / sum counts) * (colsum[e] / T) -- the arithmetic of
+// moe_b200_balance_loss, same order -- or zero when the loss is off (colsum == nullptr). One warp.
+__global__ void finish_fwd_kernel(const int32_t* __restrict__ counts_all,
+                                  int32_t* __restrict__ counts, const float* __restrict__ colsum,
+                                  int n_experts, int64_t n_tokens, float coef,
+                                  float* __restrict__ aux) {
+  moe::pdl_trigger();
+  moe::pdl_wait();
+  const int lane = threadIdx.x;
+  float dot = 0.f, tot = 0.f;
+  for (int e = lane; e < n_experts; e += 32) {
+    const int32_t ci = counts_all[e];
+    counts[e] = ci;
+    if (colsum != nullptr) {
+      const float c = float(ci);
+      dot += c * colsum[e];
+      tot += c;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    tot += __shfl_xor_sync(0xffffffffu, tot, o);
+  }
+  if (lane == 0)
+    aux[0] = colsum == nullptr ? 0.f
+                               : coef * float(n_experts) * dot / fmaxf(tot, 1.f) /
+                                     float(n_tokens > 0 ? n_tokens : 1);
+}
+inline int finish_fwd(const int32_t* counts_all, int32_t* counts, const float* colsum,
+                      int n_experts, int64_t n_tokens, float coef, float* aux, cudaStream_t st) {
+  moe::launch_pdl(finish_fwd_kernel, dim3(1), dim3(32), 0, st, counts_all, counts, colsum,
+                  n_experts, n_tokens, coef, aux);
   return cudaGetLastError() == cudaSuccess ? MOE_B200_OK : MOE_B200_ERR_CUDA;
 }
 
@@ -251,11 +324,10 @@ int moe_b200_block_fwd(const void* x, int64_t n_tokens, int32_t d_model, const v
   const int32_t* first_shared = pad_offsets + n_experts;   // start of the first shared run
 
   // router: zero-padded weight, logits GEMM (one fixed group, no pair weights), routing + dispatch
-  STEP(moe_b200_copy_cols(router_w, d_model, n_experts, n_experts, router_w_padded, z.ld, stream));
+  float* colsum = full_softmax ? f.colsum : nullptr;
+  STEP(pad_router(router_w, d_model, n_experts, router_w_padded, z.ld, colsum, st));
   STEP(moe_b200_down_gemm(x, n_tokens, d_model, router_w_padded, 1, nullptr, 0, z.ld, nullptr,
                           nullptr, 1, nullptr, nullptr, 0, logits, nullptr, status, stream));
-  float* colsum = full_softmax ? f.colsum : nullptr;
-  if (colsum) STEP(zero_words(colsum, n_experts, st));
   STEP(moe_b200_router_dispatch(logits, z.ld, logit_bias, noise, n_tokens, n_experts, top_k,
                                 n_shared, normalize, full_softmax, w_all, idx_all, colsum,
                                 sorted_ids, expert_ids, pad_offsets, counts_all, n_post_pad,
@@ -280,12 +352,7 @@ int moe_b200_block_fwd(const void* x, int64_t n_tokens, int32_t d_model, const v
                                 expert_ids, n_post_pad, 0, sorted_ids, w_all, z.m, z.ks, out,
                                 n_tokens, nullptr, status, stream));
   }
-  STEP(copy_words(counts_all, counts, n_experts, st));
-  if (full_softmax) {
-    STEP(moe_b200_balance_loss(colsum, counts_all, n_experts, n_tokens, aux_coef, aux, stream));
-  } else {
-    STEP(zero_words(aux, 1, st));
-  }
+  STEP(finish_fwd(counts_all, counts, colsum, n_experts, n_tokens, aux_coef, aux, st));
   if (n_launches) *n_launches = launched;
   return MOE_B200_OK;
 }
