@@ -77,11 +77,12 @@ inline int pad_router(const void* src, int64_t rows, int32_t cols, void* dst, in
 // The forward's last launch: the routed experts' counts for the caller and the balance loss
 // aux = coef * E * sum_e (counts[e] / sum counts) * (colsum[e] / T) -- the arithmetic of
 // moe_b200_balance_loss, same order -- or zero when the loss is off (colsum == nullptr). One warp.
+// It does not release its dependents early: when a backward follows in the same graph, letting
+// that backward's first kernel become resident under the down GEMM cost the step 2 us.
 __global__ void finish_fwd_kernel(const int32_t* __restrict__ counts_all,
                                   int32_t* __restrict__ counts, const float* __restrict__ colsum,
                                   int n_experts, int64_t n_tokens, float coef,
                                   float* __restrict__ aux) {
-  moe::pdl_trigger();
   moe::pdl_wait();
   const int lane = threadIdx.x;
   float dot = 0.f, tot = 0.f;
