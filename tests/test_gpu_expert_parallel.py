@@ -374,7 +374,9 @@ def _peer_allreduce_worker(rank, world, port, q):
             torch.cuda.synchronize()
             worst = max(worst, float((got.float() - want.float()).abs().max()))
         q.put((rank, worst, int(got.numel()), 0, 0))
-        dist.barrier()
+        q.close()
+        q.join_thread()   # os._exit below skips the queue's own flush: without this the result
+        dist.barrier()    # can be lost and the parent waits for a rank that has long finished
         torch.cuda.synchronize()
         os._exit(0)       # (symmetric-memory buffers: leave without tearing the group down)
     except Exception as exc:
