@@ -201,10 +201,10 @@ __global__ void __launch_bounds__(RF4_THREADS)
                          float* __restrict__ colsum, int tokens_per_block,
                          int32_t* __restrict__ block_hist, int32_t* __restrict__ sorted_ids,
                          int64_t l_cap, const ScatterArgs sc) {
-  // No early release of the next kernel when a scatter launch follows: with it the step was 4.5 us
-  // slower (the dispatch's scatter blocks, 512 threads each, became resident beside this kernel's
-  // blocks, which are short of issue slots as it is). A batch that one block routes, plans and
-  // scatters (decode) keeps it: there the launch chain is what counts.
+  // No early release of the next kernel when a scatter launch follows: with it the step measured
+  // 4.5 us slower (the likely reason: the dispatch's scatter blocks, 512 threads each, become
+  // resident beside this kernel's blocks, which are short of issue slots as it is). A batch that
+  // one block routes, plans and scatters (decode) keeps it: there the launch chain is what counts.
   if (sc.counts != nullptr) pdl_trigger();
   pdl_wait();
   static_assert(EPL % 8 == 0, "a lane loads its experts as 16-byte pieces");
